@@ -1,0 +1,502 @@
+// Persistent, warp-specialised bf16 GEMM for sm_100a:  C[M,N] (+)= A[M,K] * B[N,K]^T.
+//
+//   * 128x256 output tile per CTA, K step 64, UMMA 128x256x16 (tcgen05.mma, cta_group::1)
+//   * operands staged by TMA (tiled, 128-byte swizzle) through a 4-stage mbarrier ring
+//   * fp32 accumulators in TMEM, double buffered (2 x 256 columns) so the epilogue of
+//     tile i overlaps the main loop of tile i+1
+//   * epilogue: tcgen05.ld -> registers -> swizzled smem staging -> TMA store / reduce-add
+//
+// Operand layouts (row-major storage, `ld` in elements):
+//   A "K-major":  A[M][K]  (activations in the forward pass)       a_mn = 0
+//   A "MN-major": A[K][M]  (dY^T in the weight gradient)           a_mn = 1
+//   B "K-major":  B[N][K]  (nn.Linear weight [out,in] forward)     b_mn = 0
+//   B "MN-major": B[K][N]  (weight [out,in] in dX = dY W, X in dW) b_mn = 1
+//
+// Epilogues: plain store (bf16 / fp32, optional bias, optional accumulate through TMA
+// reduce-add), cut-cross-entropy statistics (online max / sum-exp / target logit per row,
+// logits never leave the SM), and cut-cross-entropy dlogits ((softmax - onehot) * coef).
+//
+// The B operand may be a buffer that other CTAs (the all-gather pull of the FSDP path)
+// are still filling: with `b_flags` set, the producer acquires one flag per `b_flag_rows`
+// rows of B before issuing the TMA load of a tile (bounded wait).
+//
+// Counterpart in the reference: XLA dot_general behind `linear`
+// (src/causal_trainer/modeling/architecture.py:186-202) and the Pallas cut-CE kernels
+// (src/causal_trainer/kernels/cut_cross_entropy.py:85-156, 225-278).
+#include "gemm.h"
+
+#include <algorithm>
+
+namespace ctb {
+namespace gemm {
+
+constexpr int BM = 128;
+constexpr int BN = 256;
+constexpr int BK = 64;
+constexpr int NSTAGE = 4;
+constexpr int A_STAGE = BM * BK * 2;   // 16 KiB
+constexpr int B_STAGE = BN * BK * 2;   // 32 KiB
+constexpr int EPI_BUF = 128 * 128;     // 128 rows x 128 B
+constexpr int OFF_B = NSTAGE * A_STAGE;
+constexpr int OFF_EPI = OFF_B + NSTAGE * B_STAGE;
+constexpr int OFF_BAR = OFF_EPI + 2 * EPI_BUF;
+constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;  // + barrier block + alignment slack
+constexpr int NTHREADS = 256;
+constexpr int GROUP_M = 16;
+
+enum : unsigned {
+  SITE_PRODUCER_EMPTY = 0x0101,
+  SITE_MMA_FULL = 0x0102,
+  SITE_MMA_TEMPTY = 0x0103,
+  SITE_EPI_TFULL = 0x0104,
+  SITE_PRODUCER_FLAG = 0x0105,
+  SITE_DRAIN = 0x0106,
+};
+
+struct TileCoord {
+  int m0, n0;
+};
+
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) {
+  const int per_group = GROUP_M * num_n;
+  const int group = tile / per_group;
+  const int first_m = group * GROUP_M;
+  const int rows = min(GROUP_M, num_m - first_m);
+  const int local = tile - group * per_group;
+  TileCoord c;
+  c.m0 = (first_m + local % rows) * BM;
+  c.n0 = (local / rows) * BN;
+  return c;
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(NTHREADS, 1)
+gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
+            const __grid_constant__ CUtensorMap map_c, const GemmArgs args) {
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+  uint64_t* empty = full + NSTAGE;
+  uint64_t* tfull = empty + NSTAGE;
+  uint64_t* tempty = tfull + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tempty + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int num_m = (args.M + BM - 1) / BM;
+  const int num_n = (args.N + BN - 1) / BN;
+  const int num_k = (args.K + BK - 1) / BK;
+  const int total = num_m * num_n;
+  DeviceStatus* st = args.status;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < NSTAGE; ++s) {
+      mbar_init(&full[s], 1);
+      mbar_init(&empty[s], 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(&tfull[a], 1);
+      mbar_init(&tempty[a], 4);
+    }
+    *abort_flag = 0u;
+    mbar_fence_init();
+  }
+  if (warp == 3 && lane == 0) {
+    tma_prefetch_desc(&map_a);
+    tma_prefetch_desc(&map_b);
+    if (EPI != EPI_CE_STATS) tma_prefetch_desc(&map_c);
+  }
+  if (warp == 2) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ------------------------------ TMA producer ------------------------------
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      uint32_t armed = 0;      // bit s set: full[s] was armed by this thread at least once
+      uint32_t armed_par = 0;  // bit s: parity of the phase last armed on full[s]
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+        const TileCoord tc = tile_coord(tile, num_m, num_n);
+        if (args.b_flags != nullptr) {
+          // Rows [n0, n0+BN) of B must have landed in this GPU's memory.
+          const int first = tc.n0 / args.b_flag_rows;
+          const int last = (min(tc.n0 + BN, args.N) - 1) / args.b_flag_rows;
+          for (int f = first; ok && f <= last; ++f) {
+            const long long t0 = clock64();
+            while (true) {
+              unsigned v;
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(args.b_flags + f) : "memory");
+              if (v >= args.b_flag_epoch) break;
+              if (*abort_flag || clock64() - t0 > args.spin_budget) {
+                *abort_flag = 1u;
+                report_failure(st, SITE_PRODUCER_FLAG, static_cast<unsigned>(f), args.b_flag_epoch);
+                ok = false;
+                break;
+              }
+              __nanosleep(64);
+            }
+          }
+          if (!ok) break;
+          fence_proxy_async_all();  // generic-proxy writes of the pull CTAs -> async-proxy reads below
+        }
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, st, SITE_PRODUCER_EMPTY, args.spin_budget)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full[stage], A_STAGE + B_STAGE);
+          armed |= 1u << stage;
+          armed_par = (armed_par & ~(1u << stage)) | (phase << stage);
+          uint8_t* sa = smem + stage * A_STAGE;
+          uint8_t* sb = smem + OFF_B + stage * B_STAGE;
+          const int k0 = kb * BK;
+          if (A_MN) {
+#pragma unroll
+            for (int a = 0; a < BM / 64; ++a) tma_load_2d(sa + a * 8192, &map_a, &full[stage], tc.m0 + a * 64, k0);
+          } else {
+            tma_load_2d(sa, &map_a, &full[stage], k0, tc.m0);
+          }
+          if (B_MN) {
+#pragma unroll
+            for (int a = 0; a < BN / 64; ++a) tma_load_2d(sb + a * 8192, &map_b, &full[stage], tc.n0 + a * 64, k0);
+          } else {
+            tma_load_2d(sb, &map_b, &full[stage], k0, tc.n0);
+          }
+          if (++stage == NSTAGE) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+      if (!ok || *abort_flag) {
+        // Leave no copy of ours in flight: wait (bounded) until the last phase armed on
+        // each stage has completed, i.e. its TMA bytes have landed.
+        for (int s = 0; s < NSTAGE; ++s) {
+          if (!(armed & (1u << s))) continue;
+          const uint32_t par = (armed_par >> s) & 1u;
+          const long long t0 = clock64();
+          while (!mbar_try_wait(&full[s], par)) {
+            if (clock64() - t0 > 20000000ll) {
+              report_failure(st, SITE_DRAIN, static_cast<unsigned>(s), par);
+              break;
+            }
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0) {
+      constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
+      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+        if (!mbar_wait(&tempty[acc], acc_phase ^ 1u, abort_flag, st, SITE_MMA_TEMPTY, args.spin_budget)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_k; ++kb) {
+          if (!mbar_wait(&full[stage], phase, abort_flag, st, SITE_MMA_FULL, args.spin_budget)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(smem + stage * A_STAGE);
+          const uint32_t sb = smem_u32(smem + OFF_B + stage * B_STAGE);
+#pragma unroll
+          for (int k = 0; k < BK / 16; ++k) {
+            const uint64_t da = A_MN ? desc_mnmajor(sa, k, 8192) : desc_kmajor(sa, k);
+            const uint64_t db = B_MN ? desc_mnmajor(sb, k, 8192) : desc_kmajor(sb, k);
+            umma_bf16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&empty[stage]);
+          if (++stage == NSTAGE) {
+            stage = 0;
+            phase ^= 1u;
+          }
+        }
+        if (!ok) break;
+        umma_commit(&tfull[acc]);
+        acc ^= 1u;
+        if (acc == 0) acc_phase ^= 1u;
+      }
+    }
+  } else if (warp >= 4) {
+    // ------------------------------ epilogue (4 warps, 128 TMEM lanes) ------------------------------
+    const int q = warp & 3;                 // TMEM lane quadrant of this warp
+    const int row = q * 32 + lane;          // row of the tile owned by this thread
+    const int etid = threadIdx.x - 128;
+    uint32_t acc = 0, acc_phase = 0, buf_idx = 0;
+    uint8_t* epi = smem + OFF_EPI;
+    for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
+      const TileCoord tc = tile_coord(tile, num_m, num_n);
+      // The four epilogue warps decide together: a thread that gave up must not leave
+      // the others waiting at the staging barriers below.
+      const bool got = mbar_wait(&tfull[acc], acc_phase, abort_flag, st, SITE_EPI_TFULL, args.spin_budget);
+      if (named_bar_or(2, 128, !got)) break;
+      tc_fence_after();
+      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
+      const int grow = tc.m0 + row;
+
+      if (EPI == EPI_CE_STATS) {
+        // Online softmax statistics of this 256-column slab for one row per thread.
+        const int target = (grow < args.M) ? args.ce_targets[grow] : -1;
+        float vmax = -INFINITY, vsum = 0.f, tlogit = 0.f;
+        bool has_target = false;
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = tc.n0 + c * 32;
+          if (col0 >= args.N) break;
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          float cmax = -INFINITY;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const float v = (col0 + j < args.N) ? __uint_as_float(r[j]) : -INFINITY;
+            r[j] = __float_as_uint(v);
+            cmax = fmaxf(cmax, v);
+            if (col0 + j == target) {
+              tlogit = v;
+              has_target = true;
+            }
+          }
+          const float nmax = fmaxf(vmax, cmax);
+          float s = 0.f;
+#pragma unroll
+          for (int j = 0; j < 32; ++j) s += __expf(__uint_as_float(r[j]) - nmax);
+          vsum = vsum * __expf(vmax - nmax) + s;
+          vmax = nmax;
+        }
+        if (grow < args.M) {
+          const int slab = tc.n0 / BN;
+          args.ce_max[static_cast<size_t>(slab) * args.M + grow] = vmax;
+          args.ce_sum[static_cast<size_t>(slab) * args.M + grow] = vsum;
+          if (has_target) args.ce_target_logit[grow] = tlogit;
+        }
+      } else if (args.out_f32) {
+#pragma unroll 1
+        for (int c = 0; c < BN / 32; ++c) {
+          const int col0 = tc.n0 + c * 32;
+          if (col0 >= args.N) break;
+          uint32_t r[32];
+          tmem_ld32(taddr + c * 32, r);
+          tmem_ld_wait();
+          uint8_t* buf = epi + (buf_idx & 1u) * EPI_BUF;
+          if (etid == 0) tma_wait_group_read<1>();
+          named_bar_sync(1, 128);
+#pragma unroll
+          for (int j = 0; j < 8; ++j) {
+            float4 v;
+            v.x = __uint_as_float(r[4 * j + 0]) * args.alpha;
+            v.y = __uint_as_float(r[4 * j + 1]) * args.alpha;
+            v.z = __uint_as_float(r[4 * j + 2]) * args.alpha;
+            v.w = __uint_as_float(r[4 * j + 3]) * args.alpha;
+            *reinterpret_cast<float4*>(buf + sw128_offset(row, j)) = v;
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(1, 128);
+          if (etid == 0) {
+            if (args.accumulate) tma_reduce_add_2d(&map_c, buf, col0, tc.m0);
+            else tma_store_2d(&map_c, buf, col0, tc.m0);
+            tma_commit_group();
+          }
+          ++buf_idx;
+        }
+      } else {
+        float lse = 0.f, coef = 0.f;
+        int target = -1;
+        if (EPI == EPI_CE_DLOGITS && grow < args.M) {
+          lse = args.ce_lse[grow];
+          coef = args.ce_coef[grow];
+          target = args.ce_targets[grow];
+        }
+#pragma unroll 1
+        for (int c = 0; c < BN / 64; ++c) {
+          const int col0 = tc.n0 + c * 64;
+          if (col0 >= args.N) break;
+          uint32_t r0[32], r1[32];
+          tmem_ld32(taddr + c * 64, r0);
+          tmem_ld32(taddr + c * 64 + 32, r1);
+          tmem_ld_wait();
+          if (EPI == EPI_CE_DLOGITS) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              float p0 = __expf(__uint_as_float(r0[j]) - lse);
+              float p1 = __expf(__uint_as_float(r1[j]) - lse);
+              if (col0 + j == target) p0 -= 1.f;
+              if (col0 + 32 + j == target) p1 -= 1.f;
+              r0[j] = __float_as_uint(p0 * coef);
+              r1[j] = __float_as_uint(p1 * coef);
+            }
+          } else if (args.bias != nullptr) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const float b0 = (col0 + j < args.N) ? __bfloat162float(args.bias[col0 + j]) : 0.f;
+              const float b1 = (col0 + 32 + j < args.N) ? __bfloat162float(args.bias[col0 + 32 + j]) : 0.f;
+              r0[j] = __float_as_uint(__uint_as_float(r0[j]) + b0);
+              r1[j] = __float_as_uint(__uint_as_float(r1[j]) + b1);
+            }
+          }
+          if (args.alpha != 1.f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              r0[j] = __float_as_uint(__uint_as_float(r0[j]) * args.alpha);
+              r1[j] = __float_as_uint(__uint_as_float(r1[j]) * args.alpha);
+            }
+          }
+          uint8_t* buf = epi + (buf_idx & 1u) * EPI_BUF;
+          if (etid == 0) tma_wait_group_read<1>();
+          named_bar_sync(1, 128);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
+            v.y = pack_bf16(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
+            v.z = pack_bf16(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
+            v.w = pack_bf16(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
+            *reinterpret_cast<uint4*>(buf + sw128_offset(row, j)) = v;
+          }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            uint4 v;
+            v.x = pack_bf16(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
+            v.y = pack_bf16(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
+            v.z = pack_bf16(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
+            v.w = pack_bf16(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
+            *reinterpret_cast<uint4*>(buf + sw128_offset(row, 4 + j)) = v;
+          }
+          fence_proxy_async_smem();
+          named_bar_sync(1, 128);
+          if (etid == 0) {
+            if (args.accumulate) tma_reduce_add_2d(&map_c, buf, col0, tc.m0);
+            else tma_store_2d(&map_c, buf, col0, tc.m0);
+            tma_commit_group();
+          }
+          ++buf_idx;
+        }
+      }
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&tempty[acc]);
+      acc ^= 1u;
+      if (acc == 0) acc_phase ^= 1u;
+    }
+    if (etid == 0) tma_wait_group<0>();
+  }
+
+  // ------------------------------ teardown ------------------------------
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 2) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <bool A_MN, bool B_MN, int EPI>
+int launch(const CUtensorMap* ma, const CUtensorMap* mb, const CUtensorMap* mc, const GemmArgs& args, int grid,
+           cudaStream_t stream) {
+  auto kern = gemm_kernel<A_MN, B_MN, EPI>;
+  static bool configured = false;  // per instantiation; the attribute is per function, all devices of the context
+  static int configured_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (!configured || configured_dev != dev) {
+    CTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
+    configured = true;
+    configured_dev = dev;
+  }
+  kern<<<grid, NTHREADS, SMEM_BYTES, stream>>>(*ma, *mb, *mc, args);
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace gemm
+
+int run_gemm(const GemmCall& c) {
+  using namespace gemm;
+  if (c.M <= 0 || c.N <= 0 || c.K <= 0) return fail("gemm: M, N, K must be positive");
+  if ((c.lda % 8) || (c.ldb % 8)) return fail("gemm: lda and ldb must be multiples of 8 elements (16 bytes)");
+  const bool needs_c = (c.epi != EPI_CE_STATS);
+  if (needs_c && (c.ldc % (c.out_f32 ? 4 : 8))) return fail("gemm: ldc must be a multiple of 16 bytes");
+  const CUtensorMap* ma = c.a_mn ? get_tensor_map_2d(c.A, Elt::BF16, c.M, c.K, c.lda, 64, 64, true)
+                                 : get_tensor_map_2d(c.A, Elt::BF16, c.K, c.M, c.lda, 64, BM, true);
+  if (!ma) return 1;
+  const CUtensorMap* mb = c.b_mn ? get_tensor_map_2d(c.B, Elt::BF16, c.N, c.K, c.ldb, 64, 64, true)
+                                 : get_tensor_map_2d(c.B, Elt::BF16, c.K, c.N, c.ldb, 64, BN, true);
+  if (!mb) return 1;
+  const CUtensorMap* mc = ma;  // placeholder when no C tensor is written
+  if (needs_c) {
+    mc = c.out_f32 ? get_tensor_map_2d(c.C, Elt::F32, c.N, c.M, c.ldc, 32, 128, true)
+                   : get_tensor_map_2d(c.C, Elt::BF16, c.N, c.M, c.ldc, 64, 128, true);
+    if (!mc) return 1;
+  }
+  GemmArgs a{};
+  a.M = c.M;
+  a.N = c.N;
+  a.K = c.K;
+  a.out_f32 = c.out_f32;
+  a.accumulate = c.accumulate;
+  a.alpha = c.alpha;
+  a.bias = static_cast<const __nv_bfloat16*>(c.bias);
+  a.status = device_status();
+  a.spin_budget = c.spin_budget > 0 ? c.spin_budget : CTB_SPIN_BUDGET;
+  a.b_flags = c.b_flags;
+  a.b_flag_rows = c.b_flag_rows > 0 ? c.b_flag_rows : 1;
+  a.b_flag_epoch = c.b_flag_epoch;
+  a.ce_targets = c.ce_targets;
+  a.ce_max = c.ce_max;
+  a.ce_sum = c.ce_sum;
+  a.ce_target_logit = c.ce_target_logit;
+  a.ce_lse = c.ce_lse;
+  a.ce_coef = c.ce_coef;
+  const int tiles = ((c.M + BM - 1) / BM) * ((c.N + BN - 1) / BN);
+  int grid = std::min(tiles, c.max_ctas > 0 ? c.max_ctas : sm_count());
+  cudaStream_t s = static_cast<cudaStream_t>(c.stream);
+#define CTB_DISPATCH(AM, BMN)                                                         \
+  switch (c.epi) {                                                                    \
+    case EPI_STORE: return launch<AM, BMN, EPI_STORE>(ma, mb, mc, a, grid, s);        \
+    case EPI_CE_STATS: return launch<AM, BMN, EPI_CE_STATS>(ma, mb, mc, a, grid, s);  \
+    case EPI_CE_DLOGITS: return launch<AM, BMN, EPI_CE_DLOGITS>(ma, mb, mc, a, grid, s); \
+    default: return fail("gemm: unknown epilogue");                                   \
+  }
+  if (!c.a_mn && !c.b_mn) { CTB_DISPATCH(false, false) }
+  if (!c.a_mn && c.b_mn) { CTB_DISPATCH(false, true) }
+  if (c.a_mn && c.b_mn) { CTB_DISPATCH(true, true) }
+  CTB_DISPATCH(true, false)
+#undef CTB_DISPATCH
+}
+
+}  // namespace ctb
+
+// C ABI ------------------------------------------------------------------------------------
+// C[M,N] = alpha * A*B^T (+ bias) ; see the layout table at the top of this file.
+CTB_API int ctb_gemm(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
+                     int a_mn, int b_mn, int out_f32, int accumulate, float alpha, const void* bias, int max_ctas,
+                     void* stream) {
+  ctb::GemmCall c{};
+  c.A = A; c.B = B; c.C = C; c.M = M; c.N = N; c.K = K; c.lda = lda; c.ldb = ldb; c.ldc = ldc;
+  c.a_mn = a_mn; c.b_mn = b_mn; c.out_f32 = out_f32; c.accumulate = accumulate; c.alpha = alpha; c.bias = bias;
+  c.epi = ctb::EPI_STORE; c.max_ctas = max_ctas; c.stream = stream;
+  return ctb::run_gemm(c);
+}
+
+// Same GEMM whose B rows are published by another kernel: flags[i] >= epoch means rows
+// [i*flag_rows, (i+1)*flag_rows) of B are complete in local memory.
+CTB_API int ctb_gemm_flagged(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
+                             const void* bias, const unsigned* flags, int flag_rows, unsigned epoch,
+                             long long spin_budget, int max_ctas, void* stream) {
+  ctb::GemmCall c{};
+  c.A = A; c.B = B; c.C = C; c.M = M; c.N = N; c.K = K; c.lda = lda; c.ldb = ldb; c.ldc = ldc;
+  c.alpha = 1.f; c.bias = bias; c.epi = ctb::EPI_STORE; c.max_ctas = max_ctas; c.stream = stream;
+  c.b_flags = flags; c.b_flag_rows = flag_rows; c.b_flag_epoch = epoch; c.spin_budget = spin_budget;
+  return ctb::run_gemm(c);
+}

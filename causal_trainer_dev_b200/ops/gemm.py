@@ -1,0 +1,77 @@
+"""Python face of the tcgen05 GEMM family (``csrc/gemm.cu``).
+
+``gemm(a, b)`` computes ``C[M,N] = alpha * A @ B^T (+ bias)`` for bf16 operands with
+fp32 accumulation.  ``a_mn`` / ``b_mn`` say that the tensor passed holds the transpose
+(``[K,M]`` / ``[K,N]`` row-major), which is how dgrad and wgrad read weights and
+activations in place, without a transpose pass.
+
+Reference counterpart: ``linear`` (src/causal_trainer/modeling/architecture.py:186-202),
+whose three matmuls per projection XLA derives from one ``dot_general``.
+"""
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import lib as _lib
+
+
+def _check_operand(t: torch.Tensor, name: str) -> None:
+    if t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1 or not t.is_cuda:
+        raise ValueError(f"{name} must be a 2-D bf16 CUDA tensor with unit inner stride")
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    out: torch.Tensor | None = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    accumulate: bool = False,
+    alpha: float = 1.0,
+    bias: torch.Tensor | None = None,
+    max_ctas: int = 0,
+) -> torch.Tensor:
+    _check_operand(a, "a")
+    _check_operand(b, "b")
+    m, k = (a.shape[1], a.shape[0]) if a_mn else (a.shape[0], a.shape[1])
+    n, kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if k != kb:
+        raise ValueError(f"inner dimensions differ: {k} vs {kb}")
+    if out is None:
+        if accumulate:
+            raise ValueError("accumulate=True needs an existing `out`")
+        out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    if out.shape != (m, n) or out.stride(1) != 1 or out.dtype not in (torch.bfloat16, torch.float32):
+        raise ValueError("out must be [M,N] bf16/fp32 with unit inner stride")
+    if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != n):
+        raise ValueError("bias must be bf16 of length N")
+    code = _lib.lib().ctb_gemm(
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), m, n, k,
+        ctypes.c_long(a.stride(0)), ctypes.c_long(b.stride(0)), ctypes.c_long(out.stride(0)),
+        int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), ctypes.c_float(alpha),
+        _lib.ptr(bias), max_ctas, _lib.stream_ptr(),
+    )
+    _lib.check(code, "ctb_gemm")
+    return out
+
+
+def linear_forward(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``y[T,out] = x[T,in] @ w[out,in]^T (+ bias)``."""
+    return gemm(x, w, bias=bias)
+
+
+def linear_dgrad(dy: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``dx[T,in] = dy[T,out] @ w[out,in]`` reading ``w`` in place."""
+    return gemm(dy, w, b_mn=True)
+
+
+def linear_wgrad(
+    dy: torch.Tensor, x: torch.Tensor, out: torch.Tensor | None = None, accumulate: bool = False,
+    out_dtype: torch.dtype = torch.bfloat16,
+) -> torch.Tensor:
+    """``dw[out,in] (+)= dy[T,out]^T @ x[T,in]`` reading both in place."""
+    return gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=accumulate, out_dtype=out_dtype)

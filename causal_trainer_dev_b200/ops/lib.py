@@ -1,0 +1,82 @@
+"""ctypes loader of the in-tree CUDA library and the error/status plumbing.
+
+The library is built by :func:`causal_trainer_dev_b200.ops.build.build`.  On a machine
+with a GPU a missing library is an error (ops never fall back silently to PyTorch
+math); on a CPU-only host ``available()`` is False and callers use the PyTorch oracle.
+"""
+from __future__ import annotations
+
+import ctypes
+from functools import lru_cache
+
+import torch
+
+from .build import LIB_PATH
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments, a CUDA call failed, or a bounded wait ran out."""
+
+
+@lru_cache(maxsize=1)
+def _load() -> ctypes.CDLL | None:
+    if not LIB_PATH.exists():
+        return None
+    lib = ctypes.CDLL(str(LIB_PATH))
+    lib.ctb_last_error.restype = ctypes.c_char_p
+    return lib
+
+
+def available() -> bool:
+    """True when the CUDA library is built and a GPU is present."""
+    return torch.cuda.is_available() and _load() is not None
+
+
+def lib() -> ctypes.CDLL:
+    handle = _load()
+    if handle is None:
+        raise KernelError(
+            f"{LIB_PATH} is missing: run `python -m causal_trainer_dev_b200.ops.build` (nvcc, no GPU needed)"
+        )
+    return handle
+
+
+def require_gpu_lib() -> None:
+    """Fails loudly when a GPU is present but the native library is not."""
+    if torch.cuda.is_available():
+        lib()
+
+
+def check(code: int, what: str) -> None:
+    if code != 0:
+        raise KernelError(f"{what}: {lib().ctb_last_error().decode()}")
+
+
+def stream_ptr() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+_SITES = {
+    0x0101: "gemm producer: stage never freed",
+    0x0102: "gemm mma: operands never arrived",
+    0x0103: "gemm mma: accumulator never drained",
+    0x0104: "gemm epilogue: accumulator never completed",
+    0x0105: "gemm producer: B-ready flag never published",
+    0x0106: "gemm producer: copy still in flight at teardown",
+}
+
+
+def device_status(raise_on_error: bool = True) -> tuple[int, int, int, int]:
+    """Reads (and clears) the device status word written by bounded waits that gave up."""
+    out = (ctypes.c_uint * 4)()
+    check(lib().ctb_status(out, stream_ptr()), "ctb_status")
+    code, block, d0, d1 = (int(x) for x in out)
+    if code and raise_on_error:
+        raise KernelError(
+            f"device wait ran out: {_SITES.get(code, hex(code))} (block {block}, detail {d0}, {d1})"
+        )
+    return code, block, d0, d1

@@ -1,0 +1,56 @@
+"""tcgen05 GEMM family against an fp32 PyTorch matmul of the same operands."""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-9)).item()
+
+
+@pytest.mark.parametrize("a_mn", [False, True])
+@pytest.mark.parametrize("b_mn", [False, True])
+@pytest.mark.parametrize("shape", [(128, 256, 64), (256, 512, 256), (200, 328, 136), (1000, 520, 72)])
+def test_layouts(cuda_lib, a_mn, b_mn, shape):
+    from causal_trainer_dev_b200.ops import gemm as G
+
+    m, n, k = shape
+    torch.manual_seed(1)
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    b = torch.randn(n, k, device="cuda").bfloat16()
+    ref = a.float() @ b.float().t()
+    out = G.gemm(a.t().contiguous() if a_mn else a, b.t().contiguous() if b_mn else b, a_mn=a_mn, b_mn=b_mn)
+    assert _rel(out, ref) < 4e-3
+    assert cuda_lib.device_status() == (0, 0, 0, 0)
+
+
+def test_fp32_out_accumulate_bias_alpha(cuda_lib):
+    from causal_trainer_dev_b200.ops import gemm as G
+
+    torch.manual_seed(2)
+    a = torch.randn(384, 192, device="cuda").bfloat16()
+    b = torch.randn(520, 192, device="cuda").bfloat16()
+    ref = a.float() @ b.float().t()
+    out = G.gemm(a, b, out_dtype=torch.float32)
+    assert _rel(out, ref) < 1e-5
+    acc = torch.randn(384, 520, device="cuda")
+    expect = acc + 0.5 * ref
+    G.gemm(a, b, out=acc, accumulate=True, alpha=0.5)
+    assert _rel(acc, expect) < 1e-5
+    bias = torch.randn(520, device="cuda").bfloat16()
+    out = G.gemm(a, b, bias=bias)
+    assert _rel(out, ref + bias.float()) < 4e-3
+    assert cuda_lib.device_status() == (0, 0, 0, 0)
+
+
+def test_linear_triplet_matches_autograd(cuda_lib):
+    from causal_trainer_dev_b200.ops import gemm as G
+
+    torch.manual_seed(3)
+    x = torch.randn(640, 256, device="cuda").bfloat16()
+    w = torch.randn(384, 256, device="cuda").bfloat16()
+    dy = torch.randn(640, 384, device="cuda").bfloat16()
+    assert _rel(G.linear_forward(x, w), x.float() @ w.float().t()) < 4e-3
+    assert _rel(G.linear_dgrad(dy, w), dy.float() @ w.float()) < 4e-3
+    assert _rel(G.linear_wgrad(dy, x), dy.float().t() @ x.float()) < 4e-3
