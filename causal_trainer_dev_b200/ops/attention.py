@@ -1,0 +1,160 @@
+"""Segment-masked flash attention: visibility metadata, the sm_100a kernels and the oracle.
+
+Visibility rule (shared by every backend):
+
+    key j is visible to query i  <=>  seg[j] == seg[i] != 0  and  j <= max(i, attention_end[i])
+
+``seg`` holds canonical run ids (0 = padding) and ``attention_end`` is the optional
+inclusive end index that gives MaskGIT image blocks block-local bidirectional attention.
+Rows that see no key produce a zero output and zero gradients.
+
+Reference counterparts: ``vanilla_attention`` (src/causal_trainer/modeling/attention.py:100-148),
+``efficient_attention`` and its block summaries
+(src/causal_trainer/kernels/efficient_attention.py:313-412, 1890-1960).
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import lib as _lib
+
+BLOCK = 128
+
+
+@dataclass
+class AttentionMeta:
+    """Per-step visibility metadata, built once and reused by every layer."""
+
+    seg: torch.Tensor            # [B,S] int32 canonical segment ids
+    lim: torch.Tensor | None     # [B,S] int32 inclusive last visible key (None: plain causal)
+    kv_lo: torch.Tensor          # [B,S/128] int32
+    kv_hi: torch.Tensor          # [B,S/128] int32
+    kmin: torch.Tensor           # [B,S/128] int32
+    kmax: torch.Tensor           # [B,S/128] int32
+    q_lo: torch.Tensor           # [B,S/128] int32 first query that sees the key block
+    q_hi: torch.Tensor           # [B,S/128] int32 one past the last such query
+
+    @property
+    def batch(self) -> int:
+        return self.seg.shape[0]
+
+    @property
+    def seq(self) -> int:
+        return self.seg.shape[1]
+
+
+def build_attention_meta(segment_ids: torch.Tensor, attention_end: torch.Tensor | None = None) -> AttentionMeta:
+    """Builds block summaries from canonical segment ids (and MaskGIT ends).
+
+    ``segment_ids`` must already be canonical (contiguous runs numbered 1.., 0 for padding)
+    and ``S`` a multiple of 128.
+    """
+    seg = segment_ids.to(torch.int32).contiguous()
+    bsz, s = seg.shape
+    if s % BLOCK:
+        raise ValueError(f"sequence length {s} must be a multiple of {BLOCK}")
+    dev = seg.device
+    idx = torch.arange(s, device=dev, dtype=torch.int32).expand(bsz, s)
+    valid = seg != 0
+    big = torch.iinfo(torch.int32).max
+    prev = torch.cat([torch.zeros_like(seg[:, :1]), seg[:, :-1]], dim=1)
+    nxt = torch.cat([seg[:, 1:], torch.zeros_like(seg[:, :1])], dim=1)
+    starts = valid & (seg != prev)
+    ends = valid & (seg != nxt)
+    seg_start = torch.cummax(torch.where(starts, idx, torch.zeros_like(idx)), dim=1).values
+    rev_end = torch.where(ends, idx, torch.full_like(idx, big)).flip(1)
+    seg_end = torch.cummin(rev_end, dim=1).values.flip(1)  # inclusive last index of the run
+    if attention_end is None:
+        lim = None
+        lim_full = idx
+    else:
+        lim_full = torch.maximum(idx, attention_end.to(torch.int32))
+        lim_full = torch.minimum(lim_full, torch.where(valid, seg_end, idx)).contiguous()
+        lim = lim_full
+    nb = s // BLOCK
+
+    def blk(x):
+        return x.reshape(bsz, nb, BLOCK)
+
+    kv_lo = blk(torch.where(valid, seg_start, torch.full_like(idx, big))).amin(-1)
+    kv_hi = blk(torch.where(valid, lim_full + 1, torch.zeros_like(idx))).amax(-1)
+    kv_lo = torch.where(kv_hi > 0, kv_lo, torch.zeros_like(kv_lo))
+    kmin = blk(seg).amin(-1)
+    kmax = blk(seg).amax(-1)
+    # first query that sees key j: suffix-min over p >= j of min{i : lim[i] == p}
+    if attention_end is None:
+        first_q = idx
+    else:
+        m = torch.full((bsz, s), big, device=dev, dtype=torch.int32)
+        m = m.scatter_reduce(1, lim_full.long(), torch.where(valid, idx, torch.full_like(idx, big)), "amin")
+        first_q = torch.cummin(m.flip(1), dim=1).values.flip(1)
+        first_q = torch.minimum(first_q, idx)
+    q_lo = blk(torch.where(valid, first_q, torch.full_like(idx, big))).amin(-1)
+    q_hi = blk(torch.where(valid, seg_end + 1, torch.zeros_like(idx))).amax(-1)
+    q_lo = torch.where(q_hi > 0, q_lo, torch.zeros_like(q_lo))
+    i32 = lambda t: t.to(torch.int32).contiguous()  # noqa: E731
+    return AttentionMeta(seg, lim, i32(kv_lo), i32(kv_hi), i32(kmin), i32(kmax), i32(q_lo), i32(q_hi))
+
+
+def visibility_mask(segment_ids: torch.Tensor, attention_end: torch.Tensor | None = None) -> torch.Tensor:
+    """Dense [B,S,S] boolean mask of the visibility rule (oracle only)."""
+    seg = segment_ids
+    s = seg.shape[1]
+    idx = torch.arange(s, device=seg.device)
+    lim = idx.expand_as(seg) if attention_end is None else torch.maximum(idx.expand_as(seg), attention_end.long())
+    same = (seg[:, :, None] == seg[:, None, :]) & (seg[:, :, None] != 0)
+    return same & (idx[None, None, :] <= lim[:, :, None])
+
+
+def vanilla_attention(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, segment_ids: torch.Tensor,
+    attention_end: torch.Tensor | None = None, scale: float | None = None,
+) -> torch.Tensor:
+    """O(S^2) fp32-softmax oracle with GQA.  q [B,S,Hq,D]; k, v [B,S,Hkv,D]."""
+    b, s, hq, d = q.shape
+    hkv = k.shape[2]
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    g = hq // hkv
+    qf = q.float().view(b, s, hkv, g, d)
+    scores = torch.einsum("bqhgd,bkhd->bhgqk", qf, k.float()) * scale
+    mask = visibility_mask(segment_ids, attention_end)[:, None, None]
+    scores = scores.masked_fill(~mask, torch.finfo(torch.float32).min)
+    probs = torch.softmax(scores, dim=-1)
+    probs = torch.where(mask.any(-1, keepdim=True), probs, torch.zeros_like(probs))
+    probs = probs * mask
+    out = torch.einsum("bhgqk,bkhd->bqhgd", probs, v.float())
+    return out.reshape(b, s, hq, d).to(q.dtype)
+
+
+def _row_stride(t: torch.Tensor) -> int:
+    # [B,S,H,D] view: D contiguous, heads D apart, batches S rows apart.
+    b, s, h, d = t.shape
+    if t.stride(3) != 1 or t.stride(2) != d or (b > 1 and t.stride(0) != t.stride(1) * s):
+        raise ValueError("attention operands must be [B,S,H,D] views with contiguous heads")
+    return t.stride(1)
+
+
+def flash_attention_forward(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: AttentionMeta, scale: float | None = None,
+    out: torch.Tensor | None = None, spin_budget: int = 0,
+) -> tuple[torch.Tensor, torch.Tensor]:
+    """Runs the tcgen05 forward kernel; returns (O [B,S,Hq,D] bf16, LSE [B,Hq,S] fp32)."""
+    b, s, hq, d = q.shape
+    hkv = k.shape[2]
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    if out is None:
+        out = torch.empty((b, s, hq, d), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((b, hq, s), dtype=torch.float32, device=q.device)
+    code = _lib.lib().ctb_attn_fwd(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(meta.seg), _lib.ptr(meta.lim),
+        _lib.ptr(meta.kv_lo), _lib.ptr(meta.kv_hi), _lib.ptr(meta.kmin), _lib.ptr(meta.kmax),
+        b, s, hq, hkv, d, ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)),
+        ctypes.c_long(_row_stride(v)), ctypes.c_long(_row_stride(out)), ctypes.c_float(scale),
+        ctypes.c_longlong(spin_budget), _lib.stream_ptr(),
+    )
+    _lib.check(code, "ctb_attn_fwd")
+    return out, lse

@@ -1,0 +1,473 @@
+// Flash attention forward for sm_100a: segment-isolated causal attention with an optional
+// per-query inclusive visibility end (MaskGIT block-local bidirectional attention), GQA.
+//
+//   key j is visible to query i  <=>  seg[j] == seg[i] != 0  and  j <= max(i, attention_end[i])
+//
+// One CTA owns 256 consecutive query rows of one (batch, query head): two 128-row tiles
+// that ping-pong so the tensor core computes one tile's S = Q K^T / O += P V while the
+// other tile's softmax runs.
+//   warp 0      TMA producer (Q tiles once, then K(j), V(j) through a 3-slot ring)
+//   warp 1      TMEM allocation + single-thread tcgen05.mma issue   (warps 2-3 idle)
+//   warps 4-7   softmax of tile 0 (one query row per thread, TMEM lane = row)
+//   warps 8-11  softmax of tile 1
+// The softmax reads each score row from TMEM twice (maximum, then exponentials) instead of
+// holding 128 scores in registers.
+// S (fp32) and O (fp32) live in TMEM.  P is written as bf16 into a 128B-swizzled K-major
+// shared tile and consumed by the second MMA; V is consumed in place as an MN-major operand.
+// The running maximum is only raised when it grows by more than 2^8 (the O rescale in TMEM
+// is rare), the final O / l and LSE are written by the softmax warps.
+// KV blocks outside [kv_lo, kv_hi) of a query block are never visited (block skipping from
+// segment summaries); rows without any visible key produce O = 0 and LSE = 0.
+//
+// Reference counterpart: causal_trainer_attention_fwd
+// (src/causal_trainer/kernels/efficient_attention.py:560-771, 931-978).
+#include "attention.h"
+
+namespace ctb {
+namespace attn {
+
+constexpr int FWD_THREADS = 384;
+constexpr int KV_SLOTS = 3;
+
+enum : unsigned {
+  SITE_F_PROD = 0x0201,
+  SITE_F_MMA_Q = 0x0202,
+  SITE_F_MMA_KV = 0x0203,
+  SITE_F_MMA_P = 0x0204,
+  SITE_F_SM_S = 0x0205,
+  SITE_F_SM_PV = 0x0206,
+};
+
+template <int D>
+struct FwdSmem {
+  static constexpr int HALVES = D / 64;
+  static constexpr int QT = HALVES * 16384;        // one 128-row Q / K / V tile
+  static constexpr int PT = 2 * 16384;             // P tile: 128 rows x 128 keys bf16
+  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_KV = 2 * QT;
+  static constexpr int OFF_P = OFF_KV + KV_SLOTS * QT;
+  static constexpr int OFF_BAR = OFF_P + 2 * PT;
+  static constexpr int BYTES = OFF_BAR + 256 + 1024;
+};
+
+template <int D>
+__global__ void __launch_bounds__(FWD_THREADS, 1)
+attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_o,
+                const FwdArgs args) {
+  using L = FwdSmem<D>;
+  constexpr int HALVES = L::HALVES;
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* q_full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* kv_full = q_full + 1;
+  uint64_t* kv_empty = kv_full + KV_SLOTS;
+  uint64_t* s_full = kv_empty + KV_SLOTS;
+  uint64_t* p_full = s_full + 2;
+  uint64_t* pv_done = p_full + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  DeviceStatus* st = args.status;
+  const long long budget = args.spin_budget;
+
+  // ---- work item ----
+  const int nqp = (args.S + 255) / 256;
+  int idx = blockIdx.x;
+  const int h = idx % args.Hq;
+  idx /= args.Hq;
+  const int b = idx % args.B;
+  const int pair = nqp - 1 - idx / args.B;
+  const int q0 = pair * 256;
+  const int hkv = h / (args.Hq / args.Hkv);
+  const int nqb = args.S / 128;
+  bool tile_valid[2];
+  int lo_t[2], hi_t[2];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    tile_valid[t] = (q0 + t * 128) < args.S;
+    lo_t[t] = 0;
+    hi_t[t] = 0;
+    if (tile_valid[t]) {
+      const int qb = q0 / 128 + t;
+      const int lo_tok = args.kv_lo[b * nqb + qb];
+      const int hi_tok = args.kv_hi[b * nqb + qb];
+      if (hi_tok > lo_tok) {
+        lo_t[t] = lo_tok / 128;
+        hi_t[t] = (hi_tok + 127) / 128;
+      }
+    }
+  }
+  int lo = 0;
+  if (hi_t[0] > lo_t[0] && hi_t[1] > lo_t[1]) lo = min(lo_t[0], lo_t[1]);
+  else if (hi_t[0] > lo_t[0]) lo = lo_t[0];
+  else if (hi_t[1] > lo_t[1]) lo = lo_t[1];
+  const int n0 = (hi_t[0] > lo_t[0]) ? hi_t[0] - lo : 0;
+  const int n1 = (hi_t[1] > lo_t[1]) ? hi_t[1] - lo : 0;
+  const int nmax = max(n0, n1);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < KV_SLOTS; ++s) {
+      mbar_init(&kv_full[s], 1);
+      mbar_init(&kv_empty[s], 1);
+    }
+    for (int t = 0; t < 2; ++t) {
+      mbar_init(&s_full[t], 1);
+      mbar_init(&p_full[t], 128);
+      mbar_init(&pv_done[t], 1);
+    }
+    *abort_flag = 0u;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s[2] = {tmem_base, tmem_base + 128};
+  const uint32_t tmem_o[2] = {tmem_base + 256, tmem_base + 256 + D};
+
+  if (warp < 4) {
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0 && nmax > 0) {
+      uint32_t bytes = 0;
+      for (int t = 0; t < 2; ++t)
+        if (tile_valid[t]) bytes += L::QT;
+      mbar_expect_tx(q_full, bytes);
+      for (int t = 0; t < 2; ++t) {
+        if (!tile_valid[t]) continue;
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf)
+          tma_load_4d(smem + L::OFF_Q + t * L::QT + hf * 16384, &map_q, q_full, hf * 64, h, q0 + t * 128, b);
+      }
+      uint32_t slot = 0, phase = 0;
+      bool ok = true;
+      for (int i = 0; ok && i < nmax; ++i) {
+        const int k0 = (lo + i) * 128;
+#pragma unroll 1
+        for (int which = 0; which < 2; ++which) {
+          if (!mbar_wait(&kv_empty[slot], phase ^ 1u, abort_flag, st, SITE_F_PROD, budget)) {
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&kv_full[slot], L::QT);
+          uint8_t* dst = smem + L::OFF_KV + slot * L::QT;
+          const CUtensorMap* m = which == 0 ? &map_k : &map_v;
+#pragma unroll
+          for (int hf = 0; hf < HALVES; ++hf) tma_load_4d(dst + hf * 16384, m, &kv_full[slot], hf * 64, hkv, k0, b);
+          if (++slot == KV_SLOTS) {
+            slot = 0;
+            phase ^= 1u;
+          }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0 && nmax > 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 128, false, false);
+      constexpr uint32_t idesc_o = make_idesc_bf16(128, D, false, true);
+      const int n_t[2] = {n0, n1};
+      uint32_t slot = 0, phase = 0;
+      uint32_t pph[2] = {0, 0};
+      bool ok = mbar_wait(q_full, 0, abort_flag, st, SITE_F_MMA_Q, budget);
+      auto issue_s = [&](int t, uint32_t kslot) {
+        const uint32_t qa = smem_u32(smem + L::OFF_Q + t * L::QT);
+        const uint32_t ka = smem_u32(smem + L::OFF_KV + kslot * L::QT);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k) {
+          const uint64_t da = desc_kmajor(qa + (k / 4) * 16384, k % 4);
+          const uint64_t db = desc_kmajor(ka + (k / 4) * 16384, k % 4);
+          umma_bf16(tmem_s[t], da, db, idesc_s, k != 0 ? 1u : 0u);
+        }
+        umma_commit(&s_full[t]);
+      };
+      uint32_t kslot = 0;
+      if (ok) {
+        ok = mbar_wait(&kv_full[slot], phase, abort_flag, st, SITE_F_MMA_KV, budget);
+        if (ok) {
+          tc_fence_after();
+          kslot = slot;
+          if (++slot == KV_SLOTS) { slot = 0; phase ^= 1u; }
+          for (int t = 0; t < 2; ++t)
+            if (n_t[t] > 0) issue_s(t, kslot);
+          umma_commit(&kv_empty[kslot]);
+        }
+      }
+      for (int i = 0; ok && i < nmax; ++i) {
+        if (!mbar_wait(&kv_full[slot], phase, abort_flag, st, SITE_F_MMA_KV, budget)) break;
+        const uint32_t vslot = slot;
+        if (++slot == KV_SLOTS) { slot = 0; phase ^= 1u; }
+        const bool has_next = (i + 1 < nmax);
+        if (has_next) {
+          if (!mbar_wait(&kv_full[slot], phase, abort_flag, st, SITE_F_MMA_KV, budget)) break;
+          kslot = slot;
+          if (++slot == KV_SLOTS) { slot = 0; phase ^= 1u; }
+        }
+        tc_fence_after();
+        const uint32_t va = smem_u32(smem + L::OFF_KV + vslot * L::QT);
+        for (int t = 0; t < 2; ++t) {
+          if (i >= n_t[t]) continue;
+          if (!mbar_wait(&p_full[t], pph[t], abort_flag, st, SITE_F_MMA_P, budget)) {
+            ok = false;
+            break;
+          }
+          pph[t] ^= 1u;
+          tc_fence_after();
+          const uint32_t pa = smem_u32(smem + L::OFF_P + t * L::PT);
+#pragma unroll
+          for (int k = 0; k < 8; ++k) {
+            const uint64_t da = desc_kmajor(pa + (k / 4) * 16384, k % 4);
+            const uint64_t db = desc_mnmajor(va, k, 16384);
+            umma_bf16(tmem_o[t], da, db, idesc_o, (i | k) != 0 ? 1u : 0u);
+          }
+          umma_commit(&pv_done[t]);
+          if (i + 1 < n_t[t]) issue_s(t, kslot);
+        }
+        if (!ok) break;
+        umma_commit(&kv_empty[vslot]);
+        if (has_next) umma_commit(&kv_empty[kslot]);
+      }
+    }
+  }
+  } else {
+    // ------------------------------ softmax warpgroups ------------------------------
+    const int t = (warp - 4) >> 2;
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const int n_mine = t == 0 ? n0 : n1;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    uint8_t* pbuf = smem + L::OFF_P + t * L::PT;
+    bool ok = true;
+    float m_ref = -INFINITY, l_sum = 0.f;
+    const int qi = q0 + t * 128 + r;
+    int my_seg = 0, my_lim = qi;
+    if (tile_valid[t]) {
+      my_seg = args.seg[b * args.S + qi];
+      if (args.lim != nullptr) my_lim = args.lim[b * args.S + qi];
+    }
+    uint32_t sph = 0, dph = 0;
+    for (int i = 0; i < n_mine; ++i) {
+      const int j = lo + i;
+      const int k0 = j * 128;
+      if (!mbar_wait(&s_full[t], sph, abort_flag, st, SITE_F_SM_S, budget)) {
+        ok = false;
+        break;
+      }
+      sph ^= 1u;
+      tc_fence_after();
+      // ---- visibility class of this row for this key block ----
+      const int bmin = args.kmin[b * nqb + j];
+      const int bmax = args.kmax[b * nqb + j];
+      const bool none = (my_seg == 0) || (my_seg < bmin) || (my_seg > bmax) || (k0 > my_lim);
+      const bool all = (my_seg != 0) && (bmin == my_seg) && (bmax == my_seg) && (k0 + 127 <= my_lim);
+      const int4* sp = reinterpret_cast<const int4*>(args.seg + b * args.S + k0);
+      // Scales 32 scores of chunk c and applies the mask (-inf where the key is hidden).
+      auto load_chunk = [&](int c, float (&x)[32]) {
+        uint32_t rr[32];
+        tmem_ld32(tmem_s[t] + lane_off + c * 32, rr);
+        tmem_ld_wait();
+        if (none) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) x[e] = -INFINITY;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) x[e] = __uint_as_float(rr[e]) * args.scale_log2;
+          if (!all) {
+#pragma unroll
+            for (int e4 = 0; e4 < 8; ++e4) {
+              const int4 sk = __ldg(sp + c * 8 + e4);
+              const int kk = k0 + c * 32 + e4 * 4;
+              if (!(sk.x == my_seg && kk + 0 <= my_lim)) x[e4 * 4 + 0] = -INFINITY;
+              if (!(sk.y == my_seg && kk + 1 <= my_lim)) x[e4 * 4 + 1] = -INFINITY;
+              if (!(sk.z == my_seg && kk + 2 <= my_lim)) x[e4 * 4 + 2] = -INFINITY;
+              if (!(sk.w == my_seg && kk + 3 <= my_lim)) x[e4 * 4 + 3] = -INFINITY;
+            }
+          }
+        }
+      };
+      // pass 1: row maximum (scores are re-read from TMEM in pass 2 instead of being
+      // held in 128 registers)
+      float mx = -INFINITY;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float x[32];
+        load_chunk(c, x);
+#pragma unroll
+        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, x[e]);
+      }
+      // ---- lazy running maximum ----
+      const bool need = (mx > m_ref + 8.f) || (m_ref == -INFINITY && mx > -INFINITY);
+      float alpha = 1.f;
+      if (need) {
+        alpha = (m_ref == -INFINITY) ? 0.f : fast_exp2(m_ref - mx);
+        m_ref = mx;
+        l_sum *= alpha;
+      }
+      if (i > 0) {
+        // PV(i-1) must be complete before P is overwritten or O is rescaled.
+        if (!mbar_wait(&pv_done[t], dph, abort_flag, st, SITE_F_SM_PV, budget)) {
+          ok = false;
+          break;
+        }
+        dph ^= 1u;
+        if (__any_sync(0xffffffffu, need)) {
+          tc_fence_after();
+#pragma unroll 1
+          for (int c = 0; c < D / 32; ++c) {
+            uint32_t rr[32];
+            tmem_ld32(tmem_o[t] + lane_off + c * 32, rr);
+            tmem_ld_wait();
+#pragma unroll
+            for (int e = 0; e < 32; ++e) rr[e] = __float_as_uint(__uint_as_float(rr[e]) * alpha);
+            tmem_st32(tmem_o[t] + lane_off + c * 32, rr);
+          }
+          tmem_st_wait();
+        }
+      }
+      const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+      float rs = 0.f;
+#pragma unroll 1
+      for (int c = 0; c < 4; ++c) {
+        float x[32];
+        load_chunk(c, x);
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          float p[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) {
+            p[e] = fast_exp2(x[g * 8 + e] - m_use);
+            rs += p[e];
+          }
+          uint4 v;
+          v.x = pack_bf16(p[0], p[1]);
+          v.y = pack_bf16(p[2], p[3]);
+          v.z = pack_bf16(p[4], p[5]);
+          v.w = pack_bf16(p[6], p[7]);
+          const int chunk16 = c * 4 + g;  // 16-byte chunk index along the 128 keys
+          *reinterpret_cast<uint4*>(pbuf + (chunk16 / 8) * 16384 + sw128_offset(r, chunk16 % 8)) = v;
+        }
+      }
+      l_sum += rs;
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&p_full[t]);
+    }
+    // ---- finalize ----
+    if (ok && n_mine > 0) {
+      ok = mbar_wait(&pv_done[t], dph, abort_flag, st, SITE_F_SM_PV, budget);
+      tc_fence_after();
+    }
+    const bool any_bad = named_bar_or(2 + t, 128, !ok);
+    if (!any_bad && tile_valid[t]) {
+      const float inv = (l_sum > 0.f) ? 1.f / l_sum : 0.f;
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t rr[32];
+        if (n_mine > 0) {
+          tmem_ld32(tmem_o[t] + lane_off + c * 32, rr);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) rr[e] = 0u;
+        }
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          uint4 v;
+          v.x = pack_bf16(__uint_as_float(rr[jj * 8 + 0]) * inv, __uint_as_float(rr[jj * 8 + 1]) * inv);
+          v.y = pack_bf16(__uint_as_float(rr[jj * 8 + 2]) * inv, __uint_as_float(rr[jj * 8 + 3]) * inv);
+          v.z = pack_bf16(__uint_as_float(rr[jj * 8 + 4]) * inv, __uint_as_float(rr[jj * 8 + 5]) * inv);
+          v.w = pack_bf16(__uint_as_float(rr[jj * 8 + 6]) * inv, __uint_as_float(rr[jj * 8 + 7]) * inv);
+          *reinterpret_cast<uint4*>(pbuf + (c / 2) * 16384 + sw128_offset(r, (c % 2) * 4 + jj)) = v;
+        }
+      }
+      fence_proxy_async_smem();
+      named_bar_sync(4 + t, 128);
+      if (r == 0) {
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf) tma_store_4d(&map_o, pbuf + hf * 16384, hf * 64, h, q0 + t * 128, b);
+        tma_commit_group();
+        tma_wait_group<0>();
+      }
+      const float lse = (l_sum > 0.f) ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : 0.f;
+      args.lse[(static_cast<size_t>(b) * args.Hq + h) * args.S + qi] = lse;
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D>
+int launch_fwd(const FwdCall& c) {
+  using L = FwdSmem<D>;
+  const uint64_t dq[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.Hq), static_cast<uint64_t>(c.S),
+                          static_cast<uint64_t>(c.B)};
+  const uint64_t dk[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.Hkv), static_cast<uint64_t>(c.S),
+                          static_cast<uint64_t>(c.B)};
+  const uint32_t box[4] = {64, 1, 128, 1};
+  const uint64_t sq[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.q_row_stride),
+                          static_cast<uint64_t>(c.q_row_stride) * c.S};
+  const uint64_t sk[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.k_row_stride),
+                          static_cast<uint64_t>(c.k_row_stride) * c.S};
+  const uint64_t sv[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.v_row_stride),
+                          static_cast<uint64_t>(c.v_row_stride) * c.S};
+  const uint64_t so[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.o_row_stride),
+                          static_cast<uint64_t>(c.o_row_stride) * c.S};
+  const CUtensorMap* mq = get_tensor_map_4d(c.q, Elt::BF16, dq, sq, box, true);
+  const CUtensorMap* mk = get_tensor_map_4d(c.k, Elt::BF16, dk, sk, box, true);
+  const CUtensorMap* mv = get_tensor_map_4d(c.v, Elt::BF16, dk, sv, box, true);
+  const CUtensorMap* mo = get_tensor_map_4d(c.o, Elt::BF16, dq, so, box, true);
+  if (!mq || !mk || !mv || !mo) return 1;
+  FwdArgs a{};
+  a.B = c.B; a.S = c.S; a.Hq = c.Hq; a.Hkv = c.Hkv;
+  a.scale_log2 = c.scale * 1.4426950408889634f;
+  a.seg = c.seg; a.lim = c.lim; a.kv_lo = c.kv_lo; a.kv_hi = c.kv_hi; a.kmin = c.kmin; a.kmax = c.kmax;
+  a.lse = c.lse;
+  a.status = device_status();
+  a.spin_budget = c.spin_budget > 0 ? c.spin_budget : CTB_SPIN_BUDGET;
+  auto kern = attn_fwd_kernel<D>;
+  static int configured_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev != dev) {
+    CTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES));
+    configured_dev = dev;
+  }
+  const int grid = c.B * c.Hq * ((c.S + 255) / 256);
+  kern<<<grid, FWD_THREADS, L::BYTES, static_cast<cudaStream_t>(c.stream)>>>(*mq, *mk, *mv, *mo, a);
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace attn
+}  // namespace ctb
+
+// q/k/v/o are [B, S, H, D] views with arbitrary row stride (elements between consecutive
+// tokens), so the packed QKV projection output is read in place.  lse is [B, Hq, S] fp32.
+CTB_API int ctb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* seg,
+                         const int* lim, const int* kv_lo, const int* kv_hi, const int* kmin, const int* kmax, int B,
+                         int S, int Hq, int Hkv, int D, long q_row_stride, long k_row_stride, long v_row_stride,
+                         long o_row_stride, float scale, long long spin_budget, void* stream) {
+  if (S % 128) return ctb::fail("attention: sequence length must be a multiple of 128");
+  if (Hq % Hkv) return ctb::fail("attention: Hq must be a multiple of Hkv");
+  ctb::attn::FwdCall c{};
+  c.q = q; c.k = k; c.v = v; c.o = o; c.lse = lse; c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi;
+  c.kmin = kmin; c.kmax = kmax; c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
+  c.q_row_stride = q_row_stride; c.k_row_stride = k_row_stride; c.v_row_stride = v_row_stride;
+  c.o_row_stride = o_row_stride; c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
+  if (D == 128) return ctb::attn::launch_fwd<128>(c);
+  if (D == 64) return ctb::attn::launch_fwd<64>(c);
+  return ctb::fail("attention: head_dim must be 64 or 128");
+}

@@ -36,7 +36,7 @@ EncodeFn encode_fn() {
 }
 
 struct MapKey {
-  uint64_t v[12];
+  uint64_t v[16];
   bool operator==(const MapKey& o) const { return std::memcmp(v, o.v, sizeof(v)) == 0; }
 };
 struct MapKeyHash {
@@ -64,10 +64,10 @@ const CUtensorMap* lookup_or_encode(const MapKey& key, const void* base, Elt elt
     return nullptr;
   }
   const uint64_t esize = (elt == Elt::BF16) ? 2 : 4;
-  cuuint64_t gdims[3];
-  cuuint64_t gstrides[2];
-  cuuint32_t gbox[3];
-  cuuint32_t estr[3] = {1, 1, 1};
+  cuuint64_t gdims[4];
+  cuuint64_t gstrides[3];
+  cuuint32_t gbox[4];
+  cuuint32_t estr[4] = {1, 1, 1, 1};
   for (uint32_t i = 0; i < rank; ++i) {
     gdims[i] = dims[i];
     gbox[i] = box[i];
@@ -133,6 +133,20 @@ const CUtensorMap* get_tensor_map_3d(const void* base, Elt elt, uint64_t d0, uin
   uint64_t strides[2] = {s1, s2};
   uint32_t box[3] = {b0, b1, b2};
   return lookup_or_encode(key, base, elt, 3, dims, strides, box, swizzle128);
+}
+
+const CUtensorMap* get_tensor_map_4d(const void* base, Elt elt, const uint64_t dims[4], const uint64_t strides[3],
+                                     const uint32_t box[4], bool swizzle128) {
+  MapKey key{};
+  key.v[0] = reinterpret_cast<uint64_t>(base);
+  key.v[1] = static_cast<uint64_t>(elt) | (4ull << 8) | (swizzle128 ? 1ull << 16 : 0);
+  for (int i = 0; i < 4; ++i) key.v[2 + i] = dims[i];
+  for (int i = 0; i < 3; ++i) key.v[6 + i] = strides[i];
+  for (int i = 0; i < 4; ++i) key.v[9 + i] = box[i];
+  int dev = 0;
+  cudaGetDevice(&dev);
+  key.v[13] = static_cast<uint64_t>(dev);
+  return lookup_or_encode(key, base, elt, 4, dims, strides, box, swizzle128);
 }
 
 namespace {

@@ -38,6 +38,10 @@ const CUtensorMap* get_tensor_map_2d(const void* base, Elt elt, uint64_t inner, 
 const CUtensorMap* get_tensor_map_3d(const void* base, Elt elt, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t s1,
                                      uint64_t s2, uint32_t b0, uint32_t b1, uint32_t b2, bool swizzle128);
 
+// 4-D variant used by attention: dims {d0 (contiguous), d1, d2, d3}, element strides s1..s3.
+const CUtensorMap* get_tensor_map_4d(const void* base, Elt elt, const uint64_t dims[4], const uint64_t strides[3],
+                                     const uint32_t box[4], bool swizzle128);
+
 // Per-device status word in device memory (allocated on first use).
 DeviceStatus* device_status();
 
