@@ -37,6 +37,11 @@ class AttentionMeta:
     kmax: torch.Tensor           # [B,S/128] int32
     q_lo: torch.Tensor           # [B,S/128] int32 first query that sees the key block
     q_hi: torch.Tensor           # [B,S/128] int32 one past the last such query
+    seg_min64: torch.Tensor      # [B,S/64] int32
+    seg_max64: torch.Tensor      # [B,S/64] int32
+    lim_min64: torch.Tensor      # [B,S/64] int32
+    lim_max64: torch.Tensor      # [B,S/64] int32
+    attention_end: torch.Tensor | None = None  # kept for the oracle backend
 
     @property
     def batch(self) -> int:
@@ -97,7 +102,12 @@ def build_attention_meta(segment_ids: torch.Tensor, attention_end: torch.Tensor 
     q_hi = blk(torch.where(valid, seg_end + 1, torch.zeros_like(idx))).amax(-1)
     q_lo = torch.where(q_hi > 0, q_lo, torch.zeros_like(q_lo))
     i32 = lambda t: t.to(torch.int32).contiguous()  # noqa: E731
-    return AttentionMeta(seg, lim, i32(kv_lo), i32(kv_hi), i32(kmin), i32(kmax), i32(q_lo), i32(q_hi))
+    seg64 = seg.reshape(bsz, s // 64, 64)
+    lim64 = lim_full.reshape(bsz, s // 64, 64)
+    return AttentionMeta(
+        seg, lim, i32(kv_lo), i32(kv_hi), i32(kmin), i32(kmax), i32(q_lo), i32(q_hi),
+        i32(seg64.amin(-1)), i32(seg64.amax(-1)), i32(lim64.amin(-1)), i32(lim64.amax(-1)), attention_end,
+    )
 
 
 def visibility_mask(segment_ids: torch.Tensor, attention_end: torch.Tensor | None = None) -> torch.Tensor:
@@ -158,3 +168,54 @@ def flash_attention_forward(
     )
     _lib.check(code, "ctb_attn_fwd")
     return out, lse
+
+
+def flash_attention_backward(
+    q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, dout: torch.Tensor, lse: torch.Tensor,
+    meta: AttentionMeta, scale: float | None = None, spin_budget: int = 0,
+    dq: torch.Tensor | None = None, dk: torch.Tensor | None = None, dv: torch.Tensor | None = None,
+) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
+    """dQ (query-tile-owned kernel) and dK/dV (key-tile-owned kernel, group reduced in TMEM)."""
+    b, s, hq, d = q.shape
+    hkv = k.shape[2]
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    delta = (out.float() * dout.float()).sum(-1).permute(0, 2, 1).contiguous()  # [B,Hq,S]
+    dq = torch.empty((b, s, hq, d), dtype=torch.bfloat16, device=q.device) if dq is None else dq
+    dk = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dk is None else dk
+    dv = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dv is None else dv
+    L = _lib.lib()
+    for mode in (0, 1):
+        code = L.ctb_attn_bwd(
+            mode, _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
+            _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(meta.seg), _lib.ptr(meta.lim), _lib.ptr(meta.kv_lo),
+            _lib.ptr(meta.kv_hi), _lib.ptr(meta.q_lo), _lib.ptr(meta.q_hi), _lib.ptr(meta.seg_min64),
+            _lib.ptr(meta.seg_max64), _lib.ptr(meta.lim_min64), _lib.ptr(meta.lim_max64),
+            b, s, hq, hkv, d,
+            ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)), ctypes.c_long(_row_stride(v)),
+            ctypes.c_long(_row_stride(dout)), ctypes.c_long(_row_stride(dq)), ctypes.c_long(_row_stride(dk)),
+            ctypes.c_long(_row_stride(dv)), ctypes.c_float(scale), ctypes.c_longlong(spin_budget), _lib.stream_ptr(),
+        )
+        _lib.check(code, "ctb_attn_bwd")
+    return dq, dk, dv
+
+
+class _FlashAttention(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, meta, scale):
+        out, lse = flash_attention_forward(q, k, v, meta, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.meta = meta
+        ctx.scale = scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dout = dout if dout.stride(3) == 1 and dout.stride(2) == dout.shape[3] else dout.contiguous()
+        dq, dk, dv = flash_attention_backward(q, k, v, out, dout, lse, ctx.meta, ctx.scale)
+        return dq, dk, dv, None, None
+
+
+def flash_attention(q, k, v, meta: AttentionMeta, scale: float | None = None) -> torch.Tensor:
+    """Differentiable segment-masked flash attention on the sm_100a kernels."""
+    return _FlashAttention.apply(q, k, v, meta, scale)

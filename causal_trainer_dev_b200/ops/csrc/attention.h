@@ -36,5 +36,42 @@ struct FwdCall {
   void* stream;
 };
 
+enum : int { MODE_DKV = 0, MODE_DQ = 1 };
+
+// Extra metadata of the backward kernels, at 64-row granularity:
+//   seg_min64 / seg_max64 [B,S/64]  min / max segment id of each 64-token block
+//   lim_min64 / lim_max64 [B,S/64]  min / max of lim over each 64-token block
+struct BwdArgs {
+  int B, S, Hq, Hkv;
+  float scale, scale_log2;
+  const int* seg;
+  const int* lim;
+  const int* kv_lo;
+  const int* kv_hi;
+  const int* q_lo;
+  const int* q_hi;
+  const int* seg_min64;
+  const int* seg_max64;
+  const int* lim_min64;
+  const int* lim_max64;
+  const float* lse;
+  const float* delta;
+  DeviceStatus* status;
+  long long spin_budget;
+};
+
+struct BwdCall {
+  const void* q; const void* k; const void* v; const void* dout;
+  void* dq; void* dk; void* dv;
+  const float* lse; const float* delta;
+  const int* seg; const int* lim; const int* kv_lo; const int* kv_hi; const int* q_lo; const int* q_hi;
+  const int* seg_min64; const int* seg_max64; const int* lim_min64; const int* lim_max64;
+  int B, S, Hq, Hkv;
+  long q_row_stride, k_row_stride, v_row_stride, do_row_stride, dq_row_stride, dk_row_stride, dv_row_stride;
+  float scale;
+  long long spin_budget;
+  void* stream;
+};
+
 }  // namespace attn
 }  // namespace ctb

@@ -1,0 +1,483 @@
+// Flash attention backward for sm_100a, two kernels from one template, no atomics:
+//
+//   MODE_DKV  KV-tile-owned: a CTA owns 128 keys of one KV head and walks every query
+//             block (64 rows) of every query head of the GQA group that can see them.
+//                 S^T = K Q^T          dP^T = V dO^T            (tcgen05, TMEM)
+//                 P^T = exp2(S^T c - lse),  dS^T = P^T (dP^T - delta)   (registers)
+//                 dV += P^T dO         dK += dS^T Q             (tcgen05, TMEM accumulators)
+//             The reduction over the group's query heads happens in the TMEM accumulators.
+//   MODE_DQ   Q-tile-owned: a CTA owns 128 query rows of one query head and walks the
+//             64-key blocks it can see:  S = Q K^T, dP = dO V^T, dS = P (dP - delta),
+//             dQ += dS K.
+//
+// Structure of both: resident operand pair X (K,V or Q,dO), streamed pair Y (Q,dO or K,V)
+// through a 3-stage TMA ring, two compute warpgroups that alternate Y blocks so the tensor
+// core works on block i+1 while block i is exponentiated.  P^T / dS tiles are written as
+// bf16 into 128B-swizzled K-major shared tiles; the Y tiles are reused in place as
+// MN-major operands of the accumulate MMAs.
+//
+// Reference counterparts: causal_trainer_attention_dq / _dkv
+// (src/causal_trainer/kernels/efficient_attention.py:985-1173, 1270-1436); the psum that
+// follows the reference's dK/dV kernel is not needed on one GPU because the group is reduced
+// in TMEM.
+#include "attention.h"
+
+namespace ctb {
+namespace attn {
+
+constexpr int BWD_THREADS = 384;
+constexpr int Y_STAGES = 3;
+
+enum : unsigned {
+  SITE_B_PROD = 0x0301,
+  SITE_B_MMA_X = 0x0302,
+  SITE_B_MMA_Y = 0x0303,
+  SITE_B_MMA_T = 0x0304,
+  SITE_B_CW_S = 0x0305,
+  SITE_B_CW_T = 0x0306,
+  SITE_B_CW_ACC = 0x0307,
+};
+
+template <int D>
+struct BwdSmem {
+  static constexpr int HALVES = D / 64;
+  static constexpr int XT = HALVES * 16384;   // 128-row resident tile
+  static constexpr int YT = HALVES * 8192;    // 64-row streamed tile
+  static constexpr int TT = 16384;            // 128 x 64 bf16 P^T or dS tile
+  static constexpr int OFF_X = 0;             // X1, X2
+  static constexpr int OFF_Y = 2 * XT;        // stages of (Y1, Y2)
+  static constexpr int OFF_T = OFF_Y + Y_STAGES * 2 * YT;  // per warpgroup: (P^T, dS)
+  static constexpr int OFF_BAR = OFF_T + 2 * 2 * TT;
+  static constexpr int BYTES = OFF_BAR + 256 + 1024;
+};
+
+template <int D, int MODE>
+__global__ void __launch_bounds__(BWD_THREADS, 1)
+attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
+                const __grid_constant__ CUtensorMap map_v, const __grid_constant__ CUtensorMap map_do,
+                const __grid_constant__ CUtensorMap map_out1, const __grid_constant__ CUtensorMap map_out2,
+                const BwdArgs args) {
+  using L = BwdSmem<D>;
+  constexpr int HALVES = L::HALVES;
+  constexpr bool DKV = (MODE == MODE_DKV);
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+  uint64_t* x_full = reinterpret_cast<uint64_t*>(smem + L::OFF_BAR);
+  uint64_t* y_full = x_full + 1;
+  uint64_t* y_empty = y_full + Y_STAGES;
+  uint64_t* s_full = y_empty + Y_STAGES;   // [2] S and dP of buffer u ready
+  uint64_t* t_full = s_full + 2;           // [2] P^T / dS tiles of buffer u written
+  uint64_t* t_done = t_full + 2;           // [2] accumulate MMAs that read buffer u complete
+  uint64_t* acc_full = t_done + 2;
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
+  volatile uint32_t* abort_flag = tmem_slot + 1;
+
+  const int warp = threadIdx.x >> 5;
+  const int lane = threadIdx.x & 31;
+  DeviceStatus* st = args.status;
+  const long long budget = args.spin_budget;
+  const int group = args.Hq / args.Hkv;
+  const int nb128 = args.S / 128;
+  const int nb64 = args.S / 64;
+
+  // ---- work item ----
+  int idx = blockIdx.x;
+  int b, head, x0, y_lo64, y_n64, heads_in_loop;
+  if (DKV) {
+    head = idx % args.Hkv;      // kv head
+    idx /= args.Hkv;
+    b = idx % args.B;
+    const int kb = idx / args.B;  // ascending: key blocks near the start see the most queries
+    x0 = kb * 128;
+    const int qlo = args.q_lo[b * nb128 + kb];
+    const int qhi = args.q_hi[b * nb128 + kb];
+    y_lo64 = qlo / 64;
+    y_n64 = qhi > qlo ? (qhi + 63) / 64 - y_lo64 : 0;
+    heads_in_loop = group;
+  } else {
+    head = idx % args.Hq;       // query head
+    idx /= args.Hq;
+    b = idx % args.B;
+    const int qb = nb128 - 1 - idx / args.B;  // descending: late query blocks see the most keys
+    x0 = qb * 128;
+    const int klo = args.kv_lo[b * nb128 + qb];
+    const int khi = args.kv_hi[b * nb128 + qb];
+    y_lo64 = klo / 64;
+    y_n64 = khi > klo ? (khi + 63) / 64 - y_lo64 : 0;
+    heads_in_loop = 1;
+  }
+  const int n_iter = y_n64 * heads_in_loop;
+  const int hkv = DKV ? head : head / group;
+
+  if (threadIdx.x == 0) {
+    mbar_init(x_full, 1);
+    for (int s = 0; s < Y_STAGES; ++s) {
+      mbar_init(&y_full[s], 1);
+      mbar_init(&y_empty[s], 1);
+    }
+    for (int u = 0; u < 2; ++u) {
+      mbar_init(&s_full[u], 1);
+      mbar_init(&t_full[u], 128);
+      mbar_init(&t_done[u], 1);
+    }
+    mbar_init(acc_full, 1);
+    *abort_flag = 0u;
+    mbar_fence_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(tmem_slot, 512);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+  const uint32_t tmem_s[2] = {tmem_base, tmem_base + 64};
+  const uint32_t tmem_dp[2] = {tmem_base + 128, tmem_base + 192};
+  const uint32_t tmem_acc1 = tmem_base + 256;       // dV (DKV) or dQ (DQ)
+  const uint32_t tmem_acc2 = tmem_base + 256 + D;   // dK (DKV)
+
+  if (warp == 0) {
+    // ------------------------------ producer ------------------------------
+    if (lane == 0 && n_iter > 0) {
+      mbar_expect_tx(x_full, 2 * L::XT);
+      const CUtensorMap* mx1 = DKV ? &map_k : &map_q;
+      const CUtensorMap* mx2 = DKV ? &map_v : &map_do;
+      const int xh = DKV ? hkv : head;
+#pragma unroll
+      for (int hf = 0; hf < HALVES; ++hf) {
+        tma_load_4d(smem + L::OFF_X + hf * 16384, mx1, x_full, hf * 64, xh, x0, b);
+        tma_load_4d(smem + L::OFF_X + L::XT + hf * 16384, mx2, x_full, hf * 64, xh, x0, b);
+      }
+      const CUtensorMap* my1 = DKV ? &map_q : &map_k;
+      const CUtensorMap* my2 = DKV ? &map_do : &map_v;
+      uint32_t stage = 0, phase = 0;
+      for (int it = 0; it < n_iter; ++it) {
+        const int yh = DKV ? (hkv * group + it / y_n64) : hkv;
+        const int y0 = (y_lo64 + it % y_n64) * 64;
+        if (!mbar_wait(&y_empty[stage], phase ^ 1u, abort_flag, st, SITE_B_PROD, budget)) break;
+        mbar_expect_tx(&y_full[stage], 2 * L::YT);
+        uint8_t* dst = smem + L::OFF_Y + stage * 2 * L::YT;
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf) {
+          tma_load_4d(dst + hf * 8192, my1, &y_full[stage], hf * 64, yh, y0, b);
+          tma_load_4d(dst + L::YT + hf * 8192, my2, &y_full[stage], hf * 64, yh, y0, b);
+        }
+        if (++stage == Y_STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------ MMA issuer ------------------------------
+    if (lane == 0 && n_iter > 0) {
+      constexpr uint32_t idesc_s = make_idesc_bf16(128, 64, false, false);
+      constexpr uint32_t idesc_acc = make_idesc_bf16(128, D, false, true);
+      const uint32_t x1 = smem_u32(smem + L::OFF_X);
+      const uint32_t x2 = smem_u32(smem + L::OFF_X + L::XT);
+      bool ok = mbar_wait(x_full, 0, abort_flag, st, SITE_B_MMA_X, budget);
+      uint32_t stage = 0, phase = 0;       // stage of the block whose S/dP is issued next
+      uint32_t astage = 0;                 // stage of the block whose accumulate MMAs come next
+      uint32_t tph[2] = {0, 0};
+      auto accumulate_block = [&](int k) -> bool {
+        const int u = k & 1;
+        if (!mbar_wait(&t_full[u], tph[u], abort_flag, st, SITE_B_MMA_T, budget)) return false;
+        tph[u] ^= 1u;
+        tc_fence_after();
+        const uint32_t y1 = smem_u32(smem + L::OFF_Y + astage * 2 * L::YT);
+        const uint32_t y2 = y1 + L::YT;
+        const uint32_t tp = smem_u32(smem + L::OFF_T + u * 2 * L::TT);
+        const uint32_t tds = tp + L::TT;
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) {
+          if (DKV) {
+            umma_bf16(tmem_acc1, desc_kmajor(tp, kk), desc_mnmajor(y2, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
+            umma_bf16(tmem_acc2, desc_kmajor(tds, kk), desc_mnmajor(y1, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
+          } else {
+            umma_bf16(tmem_acc1, desc_kmajor(tds, kk), desc_mnmajor(y1, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
+          }
+        }
+        umma_commit(&y_empty[astage]);
+        umma_commit(&t_done[u]);
+        if (++astage == Y_STAGES) astage = 0;
+        return true;
+      };
+      for (int it = 0; ok && it < n_iter; ++it) {
+        const int u = it & 1;
+        if (!mbar_wait(&y_full[stage], phase, abort_flag, st, SITE_B_MMA_Y, budget)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const uint32_t y1 = smem_u32(smem + L::OFF_Y + stage * 2 * L::YT);
+        const uint32_t y2 = y1 + L::YT;
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16(tmem_s[u], desc_kmajor(x1 + (k / 4) * 16384, k % 4), desc_kmajor(y1 + (k / 4) * 8192, k % 4),
+                    idesc_s, k != 0 ? 1u : 0u);
+#pragma unroll
+        for (int k = 0; k < D / 16; ++k)
+          umma_bf16(tmem_dp[u], desc_kmajor(x2 + (k / 4) * 16384, k % 4), desc_kmajor(y2 + (k / 4) * 8192, k % 4),
+                    idesc_s, k != 0 ? 1u : 0u);
+        umma_commit(&s_full[u]);
+        if (++stage == Y_STAGES) {
+          stage = 0;
+          phase ^= 1u;
+        }
+        if (it > 0) ok = accumulate_block(it - 1);
+      }
+      if (ok) ok = accumulate_block(n_iter - 1);
+      if (ok) umma_commit(acc_full);
+    }
+  } else if (warp >= 4) {
+    // ------------------------------ compute warpgroups ------------------------------
+    const int u = (warp - 4) >> 2;
+    const int quad = warp & 3;
+    const int r = quad * 32 + lane;
+    const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
+    uint8_t* t_p = smem + L::OFF_T + u * 2 * L::TT;
+    uint8_t* t_ds = t_p + L::TT;
+    const int xi = x0 + r;  // key index (DKV) or query index (DQ) of this thread's row
+    const float LOG2E = 1.4426950408889634f;
+    int row_seg = args.seg[b * args.S + xi];
+    int row_lim = xi;
+    float row_lse2 = 0.f, row_delta = 0.f;
+    if (!DKV) {
+      if (args.lim != nullptr) row_lim = args.lim[b * args.S + xi];
+      row_lse2 = args.lse[(static_cast<size_t>(b) * args.Hq + head) * args.S + xi] * LOG2E;
+      row_delta = args.delta[(static_cast<size_t>(b) * args.Hq + head) * args.S + xi];
+    }
+    bool ok = true;
+    uint32_t sph = 0, dph = 0;
+    int uses = 0;
+    for (int it = u; it < n_iter; it += 2, ++uses) {
+      const int yb = y_lo64 + it % y_n64;
+      const int y0 = yb * 64;
+      const int hq = DKV ? (hkv * group + it / y_n64) : head;
+      if (!mbar_wait(&s_full[u], sph, abort_flag, st, SITE_B_CW_S, budget)) {
+        ok = false;
+        break;
+      }
+      sph ^= 1u;
+      if (uses > 0) {
+        if (!mbar_wait(&t_done[u], dph, abort_flag, st, SITE_B_CW_T, budget)) {
+          ok = false;
+          break;
+        }
+        dph ^= 1u;
+      }
+      tc_fence_after();
+      // ---- visibility class of this row against the 64 columns ----
+      const int cmin = args.seg_min64[b * nb64 + yb];
+      const int cmax = args.seg_max64[b * nb64 + yb];
+      bool none, all;
+      if (DKV) {
+        const int lmin = args.lim_min64[b * nb64 + yb];
+        const int lmax = args.lim_max64[b * nb64 + yb];
+        none = (row_seg == 0) || (row_seg < cmin) || (row_seg > cmax) || (lmax < xi);
+        all = (row_seg != 0) && (cmin == row_seg) && (cmax == row_seg) && (lmin >= xi);
+      } else {
+        none = (row_seg == 0) || (row_seg < cmin) || (row_seg > cmax) || (y0 > row_lim);
+        all = (row_seg != 0) && (cmin == row_seg) && (cmax == row_seg) && (y0 + 63 <= row_lim);
+      }
+      const int* col_seg = args.seg + b * args.S + y0;
+      const int* col_lim = (args.lim != nullptr) ? args.lim + b * args.S + y0 : nullptr;
+      const float* col_lse = args.lse + (static_cast<size_t>(b) * args.Hq + hq) * args.S + y0;
+      const float* col_delta = args.delta + (static_cast<size_t>(b) * args.Hq + hq) * args.S + y0;
+#pragma unroll 1
+      for (int c = 0; c < 2; ++c) {
+        uint32_t rs[32], rd[32];
+        tmem_ld32(tmem_s[u] + lane_off + c * 32, rs);
+        tmem_ld32(tmem_dp[u] + lane_off + c * 32, rd);
+        tmem_ld_wait();
+        float p[32], ds[32];
+        if (none) {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            p[e] = 0.f;
+            ds[e] = 0.f;
+          }
+        } else {
+#pragma unroll
+          for (int e4 = 0; e4 < 8; ++e4) {
+            float l2[4], dl[4];
+            if (DKV) {
+              const float4 lv = __ldg(reinterpret_cast<const float4*>(col_lse) + c * 8 + e4);
+              const float4 dv = __ldg(reinterpret_cast<const float4*>(col_delta) + c * 8 + e4);
+              l2[0] = lv.x * LOG2E; l2[1] = lv.y * LOG2E; l2[2] = lv.z * LOG2E; l2[3] = lv.w * LOG2E;
+              dl[0] = dv.x; dl[1] = dv.y; dl[2] = dv.z; dl[3] = dv.w;
+            } else {
+              l2[0] = l2[1] = l2[2] = l2[3] = row_lse2;
+              dl[0] = dl[1] = dl[2] = dl[3] = row_delta;
+            }
+            bool vis[4] = {true, true, true, true};
+            if (!all) {
+              const int4 sg = __ldg(reinterpret_cast<const int4*>(col_seg) + c * 8 + e4);
+              const int col0 = y0 + c * 32 + e4 * 4;
+              if (DKV) {
+                int4 lm = make_int4(col0, col0 + 1, col0 + 2, col0 + 3);
+                if (col_lim != nullptr) lm = __ldg(reinterpret_cast<const int4*>(col_lim) + c * 8 + e4);
+                vis[0] = (sg.x == row_seg) && (xi <= lm.x);
+                vis[1] = (sg.y == row_seg) && (xi <= lm.y);
+                vis[2] = (sg.z == row_seg) && (xi <= lm.z);
+                vis[3] = (sg.w == row_seg) && (xi <= lm.w);
+              } else {
+                vis[0] = (sg.x == row_seg) && (col0 + 0 <= row_lim);
+                vis[1] = (sg.y == row_seg) && (col0 + 1 <= row_lim);
+                vis[2] = (sg.z == row_seg) && (col0 + 2 <= row_lim);
+                vis[3] = (sg.w == row_seg) && (col0 + 3 <= row_lim);
+              }
+            }
+#pragma unroll
+            for (int q4 = 0; q4 < 4; ++q4) {
+              const int e = e4 * 4 + q4;
+              const float pe = vis[q4] ? fast_exp2(__uint_as_float(rs[e]) * args.scale_log2 - l2[q4]) : 0.f;
+              p[e] = pe;
+              ds[e] = pe * (__uint_as_float(rd[e]) - dl[q4]);
+            }
+          }
+        }
+#pragma unroll
+        for (int g = 0; g < 4; ++g) {
+          uint4 v;
+          if (DKV) {
+            v.x = pack_bf16(p[g * 8 + 0], p[g * 8 + 1]);
+            v.y = pack_bf16(p[g * 8 + 2], p[g * 8 + 3]);
+            v.z = pack_bf16(p[g * 8 + 4], p[g * 8 + 5]);
+            v.w = pack_bf16(p[g * 8 + 6], p[g * 8 + 7]);
+            *reinterpret_cast<uint4*>(t_p + sw128_offset(r, c * 4 + g)) = v;
+          }
+          v.x = pack_bf16(ds[g * 8 + 0], ds[g * 8 + 1]);
+          v.y = pack_bf16(ds[g * 8 + 2], ds[g * 8 + 3]);
+          v.z = pack_bf16(ds[g * 8 + 4], ds[g * 8 + 5]);
+          v.w = pack_bf16(ds[g * 8 + 6], ds[g * 8 + 7]);
+          *reinterpret_cast<uint4*>(t_ds + sw128_offset(r, c * 4 + g)) = v;
+        }
+      }
+      fence_proxy_async_smem();
+      tc_fence_before();
+      mbar_arrive(&t_full[u]);
+    }
+    // ---- epilogue: accumulators -> bf16 -> staging -> TMA store ----
+    if (ok && n_iter > 0) {
+      ok = mbar_wait(acc_full, 0, abort_flag, st, SITE_B_CW_ACC, budget);
+      tc_fence_after();
+    }
+    const bool any_bad = named_bar_or(2 + u, 128, !ok);
+    const bool writes = DKV || (u == 0);
+    if (!any_bad && writes) {
+      // DKV: warpgroup 0 stores dV, warpgroup 1 stores dK (scaled); DQ: warpgroup 0 stores dQ (scaled).
+      const uint32_t acc = (DKV && u == 1) ? tmem_acc2 : tmem_acc1;
+      const float mul = (DKV && u == 0) ? 1.f : args.scale;
+      uint8_t* stage_buf = smem + L::OFF_T + u * 2 * L::TT;  // 32 KiB: [HALVES][128 rows][128 B]
+#pragma unroll 1
+      for (int c = 0; c < D / 32; ++c) {
+        uint32_t rr[32];
+        if (n_iter > 0) {
+          tmem_ld32(acc + lane_off + c * 32, rr);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) rr[e] = 0u;
+        }
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+          uint4 v;
+          v.x = pack_bf16(__uint_as_float(rr[jj * 8 + 0]) * mul, __uint_as_float(rr[jj * 8 + 1]) * mul);
+          v.y = pack_bf16(__uint_as_float(rr[jj * 8 + 2]) * mul, __uint_as_float(rr[jj * 8 + 3]) * mul);
+          v.z = pack_bf16(__uint_as_float(rr[jj * 8 + 4]) * mul, __uint_as_float(rr[jj * 8 + 5]) * mul);
+          v.w = pack_bf16(__uint_as_float(rr[jj * 8 + 6]) * mul, __uint_as_float(rr[jj * 8 + 7]) * mul);
+          *reinterpret_cast<uint4*>(stage_buf + (c / 2) * 16384 + sw128_offset(r, (c % 2) * 4 + jj)) = v;
+        }
+      }
+      fence_proxy_async_smem();
+      named_bar_sync(4 + u, 128);
+      if (r == 0) {
+        const CUtensorMap* mo = (DKV && u == 1) ? &map_out2 : &map_out1;
+        const int oh = DKV ? hkv : head;
+#pragma unroll
+        for (int hf = 0; hf < HALVES; ++hf) tma_store_4d(mo, stage_buf + hf * 16384, hf * 64, oh, x0, b);
+        tma_commit_group();
+        tma_wait_group<0>();
+      }
+    }
+  }
+
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
+template <int D, int MODE>
+int launch_bwd(const BwdCall& c) {
+  using L = BwdSmem<D>;
+  auto make = [&](const void* base, int heads, long row_stride, int rows) -> const CUtensorMap* {
+    const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(heads), static_cast<uint64_t>(c.S),
+                              static_cast<uint64_t>(c.B)};
+    const uint64_t strides[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(row_stride),
+                                 static_cast<uint64_t>(row_stride) * c.S};
+    const uint32_t box[4] = {64, 1, static_cast<uint32_t>(rows), 1};
+    return get_tensor_map_4d(base, Elt::BF16, dims, strides, box, true);
+  };
+  constexpr bool DKV = (MODE == MODE_DKV);
+  // Resident operands use 128-row boxes, streamed operands 64-row boxes.
+  const CUtensorMap* mq = make(c.q, c.Hq, c.q_row_stride, DKV ? 64 : 128);
+  const CUtensorMap* mk = make(c.k, c.Hkv, c.k_row_stride, DKV ? 128 : 64);
+  const CUtensorMap* mv = make(c.v, c.Hkv, c.v_row_stride, DKV ? 128 : 64);
+  const CUtensorMap* mdo = make(c.dout, c.Hq, c.do_row_stride, DKV ? 64 : 128);
+  const CUtensorMap* mo1 = DKV ? make(c.dv, c.Hkv, c.dv_row_stride, 128) : make(c.dq, c.Hq, c.dq_row_stride, 128);
+  const CUtensorMap* mo2 = DKV ? make(c.dk, c.Hkv, c.dk_row_stride, 128) : mo1;
+  if (!mq || !mk || !mv || !mdo || !mo1 || !mo2) return 1;
+  BwdArgs a{};
+  a.B = c.B; a.S = c.S; a.Hq = c.Hq; a.Hkv = c.Hkv;
+  a.scale = c.scale;
+  a.scale_log2 = c.scale * 1.4426950408889634f;
+  a.seg = c.seg; a.lim = c.lim; a.kv_lo = c.kv_lo; a.kv_hi = c.kv_hi; a.q_lo = c.q_lo; a.q_hi = c.q_hi;
+  a.seg_min64 = c.seg_min64; a.seg_max64 = c.seg_max64; a.lim_min64 = c.lim_min64; a.lim_max64 = c.lim_max64;
+  a.lse = c.lse; a.delta = c.delta;
+  a.status = device_status();
+  a.spin_budget = c.spin_budget > 0 ? c.spin_budget : CTB_SPIN_BUDGET;
+  auto kern = attn_bwd_kernel<D, MODE>;
+  static int configured_dev = -1;
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (configured_dev != dev) {
+    CTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES));
+    configured_dev = dev;
+  }
+  const int grid = c.B * (DKV ? c.Hkv : c.Hq) * (c.S / 128);
+  kern<<<grid, BWD_THREADS, L::BYTES, static_cast<cudaStream_t>(c.stream)>>>(*mq, *mk, *mv, *mdo, *mo1, *mo2, a);
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace attn
+}  // namespace ctb
+
+// mode 0: dK/dV kernel, mode 1: dQ kernel.  All tensors are [B,S,H,D] views with a row
+// stride; lse and delta are [B,Hq,S] fp32.
+CTB_API int ctb_attn_bwd(int mode, const void* q, const void* k, const void* v, const void* dout, void* dq, void* dk,
+                         void* dv, const float* lse, const float* delta, const int* seg, const int* lim,
+                         const int* kv_lo, const int* kv_hi, const int* q_lo, const int* q_hi, const int* seg_min64,
+                         const int* seg_max64, const int* lim_min64, const int* lim_max64, int B, int S, int Hq,
+                         int Hkv, int D, long q_rs, long k_rs, long v_rs, long do_rs, long dq_rs, long dk_rs,
+                         long dv_rs, float scale, long long spin_budget, void* stream) {
+  if (S % 128) return ctb::fail("attention: sequence length must be a multiple of 128");
+  if (Hq % Hkv) return ctb::fail("attention: Hq must be a multiple of Hkv");
+  ctb::attn::BwdCall c{};
+  c.q = q; c.k = k; c.v = v; c.dout = dout; c.dq = dq; c.dk = dk; c.dv = dv; c.lse = lse; c.delta = delta;
+  c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi; c.q_lo = q_lo; c.q_hi = q_hi;
+  c.seg_min64 = seg_min64; c.seg_max64 = seg_max64; c.lim_min64 = lim_min64; c.lim_max64 = lim_max64;
+  c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
+  c.q_row_stride = q_rs; c.k_row_stride = k_rs; c.v_row_stride = v_rs; c.do_row_stride = do_rs;
+  c.dq_row_stride = dq_rs; c.dk_row_stride = dk_rs; c.dv_row_stride = dv_rs;
+  c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
+  using namespace ctb::attn;
+  if (D == 128) return mode == 0 ? launch_bwd<128, MODE_DKV>(c) : launch_bwd<128, MODE_DQ>(c);
+  if (D == 64) return mode == 0 ? launch_bwd<64, MODE_DKV>(c) : launch_bwd<64, MODE_DQ>(c);
+  return ctb::fail("attention: head_dim must be 64 or 128");
+}
