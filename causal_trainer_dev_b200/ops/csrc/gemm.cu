@@ -500,3 +500,26 @@ CTB_API int ctb_gemm_flagged(const void* A, const void* B, void* C, int M, int N
   c.b_flags = flags; c.b_flag_rows = flag_rows; c.b_flag_epoch = epoch; c.spin_budget = spin_budget;
   return ctb::run_gemm(c);
 }
+
+// Cut cross-entropy statistics: logits = hidden[rows,d] * head[vocab,d]^T are reduced per
+// 256-column slab to pmax/psum[slab][row]; target_logit[row] is written by the slab that
+// holds the row's target (rows with target < 0 are never written).
+CTB_API int ctb_ce_stats(const void* hidden, const void* head, int rows, int vocab, int d, long ldh, long ldw,
+                         const int* targets, float* pmax, float* psum, float* target_logit, void* stream) {
+  ctb::GemmCall c{};
+  c.A = hidden; c.B = head; c.M = rows; c.N = vocab; c.K = d; c.lda = ldh; c.ldb = ldw;
+  c.epi = ctb::EPI_CE_STATS; c.stream = stream;
+  c.ce_targets = targets; c.ce_max = pmax; c.ce_sum = psum; c.ce_target_logit = target_logit;
+  return ctb::run_gemm(c);
+}
+
+// Cut cross-entropy backward slab: G[rows,vocab] = (exp(logits - lse[row]) - onehot) * coef[row], bf16.
+CTB_API int ctb_ce_dlogits(const void* hidden, const void* head, void* g, int rows, int vocab, int d, long ldh,
+                           long ldw, long ldg, const int* targets, const float* lse, const float* coef,
+                           void* stream) {
+  ctb::GemmCall c{};
+  c.A = hidden; c.B = head; c.C = g; c.M = rows; c.N = vocab; c.K = d; c.lda = ldh; c.ldb = ldw; c.ldc = ldg;
+  c.epi = ctb::EPI_CE_DLOGITS; c.stream = stream;
+  c.ce_targets = targets; c.ce_lse = lse; c.ce_coef = coef;
+  return ctb::run_gemm(c);
+}

@@ -1,0 +1,97 @@
+"""tcgen05 flash attention (forward, dQ, dK/dV) against the O(S^2) fp32 oracle.
+
+Tolerances are those of the reference's accelerator tests
+(tests/kernels/test_efficient_attention_tpu.py:54-59); leakage checks are bit-exact.
+"""
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def _rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm().clamp_min(1e-9)).item()
+
+
+def _segments(b, s, ndoc, pad_left=0, seed=0):
+    gen = torch.Generator().manual_seed(seed)
+    seg = torch.zeros(b, s, dtype=torch.int32)
+    for i in range(b):
+        cuts = sorted((torch.randperm(s - pad_left - 1, generator=gen)[: ndoc - 1] + 1 + pad_left).tolist())
+        bounds = [pad_left] + cuts + [s]
+        for j in range(len(bounds) - 1):
+            seg[i, bounds[j]:bounds[j + 1]] = j + 1
+    return seg.cuda()
+
+
+def _run(b, s, hq, hkv, d, seg, end=None, seed=0):
+    from causal_trainer_dev_b200.ops import attention as A
+
+    torch.manual_seed(seed)
+    q = torch.randn(b, s, hq, d, device="cuda").bfloat16()
+    k = torch.randn(b, s, hkv, d, device="cuda").bfloat16()
+    v = torch.randn(b, s, hkv, d, device="cuda").bfloat16()
+    do = torch.randn(b, s, hq, d, device="cuda").bfloat16()
+    meta = A.build_attention_meta(seg, end)
+    o, lse = A.flash_attention_forward(q, k, v, meta)
+    dq, dk, dv = A.flash_attention_backward(q, k, v, o, do, lse, meta)
+    return (q, k, v, do), (o, lse, dq, dk, dv)
+
+
+@pytest.mark.parametrize("d,hq,hkv", [(128, 4, 2), (64, 4, 2), (128, 4, 1)])
+@pytest.mark.parametrize("layout", ["one", "packed", "padded", "maskgit"])
+def test_matches_oracle(cuda_lib, d, hq, hkv, layout):
+    from causal_trainer_dev_b200.ops import attention as A
+
+    b, s = 2, 768
+    seg = _segments(b, s, {"one": 1, "packed": 5, "padded": 3, "maskgit": 2}[layout],
+                    pad_left=90 if layout in ("padded", "maskgit") else 0)
+    end = None
+    if layout == "maskgit":
+        end = torch.arange(s, device="cuda", dtype=torch.int32).repeat(b, 1)
+        for i in range(b):
+            st, en = 120, 330
+            if seg[i, st] == seg[i, en - 1]:
+                end[i, st:en] = en - 1
+    (q, k, v, do), (o, lse, dq, dk, dv) = _run(b, s, hq, hkv, d, seg, end)
+    qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+    ref = A.vanilla_attention(qf, kf, vf, seg, end)
+    ref.backward(do.float())
+    assert _rel(o, ref) < 0.04
+    assert _rel(dq, qf.grad) < 0.10
+    assert _rel(dk, kf.grad) < 0.12
+    assert _rel(dv, vf.grad) < 0.10
+    # padding rows: zero output, zero gradients
+    pad = seg == 0
+    if pad.any():
+        assert torch.all(o[pad] == 0) and torch.all(dq[pad] == 0) and torch.all(dk[pad] == 0) and torch.all(dv[pad] == 0)
+        assert torch.all(lse.permute(0, 2, 1)[pad] == 0)
+    assert cuda_lib.device_status() == (0, 0, 0, 0)
+
+
+def test_no_leakage_between_documents(cuda_lib):
+    """Perturbing document 1 changes nothing, bit for bit, in document 2."""
+    from causal_trainer_dev_b200.ops import attention as A
+
+    b, s, hq, hkv, d = 1, 512, 4, 2, 128
+    seg = torch.ones(b, s, dtype=torch.int32, device="cuda")
+    seg[:, 200:] = 2
+    (q, k, v, do), base = _run(b, s, hq, hkv, d, seg)
+    q2, k2, v2 = q.clone(), k.clone(), v.clone()
+    q2[:, :200] += 1
+    k2[:, :200] -= 1
+    v2[:, :200] *= 2
+    meta = A.build_attention_meta(seg)
+    o2, lse2 = A.flash_attention_forward(q2, k2, v2, meta)
+    dq2, dk2, dv2 = A.flash_attention_backward(q2, k2, v2, o2, do, lse2, meta)
+    o, lse, dq, dk, dv = base
+    for a, c in ((o, o2), (dq, dq2), (dk, dk2), (dv, dv2)):
+        assert torch.equal(a[:, 200:], c[:, 200:])
+
+
+def test_deterministic(cuda_lib):
+    seg = _segments(2, 512, 3)
+    _, first = _run(2, 512, 4, 2, 128, seg, seed=5)
+    _, second = _run(2, 512, 4, 2, 128, seg, seed=5)
+    for a, c in zip(first, second):
+        assert torch.equal(a, c)
