@@ -179,7 +179,10 @@ def flash_attention_backward(
     b, s, hq, d = q.shape
     hkv = k.shape[2]
     scale = 1.0 / math.sqrt(d) if scale is None else scale
-    delta = (out.float() * dout.float()).sum(-1).permute(0, 2, 1).contiguous()  # [B,Hq,S]
+    from .elementwise import attention_delta
+
+    _row_stride(out), _row_stride(dout)
+    delta = attention_delta(out, dout)  # [B,Hq,S] fp32
     dq = torch.empty((b, s, hq, d), dtype=torch.bfloat16, device=q.device) if dq is None else dq
     dk = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dk is None else dk
     dv = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dv is None else dv

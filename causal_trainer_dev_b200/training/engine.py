@@ -1,0 +1,270 @@
+"""Layerwise sm_100a training engine: explicit forward, recompute and backward schedule.
+
+The reference traces one XLA program per step and lets ``jax.checkpoint(nothing_saveable)``
+recompute each layer in the backward pass (src/causal_trainer/modeling/architecture.py:
+777-786).  On B200 the same schedule is written out by hand, with no autograd graph and no
+tracing compiler:
+
+* forward keeps only each layer's input (residual stream + pending branch), bf16;
+* backward walks the layers in reverse, re-runs the layer forward saving its internals,
+  then runs the hand-derived layer backward;
+* every matmul is the tcgen05 GEMM (forward, dgrad reading ``W`` in place as an MN-major
+  operand, wgrad reading ``dY`` and ``X`` in place, optionally accumulating in fp32
+  through TMA reduce-add), attention is the tcgen05 flash kernels, the loss is the
+  projection-fused cut cross-entropy and everything else the fused memory-bound kernels;
+* weights come from a *provider*: plain local buffers on one GPU, or the FSDP runtime,
+  which hands out gathered unit buffers and takes gradients back for reduce-scatter.
+
+The residual add of a layer's MLP output is fused into the next layer's input RMSNorm
+(``h = resid + branch`` is produced by the norm kernel), so the residual stream is written
+once per half-layer.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+
+from ..models.config import ModelConfig
+from ..models.decoder import canonicalize_segment_ids, make_position_ids
+from ..models.params import ModelParams, Unit
+from ..ops import attention as attn_ops
+from ..ops import cross_entropy as ce
+from ..ops import elementwise as ew
+from ..ops import lib as _lib
+from ..ops.gemm import gemm
+from . import losses
+
+
+class LocalProvider:
+    """Weight provider for a single replica: units are used where they live."""
+
+    def __init__(self, params: ModelParams, grad_dtype: torch.dtype):
+        self.params = params
+        self.grad_dtype = grad_dtype
+
+    def acquire(self, name: str, prefetch: str | None = None) -> Unit:
+        return self.params.units[name]
+
+    def grad_buffer(self, name: str) -> torch.Tensor:
+        u = self.params.units[name]
+        if u.grad is None or u.grad.dtype != self.grad_dtype:
+            u.grad = torch.zeros(u.layout.numel, dtype=self.grad_dtype, device=u.data.device)
+        return u.grad
+
+    def release(self, name: str) -> None:
+        pass
+
+    def grads_ready(self, name: str, last_microbatch: bool) -> None:
+        pass
+
+
+@dataclass
+class EngineOptions:
+    cut_chunk_rows: int = 4096
+    attention_options: object | None = None
+    optimizer_step: int | None = None
+    train_lm_head: bool = True
+    train_embed: bool = True
+    train_norm: bool = True
+
+
+class LayerwiseEngine:
+    """Gradient producer (see ``training.steps.GradientProducer``) running on the CUDA kernels."""
+
+    def __init__(self, cfg: ModelConfig, provider, options: EngineOptions | None = None):
+        _lib.require_gpu_lib()
+        self.cfg = cfg
+        self.provider = provider
+        self.options = options or EngineOptions()
+        self.launches = 0
+        self._inv_freq: torch.Tensor | None = None
+
+    # ------------------------------------------------------------------ helpers
+    def _views(self, unit: Unit, base: torch.Tensor | None = None) -> dict[str, torch.Tensor]:
+        return {seg.name: unit.view(seg.name, of=base) for seg in unit.layout.segments}
+
+    def _count(self, n: int = 1) -> None:
+        self.launches += n
+
+    def _wgrad(self, dy: torch.Tensor, x: torch.Tensor, gview: torch.Tensor, accumulate: bool) -> None:
+        gemm(dy, x, a_mn=True, b_mn=True, out=gview, accumulate=accumulate)
+        self._count()
+
+    def _bias_grad(self, dy: torch.Tensor, gview: torch.Tensor, accumulate: bool) -> None:
+        s = dy.float().sum(0)
+        if accumulate:
+            gview.add_(s.to(gview.dtype))
+        else:
+            gview.copy_(s.to(gview.dtype))
+        self._count(2)
+
+    # ------------------------------------------------------------------ layer forward
+    def _layer_forward(self, w: dict[str, torch.Tensor], resid: torch.Tensor, branch: torch.Tensor | None, ctx: dict,
+                       li: int, save: bool) -> tuple[torch.Tensor, torch.Tensor, dict | None]:
+        cfg = self.cfg
+        t = resid.shape[0]
+        qw, kvw, d_head = cfg.query_width, cfg.key_value_width, cfg.head_dim
+        n1, rstd1, x = ew.rmsnorm_forward(resid, w["ln1"], cfg.rms_norm_eps, residual=branch)
+        qkv = gemm(n1, w["qkv_w"], bias=w.get("qkv_b"))
+        ew.rope_inplace(qkv, ctx["cos"], ctx["sin"], cfg.num_attention_heads + cfg.num_key_value_heads, d_head,
+                        cfg.rotary_dim, cfg.rope_style)
+        b, s = ctx["batch"], ctx["seq"]
+        q = qkv[:, :qw].view(b, s, cfg.num_attention_heads, d_head)
+        k = qkv[:, qw:qw + kvw].view(b, s, cfg.num_key_value_heads, d_head)
+        v = qkv[:, qw + kvw:].view(b, s, cfg.num_key_value_heads, d_head)
+        o, lse = attn_ops.flash_attention_forward(q, k, v, ctx["meta"])
+        attn_out = gemm(o.view(t, qw), w["o_w"])
+        n2, rstd2, h = ew.rmsnorm_forward(x, w["ln2"], cfg.rms_norm_eps, residual=attn_out)
+        gu = gemm(n2, w["gu_w"])
+        act = ew.swiglu_forward(gu)
+        mlp = gemm(act, w["down_w"])
+        self._count(10)
+        saved = None
+        if save:
+            saved = dict(x=x, n1=n1, rstd1=rstd1, qkv=qkv, o=o, lse=lse, h=h, n2=n2, rstd2=rstd2, gu=gu, act=act)
+        return h, mlp, saved
+
+    # ------------------------------------------------------------------ layer backward
+    def _layer_backward(self, w: dict[str, torch.Tensor], g: dict[str, torch.Tensor], sv: dict, dout: torch.Tensor,
+                        ctx: dict, accumulate: bool) -> torch.Tensor:
+        """``dout`` is the gradient of the layer output (h + mlp); returns the gradient of its input x."""
+        cfg = self.cfg
+        t = dout.shape[0]
+        qw, kvw, d_head = cfg.query_width, cfg.key_value_width, cfg.head_dim
+        b, s = ctx["batch"], ctx["seq"]
+        # MLP branch
+        dact = gemm(dout, w["down_w"], b_mn=True)
+        self._wgrad(dout, sv["act"], g["down_w"], accumulate)
+        dgu = ew.swiglu_backward(sv["gu"], dact)
+        del dact
+        dn2 = gemm(dgu, w["gu_w"], b_mn=True)
+        self._wgrad(dgu, sv["n2"], g["gu_w"], accumulate)
+        del dgu
+        dh, _ = ew.rmsnorm_backward(dn2, sv["h"], w["ln2"], sv["rstd2"], dres=dout, dw_out=g["ln2"],
+                                    dw_accumulate=accumulate)
+        del dn2
+        # attention branch: dh is the gradient of h = x + attn_out
+        do = gemm(dh, w["o_w"], b_mn=True)
+        self._wgrad(dh, sv["o"].view(t, qw), g["o_w"], accumulate)
+        qkv = sv["qkv"]
+        q = qkv[:, :qw].view(b, s, cfg.num_attention_heads, d_head)
+        k = qkv[:, qw:qw + kvw].view(b, s, cfg.num_key_value_heads, d_head)
+        v = qkv[:, qw + kvw:].view(b, s, cfg.num_key_value_heads, d_head)
+        dqkv = torch.empty_like(qkv)
+        dq = dqkv[:, :qw].view(b, s, cfg.num_attention_heads, d_head)
+        dk = dqkv[:, qw:qw + kvw].view(b, s, cfg.num_key_value_heads, d_head)
+        dv = dqkv[:, qw + kvw:].view(b, s, cfg.num_key_value_heads, d_head)
+        attn_ops.flash_attention_backward(q, k, v, sv["o"], do.view(b, s, cfg.num_attention_heads, d_head), sv["lse"],
+                                          ctx["meta"], dq=dq, dk=dk, dv=dv)
+        ew.rope_inplace(dqkv, ctx["cos"], ctx["sin"], cfg.num_attention_heads + cfg.num_key_value_heads, d_head,
+                        cfg.rotary_dim, cfg.rope_style, inverse=True)
+        dn1 = gemm(dqkv, w["qkv_w"], b_mn=True)
+        self._wgrad(dqkv, sv["n1"], g["qkv_w"], accumulate)
+        if "qkv_b" in w:
+            self._bias_grad(dqkv, g["qkv_b"], accumulate)
+        dx, _ = ew.rmsnorm_backward(dn1, sv["x"], w["ln1"], sv["rstd1"], dres=dh, dw_out=g["ln1"],
+                                    dw_accumulate=accumulate)
+        self._count(12)
+        return dx
+
+    # ------------------------------------------------------------------ step context
+    def _context(self, batch: dict[str, torch.Tensor]) -> dict:
+        cfg = self.cfg
+        ids = batch["input_ids"]
+        mask = batch["attention_mask"]
+        seg = canonicalize_segment_ids(mask, batch.get("segment_ids"))
+        pos = batch.get("position_ids")
+        if pos is None:
+            pos = make_position_ids(mask, seg, canonical=True)
+        if self._inv_freq is None or self._inv_freq.device != ids.device:
+            self._inv_freq = ew.inverse_frequencies(cfg.rotary_dim, cfg.rope_theta, device=ids.device)
+        cos, sin = ew.rope_table(pos, self._inv_freq)
+        end = batch.get("attention_end")
+        meta = attn_ops.build_attention_meta(seg, end)
+        self._count(30)  # metadata is a few dozen tiny launches, once per micro-batch
+        return dict(batch=ids.shape[0], seq=ids.shape[1], cos=cos, sin=sin, meta=meta, seg=seg)
+
+    # ------------------------------------------------------------------ forward only
+    @torch.no_grad()
+    def forward_hidden(self, batch: dict[str, torch.Tensor]) -> torch.Tensor:
+        """Final-norm hidden states [B*S, d] (evaluation / tests)."""
+        ctx = self._context(batch)
+        cfg = self.cfg
+        embed = self.provider.acquire("embed")
+        resid = ew.embedding_gather(batch["input_ids"], embed.view("embed"))
+        self.provider.release("embed")
+        branch = None
+        for li in range(cfg.num_hidden_layers):
+            unit = self.provider.acquire(f"layer.{li}", prefetch=f"layer.{li + 1}" if li + 1 < cfg.num_hidden_layers else "final")
+            resid, branch, _ = self._layer_forward(self._views(unit), resid, branch, ctx, li, save=False)
+            self.provider.release(f"layer.{li}")
+        final = self.provider.acquire("final")
+        y, _, _ = ew.rmsnorm_forward(resid, final.view("norm"), cfg.rms_norm_eps, residual=branch)
+        self.provider.release("final")
+        return y
+
+    # ------------------------------------------------------------------ gradient producer
+    @torch.no_grad()
+    def __call__(self, batch: dict[str, torch.Tensor], grad_scale: float, first: bool, last: bool = True):
+        cfg = self.cfg
+        prov = self.provider
+        accumulate = not first
+        ctx = self._context(batch)
+        nl = cfg.num_hidden_layers
+        # ---------------- forward: keep (resid, branch) per layer ----------------
+        embed = prov.acquire("embed", prefetch="layer.0")
+        resid = ew.embedding_gather(batch["input_ids"], embed.view("embed"))
+        self._count()
+        prov.release("embed")
+        branch = None
+        inputs: list[tuple[torch.Tensor, torch.Tensor | None]] = []
+        for li in range(nl):
+            unit = prov.acquire(f"layer.{li}", prefetch=f"layer.{li + 1}" if li + 1 < nl else "final")
+            inputs.append((resid, branch))
+            resid, branch, _ = self._layer_forward(self._views(unit), resid, branch, ctx, li, save=False)
+            prov.release(f"layer.{li}")
+        # ---------------- head: final norm + cut cross-entropy ----------------
+        final = prov.acquire("final", prefetch=f"layer.{nl - 1}")
+        fw = self._views(final)
+        fg = self._views(final, prov.grad_buffer("final"))
+        y, rstd_f, xf = ew.rmsnorm_forward(resid, fw["norm"], cfg.rms_norm_eps, residual=branch)
+        targets, weights = losses.aligned_targets_and_weights(batch)
+        targets, weights = targets.reshape(-1), weights.reshape(-1)
+        nll, wsum, lse, coef = ce.cut_ce_forward(y, fw["lm_head"], targets, weights, grad_scale)
+        train_head = self.options.train_lm_head
+        dy, _ = ce.cut_ce_backward(y, fw["lm_head"], targets, lse, coef, chunk_rows=self.options.cut_chunk_rows,
+                                   need_dhead=train_head, dhead_out=fg["lm_head"] if train_head else None,
+                                   dhead_accumulate=accumulate)
+        self._count(4 + 3 * ((y.shape[0] + self.options.cut_chunk_rows - 1) // self.options.cut_chunk_rows))
+        dout, _ = ew.rmsnorm_backward(dy, xf, fw["norm"], rstd_f, dw_out=fg["norm"], dw_accumulate=accumulate)
+        del y, dy, xf
+        prov.release("final")
+        prov.grads_ready("final", last)
+        # ---------------- backward: recompute + hand-written layer backward ----------------
+        for li in reversed(range(nl)):
+            unit = prov.acquire(f"layer.{li}", prefetch=f"layer.{li - 1}" if li > 0 else "embed")
+            w = self._views(unit)
+            g = self._views(unit, prov.grad_buffer(f"layer.{li}"))
+            r_in, b_in = inputs.pop()
+            _, _, saved = self._layer_forward(w, r_in, b_in, ctx, li, save=True)
+            dout = self._layer_backward(w, g, saved, dout, ctx, accumulate)
+            del saved
+            prov.release(f"layer.{li}")
+            prov.grads_ready(f"layer.{li}", last)
+        # ---------------- embedding ----------------
+        if self.options.train_embed:
+            embed = prov.acquire("embed")
+            gbuf = embed.view("embed", of=prov.grad_buffer("embed"))
+            if first:
+                gbuf.zero_()
+            ids = batch["input_ids"].reshape(-1)
+            keep = ids != cfg.pad_token_id
+            uniq, inverse = torch.unique(ids[keep], return_inverse=True)
+            tmp = torch.zeros((uniq.numel(), cfg.hidden_size), dtype=torch.float32, device=ids.device)
+            tmp.index_add_(0, inverse, dout[keep].float())
+            gbuf[uniq] += tmp.to(gbuf.dtype)
+            self._count(8)
+            prov.release("embed")
+            prov.grads_ready("embed", last)
+        return nll, wsum
