@@ -1,0 +1,239 @@
+#!/usr/bin/env python
+"""Headline benchmark: training tokens/s of a Llama-3-8B-shape model, seq 4096, global batch
+32 sequences, bf16, FSDP over N B200s of one node (strong scaling: the global batch is fixed).
+
+    python bench.py --gpus 1 --steps 3 --warmup 3
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
+        --master-port 29500 bench.py --gpus 8 --steps 3 --warmup 3
+
+Rank 0 prints one JSON line.  ``value`` is device-timed (CUDA events, max over ranks) on
+inputs already resident on the GPU; ``e2e`` repeats the measurement through
+``Trainer.train_step`` with the step's inputs copied from pinned host memory and the loss
+read back every step.  Data is synthetic (packed log-normal documents, uniform token ids),
+weights are random N(0, 0.02).
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+sys.path.insert(0, str(ROOT))
+
+METRIC = "tokens/s Llama-3-8B-shape seq4096 FSDP bf16"
+
+
+def parse() -> argparse.Namespace:
+    p = argparse.ArgumentParser()
+    p.add_argument("--gpus", type=int, default=1)
+    p.add_argument("--steps", type=int, default=3)
+    p.add_argument("--warmup", type=int, default=3)
+    p.add_argument("--impl", choices=("ours", "reference", "nccl"), default="ours",
+                   help="ours: fused in-kernel collectives; nccl: same engine with NCCL-only collectives; "
+                        "reference: the unmodified reference trainer")
+    p.add_argument("--model", default="llama3-8b")
+    p.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; invalid as a result)")
+    p.add_argument("--seq-len", type=int, default=4096)
+    p.add_argument("--global-batch", type=int, default=32)
+    p.add_argument("--micro-batch", type=int, default=4)
+    return p.parse_args()
+
+
+def reference_arm() -> None:
+    reason = (
+        "unavailable on this box: the reference needs jax/jaxlib/optax (not installed, no network), raises for any "
+        "non-TPU backend (training/runner.py:337-338), rejects every config but its fixed 40-layer MQA model "
+        "(runner.py:190-216) and its kernels are Pallas-TPU programs with no GPU lowering"
+    )
+    print(json.dumps({"impl": "reference", "unavailable": reason}))
+
+
+class ClockSampler:
+    QUERY = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,"
+             "clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index = index
+        self.proc = None
+        self.path = None
+
+    def start(self) -> None:
+        try:
+            fd, self.path = tempfile.mkstemp(suffix=".csv")
+            os.close(fd)
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-lms", "200",
+                 "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
+        except OSError:
+            self.proc = None
+
+    def stop(self) -> dict:
+        out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+        if self.proc is None:
+            return out
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, smax, reasons = [], [], set()
+        names = ("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap")
+        for line in Path(self.path).read_text().splitlines():
+            parts = [x.strip() for x in line.split(",")]
+            if len(parts) < 9:
+                continue
+            try:
+                sm.append(float(parts[1]))
+                smax.append(float(parts[2]))
+            except ValueError:
+                continue
+            for name, val in zip(names, parts[5:9]):
+                if val.lower().startswith("active"):
+                    reasons.add(name)
+        os.unlink(self.path)
+        if sm:
+            out["sm_mhz"] = statistics.median(sm)
+            out["sm_max_mhz"] = max(smax)
+            out["samples"] = len(sm)
+        out["reasons"] = sorted(reasons)
+        return out
+
+
+def main() -> None:
+    args = parse()
+    if args.impl == "reference":
+        reference_arm()
+        return
+    import torch
+    import torch.distributed as dist
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    if world != args.gpus:
+        raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
+
+    from causal_trainer_dev_b200.api import Trainer, TrainerConfig
+    from causal_trainer_dev_b200.data.synthetic import pretraining_rows
+    from causal_trainer_dev_b200.models.config import preset
+    from causal_trainer_dev_b200.training.optimizer import AdamWConfig, ScheduleConfig
+
+    overrides = {"num_hidden_layers": args.layers} if args.layers else {}
+    cfg = preset(args.model, **overrides)
+    if args.global_batch % world:
+        raise SystemExit("global batch must divide by the number of GPUs")
+    rows_per_rank = args.global_batch // world
+    micro = min(args.micro_batch, rows_per_rank)
+    tcfg = TrainerConfig(
+        micro_batch_rows=micro,
+        adamw=AdamWConfig(weight_decay=0.1, max_grad_norm=1.0),
+        schedule=ScheduleConfig(learning_rate=2e-5, learning_rate_end=2e-6, scheduler="cosine", warmup_steps=2,
+                                total_steps=1000),
+        fused_collectives=(args.impl == "ours"),
+    )
+    trainer = Trainer(cfg, tcfg)
+
+    # Two distinct global batches, identical on every rank; each rank keeps its rows (pinned).
+    pool = []
+    for seed in (11, 12):
+        data = pretraining_rows(args.global_batch, args.seq_len, cfg.vocab_size, eos_token_id=int(
+            cfg.eos_token_id if isinstance(cfg.eos_token_id, int) else cfg.eos_token_id[0]),
+            pad_token_id=cfg.pad_token_id, median_len=600.0, sigma=1.0, min_len=32, seed=seed)
+        mine = {k: torch.from_numpy(v[rank * rows_per_rank:(rank + 1) * rows_per_rank].copy()).pin_memory()
+                for k, v in data.items()}
+        pool.append(mine)
+    tokens_per_step = args.global_batch * args.seq_len
+
+    def sync() -> None:
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for i in range(args.warmup):
+        m = trainer.train_step(pool[i % 2])
+    sync()
+
+    # ---------------- device-timed region ----------------
+    dev_batches = [trainer.upload(b) for b in pool]
+    sync()
+    launches0 = trainer.launches()
+    sampler = ClockSampler(local)
+    if rank == 0:
+        sampler.start()
+    start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sync()
+    start.record()
+    for i in range(args.steps):
+        metrics = trainer.train_step_device(dev_batches[i % 2])
+    end.record()
+    sync()
+    ms = start.elapsed_time(end)
+    clocks = sampler.stop() if rank == 0 else {}
+    launches = trainer.launches() - launches0
+    loss = float(metrics.loss)
+
+    # ---------------- end-to-end region (pinned host inputs, loss read back each step) ----------------
+    h2d0, d2h0 = trainer.transfer_counters()
+    sync()
+    t0 = time.perf_counter()
+    start.record()
+    for i in range(args.steps):
+        out = trainer.train_step(pool[i % 2])
+    end.record()
+    sync()
+    e2e_ms = max(start.elapsed_time(end), (time.perf_counter() - t0) * 1e3)
+    h2d1, d2h1 = trainer.transfer_counters()
+
+    if world > 1:
+        t = torch.tensor([ms, e2e_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms, e2e_ms = t.tolist()
+    if rank == 0:
+        ms_per_step = ms / args.steps
+        value = tokens_per_step / (ms_per_step / 1e3)
+        e2e_value = tokens_per_step / (e2e_ms / args.steps / 1e3)
+        peaks = {}
+        peaks_file = ROOT / "MEASURED_PEAKS.json"
+        if peaks_file.exists():
+            peaks = json.loads(peaks_file.read_text())
+        peak = float(peaks.get("bf16_tflops_sustained", 1400.0)) * 1e12
+        flops_per_token = cfg.flops_per_token(args.seq_len)
+        result = {
+            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
+            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (packed log-normal documents, uniform token ids, "
+            "random-init N(0,0.02) weights)", "impl": args.impl,
+            "config": {
+                "model": args.model + (f"-{args.layers}layers" if args.layers else ""), "global_batch": args.global_batch,
+                "seq_len": args.seq_len, "parallelism": f"fsdp{world}", "micro_batch_rows": micro,
+                "grad_accumulation": rows_per_rank // micro, "loss": "cut cross-entropy", "remat": "per layer",
+                "optimizer": "AdamW, bf16 moments, global-norm clip", "l2": "inputs larger than L2 (weights + state "
+                "are tens of GB per GPU, 126 MB L2)",
+            },
+            "mfu_of_measured_sustained": value * flops_per_token / (world * peak),
+            "model_flops_per_token": flops_per_token,
+            "loss_last_step": loss,
+            "clocks": clocks,
+            "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": (h2d1 - h2d0) // args.steps,
+                    "d2h_bytes_per_step": (d2h1 - d2h0) // args.steps, "loss": out["loss"]},
+            "gpu_launches": launches,
+        }
+        print(json.dumps(result))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

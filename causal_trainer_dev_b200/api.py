@@ -1,0 +1,127 @@
+"""Public training API: the calls a user of the framework makes.
+
+``Trainer`` owns the sharded parameters, the optimizer state and the sm_100a engine of one
+rank (one process per GPU).  ``train_step`` takes the rank's rows of one global batch as
+*host* tensors (pinned for asynchronous copies), uploads them, runs every micro-batch
+through forward / recompute / backward, reduces and applies the update, and returns the
+step metrics as Python floats (one device-to-host read).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from .models.config import ModelConfig
+from .models.params import ModelParams
+from .training.engine import EngineOptions, LayerwiseEngine, LocalProvider
+from .training.optimizer import AdamWConfig, ScheduleConfig, learning_rate_at
+from .training.steps import TrainStep
+
+BATCH_FIELDS = ("input_ids", "attention_mask", "segment_ids", "position_ids", "loss_weights", "attention_end",
+                "prediction_targets", "prediction_weights")
+
+
+@dataclass
+class TrainerConfig:
+    micro_batch_rows: int = 4
+    adamw: AdamWConfig = AdamWConfig()
+    schedule: ScheduleConfig = ScheduleConfig(learning_rate=2e-5, total_steps=1000)
+    seed: int = 0
+    fsdp: bool = True                  # shard parameters, gradients and optimizer state over all ranks
+    fused_collectives: bool = True     # in-kernel NVLink all-gather / reduce-scatter instead of NCCL
+    cut_chunk_rows: int = 4096
+    init: str = "normal"               # "normal": N(0, initializer_range) on the device; "hf": ModelParams.init_random
+
+
+class Trainer:
+    def __init__(self, model: ModelConfig, cfg: TrainerConfig | None = None, device: torch.device | None = None):
+        self.model = model
+        self.cfg = cfg or TrainerConfig()
+        self.device = device or torch.device("cuda", torch.cuda.current_device())
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self._bytes_h2d = 0
+        self._bytes_d2h = 0
+        if self.world > 1 and self.cfg.fsdp:
+            from .parallel.fsdp import FsdpRuntime
+
+            self.runtime = FsdpRuntime(model, self.cfg, self.device)
+            self.engine = LayerwiseEngine(model, self.runtime, EngineOptions(cut_chunk_rows=self.cfg.cut_chunk_rows))
+            self.step_fn = self.runtime.make_step(self.engine)
+        else:
+            self.params = self._init_params()
+            self.provider = LocalProvider(self.params, torch.bfloat16)
+            self.engine = LayerwiseEngine(model, self.provider, EngineOptions(cut_chunk_rows=self.cfg.cut_chunk_rows))
+            self.step_fn = TrainStep(self.params, self.engine, self.cfg.adamw, self.cfg.schedule)
+        self._accum_checked = False
+
+    def _init_params(self) -> ModelParams:
+        if self.cfg.init == "hf":
+            return ModelParams.init_random(self.model, self.cfg.seed, torch.bfloat16).to(self.device)
+        params = ModelParams(self.model, torch.bfloat16, self.device)
+        gen = torch.Generator(device=self.device).manual_seed(self.cfg.seed)
+        for name, t in params.named_tensors():
+            if name.endswith("layernorm.weight") or name == "model.norm.weight":
+                t.fill_(1.0)
+            elif name.endswith(".bias"):
+                t.zero_()
+            else:
+                t.normal_(0.0, self.model.initializer_range, generator=gen)
+        params.tensor("model.embed_tokens.weight")[self.model.pad_token_id].zero_()
+        return params
+
+    # ------------------------------------------------------------------ data movement
+    def upload(self, host_batch: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
+        out = {}
+        for k, v in host_batch.items():
+            if k not in BATCH_FIELDS:
+                continue
+            self._bytes_h2d += v.numel() * v.element_size()
+            out[k] = v.to(self.device, non_blocking=True)
+        return out
+
+    def split_micro_batches(self, batch: dict[str, torch.Tensor]) -> list[dict[str, torch.Tensor]]:
+        rows = batch["input_ids"].shape[0]
+        mb = min(self.cfg.micro_batch_rows, rows)
+        if rows % mb:
+            raise ValueError(f"{rows} local rows are not a multiple of micro_batch_rows={mb}")
+        return [{k: v[i:i + mb] for k, v in batch.items()} for i in range(0, rows, mb)]
+
+    # ------------------------------------------------------------------ steps
+    def train_step_device(self, device_batch: dict[str, torch.Tensor]):
+        """Step on inputs that already live on the GPU; returns device-resident metrics."""
+        micro = self.split_micro_batches(device_batch)
+        if len(micro) > 1 and not self._accum_checked:
+            self._switch_to_fp32_accumulation()
+        return self.step_fn.run(micro)
+
+    def train_step(self, host_batch: dict[str, torch.Tensor]) -> dict[str, float]:
+        """Host tensors in, Python floats out (includes the H2D copies and one D2H read)."""
+        metrics = self.train_step_device(self.upload(host_batch))
+        packed = torch.stack([metrics.loss.float(), metrics.nll_sum.float(), metrics.token_count.float(),
+                              metrics.grad_norm.float()]).cpu()
+        self._bytes_d2h += packed.numel() * 4
+        loss, nll, count, gnorm = packed.tolist()
+        return {"loss": loss, "nll_sum": nll, "token_count": count, "grad_norm": gnorm,
+                "learning_rate": metrics.learning_rate}
+
+    def _switch_to_fp32_accumulation(self) -> None:
+        # Several micro-batches per step accumulate in fp32 (the reference's scan does the same).
+        self._accum_checked = True
+        if hasattr(self, "provider"):
+            self.provider.grad_dtype = torch.float32
+        elif hasattr(self, "runtime"):
+            self.runtime.set_grad_dtype(torch.float32)
+
+    def transfer_counters(self) -> tuple[int, int]:
+        return self._bytes_h2d, self._bytes_d2h
+
+    def launches(self) -> int:
+        from .ops import lib
+
+        return lib.launch_count()
+
+    def current_learning_rate(self) -> float:
+        return learning_rate_at(self.cfg.schedule, self.step_fn.optimizer_step)

@@ -375,12 +375,13 @@ __global__ void ce_combine_kernel(const float* __restrict__ pmax, const float* _
 // Sum of squares (fp32) of a bf16 / fp32 vector into per-block partials.
 // ------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void sumsq_kernel(const T* __restrict__ x, long n, float* __restrict__ partial) {
+__global__ void sumsq_kernel(const T* __restrict__ x, long n, float* __restrict__ partial, int round_bf16) {
   __shared__ float scratch[33];
   float acc = 0.f;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
-    const float v = static_cast<float>(x[i]);
+    float v = static_cast<float>(x[i]);
+    if (round_bf16) v = __bfloat162float(__float2bfloat16(v));
     acc += v * v;
   }
   const float t = block_sum(acc, scratch);
@@ -397,11 +398,14 @@ __global__ void sumsq_kernel(const T* __restrict__ x, long n, float* __restrict_
 template <typename GT>
 __global__ void adamw_kernel(__nv_bfloat16* __restrict__ p, const GT* __restrict__ g, __nv_bfloat16* __restrict__ m,
                              __nv_bfloat16* __restrict__ v, long n, float lr, float b1, float b2, float eps,
-                             float decay, float bc1, float bc2, const float* __restrict__ clip, float gscale) {
+                             float decay, float bc1, float bc2, const float* __restrict__ clip, float gscale,
+                             int round_bf16) {
   const float cs = (clip ? *clip : 1.f) * gscale;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < n;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
-    const float gi = static_cast<float>(g[i]) * cs;
+    float graw = static_cast<float>(g[i]);
+    if (round_bf16) graw = __bfloat162float(__float2bfloat16(graw));
+    const float gi = graw * cs;
     const float mi = b1 * __bfloat162float(m[i]) + (1.f - b1) * gi;
     const float vi = b2 * __bfloat162float(v[i]) + (1.f - b2) * gi * gi;
     const float pi = __bfloat162float(p[i]);
@@ -543,28 +547,31 @@ CTB_API int ctb_ce_combine(const float* pmax, const float* psum, int slabs, cons
 
 // partial must hold ctb_sumsq_parts() floats.
 CTB_API int ctb_sumsq_parts() { return sm_count() * 4; }
-CTB_API int ctb_sumsq(const void* x, long n, int is_f32, float* partial, void* stream) {
+// round_bf16: square the bf16 rounding of each fp32 element (the norm of gradients "cast to
+// the parameter dtype" without materialising the cast).
+CTB_API int ctb_sumsq(const void* x, long n, int is_f32, int round_bf16, float* partial, void* stream) {
   const int grid = ctb_sumsq_parts();
   cudaStream_t s = static_cast<cudaStream_t>(stream);
-  if (is_f32) sumsq_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), n, partial);
-  else sumsq_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), n, partial);
+  if (is_f32) sumsq_kernel<float><<<grid, 256, 0, s>>>(static_cast<const float*>(x), n, partial, round_bf16);
+  else sumsq_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<const __nv_bfloat16*>(x), n, partial, 0);
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
 CTB_API int ctb_adamw(void* p, const void* g, int g_f32, void* m, void* v, long n, float lr, float b1, float b2,
-                      float eps, float decay, float bc1, float bc2, const float* clip, float gscale, void* stream) {
+                      float eps, float decay, float bc1, float bc2, const float* clip, float gscale, int round_bf16,
+                      void* stream) {
   cudaStream_t s = static_cast<cudaStream_t>(stream);
   const int grid = grid_for(n, 256, 16);
   if (g_f32)
     adamw_kernel<float><<<grid, 256, 0, s>>>(static_cast<__nv_bfloat16*>(p), static_cast<const float*>(g),
                                               static_cast<__nv_bfloat16*>(m), static_cast<__nv_bfloat16*>(v), n, lr,
-                                              b1, b2, eps, decay, bc1, bc2, clip, gscale);
+                                              b1, b2, eps, decay, bc1, bc2, clip, gscale, round_bf16);
   else
     adamw_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(static_cast<__nv_bfloat16*>(p),
                                                       static_cast<const __nv_bfloat16*>(g),
                                                       static_cast<__nv_bfloat16*>(m), static_cast<__nv_bfloat16*>(v), n,
-                                                      lr, b1, b2, eps, decay, bc1, bc2, clip, gscale);
+                                                      lr, b1, b2, eps, decay, bc1, bc2, clip, gscale, 0);
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
 }

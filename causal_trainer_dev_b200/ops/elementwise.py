@@ -164,13 +164,17 @@ def attention_delta(o: torch.Tensor, dout: torch.Tensor) -> torch.Tensor:
 
 
 # ------------------------------------------------------------------------------ optimizer pieces
-def sum_of_squares(x: torch.Tensor) -> torch.Tensor:
-    """fp32 scalar tensor on the device (no host sync)."""
+def sum_of_squares(x: torch.Tensor, round_bf16: bool = False) -> torch.Tensor:
+    """fp32 scalar tensor on the device (no host sync).
+
+    ``round_bf16`` squares the bf16 rounding of fp32 elements: the norm of gradients cast to
+    the parameter dtype, without writing the cast anywhere."""
     L = _lib.lib()
     parts = L.ctb_sumsq_parts()
     partial = torch.empty(parts, dtype=torch.float32, device=x.device)
     flat = x.reshape(-1)
-    _lib.check(L.ctb_sumsq(_lib.ptr(flat), _l(flat.numel()), int(x.dtype == torch.float32), _lib.ptr(partial),
+    _lib.check(L.ctb_sumsq(_lib.ptr(flat), _l(flat.numel()), int(x.dtype == torch.float32), int(round_bf16),
+                           _lib.ptr(partial),
                            _lib.stream_ptr()), "ctb_sumsq")
     return partial.sum()
 
@@ -186,11 +190,12 @@ def adamw_reference(p, g, m, v, *, lr, b1, b2, eps, decay, step, clip=1.0, gscal
     p.copy_((p.float() + upd.to(p.dtype).float()).to(p.dtype))
 
 
-def adamw_update(p, g, m, v, *, lr, b1, b2, eps, decay, step, clip: torch.Tensor | None = None, gscale=1.0) -> None:
+def adamw_update(p, g, m, v, *, lr, b1, b2, eps, decay, step, clip: torch.Tensor | None = None, gscale=1.0,
+                 round_bf16: bool = False) -> None:
     n = p.numel()
     code = _lib.lib().ctb_adamw(
         _lib.ptr(p), _lib.ptr(g), int(g.dtype == torch.float32), _lib.ptr(m), _lib.ptr(v), _l(n), _f(lr), _f(b1),
         _f(b2), _f(eps), _f(decay), _f(1 - b1 ** step), _f(1 - b2 ** step), _lib.ptr(clip), _f(gscale),
-        _lib.stream_ptr(),
+        int(round_bf16), _lib.stream_ptr(),
     )
     _lib.check(code, "ctb_adamw")

@@ -47,7 +47,17 @@ def require_gpu_lib() -> None:
         lib()
 
 
+_LAUNCHES = 0
+
+
+def launch_count() -> int:
+    """Number of library calls that launched kernels since import (each launches >= 1)."""
+    return _LAUNCHES
+
+
 def check(code: int, what: str) -> None:
+    global _LAUNCHES
+    _LAUNCHES += 1
     if code != 0:
         raise KernelError(f"{what}: {lib().ctb_last_error().decode()}")
 

@@ -71,17 +71,23 @@ class FlatAdamW:
         return [t for pair in zip(self.m, self.v) for t in pair]
 
     @staticmethod
-    def global_norm(grads: list[torch.Tensor]) -> torch.Tensor:
+    def global_norm(grads: list[torch.Tensor], round_bf16: bool = False) -> torch.Tensor:
         total = None
         for g in grads:
-            sq = ew.sum_of_squares(g) if g.is_cuda and g.dtype in (torch.bfloat16, torch.float32) else g.float().pow(2).sum()
+            if g.is_cuda and g.dtype in (torch.bfloat16, torch.float32):
+                sq = ew.sum_of_squares(g, round_bf16=round_bf16)
+            else:
+                sq = g.float().pow(2).sum()
             total = sq if total is None else total + sq
         return torch.sqrt(total)
 
     def update(self, grads: list[torch.Tensor], lr: float, grad_norm: torch.Tensor | None = None) -> torch.Tensor:
         c = self.cfg
+        # fp32 accumulators feeding bf16 parameters: the cast to the parameter dtype happens
+        # inside the kernels (norm and update both see the rounded value).
+        rounding = [g.dtype == torch.float32 and p.dtype == torch.bfloat16 for (p, _), g in zip(self.regions, grads)]
         if grad_norm is None:
-            grad_norm = self.global_norm(grads)
+            grad_norm = self.global_norm(grads, round_bf16=any(rounding))
         clip = torch.ones_like(grad_norm)
         if c.max_grad_norm > 0:
             clip = torch.clamp(c.max_grad_norm / torch.clamp(grad_norm, min=1e-16), max=1.0)
@@ -92,7 +98,8 @@ class FlatAdamW:
                       step=self.count)
             with torch.no_grad():
                 if p.is_cuda and p.dtype == torch.bfloat16:
-                    ew.adamw_update(p, g, m, v, clip=clip.float().reshape(1), **kw)
+                    ew.adamw_update(p, g, m, v, clip=clip.float().reshape(1), round_bf16=g.dtype == torch.float32,
+                                    **kw)
                 else:
                     ew.adamw_reference(p, g, m, v, clip=float(clip), **kw)
         return grad_norm

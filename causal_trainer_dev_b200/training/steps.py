@@ -154,7 +154,7 @@ class TrainStep:
             g = g_of()
             if distributed:
                 dist.all_reduce(g, group=self.dp_group)
-            grads.append(g.to(p.dtype))
+            grads.append(g if (g.is_cuda and p.dtype == torch.bfloat16) else g.to(p.dtype))
         step = self.optimizer.count if lr_position is None else lr_position
         lr = learning_rate_at(self.schedule, step)
         grad_norm = self.optimizer.update(grads, lr)
