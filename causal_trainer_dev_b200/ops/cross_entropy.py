@@ -76,9 +76,14 @@ def cut_ce_forward(hidden, head, targets, weights, grad_scale: float = 1.0):
     tgt = targets.to(torch.int32).contiguous()
     w = weights.to(torch.float32).contiguous()
     L = _lib.lib()
+    from .gemm import _FLAG_SOURCES, flag_source_of
+
+    hit = flag_source_of(head) if _FLAG_SOURCES else None
+    fl, chunk, base, epoch = (None, 0, 0, 0) if hit is None else (hit[0].flags, hit[0].chunk_elems, hit[1], hit[0].epoch)
     code = L.ctb_ce_stats(_lib.ptr(hidden), _lib.ptr(head), rows, vocab, d, ctypes.c_long(hidden.stride(0)),
                           ctypes.c_long(head.stride(0)), _lib.ptr(tgt), _lib.ptr(pmax), _lib.ptr(psum),
-                          _lib.ptr(tlogit), _lib.stream_ptr())
+                          _lib.ptr(tlogit), _lib.ptr(fl), ctypes.c_long(chunk), ctypes.c_long(base),
+                          ctypes.c_uint(epoch), _lib.stream_ptr())
     _lib.check(code, "ctb_ce_stats")
     lse = torch.empty(rows, dtype=torch.float32, device=dev)
     coef = torch.empty(rows, dtype=torch.float32, device=dev)

@@ -123,12 +123,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       uint32_t armed = 0;      // bit s set: full[s] was armed by this thread at least once
       uint32_t armed_par = 0;  // bit s: parity of the phase last armed on full[s]
       bool ok = true;
+      bool flags_all_seen = false;
       for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
         const TileCoord tc = tile_coord(tile, num_m, num_n);
-        if (args.b_flags != nullptr) {
-          // Rows [n0, n0+BN) of B must have landed in this GPU's memory.
-          const int first = tc.n0 / args.b_flag_rows;
-          const int last = (min(tc.n0 + BN, args.N) - 1) / args.b_flag_rows;
+        if (args.b_flags != nullptr && !(flags_all_seen)) {
+          // The elements of B this tile reads must have landed in this GPU's memory.  A
+          // K-major B tile is rows [n0, n0+BN) of the weight; an MN-major B (dgrad) strides
+          // over the whole matrix, so it waits for all of it once.
+          long e0, e1;
+          if (B_MN || args.b_wait_all) {
+            e0 = args.b_flag_base;
+            e1 = args.b_flag_base + static_cast<long>(B_MN ? args.K : args.N) * args.ldb;
+            flags_all_seen = true;
+          } else {
+            const int nend = min(tc.n0 + BN, args.N);
+            e0 = args.b_flag_base + static_cast<long>(tc.n0) * args.ldb;
+            e1 = args.b_flag_base + static_cast<long>(nend - 1) * args.ldb + args.K;
+          }
+          const int first = static_cast<int>(e0 / args.b_flag_chunk);
+          const int last = static_cast<int>((e1 - 1) / args.b_flag_chunk);
           for (int f = first; ok && f <= last; ++f) {
             const long long t0 = clock64();
             while (true) {
@@ -450,8 +463,11 @@ int run_gemm(const GemmCall& c) {
   a.status = device_status();
   a.spin_budget = c.spin_budget > 0 ? c.spin_budget : CTB_SPIN_BUDGET;
   a.b_flags = c.b_flags;
-  a.b_flag_rows = c.b_flag_rows > 0 ? c.b_flag_rows : 1;
+  a.b_flag_chunk = c.b_flag_chunk > 0 ? c.b_flag_chunk : 1;
+  a.b_flag_base = c.b_flag_base;
   a.b_flag_epoch = c.b_flag_epoch;
+  a.b_wait_all = c.b_wait_all;
+  a.ldb = c.ldb;
   a.ce_targets = c.ce_targets;
   a.ce_max = c.ce_max;
   a.ce_sum = c.ce_sum;
@@ -489,15 +505,19 @@ CTB_API int ctb_gemm(const void* A, const void* B, void* C, int M, int N, int K,
   return ctb::run_gemm(c);
 }
 
-// Same GEMM whose B rows are published by another kernel: flags[i] >= epoch means rows
-// [i*flag_rows, (i+1)*flag_rows) of B are complete in local memory.
+// Same GEMM family whose B operand lives in a buffer that another kernel (the all-gather
+// pull) is still filling: flags[i] >= epoch means elements [i*chunk, (i+1)*chunk) of that
+// buffer are complete; `flag_base` is the element offset of B inside the buffer.
 CTB_API int ctb_gemm_flagged(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
-                             const void* bias, const unsigned* flags, int flag_rows, unsigned epoch,
+                             int a_mn, int b_mn, int out_f32, int accumulate, float alpha, const void* bias,
+                             const unsigned* flags, long flag_chunk, long flag_base, unsigned epoch, int wait_all,
                              long long spin_budget, int max_ctas, void* stream) {
   ctb::GemmCall c{};
   c.A = A; c.B = B; c.C = C; c.M = M; c.N = N; c.K = K; c.lda = lda; c.ldb = ldb; c.ldc = ldc;
-  c.alpha = 1.f; c.bias = bias; c.epi = ctb::EPI_STORE; c.max_ctas = max_ctas; c.stream = stream;
-  c.b_flags = flags; c.b_flag_rows = flag_rows; c.b_flag_epoch = epoch; c.spin_budget = spin_budget;
+  c.a_mn = a_mn; c.b_mn = b_mn; c.out_f32 = out_f32; c.accumulate = accumulate; c.alpha = alpha; c.bias = bias;
+  c.epi = ctb::EPI_STORE; c.max_ctas = max_ctas; c.stream = stream;
+  c.b_flags = flags; c.b_flag_chunk = flag_chunk; c.b_flag_base = flag_base; c.b_flag_epoch = epoch;
+  c.b_wait_all = wait_all; c.spin_budget = spin_budget;
   return ctb::run_gemm(c);
 }
 
@@ -505,8 +525,10 @@ CTB_API int ctb_gemm_flagged(const void* A, const void* B, void* C, int M, int N
 // 256-column slab to pmax/psum[slab][row]; target_logit[row] is written by the slab that
 // holds the row's target (rows with target < 0 are never written).
 CTB_API int ctb_ce_stats(const void* hidden, const void* head, int rows, int vocab, int d, long ldh, long ldw,
-                         const int* targets, float* pmax, float* psum, float* target_logit, void* stream) {
+                         const int* targets, float* pmax, float* psum, float* target_logit, const unsigned* flags,
+                         long flag_chunk, long flag_base, unsigned epoch, void* stream) {
   ctb::GemmCall c{};
+  c.b_flags = flags; c.b_flag_chunk = flag_chunk; c.b_flag_base = flag_base; c.b_flag_epoch = epoch;
   c.A = hidden; c.B = head; c.M = rows; c.N = vocab; c.K = d; c.lda = ldh; c.ldb = ldw;
   c.epi = ctb::EPI_CE_STATS; c.stream = stream;
   c.ce_targets = targets; c.ce_max = pmax; c.ce_sum = psum; c.ce_target_logit = target_logit;

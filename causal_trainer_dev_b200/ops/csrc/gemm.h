@@ -20,8 +20,11 @@ struct GemmArgs {
   DeviceStatus* status;
   long long spin_budget;
   const unsigned* b_flags;
-  int b_flag_rows;
+  long b_flag_chunk;
+  long b_flag_base;
   unsigned b_flag_epoch;
+  int b_wait_all;
+  long ldb;
   const int* ce_targets;
   float* ce_max;
   float* ce_sum;
@@ -45,8 +48,10 @@ struct GemmCall {
   int max_ctas = 0;
   void* stream = nullptr;
   const unsigned* b_flags = nullptr;
-  int b_flag_rows = 0;
+  long b_flag_chunk = 0;
+  long b_flag_base = 0;
   unsigned b_flag_epoch = 0;
+  int b_wait_all = 0;
   long long spin_budget = 0;
   const int* ce_targets = nullptr;
   float* ce_max = nullptr;

@@ -17,6 +17,39 @@ import torch
 from . import lib as _lib
 
 
+class FlagSource:
+    """A gathered buffer that an all-gather pull is filling, with its per-chunk flags."""
+
+    def __init__(self, buffer: torch.Tensor, flags: torch.Tensor, chunk_elems: int):
+        self.start = buffer.data_ptr()
+        self.end = self.start + buffer.numel() * buffer.element_size()
+        self.flags = flags
+        self.chunk_elems = chunk_elems
+        self.epoch = 0
+        self.spin_budget = 0
+
+
+_FLAG_SOURCES: list[FlagSource] = []
+
+
+def register_flag_source(src: FlagSource) -> None:
+    """GEMMs whose B operand lies inside ``src`` acquire its flags tile by tile."""
+    _FLAG_SOURCES.append(src)
+
+
+def unregister_flag_source(src: FlagSource) -> None:
+    if src in _FLAG_SOURCES:
+        _FLAG_SOURCES.remove(src)
+
+
+def flag_source_of(t: torch.Tensor) -> tuple[FlagSource, int] | None:
+    p = t.data_ptr()
+    for src in _FLAG_SOURCES:
+        if src.start <= p < src.end and src.epoch > 0:
+            return src, (p - src.start) // t.element_size()
+    return None
+
+
 def _check_operand(t: torch.Tensor, name: str) -> None:
     if t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1 or not t.is_cuda:
         raise ValueError(f"{name} must be a 2-D bf16 CUDA tensor with unit inner stride")
@@ -49,6 +82,18 @@ def gemm(
         raise ValueError("out must be [M,N] bf16/fp32 with unit inner stride")
     if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != n):
         raise ValueError("bias must be bf16 of length N")
+    hit = flag_source_of(b) if _FLAG_SOURCES else None
+    if hit is not None:
+        src, base = hit
+        code = _lib.lib().ctb_gemm_flagged(
+            _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), m, n, k,
+            ctypes.c_long(a.stride(0)), ctypes.c_long(b.stride(0)), ctypes.c_long(out.stride(0)),
+            int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), ctypes.c_float(alpha),
+            _lib.ptr(bias), _lib.ptr(src.flags), ctypes.c_long(src.chunk_elems), ctypes.c_long(base),
+            ctypes.c_uint(src.epoch), 0, ctypes.c_longlong(src.spin_budget), max_ctas, _lib.stream_ptr(),
+        )
+        _lib.check(code, "ctb_gemm_flagged")
+        return out
     code = _lib.lib().ctb_gemm(
         _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), m, n, k,
         ctypes.c_long(a.stride(0)), ctypes.c_long(b.stride(0)), ctypes.c_long(out.stride(0)),

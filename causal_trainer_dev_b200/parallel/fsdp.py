@@ -1,0 +1,425 @@
+"""FSDP (ZeRO-3) runtime over NVLink peer memory: explicit schedule, fused collectives.
+
+The reference gets FSDP implicitly: weights carry an ``fsdp`` axis in their PartitionSpec
+and GSPMD inserts an all-gather before each use and a reduce-scatter of the gradients
+(src/causal_trainer/distributed/runtime.py:334-360, src/causal_trainer/training/steps.py:
+200-208, 560-588).  There is no compiler here, so the schedule is written out:
+
+* every *unit* (embedding, one decoder layer, final norm + LM head) is one flat bf16 buffer,
+  padded to ``world * CHUNK`` elements and split evenly; rank r owns slice r together with
+  its AdamW moments and (with several micro-batches) an fp32 gradient accumulator;
+* parameter shards live in **symmetric memory**: every rank maps every peer's arena;
+* **all-gather -> GEMM**: ``acquire(unit, prefetch=next)`` launches the pull kernel for the
+  next unit on a side stream; the pull publishes a flag per 128 KiB chunk and the tcgen05
+  GEMMs that read the gathered weights acquire exactly the flags their B tile needs
+  (``ops/csrc/gemm.cu``), so no stream-level dependency sits between transfer and math;
+* **reduce-scatter -> cast -> sum-of-squares -> AdamW**: weight gradients are written in bf16
+  straight into a symmetric staging slot, ``grads_ready`` publishes a flag to all peers and
+  launches the fused reduce kernel on the side stream (``ops/csrc/collectives.cu``); the
+  global-norm clip needs one 4-byte all-reduce, after which AdamW sweeps the shards (when
+  clipping is off the update happens inside the reduce kernel);
+* an NCCL-only variant of the same schedule (``fused=False``) is the measured baseline.
+
+All cross-rank waits are bounded device-side spins; nothing here can hang a GPU.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+
+import torch
+import torch.distributed as dist
+
+from ..models.config import ModelConfig
+from ..models.params import Unit, UnitLayout, unit_layouts
+from ..ops import elementwise as ew
+from ..ops import lib as _lib
+from ..ops.gemm import FlagSource, register_flag_source
+from ..training import losses
+from ..training.optimizer import learning_rate_at
+from ..training.steps import StepMetrics
+
+CHUNK = 65536          # elements per flag (128 KiB of bf16)
+N_GATHER = 3           # gathered-unit buffers (current, prefetched, draining)
+N_SLOTS = 3            # gradient staging slots
+PULL_CTAS = 24
+REDUCE_CTAS = 32
+
+
+def _ptr_array(ptrs: list[int]):
+    arr = (ctypes.c_void_p * len(ptrs))()
+    for i, p in enumerate(ptrs):
+        arr[i] = p
+    return arr
+
+
+@dataclass
+class _UnitState:
+    layout: UnitLayout
+    padded: int
+    shard_elems: int
+    arena_offset: int          # element offset of this unit's shard in the parameter arena
+    has_gaps: bool
+
+
+class _Gathered:
+    def __init__(self, elems: int, device):
+        self.buffer = torch.zeros(elems, dtype=torch.bfloat16, device=device)
+        self.flags = torch.zeros(elems // CHUNK + 1, dtype=torch.int32, device=device)
+        self.source = FlagSource(self.buffer, self.flags, CHUNK)
+        self.unit: str | None = None
+        self.epoch = 0
+        self.pull_done = torch.cuda.Event()
+        self.free_event: torch.cuda.Event | None = None   # main stream finished with the occupant
+        register_flag_source(self.source)
+
+
+class FsdpRuntime:
+    """Weight provider (see ``training.engine``) plus the sharded optimizer step."""
+
+    def __init__(self, cfg: ModelConfig, tcfg, device: torch.device, group=None):
+        _lib.require_gpu_lib()
+        import torch.distributed._symmetric_memory as symm_mem
+
+        self.cfg, self.tcfg, self.device = cfg, tcfg, device
+        self.group = group if group is not None else dist.group.WORLD
+        self.world = dist.get_world_size(self.group)
+        self.rank = dist.get_rank(self.group)
+        self.fused = bool(getattr(tcfg, "fused_collectives", True))
+        self.grad_dtype = torch.bfloat16
+        self.main = torch.cuda.current_stream(device)
+        self.side = torch.cuda.Stream(device, priority=-1)
+        self.spin_budget = 4_000_000_000
+        L = _lib.lib()
+        if self.world > L.ctb_max_ranks():
+            raise ValueError("too many ranks for the peer-pointer tables")
+
+        # ---- unit geometry ----
+        self.units: dict[str, _UnitState] = {}
+        off = 0
+        grain = self.world * CHUNK
+        for lay in unit_layouts(cfg):
+            padded = (lay.numel + grain - 1) // grain * grain
+            covered = sum(s.numel for s in lay.segments)
+            self.units[lay.name] = _UnitState(lay, padded, padded // self.world, off, covered != lay.numel)
+            off += padded // self.world
+        self.arena_elems = off
+        self.max_padded = max(u.padded for u in self.units.values())
+        self.order = list(self.units)
+
+        # ---- symmetric memory: parameter shards, gradient staging, signal pads ----
+        gname = self.group.group_name
+        try:
+            symm_mem.enable_symm_mem_for_group(gname)
+        except Exception:  # newer torch enables groups lazily
+            pass
+        self.param_arena = symm_mem.empty(self.arena_elems, dtype=torch.bfloat16, device=device)
+        self.h_params = symm_mem.rendezvous(self.param_arena, gname)
+        self.staging = symm_mem.empty(N_SLOTS * self.max_padded, dtype=torch.bfloat16, device=device)
+        self.h_staging = symm_mem.rendezvous(self.staging, gname)
+        self.pads = symm_mem.empty(2 * N_SLOTS * self.world + 64, dtype=torch.int32, device=device)
+        self.pads.zero_()
+        self.h_pads = symm_mem.rendezvous(self.pads, gname)
+        self.param_arena.zero_()
+        self.staging.zero_()
+        torch.cuda.synchronize(device)
+        dist.barrier(self.group)
+        self.param_ptrs = [int(p) for p in self.h_params.buffer_ptrs]
+        self.staging_ptrs = [int(p) for p in self.h_staging.buffer_ptrs]
+        self.pad_ptrs = [int(p) for p in self.h_pads.buffer_ptrs]
+        self.ready_base = 0                       # pads[slot*world + rank]
+        self.done_base = N_SLOTS * self.world     # pads[done_base + slot*world + rank]
+
+        # ---- local state ----
+        self.m = torch.zeros(self.arena_elems, dtype=torch.bfloat16, device=device)
+        self.v = torch.zeros(self.arena_elems, dtype=torch.bfloat16, device=device)
+        self.grad_shards = torch.zeros(self.arena_elems, dtype=torch.bfloat16, device=device)
+        self.accum: torch.Tensor | None = None
+        self.sumsq = torch.zeros((len(self.units), REDUCE_CTAS), dtype=torch.float32, device=device)
+        self.finish_counter = torch.zeros(1, dtype=torch.int32, device=device)
+        self.gathered = [_Gathered(self.max_padded, device) for _ in range(N_GATHER)]
+        self.where: dict[str, _Gathered] = {}
+        self.slot_of: dict[str, int] = {}
+        self.slot_epoch = [0] * N_SLOTS          # epoch last published for each slot
+        self.slot_counter = 0
+        self.epoch = 0
+        self.count = 0                           # optimizer steps taken
+        self.mb_first = True
+        self.mb_last = True
+        self._init_parameters()
+
+    # ------------------------------------------------------------------ parameters
+    def shard_view(self, name: str, of: torch.Tensor | None = None) -> torch.Tensor:
+        u = self.units[name]
+        base = self.param_arena if of is None else of
+        return base[u.arena_offset:u.arena_offset + u.shard_elems]
+
+    def _init_parameters(self) -> None:
+        """Random N(0, initializer_range) weights, identical to a single-replica initialisation:
+        every rank draws the full unit from the same seeded generator and keeps its slice."""
+        cfg = self.cfg
+        gen = torch.Generator(device=self.device).manual_seed(self.tcfg.seed)
+        scratch = torch.zeros(self.max_padded, dtype=torch.bfloat16, device=self.device)
+        for name, u in self.units.items():
+            scratch.zero_()
+            unit = Unit(u.layout, scratch)
+            for seg in u.layout.segments:
+                t = unit.view(seg.name)
+                if seg.name in ("ln1", "ln2", "norm"):
+                    t.fill_(1.0)
+                elif seg.name.endswith("_b"):
+                    t.zero_()
+                else:
+                    t.normal_(0.0, cfg.initializer_range, generator=gen)
+            if name == "embed":
+                unit.view("embed")[cfg.pad_token_id].zero_()
+            lo = self.rank * u.shard_elems
+            self.shard_view(name).copy_(scratch[lo:lo + u.shard_elems])
+        del scratch
+        torch.cuda.synchronize(self.device)
+        dist.barrier(self.group)
+
+    def load_full_unit(self, name: str, full: torch.Tensor) -> None:
+        """Stores this rank's slice of a full (unpadded) unit buffer."""
+        u = self.units[name]
+        lo = self.rank * u.shard_elems
+        hi = min(lo + u.shard_elems, full.numel())
+        view = self.shard_view(name)
+        view.zero_()
+        if hi > lo:
+            view[:hi - lo].copy_(full[lo:hi])
+
+    def gather_full_unit(self, name: str) -> torch.Tensor:
+        """Full unit on every rank through NCCL (checkpoint export, tests)."""
+        u = self.units[name]
+        out = torch.empty(u.padded, dtype=torch.bfloat16, device=self.device)
+        dist.all_gather_into_tensor(out, self.shard_view(name).contiguous(), group=self.group)
+        return out[:u.layout.numel]
+
+    def set_grad_dtype(self, dtype: torch.dtype) -> None:
+        if dtype == torch.float32 and self.accum is None:
+            self.accum = torch.zeros(self.arena_elems, dtype=torch.float32, device=self.device)
+
+    # ------------------------------------------------------------------ all-gather (pull) + flags
+    def _pick_buffer(self, keep: set[str]) -> _Gathered:
+        for g in self.gathered:
+            if g.unit is None:
+                return g
+        for g in self.gathered:
+            if g.unit not in keep:
+                return g
+        raise RuntimeError("no gathered buffer free")
+
+    def _start_pull(self, name: str, keep: set[str]) -> _Gathered:
+        g = self._pick_buffer(keep | {name})
+        if g.unit is not None:
+            self.where.pop(g.unit, None)
+        u = self.units[name]
+        self.epoch += 1
+        g.unit, g.epoch = name, self.epoch
+        g.source.epoch = self.epoch
+        g.source.spin_budget = self.spin_budget
+        self.where[name] = g
+        if g.free_event is not None:
+            self.side.wait_event(g.free_event)
+        with torch.cuda.stream(self.side):
+            if self.fused:
+                ptrs = _ptr_array([p + 2 * u.arena_offset for p in self.param_ptrs])
+                code = _lib.lib().ctb_ag_pull(ptrs, _lib.ptr(g.buffer), ctypes.c_long(u.shard_elems), self.rank,
+                                              self.world, CHUNK, _lib.ptr(g.flags), ctypes.c_uint(self.epoch),
+                                              PULL_CTAS, ctypes.c_void_p(self.side.cuda_stream))
+                _lib.check(code, "ctb_ag_pull")
+            else:
+                dist.all_gather_into_tensor(g.buffer[:u.padded], self.shard_view(name), group=self.group)
+                g.flags.fill_(self.epoch)
+            g.pull_done.record(self.side)
+        return g
+
+    def acquire(self, name: str, prefetch: str | None = None) -> Unit:
+        keep = {name} | ({prefetch} if prefetch else set())
+        g = self.where.get(name)
+        if g is None:
+            g = self._start_pull(name, keep)
+        if prefetch is not None and prefetch not in self.where:
+            self._start_pull(prefetch, keep)
+        u = self.units[name]
+        if self.fused and name.startswith("layer."):
+            # vectors (norm scales, biases) are read by non-GEMM kernels: wait for their chunks only
+            nvec = max(1, math.ceil(u.layout.vector_numel / CHUNK))
+            code = _lib.lib().ctb_wait_flags(_lib.ptr(g.flags), 0, 1, nvec, ctypes.c_uint(g.epoch),
+                                             ctypes.c_longlong(self.spin_budget), _lib.stream_ptr())
+            _lib.check(code, "ctb_wait_flags")
+        elif self.fused and name == "final":
+            code = _lib.lib().ctb_wait_flags(_lib.ptr(g.flags), 0, 1, 1, ctypes.c_uint(g.epoch),
+                                             ctypes.c_longlong(self.spin_budget), _lib.stream_ptr())
+            _lib.check(code, "ctb_wait_flags")
+        else:
+            self.main.wait_event(g.pull_done)   # embedding rows are gathered at random: whole unit
+        return Unit(u.layout, g.buffer[:u.layout.numel])
+
+    def release(self, name: str) -> None:
+        g = self.where.get(name)
+        if g is not None:
+            ev = torch.cuda.Event()
+            ev.record(self.main)
+            g.free_event = ev
+
+    # ------------------------------------------------------------------ gradients
+    def grad_buffer(self, name: str) -> torch.Tensor:
+        if name in self.slot_of:
+            slot = self.slot_of[name]
+        else:
+            slot = self.slot_counter % N_SLOTS
+            self.slot_counter += 1
+            self.slot_of[name] = slot
+            prev = self.slot_epoch[slot]
+            if prev > 0 and self.fused:
+                # every peer must have finished reducing the previous occupant of this slot
+                code = _lib.lib().ctb_wait_flags(_lib.ptr(self.pads), self.done_base + slot * self.world, 1,
+                                                 self.world, ctypes.c_uint(prev), ctypes.c_longlong(self.spin_budget),
+                                                 _lib.stream_ptr())
+                _lib.check(code, "ctb_wait_flags")
+            elif prev > 0:
+                self.main.wait_stream(self.side)
+            u = self.units[name]
+            view = self.staging[slot * self.max_padded:slot * self.max_padded + u.padded]
+            if u.has_gaps:
+                view.zero_()
+            else:
+                view[u.layout.numel:].zero_()
+        return self.staging[slot * self.max_padded:slot * self.max_padded + self.units[name].padded]
+
+    def grads_ready(self, name: str, last_microbatch: bool) -> None:
+        u = self.units[name]
+        slot = self.slot_of.pop(name)
+        self.epoch += 1
+        epoch = self.epoch
+        self.slot_epoch[slot] = epoch
+        idx = self.order.index(name)
+        first, last = self.mb_first, self.mb_last
+        L = _lib.lib()
+        off = u.arena_offset
+        if self.fused:
+            code = L.ctb_signal_peers(_ptr_array(self.pad_ptrs), self.world, self.ready_base + slot * self.world + self.rank,
+                                      ctypes.c_uint(epoch), _lib.stream_ptr())
+            _lib.check(code, "ctb_signal_peers")
+            ev = torch.cuda.Event()
+            ev.record(self.main)
+            self.side.wait_event(ev)
+            accum = self.accum[off:off + u.shard_elems] if self.accum is not None else None
+            staging = _ptr_array([p + 2 * slot * self.max_padded for p in self.staging_ptrs])
+            done = _ptr_array([p + 4 * (self.done_base + slot * self.world + self.rank) for p in self.pad_ptrs])
+            with torch.cuda.stream(self.side):
+                code = L.ctb_rs_reduce(
+                    staging, ctypes.c_long(self.rank * u.shard_elems), ctypes.c_long(u.shard_elems), self.world,
+                    _lib.ptr(self.pads), self.ready_base + slot * self.world, ctypes.c_uint(epoch),
+                    _lib.ptr(accum), int(not first), int(last),
+                    _lib.ptr(self.grad_shards[off:off + u.shard_elems]), _lib.ptr(self.sumsq[idx]),
+                    0, None, None, None, ctypes.c_long(0), *(ctypes.c_float(0.0),) * 7,
+                    done, 0, _lib.ptr(self.finish_counter), REDUCE_CTAS, ctypes.c_longlong(self.spin_budget),
+                    ctypes.c_void_p(self.side.cuda_stream),
+                )
+                _lib.check(code, "ctb_rs_reduce")
+        else:
+            ev = torch.cuda.Event()
+            ev.record(self.main)
+            self.side.wait_event(ev)
+            with torch.cuda.stream(self.side):
+                src = self.staging[slot * self.max_padded:slot * self.max_padded + u.padded]
+                red = torch.empty(u.shard_elems, dtype=torch.bfloat16, device=self.device)
+                dist.reduce_scatter_tensor(red, src, group=self.group)
+                if self.accum is not None:
+                    acc = self.accum[off:off + u.shard_elems]
+                    if first:
+                        acc.copy_(red)
+                    else:
+                        acc.add_(red)
+                    final = acc
+                else:
+                    final = red
+                if last:
+                    g = self.grad_shards[off:off + u.shard_elems]
+                    g.copy_(final)
+                    self.sumsq[idx].zero_()
+                    self.sumsq[idx, 0] = g.float().pow(2).sum()
+
+    # ------------------------------------------------------------------ optimizer step
+    def _adam_regions(self, name: str) -> list[tuple[int, int, bool]]:
+        """(start, stop, decay) pieces of this rank's shard, in shard-local element indices."""
+        u = self.units[name]
+        lo = self.rank * u.shard_elems
+        hi = lo + u.shard_elems
+        cut = min(max(u.layout.vector_numel, lo), hi)
+        out = []
+        if cut > lo:
+            out.append((0, cut - lo, False))
+        if hi > cut:
+            out.append((cut - lo, hi - lo, True))
+        return out
+
+    def apply_update(self, lr: float) -> torch.Tensor:
+        a = self.tcfg.adamw
+        self.main.wait_stream(self.side)
+        total = self.sumsq.sum().reshape(1)
+        dist.all_reduce(total, group=self.group)          # also orders every peer's pulls before the update
+        grad_norm = torch.sqrt(total)
+        clip = torch.ones_like(grad_norm)
+        if a.max_grad_norm > 0:
+            clip = torch.clamp(a.max_grad_norm / torch.clamp(grad_norm, min=1e-16), max=1.0)
+            clip = torch.where(torch.isfinite(grad_norm), clip, torch.ones_like(clip))
+        self.count += 1
+        for name, u in self.units.items():
+            off = u.arena_offset
+            for lo, hi, decay in self._adam_regions(name):
+                sl = slice(off + lo, off + hi)
+                ew.adamw_update(self.param_arena[sl], self.grad_shards[sl], self.m[sl], self.v[sl], lr=lr, b1=a.beta1,
+                                b2=a.beta2, eps=a.epsilon, decay=a.weight_decay if decay else 0.0, step=self.count,
+                                clip=clip)
+        fence = torch.zeros(1, device=self.device)
+        dist.all_reduce(fence, group=self.group)          # nobody pulls before every shard is updated
+        self.where.clear()
+        for g in self.gathered:
+            g.unit = None
+        return grad_norm[0]
+
+    # ------------------------------------------------------------------ step driver
+    def make_step(self, engine) -> "FsdpStep":
+        return FsdpStep(self, engine)
+
+
+class FsdpStep:
+    """Counterpart of ``training.steps.TrainStep`` for sharded state."""
+
+    def __init__(self, runtime: FsdpRuntime, engine):
+        self.rt = runtime
+        self.engine = engine
+
+    @property
+    def optimizer_step(self) -> int:
+        return self.rt.count
+
+    def run(self, micro_batches: list[dict[str, torch.Tensor]], lr_position: int | None = None) -> StepMetrics:
+        rt = self.rt
+        total = None
+        for b in micro_batches:
+            _, w = losses.aligned_targets_and_weights(b)
+            s = w.sum(dtype=torch.float32)
+            total = s if total is None else total + s
+        total = total.reshape(1).clone()
+        dist.all_reduce(total, group=rt.group)
+        denom = torch.clamp(total, min=1.0)
+        scale = float(1.0 / denom)
+        if len(micro_batches) > 1:
+            rt.set_grad_dtype(torch.float32)
+        nll_sum = None
+        for i, batch in enumerate(micro_batches):
+            rt.mb_first, rt.mb_last = i == 0, i == len(micro_batches) - 1
+            nll, _ = self.engine(batch, scale, True, rt.mb_last)
+            nll_sum = nll if nll_sum is None else nll_sum + nll
+        nll_sum = nll_sum.reshape(1).clone()
+        dist.all_reduce(nll_sum, group=rt.group)
+        step = rt.count if lr_position is None else lr_position
+        lr = learning_rate_at(rt.tcfg.schedule, step)
+        grad_norm = rt.apply_update(lr)
+        return StepMetrics((nll_sum / denom)[0], nll_sum[0], total[0], grad_norm, lr)

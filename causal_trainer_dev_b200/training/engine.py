@@ -27,7 +27,7 @@ import torch
 
 from ..models.config import ModelConfig
 from ..models.decoder import canonicalize_segment_ids, make_position_ids
-from ..models.params import ModelParams, Unit
+from ..models.params import ModelParams, Unit, embed_layout
 from ..ops import attention as attn_ops
 from ..ops import cross_entropy as ce
 from ..ops import elementwise as ew
@@ -254,8 +254,9 @@ class LayerwiseEngine:
             prov.grads_ready(f"layer.{li}", last)
         # ---------------- embedding ----------------
         if self.options.train_embed:
-            embed = prov.acquire("embed")
-            gbuf = embed.view("embed", of=prov.grad_buffer("embed"))
+            lay = embed_layout(cfg)
+            seg = lay.segment("embed")
+            gbuf = prov.grad_buffer("embed")[seg.offset:seg.offset + seg.numel].view(seg.shape)
             if first:
                 gbuf.zero_()
             ids = batch["input_ids"].reshape(-1)
@@ -265,6 +266,5 @@ class LayerwiseEngine:
             tmp.index_add_(0, inverse, dout[keep].float())
             gbuf[uniq] += tmp.to(gbuf.dtype)
             self._count(8)
-            prov.release("embed")
             prov.grads_ready("embed", last)
         return nll, wsum

@@ -1,0 +1,44 @@
+"""Worker of the multi-GPU FSDP test (launched by torch.distributed.run)."""
+import json
+import os
+import sys
+from pathlib import Path
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
+
+
+def main() -> None:
+    fused = sys.argv[1] == "fused"
+    out_path = sys.argv[2]
+    steps = int(sys.argv[3]) if len(sys.argv) > 3 else 2
+    local = int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    from causal_trainer_dev_b200.api import Trainer, TrainerConfig
+    from causal_trainer_dev_b200.data.synthetic import pretraining_rows
+    from causal_trainer_dev_b200.models.config import preset
+    from causal_trainer_dev_b200.ops import lib
+    from causal_trainer_dev_b200.training.optimizer import AdamWConfig, ScheduleConfig
+
+    world, rank = dist.get_world_size(), dist.get_rank()
+    cfg = preset("tiny", vocab_size=4096, num_hidden_layers=3)
+    tcfg = TrainerConfig(micro_batch_rows=2, adamw=AdamWConfig(weight_decay=0.1, max_grad_norm=1.0),
+                         schedule=ScheduleConfig(1e-3, 0.0, "constant", 0, 10), fused_collectives=fused, seed=3)
+    trainer = Trainer(cfg, tcfg)
+    rows = 8
+    data = pretraining_rows(rows, 256, cfg.vocab_size, eos_token_id=2, pad_token_id=0, median_len=80, min_len=8, seed=5)
+    per = rows // world
+    mine = {k: torch.from_numpy(v[rank * per:(rank + 1) * per].copy()).pin_memory() for k, v in data.items()}
+    history = [trainer.train_step(mine) for _ in range(steps)]
+    status = lib.device_status(raise_on_error=False)
+    checksum = float(trainer.runtime.gather_full_unit("layer.1").float().abs().sum())
+    if rank == 0:
+        Path(out_path).write_text(json.dumps({"history": history, "status": status, "checksum": checksum}))
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
