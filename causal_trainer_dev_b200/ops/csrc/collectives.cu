@@ -31,7 +31,10 @@ namespace ctb {
 namespace coll {
 
 constexpr int MAX_RANKS = 16;
-constexpr int PULL_THREADS = 512;
+// 256 threads and a register cap keep these CTAs small enough to share an SM with a
+// resident tcgen05 GEMM CTA (256 threads x 168 registers, ~225 KiB shared memory), which is
+// what lets the transfer overlap the math instead of queueing behind it.
+constexpr int PULL_THREADS = 256;
 
 struct PeerPtrs {
   const void* p[MAX_RANKS];
@@ -67,7 +70,7 @@ __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
 // ------------------------------------------------------------------------------------------
 // all-gather by pull with per-chunk flags
 // ------------------------------------------------------------------------------------------
-__global__ void __launch_bounds__(PULL_THREADS)
+__global__ void __launch_bounds__(PULL_THREADS, 4)
 ag_pull_kernel(PeerPtrs shards, __nv_bfloat16* __restrict__ gathered, long shard_elems, int rank, int world,
                int chunk_elems, unsigned* __restrict__ flags, unsigned epoch) {
   const int chunks_per_shard = static_cast<int>(shard_elems / chunk_elems);
@@ -89,15 +92,16 @@ ag_pull_kernel(PeerPtrs shards, __nv_bfloat16* __restrict__ gathered, long shard
                                                        static_cast<long>(c) * chunk_elems);
     uint4* to = reinterpret_cast<uint4*>(gathered + static_cast<long>(src) * shard_elems +
                                          static_cast<long>(c) * chunk_elems);
-    for (int v = threadIdx.x; v < vec_per_chunk; v += PULL_THREADS * 4) {
-      uint4 r[4];
+    // 8 x 16 B per thread in flight: a CTA keeps 64 KiB outstanding across the NVLink latency
+    for (int v = threadIdx.x; v < vec_per_chunk; v += PULL_THREADS * 8) {
+      uint4 r[8];
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         const int i = v + u * PULL_THREADS;
         if (i < vec_per_chunk) r[u] = ld_peer(from + i);
       }
 #pragma unroll
-      for (int u = 0; u < 4; ++u) {
+      for (int u = 0; u < 8; ++u) {
         const int i = v + u * PULL_THREADS;
         if (i < vec_per_chunk) to[i] = r[u];
       }
@@ -167,7 +171,58 @@ struct RsArgs {
   DeviceStatus* status;
 };
 
-__global__ void __launch_bounds__(PULL_THREADS)
+// Per-vector tail of the reduce: accumulate / cast / sum of squares / optional AdamW.
+__device__ __forceinline__ void rs_finish_vector(const RsArgs& a, long v, float (&s)[8], float& sq) {
+  if (a.accum != nullptr) {
+    float4* acc = reinterpret_cast<float4*>(a.accum + v * 8);
+    if (a.accumulate_in) {
+      const float4 a0 = acc[0], a1 = acc[1];
+      s[0] += a0.x; s[1] += a0.y; s[2] += a0.z; s[3] += a0.w;
+      s[4] += a1.x; s[5] += a1.y; s[6] += a1.z; s[7] += a1.w;
+    }
+    if (!a.last) {
+      acc[0] = make_float4(s[0], s[1], s[2], s[3]);
+      acc[1] = make_float4(s[4], s[5], s[6], s[7]);
+    }
+  }
+  if (!a.last) return;
+  uint4 out;
+  __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&out);
+  float g[8];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    oh[e] = __floats2bfloat162_rn(s[2 * e], s[2 * e + 1]);
+    const float2 back = __bfloat1622float2(oh[e]);
+    g[2 * e] = back.x;
+    g[2 * e + 1] = back.y;
+    sq += back.x * back.x + back.y * back.y;
+  }
+  if (a.grad_out != nullptr) reinterpret_cast<uint4*>(a.grad_out)[v] = out;
+  if (a.apply_adam) {
+    uint4 pr = reinterpret_cast<const uint4*>(a.param)[v];
+    uint4 mr = reinterpret_cast<const uint4*>(a.m)[v];
+    uint4 vr = reinterpret_cast<const uint4*>(a.v)[v];
+    __nv_bfloat16* pe = reinterpret_cast<__nv_bfloat16*>(&pr);
+    __nv_bfloat16* me = reinterpret_cast<__nv_bfloat16*>(&mr);
+    __nv_bfloat16* ve = reinterpret_cast<__nv_bfloat16*>(&vr);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float dec = (v * 8 + e >= a.decay_from) ? a.decay : 0.f;
+      const float mi = a.b1 * __bfloat162float(me[e]) + (1.f - a.b1) * g[e];
+      const float vi = a.b2 * __bfloat162float(ve[e]) + (1.f - a.b2) * g[e] * g[e];
+      const float pi = __bfloat162float(pe[e]);
+      const float upd = -a.lr * ((mi / a.bc1) / (sqrtf(vi / a.bc2) + a.eps) + dec * pi);
+      me[e] = __float2bfloat16(mi);
+      ve[e] = __float2bfloat16(vi);
+      pe[e] = __float2bfloat16(pi + __bfloat162float(__float2bfloat16(upd)));
+    }
+    reinterpret_cast<uint4*>(a.param)[v] = pr;
+    reinterpret_cast<uint4*>(a.m)[v] = mr;
+    reinterpret_cast<uint4*>(a.v)[v] = vr;
+  }
+}
+
+__global__ void __launch_bounds__(PULL_THREADS, 3)
 rs_reduce_kernel(const RsArgs a) {
   __shared__ float red[PULL_THREADS / 32];
   __shared__ int give_up;
@@ -189,69 +244,40 @@ rs_reduce_kernel(const RsArgs a) {
   float sq = 0.f;
   if (!give_up) {
     const long nvec = a.shard_elems / 8;
-    for (long v = blockIdx.x * static_cast<long>(PULL_THREADS) + threadIdx.x; v < nvec;
-         v += static_cast<long>(gridDim.x) * PULL_THREADS) {
-      float s[8];
+    constexpr int UNR = 4;  // vectors per thread per round: UNR * world peer loads in flight
+    const long stride = static_cast<long>(gridDim.x) * PULL_THREADS;
+    for (long v0 = blockIdx.x * static_cast<long>(PULL_THREADS) + threadIdx.x; v0 < nvec; v0 += stride * UNR) {
+      float s[UNR][8];
 #pragma unroll
-      for (int e = 0; e < 8; ++e) s[e] = 0.f;
+      for (int u = 0; u < UNR; ++u)
+#pragma unroll
+        for (int e = 0; e < 8; ++e) s[u][e] = 0.f;
       for (int p = 0; p < a.world; ++p) {
-        const uint4 raw = ld_peer(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.staging.p[p]) +
-                                                                 a.shard_offset) + v);
-        const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+        const uint4* base = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(a.staging.p[p]) +
+                                                           a.shard_offset);
+        uint4 raw[UNR];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const float2 f2 = __bfloat1622float2(h[e]);
-          s[2 * e] += f2.x;
-          s[2 * e + 1] += f2.y;
+        for (int u = 0; u < UNR; ++u) {
+          const long v = v0 + u * stride;
+          if (v < nvec) raw[u] = ld_peer(base + v);
+          else raw[u] = make_uint4(0, 0, 0, 0);
         }
-      }
-      if (a.accum != nullptr) {
-        float4* acc = reinterpret_cast<float4*>(a.accum + v * 8);
-        if (a.accumulate_in) {
-          const float4 a0 = acc[0], a1 = acc[1];
-          s[0] += a0.x; s[1] += a0.y; s[2] += a0.z; s[3] += a0.w;
-          s[4] += a1.x; s[5] += a1.y; s[6] += a1.z; s[7] += a1.w;
-        }
-        if (!a.last) {
-          acc[0] = make_float4(s[0], s[1], s[2], s[3]);
-          acc[1] = make_float4(s[4], s[5], s[6], s[7]);
-        }
-      }
-      if (a.last) {
-        uint4 out;
-        __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&out);
-        float g[8];
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          oh[e] = __floats2bfloat162_rn(s[2 * e], s[2 * e + 1]);
-          const float2 back = __bfloat1622float2(oh[e]);
-          g[2 * e] = back.x;
-          g[2 * e + 1] = back.y;
-          sq += back.x * back.x + back.y * back.y;
-        }
-        if (a.grad_out != nullptr) reinterpret_cast<uint4*>(a.grad_out)[v] = out;
-        if (a.apply_adam) {
-          uint4 pr = reinterpret_cast<const uint4*>(a.param)[v];
-          uint4 mr = reinterpret_cast<const uint4*>(a.m)[v];
-          uint4 vr = reinterpret_cast<const uint4*>(a.v)[v];
-          __nv_bfloat16* pe = reinterpret_cast<__nv_bfloat16*>(&pr);
-          __nv_bfloat16* me = reinterpret_cast<__nv_bfloat16*>(&mr);
-          __nv_bfloat16* ve = reinterpret_cast<__nv_bfloat16*>(&vr);
+        for (int u = 0; u < UNR; ++u) {
+          const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw[u]);
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            const float dec = (v * 8 + e >= a.decay_from) ? a.decay : 0.f;
-            const float mi = a.b1 * __bfloat162float(me[e]) + (1.f - a.b1) * g[e];
-            const float vi = a.b2 * __bfloat162float(ve[e]) + (1.f - a.b2) * g[e] * g[e];
-            const float pi = __bfloat162float(pe[e]);
-            const float upd = -a.lr * ((mi / a.bc1) / (sqrtf(vi / a.bc2) + a.eps) + dec * pi);
-            me[e] = __float2bfloat16(mi);
-            ve[e] = __float2bfloat16(vi);
-            pe[e] = __float2bfloat16(pi + __bfloat162float(__float2bfloat16(upd)));
+          for (int e = 0; e < 4; ++e) {
+            const float2 f2 = __bfloat1622float2(h[e]);
+            s[u][2 * e] += f2.x;
+            s[u][2 * e + 1] += f2.y;
           }
-          reinterpret_cast<uint4*>(a.param)[v] = pr;
-          reinterpret_cast<uint4*>(a.m)[v] = mr;
-          reinterpret_cast<uint4*>(a.v)[v] = vr;
         }
+      }
+#pragma unroll
+      for (int u = 0; u < UNR; ++u) {
+        const long v = v0 + u * stride;
+        if (v >= nvec) continue;
+        rs_finish_vector(a, v, s[u], sq);
       }
     }
   }

@@ -57,15 +57,20 @@ struct TileCoord {
   int m0, n0;
 };
 
-__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n) {
+// Tiles are walked in bands of GROUP_M row tiles; inside a band the column tile advances
+// slowly so the B tile stays hot in L2.  `n_rotate` shifts the column order so that a rank
+// starts on the weight rows it already owns while the all-gather pull brings the rest.
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int n_rotate) {
   const int per_group = GROUP_M * num_n;
   const int group = tile / per_group;
   const int first_m = group * GROUP_M;
   const int rows = min(GROUP_M, num_m - first_m);
   const int local = tile - group * per_group;
+  int n = local / rows + n_rotate;
+  if (n >= num_n) n -= num_n;
   TileCoord c;
   c.m0 = (first_m + local % rows) * BM;
-  c.n0 = (local / rows) * BN;
+  c.n0 = n * BN;
   return c;
 }
 
@@ -118,48 +123,52 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
-    if (lane == 0) {
-      uint32_t stage = 0, phase = 0;
-      uint32_t armed = 0;      // bit s set: full[s] was armed by this thread at least once
-      uint32_t armed_par = 0;  // bit s: parity of the phase last armed on full[s]
-      bool ok = true;
-      bool flags_all_seen = false;
-      for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
-        const TileCoord tc = tile_coord(tile, num_m, num_n);
-        if (args.b_flags != nullptr && !(flags_all_seen)) {
-          // The elements of B this tile reads must have landed in this GPU's memory.  A
-          // K-major B tile is rows [n0, n0+BN) of the weight; an MN-major B (dgrad) strides
-          // over the whole matrix, so it waits for all of it once.
-          long e0, e1;
-          if (B_MN || args.b_wait_all) {
-            e0 = args.b_flag_base;
-            e1 = args.b_flag_base + static_cast<long>(B_MN ? args.K : args.N) * args.ldb;
-            flags_all_seen = true;
-          } else {
-            const int nend = min(tc.n0 + BN, args.N);
-            e0 = args.b_flag_base + static_cast<long>(tc.n0) * args.ldb;
-            e1 = args.b_flag_base + static_cast<long>(nend - 1) * args.ldb + args.K;
-          }
-          const int first = static_cast<int>(e0 / args.b_flag_chunk);
-          const int last = static_cast<int>((e1 - 1) / args.b_flag_chunk);
-          for (int f = first; ok && f <= last; ++f) {
-            const long long t0 = clock64();
-            while (true) {
-              unsigned v;
-              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(args.b_flags + f) : "memory");
-              if (v >= args.b_flag_epoch) break;
-              if (*abort_flag || clock64() - t0 > args.spin_budget) {
-                *abort_flag = 1u;
-                report_failure(st, SITE_PRODUCER_FLAG, static_cast<unsigned>(f), args.b_flag_epoch);
-                ok = false;
-                break;
-              }
-              __nanosleep(64);
-            }
-          }
-          if (!ok) break;
-          fence_proxy_async_all();  // generic-proxy writes of the pull CTAs -> async-proxy reads below
+    // All 32 lanes take part in the flag acquisition (one chunk flag per lane per round);
+    // lane 0 alone arms the barriers and issues the copies.
+    uint32_t stage = 0, phase = 0;
+    uint32_t armed = 0;      // bit s set: full[s] was armed by this thread at least once
+    uint32_t armed_par = 0;  // bit s: parity of the phase last armed on full[s]
+    bool ok = true;
+    bool flags_all_seen = false;
+    for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
+      const TileCoord tc = tile_coord(tile, num_m, num_n, args.n_rotate);
+      if (args.b_flags != nullptr && !flags_all_seen) {
+        // The elements of B this tile reads must have landed in this GPU's memory.  A
+        // K-major B tile is rows [n0, n0+BN) of the weight; an MN-major B (dgrad) strides
+        // over the whole matrix, so it waits for all of it once.
+        long e0, e1;
+        if (B_MN || args.b_wait_all) {
+          e0 = args.b_flag_base;
+          e1 = args.b_flag_base + static_cast<long>(B_MN ? args.K : args.N) * args.ldb;
+          flags_all_seen = true;
+        } else {
+          const int nend = min(tc.n0 + BN, args.N);
+          e0 = args.b_flag_base + static_cast<long>(tc.n0) * args.ldb;
+          e1 = args.b_flag_base + static_cast<long>(nend - 1) * args.ldb + args.K;
         }
+        const int first = static_cast<int>(e0 / args.b_flag_chunk);
+        const int last = static_cast<int>((e1 - 1) / args.b_flag_chunk);
+        bool mine = true;
+        for (int f = first + lane; mine && f <= last; f += 32) {
+          const long long t0 = clock64();
+          while (true) {
+            unsigned v;
+            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(args.b_flags + f) : "memory");
+            if (v >= args.b_flag_epoch) break;
+            if (*abort_flag || clock64() - t0 > args.spin_budget) {
+              *abort_flag = 1u;
+              report_failure(st, SITE_PRODUCER_FLAG, static_cast<unsigned>(f), args.b_flag_epoch);
+              mine = false;
+              break;
+            }
+            __nanosleep(64);
+          }
+        }
+        ok = __all_sync(0xffffffffu, mine);
+        if (!ok) break;
+        fence_proxy_async_all();  // generic-proxy writes of the pull CTAs -> async-proxy reads below
+      }
+      if (lane == 0) {
         for (int kb = 0; kb < num_k; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, st, SITE_PRODUCER_EMPTY, args.spin_budget)) {
             ok = false;
@@ -189,18 +198,19 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
         }
       }
-      if (!ok || *abort_flag) {
-        // Leave no copy of ours in flight: wait (bounded) until the last phase armed on
-        // each stage has completed, i.e. its TMA bytes have landed.
-        for (int s = 0; s < NSTAGE; ++s) {
-          if (!(armed & (1u << s))) continue;
-          const uint32_t par = (armed_par >> s) & 1u;
-          const long long t0 = clock64();
-          while (!mbar_try_wait(&full[s], par)) {
-            if (clock64() - t0 > 20000000ll) {
-              report_failure(st, SITE_DRAIN, static_cast<unsigned>(s), par);
-              break;
-            }
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    }
+    if (lane == 0 && (!ok || *abort_flag)) {
+      // Leave no copy of ours in flight: wait (bounded) until the last phase armed on
+      // each stage has completed, i.e. its TMA bytes have landed.
+      for (int s = 0; s < NSTAGE; ++s) {
+        if (!(armed & (1u << s))) continue;
+        const uint32_t par = (armed_par >> s) & 1u;
+        const long long t0 = clock64();
+        while (!mbar_try_wait(&full[s], par)) {
+          if (clock64() - t0 > 20000000ll) {
+            report_failure(st, SITE_DRAIN, static_cast<unsigned>(s), par);
+            break;
           }
         }
       }
@@ -249,7 +259,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint32_t acc = 0, acc_phase = 0, buf_idx = 0;
     uint8_t* epi = smem + OFF_EPI;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
-      const TileCoord tc = tile_coord(tile, num_m, num_n);
+      const TileCoord tc = tile_coord(tile, num_m, num_n, args.n_rotate);
       // The four epilogue warps decide together: a thread that gave up must not leave
       // the others waiting at the staging barriers below.
       const bool got = mbar_wait(&tfull[acc], acc_phase, abort_flag, st, SITE_EPI_TFULL, args.spin_budget);
@@ -468,6 +478,10 @@ int run_gemm(const GemmCall& c) {
   a.b_flag_epoch = c.b_flag_epoch;
   a.b_wait_all = c.b_wait_all;
   a.ldb = c.ldb;
+  {
+    const int num_n = (c.N + gemm::BN - 1) / gemm::BN;
+    a.n_rotate = (c.n_rotate > 0 && c.n_rotate < num_n) ? c.n_rotate : 0;
+  }
   a.ce_targets = c.ce_targets;
   a.ce_max = c.ce_max;
   a.ce_sum = c.ce_sum;
@@ -511,13 +525,13 @@ CTB_API int ctb_gemm(const void* A, const void* B, void* C, int M, int N, int K,
 CTB_API int ctb_gemm_flagged(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
                              int a_mn, int b_mn, int out_f32, int accumulate, float alpha, const void* bias,
                              const unsigned* flags, long flag_chunk, long flag_base, unsigned epoch, int wait_all,
-                             long long spin_budget, int max_ctas, void* stream) {
+                             int n_rotate, long long spin_budget, int max_ctas, void* stream) {
   ctb::GemmCall c{};
   c.A = A; c.B = B; c.C = C; c.M = M; c.N = N; c.K = K; c.lda = lda; c.ldb = ldb; c.ldc = ldc;
   c.a_mn = a_mn; c.b_mn = b_mn; c.out_f32 = out_f32; c.accumulate = accumulate; c.alpha = alpha; c.bias = bias;
   c.epi = ctb::EPI_STORE; c.max_ctas = max_ctas; c.stream = stream;
   c.b_flags = flags; c.b_flag_chunk = flag_chunk; c.b_flag_base = flag_base; c.b_flag_epoch = epoch;
-  c.b_wait_all = wait_all; c.spin_budget = spin_budget;
+  c.b_wait_all = wait_all; c.spin_budget = spin_budget; c.n_rotate = n_rotate;
   return ctb::run_gemm(c);
 }
 

@@ -24,6 +24,7 @@ struct GemmArgs {
   long b_flag_base;
   unsigned b_flag_epoch;
   int b_wait_all;
+  int n_rotate;
   long ldb;
   const int* ce_targets;
   float* ce_max;
@@ -52,6 +53,7 @@ struct GemmCall {
   long b_flag_base = 0;
   unsigned b_flag_epoch = 0;
   int b_wait_all = 0;
+  int n_rotate = 0;
   long long spin_budget = 0;
   const int* ce_targets = nullptr;
   float* ce_max = nullptr;

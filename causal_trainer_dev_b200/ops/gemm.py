@@ -27,6 +27,10 @@ class FlagSource:
         self.chunk_elems = chunk_elems
         self.epoch = 0
         self.spin_budget = 0
+        self.complete = None        # torch.cuda.Event recorded after the pull; once it has fired
+                                    # the buffer is plain memory and GEMMs skip the flags
+        self.own_start = 0          # element range of the buffer that this rank owns (arrives first)
+        self.own_stop = 0
 
 
 _FLAG_SOURCES: list[FlagSource] = []
@@ -46,6 +50,8 @@ def flag_source_of(t: torch.Tensor) -> tuple[FlagSource, int] | None:
     p = t.data_ptr()
     for src in _FLAG_SOURCES:
         if src.start <= p < src.end and src.epoch > 0:
+            if src.complete is not None and src.complete.query():
+                return None
             return src, (p - src.start) // t.element_size()
     return None
 
@@ -85,12 +91,19 @@ def gemm(
     hit = flag_source_of(b) if _FLAG_SOURCES else None
     if hit is not None:
         src, base = hit
+        n_rotate = 0
+        if not b_mn and src.own_stop > src.own_start:
+            # start on the weight rows this rank already owns; the pull delivers the rest in
+            # increasing (wrapping) rank order, which is the order the rotated walk needs them
+            first_own_row = max(0, -(-(src.own_start - base) // b.stride(0)))
+            if first_own_row < n:
+                n_rotate = -(-first_own_row // 256)
         code = _lib.lib().ctb_gemm_flagged(
             _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), m, n, k,
             ctypes.c_long(a.stride(0)), ctypes.c_long(b.stride(0)), ctypes.c_long(out.stride(0)),
             int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), ctypes.c_float(alpha),
             _lib.ptr(bias), _lib.ptr(src.flags), ctypes.c_long(src.chunk_elems), ctypes.c_long(base),
-            ctypes.c_uint(src.epoch), 0, ctypes.c_longlong(src.spin_budget), max_ctas, _lib.stream_ptr(),
+            ctypes.c_uint(src.epoch), 0, n_rotate, ctypes.c_longlong(src.spin_budget), max_ctas, _lib.stream_ptr(),
         )
         _lib.check(code, "ctb_gemm_flagged")
         return out

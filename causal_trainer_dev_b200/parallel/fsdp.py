@@ -43,8 +43,8 @@ from ..training.steps import StepMetrics
 CHUNK = 65536          # elements per flag (128 KiB of bf16)
 N_GATHER = 3           # gathered-unit buffers (current, prefetched, draining)
 N_SLOTS = 3            # gradient staging slots
-PULL_CTAS = 24
-REDUCE_CTAS = 32
+PULL_CTAS = 64
+REDUCE_CTAS = 64
 
 
 def _ptr_array(ptrs: list[int]):
@@ -89,7 +89,8 @@ class FsdpRuntime:
         self.fused = bool(getattr(tcfg, "fused_collectives", True))
         self.grad_dtype = torch.bfloat16
         self.main = torch.cuda.current_stream(device)
-        self.side = torch.cuda.Stream(device, priority=-1)
+        self.side = torch.cuda.Stream(device, priority=-1)       # all-gather pulls
+        self.reduce_stream = torch.cuda.Stream(device, priority=-1)  # reduce-scatter kernels
         self.spin_budget = 4_000_000_000
         L = _lib.lib()
         if self.world > L.ctb_max_ranks():
@@ -220,6 +221,9 @@ class FsdpRuntime:
         g.unit, g.epoch = name, self.epoch
         g.source.epoch = self.epoch
         g.source.spin_budget = self.spin_budget
+        g.source.complete = g.pull_done
+        g.source.own_start = self.rank * u.shard_elems
+        g.source.own_stop = (self.rank + 1) * u.shard_elems
         self.where[name] = g
         if g.free_event is not None:
             self.side.wait_event(g.free_event)
@@ -281,7 +285,7 @@ class FsdpRuntime:
                                                  _lib.stream_ptr())
                 _lib.check(code, "ctb_wait_flags")
             elif prev > 0:
-                self.main.wait_stream(self.side)
+                self.main.wait_stream(self.reduce_stream)
             u = self.units[name]
             view = self.staging[slot * self.max_padded:slot * self.max_padded + u.padded]
             if u.has_gaps:
@@ -306,11 +310,11 @@ class FsdpRuntime:
             _lib.check(code, "ctb_signal_peers")
             ev = torch.cuda.Event()
             ev.record(self.main)
-            self.side.wait_event(ev)
+            self.reduce_stream.wait_event(ev)
             accum = self.accum[off:off + u.shard_elems] if self.accum is not None else None
             staging = _ptr_array([p + 2 * slot * self.max_padded for p in self.staging_ptrs])
             done = _ptr_array([p + 4 * (self.done_base + slot * self.world + self.rank) for p in self.pad_ptrs])
-            with torch.cuda.stream(self.side):
+            with torch.cuda.stream(self.reduce_stream):
                 code = L.ctb_rs_reduce(
                     staging, ctypes.c_long(self.rank * u.shard_elems), ctypes.c_long(u.shard_elems), self.world,
                     _lib.ptr(self.pads), self.ready_base + slot * self.world, ctypes.c_uint(epoch),
@@ -318,14 +322,14 @@ class FsdpRuntime:
                     _lib.ptr(self.grad_shards[off:off + u.shard_elems]), _lib.ptr(self.sumsq[idx]),
                     0, None, None, None, ctypes.c_long(0), *(ctypes.c_float(0.0),) * 7,
                     done, 0, _lib.ptr(self.finish_counter), REDUCE_CTAS, ctypes.c_longlong(self.spin_budget),
-                    ctypes.c_void_p(self.side.cuda_stream),
+                    ctypes.c_void_p(self.reduce_stream.cuda_stream),
                 )
                 _lib.check(code, "ctb_rs_reduce")
         else:
             ev = torch.cuda.Event()
             ev.record(self.main)
-            self.side.wait_event(ev)
-            with torch.cuda.stream(self.side):
+            self.reduce_stream.wait_event(ev)
+            with torch.cuda.stream(self.reduce_stream):
                 src = self.staging[slot * self.max_padded:slot * self.max_padded + u.padded]
                 red = torch.empty(u.shard_elems, dtype=torch.bfloat16, device=self.device)
                 dist.reduce_scatter_tensor(red, src, group=self.group)
@@ -361,6 +365,7 @@ class FsdpRuntime:
     def apply_update(self, lr: float) -> torch.Tensor:
         a = self.tcfg.adamw
         self.main.wait_stream(self.side)
+        self.main.wait_stream(self.reduce_stream)
         total = self.sumsq.sum().reshape(1)
         dist.all_reduce(total, group=self.group)          # also orders every peer's pulls before the update
         grad_norm = torch.sqrt(total)
