@@ -1,0 +1,299 @@
+"""Checkpoint bundles: completion manifest, validation, resume discovery, pruning.
+
+A bundle is a directory (``output_dir`` for the final export, ``output_dir/checkpoint-<step>``
+for periodic ones) whose ``checkpoint_manifest.json`` is written **last** and deleted
+**first** on overwrite, so a directory with a manifest is complete by construction.  The
+manifest (format ``training-checkpoint-bundle``, version 4) records sizes and SHA-256 digests
+of every artifact, the checkpoint id shared by all tensor files, the step, and the training
+signature of the run that wrote it (src/causal_trainer/checkpointing/bundles.py:926-943).
+
+Discovery (``find_latest_checkpoint``) treats a bundle with another signature or artifact kind
+as *incompatible* and a bundle that fails structural or digest validation as *corrupt*; both
+are hard errors, never silently skipped (``bundles.py:620-775``).  Among valid candidates the
+preference is: completed-streaming root, then highest step, then the root at equal step.
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import shutil
+from dataclasses import dataclass
+from pathlib import Path
+from typing import Any
+
+from ..parallel import runtime as rt
+from . import safetensors_io as st
+
+BUNDLE_FORMAT = "training-checkpoint-bundle"
+BUNDLE_FORMAT_VERSION = 4
+ARTIFACT_KINDS = ("merged", "peft-adapter")
+MANIFEST_NAME = "checkpoint_manifest.json"
+
+
+@dataclass(frozen=True)
+class ResumeCheckpoint:
+    path: Path
+    global_step: int
+    total_steps: int
+    has_optimizer_state: bool
+    checkpoint_id: str
+    manifest_digest: str
+    artifact_kind: str = "merged"
+    source_examples_seen: int = 0
+    training_complete: bool = False
+    streaming_data_digest: str | None = None
+
+
+def training_signature(payload: Any) -> str:
+    raw = json.dumps(payload, ensure_ascii=False, separators=(",", ":"), sort_keys=True).encode("utf-8")
+    return hashlib.sha256(raw).hexdigest()
+
+
+def file_sha256(path: Path) -> str:
+    h = hashlib.sha256()
+    with path.open("rb") as f:
+        for block in iter(lambda: f.read(1 << 22), b""):
+            h.update(block)
+    return h.hexdigest()
+
+
+def _is_hex(value: Any, length: int) -> bool:
+    return isinstance(value, str) and len(value) == length and all(c in "0123456789abcdef" for c in value)
+
+
+def _read_manifest(path: Path) -> dict[str, Any] | None:
+    m = path / MANIFEST_NAME
+    if m.is_symlink() or not m.is_file():
+        return None
+    try:
+        value = json.loads(m.read_text(encoding="utf-8"))
+    except (OSError, ValueError):
+        return None
+    return value if isinstance(value, dict) else None
+
+
+def artifact_files(path: Path, kind: str, has_optimizer: bool) -> list[Path]:
+    """Every regular file that belongs to a bundle (the manifest itself and nested bundles excluded)."""
+    out = []
+    for p in sorted(path.rglob("*")):
+        rel = p.relative_to(path)
+        if rel.parts[0].startswith("checkpoint-") or rel.name == MANIFEST_NAME or rel.name == "training_args.json":
+            continue
+        if rel.parts[0] == "optimizer" and not has_optimizer:
+            continue
+        if p.is_file() and not p.is_symlink() and not p.name.endswith(".tmp"):
+            out.append(p)
+    return out
+
+
+def _header_matches(path: Path, checkpoint_id: str, layout: dict[str, tuple[str, tuple[int, ...]]] | None) -> bool:
+    try:
+        tensors, meta, _ = st.read_header(path)
+    except (OSError, ValueError):
+        return False
+    if meta.get("checkpoint_id") != checkpoint_id:
+        return False
+    if layout is not None:
+        got = {k: (v.dtype, tuple(v.shape)) for k, v in tensors.items()}
+        want = {k: (dt, tuple(shape)) for k, (dt, shape) in layout.items()}
+        if got != want:
+            return False
+    return True
+
+
+def _optimizer_state_valid(path: Path, step: int, checkpoint_id: str) -> bool:
+    d = path / "optimizer"
+    try:
+        manifest = json.loads((d / "manifest.json").read_text(encoding="utf-8"))
+    except (OSError, ValueError):
+        return False
+    if (manifest.get("format") != "optimizer-state-safetensors" or manifest.get("format_version") != 1
+            or manifest.get("global_step") != step or manifest.get("checkpoint_id") != checkpoint_id):
+        return False
+    try:
+        tensors, meta, _ = st.read_header(d / "state.safetensors")
+    except (OSError, ValueError):
+        return False
+    if meta.get("checkpoint_id") != checkpoint_id or manifest.get("tensor_count") != len(tensors):
+        return False
+    for e in manifest.get("tensors", []):
+        info = tensors.get(e.get("key"))
+        if info is None or info.dtype != e.get("dtype") or list(info.shape) != e.get("shape"):
+            return False
+    return True
+
+
+def _artifacts_match(path: Path, manifest: dict[str, Any], verify_digests: bool) -> bool:
+    sizes, digests = manifest.get("artifact_sizes"), manifest.get("artifact_digests")
+    if not isinstance(sizes, dict) or not isinstance(digests, dict) or set(sizes) != set(digests):
+        return False
+    files = {str(p.relative_to(path)): p for p in artifact_files(path, manifest["artifact_kind"],
+                                                                  manifest["has_optimizer_state"])}
+    if set(files) != set(sizes):
+        return False
+    for rel, p in files.items():
+        if p.stat().st_size != sizes[rel]:
+            return False
+        if verify_digests and file_sha256(p) != digests[rel]:
+            return False
+    return True
+
+
+def find_latest_checkpoint(output_dir: str | Path, expected_signature: str, *,
+                           expected_model_layout: dict[str, tuple[str, tuple[int, ...]]] | None = None,
+                           expected_artifact_kind: str = "merged", verify_artifact_digests: bool = True
+                           ) -> ResumeCheckpoint | None:
+    if expected_artifact_kind not in ARTIFACT_KINDS:
+        raise ValueError(f"unknown expected artifact kind {expected_artifact_kind!r}")
+    root = Path(output_dir)
+    paths = [root]
+    if root.is_dir():
+        paths += sorted(p for p in root.glob("checkpoint-*") if p.is_dir() and not p.is_symlink())
+    good: list[ResumeCheckpoint] = []
+    incompatible: list[Path] = []
+    corrupt: list[Path] = []
+    for path in paths:
+        mpath = path / MANIFEST_NAME
+        m = _read_manifest(path)
+        if m is None:
+            if mpath.exists() or mpath.is_symlink():
+                corrupt.append(path)
+            continue
+        if m.get("format") != BUNDLE_FORMAT:
+            corrupt.append(path)
+            continue
+        kind = m.get("artifact_kind")
+        if (m.get("format_version") != BUNDLE_FORMAT_VERSION or m.get("training_signature") != expected_signature
+                or kind != expected_artifact_kind or kind not in ARTIFACT_KINDS):
+            incompatible.append(path)
+            continue
+        step, total, cid = m.get("global_step"), m.get("total_steps"), m.get("checkpoint_id")
+        seen, done, sdig = m.get("source_examples_seen", 0), m.get("training_complete", False), m.get("streaming_data_digest")
+        ok = (
+            type(step) is int and type(total) is int and 0 <= step <= total and total > 0 and _is_hex(cid, 32)
+            and isinstance(m.get("has_optimizer_state"), bool) and type(seen) is int and seen >= 0
+            and isinstance(done, bool) and (sdig is None or _is_hex(sdig, 64)) and not (seen > 0 and sdig is None)
+            and not (done and (path != root or step != total or sdig is None))
+        )
+        if ok and path != root:
+            try:
+                ok = int(path.name.removeprefix("checkpoint-")) == step
+            except ValueError:
+                ok = False
+        if ok:
+            ok = _artifacts_match(path, m, verify_artifact_digests)
+        if ok and kind == "merged":
+            ok = (path / "config.json").is_file() and _header_matches(path / "model.safetensors", cid, expected_model_layout)
+        if ok and kind == "peft-adapter":
+            ok = (path / "adapter_config.json").is_file() and _header_matches(
+                path / "adapter_model.safetensors", cid, expected_model_layout)
+        if ok and m["has_optimizer_state"]:
+            ok = _optimizer_state_valid(path, step, cid)
+        if not ok:
+            corrupt.append(path)
+            continue
+        good.append(ResumeCheckpoint(path, step, total, m["has_optimizer_state"], cid, training_signature(m), kind,
+                                     seen, done, sdig))
+    if incompatible:
+        raise ValueError("output_dir contains checkpoints from an incompatible training configuration: "
+                         + ", ".join(str(p) for p in incompatible[:3]))
+    if corrupt:
+        raise ValueError("output_dir contains corrupt completed checkpoints: " + ", ".join(str(p) for p in corrupt[:3]))
+    if not good:
+        return None
+    return max(good, key=lambda c: (c.training_complete and c.path == root, c.global_step, c.path == root))
+
+
+def resume_action(checkpoint: ResumeCheckpoint | None, total_steps: int, *, streaming: bool = False) -> str:
+    """``start`` | ``continue`` | ``finalize`` | ``complete`` (src/causal_trainer/training/runner.py:573-600)."""
+    if checkpoint is None:
+        return "start"
+    if checkpoint.total_steps != total_steps and not streaming:
+        raise ValueError(f"checkpoint was written for {checkpoint.total_steps} total steps, this run has {total_steps}")
+    finished = checkpoint.global_step >= total_steps or checkpoint.training_complete
+    if not finished:
+        return "continue"
+    is_root_final = checkpoint.path.name.startswith("checkpoint-") is False
+    return "complete" if is_root_final else "finalize"
+
+
+def invalidate(path: Path) -> None:
+    """Deletes the manifest first so a half-overwritten bundle can never look complete."""
+    (path / MANIFEST_NAME).unlink(missing_ok=True)
+
+
+def write_manifest(path: Path, *, artifact_kind: str, checkpoint_id: str, global_step: int, total_steps: int,
+                   has_optimizer_state: bool, signature: str, source_examples_seen: int = 0,
+                   streaming_data_digest: str | None = None, training_complete: bool = False) -> dict[str, Any]:
+    files = artifact_files(path, artifact_kind, has_optimizer_state)
+    manifest = {
+        "format": BUNDLE_FORMAT, "format_version": BUNDLE_FORMAT_VERSION, "artifact_kind": artifact_kind,
+        "artifact_sizes": {str(p.relative_to(path)): p.stat().st_size for p in files},
+        "artifact_digests": {str(p.relative_to(path)): file_sha256(p) for p in files},
+        "checkpoint_id": checkpoint_id, "global_step": int(global_step), "total_steps": int(total_steps),
+        "has_optimizer_state": bool(has_optimizer_state), "source_examples_seen": int(source_examples_seen),
+        "streaming_data_digest": streaming_data_digest, "training_complete": bool(training_complete),
+        "training_signature": signature,
+    }
+    tmp = path / (MANIFEST_NAME + ".tmp")
+    tmp.write_text(json.dumps(manifest, indent=2, sort_keys=True) + "\n", encoding="utf-8")
+    with tmp.open("rb") as f:
+        os.fsync(f.fileno())
+    os.replace(tmp, path / MANIFEST_NAME)
+    return manifest
+
+
+def save_checkpoint_bundle(destination: str | Path, *, export_model, export_optimizer=None, artifact_kind: str = "merged",
+                           global_step: int, total_steps: int, signature: str, source_examples_seen: int = 0,
+                           streaming_data_digest: str | None = None, training_complete: bool = False) -> str:
+    """Collective.  ``export_model(dest, checkpoint_id)`` and ``export_optimizer(dest, checkpoint_id)`` do the
+    tensor I/O (both collective); rank 0 then hashes every artifact and writes the manifest last."""
+    from .huggingface import new_checkpoint_id, remove_optimizer_checkpoint
+
+    dest = Path(destination)
+    error: BaseException | None = None
+    cid = new_checkpoint_id()
+    if rt.process_index() == 0:
+        try:
+            dest.mkdir(parents=True, exist_ok=True)
+            invalidate(dest)
+        except BaseException as exc:  # noqa: BLE001
+            error = exc
+    rt.raise_if_process_zero_error(error, "prepare checkpoint directory")
+    remove_optimizer_checkpoint(dest)
+    export_model(dest, cid)
+    if export_optimizer is not None:
+        export_optimizer(dest, cid)
+    if rt.process_index() == 0:
+        try:
+            write_manifest(dest, artifact_kind=artifact_kind, checkpoint_id=cid, global_step=global_step,
+                           total_steps=total_steps, has_optimizer_state=export_optimizer is not None,
+                           signature=signature, source_examples_seen=source_examples_seen,
+                           streaming_data_digest=streaming_data_digest, training_complete=training_complete)
+        except BaseException as exc:  # noqa: BLE001
+            error = exc
+    rt.raise_if_process_zero_error(error, "write checkpoint manifest")
+    rt.sync_processes(f"checkpoint-{global_step}")
+    return cid
+
+
+def prune_periodic_exports(output_dir: str | Path, limit: int, signature: str) -> list[Path]:
+    """Keeps the newest ``limit`` fully valid periodic bundles of this run (0 keeps all); rank 0 only."""
+    if limit <= 0 or rt.process_index() != 0:
+        return []
+    root = Path(output_dir)
+    valid: list[tuple[int, Path]] = []
+    for p in root.glob("checkpoint-*"):
+        m = _read_manifest(p)
+        if (p.is_dir() and not p.is_symlink() and m is not None and m.get("format") == BUNDLE_FORMAT
+                and m.get("training_signature") == signature and type(m.get("global_step")) is int
+                and p.name == f"checkpoint-{m['global_step']}" and _artifacts_match(p, m, verify_digests=False)):
+            valid.append((m["global_step"], p))
+    valid.sort()
+    removed = []
+    for _, p in valid[:-limit]:
+        invalidate(p)
+        shutil.rmtree(p)
+        removed.append(p)
+    return removed

@@ -1,0 +1,336 @@
+"""Hugging Face checkpoint import / export for single-replica and FSDP-sharded parameters.
+
+Formats are those of the reference (src/causal_trainer/checkpointing/huggingface.py):
+
+* ``model.safetensors``: HF Llama key names, ``[out,in]`` layout, one dtype, tensor order =
+  sorted parameter-tree order (``hf_export_order``), ``__metadata__ = {"format": "pt",
+  "checkpoint_id": <32 hex>}`` (``:634-655, 1156-1213``);
+* ``config.json`` rewritten with the actual parameter dtype; tokenizer files and
+  ``chat_templates/*.jinja`` copied (``:676-739``);
+* ``optimizer/state.safetensors`` with keys ``state/%06d`` + ``optimizer/manifest.json``
+  (``format: optimizer-state-safetensors``, ``format_version: 1``) (``:1517-1646``).
+
+Because ``nn.Linear`` already stores ``[out,in]``, no transposes happen anywhere.  Loading is
+lazy: a rank maps the files and copies only the byte ranges that fall into its shard.
+Export streams one tensor at a time to rank 0 in bounded rounds (64 MiB), so host memory on
+every rank stays bounded by one round regardless of model size (``:787-988, 1099-1337``).
+"""
+from __future__ import annotations
+
+import hashlib
+import json
+import os
+import shutil
+import uuid
+from pathlib import Path
+from typing import Any, Callable, Iterator
+
+import torch
+import torch.distributed as dist
+
+from ..models.config import ModelConfig
+from ..models.params import ModelParams, hf_export_order, hf_name_map, unit_layouts
+from ..parallel import runtime as rt
+from . import safetensors_io as st
+
+GATHER_ROUND_BYTES = 64 * 1024 * 1024
+TOKENIZER_NAMES = {
+    "added_tokens.json", "chat_template.json", "generation_config.json", "merges.txt", "preprocessor_config.json",
+    "processor_config.json", "special_tokens_map.json", "tokenizer.json", "tokenizer.model", "tokenizer_config.json",
+    "vocab.json",
+}
+TOKENIZER_SUFFIXES = (".jinja", ".model", ".tiktoken")
+TORCH_DTYPE_NAMES = {torch.bfloat16: "bfloat16", torch.float32: "float32", torch.float16: "float16"}
+
+
+# --------------------------------------------------------------------------------------- sources
+def resolve_hf_source(repo_id_or_path: str | os.PathLike[str], *, revision: str | None = None,
+                      token: str | None = None, cache_dir: str | None = None, local_files_only: bool = False) -> Path:
+    """A local directory is used as is; anything else is fetched from the Hub (with retries)."""
+    candidate = Path(repo_id_or_path).expanduser()
+    if candidate.exists():
+        if not candidate.is_dir():
+            raise ValueError(f"model source must be a directory, got {candidate}")
+        return candidate.resolve()
+    from huggingface_hub import snapshot_download
+
+    from ..hf_retry import retry_hf_call
+
+    return Path(retry_hf_call(lambda: snapshot_download(
+        repo_id=str(repo_id_or_path), revision=revision, token=token, cache_dir=cache_dir,
+        local_files_only=local_files_only,
+        allow_patterns=["*.json", "*.jinja", "chat_templates/*.jinja", "*.model", "*.safetensors", "*.tiktoken", "*.txt"],
+    ), description=f"download {repo_id_or_path}"))
+
+
+def load_hf_config(source: str | os.PathLike[str]) -> dict[str, Any]:
+    path = Path(source) / "config.json"
+    if not path.is_file():
+        raise FileNotFoundError(f"missing model config: {path}")
+    value = json.loads(path.read_text(encoding="utf-8"))
+    if not isinstance(value, dict):
+        raise ValueError(f"{path} must contain a JSON object")
+    return value
+
+
+def expected_model_layout(cfg: ModelConfig, dtype: torch.dtype) -> dict[str, tuple[str, tuple[int, ...]]]:
+    """``{hf_key: (safetensors dtype, shape)}`` of a merged checkpoint of this architecture."""
+    mapping = hf_name_map(cfg)
+    layouts = {lay.name: lay for lay in unit_layouts(cfg)}
+    out = {}
+    for name in hf_export_order(cfg):
+        unit, seg, _, rows = mapping[name]
+        shape = layouts[unit].segment(seg).shape
+        out[name] = (st.DTYPE_NAMES[dtype], (rows, *shape[1:]))
+    return out
+
+
+# --------------------------------------------------------------------------------------- loading
+def _check_source(index: st.SafeTensorIndex, cfg: ModelConfig) -> None:
+    want = expected_model_layout(cfg, torch.bfloat16)
+    missing = [k for k in want if k not in index.where]
+    if missing:
+        raise KeyError(f"checkpoint is missing tensors: {missing[:4]}{'...' if len(missing) > 4 else ''}")
+    for key, (_, shape) in want.items():
+        got = index.info(key).shape
+        if tuple(got) != tuple(shape):
+            raise ValueError(f"{key}: checkpoint shape {tuple(got)} does not match the architecture {tuple(shape)}")
+
+
+def load_parameters(source: str | os.PathLike[str], params: ModelParams) -> None:
+    """Fills a full replica from ``model.safetensors`` (cast to the replica's dtype)."""
+    index = st.SafeTensorIndex(source)
+    try:
+        _check_source(index, params.config)
+        with torch.no_grad():
+            for name in params.hf_names():
+                params.tensor(name).copy_(index.tensor(name).to(params.dtype))
+    finally:
+        index.close()
+
+
+def load_sharded_parameters(source: str | os.PathLike[str], runtime) -> None:
+    """Fills the FSDP shards: every rank reads only the byte ranges that fall inside its slices."""
+    cfg = runtime.cfg
+    index = st.SafeTensorIndex(source)
+    mapping = hf_name_map(cfg)
+    try:
+        _check_source(index, cfg)
+        by_unit: dict[str, list[str]] = {}
+        for name in hf_export_order(cfg):
+            by_unit.setdefault(mapping[name][0], []).append(name)
+        with torch.no_grad():
+            for unit_name, names in by_unit.items():
+                u = runtime.units[unit_name]
+                lo, hi = runtime.rank * u.shard_elems, (runtime.rank + 1) * u.shard_elems
+                shard = runtime.shard_view(unit_name)
+                shard.zero_()
+                for name in names:
+                    _, seg_name, r0, rows = mapping[name]
+                    seg = u.layout.segment(seg_name)
+                    inner = 1
+                    for s in seg.shape[1:]:
+                        inner *= s
+                    t0 = seg.offset + r0 * inner            # flat extent of this HF tensor in the unit
+                    t1 = t0 + rows * inner
+                    a, b = max(t0, lo), min(t1, hi)
+                    if b <= a:
+                        continue
+                    piece = index.file_of(name).flat_range(name, a - t0, b - t0)
+                    shard[a - lo:b - lo].copy_(piece.to(torch.bfloat16))
+    finally:
+        index.close()
+
+
+# --------------------------------------------------------------------------------------- export
+class TensorSource:
+    """Where export reads tensors from: a local replica or the FSDP runtime (bounded gathers)."""
+
+    def __init__(self, cfg: ModelConfig, params: ModelParams | None = None, runtime=None,
+                 transform: Callable[[str, torch.Tensor], torch.Tensor] | None = None):
+        if (params is None) == (runtime is None):
+            raise ValueError("give exactly one of params / runtime")
+        self.cfg, self.params, self.runtime, self.transform = cfg, params, runtime, transform
+        self.mapping = hf_name_map(cfg)
+        self.dtype = params.dtype if params is not None else torch.bfloat16
+
+    def chunks(self, name: str) -> Iterator[torch.Tensor]:
+        """Flat CPU pieces of tensor ``name`` in order; collective under FSDP, data on rank 0 only."""
+        if self.params is not None:
+            t = self.params.tensor(name).detach()
+            if self.transform is not None:
+                t = self.transform(name, t)
+            flat = t.reshape(-1)
+            step = max(1, GATHER_ROUND_BYTES // flat.element_size())
+            for i in range(0, flat.numel(), step):
+                yield flat[i:i + step].cpu()
+            return
+        yield from self._sharded_chunks(name)
+
+    def _sharded_chunks(self, name: str) -> Iterator[torch.Tensor]:
+        rtm = self.runtime
+        unit_name, seg_name, r0, rows = self.mapping[name]
+        u = rtm.units[unit_name]
+        seg = u.layout.segment(seg_name)
+        inner = 1
+        for s in seg.shape[1:]:
+            inner *= s
+        t0 = seg.offset + r0 * inner
+        t1 = t0 + rows * inner
+        step = max(1, GATHER_ROUND_BYTES // 2)
+        shard = rtm.shard_view(unit_name)
+        for a in range(t0, t1, step):
+            b = min(t1, a + step)
+            # each rank contributes the part of [a, b) it owns; rank 0 assembles
+            lo, hi = rtm.rank * u.shard_elems, (rtm.rank + 1) * u.shard_elems
+            x, y = max(a, lo), min(b, hi)
+            mine = shard[x - lo:y - lo].detach().cpu() if y > x else torch.empty(0, dtype=torch.bfloat16)
+            pieces = rt.gather_object_to_zero((x, mine))   # only rank 0 ever holds the round
+            if rtm.rank == 0:
+                out = torch.empty(b - a, dtype=torch.bfloat16)
+                for start, piece in pieces:
+                    if piece.numel():
+                        out[start - a:start - a + piece.numel()] = piece
+                yield out
+            else:
+                yield torch.empty(0, dtype=torch.bfloat16)
+
+
+def copy_hf_assets(source: Path | None, destination: Path, cfg: ModelConfig, dtype: torch.dtype) -> None:
+    """``config.json`` (normalised, actual dtype) plus tokenizer files and chat templates."""
+    destination.mkdir(parents=True, exist_ok=True)
+    config = cfg.to_dict()
+    if source is not None and (source / "config.json").is_file():
+        original = json.loads((source / "config.json").read_text(encoding="utf-8"))
+        config = {**original, **{k: v for k, v in config.items() if k in original or k in ("torch_dtype",)}}
+    config["torch_dtype"] = TORCH_DTYPE_NAMES.get(dtype, "bfloat16")
+    config.pop("dtype", None)
+    config.setdefault("architectures", ["LlamaForCausalLM"])
+    (destination / "config.json").write_text(json.dumps(config, indent=2, sort_keys=True) + "\n", encoding="utf-8")
+    if source is None:
+        return
+    for item in sorted(source.iterdir()):
+        if item.is_file() and (item.name in TOKENIZER_NAMES or item.name.endswith(TOKENIZER_SUFFIXES)):
+            if item.resolve() != (destination / item.name).resolve():
+                shutil.copy2(item, destination / item.name)
+    templates = source / "chat_templates"
+    if templates.is_dir():
+        (destination / "chat_templates").mkdir(exist_ok=True)
+        for item in sorted(templates.glob("*.jinja")):
+            shutil.copy2(item, destination / "chat_templates" / item.name)
+
+
+def export_plan_digest(names: list[str], layout: dict[str, tuple[str, tuple[int, ...]]]) -> bytes:
+    return rt.digest_of([[n, layout[n][0], list(layout[n][1])] for n in names])
+
+
+def export_hf_checkpoint(destination: str | os.PathLike[str], source: TensorSource, *, checkpoint_id: str,
+                         assets_from: Path | None = None) -> None:
+    """Streams ``model.safetensors`` (+ assets) into ``destination``; collective, rank 0 writes."""
+    dest = Path(destination)
+    cfg = source.cfg
+    layout = expected_model_layout(cfg, source.dtype)
+    names = hf_export_order(cfg)
+    rt.assert_equal(export_plan_digest(names, layout), "checkpoint export plan")
+    writer = None
+    error: BaseException | None = None
+    if rt.process_index() == 0:
+        try:
+            entries = [(n, layout[n][0], layout[n][1]) for n in names]
+            writer = st.StreamingWriter(dest / "model.safetensors", entries,
+                                        {"format": "pt", "checkpoint_id": checkpoint_id})
+        except BaseException as exc:  # noqa: BLE001 - propagated through the error bus
+            error = exc
+    rt.raise_if_process_zero_error(error, "open model.safetensors")
+    try:
+        for name in names:
+            pieces = source.chunks(name)
+            if writer is not None:
+                writer.write_chunks(name, pieces)
+            else:
+                for _ in pieces:
+                    pass
+    except BaseException as exc:  # noqa: BLE001
+        error = exc
+        if writer is not None:
+            writer.abort()
+            writer = None
+    rt.raise_if_any_process_error(error, "stream model tensors")
+    if rt.process_index() == 0:
+        try:
+            writer.close()
+            copy_hf_assets(assets_from, dest, cfg, source.dtype)
+        except BaseException as exc:  # noqa: BLE001
+            error = exc
+    rt.raise_if_process_zero_error(error, "finalize model.safetensors")
+
+
+# --------------------------------------------------------------------------------------- optimizer state
+def layout_fingerprint(entries: list[dict[str, Any]]) -> str:
+    payload = [[e["path"], e["dtype"], e["shape"]] for e in entries]
+    return hashlib.sha256(json.dumps(payload, separators=(",", ":")).encode()).hexdigest()
+
+
+def export_optimizer_checkpoint(destination: str | os.PathLike[str], state: list[tuple[str, torch.Tensor]], *,
+                                global_step: int, checkpoint_id: str) -> None:
+    """Writes ``optimizer/state.safetensors`` + ``optimizer/manifest.json`` (rank 0; state already whole).
+
+    ``state`` is an ordered list of ``(path, tensor)``: ``count`` first, then ``mu/<unit>`` and
+    ``nu/<unit>`` flat buffers.
+    """
+    if rt.process_index() != 0:
+        return
+    out = Path(destination) / "optimizer"
+    out.mkdir(parents=True, exist_ok=True)
+    tensors = {f"state/{i:06d}": t.detach().cpu() for i, (_, t) in enumerate(state)}
+    st.save_file(tensors, out / "state.safetensors", {"format": "pt", "checkpoint_id": checkpoint_id})
+    entries = [{"dtype": st.DTYPE_NAMES[t.dtype], "file": "state.safetensors", "key": f"state/{i:06d}", "ordinal": i,
+                "path": path, "shape": list(t.shape)} for i, (path, t) in enumerate(state)]
+    manifest = {
+        "format": "optimizer-state-safetensors", "format_version": 1, "global_step": int(global_step),
+        "jax_version": f"torch-{torch.__version__}", "optax_version": "causal-trainer-b200-adamw-1",
+        "layout_fingerprint": layout_fingerprint(entries), "tensor_count": len(entries), "tensors": entries,
+        "total_size": int(sum(t.numel() * t.element_size() for t in tensors.values())), "checkpoint_id": checkpoint_id,
+    }
+    tmp = out / "manifest.json.tmp"
+    tmp.write_text(json.dumps(manifest, indent=2, sort_keys=True) + "\n", encoding="utf-8")
+    os.replace(tmp, out / "manifest.json")
+
+
+def load_optimizer_checkpoint(source: str | os.PathLike[str], expected_paths: list[str], *, global_step: int
+                              ) -> dict[str, torch.Tensor]:
+    """Reads optimizer state back; refuses a foreign framework version, layout or step."""
+    d = Path(source) / "optimizer"
+    manifest = json.loads((d / "manifest.json").read_text(encoding="utf-8"))
+    if manifest.get("format") != "optimizer-state-safetensors" or manifest.get("format_version") != 1:
+        raise ValueError("unsupported optimizer checkpoint format")
+    if manifest.get("optax_version") != "causal-trainer-b200-adamw-1":
+        raise ValueError("optimizer state was written by a different optimizer implementation")
+    if manifest.get("global_step") != global_step:
+        raise ValueError(f"optimizer state is for step {manifest.get('global_step')}, expected {global_step}")
+    paths = [e["path"] for e in manifest["tensors"]]
+    if paths != expected_paths:
+        raise ValueError("optimizer state layout does not match this run")
+    if manifest.get("layout_fingerprint") != layout_fingerprint(manifest["tensors"]):
+        raise ValueError("optimizer manifest fingerprint mismatch")
+    with st.SafeTensorsFile(d / "state.safetensors") as f:
+        if f.metadata.get("checkpoint_id") != manifest.get("checkpoint_id"):
+            raise ValueError("optimizer state belongs to a different checkpoint")
+        out = {e["path"]: f.tensor(e["key"]).clone() for e in manifest["tensors"]}
+    count = out.get("count")
+    if count is not None and int(count) != global_step:
+        raise ValueError("optimizer step counter does not match the checkpoint step")
+    return out
+
+
+def remove_optimizer_checkpoint(destination: str | os.PathLike[str]) -> None:
+    d = Path(destination) / "optimizer"
+    if d.is_dir() and rt.process_index() == 0:
+        shutil.rmtree(d)
+
+
+def new_checkpoint_id() -> str:
+    """uuid4 hex chosen on rank 0 and broadcast (paths may differ per host, the id may not)."""
+    value = uuid.uuid4().hex if rt.process_index() == 0 else None
+    raw = rt.host_broadcast_bytes(value.encode() if value else None, 32)
+    return raw.decode("ascii")
