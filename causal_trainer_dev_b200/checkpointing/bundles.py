@@ -205,17 +205,25 @@ def find_latest_checkpoint(output_dir: str | Path, expected_signature: str, *,
     return max(good, key=lambda c: (c.training_complete and c.path == root, c.global_step, c.path == root))
 
 
-def resume_action(checkpoint: ResumeCheckpoint | None, total_steps: int, *, streaming: bool = False) -> str:
-    """``start`` | ``continue`` | ``finalize`` | ``complete`` (src/causal_trainer/training/runner.py:573-600)."""
+def resume_action(checkpoint: ResumeCheckpoint | None, *, output_dir: Path, total_steps: int) -> str:
+    """``start`` | ``continue`` | ``finalize`` | ``complete``; never silently resets training state
+    (src/causal_trainer/training/runner.py:573-600)."""
     if checkpoint is None:
         return "start"
-    if checkpoint.total_steps != total_steps and not streaming:
-        raise ValueError(f"checkpoint was written for {checkpoint.total_steps} total steps, this run has {total_steps}")
-    finished = checkpoint.global_step >= total_steps or checkpoint.training_complete
-    if not finished:
-        return "continue"
-    is_root_final = checkpoint.path.name.startswith("checkpoint-") is False
-    return "complete" if is_root_final else "finalize"
+    if checkpoint.training_complete:
+        if checkpoint.path != output_dir:
+            raise ValueError("a completed streaming checkpoint must be stored at output_dir")
+        return "complete"
+    if checkpoint.total_steps != total_steps:
+        raise ValueError(f"checkpoint total_steps={checkpoint.total_steps} does not match current plan {total_steps}")
+    if checkpoint.global_step < total_steps and not checkpoint.has_optimizer_state:
+        raise ValueError(
+            "the latest checkpoint does not contain optimizer state, so exact continuation is impossible; optimizer "
+            "state must have been saved before the interruption with --save_optimizer_state True, and enabling it "
+            "only now cannot repair this checkpoint")
+    if checkpoint.global_step == total_steps:
+        return "complete" if checkpoint.path == output_dir else "finalize"
+    return "continue"
 
 
 def invalidate(path: Path) -> None:

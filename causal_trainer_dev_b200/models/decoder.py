@@ -169,6 +169,8 @@ def decoder_forward(
     elif opts.attn_mechanism != "vanilla" and input_ids.is_cuda:
         raise ValueError("the efficient attention backend needs a sequence length that is a multiple of 128")
     embed = params.units["embed"].view("embed")
+    if opts.lora is not None and opts.lora.train_embed_and_lm_head:
+        embed = opts.lora.embed
     h = embedding_lookup(embed, input_ids, cfg.pad_token_id).to(dtype)
     for li in range(cfg.num_hidden_layers):
         views = _unit_views(params, f"layer.{li}")

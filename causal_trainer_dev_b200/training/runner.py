@@ -1,0 +1,627 @@
+"""``causal-train`` orchestration.
+
+Program lifetime (same stages as src/causal_trainer/training/runner.py:642-2393, written as a
+staged :class:`TrainingRun` instead of one function):
+
+ 1. parse flags; start ``torch.distributed``; all ranks must present the same flags;
+ 2. build the rank lattice ``(dp, fsdp, ep, tp, sp)`` and validate it against the model;
+ 3. resolve the model source, read ``config.json``, load the tokenizer when data is raw;
+ 4. data, one of four modes: prepared+materialised, prepared+streaming, raw+materialised
+    (shard -> tokenise -> pack -> merge), raw+streaming;
+ 5. training signature -> resume discovery (every rank must find the same checkpoint)
+    -> ``start | continue | finalize | complete``;
+ 6. parameters (HF checkpoint, lazily sharded) -> LoRA / frozen components -> optimizer state;
+ 7. the step loop: batches are prefetched to pinned memory and copied asynchronously, metrics
+    stay on the device for up to ``async_dispatch_steps`` steps, periodic bundles are written
+    and pruned;
+ 8. the final bundle in ``output_dir``.
+
+Every fallible host stage funnels its exception through the collective error bus so that no
+rank enters the next collective alone.  Devices: bf16 on CUDA uses the layerwise sm_100a
+engine (FSDP over all data ranks when there are several); anything else runs the PyTorch
+oracle path with gradient all-reduce.
+"""
+from __future__ import annotations
+
+import dataclasses
+import hashlib
+import json
+import logging
+import math
+import time
+from collections import deque
+from pathlib import Path
+from typing import Any, Iterator
+
+import numpy as np
+import torch
+
+from ..checkpointing import bundles
+from ..checkpointing import huggingface as hfio
+from ..checkpointing import safetensors_io as st
+from ..data import batching, maskgit, pipeline, prepared, streaming, streaming_batching
+from ..data.preprocessing import EndPromptSettings
+from ..data.tokenizer import TrainingTokenizer
+from ..models.config import ModelConfig, validate_splash_block_size
+from ..models.decoder import ForwardOptions
+from ..models.lora import LoraState, peft_adapter_config
+from ..models.params import ModelParams
+from ..parallel import runtime as rt
+from . import logging as tlog
+from .arguments import parse_args
+from .optimizer import AdamWConfig, ScheduleConfig
+from .steps import AutogradProducer, TrainStep
+
+log = logging.getLogger("causal_trainer")
+
+STREAMING_SCHEDULE_POLICY = "buffered-estimate-v1"
+_SIGNATURE_ARGUMENTS = (
+    "repo_id", "dataset_name", "dataset_format", "dataset_config_name", "dataset_revision", "dataset_split",
+    "dataset_streaming", "dataset_text_field", "processor_repo_id", "processor_revision", "revision",
+    "max_sequence_length", "packing", "packing_batch_size", "streaming_shuffle_buffer", "assistant_only_loss",
+    "last_assistant_only_loss", "endprompt_enable", "endprompt_logical_length", "endprompt_logical_length_min",
+    "endprompt_prompts", "endprompt_prompt_loss_weight", "endprompt_context_loss_weight", "preprocessing_mode",
+    "attn_mechanism", "block_size_q", "block_size_k", "loss_token_budget", "loss_implementation", "mlp_chunk_size",
+    "scan_layers", "total_batch_size", "gradient_accumulation_steps", "learning_rate", "learning_rate_end",
+    "scheduler", "warmup_steps", "weight_decay", "max_grad_norm", "adam_beta1", "adam_beta2", "adam_epsilon",
+    "num_train_epochs", "max_steps", "shuffle", "seed", "gradient_checkpointing", "lora", "lora_rank",
+    "lora_train_embed_and_lm_head", "lora_save_adapter_only", "frozen_parameters", "param_dtype", "dtype",
+    "sharding_axis", "sharding_dcn_axis",
+)
+
+
+# --------------------------------------------------------------------------------------- pure helpers
+def arguments_digest(args) -> bytes:
+    """SHA-256 of every flag except the per-process ones (``process_id``, ``local_device_ids``)."""
+    values = {f.name: getattr(args, f.name) for f in dataclasses.fields(args)
+              if f.name not in ("process_id", "local_device_ids")}
+    return rt.digest_of(values)
+
+
+def prepared_streaming_limits(total_rows: int, effective_batch: int, epochs: float, max_steps: int
+                              ) -> tuple[int, int | None]:
+    """``(total optimizer steps, whole epochs or None)`` for a prepared artifact of known size."""
+    if max_steps > 0:
+        return max_steps, None
+    per_epoch = math.ceil(total_rows / effective_batch)
+    return max(1, math.floor(per_epoch * epochs)), max(1, math.ceil(epochs))
+
+
+def buffered_streaming_schedule_total(estimated_steps: int) -> int:
+    """Schedule horizon for a stream of estimated length: 5 % slack, at least one extra step."""
+    return estimated_steps + max(1, math.ceil(estimated_steps * 0.05))
+
+
+def streaming_schedule_position(step_in_epoch: int, epoch: int, estimate_per_epoch: int) -> int:
+    """Learning-rate position: capped at the per-epoch estimate inside an epoch."""
+    return epoch * estimate_per_epoch + min(step_in_epoch, estimate_per_epoch)
+
+
+def project_streaming_progress_total(steps_done: int, epochs_done: int, epochs_total: int) -> int:
+    """Progress-bar total extrapolated from completed epochs (never below the steps already done)."""
+    if epochs_done <= 0:
+        return steps_done
+    return max(steps_done, math.ceil(steps_done / epochs_done * epochs_total))
+
+
+def validate_structure(args, cfg: ModelConfig, lattice: rt.RankLattice) -> None:
+    """Divisibility and mode rules (the fixed-architecture gate of the reference is not kept)."""
+    lattice.validate()
+    tp, sp, fsdp, dp = (lattice.size(a) for a in ("tp", "sp", "fsdp", "dp"))
+    if cfg.num_attention_heads % tp or cfg.intermediate_size % tp or cfg.vocab_size % tp:
+        raise ValueError("tp must divide num_attention_heads, intermediate_size and vocab_size")
+    if cfg.num_key_value_heads % tp and tp % cfg.num_key_value_heads:
+        raise ValueError("tp must divide, or be a multiple of, num_key_value_heads")
+    if args.max_sequence_length % (sp * 128 if sp > 1 else 1):
+        raise ValueError("max_sequence_length must be a multiple of 128 * sp under sequence parallelism")
+    if args.total_batch_size % (dp * fsdp):
+        raise ValueError(f"total_batch_size={args.total_batch_size} must divide by dp*fsdp={dp * fsdp}")
+    if args.projection_chunk_size > 0 and (dp != 1 or fsdp != 1):
+        raise ValueError("projection_chunk_size requires dp=fsdp=ep=1")
+    if args.attention_options is not None:
+        args.attention_options.validate_layers(cfg.num_hidden_layers)
+    if args.attn_mechanism == "splash":
+        validate_splash_block_size(args.max_sequence_length, args.block_size_q, "block_size_q")
+        validate_splash_block_size(args.max_sequence_length, args.block_size_k, "block_size_k")
+
+
+def resume_signature_payload(args, cfg: ModelConfig, plan, dataset_fingerprint, mesh_shape, *, process_count: int,
+                             real_rows: int, dummy_rows: int, prepared_revision: str | None = None) -> dict[str, Any]:
+    arguments = {n: getattr(args, n) for n in _SIGNATURE_ARGUMENTS}
+    arguments["output_dir"] = None
+    for name in ("projection_chunk_size", "remat_group_size", "cut_chunk_size"):
+        if getattr(args, name) != (1 if name == "remat_group_size" else 0):
+            arguments[name] = getattr(args, name)
+    if args.attention_options is not None:
+        arguments["attention_options"] = dataclasses.asdict(args.attention_options)
+    if args.maskgit_probability:
+        arguments["maskgit_probability"] = args.maskgit_probability
+    payload = {
+        "arguments": json.loads(json.dumps(arguments, default=str)),
+        "dataset_fingerprint": dataset_fingerprint,
+        "preprocessing_process_count": process_count,
+        "prepared_real_rows": real_rows, "prepared_dummy_rows": dummy_rows,
+        "mesh_shape": dict(zip(rt.AXES, (int(x) for x in mesh_shape))),
+        "model_config": cfg.to_dict(), "plan": dataclasses.asdict(plan),
+        "streaming_scheduler_policy": STREAMING_SCHEDULE_POLICY if args.uses_raw_streaming and args.max_steps <= 0 else None,
+    }
+    if args.dataset_format == "prepared":
+        payload["prepared_revision"] = prepared_revision
+    return payload
+
+
+def resume_identity(ckpt: bundles.ResumeCheckpoint | None, output_dir: Path, signature: str) -> bytes:
+    payload = {
+        "checkpoint_id": ckpt.checkpoint_id if ckpt else None, "exists": ckpt is not None,
+        "global_step": ckpt.global_step if ckpt else 0, "has_optimizer_state": ckpt.has_optimizer_state if ckpt else False,
+        "is_output_root": ckpt is not None and ckpt.path == output_dir,
+        "manifest_digest": ckpt.manifest_digest if ckpt else None,
+        "source_examples_seen": ckpt.source_examples_seen if ckpt else 0,
+        "streaming_data_digest": ckpt.streaming_data_digest if ckpt else None,
+        "total_steps": ckpt.total_steps if ckpt else 0, "training_complete": ckpt.training_complete if ckpt else False,
+        "training_signature": signature,
+    }
+    return hashlib.sha256(json.dumps(payload, ensure_ascii=False, separators=(",", ":"), sort_keys=True).encode()).digest()
+
+
+class MetricWindow:
+    """At most ``limit`` finished steps keep their metrics on the device; older ones are read back."""
+
+    def __init__(self, limit: int):
+        self.limit = limit
+        self.pending: deque = deque()
+        self.latest: dict[str, float] | None = None
+
+    def push(self, step: int, metrics) -> None:
+        self.pending.append((step, metrics))
+        while len(self.pending) > self.limit:
+            self._pop()
+
+    def _pop(self) -> None:
+        step, m = self.pending.popleft()
+        self.latest = dict(m.to_floats(), step=step)
+
+    def drain(self) -> dict[str, float] | None:
+        while self.pending:
+            self._pop()
+        return self.latest
+
+
+def endprompt_settings(args) -> EndPromptSettings | None:
+    if not args.endprompt_enable:
+        return None
+    return EndPromptSettings(args.effective_endprompt_logical_length_min, args.effective_endprompt_logical_length,
+                             args.endprompt_prompt_texts, args.endprompt_prompt_loss_weight,
+                             args.endprompt_context_loss_weight)
+
+
+def _guarded(stage: str):
+    """Decorator: run a host stage, then agree with all ranks on whether it failed."""
+    def wrap(fn):
+        def inner(*a, **k):
+            error: BaseException | None = None
+            result = None
+            try:
+                result = fn(*a, **k)
+            except Exception as exc:  # noqa: BLE001 - re-raised on every rank by the bus
+                error = exc
+            rt.raise_if_any_process_error(error, stage)
+            return result
+        return inner
+    return wrap
+
+
+# --------------------------------------------------------------------------------------- the run
+class TrainingRun:
+    def __init__(self, args):
+        self.args = args
+        self.env = rt.initialize_distributed(args.coordinator_address, args.num_processes, args.process_id,
+                                             args.local_device_ids, enabled=args.distributed)
+        tlog.configure_logging(rt.process_index())
+        rt.assert_equal(arguments_digest(args), "command-line arguments")
+        self.lattice = rt.RankLattice.create(args.sharding_axis)
+        self.cuda = torch.cuda.is_available()
+        self.device = torch.device("cuda", self.env.local_rank) if self.cuda else torch.device("cpu")
+        self.param_dtype = torch.bfloat16 if args.param_dtype == "bfloat16" else torch.float32
+        self.use_engine = (self.cuda and self.param_dtype == torch.bfloat16 and args.dtype == "bfloat16"
+                           and args.attn_mechanism != "vanilla" and not args.lora and args.loss_implementation != "xla"
+                           and self.lattice.size("tp") == 1 and self.lattice.size("sp") == 1
+                           and args.attention_options is None)
+        self.prepared_revision: str | None = None
+        self.source_examples_seen = 0
+        self.stream_digest: str | None = None
+        self.training_complete = False
+
+    # ---- stage 3: model source ----
+    @_guarded("resolve model source")
+    def resolve_model(self) -> None:
+        a = self.args
+        self.source = hfio.resolve_hf_source(a.repo_id, revision=a.revision, token=a.token)
+        self.cfg = ModelConfig.from_dict(hfio.load_hf_config(self.source))
+        validate_structure(a, self.cfg, self.lattice)
+        self.processor_source = self.source if a.processor_repo_id is None else hfio.resolve_hf_source(
+            a.processor_repo_id, revision=a.processor_revision, token=a.token)
+        self.tokenizer = None
+        if a.dataset_format == "raw" or a.maskgit_probability:
+            self.tokenizer = TrainingTokenizer.from_directory(self.processor_source)
+            self.tokenizer.validate_model_vocabulary(self.cfg.vocab_size)
+        self.has_weights = any(self.source.glob("*.safetensors"))
+
+    # ---- stage 4: data ----
+    def _pad_token_id(self) -> int:
+        if self.tokenizer is not None and self.tokenizer.pad_token_id is not None:
+            return int(self.tokenizer.pad_token_id)
+        return int(self.cfg.pad_token_id)
+
+    @_guarded("load dataset")
+    def load_data(self) -> None:
+        a = self.args
+        nproc, pidx = rt.process_count(), rt.process_index()
+        effective = a.effective_batch_size
+        self.streaming = a.dataset_streaming
+        self.dummy_rows = 0
+        self.fingerprint: Any = None
+        if a.dataset_format == "prepared":
+            self.prepared_revision = prepared.resolve_prepared_revision(a.dataset_name, token=a.token,
+                                                                        revision=a.dataset_revision)
+            self.manifest = prepared.load_prepared_manifest(a.dataset_name, token=a.token, revision=self.prepared_revision)
+            if self.manifest.max_sequence_length != a.max_sequence_length:
+                raise ValueError("prepared dataset max_sequence_length does not match --max_sequence_length")
+            if self.manifest.max_token_id >= self.cfg.vocab_size:
+                raise ValueError("prepared dataset contains token ids outside the model vocabulary")
+            if a.uses_assistant_loss_mask and not self.manifest.uses_assistant_loss_mask:
+                raise ValueError("assistant-only loss needs a prepared dataset built with an assistant mask")
+            self.fingerprint = self.manifest.global_digest
+            rt.assert_equal(bytes.fromhex(self.manifest.global_digest), "prepared dataset manifest")
+            if self.streaming:
+                steps, epochs = prepared_streaming_limits(self.manifest.total_rows, effective, a.num_train_epochs,
+                                                          a.max_steps)
+                self.plan = streaming_batching.StreamingBatchPlan.create(
+                    self.manifest.total_rows, a.total_batch_size, a.gradient_accumulation_steps, epochs or 1,
+                    a.max_steps if a.max_steps > 0 else steps)
+                self.real_rows = self.manifest.total_rows
+                return
+            local = prepared.load_prepared_dataset(a.dataset_name, self.manifest, token=a.token,
+                                                   revision=self.prepared_revision, process_index=pidx,
+                                                   process_count=nproc)
+            columns = rt.merge_packed_host_arrays(local)
+        elif self.streaming:
+            dataset = pipeline.load_training_split(a.dataset_name, a.dataset_split, token=a.token,
+                                                   config_name=a.dataset_config_name, revision=a.dataset_revision,
+                                                   streaming=True)
+            meta = streaming.streaming_dataset_metadata(dataset, a.dataset_split)
+            self.stream_source = dataset
+            self.fingerprint = getattr(dataset, "_fingerprint", None)
+            self.plan = streaming_batching.StreamingBatchPlan.create(
+                meta.num_examples, a.total_batch_size, a.gradient_accumulation_steps,
+                int(a.num_train_epochs) if a.max_steps <= 0 else 1, a.max_steps)
+            self.real_rows = 0
+            return
+        else:
+            dataset = pipeline.load_training_split(a.dataset_name, a.dataset_split, token=a.token,
+                                                   config_name=a.dataset_config_name, revision=a.dataset_revision)
+            rt.assert_equal(pipeline.source_dataset_identity(dataset), "source dataset")
+            self.fingerprint = getattr(dataset, "_fingerprint", None)
+            sharded = a.preprocessing_mode == "shard_then_merge" and nproc > 1
+            shard, offset = (pipeline.select_process_shard(dataset, process_index=pidx, process_count=nproc)
+                             if sharded else (dataset, 0))
+            rows = pipeline.prepare_training_dataset(
+                shard, self.tokenizer, dataset_text_field=a.dataset_text_field,
+                max_sequence_length=a.max_sequence_length, packing=a.packing, packing_batch_size=a.packing_batch_size,
+                pad_token_id=self._pad_token_id(), assistant_only_loss=a.assistant_only_loss,
+                last_assistant_only_loss=a.last_assistant_only_loss, endprompt=endprompt_settings(a),
+                num_proc=a.preprocessing_num_workers, example_index_offset=offset, allow_empty=sharded)
+            explicit = a.endprompt_enable
+            local = pipeline.packed_dataset_to_arrays(rows, max_sequence_length=a.max_sequence_length,
+                                                      assistant_only_loss=a.uses_assistant_loss_mask,
+                                                      has_explicit_loss_weights=explicit)
+            columns = rt.merge_packed_host_arrays(local) if sharded else local
+        self.dataset, self.dummy_rows = pipeline.pad_packed_arrays_to_batch_multiple(columns, batch_multiple=effective)
+        self.real_rows = self.dataset.real_rows
+        self.plan = batching.BatchPlan.create(len(self.dataset), a.total_batch_size, a.gradient_accumulation_steps,
+                                              a.num_train_epochs, a.max_steps)
+
+    # ---- stage 5: resume ----
+    @_guarded("discover checkpoints")
+    def discover_resume(self) -> None:
+        a = self.args
+        payload = resume_signature_payload(
+            a, self.cfg, self.plan, self.fingerprint, self.lattice.shape, process_count=rt.process_count(),
+            real_rows=self.real_rows, dummy_rows=self.dummy_rows, prepared_revision=self.prepared_revision)
+        self.signature = bundles.training_signature(payload)
+        self.artifact_kind = "peft-adapter" if (a.lora and a.lora_save_adapter_only) else "merged"
+        layout = hfio.expected_model_layout(self.cfg, self.param_dtype) if self.artifact_kind == "merged" else None
+        self.checkpoint = bundles.find_latest_checkpoint(
+            a.output_dir, self.signature, expected_model_layout=layout, expected_artifact_kind=self.artifact_kind,
+            verify_artifact_digests=rt.process_index() == 0)
+        rt.assert_equal(resume_identity(self.checkpoint, Path(a.output_dir), self.signature), "resume checkpoint")
+        self.action = bundles.resume_action(self.checkpoint, output_dir=Path(a.output_dir),
+                                            total_steps=self.plan.total_steps)
+        self.start_step = self.checkpoint.global_step if self.checkpoint is not None else 0
+
+    # ---- stage 6: parameters, optimizer ----
+    @_guarded("load parameters")
+    def build_model(self) -> None:
+        a = self.args
+        adamw = AdamWConfig(a.weight_decay, a.max_grad_norm, a.adam_beta1, a.adam_beta2, a.adam_epsilon)
+        total = self.plan.total_steps
+        if self.streaming and a.max_steps <= 0 and self.plan.steps_per_epoch is not None:
+            total = buffered_streaming_schedule_total(self.plan.steps_per_epoch * max(1, int(a.num_train_epochs)))
+        schedule = ScheduleConfig(a.learning_rate, a.learning_rate_end, a.scheduler, a.warmup_steps, total)
+        weights_from = self.checkpoint.path if (self.checkpoint is not None and self.artifact_kind == "merged") \
+            else (self.source if self.has_weights else None)
+        data_ranks = self.lattice.size("dp") * self.lattice.size("fsdp")
+        self.lora: LoraState | None = None
+        if self.use_engine and data_ranks > 1:
+            from ..api import TrainerConfig
+            from ..parallel.fsdp import FsdpRuntime
+            from .engine import EngineOptions, LayerwiseEngine
+
+            tcfg = TrainerConfig(micro_batch_rows=a.micro_batch_rows or a.total_batch_size // data_ranks, adamw=adamw,
+                                 schedule=schedule, seed=a.seed, fused_collectives=a.fused_collectives,
+                                 cut_chunk_rows=a.cut_chunk_size or 4096)
+            self.runtime = FsdpRuntime(self.cfg, tcfg, self.device)
+            if weights_from is not None:
+                hfio.load_sharded_parameters(weights_from, self.runtime)
+            engine = LayerwiseEngine(self.cfg, self.runtime, EngineOptions(cut_chunk_rows=tcfg.cut_chunk_rows))
+            self.step_fn = self.runtime.make_step(engine)
+            self.params = None
+        else:
+            self.runtime = None
+            if weights_from is not None:
+                self.params = ModelParams(self.cfg, self.param_dtype, "cpu")
+                hfio.load_parameters(weights_from, self.params)
+            else:
+                log.warning("no *.safetensors in %s: initialising N(0, %g) weights", self.source,
+                            self.cfg.initializer_range)
+                self.params = ModelParams.init_random(self.cfg, a.seed, self.param_dtype)
+            self.params.to(self.device)
+            frozen = a.frozen_parameter_components if not a.lora else ()
+            if self.use_engine:
+                from .engine import EngineOptions, LayerwiseEngine, LocalProvider
+
+                grad_dtype = torch.float32 if a.gradient_accumulation_steps > 1 else torch.bfloat16
+                producer = LayerwiseEngine(self.cfg, LocalProvider(self.params, grad_dtype), EngineOptions(
+                    cut_chunk_rows=a.cut_chunk_size or 4096, train_lm_head="lm_head" not in frozen,
+                    train_embed="embed" not in frozen))
+                self.step_fn = TrainStep(self.params, producer, adamw, schedule, frozen=frozen)
+            else:
+                opts = ForwardOptions(
+                    attn_mechanism="vanilla" if (a.attn_mechanism == "vanilla" or not self.cuda) else "efficient",
+                    gradient_checkpointing=a.gradient_checkpointing == "nothing_saveable", mlp_chunk_size=a.mlp_chunk_size,
+                    attention_options=a.attention_options,
+                    compute_dtype=torch.bfloat16 if a.dtype == "bfloat16" and self.cuda else self.param_dtype)
+                extra = []
+                if a.lora:
+                    self.lora = LoraState.init(self.cfg, a.lora_rank, seed=a.seed, dtype=self.param_dtype,
+                                               device=self.device, train_embed_and_lm_head=a.lora_train_embed_and_lm_head,
+                                               base=self.params)
+                    if self.checkpoint is not None and self.artifact_kind == "peft-adapter":
+                        self.lora.load_peft_tensors(st.load_file(self.checkpoint.path / "adapter_model.safetensors"))
+                    opts.lora = self.lora
+                    extra = [(t.detach(), t.dim() > 1, (lambda t=t: t.grad)) for _, t in self.lora.trainable()]
+                producer = AutogradProducer(self.params, opts, a.loss_implementation, a.loss_token_budget,
+                                            a.cut_chunk_size, lora=self.lora)
+                dp_group = rt.host_group() if (rt.process_count() > 1 and not self.cuda) else None
+                self.step_fn = TrainStep(self.params, producer, adamw, schedule, frozen=frozen, dp_group=dp_group,
+                                         extra_regions=extra, train_base=not a.lora)
+        if self.checkpoint is not None and self.checkpoint.has_optimizer_state and self.action == "continue":
+            self.load_optimizer_state(self.checkpoint.path, self.checkpoint.global_step)
+
+    # ---- optimizer state <-> checkpoint ----
+    def optimizer_state(self) -> list[tuple[str, torch.Tensor]]:
+        if self.runtime is not None:
+            r = self.runtime
+            out = [("count", torch.tensor(r.count, dtype=torch.int64))]
+            for kind, arena in (("mu", r.m), ("nu", r.v)):
+                for name, u in r.units.items():
+                    full = torch.empty(u.padded, dtype=torch.bfloat16, device=self.device)
+                    torch.distributed.all_gather_into_tensor(full, r.shard_view(name, of=arena).contiguous(), group=r.group)
+                    out.append((f"{kind}/{name}", full[:u.layout.numel].cpu()))
+            return out
+        opt = self.step_fn.optimizer
+        out = [("count", torch.tensor(opt.count, dtype=torch.int64))]
+        for i, (m, v) in enumerate(zip(opt.m, opt.v)):
+            out.append((f"mu/{i:05d}", m.detach().cpu()))
+            out.append((f"nu/{i:05d}", v.detach().cpu()))
+        return out
+
+    def load_optimizer_state(self, path: Path, step: int) -> None:
+        names = [n for n, _ in self.optimizer_state()]
+        state = hfio.load_optimizer_checkpoint(path, names, global_step=step)
+        if self.runtime is not None:
+            r = self.runtime
+            r.count = int(state["count"])
+            for kind, arena in (("mu", r.m), ("nu", r.v)):
+                for name, u in r.units.items():
+                    full = state[f"{kind}/{name}"]
+                    lo = r.rank * u.shard_elems
+                    piece = full[lo:min(lo + u.shard_elems, full.numel())]
+                    view = r.shard_view(name, of=arena)
+                    view.zero_()
+                    view[:piece.numel()].copy_(piece)
+            return
+        opt = self.step_fn.optimizer
+        opt.count = int(state["count"])
+        for i, (m, v) in enumerate(zip(opt.m, opt.v)):
+            m.copy_(state[f"mu/{i:05d}"])
+            v.copy_(state[f"nu/{i:05d}"])
+
+    # ---- checkpoint bundles ----
+    def save_bundle(self, destination: Path, step: int) -> None:
+        a = self.args
+
+        def export_model(dest: Path, cid: str) -> None:
+            if self.artifact_kind == "peft-adapter":
+                if rt.process_index() == 0:
+                    st.save_file(self.lora.peft_tensors(), dest / "adapter_model.safetensors",
+                                 {"format": "pt", "checkpoint_id": cid})
+                    (dest / "adapter_config.json").write_text(json.dumps(peft_adapter_config(
+                        a.repo_id, a.lora_rank, train_embed_and_lm_head=a.lora_train_embed_and_lm_head,
+                        revision=a.revision), indent=2, sort_keys=True) + "\n")
+                return
+            source = hfio.TensorSource(self.cfg, params=self.params, runtime=self.runtime,
+                                       transform=self.lora.export_transform() if self.lora is not None else None)
+            hfio.export_hf_checkpoint(dest, source, checkpoint_id=cid, assets_from=self.processor_source)
+
+        export_optimizer = None
+        if a.save_optimizer_state:
+            state = self.optimizer_state()
+
+            def export_optimizer(dest: Path, cid: str) -> None:
+                hfio.export_optimizer_checkpoint(dest, state, global_step=step, checkpoint_id=cid)
+        bundles.save_checkpoint_bundle(
+            destination, export_model=export_model, export_optimizer=export_optimizer, artifact_kind=self.artifact_kind,
+            global_step=step, total_steps=self.plan.total_steps, signature=self.signature,
+            source_examples_seen=self.source_examples_seen, streaming_data_digest=self.stream_digest,
+            training_complete=self.training_complete)
+
+    # ---- stage 7: batches ----
+    def global_batches(self) -> Iterator[Any]:
+        a = self.args
+        if not self.streaming:
+            it = batching.iter_global_batches(self.dataset, self.plan, assistant_only_loss=a.uses_assistant_loss_mask,
+                                              shuffle=a.shuffle, seed=a.seed, start_step=self.start_step)
+        else:
+            if a.dataset_format == "prepared":
+                envelopes = prepared.iter_prepared_streaming_batches(
+                    a.dataset_name, self.manifest, num_epochs=self.plan.epochs, window_size=a.packing_batch_size,
+                    token=a.token, revision=self.prepared_revision)
+            else:
+                source = self.stream_source
+
+                def factory(epoch: int):
+                    s = source.shuffle(seed=a.seed, buffer_size=a.streaming_shuffle_buffer) if a.shuffle else source
+                    if hasattr(s, "set_epoch"):
+                        s.set_epoch(epoch)
+                    return s
+
+                envelopes = streaming.iter_streaming_batches(
+                    factory, self.tokenizer, num_epochs=self.plan.epochs, dataset_text_field=a.dataset_text_field,
+                    max_sequence_length=a.max_sequence_length, pad_token_id=self._pad_token_id(),
+                    assistant_only_loss=a.assistant_only_loss, last_assistant_only_loss=a.last_assistant_only_loss,
+                    endprompt=endprompt_settings(a), packing=a.packing, packing_batch_size=a.packing_batch_size,
+                    retry_initial_delay=a.hf_retry_initial_delay, retry_max_delay=a.hf_retry_max_delay)
+            ck = self.checkpoint
+            it = streaming_batching.iter_streaming_global_batches(
+                envelopes, self.plan, assistant_only_loss=a.uses_assistant_loss_mask, start_step=self.start_step,
+                expected_source_examples_before=ck.source_examples_seen if ck else None,
+                expected_stream_digest_before=ck.streaming_data_digest if ck else None)
+        if a.maskgit_probability:
+            it = maskgit.MaskGITBatchTransform(self.tokenizer, probability=a.maskgit_probability,
+                                               seed=a.seed).batches(it, start_step=self.start_step)
+        return it
+
+    def vote_on_stream_batch(self, batch, error: BaseException | None) -> str:
+        """One byte of status plus the batch digest from every rank: BATCH, EOF or ERROR must agree."""
+        if error is not None:
+            payload = b"E" + bytes(32)
+        elif batch is None:
+            payload = b"F" + bytes(32)
+        else:
+            payload = b"B" + streaming_batching.streaming_global_batch_digest(batch)
+        votes = rt.host_allgather_bytes(payload, 33)
+        kinds = {v[:1] for v in votes}
+        if b"E" in kinds:
+            raise error if error is not None else RuntimeError("another process failed while reading the stream")
+        if len(kinds) != 1 or len({v for v in votes}) != 1:
+            raise RuntimeError("processes disagree on the streaming batch (different data or end of stream)")
+        return "eof" if batch is None else "batch"
+
+    def to_device(self, data: dict[str, np.ndarray]) -> list[dict[str, torch.Tensor]]:
+        """This rank's rows of a global batch as device micro-batches (pinned staging, async copies)."""
+        a = self.args
+        ranks = self.lattice.size("dp") * self.lattice.size("fsdp")
+        idx = self.lattice.index_in(("dp", "fsdp")) if ranks > 1 else 0
+        per_micro = a.total_batch_size // ranks
+        micro = []
+        split = batching.split_accumulation(data, a.gradient_accumulation_steps)
+        for g in range(a.gradient_accumulation_steps):
+            rows = {}
+            for k, v in split.items():
+                t = torch.from_numpy(np.ascontiguousarray(v[g][idx * per_micro:(idx + 1) * per_micro]))
+                if self.cuda:
+                    t = t.pin_memory().to(self.device, non_blocking=True)
+                rows[k] = t
+            sub = a.micro_batch_rows or per_micro
+            for r0 in range(0, per_micro, sub):
+                micro.append({k: v[r0:r0 + sub] for k, v in rows.items()})
+        return micro
+
+    # ---- the loop ----
+    def train(self) -> None:
+        a = self.args
+        out = Path(a.output_dir)
+        if self.action == "complete":
+            log.info("training is already complete at step %d", self.start_step)
+            return
+        if rt.process_index() == 0:
+            out.mkdir(parents=True, exist_ok=True)
+            (out / "training_args.json").write_text(json.dumps(
+                {f.name: getattr(a, f.name) for f in dataclasses.fields(a)}, indent=2, sort_keys=True, default=str))
+        rt.sync_processes("training-args-written")
+        tracker = tlog.ThroughputTracker(self.cfg, a.max_sequence_length, rt.process_count())
+        wandb_run = tlog.init_wandb(a) if rt.process_index() == 0 else None
+        window = MetricWindow(a.async_dispatch_steps)
+        step = self.start_step
+        if self.action != "finalize":
+            batches = batching.prefetch_map(self.global_batches(), lambda b: (b, self.to_device(
+                b if isinstance(b, dict) else b.data)), prefetch_batches=a.prefetch_batches)
+            it = iter(batches)
+            while step < self.plan.total_steps:
+                item, error = None, None
+                try:
+                    item = next(it)
+                except StopIteration:
+                    item = None
+                except Exception as exc:  # noqa: BLE001
+                    error = exc
+                if self.streaming:
+                    if self.vote_on_stream_batch(item[0] if item else None, error) == "eof":
+                        break
+                elif error is not None:
+                    rt.raise_if_any_process_error(error, "read batch")
+                elif item is None:
+                    break
+                raw, micro = item
+                t0 = time.monotonic()
+                lr_position = None
+                if self.streaming and a.max_steps <= 0 and self.plan.steps_per_epoch:
+                    lr_position = streaming_schedule_position(
+                        step - raw.epoch * self.plan.steps_per_epoch if hasattr(raw, "epoch") else step,
+                        getattr(raw, "epoch", 0), self.plan.steps_per_epoch)
+                metrics = self.step_fn.run(micro, lr_position=lr_position)
+                step += 1
+                if hasattr(raw, "source_examples_seen"):
+                    self.source_examples_seen, self.stream_digest = raw.source_examples_seen, raw.stream_digest
+                window.push(step, metrics)
+                tracker.step(a.effective_batch_size, time.monotonic() - t0)
+                first_or_last = step == self.start_step + 1 or step == self.plan.total_steps
+                if step % a.logging_steps == 0 or first_or_last:
+                    latest = window.drain()
+                    if self.cuda:
+                        torch.cuda.synchronize(self.device)
+                    tlog.log_step(latest, tracker, self.device if a.track_memory else None, wandb_run)
+                if a.save_steps and step % a.save_steps == 0 and step < self.plan.total_steps:
+                    window.drain()
+                    self.save_bundle(out / f"checkpoint-{step}", step)
+                    bundles.prune_periodic_exports(out, a.save_total_limit, self.signature)
+            window.drain()
+        if self.streaming and not self.plan.has_exact_step_limit:
+            self.training_complete = True
+            self.plan = dataclasses.replace(self.plan, total_steps=step)
+        self.save_bundle(out, step)
+        rt.sync_processes("training-complete")
+        if wandb_run is not None:
+            wandb_run.finish()
+
+
+def main(argv: list[str] | None = None) -> int:
+    args = parse_args(argv)
+    run = TrainingRun(args)
+    run.resolve_model()
+    run.load_data()
+    run.discover_resume()
+    run.build_model()
+    run.train()
+    return 0

@@ -28,7 +28,6 @@ from ..models.params import ModelParams
 from . import losses
 from .optimizer import AdamWConfig, FlatAdamW, ScheduleConfig, learning_rate_at
 
-FROZEN_COMPONENTS = {"embed": ("embed", "embed"), "lm_head": ("final", "lm_head"), "norm": ("final", "norm")}
 
 
 class GradientProducer(Protocol):
@@ -119,7 +118,9 @@ class TrainStep:
     def __post_init__(self) -> None:
         self._regions: list[tuple[torch.Tensor, bool]] = []
         self._grad_of: list[Callable[[], torch.Tensor]] = []
-        frozen_segs = {FROZEN_COMPONENTS[c] for c in self.frozen}
+        from ..models.freezing import frozen_segments
+
+        frozen_segs = frozen_segments(self.params.config, tuple(self.frozen))
         if self.train_base:
             for name, u in self.params.units.items():
                 for seg in u.layout.segments:

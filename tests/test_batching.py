@@ -1,0 +1,54 @@
+import numpy as np
+import pytest
+
+from causal_trainer_dev_b200.data.batching import BatchPlan, collate, iter_global_batches, prefetch_map
+
+
+def test_plan_arithmetic():
+    p = BatchPlan.create(128, 16, 2, 1.0, -1)
+    assert p.effective_batch_size == 32 and p.steps_per_epoch == 4 and p.total_steps == 4
+    assert BatchPlan.create(128, 16, 2, 1.0, 9).total_steps == 9
+    with pytest.raises(ValueError, match="divisible"):
+        BatchPlan.create(100, 16, 2, 1.0, -1)
+
+
+def _dataset(n, s=4):
+    return [dict(input_ids=[i] * s, attention_mask=[1] * s, position_ids=list(range(s)), segment_ids=[1] * s)
+            for i in range(n)]
+
+
+def test_resume_reproduces_the_tail():
+    ds = _dataset(16)
+    plan = BatchPlan.create(16, 2, 1, 2.0, -1)
+    kw = dict(assistant_only_loss=False, shuffle=True, seed=3)
+    full = [b["input_ids"][:, 0].tolist() for b in iter_global_batches(ds, plan, **kw)]
+    tail = [b["input_ids"][:, 0].tolist() for b in iter_global_batches(ds, plan, start_step=7, **kw)]
+    assert len(full) == 16 and tail == full[7:]
+    assert sorted(sum(full[:8], [])) == list(range(16))  # one epoch covers every row once
+
+
+def test_loss_weight_precedence():
+    base = dict(input_ids=[1, 2], attention_mask=[1, 1], position_ids=[0, 1], segment_ids=[1, 1])
+    plain = collate([base], np.array([0]), False)
+    assert plain["loss_weights"].tolist() == [[1.0, 1.0]]
+    masked = collate([dict(base, assistant_masks=[0, 1])], np.array([0]), True)
+    assert masked["loss_weights"].tolist() == [[0.0, 1.0]]
+    explicit = collate([dict(base, assistant_masks=[0, 1], loss_weights=[0.5, 0.25])], np.array([0]), True)
+    assert explicit["loss_weights"].tolist() == [[0.5, 0.25]]
+    with pytest.raises(ValueError, match="mix weighted"):
+        collate([dict(base, loss_weights=[1.0, 1.0]), base], np.array([0, 1]), False)
+    with pytest.raises(ValueError, match="missing assistant_masks"):
+        collate([base], np.array([0]), True)
+
+
+def test_prefetch_converts_exactly_one_ahead():
+    seen = []
+
+    def f(x):
+        seen.append(x)
+        return x * 10
+
+    it = prefetch_map(range(4), f, prefetch_batches=1)
+    assert next(it) == 0 and seen == [0, 1]
+    assert next(it) == 10 and seen == [0, 1, 2]
+    assert list(it) == [20, 30] and seen == [0, 1, 2, 3]

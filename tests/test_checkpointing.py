@@ -1,0 +1,145 @@
+import json
+import struct
+
+import pytest
+import torch
+
+from causal_trainer_dev_b200.checkpointing import bundles, huggingface as hfio, safetensors_io as st
+from causal_trainer_dev_b200.models.config import preset
+from causal_trainer_dev_b200.models.params import ModelParams, hf_export_order
+
+
+def test_roundtrip_is_bit_exact_and_interoperates_with_the_safetensors_package(tmp_path):
+    torch.manual_seed(0)
+    tensors = {"b": torch.randn(3, 5).bfloat16(), "a": torch.randn(7), "i": torch.arange(6).view(2, 3),
+               "s": torch.tensor(3.5)}
+    st.save_file(tensors, tmp_path / "x.safetensors", {"format": "pt"})
+    back = st.load_file(tmp_path / "x.safetensors")
+    assert list(back) == list(tensors)
+    for k in tensors:
+        assert back[k].dtype == tensors[k].dtype and torch.equal(back[k], tensors[k])
+    raw = (tmp_path / "x.safetensors").read_bytes()
+    (hlen,) = struct.unpack("<Q", raw[:8])
+    assert hlen % 8 == 0 and raw[8:8 + hlen].rstrip(b" ").endswith(b"}")
+    from safetensors.torch import load_file, save_file
+
+    theirs = load_file(str(tmp_path / "x.safetensors"))
+    assert all(torch.equal(theirs[k], tensors[k]) for k in tensors)
+    save_file({k: v.contiguous() for k, v in tensors.items()}, str(tmp_path / "y.safetensors"))
+    ours = st.load_file(tmp_path / "y.safetensors")
+    assert all(torch.equal(ours[k], tensors[k]) for k in tensors)
+
+
+def test_reader_slices_and_validation(tmp_path):
+    t = torch.arange(40, dtype=torch.float32).view(10, 4)
+    st.save_file({"w": t}, tmp_path / "w.safetensors")
+    with st.SafeTensorsFile(tmp_path / "w.safetensors") as f:
+        assert torch.equal(f.rows("w", 3, 6), t[3:6]) and torch.equal(f.flat_range("w", 5, 9), t.reshape(-1)[5:9])
+    raw = bytearray((tmp_path / "w.safetensors").read_bytes())
+    (tmp_path / "trunc.safetensors").write_bytes(raw[:-4])
+    with pytest.raises(ValueError, match="payload size"):
+        st.read_header(tmp_path / "trunc.safetensors")
+    w = st.StreamingWriter(tmp_path / "o.safetensors", [("a", "F32", (2,)), ("b", "F32", (2,))])
+    with pytest.raises(ValueError, match="header order"):
+        w.write("b", torch.zeros(2))
+    w.abort()
+    assert not (tmp_path / "o.safetensors").exists() and not (tmp_path / "o.safetensors.tmp").exists()
+
+
+def _export(tmp_path, name="out", step=3, total=10, signature="sig", seed=0, optimizer=False, **kw):
+    cfg = preset("tiny", vocab_size=128, num_hidden_layers=1, hidden_size=64, intermediate_size=128,
+                 num_attention_heads=1, num_key_value_heads=1)
+    params = ModelParams.init_random(cfg, seed=seed, dtype=torch.bfloat16)
+    dest = tmp_path / name
+
+    def export_model(d, cid):
+        hfio.export_hf_checkpoint(d, hfio.TensorSource(cfg, params=params), checkpoint_id=cid)
+
+    export_opt = None
+    if optimizer:
+        state = [("count", torch.tensor(step)), ("mu/0", torch.zeros(4).bfloat16()), ("nu/0", torch.ones(4).bfloat16())]
+
+        def export_opt(d, cid):
+            hfio.export_optimizer_checkpoint(d, state, global_step=step, checkpoint_id=cid)
+    bundles.save_checkpoint_bundle(dest, export_model=export_model, export_optimizer=export_opt, global_step=step,
+                                   total_steps=total, signature=signature, **kw)
+    return cfg, params, dest
+
+
+def test_export_order_metadata_and_reload_bit_exact(tmp_path):
+    cfg, params, dest = _export(tmp_path)
+    tensors, meta, _ = st.read_header(dest / "model.safetensors")
+    assert list(tensors) == hf_export_order(cfg) and meta["format"] == "pt" and len(meta["checkpoint_id"]) == 32
+    assert list(tensors)[:2] == ["model.embed_tokens.weight", "model.layers.0.self_attn.k_proj.weight"]
+    assert list(tensors)[-2:] == ["lm_head.weight", "model.norm.weight"]
+    again = ModelParams(cfg, torch.bfloat16)
+    hfio.load_parameters(dest, again)
+    for name in params.hf_names():
+        assert torch.equal(again.tensor(name), params.tensor(name))
+    assert json.loads((dest / "config.json").read_text())["torch_dtype"] == "bfloat16"
+
+
+def test_discovery_prefers_highest_step_and_root_at_equal_step(tmp_path):
+    out = tmp_path / "run"
+    _export(out, "checkpoint-3", step=3)
+    _export(out, "checkpoint-6", step=6)
+    found = bundles.find_latest_checkpoint(out, "sig")
+    assert found.global_step == 6 and found.path.name == "checkpoint-6"
+    _export(tmp_path, "run", step=6)
+    assert bundles.find_latest_checkpoint(out, "sig").path == out
+    assert bundles.find_latest_checkpoint(tmp_path / "nothing", "sig") is None
+
+
+def test_incompatible_and_corrupt_bundles_are_hard_errors(tmp_path):
+    out = tmp_path / "run"
+    _, _, d = _export(out, "checkpoint-3", step=3)
+    with pytest.raises(ValueError, match="incompatible"):
+        bundles.find_latest_checkpoint(out, "other-signature")
+    blob = bytearray((d / "model.safetensors").read_bytes())
+    blob[-1] ^= 0xFF                                     # same size, different payload
+    (d / "model.safetensors").write_bytes(blob)
+    with pytest.raises(ValueError, match="corrupt"):
+        bundles.find_latest_checkpoint(out, "sig")
+    assert bundles.find_latest_checkpoint(out, "sig", verify_artifact_digests=False) is not None
+
+
+def test_model_file_from_another_bundle_is_caught_by_checkpoint_id(tmp_path):
+    out = tmp_path / "run"
+    _, _, a = _export(out, "checkpoint-3", step=3)
+    _, _, b = _export(tmp_path, "other", step=3)
+    m = json.loads((a / bundles.MANIFEST_NAME).read_text())
+    (a / "model.safetensors").write_bytes((b / "model.safetensors").read_bytes())
+    m["artifact_digests"]["model.safetensors"] = bundles.file_sha256(a / "model.safetensors")
+    (a / bundles.MANIFEST_NAME).write_text(json.dumps(m))
+    with pytest.raises(ValueError, match="corrupt"):
+        bundles.find_latest_checkpoint(out, "sig")
+
+
+def test_resume_action_table(tmp_path):
+    out = tmp_path / "run"
+    mk = lambda **k: bundles.ResumeCheckpoint(**{**dict(path=out / "checkpoint-5", global_step=5, total_steps=10,
+                                                        has_optimizer_state=True, checkpoint_id="0" * 32,
+                                                        manifest_digest="d"), **k})
+    ra = lambda c: bundles.resume_action(c, output_dir=out, total_steps=10)
+    assert ra(None) == "start" and ra(mk()) == "continue"
+    assert ra(mk(global_step=10, path=out / "checkpoint-10")) == "finalize" and ra(mk(global_step=10, path=out)) == "complete"
+    with pytest.raises(ValueError, match="optimizer state"):
+        ra(mk(has_optimizer_state=False))
+    with pytest.raises(ValueError, match="total_steps"):
+        ra(mk(total_steps=11))
+    assert ra(mk(training_complete=True, path=out, global_step=10, streaming_data_digest="0" * 64)) == "complete"
+
+
+def test_optimizer_state_roundtrip_and_pruning(tmp_path):
+    out = tmp_path / "run"
+    _, _, d = _export(out, "checkpoint-3", step=3, optimizer=True)
+    found = bundles.find_latest_checkpoint(out, "sig")
+    assert found.has_optimizer_state
+    state = hfio.load_optimizer_checkpoint(d, ["count", "mu/0", "nu/0"], global_step=3)
+    assert int(state["count"]) == 3 and state["nu/0"].dtype == torch.bfloat16
+    with pytest.raises(ValueError, match="layout"):
+        hfio.load_optimizer_checkpoint(d, ["count", "mu/1", "nu/1"], global_step=3)
+    _export(out, "checkpoint-6", step=6)
+    _export(out, "checkpoint-9", step=9)
+    removed = bundles.prune_periodic_exports(out, 2, "sig")
+    assert [p.name for p in removed] == ["checkpoint-3"] and (out / "checkpoint-9").is_dir()

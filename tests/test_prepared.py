@@ -1,0 +1,96 @@
+import json
+
+import numpy as np
+import pytest
+
+from causal_trainer_dev_b200 import prepare
+from causal_trainer_dev_b200.data import prepared as P
+from helpers import write_tokenizer
+
+
+def _write_jsonl(path, n=30):
+    rows = [{"text": " ".join(f"w{(i * 7 + j) % 40}" for j in range(2 + i % 9))} for i in range(n)]
+    path.write_text("\n".join(json.dumps(r) for r in rows))
+    return path
+
+
+def _prepare(tmp_path, shards=2, extra=()):
+    tok = write_tokenizer(tmp_path / "tok")
+    data = _write_jsonl(tmp_path / "d.jsonl")
+    out = tmp_path / "prepared"
+    args = prepare.parse_args(["--dataset_name", str(data), "--tokenizer_name_or_path", str(tok), "--output_dir", str(out),
+                               "--max_sequence_length", "16", "--packing", "--num_shards", str(shards), *extra])
+    return prepare.prepare_dataset(args), out
+
+
+def test_prepare_cli_writes_manifest_last_and_valid_shards(tmp_path):
+    manifest, out = _prepare(tmp_path)
+    assert (out / P.PREPARED_MANIFEST_FILENAME).is_file() and len(manifest.shards) == 2
+    assert [s.path for s in manifest.shards] == ["data/shard-00000-of-00002.parquet", "data/shard-00001-of-00002.parquet"]
+    again = P.load_prepared_manifest(str(out))
+    assert again.global_digest == manifest.global_digest and again.to_dict()["format"] == "causal-trainer-prepared"
+    cols = P.load_prepared_dataset(str(out), again)
+    assert cols["input_ids"].shape == (manifest.total_rows, 16) and cols["loss_weights"].dtype == np.float32
+    assert cols["input_ids"].dtype == np.int32 and (cols["segment_ids"] > 0).sum() == (cols["attention_mask"] == 1).sum()
+    # contiguous file assignment per process
+    a = P.load_prepared_dataset(str(out), again, process_index=0, process_count=2)
+    b = P.load_prepared_dataset(str(out), again, process_index=1, process_count=2)
+    assert np.array_equal(np.concatenate([a["input_ids"], b["input_ids"]]), cols["input_ids"])
+
+
+def test_output_dir_must_be_empty_and_failures_clean_up(tmp_path):
+    _, out = _prepare(tmp_path)
+    with pytest.raises(FileExistsError):
+        _prepare(tmp_path)
+    bad = tmp_path / "bad"
+    tok = tmp_path / "tok"
+    args = prepare.parse_args(["--dataset_name", str(tmp_path / "d.jsonl"), "--tokenizer_name_or_path", str(tok),
+                               "--output_dir", str(bad), "--max_sequence_length", "16", "--dataset_text_field", "nope"])
+    with pytest.raises(KeyError):
+        prepare.prepare_dataset(args)
+    assert not bad.exists()
+
+
+def test_corrupt_shard_is_detected_by_digest(tmp_path):
+    manifest, out = _prepare(tmp_path, shards=1)
+    f = out / manifest.shards[0].path
+    blob = bytearray(f.read_bytes())
+    blob[len(blob) // 2] ^= 0xFF
+    f.write_bytes(blob)
+    with pytest.raises(RuntimeError, match="SHA-256"):
+        P.load_prepared_dataset(str(out), manifest)
+
+
+def test_manifest_validation():
+    shard = P.PreparedShard("data/a.parquet", 3, "0" * 64)
+    m = P.PreparedDatasetManifest(8, "train", (shard,), {}, {}, {}, 10, 7)
+    d = m.to_dict()
+    assert P.PreparedDatasetManifest.from_dict(d).global_digest == m.global_digest
+    with pytest.raises(ValueError, match="total_rows"):
+        P.PreparedDatasetManifest.from_dict({**d, "total_rows": 4})
+    with pytest.raises(ValueError, match="fields mismatch"):
+        P.PreparedDatasetManifest.from_dict({k: v for k, v in d.items() if k != "schema"})
+    for bad in ("../x.parquet", "/abs/x.parquet", "a\\b.parquet", "x.txt"):
+        with pytest.raises(ValueError):
+            P.PreparedShard(bad, 1, "0" * 64)
+
+
+def test_semantic_row_validation():
+    ok = dict(input_ids=[[5, 6, 7, 0]], attention_mask=[[1, 1, 1, 0]], position_ids=[[0, 1, 2, 0]],
+              segment_ids=[[1, 1, 1, 0]], loss_weights=[[1.0, 1.0, 1.0, 0.0]])
+    kw = dict(max_sequence_length=4, max_token_id=10, max_position_id=5, uses_assistant_loss_mask=False)
+    P.validate_prepared_batch(ok, **kw)
+    for field, value, msg in [
+        ("input_ids", [[5, 6, 11, 0]], "max_token_id"), ("attention_mask", [[1, 2, 1, 0]], "0/1"),
+        ("segment_ids", [[1, 1, 0, 0]], "positive exactly"), ("position_ids", [[0, 1, 2, 3]], "zero outside"),
+        ("loss_weights", [[1.0, 1.0, 1.0, 0.5]], "zero outside"), ("loss_weights", [[1.0, 0.0, 0.0, 0.0]], "no positive-weight"),
+        ("segment_ids", [[1, 2, 1, 0]], "reuses a segment id"),
+    ]:
+        with pytest.raises(ValueError, match=msg):
+            P.validate_prepared_batch({**ok, field: value}, **kw)
+
+
+def test_prepared_streaming_envelopes(tmp_path):
+    manifest, out = _prepare(tmp_path)
+    env = list(P.iter_prepared_streaming_batches(str(out), manifest, num_epochs=2, window_size=3))
+    assert sum(e.is_epoch_end for e in env) == 2 and sum(e.source_examples for e in env) == 2 * manifest.total_rows
