@@ -258,7 +258,12 @@ class PackedArrayDataset:
             raise IndexError(index)
         if index >= self.real_rows:
             return dict(self._dummy)
-        return {k: v[index] for k, v in self.columns.items()}
+        row = {k: v[index] for k, v in self.columns.items()}
+        if self._dummy is not None and "loss_weights" not in row:
+            # dummy rows carry explicit zero weights, so real rows of the same batches state theirs too
+            source = row["assistant_masks"] if "assistant_masks" in row else row["attention_mask"]
+            row["loss_weights"] = source.astype(np.float32)
+        return row
 
 
 def first_row_without_target(columns: Mapping[str, np.ndarray], chunk: int = 4096) -> int | None:

@@ -1,0 +1,100 @@
+"""causal-train end to end on CPU: raw JSONL -> tokenise -> pack -> train -> bundle -> resume."""
+import json
+
+import pytest
+import torch
+
+from causal_trainer_dev_b200.checkpointing import bundles, safetensors_io as st
+from causal_trainer_dev_b200.training import runner
+from causal_trainer_dev_b200.training.arguments import parse_args
+from helpers import write_model_dir
+
+
+def _data(path, n=40):
+    rows = [{"text": " ".join(f"w{(i * 3 + j) % 40}" for j in range(4 + i % 11))} for i in range(n)]
+    path.write_text("\n".join(json.dumps(r) for r in rows))
+    return path
+
+
+def _argv(tmp_path, *extra):
+    model = write_model_dir(tmp_path / "model") if not (tmp_path / "model").exists() else tmp_path / "model"
+    data = _data(tmp_path / "train.jsonl")
+    return ["--repo_id", str(model), "--dataset_name", str(data), "--output_dir", str(tmp_path / "out"),
+            "--max_sequence_length", "32", "--packing", "--total_batch_size", "2", "--sharding_axis", "1,1,1,1,1",
+            "--param_dtype", "float32", "--dtype", "float32", "--attn_mechanism", "vanilla", "--loss_implementation", "xla",
+            "--learning_rate", "1e-2", "--scheduler", "constant", "--logging_steps", "1", "--no-distributed", *extra]
+
+
+def test_train_save_resume_complete(tmp_path):
+    argv = _argv(tmp_path, "--max_steps", "4", "--save_steps", "2", "--save_optimizer_state", "--save_total_limit", "1")
+    assert runner.main(argv) == 0
+    out = tmp_path / "out"
+    manifest = json.loads((out / bundles.MANIFEST_NAME).read_text())
+    assert manifest["global_step"] == 4 and manifest["total_steps"] == 4 and manifest["has_optimizer_state"]
+    assert manifest["format_version"] == 4 and manifest["artifact_kind"] == "merged"
+    assert (out / "model.safetensors").is_file() and (out / "tokenizer.json").is_file() and (out / "training_args.json").is_file()
+    assert (out / "checkpoint-2").is_dir()                     # the only periodic bundle (limit 1, step 4 is the final one)
+    tensors, meta, _ = st.read_header(out / "model.safetensors")
+    assert meta["checkpoint_id"] == manifest["checkpoint_id"] and tensors["lm_head.weight"].dtype == "F32"
+    # a second launch finds the finished run and does nothing
+    before = (out / "model.safetensors").read_bytes()
+    assert runner.main(argv) == 0 and (out / "model.safetensors").read_bytes() == before
+
+
+def test_interrupted_run_continues_bit_exactly(tmp_path):
+    full = _argv(tmp_path, "--max_steps", "4", "--save_optimizer_state")
+    run = runner.TrainingRun(parse_args(full))
+    run.resolve_model(); run.load_data(); run.discover_resume(); run.build_model(); run.train()
+    reference = st.load_file(tmp_path / "out" / "model.safetensors")
+    # same run, interrupted after step 2 (a periodic bundle exists), then relaunched
+    import shutil
+
+    shutil.rmtree(tmp_path / "out")
+    argv = _argv(tmp_path, "--max_steps", "4", "--save_optimizer_state", "--save_steps", "2")
+    run = runner.TrainingRun(parse_args(argv))
+    run.resolve_model(); run.load_data(); run.discover_resume(); run.build_model()
+    run.plan = type(run.plan)(**{**run.plan.__dict__, "total_steps": 4})
+    it = iter(run.global_batches())
+    for step in (1, 2):
+        raw = next(it)
+        run.step_fn.run(run.to_device(raw))
+    run.save_bundle(tmp_path / "out" / "checkpoint-2", 2)
+    resumed = runner.TrainingRun(parse_args(argv))
+    resumed.resolve_model(); resumed.load_data(); resumed.discover_resume()
+    assert resumed.action == "continue" and resumed.start_step == 2
+    resumed.build_model(); resumed.train()
+    again = st.load_file(tmp_path / "out" / "model.safetensors")
+    assert all(torch.equal(again[k], reference[k]) for k in reference)
+
+
+def test_changed_flags_make_old_checkpoints_incompatible(tmp_path):
+    assert runner.main(_argv(tmp_path, "--max_steps", "2")) == 0
+    with pytest.raises(ValueError, match="incompatible"):
+        runner.main(_argv(tmp_path, "--max_steps", "2", "--learning_rate", "3e-3"))
+
+
+def test_streaming_and_lora_adapter_modes(tmp_path):
+    argv = _argv(tmp_path, "--dataset_streaming", "--num_train_epochs", "1", "--no-shuffle")
+    assert runner.main(argv) == 0
+    m = json.loads((tmp_path / "out" / bundles.MANIFEST_NAME).read_text())
+    assert m["training_complete"] and m["source_examples_seen"] == 40 and len(m["streaming_data_digest"]) == 64
+    out2 = tmp_path / "lora"
+    argv = _argv(tmp_path, "--max_steps", "2", "--lora", "--lora_rank", "4", "--lora_save_adapter_only")
+    argv[argv.index("--output_dir") + 1] = str(out2)
+    assert runner.main(argv) == 0
+    cfg = json.loads((out2 / "adapter_config.json").read_text())
+    assert cfg["r"] == 4 and cfg["lora_alpha"] == 4 and cfg["peft_type"] == "LORA"
+    keys = st.read_header(out2 / "adapter_model.safetensors")[0]
+    assert "base_model.model.model.layers.0.self_attn.q_proj.lora_A.weight" in keys
+    assert json.loads((out2 / bundles.MANIFEST_NAME).read_text())["artifact_kind"] == "peft-adapter"
+
+
+def test_pure_helpers():
+    assert runner.prepared_streaming_limits(10, 4, 1.5, -1) == (4, 2)
+    assert runner.prepared_streaming_limits(2, 8, 0.25, -1) == (1, 1)
+    assert runner.prepared_streaming_limits(10, 4, 0, 7) == (7, None)
+    assert [runner.buffered_streaming_schedule_total(n) for n in (0, 1, 19, 20, 100, 101)] == [1, 2, 20, 21, 105, 107]
+    pos = [runner.streaming_schedule_position(s, e, 3) for e, s in ((0, 0), (0, 2), (0, 3), (0, 5), (1, 0), (2, 0), (2, 9))]
+    assert pos == [0, 2, 3, 3, 3, 6, 9]
+    assert runner.project_streaming_progress_total(5, 1, 3) == 15 and runner.project_streaming_progress_total(10, 2, 3) == 15
+    assert runner.project_streaming_progress_total(14, 3, 3) == 14
