@@ -47,12 +47,26 @@ def parse() -> argparse.Namespace:
 
 
 def reference_arm() -> None:
-    reason = (
-        "unavailable on this box: the reference needs jax/jaxlib/optax (not installed, no network), raises for any "
-        "non-TPU backend (training/runner.py:337-338), rejects every config but its fixed 40-layer MQA model "
-        "(runner.py:190-216) and its kernels are Pallas-TPU programs with no GPU lowering"
-    )
-    print(json.dumps({"impl": "reference", "unavailable": reason}))
+    """Runs the unmodified reference from ``baseline/_ref`` when that is possible at all.
+
+    The package itself installs offline (``pip --no-deps --target baseline/_ref``), but its
+    trainer imports JAX, refuses every backend but TPU and every architecture but its own, so
+    on a CUDA box the arm can only report why it cannot run.
+    """
+    ref = ROOT / "baseline" / "_ref"
+    reasons = []
+    if not (ref / "causal_trainer").is_dir():
+        reasons.append("baseline/_ref is not installed")
+    else:
+        sys.path.insert(0, str(ref))
+        try:
+            import jax  # noqa: F401
+        except ImportError:
+            reasons.append("jax/jaxlib/optax are not installed and there is no network to fetch them")
+    reasons.append("the reference trainer raises for any non-TPU backend (training/runner.py:337-338), rejects every "
+                   "config but its fixed 40-layer MQA model (runner.py:190-216), and its attention and loss kernels "
+                   "are Pallas-TPU programs with no GPU lowering")
+    print(json.dumps({"impl": "reference", "unavailable": "unavailable on this box: " + "; ".join(reasons)}))
 
 
 class ClockSampler:

@@ -1,0 +1,108 @@
+"""Small, self-terminating single-kernel workloads for profiling and roofline numbers.
+
+    python -m causal_trainer_dev_b200.benchmarks.kernel_cases gemm|wgrad|attn_fwd|attn_bwd|cut_ce|rmsnorm|adamw
+
+Each case holds a few hundred MB (more than the 126 MB L2, far less than a GB-scale step),
+launches its kernel a handful of times, and prints device-timed milliseconds plus the achieved
+fraction of the measured peaks (``MEASURED_PEAKS.json`` beside the repository root when present).
+"""
+from __future__ import annotations
+
+import json
+import sys
+from pathlib import Path
+
+import torch
+
+ROOT = Path(__file__).resolve().parents[2]
+sys.path.insert(0, str(ROOT))
+
+
+def peaks() -> dict:
+    p = ROOT / "MEASURED_PEAKS.json"
+    return json.loads(p.read_text()) if p.exists() else {"bf16_tflops": 1590.0, "hbm_gbs": 6650.0, "fallback": True}
+
+
+def timed(fn, iters: int = 5, warmup: int = 3) -> float:
+    for _ in range(warmup):
+        fn()
+    torch.cuda.synchronize()
+    s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    s.record()
+    for _ in range(iters):
+        fn()
+    e.record()
+    torch.cuda.synchronize()
+    return s.elapsed_time(e) / iters
+
+
+def main() -> None:
+    from causal_trainer_dev_b200.ops import attention as A, cross_entropy as CE, elementwise as E, gemm as G
+
+    case = sys.argv[1] if len(sys.argv) > 1 else "gemm"
+    pk = peaks()
+    torch.manual_seed(0)
+    out: dict = {"case": case, "peaks": "measured" if "fallback" not in pk else "fallback"}
+    dev = "cuda"
+    if case in ("gemm", "wgrad", "dgrad"):
+        m, n, k = 8192, 8192, 4096
+        if case == "gemm":
+            a, b = torch.randn(m, k, device=dev).bfloat16(), torch.randn(n, k, device=dev).bfloat16()
+            fn = lambda: G.gemm(a, b)  # noqa: E731
+        elif case == "dgrad":
+            a, b = torch.randn(m, k, device=dev).bfloat16(), torch.randn(k, n, device=dev).bfloat16()
+            fn = lambda: G.gemm(a, b, b_mn=True)  # noqa: E731
+        else:
+            a, b = torch.randn(k, m, device=dev).bfloat16(), torch.randn(k, n, device=dev).bfloat16()
+            fn = lambda: G.gemm(a, b, a_mn=True, b_mn=True)  # noqa: E731
+        ms = timed(fn)
+        tf = 2.0 * m * n * k / ms / 1e9
+        out.update(ms=ms, tflops=tf, fraction_of_measured_bf16_peak=tf / pk["bf16_tflops"])
+    elif case in ("attn_fwd", "attn_bwd"):
+        b, s, hq, hkv, d = 2, 4096, 32, 8, 128
+        q = torch.randn(b, s, hq, d, device=dev).bfloat16()
+        k = torch.randn(b, s, hkv, d, device=dev).bfloat16()
+        v = torch.randn(b, s, hkv, d, device=dev).bfloat16()
+        meta = A.build_attention_meta(torch.ones(b, s, dtype=torch.int32, device=dev))
+        o, lse = A.flash_attention_forward(q, k, v, meta)
+        if case == "attn_fwd":
+            ms = timed(lambda: A.flash_attention_forward(q, k, v, meta))
+            flops = 4.0 * b * hq * s * s * d / 2
+        else:
+            do = torch.randn_like(o)
+            ms = timed(lambda: A.flash_attention_backward(q, k, v, o, do, lse, meta))
+            flops = 10.0 * b * hq * s * s * d / 2
+        tf = flops / ms / 1e9
+        out.update(ms=ms, causal_tflops=tf, fraction_of_measured_bf16_peak=tf / pk["bf16_tflops"])
+    elif case == "cut_ce":
+        rows, d, vocab = 4096, 4096, 128256
+        h = torch.randn(rows, d, device=dev).bfloat16()
+        w = (0.02 * torch.randn(vocab, d, device=dev)).bfloat16()
+        t = torch.randint(0, vocab, (rows,), device=dev)
+        wt = torch.ones(rows, device=dev)
+        ms = timed(lambda: CE.cut_ce_forward(h, w, t, wt))
+        tf = 2.0 * rows * d * vocab / ms / 1e9
+        out.update(ms=ms, tflops=tf, fraction_of_measured_bf16_peak=tf / pk["bf16_tflops"])
+    elif case == "rmsnorm":
+        rows, d = 32768, 4096
+        x = torch.randn(rows, d, device=dev).bfloat16()
+        r = torch.randn(rows, d, device=dev).bfloat16()
+        w = torch.ones(d, device=dev).bfloat16()
+        ms = timed(lambda: E.rmsnorm_forward(x, w, 1e-6, residual=r))
+        gbs = 4.0 * rows * d * 2 / ms / 1e6
+        out.update(ms=ms, gbs=gbs, fraction_of_measured_copy_bandwidth=gbs / pk["hbm_gbs"])
+    elif case == "adamw":
+        n = 1 << 27
+        p, g, m, v = (torch.randn(n, device=dev).bfloat16() for _ in range(4))
+        v.abs_()
+        clip = torch.ones(1, device=dev)
+        ms = timed(lambda: E.adamw_update(p, g, m, v, lr=1e-4, b1=0.9, b2=0.999, eps=1e-8, decay=0.1, step=2, clip=clip))
+        gbs = 7.0 * n * 2 / ms / 1e6
+        out.update(ms=ms, gbs=gbs, fraction_of_measured_copy_bandwidth=gbs / pk["hbm_gbs"])
+    else:
+        raise SystemExit(f"unknown case {case}")
+    print(json.dumps(out))
+
+
+if __name__ == "__main__":
+    main()
