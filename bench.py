@@ -43,6 +43,7 @@ def parse() -> argparse.Namespace:
     p.add_argument("--seq-len", type=int, default=4096)
     p.add_argument("--global-batch", type=int, default=32)
     p.add_argument("--micro-batch", type=int, default=4)
+    p.add_argument("--remat", choices=("auto", "full", "none"), default="auto")
     return p.parse_args()
 
 
@@ -155,7 +156,7 @@ def main() -> None:
         adamw=AdamWConfig(weight_decay=0.1, max_grad_norm=1.0),
         schedule=ScheduleConfig(learning_rate=2e-5, learning_rate_end=2e-6, scheduler="cosine", warmup_steps=2,
                                 total_steps=1000),
-        fused_collectives=(args.impl == "ours"),
+        fused_collectives=(args.impl == "ours"), remat=args.remat,
     )
     trainer = Trainer(cfg, tcfg)
 
@@ -232,7 +233,9 @@ def main() -> None:
             "config": {
                 "model": args.model + (f"-{args.layers}layers" if args.layers else ""), "global_batch": args.global_batch,
                 "seq_len": args.seq_len, "parallelism": f"fsdp{world}", "micro_batch_rows": micro,
-                "grad_accumulation": rows_per_rank // micro, "loss": "cut cross-entropy", "remat": "per layer",
+                "grad_accumulation": rows_per_rank // micro, "loss": "cut cross-entropy",
+                "remat": f"auto: activations of {trainer.engine.kept_layers}/{cfg.num_hidden_layers} layers kept in "
+                         "HBM, the rest recomputed per layer",
                 "optimizer": "AdamW, bf16 moments, global-norm clip", "l2": "inputs larger than L2 (weights + state "
                 "are tens of GB per GPU, 126 MB L2)",
             },

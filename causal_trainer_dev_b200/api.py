@@ -33,6 +33,7 @@ class TrainerConfig:
     fused_collectives: bool = True     # in-kernel NVLink all-gather / reduce-scatter instead of NCCL
     cut_chunk_rows: int = 4096
     init: str = "normal"               # "normal": N(0, initializer_range) on the device; "hf": ModelParams.init_random
+    remat: str = "auto"                # "auto": keep activations that fit, recompute the rest; "full"; "none"
 
 
 class Trainer:
@@ -48,12 +49,12 @@ class Trainer:
             from .parallel.fsdp import FsdpRuntime
 
             self.runtime = FsdpRuntime(model, self.cfg, self.device)
-            self.engine = LayerwiseEngine(model, self.runtime, EngineOptions(cut_chunk_rows=self.cfg.cut_chunk_rows))
+            self.engine = LayerwiseEngine(model, self.runtime, EngineOptions(cut_chunk_rows=self.cfg.cut_chunk_rows, remat=self.cfg.remat))
             self.step_fn = self.runtime.make_step(self.engine)
         else:
             self.params = self._init_params()
             self.provider = LocalProvider(self.params, torch.bfloat16)
-            self.engine = LayerwiseEngine(model, self.provider, EngineOptions(cut_chunk_rows=self.cfg.cut_chunk_rows))
+            self.engine = LayerwiseEngine(model, self.provider, EngineOptions(cut_chunk_rows=self.cfg.cut_chunk_rows, remat=self.cfg.remat))
             self.step_fn = TrainStep(self.params, self.engine, self.cfg.adamw, self.cfg.schedule)
         self._accum_checked = False
 

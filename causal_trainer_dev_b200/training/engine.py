@@ -67,6 +67,8 @@ class EngineOptions:
     train_lm_head: bool = True
     train_embed: bool = True
     train_norm: bool = True
+    remat: str = "auto"                      # "auto" | "full" | "none"
+    memory_reserve_bytes: int = 8 << 30
 
 
 class LayerwiseEngine:
@@ -78,6 +80,7 @@ class LayerwiseEngine:
         self.provider = provider
         self.options = options or EngineOptions()
         self.launches = 0
+        self.kept_layers = 0
         self._inv_freq: torch.Tensor | None = None
 
     # ------------------------------------------------------------------ helpers
@@ -101,7 +104,7 @@ class LayerwiseEngine:
 
     # ------------------------------------------------------------------ layer forward
     def _layer_forward(self, w: dict[str, torch.Tensor], resid: torch.Tensor, branch: torch.Tensor | None, ctx: dict,
-                       li: int, save: bool) -> tuple[torch.Tensor, torch.Tensor, dict | None]:
+                       li: int, save: str | None) -> tuple[torch.Tensor, torch.Tensor, dict | None]:
         cfg = self.cfg
         t = resid.shape[0]
         qw, kvw, d_head = cfg.query_width, cfg.key_value_width, cfg.head_dim
@@ -121,8 +124,10 @@ class LayerwiseEngine:
         mlp = gemm(act, w["down_w"])
         self._count(10)
         saved = None
-        if save:
+        if save == "all":      # transient: consumed by the backward pass that follows at once
             saved = dict(x=x, n1=n1, rstd1=rstd1, qkv=qkv, o=o, lse=lse, h=h, n2=n2, rstd2=rstd2, gu=gu, act=act)
+        elif save == "keep":   # kept from the forward pass: the three cheap tensors are rebuilt in backward
+            saved = dict(x=x, rstd1=rstd1, qkv=qkv, o=o, lse=lse, h=h, rstd2=rstd2, gu=gu)
         return h, mlp, saved
 
     # ------------------------------------------------------------------ layer backward
@@ -133,6 +138,13 @@ class LayerwiseEngine:
         t = dout.shape[0]
         qw, kvw, d_head = cfg.query_width, cfg.key_value_width, cfg.head_dim
         b, s = ctx["batch"], ctx["seq"]
+        if "act" not in sv:
+            # kept activations: the memory-bound intermediates are cheaper to rebuild than to hold
+            sv = dict(sv)
+            sv["act"] = ew.swiglu_forward(sv["gu"])
+            sv["n2"] = ew.rmsnorm_forward(sv["h"], w["ln2"], cfg.rms_norm_eps)[0]
+            sv["n1"] = ew.rmsnorm_forward(sv["x"], w["ln1"], cfg.rms_norm_eps)[0]
+            self._count(3)
         # MLP branch
         dact = gemm(dout, w["down_w"], b_mn=True)
         self._wgrad(dout, sv["act"], g["down_w"], accumulate)
@@ -168,6 +180,28 @@ class LayerwiseEngine:
         self._count(12)
         return dx
 
+    # ------------------------------------------------------------------ activation policy
+    def _layers_to_keep(self, tokens: int) -> int:
+        """How many layers keep their activations instead of being recomputed in backward.
+
+        ``remat="full"`` recomputes every layer (the reference's ``nothing_saveable``), ``"none"``
+        keeps all, ``"auto"`` keeps as many as fit in the memory that is free right now, after a
+        reserve for the backward working set: on a 180 GB part an 8B model usually keeps all.
+        """
+        cfg, mode = self.cfg, self.options.remat
+        if mode == "full":
+            return 0
+        if mode == "none":
+            return cfg.num_hidden_layers
+        per_layer = tokens * 2 * (3 * cfg.hidden_size + 2 * cfg.query_width + 2 * cfg.key_value_width
+                                  + 2 * cfg.intermediate_size) + tokens * 12 * cfg.num_attention_heads
+        free, _ = torch.cuda.mem_get_info()
+        cached = torch.cuda.memory_reserved() - torch.cuda.memory_allocated()
+        working_set = tokens * 2 * (6 * cfg.intermediate_size + 8 * cfg.hidden_size) + (self.options.cut_chunk_rows
+                                                                                        * cfg.vocab_size * 2)
+        budget = free + cached - working_set - self.options.memory_reserve_bytes
+        return max(0, min(cfg.num_hidden_layers, int(budget // per_layer)))
+
     # ------------------------------------------------------------------ step context
     def _context(self, batch: dict[str, torch.Tensor]) -> dict:
         cfg = self.cfg
@@ -197,7 +231,7 @@ class LayerwiseEngine:
         branch = None
         for li in range(cfg.num_hidden_layers):
             unit = self.provider.acquire(f"layer.{li}", prefetch=f"layer.{li + 1}" if li + 1 < cfg.num_hidden_layers else "final")
-            resid, branch, _ = self._layer_forward(self._views(unit), resid, branch, ctx, li, save=False)
+            resid, branch, _ = self._layer_forward(self._views(unit), resid, branch, ctx, li, save=None)
             self.provider.release(f"layer.{li}")
         final = self.provider.acquire("final")
         y, _, _ = ew.rmsnorm_forward(resid, final.view("norm"), cfg.rms_norm_eps, residual=branch)
@@ -219,10 +253,17 @@ class LayerwiseEngine:
         prov.release("embed")
         branch = None
         inputs: list[tuple[torch.Tensor, torch.Tensor | None]] = []
+        kept: list[dict | None] = []
+        keep_layers = self._layers_to_keep(resid.shape[0])
+        self.kept_layers = keep_layers
         for li in range(nl):
             unit = prov.acquire(f"layer.{li}", prefetch=f"layer.{li + 1}" if li + 1 < nl else "final")
-            inputs.append((resid, branch))
-            resid, branch, _ = self._layer_forward(self._views(unit), resid, branch, ctx, li, save=False)
+            # the last layers are kept first: their activations are consumed soonest
+            keep = li >= nl - keep_layers
+            inputs.append(None if keep else (resid, branch))
+            resid, branch, sv = self._layer_forward(self._views(unit), resid, branch, ctx, li,
+                                                    save="keep" if keep else None)
+            kept.append(sv)
             prov.release(f"layer.{li}")
         # ---------------- head: final norm + cut cross-entropy ----------------
         final = prov.acquire("final", prefetch=f"layer.{nl - 1}")
@@ -246,10 +287,12 @@ class LayerwiseEngine:
             unit = prov.acquire(f"layer.{li}", prefetch=f"layer.{li - 1}" if li > 0 else "embed")
             w = self._views(unit)
             g = self._views(unit, prov.grad_buffer(f"layer.{li}"))
-            r_in, b_in = inputs.pop()
-            _, _, saved = self._layer_forward(w, r_in, b_in, ctx, li, save=True)
+            layer_in = inputs.pop()
+            saved = kept.pop()
+            if saved is None:
+                _, _, saved = self._layer_forward(w, layer_in[0], layer_in[1], ctx, li, save="all")
             dout = self._layer_backward(w, g, saved, dout, ctx, accumulate)
-            del saved
+            del saved, layer_in
             prov.release(f"layer.{li}")
             prov.grads_ready(f"layer.{li}", last)
         # ---------------- embedding ----------------
