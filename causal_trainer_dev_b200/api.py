@@ -34,6 +34,7 @@ class TrainerConfig:
     cut_chunk_rows: int = 4096
     init: str = "normal"               # "normal": N(0, initializer_range) on the device; "hf": ModelParams.init_random
     remat: str = "auto"                # "auto": keep activations that fit, recompute the rest; "full"; "none"
+    tp: int = 1                        # tensor-parallel degree; ranks are laid out (fsdp, tp) with tp fastest
 
 
 class Trainer:
@@ -45,7 +46,26 @@ class Trainer:
         self.rank = dist.get_rank() if dist.is_initialized() else 0
         self._bytes_h2d = 0
         self._bytes_d2h = 0
-        if self.world > 1 and self.cfg.fsdp:
+        self.data_rank, self.data_world = self.rank, self.world
+        if self.cfg.tp > 1:
+            from .parallel.fsdp import FsdpRuntime
+            from .parallel.runtime import RankLattice
+            from .parallel.tp import tp_local_config
+            from .training.tp_engine import TpLayerwiseEngine
+
+            if self.world % self.cfg.tp:
+                raise ValueError(f"tp={self.cfg.tp} must divide the number of ranks ({self.world})")
+            self.lattice = RankLattice((1, self.world // self.cfg.tp, 1, self.cfg.tp, 1), self.rank)
+            fsdp_group = self.lattice.group(("fsdp",))
+            tp_group = self.lattice.group(("tp",))
+            self.data_rank, self.data_world = self.lattice.coords()["fsdp"], self.world // self.cfg.tp
+            local = tp_local_config(model, self.cfg.tp)
+            self.runtime = FsdpRuntime(local, self.cfg, self.device, group=fsdp_group, full_cfg=model, tp_group=tp_group)
+            self.engine = TpLayerwiseEngine(model, tp_group, self.runtime,
+                                            EngineOptions(cut_chunk_rows=self.cfg.cut_chunk_rows, remat=self.cfg.remat),
+                                            fused=self.cfg.fused_collectives)
+            self.step_fn = self.runtime.make_step(self.engine)
+        elif self.world > 1 and self.cfg.fsdp:
             from .parallel.fsdp import FsdpRuntime
 
             self.runtime = FsdpRuntime(model, self.cfg, self.device)

@@ -64,8 +64,13 @@ def chunked_cross_entropy(hidden, head, targets, weights, token_budget: int = 40
     return total, weights.float().sum()
 
 
-def cut_ce_forward(hidden, head, targets, weights, grad_scale: float = 1.0):
-    """Returns (nll_sum, weight_sum, lse, coef); coef = weights * grad_scale for the backward."""
+def cut_ce_forward(hidden, head, targets, weights, grad_scale: float = 1.0, exchange=None):
+    """Returns (nll_sum, weight_sum, lse, coef); coef = weights * grad_scale for the backward.
+
+    With ``exchange`` (vocabulary-parallel head: ``head`` holds this rank's vocabulary rows and
+    ``targets`` are already relative to them, -1 elsewhere) the per-row statistics are combined
+    across the tensor-parallel ranks inside ``exchange.ce_exchange``.
+    """
     rows, d = hidden.shape
     vocab = head.shape[0]
     slabs = (vocab + SLAB - 1) // SLAB
@@ -76,15 +81,17 @@ def cut_ce_forward(hidden, head, targets, weights, grad_scale: float = 1.0):
     tgt = targets.to(torch.int32).contiguous()
     w = weights.to(torch.float32).contiguous()
     L = _lib.lib()
-    from .gemm import _FLAG_SOURCES, flag_source_of
+    from .gemm import _FLAG_SOURCES, _flag_args, _rotations, flag_source_of
 
     hit = flag_source_of(head) if _FLAG_SOURCES else None
-    fl, chunk, base, epoch = (None, 0, 0, 0) if hit is None else (hit[0].flags, hit[0].chunk_elems, hit[1], hit[0].epoch)
+    hit_a = flag_source_of(hidden) if _FLAG_SOURCES else None
+    _, m_rotate = _rotations(None, hit_a, hidden, head, False, False, rows, vocab)
     code = L.ctb_ce_stats(_lib.ptr(hidden), _lib.ptr(head), rows, vocab, d, ctypes.c_long(hidden.stride(0)),
                           ctypes.c_long(head.stride(0)), _lib.ptr(tgt), _lib.ptr(pmax), _lib.ptr(psum),
-                          _lib.ptr(tlogit), _lib.ptr(fl), ctypes.c_long(chunk), ctypes.c_long(base),
-                          ctypes.c_uint(epoch), _lib.stream_ptr())
+                          _lib.ptr(tlogit), *_flag_args(hit), *_flag_args(hit_a), m_rotate, _lib.stream_ptr())
     _lib.check(code, "ctb_ce_stats")
+    if exchange is not None:
+        return exchange.ce_exchange(pmax, psum, slabs, tlogit, w, grad_scale)
     lse = torch.empty(rows, dtype=torch.float32, device=dev)
     coef = torch.empty(rows, dtype=torch.float32, device=dev)
     nblk = (rows + 255) // 256
@@ -98,17 +105,25 @@ def cut_ce_forward(hidden, head, targets, weights, grad_scale: float = 1.0):
 
 
 def cut_ce_backward(hidden, head, targets, lse, coef, *, chunk_rows: int = 4096, need_dhead: bool = True,
-                    dhead_out: torch.Tensor | None = None, dhead_accumulate: bool = False):
-    """Returns (dhidden [rows,d] bf16, dhead [vocab,d] or None)."""
+                    dhead_out: torch.Tensor | None = None, dhead_accumulate: bool = False, push=None):
+    """Returns (dhidden [rows,d] bf16, dhead [vocab,d] or None).
+
+    With ``push`` (vocabulary-parallel head) the partial ``dhidden`` tiles are reduce-scattered
+    into the owners' receive buffers by the GEMM epilogue and ``dhidden`` is returned as None.
+    """
     rows, d = hidden.shape
     vocab = head.shape[0]
     dev = hidden.device
     tgt = targets.to(torch.int32).contiguous()
-    dhidden = torch.empty_like(hidden)
+    dhidden = torch.empty_like(hidden) if push is None else None
     dhead = None
     if need_dhead:
         dhead = dhead_out if dhead_out is not None else torch.empty((vocab, d), dtype=torch.bfloat16, device=dev)
     chunk_rows = min(chunk_rows, rows)
+    if push is not None:
+        if rows % 128:
+            raise ValueError("the push epilogue needs a multiple of 128 rows")
+        chunk_rows = max(128, chunk_rows // 128 * 128)
     slab = torch.empty((chunk_rows, vocab), dtype=torch.bfloat16, device=dev)
     L = _lib.lib()
     first = True
@@ -121,7 +136,13 @@ def cut_ce_backward(hidden, head, targets, lse, coef, *, chunk_rows: int = 4096,
                                 _lib.ptr(tgt[start:start + n]), _lib.ptr(lse[start:start + n]),
                                 _lib.ptr(coef[start:start + n]), _lib.stream_ptr())
         _lib.check(code, "ctb_ce_dlogits")
-        gemm(g, head, b_mn=True, out=dhidden[start:start + n])              # dH = G @ W
+        if push is None:
+            gemm(g, head, b_mn=True, out=dhidden[start:start + n])              # dH = G @ W
+        else:
+            from .gemm import gemm_push
+
+            gemm_push(g, head, push, b_mn=True, row_offset=start,
+                      tiles_per_dest=(push.rows_per_rank // 128) * (-(-d // 256)))
         if need_dhead:
             gemm(g, h, a_mn=True, b_mn=True, out=dhead, accumulate=(dhead_accumulate or not first))  # dW += G^T H
         first = False

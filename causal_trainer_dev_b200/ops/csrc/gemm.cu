@@ -60,7 +60,8 @@ struct TileCoord {
 // Tiles are walked in bands of GROUP_M row tiles; inside a band the column tile advances
 // slowly so the B tile stays hot in L2.  `n_rotate` shifts the column order so that a rank
 // starts on the weight rows it already owns while the all-gather pull brings the rest.
-__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int n_rotate) {
+// `m_rotate` does the same for row tiles when the A operand is being gathered.
+__device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int n_rotate, int m_rotate) {
   const int per_group = GROUP_M * num_n;
   const int group = tile / per_group;
   const int first_m = group * GROUP_M;
@@ -68,8 +69,10 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
   const int local = tile - group * per_group;
   int n = local / rows + n_rotate;
   if (n >= num_n) n -= num_n;
+  int m = first_m + local % rows + m_rotate;
+  if (m >= num_m) m -= num_m;
   TileCoord c;
-  c.m0 = (first_m + local % rows) * BM;
+  c.m0 = m * BM;
   c.n0 = n * BN;
   return c;
 }
@@ -129,10 +132,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint32_t armed = 0;      // bit s set: full[s] was armed by this thread at least once
     uint32_t armed_par = 0;  // bit s: parity of the phase last armed on full[s]
     bool ok = true;
-    bool flags_all_seen = false;
+    bool b_all_seen = false, a_all_seen = false;
+    // Acquires every chunk flag covering elements [e0, e1) of a gathered buffer (warp-wide).
+    auto acquire_range = [&](const unsigned* flags, long chunk, long e0, long e1, unsigned epoch) -> bool {
+      const int first = static_cast<int>(e0 / chunk);
+      const int last = static_cast<int>((e1 - 1) / chunk);
+      bool mine = true;
+      for (int f = first + lane; mine && f <= last; f += 32) {
+        const long long t0 = clock64();
+        while (true) {
+          unsigned v;
+          asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(flags + f) : "memory");
+          if (v >= epoch) break;
+          if (*abort_flag || clock64() - t0 > args.spin_budget) {
+            *abort_flag = 1u;
+            report_failure(st, SITE_PRODUCER_FLAG, static_cast<unsigned>(f), epoch);
+            mine = false;
+            break;
+          }
+          __nanosleep(64);
+        }
+      }
+      return __all_sync(0xffffffffu, mine);
+    };
     for (int tile = blockIdx.x; ok && tile < total; tile += gridDim.x) {
-      const TileCoord tc = tile_coord(tile, num_m, num_n, args.n_rotate);
-      if (args.b_flags != nullptr && !flags_all_seen) {
+      const TileCoord tc = tile_coord(tile, num_m, num_n, args.n_rotate, args.m_rotate);
+      if (args.b_flags != nullptr && !b_all_seen) {
         // The elements of B this tile reads must have landed in this GPU's memory.  A
         // K-major B tile is rows [n0, n0+BN) of the weight; an MN-major B (dgrad) strides
         // over the whole matrix, so it waits for all of it once.
@@ -140,33 +165,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         if (B_MN || args.b_wait_all) {
           e0 = args.b_flag_base;
           e1 = args.b_flag_base + static_cast<long>(B_MN ? args.K : args.N) * args.ldb;
-          flags_all_seen = true;
+          b_all_seen = true;
         } else {
           const int nend = min(tc.n0 + BN, args.N);
           e0 = args.b_flag_base + static_cast<long>(tc.n0) * args.ldb;
           e1 = args.b_flag_base + static_cast<long>(nend - 1) * args.ldb + args.K;
         }
-        const int first = static_cast<int>(e0 / args.b_flag_chunk);
-        const int last = static_cast<int>((e1 - 1) / args.b_flag_chunk);
-        bool mine = true;
-        for (int f = first + lane; mine && f <= last; f += 32) {
-          const long long t0 = clock64();
-          while (true) {
-            unsigned v;
-            asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(args.b_flags + f) : "memory");
-            if (v >= args.b_flag_epoch) break;
-            if (*abort_flag || clock64() - t0 > args.spin_budget) {
-              *abort_flag = 1u;
-              report_failure(st, SITE_PRODUCER_FLAG, static_cast<unsigned>(f), args.b_flag_epoch);
-              mine = false;
-              break;
-            }
-            __nanosleep(64);
-          }
-        }
-        ok = __all_sync(0xffffffffu, mine);
+        ok = acquire_range(args.b_flags, args.b_flag_chunk, e0, e1, args.b_flag_epoch);
         if (!ok) break;
         fence_proxy_async_all();  // generic-proxy writes of the pull CTAs -> async-proxy reads below
+      }
+      if (args.a_flags != nullptr && !a_all_seen) {
+        // Same for a gathered A operand (tensor-parallel all-gather of activation rows): a
+        // K-major A tile is rows [m0, m0+BM); an MN-major A waits for the whole matrix once.
+        long e0, e1;
+        if (A_MN) {
+          e0 = args.a_flag_base;
+          e1 = args.a_flag_base + static_cast<long>(args.K) * args.lda;
+          a_all_seen = true;
+        } else {
+          const int mend = min(tc.m0 + BM, args.M);
+          e0 = args.a_flag_base + static_cast<long>(tc.m0) * args.lda;
+          e1 = args.a_flag_base + static_cast<long>(mend - 1) * args.lda + args.K;
+        }
+        ok = acquire_range(args.a_flags, args.a_flag_chunk, e0, e1, args.a_flag_epoch);
+        if (!ok) break;
+        fence_proxy_async_all();
       }
       if (lane == 0) {
         for (int kb = 0; kb < num_k; ++kb) {
@@ -259,7 +283,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     uint32_t acc = 0, acc_phase = 0, buf_idx = 0;
     uint8_t* epi = smem + OFF_EPI;
     for (int tile = blockIdx.x; tile < total; tile += gridDim.x) {
-      const TileCoord tc = tile_coord(tile, num_m, num_n, args.n_rotate);
+      const TileCoord tc = tile_coord(tile, num_m, num_n, args.n_rotate, args.m_rotate);
       // The four epilogue warps decide together: a thread that gave up must not leave
       // the others waiting at the staging barriers below.
       const bool got = mbar_wait(&tfull[acc], acc_phase, abort_flag, st, SITE_EPI_TFULL, args.spin_budget);
@@ -396,14 +420,49 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             v.w = pack_bf16(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
             *reinterpret_cast<uint4*>(buf + sw128_offset(row, 4 + j)) = v;
           }
-          fence_proxy_async_smem();
-          named_bar_sync(1, 128);
-          if (etid == 0) {
-            if (args.accumulate) tma_reduce_add_2d(&map_c, buf, col0, tc.m0);
-            else tma_store_2d(&map_c, buf, col0, tc.m0);
-            tma_commit_group();
+          if (EPI == EPI_STORE && args.push.enabled) {
+            // reduce-scatter by push: 128 threads copy the staged 128 x 128 B block into the
+            // owner's receive buffer with 16-byte stores (peer memory: plain st.global only)
+            named_bar_sync(1, 128);
+            const int grow0 = args.push.row_offset + tc.m0;
+            const int dest = grow0 / args.push.rows_per_rank;
+            const long drow0 = static_cast<long>(args.push.src_rank) * args.push.rows_per_rank +
+                               (grow0 - dest * args.push.rows_per_rank);
+            __nv_bfloat16* base = args.push.dest[dest];
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int idx = i * 128 + etid;
+              const int r = idx >> 3, j = idx & 7;
+              if (tc.m0 + r < args.M && col0 + j * 8 < args.N) {
+                const uint4 v = *reinterpret_cast<const uint4*>(buf + sw128_offset(r, j));
+                *reinterpret_cast<uint4*>(base + (drow0 + r) * args.push.ld + col0 + j * 8) = v;
+              }
+            }
+          } else {
+            fence_proxy_async_smem();
+            named_bar_sync(1, 128);
+            if (etid == 0) {
+              if (args.accumulate) tma_reduce_add_2d(&map_c, buf, col0, tc.m0);
+              else tma_store_2d(&map_c, buf, col0, tc.m0);
+              tma_commit_group();
+            }
           }
           ++buf_idx;
+        }
+        if (EPI == EPI_STORE && args.push.enabled) {
+          // this tile is on its way: count it, and publish the flag with the last one
+          __threadfence_system();
+          named_bar_sync(1, 128);
+          if (etid == 0) {
+            const int dest = (args.push.row_offset + tc.m0) / args.push.rows_per_rank;
+            const unsigned done = atomicAdd(args.push.counters + dest, 1u) + 1u;
+            if (done == static_cast<unsigned>(args.push.tiles_per_dest)) {
+              args.push.counters[dest] = 0u;
+              __threadfence_system();
+              asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(args.push.flag[dest]), "r"(args.push.epoch)
+                           : "memory");
+            }
+          }
         }
       }
       tc_fence_before();
@@ -448,7 +507,7 @@ int run_gemm(const GemmCall& c) {
   using namespace gemm;
   if (c.M <= 0 || c.N <= 0 || c.K <= 0) return fail("gemm: M, N, K must be positive");
   if ((c.lda % 8) || (c.ldb % 8)) return fail("gemm: lda and ldb must be multiples of 8 elements (16 bytes)");
-  const bool needs_c = (c.epi != EPI_CE_STATS);
+  const bool needs_c = (c.epi != EPI_CE_STATS) && !c.push.enabled;
   if (needs_c && (c.ldc % (c.out_f32 ? 4 : 8))) return fail("gemm: ldc must be a multiple of 16 bytes");
   const CUtensorMap* ma = c.a_mn ? get_tensor_map_2d(c.A, Elt::BF16, c.M, c.K, c.lda, 64, 64, true)
                                  : get_tensor_map_2d(c.A, Elt::BF16, c.K, c.M, c.lda, 64, BM, true);
@@ -481,13 +540,26 @@ int run_gemm(const GemmCall& c) {
   {
     const int num_n = (c.N + gemm::BN - 1) / gemm::BN;
     a.n_rotate = (c.n_rotate > 0 && c.n_rotate < num_n) ? c.n_rotate : 0;
+    const int num_m = (c.M + gemm::BM - 1) / gemm::BM;
+    a.m_rotate = (c.m_rotate > 0 && c.m_rotate < num_m) ? c.m_rotate : 0;
   }
+  a.a_flags = c.a_flags;
+  a.a_flag_chunk = c.a_flag_chunk > 0 ? c.a_flag_chunk : 1;
+  a.a_flag_base = c.a_flag_base;
+  a.a_flag_epoch = c.a_flag_epoch;
+  a.lda = c.lda;
   a.ce_targets = c.ce_targets;
   a.ce_max = c.ce_max;
   a.ce_sum = c.ce_sum;
   a.ce_target_logit = c.ce_target_logit;
   a.ce_lse = c.ce_lse;
   a.ce_coef = c.ce_coef;
+  a.push = c.push;
+  if (c.push.enabled) {
+    if (c.out_f32 || c.accumulate || c.epi != EPI_STORE) return fail("gemm: the push epilogue writes plain bf16 tiles");
+    if (c.push.rows_per_rank % BM || c.push.row_offset % BM || c.push.ld % 8 || c.N % 8)
+      return fail("gemm: push needs 128-row aligned rank slabs and 16-byte aligned rows");
+  }
   const int tiles = ((c.M + BM - 1) / BM) * ((c.N + BN - 1) / BN);
   int grid = std::min(tiles, c.max_ctas > 0 ? c.max_ctas : sm_count());
   cudaStream_t s = static_cast<cudaStream_t>(c.stream);
@@ -525,13 +597,41 @@ CTB_API int ctb_gemm(const void* A, const void* B, void* C, int M, int N, int K,
 CTB_API int ctb_gemm_flagged(const void* A, const void* B, void* C, int M, int N, int K, long lda, long ldb, long ldc,
                              int a_mn, int b_mn, int out_f32, int accumulate, float alpha, const void* bias,
                              const unsigned* flags, long flag_chunk, long flag_base, unsigned epoch, int wait_all,
-                             int n_rotate, long long spin_budget, int max_ctas, void* stream) {
+                             int n_rotate, const unsigned* a_flags, long a_flag_chunk, long a_flag_base,
+                             unsigned a_epoch, int m_rotate, long long spin_budget, int max_ctas, void* stream) {
   ctb::GemmCall c{};
   c.A = A; c.B = B; c.C = C; c.M = M; c.N = N; c.K = K; c.lda = lda; c.ldb = ldb; c.ldc = ldc;
   c.a_mn = a_mn; c.b_mn = b_mn; c.out_f32 = out_f32; c.accumulate = accumulate; c.alpha = alpha; c.bias = bias;
   c.epi = ctb::EPI_STORE; c.max_ctas = max_ctas; c.stream = stream;
   c.b_flags = flags; c.b_flag_chunk = flag_chunk; c.b_flag_base = flag_base; c.b_flag_epoch = epoch;
   c.b_wait_all = wait_all; c.spin_budget = spin_budget; c.n_rotate = n_rotate;
+  c.a_flags = a_flags; c.a_flag_chunk = a_flag_chunk; c.a_flag_base = a_flag_base; c.a_flag_epoch = a_epoch;
+  c.m_rotate = m_rotate;
+  return ctb::run_gemm(c);
+}
+
+// Row-parallel projection with the reduce-scatter fused into the epilogue (see GemmPush).
+// `dest_ptrs[p]` is rank p's receive buffer, `flag_ptrs[p]` the address of this rank's flag
+// on rank p.  A may be a gathered buffer (a_flags) exactly as in ctb_gemm_flagged.
+CTB_API int ctb_gemm_push(const void* A, const void* B, int M, int N, int K, long lda, long ldb, int a_mn, int b_mn,
+                          float alpha, void* const* dest_ptrs, unsigned* const* flag_ptrs, int world,
+                          unsigned* counters, int rows_per_rank, int row_offset, int src_rank, int tiles_per_dest,
+                          long ld, unsigned epoch, const unsigned* b_flags, long b_flag_chunk, long b_flag_base,
+                          unsigned b_epoch, int b_wait_all, int n_rotate, int m_rotate, long long spin_budget,
+                          int max_ctas, void* stream) {
+  if (world > ctb::GEMM_MAX_RANKS) return ctb::fail("gemm_push: too many ranks");
+  ctb::GemmCall c{};
+  c.A = A; c.B = B; c.C = nullptr; c.M = M; c.N = N; c.K = K; c.lda = lda; c.ldb = ldb; c.ldc = ld;
+  c.a_mn = a_mn; c.b_mn = b_mn; c.alpha = alpha; c.epi = ctb::EPI_STORE; c.max_ctas = max_ctas; c.stream = stream;
+  c.b_flags = b_flags; c.b_flag_chunk = b_flag_chunk; c.b_flag_base = b_flag_base; c.b_flag_epoch = b_epoch;
+  c.b_wait_all = b_wait_all; c.n_rotate = n_rotate; c.m_rotate = m_rotate; c.spin_budget = spin_budget;
+  for (int i = 0; i < world; ++i) {
+    c.push.dest[i] = static_cast<__nv_bfloat16*>(dest_ptrs[i]);
+    c.push.flag[i] = flag_ptrs[i];
+  }
+  c.push.counters = counters; c.push.rows_per_rank = rows_per_rank; c.push.row_offset = row_offset;
+  c.push.src_rank = src_rank; c.push.tiles_per_dest = tiles_per_dest; c.push.ld = ld; c.push.epoch = epoch;
+  c.push.enabled = 1;
   return ctb::run_gemm(c);
 }
 
@@ -540,9 +640,12 @@ CTB_API int ctb_gemm_flagged(const void* A, const void* B, void* C, int M, int N
 // holds the row's target (rows with target < 0 are never written).
 CTB_API int ctb_ce_stats(const void* hidden, const void* head, int rows, int vocab, int d, long ldh, long ldw,
                          const int* targets, float* pmax, float* psum, float* target_logit, const unsigned* flags,
-                         long flag_chunk, long flag_base, unsigned epoch, void* stream) {
+                         long flag_chunk, long flag_base, unsigned epoch, const unsigned* a_flags, long a_flag_chunk,
+                         long a_flag_base, unsigned a_epoch, int m_rotate, void* stream) {
   ctb::GemmCall c{};
   c.b_flags = flags; c.b_flag_chunk = flag_chunk; c.b_flag_base = flag_base; c.b_flag_epoch = epoch;
+  c.a_flags = a_flags; c.a_flag_chunk = a_flag_chunk; c.a_flag_base = a_flag_base; c.a_flag_epoch = a_epoch;
+  c.m_rotate = m_rotate;
   c.A = hidden; c.B = head; c.M = rows; c.N = vocab; c.K = d; c.lda = ldh; c.ldb = ldw;
   c.epi = ctb::EPI_CE_STATS; c.stream = stream;
   c.ce_targets = targets; c.ce_max = pmax; c.ce_sum = psum; c.ce_target_logit = target_logit;

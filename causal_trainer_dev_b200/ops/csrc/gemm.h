@@ -10,6 +10,25 @@ enum GemmEpilogue : int {
   EPI_CE_DLOGITS = 2,  // C = (exp(acc - lse[row]) - onehot(target[row])) * coef[row], bf16
 };
 
+constexpr int GEMM_MAX_RANKS = 16;
+
+// Reduce-scatter by push (tensor-parallel row-parallel projections): instead of storing a
+// partial-sum tile into local memory, the epilogue writes it into the receive buffer of the
+// rank that owns those rows, `dest[p] + ((src_rank * rows_per_rank + local_row) * ld + col)`,
+// and the CTA that completes the last tile bound for rank p publishes `epoch` in `flag[p]`.
+struct GemmPush {
+  __nv_bfloat16* dest[GEMM_MAX_RANKS];   // every rank's receive buffer [world][rows_per_rank][ld]
+  unsigned* flag[GEMM_MAX_RANKS];        // &pads_of_rank_p[base + src_rank]
+  unsigned* counters;                    // local, one per destination rank, self-resetting
+  int rows_per_rank;
+  int row_offset;                        // global row of row 0 of this GEMM (chunked callers)
+  int src_rank;
+  int tiles_per_dest;                    // tiles bound for one rank, summed over all launches of the op
+  long ld;
+  unsigned epoch;
+  int enabled;
+};
+
 // Device-side argument block (passed by value).
 struct GemmArgs {
   int M, N, K;
@@ -25,13 +44,20 @@ struct GemmArgs {
   unsigned b_flag_epoch;
   int b_wait_all;
   int n_rotate;
+  int m_rotate;
   long ldb;
+  long lda;
+  const unsigned* a_flags;
+  long a_flag_chunk;
+  long a_flag_base;
+  unsigned a_flag_epoch;
   const int* ce_targets;
   float* ce_max;
   float* ce_sum;
   float* ce_target_logit;
   const float* ce_lse;
   const float* ce_coef;
+  GemmPush push;
 };
 
 // Host-side call description.
@@ -54,6 +80,11 @@ struct GemmCall {
   unsigned b_flag_epoch = 0;
   int b_wait_all = 0;
   int n_rotate = 0;
+  int m_rotate = 0;
+  const unsigned* a_flags = nullptr;
+  long a_flag_chunk = 0;
+  long a_flag_base = 0;
+  unsigned a_flag_epoch = 0;
   long long spin_budget = 0;
   const int* ce_targets = nullptr;
   float* ce_max = nullptr;
@@ -61,6 +92,7 @@ struct GemmCall {
   float* ce_target_logit = nullptr;
   const float* ce_lse = nullptr;
   const float* ce_coef = nullptr;
+  GemmPush push{};
 };
 
 int run_gemm(const GemmCall& call);

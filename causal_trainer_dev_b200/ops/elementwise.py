@@ -32,10 +32,10 @@ def rmsnorm_reference(x: torch.Tensor, w: torch.Tensor, eps: float) -> torch.Ten
     return (normed * w.to(x.dtype)).to(x.dtype)
 
 
-def rmsnorm_forward(x, w, eps, residual=None):
-    """Returns (y, rstd, h) where h = x + residual (or x itself)."""
+def rmsnorm_forward(x, w, eps, residual=None, out=None):
+    """Returns (y, rstd, h) where h = x + residual (or x itself); ``out`` receives y when given."""
     rows, d = x.shape
-    y = torch.empty_like(x)
+    y = torch.empty_like(x) if out is None else out
     rstd = torch.empty(rows, dtype=torch.float32, device=x.device)
     h = torch.empty_like(x) if residual is not None else x
     code = _lib.lib().ctb_rmsnorm_fwd(
@@ -49,7 +49,7 @@ def rmsnorm_forward(x, w, eps, residual=None):
 _norm_scratch: dict[tuple[int, int], torch.Tensor] = {}
 
 
-def rmsnorm_backward(dy, x, w, rstd, dres=None, dw_out=None, dw_accumulate=False):
+def rmsnorm_backward(dy, x, w, rstd, dres=None, dw_out=None, dw_accumulate=False, dx_out=None):
     """Returns (dx, dw).  ``dx`` includes ``dres`` when given (the residual branch gradient)."""
     rows, d = x.shape
     L = _lib.lib()
@@ -59,7 +59,7 @@ def rmsnorm_backward(dy, x, w, rstd, dres=None, dw_out=None, dw_accumulate=False
     if scratch is None:
         scratch = torch.empty(parts * d, dtype=torch.float32, device=x.device)
         _norm_scratch[key] = scratch
-    dx = torch.empty_like(x)
+    dx = torch.empty_like(x) if dx_out is None else dx_out
     if dw_out is None:
         dw_out = torch.empty(d, dtype=torch.float32, device=x.device)
         dw_accumulate = False
@@ -151,6 +151,26 @@ def embedding_gather(ids: torch.Tensor, table: torch.Tensor) -> torch.Tensor:
                                            table.shape[1], table.shape[0], _lib.stream_ptr())
     _lib.check(code, "ctb_embedding_gather")
     return out
+
+
+def embedding_backward(ids: torch.Tensor, dout: torch.Tensor, grad: torch.Tensor, pad_id: int, vocab_lo: int = 0) -> None:
+    """``grad[id - vocab_lo] += sum of dout rows whose token is id`` (deterministic; pad row skipped).
+
+    ``grad`` is the ``[rows, d]`` gradient table of the embedding rows ``[vocab_lo, vocab_lo + rows)``
+    (bf16 or fp32); tokens outside that range belong to another vocabulary shard and are ignored.
+    """
+    flat = ids.reshape(-1).to(torch.int32)
+    order = torch.sort(flat, stable=True)
+    sorted_ids = order.values.contiguous()
+    perm = order.indices.to(torch.int32).contiguous()
+    change = torch.ones_like(sorted_ids, dtype=torch.bool)
+    change[1:] = sorted_ids[1:] != sorted_ids[:-1]
+    starts = torch.nonzero(change).reshape(-1).to(torch.int32).contiguous()
+    code = _lib.lib().ctb_embedding_backward(_lib.ptr(sorted_ids), _lib.ptr(perm), _lib.ptr(starts), starts.numel(),
+                                             _l(flat.numel()), _lib.ptr(dout), _lib.ptr(grad),
+                                             int(grad.dtype == torch.float32), dout.shape[1], vocab_lo, grad.shape[0],
+                                             pad_id, _lib.stream_ptr())
+    _lib.check(code, "ctb_embedding_backward")
 
 
 def attention_delta(o: torch.Tensor, dout: torch.Tensor) -> torch.Tensor:

@@ -56,6 +56,36 @@ def flag_source_of(t: torch.Tensor) -> tuple[FlagSource, int] | None:
     return None
 
 
+def _flag_args(hit):
+    """(flags, chunk, base, epoch) of one operand for the C entry points (nulls when unflagged)."""
+    if hit is None:
+        return None, ctypes.c_long(0), ctypes.c_long(0), ctypes.c_uint(0)
+    src, base = hit
+    return _lib.ptr(src.flags), ctypes.c_long(src.chunk_elems), ctypes.c_long(base), ctypes.c_uint(src.epoch)
+
+
+def _rotations(hit, hit_a, a, b, a_mn, b_mn, m, n) -> tuple[int, int]:
+    """Tile-walk rotations that start a GEMM on the part of a gathered operand this rank owns.
+
+    The pull delivers the rest in increasing (wrapping) rank order, which is the order the
+    rotated walk needs it.
+    """
+    n_rotate = m_rotate = 0
+    if hit is not None and not b_mn:
+        src, base = hit
+        if src.own_stop > src.own_start:
+            first_own_row = max(0, -(-(src.own_start - base) // b.stride(0)))
+            if first_own_row < n:
+                n_rotate = -(-first_own_row // 256)
+    if hit_a is not None and not a_mn:
+        src, base = hit_a
+        if src.own_stop > src.own_start:
+            first_own_row = max(0, -(-(src.own_start - base) // a.stride(0)))
+            if first_own_row < m:
+                m_rotate = -(-first_own_row // 128)
+    return n_rotate, m_rotate
+
+
 def _check_operand(t: torch.Tensor, name: str) -> None:
     if t.dtype != torch.bfloat16 or t.dim() != 2 or t.stride(1) != 1 or not t.is_cuda:
         raise ValueError(f"{name} must be a 2-D bf16 CUDA tensor with unit inner stride")
@@ -89,21 +119,17 @@ def gemm(
     if bias is not None and (bias.dtype != torch.bfloat16 or bias.numel() != n):
         raise ValueError("bias must be bf16 of length N")
     hit = flag_source_of(b) if _FLAG_SOURCES else None
-    if hit is not None:
-        src, base = hit
-        n_rotate = 0
-        if not b_mn and src.own_stop > src.own_start:
-            # start on the weight rows this rank already owns; the pull delivers the rest in
-            # increasing (wrapping) rank order, which is the order the rotated walk needs them
-            first_own_row = max(0, -(-(src.own_start - base) // b.stride(0)))
-            if first_own_row < n:
-                n_rotate = -(-first_own_row // 256)
+    hit_a = flag_source_of(a) if _FLAG_SOURCES else None
+    if hit is not None or hit_a is not None:
+        n_rotate, m_rotate = _rotations(hit, hit_a, a, b, a_mn, b_mn, m, n)
+        bf = _flag_args(hit)
+        af = _flag_args(hit_a)
+        budget = max(hit[0].spin_budget if hit else 0, hit_a[0].spin_budget if hit_a else 0)
         code = _lib.lib().ctb_gemm_flagged(
             _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), m, n, k,
             ctypes.c_long(a.stride(0)), ctypes.c_long(b.stride(0)), ctypes.c_long(out.stride(0)),
             int(a_mn), int(b_mn), int(out.dtype == torch.float32), int(accumulate), ctypes.c_float(alpha),
-            _lib.ptr(bias), _lib.ptr(src.flags), ctypes.c_long(src.chunk_elems), ctypes.c_long(base),
-            ctypes.c_uint(src.epoch), 0, n_rotate, ctypes.c_longlong(src.spin_budget), max_ctas, _lib.stream_ptr(),
+            _lib.ptr(bias), *bf, 0, n_rotate, *af, m_rotate, ctypes.c_longlong(budget), max_ctas, _lib.stream_ptr(),
         )
         _lib.check(code, "ctb_gemm_flagged")
         return out
@@ -115,6 +141,40 @@ def gemm(
     )
     _lib.check(code, "ctb_gemm")
     return out
+
+
+def gemm_push(a: torch.Tensor, b: torch.Tensor, push, *, b_mn: bool = False, row_offset: int = 0,
+              tiles_per_dest: int | None = None, alpha: float = 1.0, max_ctas: int = 0) -> None:
+    """``A @ B^T`` whose bf16 partial-sum tiles go straight into the receive buffers of the ranks
+    that own the rows (reduce-scatter by push, see ``GemmPush`` in ``csrc/gemm.h``).
+
+    ``push`` describes the destination: ``dest_ptrs``/``flag_ptrs`` (ctypes arrays, one entry per
+    rank), ``world``, ``counters`` (int32 tensor), ``rows_per_rank``, ``src_rank``, ``ld``,
+    ``epoch`` and ``spin_budget``.
+    """
+    _check_operand(a, "a")
+    _check_operand(b, "b")
+    m, k = a.shape
+    n, kb = (b.shape[1], b.shape[0]) if b_mn else (b.shape[0], b.shape[1])
+    if k != kb:
+        raise ValueError(f"inner dimensions differ: {k} vs {kb}")
+    hit = flag_source_of(b) if _FLAG_SOURCES else None
+    n_rotate, _ = _rotations(hit, None, a, b, False, b_mn, m, n)
+    # every rank starts on the rows of its right-hand neighbour and finishes on its own, so the
+    # receivers' inbound links are used evenly and nobody waits for a straggling last slab
+    num_m = -(-m // 128)
+    first = ((push.src_rank + 1) % push.world) * push.rows_per_rank - row_offset
+    m_rotate = (first // 128) % num_m if 0 <= first < m else 0
+    if tiles_per_dest is None:
+        tiles_per_dest = (push.rows_per_rank // 128) * (-(-n // 256))
+    code = _lib.lib().ctb_gemm_push(
+        _lib.ptr(a), _lib.ptr(b), m, n, k, ctypes.c_long(a.stride(0)), ctypes.c_long(b.stride(0)), 0, int(b_mn),
+        ctypes.c_float(alpha), push.dest_ptrs, push.flag_ptrs, push.world, _lib.ptr(push.counters),
+        push.rows_per_rank, row_offset, push.src_rank, tiles_per_dest, ctypes.c_long(push.ld),
+        ctypes.c_uint(push.epoch), *_flag_args(hit), 0, n_rotate, m_rotate, ctypes.c_longlong(push.spin_budget),
+        max_ctas, _lib.stream_ptr(),
+    )
+    _lib.check(code, "ctb_gemm_push")
 
 
 def linear_forward(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:

@@ -78,11 +78,16 @@ class _Gathered:
 class FsdpRuntime:
     """Weight provider (see ``training.engine``) plus the sharded optimizer step."""
 
-    def __init__(self, cfg: ModelConfig, tcfg, device: torch.device, group=None):
+    def __init__(self, cfg: ModelConfig, tcfg, device: torch.device, group=None, full_cfg: ModelConfig | None = None,
+                 tp_group=None):
+        """``cfg`` describes what this rank stores: the whole model, or (with ``tp_group``) one
+        tensor-parallel slice of ``full_cfg`` (see ``parallel.tp.tp_local_config``)."""
         _lib.require_gpu_lib()
-        import torch.distributed._symmetric_memory as symm_mem
-
         self.cfg, self.tcfg, self.device = cfg, tcfg, device
+        self.full_cfg = full_cfg if full_cfg is not None else cfg
+        self.tp_group = tp_group
+        self.tp_world = dist.get_world_size(tp_group) if tp_group is not None else 1
+        self.tp_rank = dist.get_rank(tp_group) if tp_group is not None else 0
         self.group = group if group is not None else dist.group.WORLD
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
@@ -110,25 +115,37 @@ class FsdpRuntime:
         self.order = list(self.units)
 
         # ---- symmetric memory: parameter shards, gradient staging, signal pads ----
-        gname = self.group.group_name
-        try:
-            symm_mem.enable_symm_mem_for_group(gname)
-        except Exception:  # newer torch enables groups lazily
-            pass
-        self.param_arena = symm_mem.empty(self.arena_elems, dtype=torch.bfloat16, device=device)
-        self.h_params = symm_mem.rendezvous(self.param_arena, gname)
-        self.staging = symm_mem.empty(N_SLOTS * self.max_padded, dtype=torch.bfloat16, device=device)
-        self.h_staging = symm_mem.rendezvous(self.staging, gname)
-        self.pads = symm_mem.empty(2 * N_SLOTS * self.world + 64, dtype=torch.int32, device=device)
-        self.pads.zero_()
-        self.h_pads = symm_mem.rendezvous(self.pads, gname)
-        self.param_arena.zero_()
-        self.staging.zero_()
-        torch.cuda.synchronize(device)
-        dist.barrier(self.group)
-        self.param_ptrs = [int(p) for p in self.h_params.buffer_ptrs]
-        self.staging_ptrs = [int(p) for p in self.h_staging.buffer_ptrs]
-        self.pad_ptrs = [int(p) for p in self.h_pads.buffer_ptrs]
+        n_pads = 2 * N_SLOTS * self.world + 64
+        if self.world > 1:
+            import torch.distributed._symmetric_memory as symm_mem
+
+            gname = self.group.group_name
+            try:
+                symm_mem.enable_symm_mem_for_group(gname)
+            except Exception:  # newer torch enables groups lazily
+                pass
+            self.param_arena = symm_mem.empty(self.arena_elems, dtype=torch.bfloat16, device=device)
+            self.h_params = symm_mem.rendezvous(self.param_arena, gname)
+            self.staging = symm_mem.empty(N_SLOTS * self.max_padded, dtype=torch.bfloat16, device=device)
+            self.h_staging = symm_mem.rendezvous(self.staging, gname)
+            self.pads = symm_mem.empty(n_pads, dtype=torch.int32, device=device)
+            self.pads.zero_()
+            self.h_pads = symm_mem.rendezvous(self.pads, gname)
+            self.param_arena.zero_()
+            self.staging.zero_()
+            torch.cuda.synchronize(device)
+            dist.barrier(self.group)
+            self.param_ptrs = [int(p) for p in self.h_params.buffer_ptrs]
+            self.staging_ptrs = [int(p) for p in self.h_staging.buffer_ptrs]
+            self.pad_ptrs = [int(p) for p in self.h_pads.buffer_ptrs]
+        else:
+            # a group of one (pure tensor parallelism): the same kernels run on ordinary memory
+            self.param_arena = torch.zeros(self.arena_elems, dtype=torch.bfloat16, device=device)
+            self.staging = torch.zeros(N_SLOTS * self.max_padded, dtype=torch.bfloat16, device=device)
+            self.pads = torch.zeros(n_pads, dtype=torch.int32, device=device)
+            self.param_ptrs = [self.param_arena.data_ptr()]
+            self.staging_ptrs = [self.staging.data_ptr()]
+            self.pad_ptrs = [self.pads.data_ptr()]
         self.ready_base = 0                       # pads[slot*world + rank]
         self.done_base = N_SLOTS * self.world     # pads[done_base + slot*world + rank]
 
@@ -158,26 +175,40 @@ class FsdpRuntime:
 
     def _init_parameters(self) -> None:
         """Random N(0, initializer_range) weights, identical to a single-replica initialisation:
-        every rank draws the full unit from the same seeded generator and keeps its slice."""
-        cfg = self.cfg
+        every rank draws the full unit from the same seeded generator and keeps its slice (its
+        tensor-parallel slice of every segment first, then its FSDP shard of that)."""
+        from .tp import slice_unit_tensor
+
+        full_cfg = self.full_cfg
+        full_layouts = {lay.name: lay for lay in unit_layouts(full_cfg)}
         gen = torch.Generator(device=self.device).manual_seed(self.tcfg.seed)
-        scratch = torch.zeros(self.max_padded, dtype=torch.bfloat16, device=self.device)
+        scratch_full = torch.zeros(max(lay.numel for lay in full_layouts.values()), dtype=torch.bfloat16,
+                                   device=self.device)
+        scratch = torch.zeros(self.max_padded, dtype=torch.bfloat16, device=self.device) if self.tp_world > 1 else scratch_full
+        if scratch.numel() < self.max_padded:
+            scratch = scratch_full = torch.zeros(self.max_padded, dtype=torch.bfloat16, device=self.device)
         for name, u in self.units.items():
-            scratch.zero_()
-            unit = Unit(u.layout, scratch)
-            for seg in u.layout.segments:
-                t = unit.view(seg.name)
+            scratch_full.zero_()
+            full_unit = Unit(full_layouts[name], scratch_full)
+            for seg in full_layouts[name].segments:
+                t = full_unit.view(seg.name)
                 if seg.name in ("ln1", "ln2", "norm"):
                     t.fill_(1.0)
                 elif seg.name.endswith("_b"):
                     t.zero_()
                 else:
-                    t.normal_(0.0, cfg.initializer_range, generator=gen)
+                    t.normal_(0.0, full_cfg.initializer_range, generator=gen)
             if name == "embed":
-                unit.view("embed")[cfg.pad_token_id].zero_()
+                full_unit.view("embed")[full_cfg.pad_token_id].zero_()
+            if self.tp_world > 1:
+                scratch.zero_()
+                unit = Unit(u.layout, scratch)
+                for seg in u.layout.segments:
+                    unit.view(seg.name).copy_(slice_unit_tensor(seg.name, full_unit.view(seg.name), full_cfg,
+                                                                self.tp_world, self.tp_rank))
             lo = self.rank * u.shard_elems
             self.shard_view(name).copy_(scratch[lo:lo + u.shard_elems])
-        del scratch
+        del scratch, scratch_full
         torch.cuda.synchronize(self.device)
         dist.barrier(self.group)
 
@@ -367,6 +398,13 @@ class FsdpRuntime:
         self.main.wait_stream(self.side)
         self.main.wait_stream(self.reduce_stream)
         total = self.sumsq.sum().reshape(1)
+        if self.tp_world > 1:
+            # norm scales are replicated over tp: every tp rank holds the same (already summed)
+            # gradient, so its square counts once
+            rep = self._replicated_index()
+            if rep.numel():
+                total = total - (1.0 - 1.0 / self.tp_world) * self.grad_shards[rep].float().pow(2).sum()
+            dist.all_reduce(total, group=self.tp_group)
         dist.all_reduce(total, group=self.group)          # also orders every peer's pulls before the update
         grad_norm = torch.sqrt(total)
         clip = torch.ones_like(grad_norm)
@@ -387,6 +425,23 @@ class FsdpRuntime:
         for g in self.gathered:
             g.unit = None
         return grad_norm[0]
+
+    def _replicated_index(self) -> torch.Tensor:
+        """Arena positions, inside this rank's shards, of parameters replicated over tp."""
+        if getattr(self, "_rep_index", None) is None:
+            from .tp import REPLICATED_SEGMENTS
+
+            pieces = []
+            for name, u in self.units.items():
+                lo, hi = self.rank * u.shard_elems, (self.rank + 1) * u.shard_elems
+                for seg in u.layout.segments:
+                    if seg.name in REPLICATED_SEGMENTS:
+                        a, b = max(seg.offset, lo), min(seg.offset + seg.numel, hi)
+                        if b > a:
+                            pieces.append(torch.arange(u.arena_offset + a - lo, u.arena_offset + b - lo,
+                                                       device=self.device))
+            self._rep_index = torch.cat(pieces) if pieces else torch.zeros(0, dtype=torch.long, device=self.device)
+        return self._rep_index
 
     # ------------------------------------------------------------------ step driver
     def make_step(self, engine) -> "FsdpStep":

@@ -302,12 +302,7 @@ class LayerwiseEngine:
             gbuf = prov.grad_buffer("embed")[seg.offset:seg.offset + seg.numel].view(seg.shape)
             if first:
                 gbuf.zero_()
-            ids = batch["input_ids"].reshape(-1)
-            keep = ids != cfg.pad_token_id
-            uniq, inverse = torch.unique(ids[keep], return_inverse=True)
-            tmp = torch.zeros((uniq.numel(), cfg.hidden_size), dtype=torch.float32, device=ids.device)
-            tmp.index_add_(0, inverse, dout[keep].float())
-            gbuf[uniq] += tmp.to(gbuf.dtype)
-            self._count(8)
+            ew.embedding_backward(batch["input_ids"], dout, gbuf, cfg.pad_token_id)
+            self._count(5)
             prov.grads_ready("embed", last)
         return nll, wsum

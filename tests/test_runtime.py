@@ -115,4 +115,4 @@ def test_error_bus_raises_on_every_rank(tmp_path):
 def test_disagreeing_flags_and_rank_zero_failures_are_seen_everywhere(tmp_path):
     assert _launch(tmp_path, "mismatch").count("MISMATCH") == 3
     out = _launch(tmp_path, "zero")
-    assert "ZERO-OWN 0" in out and out.count("ZERO-PEER") == 2 and "disk full" in out
+    assert out.count("ZERO-OWN") == 1 and out.count("ZERO-PEER") == 2 and "disk full" in out   # output may interleave

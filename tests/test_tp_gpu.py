@@ -1,0 +1,64 @@
+"""Tensor parallelism over NVLink peer memory: fused all-gather->GEMM, GEMM->reduce-scatter,
+vocabulary-parallel cut cross-entropy and embedding against fp32 PyTorch references, and whole
+training steps (tp=2, fsdp=2 x tp=2) against the FSDP-only run of the same model and data."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _launch(args: list[str], nproc: int, out: Path, port: int):
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
+           "--master-addr", "127.0.0.1", "--master-port", str(port), str(ROOT / "tests" / "_tp_worker.py"),
+           args[0], str(out)] + args[1:]
+    res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
+    assert res.returncode == 0, res.stdout[-3000:] + res.stderr[-3000:]
+    return json.loads(out.read_text())
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp_primitives_match_references(cuda_lib, tmp_path):
+    per_rank = _launch(["ops"], 2, tmp_path / "ops.json", 29631)
+    for r in per_rank:
+        assert r["status"] == [0, 0, 0, 0]
+        for it in range(3):
+            assert r[f"ag_gemm_{it}"] < 1e-2
+            assert r[f"ag_wgrad_{it}"] < 1e-2
+            assert r[f"gemm_rs_{it}"] < 1e-2
+        assert r["ce_lse"] < 2e-2 and r["ce_nll"] < 1e-3
+        assert r["ce_dhidden"] < 2e-2 and r["ce_dhead"] < 2e-2
+        assert r["embed"] == 0.0
+
+
+def _close(a: list[dict], b: list[dict], loss_tol: float, norm_tol: float) -> None:
+    for x, y in zip(a, b):
+        assert x["token_count"] == y["token_count"]
+        assert abs(x["loss"] - y["loss"]) < loss_tol
+        assert abs(x["grad_norm"] - y["grad_norm"]) / y["grad_norm"] < norm_tol
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp2_training_matches_fsdp2(cuda_lib, tmp_path):
+    tp_fused = _launch(["train", "2", "fused", "3"], 2, tmp_path / "tp.json", 29632)
+    tp_nccl = _launch(["train", "2", "nccl", "3"], 2, tmp_path / "tpn.json", 29633)
+    fsdp = _launch(["train", "1", "fused", "3"], 2, tmp_path / "fsdp.json", 29634)
+    assert tp_fused["status"] == [0, 0, 0, 0]
+    _close(tp_fused["history"], fsdp["history"], 2e-2, 3e-2)
+    _close(tp_nccl["history"], fsdp["history"], 2e-2, 3e-2)
+    assert tp_fused["history"][-1]["loss"] < tp_fused["history"][0]["loss"]
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
+def test_fsdp2_tp2_training_matches_fsdp4(cuda_lib, tmp_path):
+    mixed = _launch(["train", "2", "fused", "3"], 4, tmp_path / "mixed.json", 29635)
+    fsdp = _launch(["train", "1", "fused", "3"], 4, tmp_path / "fsdp4.json", 29636)
+    assert mixed["status"] == [0, 0, 0, 0]
+    _close(mixed["history"], fsdp["history"], 2e-2, 3e-2)
