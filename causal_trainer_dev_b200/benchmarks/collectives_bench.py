@@ -134,7 +134,7 @@ def main() -> None:
     sptr = _ptr_array([int(p) for p in hs.buffer_ptrs])
     pptr = [int(p) for p in hp.buffer_ptrs]
     grad = torch.empty(shard, dtype=torch.bfloat16, device="cuda")
-    sumsq = torch.zeros(256, dtype=torch.float32, device="cuda")
+    sumsq = torch.zeros(128 * 8, dtype=torch.float32, device="cuda")
     counter = torch.zeros(1, dtype=torch.int32, device="cuda")
     done = _ptr_array([p + 4 * (2 * world + rank) for p in pptr])
 

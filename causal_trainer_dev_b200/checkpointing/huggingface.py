@@ -109,13 +109,44 @@ def load_parameters(source: str | os.PathLike[str], params: ModelParams) -> None
         index.close()
 
 
+def tp_window(name: str, cfg: ModelConfig, tp: int, tp_rank: int) -> tuple[int, int, int, int, str]:
+    """``(row0, rows, col0, cols, kind)`` of the part of Hugging Face tensor ``name`` that tensor-
+    parallel rank ``tp_rank`` stores; ``kind`` is how the parts tile the tensor: ``"rows"``
+    (column-parallel weights, biases, embedding, head), ``"cols"`` (row-parallel o/down weights)
+    or ``"rep"`` (norm scales, every rank holds all of it)."""
+    d, q, kv, f, v = cfg.hidden_size, cfg.query_width, cfg.key_value_width, cfg.intermediate_size, cfg.vocab_size
+    leaf = name.split(".")[-2]
+    vector = name.endswith(".bias") or "norm" in name
+    if "norm" in name:
+        return 0, d, 0, 1, "rep"
+    rows_of = {"q_proj": q, "k_proj": kv, "v_proj": kv, "gate_proj": f, "up_proj": f, "embed_tokens": v, "lm_head": v}
+    if leaf in rows_of:
+        n = rows_of[leaf] // tp
+        return tp_rank * n, n, 0, (1 if vector else d), "rows"
+    if leaf == "o_proj":
+        return 0, d, tp_rank * (q // tp), q // tp, "cols"
+    if leaf == "down_proj":
+        return 0, d, tp_rank * (f // tp), f // tp, "cols"
+    raise KeyError(name)
+
+
+def _full_columns(name: str, cfg: ModelConfig) -> int:
+    leaf = name.split(".")[-2]
+    if name.endswith(".bias") or "norm" in name:
+        return 1
+    return {"o_proj": cfg.query_width, "down_proj": cfg.intermediate_size}.get(leaf, cfg.hidden_size)
+
+
 def load_sharded_parameters(source: str | os.PathLike[str], runtime) -> None:
-    """Fills the FSDP shards: every rank reads only the byte ranges that fall inside its slices."""
+    """Fills the FSDP shards: every rank reads only the byte ranges that fall inside its slices
+    (of its tensor-parallel window of each tensor, when the runtime holds a tp slice)."""
     cfg = runtime.cfg
+    full_cfg = getattr(runtime, "full_cfg", cfg)
+    tp, tp_rank = getattr(runtime, "tp_world", 1), getattr(runtime, "tp_rank", 0)
     index = st.SafeTensorIndex(source)
     mapping = hf_name_map(cfg)
     try:
-        _check_source(index, cfg)
+        _check_source(index, full_cfg)
         by_unit: dict[str, list[str]] = {}
         for name in hf_export_order(cfg):
             by_unit.setdefault(mapping[name][0], []).append(name)
@@ -131,12 +162,21 @@ def load_sharded_parameters(source: str | os.PathLike[str], runtime) -> None:
                     inner = 1
                     for s in seg.shape[1:]:
                         inner *= s
-                    t0 = seg.offset + r0 * inner            # flat extent of this HF tensor in the unit
+                    t0 = seg.offset + r0 * inner            # flat extent of this rank's part in the unit
                     t1 = t0 + rows * inner
                     a, b = max(t0, lo), min(t1, hi)
                     if b <= a:
                         continue
-                    piece = index.file_of(name).flat_range(name, a - t0, b - t0)
+                    f = index.file_of(name)
+                    if tp == 1:
+                        piece = f.flat_range(name, a - t0, b - t0)
+                    else:
+                        row0, _, col0, cols, _ = tp_window(name, full_cfg, tp, tp_rank)
+                        width = _full_columns(name, full_cfg)
+                        i0, i1 = (a - t0) // inner, (b - t0 - 1) // inner + 1      # local rows touched
+                        block = f.flat_range(name, (row0 + i0) * width, (row0 + i1) * width).view(i1 - i0, width)
+                        local = block[:, col0:col0 + cols].reshape(-1)
+                        piece = local[(a - t0) - i0 * inner:(b - t0) - i0 * inner]
                     shard[a - lo:b - lo].copy_(piece.to(torch.bfloat16))
     finally:
         index.close()
@@ -151,7 +191,8 @@ class TensorSource:
         if (params is None) == (runtime is None):
             raise ValueError("give exactly one of params / runtime")
         self.cfg, self.params, self.runtime, self.transform = cfg, params, runtime, transform
-        self.mapping = hf_name_map(cfg)
+        # under tensor parallelism the runtime stores slices laid out by its local config
+        self.mapping = hf_name_map(runtime.cfg if runtime is not None else cfg)
         self.dtype = params.dtype if params is not None else torch.bfloat16
 
     def chunks(self, name: str) -> Iterator[torch.Tensor]:
@@ -169,6 +210,7 @@ class TensorSource:
 
     def _sharded_chunks(self, name: str) -> Iterator[torch.Tensor]:
         rtm = self.runtime
+        tp, tp_rank = getattr(rtm, "tp_world", 1), getattr(rtm, "tp_rank", 0)
         unit_name, seg_name, r0, rows = self.mapping[name]
         u = rtm.units[unit_name]
         seg = u.layout.segment(seg_name)
@@ -176,22 +218,47 @@ class TensorSource:
         for s in seg.shape[1:]:
             inner *= s
         t0 = seg.offset + r0 * inner
-        t1 = t0 + rows * inner
+        local_numel = rows * inner
         step = max(1, GATHER_ROUND_BYTES // 2)
         shard = rtm.shard_view(unit_name)
-        for a in range(t0, t1, step):
-            b = min(t1, a + step)
-            # each rank contributes the part of [a, b) it owns; rank 0 assembles
-            lo, hi = rtm.rank * u.shard_elems, (rtm.rank + 1) * u.shard_elems
-            x, y = max(a, lo), min(b, hi)
-            mine = shard[x - lo:y - lo].detach().cpu() if y > x else torch.empty(0, dtype=torch.bfloat16)
-            pieces = rt.gather_object_to_zero((x, mine))   # only rank 0 ever holds the round
-            if rtm.rank == 0:
-                out = torch.empty(b - a, dtype=torch.bfloat16)
-                for start, piece in pieces:
+        lo, hi = rtm.rank * u.shard_elems, (rtm.rank + 1) * u.shard_elems
+        me = rt.process_index()
+
+        def gather_round(want_tp: int | None, a: int, b: int):
+            """Every process sends the part of local flat range [a, b) it owns (if its tp rank is
+            wanted); process 0 gets ``[(tp_rank, start, piece), ...]``."""
+            x, y = max(t0 + a, lo), min(t0 + b, hi)
+            mine = torch.empty(0, dtype=torch.bfloat16)
+            if y > x and (want_tp is None or want_tp == tp_rank):
+                mine = shard[x - lo:y - lo].detach().cpu()
+            return rt.gather_object_to_zero((tp_rank, x - t0, mine))
+
+        kind = "rows" if tp == 1 else tp_window(name, self.cfg, tp, 0)[4]
+        if kind in ("rows", "rep"):
+            for r in range(1 if kind == "rep" else tp):
+                for a in range(0, local_numel, step):
+                    b = min(local_numel, a + step)
+                    pieces = gather_round(r, a, b)
+                    if me == 0:
+                        out = torch.empty(b - a, dtype=torch.bfloat16)
+                        for _, start, piece in pieces:
+                            if piece.numel():
+                                out[start - a:start - a + piece.numel()] = piece
+                        yield out
+                    else:
+                        yield torch.empty(0, dtype=torch.bfloat16)
+            return
+        # row-parallel weight: every output row is the concatenation of the tp ranks' row pieces
+        block_rows = max(1, step // (inner * tp))
+        for i0 in range(0, rows, block_rows):
+            i1 = min(rows, i0 + block_rows)
+            pieces = gather_round(None, i0 * inner, i1 * inner)
+            if me == 0:
+                parts = [torch.empty((i1 - i0) * inner, dtype=torch.bfloat16) for _ in range(tp)]
+                for r, start, piece in pieces:
                     if piece.numel():
-                        out[start - a:start - a + piece.numel()] = piece
-                yield out
+                        parts[r][start - i0 * inner:start - i0 * inner + piece.numel()] = piece
+                yield torch.cat([x.view(i1 - i0, inner) for x in parts], dim=1).reshape(-1)
             else:
                 yield torch.empty(0, dtype=torch.bfloat16)
 

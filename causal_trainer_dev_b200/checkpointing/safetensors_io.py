@@ -14,6 +14,7 @@ import json
 import mmap
 import os
 import struct
+import warnings
 from dataclasses import dataclass
 from pathlib import Path
 from typing import Any, Iterator, Mapping, Sequence
@@ -97,6 +98,13 @@ def read_header(path: str | os.PathLike[str]) -> tuple[dict[str, TensorInfo], di
     return tensors, meta, data_start
 
 
+def _view_of(buffer, **kwargs) -> torch.Tensor:
+    """``torch.frombuffer`` on a read-only mapping (callers never write through these views)."""
+    with warnings.catch_warnings():
+        warnings.simplefilter("ignore", UserWarning)
+        return torch.frombuffer(buffer, **kwargs)
+
+
 class SafeTensorsFile:
     """Memory-mapped read access to one file."""
 
@@ -132,7 +140,7 @@ class SafeTensorsFile:
             count *= s
         if count == 0:
             return torch.empty(info.shape, dtype=DTYPES[info.dtype])
-        flat = torch.frombuffer(self._map, dtype=DTYPES[info.dtype], count=count,
+        flat = _view_of(self._map, dtype=DTYPES[info.dtype], count=count,
                                 offset=self._data_start + info.data_offsets[0])
         return flat.view(info.shape)
 
@@ -149,7 +157,7 @@ class SafeTensorsFile:
         if n * inner == 0:
             return torch.empty((n, *info.shape[1:]), dtype=DTYPES[info.dtype])
         esize = dtype_size(info.dtype)
-        flat = torch.frombuffer(self._map, dtype=DTYPES[info.dtype], count=n * inner,
+        flat = _view_of(self._map, dtype=DTYPES[info.dtype], count=n * inner,
                                 offset=self._data_start + info.data_offsets[0] + start * inner * esize)
         return flat.view((n, *info.shape[1:]))
 
@@ -159,7 +167,7 @@ class SafeTensorsFile:
         esize = dtype_size(info.dtype)
         if stop <= start:
             return torch.empty(0, dtype=DTYPES[info.dtype])
-        return torch.frombuffer(self._map, dtype=DTYPES[info.dtype], count=stop - start,
+        return _view_of(self._map, dtype=DTYPES[info.dtype], count=stop - start,
                                 offset=self._data_start + info.data_offsets[0] + start * esize)
 
 

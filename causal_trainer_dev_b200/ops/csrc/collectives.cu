@@ -156,7 +156,7 @@ struct RsArgs {
   int accumulate_in;           // add the previous contents of accum
   int last;                    // last micro-batch: produce the final gradient
   __nv_bfloat16* grad_out;     // final gradient, parameter dtype (last only; may be null with adam)
-  float* sumsq_partial;        // [gridDim.x] sums of squares of the rounded gradient (last only)
+  float* sumsq_partial;        // [gridDim.x * 8] per-warp sums of squares of the rounded gradient (last only)
   // fused AdamW (last && apply_adam)
   int apply_adam;
   __nv_bfloat16* param;
@@ -224,23 +224,22 @@ __device__ __forceinline__ void rs_finish_vector(const RsArgs& a, long v, float 
 
 __global__ void __launch_bounds__(PULL_THREADS, 3)
 rs_reduce_kernel(const RsArgs a) {
-  __shared__ float red[PULL_THREADS / 32];
-  __shared__ int give_up;
-  if (threadIdx.x == 0) give_up = 0;
-  __syncthreads();
+  // No shared memory (see PULL_THREADS): the verdict of the wait travels through the barrier and
+  // the sums of squares leave the CTA as one partial per warp.
+  int bad = 0;
   if (threadIdx.x < a.world) {
     const unsigned* f = a.ready + a.ready_base + threadIdx.x;
     const long long t0 = clock64();
     while (ld_acquire_sys(f) < a.epoch) {
       if (clock64() - t0 > a.budget) {
         report_failure(a.status, SITE_RS_WAIT, static_cast<unsigned>(threadIdx.x), a.epoch);
-        give_up = 1;
+        bad = 1;
         break;
       }
       __nanosleep(100);
     }
   }
-  __syncthreads();
+  const int give_up = __syncthreads_or(bad);
   float sq = 0.f;
   if (!give_up) {
     const long nvec = a.shard_elems / 8;
@@ -281,14 +280,12 @@ rs_reduce_kernel(const RsArgs a) {
       }
     }
   }
-  // block sum of squares
+  // per-warp sums of squares (the host adds the partials in a fixed order)
   for (int o = 16; o > 0; o >>= 1) sq += __shfl_xor_sync(0xffffffffu, sq, o);
-  if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = sq;
+  if ((threadIdx.x & 31) == 0 && a.sumsq_partial != nullptr)
+    a.sumsq_partial[blockIdx.x * (PULL_THREADS / 32) + (threadIdx.x >> 5)] = a.last ? sq : 0.f;
   __syncthreads();
   if (threadIdx.x == 0) {
-    float t = 0.f;
-    for (int w = 0; w < PULL_THREADS / 32; ++w) t += red[w];
-    if (a.sumsq_partial != nullptr) a.sumsq_partial[blockIdx.x] = a.last ? t : 0.f;
     // the last CTA to finish tells every peer that this rank no longer reads their slot
     __threadfence();
     const unsigned done = atomicAdd(a.finish_counter, 1u) + 1u;

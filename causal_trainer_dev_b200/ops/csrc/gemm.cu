@@ -77,8 +77,30 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
   return c;
 }
 
+// Copies a staged 128 x 128 B block (128-byte swizzle) to `out` (row stride `ld` elements) with
+// 16-byte stores: thread -> (row etid/8 + 16*i, 16-byte column etid%8), so a warp writes four
+// full 128 B rows per step.  Kept out of line so its address arithmetic does not raise the
+// register count of the whole kernel (a CTA must leave room for the pull kernels on its SM).
+__device__ __noinline__ void push_block(const uint8_t* buf, __nv_bfloat16* out, long ld, int etid, int rows_left,
+                                        int cols_left) {
+  const int j = etid & 7;
+  if (j * 8 >= cols_left) return;
+  out += static_cast<long>(etid >> 3) * ld + j * 8;
+#pragma unroll 4
+  for (int i = 0; i < 8; ++i) {
+    const int r = (etid >> 3) + i * 16;
+    if (r < rows_left)
+      *reinterpret_cast<uint4*>(out + static_cast<long>(i) * 16 * ld) =
+          *reinterpret_cast<const uint4*>(buf + sw128_offset(r, j));
+  }
+}
+
+// The kernel runs with NTHREADS (256) threads; declaring room for 384 caps it at 168 registers per
+// thread, which leaves a third of the register file to the small pull / reduce CTAs that must
+// share the SM with a resident GEMM CTA (a GEMM that waits on flags would otherwise starve the
+// kernel that publishes them).
 template <bool A_MN, bool B_MN, int EPI>
-__global__ void __launch_bounds__(NTHREADS, 1)
+__global__ void __launch_bounds__(384, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const __grid_constant__ CUtensorMap map_c, const GemmArgs args) {
   extern __shared__ uint8_t smem_raw[];
@@ -113,7 +135,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   if (warp == 3 && lane == 0) {
     tma_prefetch_desc(&map_a);
     tma_prefetch_desc(&map_b);
-    if (EPI != EPI_CE_STATS) tma_prefetch_desc(&map_c);
+    if (EPI != EPI_CE_STATS && EPI != EPI_PUSH) tma_prefetch_desc(&map_c);
   }
   if (warp == 2) {
     tmem_alloc(tmem_slot, 512);
@@ -420,7 +442,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             v.w = pack_bf16(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
             *reinterpret_cast<uint4*>(buf + sw128_offset(row, 4 + j)) = v;
           }
-          if (EPI == EPI_STORE && args.push.enabled) {
+          if (EPI == EPI_PUSH) {
             // reduce-scatter by push: 128 threads copy the staged 128 x 128 B block into the
             // owner's receive buffer with 16-byte stores (peer memory: plain st.global only)
             named_bar_sync(1, 128);
@@ -428,16 +450,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             const int dest = grow0 / args.push.rows_per_rank;
             const long drow0 = static_cast<long>(args.push.src_rank) * args.push.rows_per_rank +
                                (grow0 - dest * args.push.rows_per_rank);
-            __nv_bfloat16* base = args.push.dest[dest];
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int idx = i * 128 + etid;
-              const int r = idx >> 3, j = idx & 7;
-              if (tc.m0 + r < args.M && col0 + j * 8 < args.N) {
-                const uint4 v = *reinterpret_cast<const uint4*>(buf + sw128_offset(r, j));
-                *reinterpret_cast<uint4*>(base + (drow0 + r) * args.push.ld + col0 + j * 8) = v;
-              }
-            }
+            push_block(buf, args.push.dest[dest] + drow0 * args.push.ld + col0, args.push.ld, etid,
+                       args.M - tc.m0, args.N - col0);
           } else {
             fence_proxy_async_smem();
             named_bar_sync(1, 128);
@@ -449,7 +463,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
           ++buf_idx;
         }
-        if (EPI == EPI_STORE && args.push.enabled) {
+        if (EPI == EPI_PUSH) {
           // this tile is on its way: count it, and publish the flag with the last one
           __threadfence_system();
           named_bar_sync(1, 128);
@@ -556,7 +570,7 @@ int run_gemm(const GemmCall& c) {
   a.ce_coef = c.ce_coef;
   a.push = c.push;
   if (c.push.enabled) {
-    if (c.out_f32 || c.accumulate || c.epi != EPI_STORE) return fail("gemm: the push epilogue writes plain bf16 tiles");
+    if (c.out_f32 || c.accumulate || c.epi != EPI_PUSH) return fail("gemm: the push epilogue writes plain bf16 tiles");
     if (c.push.rows_per_rank % BM || c.push.row_offset % BM || c.push.ld % 8 || c.N % 8)
       return fail("gemm: push needs 128-row aligned rank slabs and 16-byte aligned rows");
   }
@@ -568,6 +582,7 @@ int run_gemm(const GemmCall& c) {
     case EPI_STORE: return launch<AM, BMN, EPI_STORE>(ma, mb, mc, a, grid, s);        \
     case EPI_CE_STATS: return launch<AM, BMN, EPI_CE_STATS>(ma, mb, mc, a, grid, s);  \
     case EPI_CE_DLOGITS: return launch<AM, BMN, EPI_CE_DLOGITS>(ma, mb, mc, a, grid, s); \
+    case EPI_PUSH: return launch<AM, BMN, EPI_PUSH>(ma, mb, mc, a, grid, s);          \
     default: return fail("gemm: unknown epilogue");                                   \
   }
   if (!c.a_mn && !c.b_mn) { CTB_DISPATCH(false, false) }
@@ -611,24 +626,20 @@ CTB_API int ctb_gemm_flagged(const void* A, const void* B, void* C, int M, int N
 }
 
 // Row-parallel projection with the reduce-scatter fused into the epilogue (see GemmPush).
-// `dest_ptrs[p]` is rank p's receive buffer, `flag_ptrs[p]` the address of this rank's flag
-// on rank p.  A may be a gathered buffer (a_flags) exactly as in ctb_gemm_flagged.
+// `dest_table[p]` (device memory) is rank p's receive buffer, `flag_table[p]` the address of this
+// rank's flag on rank p.  A may be a gathered buffer (a_flags) exactly as in ctb_gemm_flagged.
 CTB_API int ctb_gemm_push(const void* A, const void* B, int M, int N, int K, long lda, long ldb, int a_mn, int b_mn,
-                          float alpha, void* const* dest_ptrs, unsigned* const* flag_ptrs, int world,
-                          unsigned* counters, int rows_per_rank, int row_offset, int src_rank, int tiles_per_dest,
+                          float alpha, const void* dest_table, const void* flag_table, unsigned* counters, int rows_per_rank, int row_offset, int src_rank, int tiles_per_dest,
                           long ld, unsigned epoch, const unsigned* b_flags, long b_flag_chunk, long b_flag_base,
                           unsigned b_epoch, int b_wait_all, int n_rotate, int m_rotate, long long spin_budget,
                           int max_ctas, void* stream) {
-  if (world > ctb::GEMM_MAX_RANKS) return ctb::fail("gemm_push: too many ranks");
   ctb::GemmCall c{};
   c.A = A; c.B = B; c.C = nullptr; c.M = M; c.N = N; c.K = K; c.lda = lda; c.ldb = ldb; c.ldc = ld;
-  c.a_mn = a_mn; c.b_mn = b_mn; c.alpha = alpha; c.epi = ctb::EPI_STORE; c.max_ctas = max_ctas; c.stream = stream;
+  c.a_mn = a_mn; c.b_mn = b_mn; c.alpha = alpha; c.epi = ctb::EPI_PUSH; c.max_ctas = max_ctas; c.stream = stream;
   c.b_flags = b_flags; c.b_flag_chunk = b_flag_chunk; c.b_flag_base = b_flag_base; c.b_flag_epoch = b_epoch;
   c.b_wait_all = b_wait_all; c.n_rotate = n_rotate; c.m_rotate = m_rotate; c.spin_budget = spin_budget;
-  for (int i = 0; i < world; ++i) {
-    c.push.dest[i] = static_cast<__nv_bfloat16*>(dest_ptrs[i]);
-    c.push.flag[i] = flag_ptrs[i];
-  }
+  c.push.dest = static_cast<__nv_bfloat16* const*>(dest_table);
+  c.push.flag = static_cast<unsigned* const*>(flag_table);
   c.push.counters = counters; c.push.rows_per_rank = rows_per_rank; c.push.row_offset = row_offset;
   c.push.src_rank = src_rank; c.push.tiles_per_dest = tiles_per_dest; c.push.ld = ld; c.push.epoch = epoch;
   c.push.enabled = 1;

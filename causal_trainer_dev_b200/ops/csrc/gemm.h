@@ -8,17 +8,16 @@ enum GemmEpilogue : int {
   EPI_STORE = 0,       // C = alpha * acc (+ bias), bf16 or fp32, store or reduce-add
   EPI_CE_STATS = 1,    // per-row max / sum-exp / target logit of each 256-column slab
   EPI_CE_DLOGITS = 2,  // C = (exp(acc - lse[row]) - onehot(target[row])) * coef[row], bf16
+  EPI_PUSH = 3,        // bf16 partial tiles stored into the row owners' receive buffers (GemmPush)
 };
-
-constexpr int GEMM_MAX_RANKS = 16;
 
 // Reduce-scatter by push (tensor-parallel row-parallel projections): instead of storing a
 // partial-sum tile into local memory, the epilogue writes it into the receive buffer of the
 // rank that owns those rows, `dest[p] + ((src_rank * rows_per_rank + local_row) * ld + col)`,
 // and the CTA that completes the last tile bound for rank p publishes `epoch` in `flag[p]`.
 struct GemmPush {
-  __nv_bfloat16* dest[GEMM_MAX_RANKS];   // every rank's receive buffer [world][rows_per_rank][ld]
-  unsigned* flag[GEMM_MAX_RANKS];        // &pads_of_rank_p[base + src_rank]
+  __nv_bfloat16* const* dest;            // device table: every rank's receive buffer [world][rows_per_rank][ld]
+  unsigned* const* flag;                 // device table: &pads_of_rank_p[base + src_rank]
   unsigned* counters;                    // local, one per destination rank, self-resetting
   int rows_per_rank;
   int row_offset;                        // global row of row 0 of this GEMM (chunked callers)

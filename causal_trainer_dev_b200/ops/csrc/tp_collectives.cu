@@ -68,11 +68,14 @@ __device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
   asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
 }
 
-// Bounded wait on one flag by thread 0 of the CTA; the verdict is shared through `verdict`.
+// Bounded wait on one flag by thread 0 of the CTA; the verdict reaches every thread through the
+// barrier itself.  No shared memory: a CTA of the pull kernel has to fit beside a resident
+// tcgen05 GEMM CTA that owns nearly all of the SM's shared memory, or the GEMM would spin on
+// flags that the pull can never get on the machine to publish.
 __device__ __forceinline__ bool cta_wait_flag(const unsigned* f, unsigned epoch, long long budget, DeviceStatus* st,
-                                              unsigned site, unsigned info, int* verdict) {
+                                              unsigned site, unsigned info) {
+  int ok = 1;
   if (threadIdx.x == 0) {
-    int ok = 1;
     const long long t0 = clock64();
     while (ld_acquire_sys(f) < epoch) {
       if (clock64() - t0 > budget) {
@@ -82,12 +85,8 @@ __device__ __forceinline__ bool cta_wait_flag(const unsigned* f, unsigned epoch,
       }
       __nanosleep(64);
     }
-    *verdict = ok;
   }
-  __syncthreads();
-  const bool ok = *verdict != 0;
-  __syncthreads();
-  return ok;
+  return __syncthreads_and(ok) != 0;
 }
 
 // ------------------------------------------------------------------------------------------
@@ -97,7 +96,6 @@ __global__ void __launch_bounds__(THREADS, 4)
 tp_ag_pull_kernel(Ptrs bufs, long slab_elems, int rank, int world, int chunk_elems, unsigned* __restrict__ flags,
                   unsigned epoch, const unsigned* __restrict__ ready, unsigned ready_epoch, long long budget,
                   DeviceStatus* st) {
-  __shared__ int verdict;
   const int cps = static_cast<int>(slab_elems / chunk_elems);
   // own rows were written in place by the kernel before this one in stream order
   if (blockIdx.x == 0) {
@@ -111,7 +109,7 @@ tp_ag_pull_kernel(Ptrs bufs, long slab_elems, int rank, int world, int chunk_ele
     const int src = (rank + 1 + pos / cps) % world;
     const int c = pos % cps;
     if (src != waited_src) {
-      if (!cta_wait_flag(ready + src, ready_epoch, budget, st, SITE_TP_AG_READY, static_cast<unsigned>(src), &verdict))
+      if (!cta_wait_flag(ready + src, ready_epoch, budget, st, SITE_TP_AG_READY, static_cast<unsigned>(src)))
         return;
       waited_src = src;
     }
@@ -146,22 +144,19 @@ __global__ void __launch_bounds__(THREADS, 4)
 tp_reduce_kernel(const __nv_bfloat16* __restrict__ recv, long slab_elems, int world,
                  const unsigned* __restrict__ flags, unsigned epoch, __nv_bfloat16* __restrict__ out,
                  long long budget, DeviceStatus* st) {
-  __shared__ int give_up;
-  if (threadIdx.x == 0) give_up = 0;
-  __syncthreads();
+  int bad = 0;
   if (threadIdx.x < world) {
     const long long t0 = clock64();
     while (ld_acquire_sys(flags + threadIdx.x) < epoch) {
       if (clock64() - t0 > budget) {
         report_failure(st, SITE_TP_REDUCE, static_cast<unsigned>(threadIdx.x), epoch);
-        give_up = 1;
+        bad = 1;
         break;
       }
       __nanosleep(64);
     }
   }
-  __syncthreads();
-  if (give_up) return;
+  if (__syncthreads_or(bad)) return;
   const long nvec = slab_elems / 8;
   const long stride = static_cast<long>(gridDim.x) * THREADS;
   for (long v = blockIdx.x * static_cast<long>(THREADS) + threadIdx.x; v < nvec; v += stride) {

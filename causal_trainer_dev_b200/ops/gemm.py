@@ -148,9 +148,9 @@ def gemm_push(a: torch.Tensor, b: torch.Tensor, push, *, b_mn: bool = False, row
     """``A @ B^T`` whose bf16 partial-sum tiles go straight into the receive buffers of the ranks
     that own the rows (reduce-scatter by push, see ``GemmPush`` in ``csrc/gemm.h``).
 
-    ``push`` describes the destination: ``dest_ptrs``/``flag_ptrs`` (ctypes arrays, one entry per
-    rank), ``world``, ``counters`` (int32 tensor), ``rows_per_rank``, ``src_rank``, ``ld``,
-    ``epoch`` and ``spin_budget``.
+    ``push`` describes the destination: ``dest_table``/``flag_table`` (int64 device tensors, one
+    address per rank), ``world``, ``counters`` (int32 tensor), ``rows_per_rank``, ``src_rank``,
+    ``ld``, ``epoch`` and ``spin_budget``.
     """
     _check_operand(a, "a")
     _check_operand(b, "b")
@@ -169,7 +169,7 @@ def gemm_push(a: torch.Tensor, b: torch.Tensor, push, *, b_mn: bool = False, row
         tiles_per_dest = (push.rows_per_rank // 128) * (-(-n // 256))
     code = _lib.lib().ctb_gemm_push(
         _lib.ptr(a), _lib.ptr(b), m, n, k, ctypes.c_long(a.stride(0)), ctypes.c_long(b.stride(0)), 0, int(b_mn),
-        ctypes.c_float(alpha), push.dest_ptrs, push.flag_ptrs, push.world, _lib.ptr(push.counters),
+        ctypes.c_float(alpha), _lib.ptr(push.dest_table), _lib.ptr(push.flag_table), _lib.ptr(push.counters),
         push.rows_per_rank, row_offset, push.src_rank, tiles_per_dest, ctypes.c_long(push.ld),
         ctypes.c_uint(push.epoch), *_flag_args(hit), 0, n_rotate, m_rotate, ctypes.c_longlong(push.spin_budget),
         max_ctas, _lib.stream_ptr(),

@@ -154,7 +154,7 @@ class FsdpRuntime:
         self.v = torch.zeros(self.arena_elems, dtype=torch.bfloat16, device=device)
         self.grad_shards = torch.zeros(self.arena_elems, dtype=torch.bfloat16, device=device)
         self.accum: torch.Tensor | None = None
-        self.sumsq = torch.zeros((len(self.units), REDUCE_CTAS), dtype=torch.float32, device=device)
+        self.sumsq = torch.zeros((len(self.units), REDUCE_CTAS * 8), dtype=torch.float32, device=device)
         self.finish_counter = torch.zeros(1, dtype=torch.int32, device=device)
         self.gathered = [_Gathered(self.max_padded, device) for _ in range(N_GATHER)]
         self.where: dict[str, _Gathered] = {}

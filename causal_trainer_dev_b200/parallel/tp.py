@@ -115,8 +115,8 @@ class _Push:
     """Destination description handed to ``ops.gemm.gemm_push``."""
 
     def __init__(self, ctx: "TpContext", buf: int, epoch: int):
-        self.dest_ptrs = ctx.recv_ptr_arrays[buf]
-        self.flag_ptrs = ctx.recv_flag_ptr_arrays[buf]
+        self.dest_table = ctx.recv_tables[buf]
+        self.flag_table = ctx.recv_flag_tables[buf]
         self.world = ctx.world
         self.counters = ctx.counters
         self.rows_per_rank = ctx.rows_per_rank
@@ -214,9 +214,11 @@ class TpContext:
             torch.cuda.synchronize(device)
             dist.barrier(group)
             self.ring_ptr_arrays = [_ptr_array(p) for p in self.ring_ptrs]
-            self.recv_ptr_arrays = [_ptr_array(p) for p in self.recv_ptrs]
-            self.recv_flag_ptr_arrays = [
-                _ptr_array([p + 4 * (self.recv_base + b * w + self.rank) for p in self.pad_ptrs]) for b in range(N_RECV)]
+            # the GEMM epilogue indexes these by destination rank: device-resident address tables
+            self.recv_tables = [torch.tensor(p, dtype=torch.int64, device=device) for p in self.recv_ptrs]
+            self.recv_flag_tables = [
+                torch.tensor([p + 4 * (self.recv_base + b * w + self.rank) for p in self.pad_ptrs], dtype=torch.int64,
+                             device=device) for b in range(N_RECV)]
             self.embed_ptr_arrays = [_ptr_array(p) for p in self.embed_out_ptrs]
             self.stats_ptr_array = _ptr_array(self.stats_ptrs)
             self.ce_flag_ptr_array = _ptr_array([p + 4 * (self.ce_base + self.rank) for p in self.pad_ptrs])

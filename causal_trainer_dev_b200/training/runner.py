@@ -225,8 +225,12 @@ class TrainingRun:
         self.param_dtype = torch.bfloat16 if args.param_dtype == "bfloat16" else torch.float32
         self.use_engine = (self.cuda and self.param_dtype == torch.bfloat16 and args.dtype == "bfloat16"
                            and args.attn_mechanism != "vanilla" and not args.lora and args.loss_implementation != "xla"
-                           and self.lattice.size("tp") == 1 and self.lattice.size("sp") == 1
                            and args.attention_options is None)
+        if self.lattice.size("sp") > 1:
+            raise NotImplementedError("the sp axis must be 1: long sequences are sharded by token rows over tp")
+        if self.lattice.size("tp") > 1 and not self.use_engine:
+            raise ValueError("tensor parallelism (tp > 1) runs on the bf16 CUDA engine only: it needs GPUs, "
+                             "--attn_mechanism efficient, a fused loss, no LoRA and dense attention")
         self.prepared_revision: str | None = None
         self.source_examples_seen = 0
         self.stream_digest: str | None = None
@@ -352,18 +356,32 @@ class TrainingRun:
             else (self.source if self.has_weights else None)
         data_ranks = self.lattice.size("dp") * self.lattice.size("fsdp")
         self.lora: LoraState | None = None
-        if self.use_engine and data_ranks > 1:
+        tp = self.lattice.size("tp")
+        if self.use_engine and (data_ranks > 1 or tp > 1):
             from ..api import TrainerConfig
             from ..parallel.fsdp import FsdpRuntime
             from .engine import EngineOptions, LayerwiseEngine
 
             tcfg = TrainerConfig(micro_batch_rows=a.micro_batch_rows or a.total_batch_size // data_ranks, adamw=adamw,
                                  schedule=schedule, seed=a.seed, fused_collectives=a.fused_collectives,
-                                 cut_chunk_rows=a.cut_chunk_size or 4096)
-            self.runtime = FsdpRuntime(self.cfg, tcfg, self.device)
+                                 cut_chunk_rows=a.cut_chunk_size or 4096, tp=tp)
+            options = EngineOptions(cut_chunk_rows=tcfg.cut_chunk_rows)
+            # parameters, gradients and optimizer state are sharded over dp x fsdp (a dp replica
+            # would only cost memory); tensor-parallel ranks hold slices of every projection
+            data_group = self.lattice.group(("dp", "fsdp"))
+            if tp > 1:
+                from ..parallel.tp import tp_local_config
+                from .tp_engine import TpLayerwiseEngine
+
+                tp_group = self.lattice.group(("tp",))
+                self.runtime = FsdpRuntime(tp_local_config(self.cfg, tp), tcfg, self.device, group=data_group,
+                                           full_cfg=self.cfg, tp_group=tp_group)
+                engine = TpLayerwiseEngine(self.cfg, tp_group, self.runtime, options, fused=a.fused_collectives)
+            else:
+                self.runtime = FsdpRuntime(self.cfg, tcfg, self.device, group=data_group)
+                engine = LayerwiseEngine(self.cfg, self.runtime, options)
             if weights_from is not None:
                 hfio.load_sharded_parameters(weights_from, self.runtime)
-            engine = LayerwiseEngine(self.cfg, self.runtime, EngineOptions(cut_chunk_rows=tcfg.cut_chunk_rows))
             self.step_fn = self.runtime.make_step(engine)
             self.params = None
         else:
@@ -417,7 +435,14 @@ class TrainingRun:
                 for name, u in r.units.items():
                     full = torch.empty(u.padded, dtype=torch.bfloat16, device=self.device)
                     torch.distributed.all_gather_into_tensor(full, r.shard_view(name, of=arena).contiguous(), group=r.group)
-                    out.append((f"{kind}/{name}", full[:u.layout.numel].cpu()))
+                    if r.tp_world == 1:
+                        out.append((f"{kind}/{name}", full[:u.layout.numel].cpu()))
+                        continue
+                    # one entry per tensor-parallel slice, in tp rank order
+                    slices = [torch.empty_like(full) for _ in range(r.tp_world)]
+                    torch.distributed.all_gather(slices, full, group=r.tp_group)
+                    for t, piece in enumerate(slices):
+                        out.append((f"{kind}/{name}/tp{t}", piece[:u.layout.numel].cpu()))
             return out
         opt = self.step_fn.optimizer
         out = [("count", torch.tensor(opt.count, dtype=torch.int64))]
@@ -434,7 +459,7 @@ class TrainingRun:
             r.count = int(state["count"])
             for kind, arena in (("mu", r.m), ("nu", r.v)):
                 for name, u in r.units.items():
-                    full = state[f"{kind}/{name}"]
+                    full = state[f"{kind}/{name}" if r.tp_world == 1 else f"{kind}/{name}/tp{r.tp_rank}"]
                     lo = r.rank * u.shard_elems
                     piece = full[lo:min(lo + u.shard_elems, full.numel())]
                     view = r.shard_view(name, of=arena)
