@@ -183,10 +183,10 @@ def moba_attention(query, key, value, segments, options: AttentionOptions, scale
             return attn_ops.flash_attention(query, key, value, meta, scale)
         return attn_ops.vanilla_attention(query, key, value, segments, None, scale)
     native = _native_available() and query.is_cuda and options.backend != "reference" \
-        and query.dtype == torch.bfloat16 and s % 128 == 0
+        and query.dtype == torch.bfloat16 and s % 128 == 0 and block >= 128
     if native:
         from ..ops import moba as moba_ops
 
-        return moba_ops.moba_flash_attention(query, key, value, segments, block, options.moba_top_k, scale)
+        return moba_ops.moba_flash_attention(query, key, value, segments, block, options.moba_top_k, scale, meta)
     mask = moba_visibility(query, key, segments, block, options.moba_top_k)
     return _masked_attention(query, key, value, mask, scale)

@@ -12,6 +12,21 @@ namespace attn {
 //   kv_hi  [B,S/128]  one past the last such key index (kv_hi <= kv_lo: nothing visible)
 //   kmin/kmax [B,S/128] min / max segment id inside each 128-key block
 //   q_lo/q_hi [B,S/128] per 128-key block: range of query indices that can see it
+// MoBA block-sparse routing (all null / zero for dense attention).  Keys are cut into blocks of
+// `block` tokens counted from the start of their document; query i of head h may see key j of its
+// own document iff j <= lim[i] and bit ((j - doc_start[i]) / block) of its selection mask is set
+// (the query's own block is always selected).  Each CTA walks a list of key tiles (forward) or of
+// (64-row block, head) pairs (backward) that host code derived from the union of its rows'
+// selections, instead of a contiguous range.
+struct SparseArgs {
+  const int* it_off;       // [work items + 1] offsets into it_list, work items in blockIdx order
+  const int* it_list;      // forward: 128-key tile index; backward: 64-row block | head_in_group << 24
+  const unsigned* sel;     // [B][Hq][S][words]
+  const int* doc_start;    // [B][S]
+  int block;               // >= 128
+  int words;
+};
+
 struct FwdArgs {
   int B, S, Hq, Hkv;
   float scale_log2;
@@ -24,6 +39,7 @@ struct FwdArgs {
   float* lse;
   DeviceStatus* status;
   long long spin_budget;
+  SparseArgs sp;
 };
 
 struct FwdCall {
@@ -34,6 +50,7 @@ struct FwdCall {
   float scale;
   long long spin_budget;
   void* stream;
+  SparseArgs sp{};
 };
 
 enum : int { MODE_DKV = 0, MODE_DQ = 1 };
@@ -58,6 +75,7 @@ struct BwdArgs {
   const float* delta;
   DeviceStatus* status;
   long long spin_budget;
+  SparseArgs sp;
 };
 
 struct BwdCall {
@@ -71,7 +89,32 @@ struct BwdCall {
   float scale;
   long long spin_budget;
   void* stream;
+  SparseArgs sp{};
 };
+
+// Selection bit of document-relative block `blk` for (batch b, head h, query qi).
+__device__ __forceinline__ bool sparse_bit(const SparseArgs& sp, int b, int h, int Hq, int S, int qi, int blk) {
+  if (blk < 0 || (blk >> 5) >= sp.words) return false;
+  const unsigned w = __ldg(sp.sel + ((static_cast<size_t>(b) * Hq + h) * S + qi) * sp.words + (blk >> 5));
+  return (w >> (blk & 31)) & 1u;
+}
+
+// For a query row and the keys [k0, k0 + width): the keys before `bound` are visible iff `v0`,
+// the keys from `bound` on iff `v1` (a tile no wider than a block holds at most one boundary).
+struct SparseRow {
+  int bound;
+  bool v0, v1;
+};
+__device__ __forceinline__ SparseRow sparse_row(const SparseArgs& sp, int b, int h, int Hq, int S, int qi,
+                                                int my_start, int k0, int width) {
+  SparseRow r;
+  const int rel = k0 - my_start;
+  const int b0 = rel >= 0 ? rel / sp.block : -1;
+  r.bound = my_start + (b0 + 1) * sp.block;
+  r.v0 = sparse_bit(sp, b, h, Hq, S, qi, b0);
+  r.v1 = (r.bound < k0 + width) ? sparse_bit(sp, b, h, Hq, S, qi, b0 + 1) : r.v0;
+  return r;
+}
 
 }  // namespace attn
 }  // namespace ctb

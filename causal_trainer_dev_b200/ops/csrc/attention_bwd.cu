@@ -106,8 +106,22 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     y_n64 = khi > klo ? (khi + 63) / 64 - y_lo64 : 0;
     heads_in_loop = 1;
   }
-  const int n_iter = y_n64 * heads_in_loop;
+  int n_iter = y_n64 * heads_in_loop;
   const int hkv = DKV ? head : head / group;
+  // Block-sparse routing: the (64-row block, head) pairs come from a list instead of a range.
+  const bool sparse = args.sp.it_list != nullptr;
+  const int* it_list = nullptr;
+  if (sparse) {
+    const int base = args.sp.it_off[blockIdx.x];
+    n_iter = args.sp.it_off[blockIdx.x + 1] - base;
+    it_list = args.sp.it_list + base;
+  }
+  // iteration -> (64-row block of the streamed operand, query head)
+  auto y_block = [&](int it) -> int { return sparse ? (__ldg(it_list + it) & 0xffffff) : y_lo64 + it % y_n64; };
+  auto y_head = [&](int it) -> int {
+    if (!DKV) return head;
+    return hkv * group + (sparse ? (__ldg(it_list + it) >> 24) : it / y_n64);
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(x_full, 1);
@@ -153,8 +167,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const CUtensorMap* my2 = DKV ? &map_do : &map_v;
       uint32_t stage = 0, phase = 0;
       for (int it = 0; it < n_iter; ++it) {
-        const int yh = DKV ? (hkv * group + it / y_n64) : hkv;
-        const int y0 = (y_lo64 + it % y_n64) * 64;
+        const int yh = DKV ? y_head(it) : hkv;
+        const int y0 = y_block(it) * 64;
         if (!mbar_wait(&y_empty[stage], phase ^ 1u, abort_flag, st, SITE_B_PROD, budget)) break;
         mbar_expect_tx(&y_full[stage], 2 * L::YT);
         uint8_t* dst = smem + L::OFF_Y + stage * 2 * L::YT;
@@ -242,6 +256,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const float LOG2E = 1.4426950408889634f;
     int row_seg = args.seg[b * args.S + xi];
     int row_lim = xi;
+    const int row_start = sparse ? args.sp.doc_start[b * args.S + xi] : 0;
+    // DKV: the document-relative block of this key is the bit every query column is tested for
+    const int row_blk = (sparse && DKV) ? (xi - row_start) / args.sp.block : 0;
     float row_lse2 = 0.f, row_delta = 0.f;
     if (!DKV) {
       if (args.lim != nullptr) row_lim = args.lim[b * args.S + xi];
@@ -252,9 +269,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     uint32_t sph = 0, dph = 0;
     int uses = 0;
     for (int it = u; it < n_iter; it += 2, ++uses) {
-      const int yb = y_lo64 + it % y_n64;
+      const int yb = y_block(it);
       const int y0 = yb * 64;
-      const int hq = DKV ? (hkv * group + it / y_n64) : head;
+      const int hq = y_head(it);
       if (!mbar_wait(&s_full[u], sph, abort_flag, st, SITE_B_CW_S, budget)) {
         ok = false;
         break;
@@ -280,6 +297,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       } else {
         none = (row_seg == 0) || (row_seg < cmin) || (row_seg > cmax) || (y0 > row_lim);
         all = (row_seg != 0) && (cmin == row_seg) && (cmax == row_seg) && (y0 + 63 <= row_lim);
+      }
+      int bound = 0x7fffffff;
+      bool v0 = true, v1 = true;
+      const unsigned* col_sel = nullptr;
+      if (sparse && !none) {
+        if (DKV) {
+          all = false;
+          if ((row_blk >> 5) >= args.sp.words) none = true;
+          col_sel = args.sp.sel + ((static_cast<size_t>(b) * args.Hq + hq) * args.S + y0) * args.sp.words + (row_blk >> 5);
+        } else {
+          const SparseRow sr = sparse_row(args.sp, b, head, args.Hq, args.S, xi, row_start, y0, 64);
+          bound = sr.bound; v0 = sr.v0; v1 = sr.v1;
+          none = !v0 && !v1;
+          all = all && v0 && v1;
+        }
       }
       const int* col_seg = args.seg + b * args.S + y0;
       const int* col_lim = (args.lim != nullptr) ? args.lim + b * args.S + y0 : nullptr;
@@ -322,11 +354,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                 vis[1] = (sg.y == row_seg) && (xi <= lm.y);
                 vis[2] = (sg.z == row_seg) && (xi <= lm.z);
                 vis[3] = (sg.w == row_seg) && (xi <= lm.w);
+                if (col_sel != nullptr) {
+                  const unsigned* cs = col_sel + static_cast<size_t>(c * 32 + e4 * 4) * args.sp.words;
+                  const int bit = row_blk & 31;
+#pragma unroll
+                  for (int q4 = 0; q4 < 4; ++q4)
+                    vis[q4] = vis[q4] && ((__ldg(cs + static_cast<size_t>(q4) * args.sp.words) >> bit) & 1u);
+                }
               } else {
-                vis[0] = (sg.x == row_seg) && (col0 + 0 <= row_lim);
-                vis[1] = (sg.y == row_seg) && (col0 + 1 <= row_lim);
-                vis[2] = (sg.z == row_seg) && (col0 + 2 <= row_lim);
-                vis[3] = (sg.w == row_seg) && (col0 + 3 <= row_lim);
+                vis[0] = (sg.x == row_seg) && (col0 + 0 <= row_lim) && (col0 + 0 < bound ? v0 : v1);
+                vis[1] = (sg.y == row_seg) && (col0 + 1 <= row_lim) && (col0 + 1 < bound ? v0 : v1);
+                vis[2] = (sg.z == row_seg) && (col0 + 2 <= row_lim) && (col0 + 2 < bound ? v0 : v1);
+                vis[3] = (sg.w == row_seg) && (col0 + 3 <= row_lim) && (col0 + 3 < bound ? v0 : v1);
               }
             }
 #pragma unroll
@@ -439,6 +478,7 @@ int launch_bwd(const BwdCall& c) {
   a.seg = c.seg; a.lim = c.lim; a.kv_lo = c.kv_lo; a.kv_hi = c.kv_hi; a.q_lo = c.q_lo; a.q_hi = c.q_hi;
   a.seg_min64 = c.seg_min64; a.seg_max64 = c.seg_max64; a.lim_min64 = c.lim_min64; a.lim_max64 = c.lim_max64;
   a.lse = c.lse; a.delta = c.delta;
+  a.sp = c.sp;
   a.status = device_status();
   a.spin_budget = c.spin_budget > 0 ? c.spin_budget : CTB_SPIN_BUDGET;
   auto kern = attn_bwd_kernel<D, MODE>;
@@ -476,6 +516,37 @@ CTB_API int ctb_attn_bwd(int mode, const void* q, const void* k, const void* v, 
   c.q_row_stride = q_rs; c.k_row_stride = k_rs; c.v_row_stride = v_rs; c.do_row_stride = do_rs;
   c.dq_row_stride = dq_rs; c.dk_row_stride = dk_rs; c.dv_row_stride = dv_rs;
   c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
+  using namespace ctb::attn;
+  if (D == 128) return mode == 0 ? launch_bwd<128, MODE_DKV>(c) : launch_bwd<128, MODE_DQ>(c);
+  if (D == 64) return mode == 0 ? launch_bwd<64, MODE_DKV>(c) : launch_bwd<64, MODE_DQ>(c);
+  return ctb::fail("attention: head_dim must be 64 or 128");
+}
+
+// Block-sparse (MoBA) backward: `it_off` has one entry per CTA plus one, in grid order
+// (mode 0: (key tile ascending, batch, kv head); mode 1: (query tile descending, batch, head));
+// `it_list` holds 64-row block indices, with the head's index inside its GQA group in bits 24+
+// for mode 0.
+CTB_API int ctb_attn_bwd_sparse(int mode, const void* q, const void* k, const void* v, const void* dout, void* dq,
+                                void* dk, void* dv, const float* lse, const float* delta, const int* seg,
+                                const int* lim, const int* kv_lo, const int* kv_hi, const int* q_lo, const int* q_hi,
+                                const int* seg_min64, const int* seg_max64, const int* lim_min64,
+                                const int* lim_max64, const int* it_off, const int* it_list, const unsigned* sel,
+                                const int* doc_start, int block, int words, int B, int S, int Hq, int Hkv, int D,
+                                long q_rs, long k_rs, long v_rs, long do_rs, long dq_rs, long dk_rs, long dv_rs,
+                                float scale, long long spin_budget, void* stream) {
+  if (S % 128) return ctb::fail("attention: sequence length must be a multiple of 128");
+  if (Hq % Hkv) return ctb::fail("attention: Hq must be a multiple of Hkv");
+  if (block < 128) return ctb::fail("sparse attention: the routing block must hold at least 128 tokens");
+  ctb::attn::BwdCall c{};
+  c.q = q; c.k = k; c.v = v; c.dout = dout; c.dq = dq; c.dk = dk; c.dv = dv; c.lse = lse; c.delta = delta;
+  c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi; c.q_lo = q_lo; c.q_hi = q_hi;
+  c.seg_min64 = seg_min64; c.seg_max64 = seg_max64; c.lim_min64 = lim_min64; c.lim_max64 = lim_max64;
+  c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
+  c.q_row_stride = q_rs; c.k_row_stride = k_rs; c.v_row_stride = v_rs; c.do_row_stride = do_rs;
+  c.dq_row_stride = dq_rs; c.dk_row_stride = dk_rs; c.dv_row_stride = dv_rs;
+  c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
+  c.sp.it_off = it_off; c.sp.it_list = it_list; c.sp.sel = sel; c.sp.doc_start = doc_start;
+  c.sp.block = block; c.sp.words = words;
   using namespace ctb::attn;
   if (D == 128) return mode == 0 ? launch_bwd<128, MODE_DKV>(c) : launch_bwd<128, MODE_DQ>(c);
   if (D == 64) return mode == 0 ? launch_bwd<64, MODE_DKV>(c) : launch_bwd<64, MODE_DQ>(c);

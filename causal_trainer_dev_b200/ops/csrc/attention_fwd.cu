@@ -104,9 +104,22 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   if (hi_t[0] > lo_t[0] && hi_t[1] > lo_t[1]) lo = min(lo_t[0], lo_t[1]);
   else if (hi_t[0] > lo_t[0]) lo = lo_t[0];
   else if (hi_t[1] > lo_t[1]) lo = lo_t[1];
-  const int n0 = (hi_t[0] > lo_t[0]) ? hi_t[0] - lo : 0;
-  const int n1 = (hi_t[1] > lo_t[1]) ? hi_t[1] - lo : 0;
+  int n0 = (hi_t[0] > lo_t[0]) ? hi_t[0] - lo : 0;
+  int n1 = (hi_t[1] > lo_t[1]) ? hi_t[1] - lo : 0;
+  // Block-sparse routing: both query tiles walk the listed key tiles (rows that selected nothing in
+  // a tile see it fully masked).
+  const bool sparse = args.sp.it_list != nullptr;
+  const int* kv_list = nullptr;
+  if (sparse) {
+    const int item = blockIdx.x;
+    const int base = args.sp.it_off[item];
+    const int cnt = args.sp.it_off[item + 1] - base;
+    kv_list = args.sp.it_list + base;
+    n0 = tile_valid[0] ? cnt : 0;
+    n1 = tile_valid[1] ? cnt : 0;
+  }
   const int nmax = max(n0, n1);
+  auto kv_tile = [&](int i) -> int { return sparse ? __ldg(kv_list + i) : lo + i; };
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -150,7 +163,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       uint32_t slot = 0, phase = 0;
       bool ok = true;
       for (int i = 0; ok && i < nmax; ++i) {
-        const int k0 = (lo + i) * 128;
+        const int k0 = kv_tile(i) * 128;
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
           if (!mbar_wait(&kv_empty[slot], phase ^ 1u, abort_flag, st, SITE_F_PROD, budget)) {
@@ -248,14 +261,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     bool ok = true;
     float m_ref = -INFINITY, l_sum = 0.f;
     const int qi = q0 + t * 128 + r;
-    int my_seg = 0, my_lim = qi;
+    int my_seg = 0, my_lim = qi, my_start = 0;
     if (tile_valid[t]) {
       my_seg = args.seg[b * args.S + qi];
       if (args.lim != nullptr) my_lim = args.lim[b * args.S + qi];
+      if (sparse) my_start = args.sp.doc_start[b * args.S + qi];
     }
     uint32_t sph = 0, dph = 0;
     for (int i = 0; i < n_mine; ++i) {
-      const int j = lo + i;
+      const int j = kv_tile(i);
       const int k0 = j * 128;
       if (!mbar_wait(&s_full[t], sph, abort_flag, st, SITE_F_SM_S, budget)) {
         ok = false;
@@ -266,8 +280,16 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // ---- visibility class of this row for this key block ----
       const int bmin = args.kmin[b * nqb + j];
       const int bmax = args.kmax[b * nqb + j];
-      const bool none = (my_seg == 0) || (my_seg < bmin) || (my_seg > bmax) || (k0 > my_lim);
-      const bool all = (my_seg != 0) && (bmin == my_seg) && (bmax == my_seg) && (k0 + 127 <= my_lim);
+      bool none = (my_seg == 0) || (my_seg < bmin) || (my_seg > bmax) || (k0 > my_lim);
+      bool all = (my_seg != 0) && (bmin == my_seg) && (bmax == my_seg) && (k0 + 127 <= my_lim);
+      int bound = 0x7fffffff;     // keys below it need v0, keys from it on need v1
+      bool v0 = true, v1 = true;
+      if (sparse && !none) {
+        const SparseRow sr = sparse_row(args.sp, b, h, args.Hq, args.S, qi, my_start, k0, 128);
+        bound = sr.bound; v0 = sr.v0; v1 = sr.v1;
+        none = !v0 && !v1;
+        all = all && v0 && v1;
+      }
       const int4* sp = reinterpret_cast<const int4*>(args.seg + b * args.S + k0);
       // Scales 32 scores of chunk c and applies the mask (-inf where the key is hidden).
       auto load_chunk = [&](int c, float (&x)[32]) {
@@ -285,10 +307,10 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
             for (int e4 = 0; e4 < 8; ++e4) {
               const int4 sk = __ldg(sp + c * 8 + e4);
               const int kk = k0 + c * 32 + e4 * 4;
-              if (!(sk.x == my_seg && kk + 0 <= my_lim)) x[e4 * 4 + 0] = -INFINITY;
-              if (!(sk.y == my_seg && kk + 1 <= my_lim)) x[e4 * 4 + 1] = -INFINITY;
-              if (!(sk.z == my_seg && kk + 2 <= my_lim)) x[e4 * 4 + 2] = -INFINITY;
-              if (!(sk.w == my_seg && kk + 3 <= my_lim)) x[e4 * 4 + 3] = -INFINITY;
+              if (!(sk.x == my_seg && kk + 0 <= my_lim && (kk + 0 < bound ? v0 : v1))) x[e4 * 4 + 0] = -INFINITY;
+              if (!(sk.y == my_seg && kk + 1 <= my_lim && (kk + 1 < bound ? v0 : v1))) x[e4 * 4 + 1] = -INFINITY;
+              if (!(sk.z == my_seg && kk + 2 <= my_lim && (kk + 2 < bound ? v0 : v1))) x[e4 * 4 + 2] = -INFINITY;
+              if (!(sk.w == my_seg && kk + 3 <= my_lim && (kk + 3 < bound ? v0 : v1))) x[e4 * 4 + 3] = -INFINITY;
             }
           }
         }
@@ -435,6 +457,7 @@ int launch_fwd(const FwdCall& c) {
   a.scale_log2 = c.scale * 1.4426950408889634f;
   a.seg = c.seg; a.lim = c.lim; a.kv_lo = c.kv_lo; a.kv_hi = c.kv_hi; a.kmin = c.kmin; a.kmax = c.kmax;
   a.lse = c.lse;
+  a.sp = c.sp;
   a.status = device_status();
   a.spin_budget = c.spin_budget > 0 ? c.spin_budget : CTB_SPIN_BUDGET;
   auto kern = attn_fwd_kernel<D>;
@@ -467,6 +490,29 @@ CTB_API int ctb_attn_fwd(const void* q, const void* k, const void* v, void* o, f
   c.kmin = kmin; c.kmax = kmax; c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
   c.q_row_stride = q_row_stride; c.k_row_stride = k_row_stride; c.v_row_stride = v_row_stride;
   c.o_row_stride = o_row_stride; c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
+  if (D == 128) return ctb::attn::launch_fwd<128>(c);
+  if (D == 64) return ctb::attn::launch_fwd<64>(c);
+  return ctb::fail("attention: head_dim must be 64 or 128");
+}
+
+// Block-sparse (MoBA) forward: same operands plus the routing described at SparseArgs.  `it_off`
+// has B * Hq * ceil(S / 256) + 1 entries in the order (query pair descending, batch, head) of the grid.
+CTB_API int ctb_attn_fwd_sparse(const void* q, const void* k, const void* v, void* o, float* lse, const int* seg,
+                                const int* lim, const int* kv_lo, const int* kv_hi, const int* kmin, const int* kmax,
+                                const int* it_off, const int* it_list, const unsigned* sel, const int* doc_start,
+                                int block, int words, int B, int S, int Hq, int Hkv, int D, long q_row_stride,
+                                long k_row_stride, long v_row_stride, long o_row_stride, float scale,
+                                long long spin_budget, void* stream) {
+  if (S % 128) return ctb::fail("attention: sequence length must be a multiple of 128");
+  if (Hq % Hkv) return ctb::fail("attention: Hq must be a multiple of Hkv");
+  if (block < 128) return ctb::fail("sparse attention: the routing block must hold at least 128 tokens");
+  ctb::attn::FwdCall c{};
+  c.q = q; c.k = k; c.v = v; c.o = o; c.lse = lse; c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi;
+  c.kmin = kmin; c.kmax = kmax; c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
+  c.q_row_stride = q_row_stride; c.k_row_stride = k_row_stride; c.v_row_stride = v_row_stride;
+  c.o_row_stride = o_row_stride; c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
+  c.sp.it_off = it_off; c.sp.it_list = it_list; c.sp.sel = sel; c.sp.doc_start = doc_start;
+  c.sp.block = block; c.sp.words = words;
   if (D == 128) return ctb::attn::launch_fwd<128>(c);
   if (D == 64) return ctb::attn::launch_fwd<64>(c);
   return ctb::fail("attention: head_dim must be 64 or 128");

@@ -1,0 +1,212 @@
+"""MoBA block-sparse attention on the sm_100a kernels.
+
+Pipeline of one layer (all on the GPU):
+
+1. ``ctb_moba_pool``   mean key of every complete document-relative block (fp32);
+2. ``ctb_moba_route``  per (token, query head): ``q . mean(K_block)`` over the completed blocks
+   before the query's own, top-(k-1) with ties to the earlier block, as a selection bit mask;
+3. work lists: for every CTA of the flash kernels the key tiles (forward), the 64-key blocks
+   (dQ) and the (64-query block, head) pairs (dK/dV) that at least one of its rows selected;
+4. the tcgen05 flash kernels of ``csrc/attention_fwd.cu`` / ``attention_bwd.cu`` walk those
+   lists and test the selection bits per row, so one softmax covers the union of the query's own
+   block (causal) and its selected blocks, and unselected key tiles are never loaded.
+
+The routing carries no gradient.  Semantics follow the reference's MoBA graph
+(src/causal_trainer/modeling/approximate_attention.py:29-127) whose Pallas path groups queries by
+selected block and merges per-rank partial softmaxes
+(src/causal_trainer/kernels/grouped_moba.py:25-57,75-164,177-272, moba_current_block.py:34-127);
+here the per-row bit mask makes the merge unnecessary.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+from dataclasses import dataclass
+
+import torch
+
+from . import lib as _lib
+from .attention import AttentionMeta, _row_stride
+from .elementwise import attention_delta
+
+
+@dataclass
+class MobaRouting:
+    """Selection masks and CTA work lists of one layer."""
+
+    sel: torch.Tensor          # [B,Hq,S,W] int32 bit masks of selected document-relative blocks
+    doc_start: torch.Tensor    # [B,S] int32
+    block: int
+    words: int
+    fwd_off: torch.Tensor
+    fwd_list: torch.Tensor
+    dq_off: torch.Tensor
+    dq_list: torch.Tensor
+    dkv_off: torch.Tensor
+    dkv_list: torch.Tensor
+    visited_fraction: float    # key tiles visited by the forward kernel / tiles a dense causal kernel visits
+
+
+def document_starts(seg: torch.Tensor) -> torch.Tensor:
+    """First token index of every token's document (canonical run ids; 0 for padding)."""
+    b, s = seg.shape
+    idx = torch.arange(s, device=seg.device, dtype=torch.int32).expand(b, s)
+    prev = torch.cat([torch.zeros_like(seg[:, :1]), seg[:, :-1]], dim=1)
+    first = (seg != 0) & (seg != prev)
+    return torch.cummax(torch.where(first, idx, torch.zeros_like(idx)), dim=1).values.to(torch.int32)
+
+
+def route(q: torch.Tensor, k: torch.Tensor, seg: torch.Tensor, doc_start: torch.Tensor, block: int,
+          top_k: int) -> torch.Tensor:
+    """Selection bit masks ``[B,Hq,S,W]`` (int32) from the pooling and routing kernels."""
+    b, s, hq, d = q.shape
+    hkv = k.shape[2]
+    words = max(1, -(-(-(-s // block)) // 32))
+    L = _lib.lib()
+    pooled = torch.empty((b, s // 128, hkv, d), dtype=torch.float32, device=q.device)
+    pool_start = torch.empty((b, s // 128), dtype=torch.int32, device=q.device)
+    code = L.ctb_moba_pool(_lib.ptr(k), ctypes.c_long(_row_stride(k)), _lib.ptr(seg), _lib.ptr(doc_start), b, s, hkv,
+                           d, block, _lib.ptr(pooled), _lib.ptr(pool_start), _lib.stream_ptr())
+    _lib.check(code, "ctb_moba_pool")
+    sel = torch.empty((b, hq, s, words), dtype=torch.int32, device=q.device)
+    code = L.ctb_moba_route(_lib.ptr(q), ctypes.c_long(_row_stride(q)), _lib.ptr(pooled), _lib.ptr(pool_start),
+                            _lib.ptr(seg), _lib.ptr(doc_start), b, s, hq, hkv, d, block, top_k, words, _lib.ptr(sel),
+                            _lib.stream_ptr())
+    _lib.check(code, "ctb_moba_route")
+    return sel
+
+
+def _touched_blocks(sel: torch.Tensor, seg: torch.Tensor, doc_start: torch.Tensor, block: int) -> torch.Tensor:
+    """``[B,Hq,S/64,S/64]`` bool: some row of the 64-query block selected keys inside the 64-key block."""
+    b, hq, s, words = sel.shape
+    nb = s // 64
+    dev = sel.device
+    idx = torch.arange(s, device=dev, dtype=torch.int64)
+    row = ((torch.arange(b, device=dev)[:, None, None] * hq + torch.arange(hq, device=dev)[None, :, None]) * nb
+           + (idx // 64)[None, None, :]) * (nb + 1)                                   # [B,Hq,S]
+    diff = torch.zeros(b * hq * nb * (nb + 1), dtype=torch.int32, device=dev)
+    live = (seg != 0)[:, None, :]
+    start = doc_start.to(torch.int64)
+    for c in range(min(-(-s // block), 32 * words)):
+        bit = ((sel[..., c >> 5] >> (c & 31)) & 1).bool() & live                       # [B,Hq,S]
+        lo = start + c * block                                                         # [B,S]
+        hi = torch.minimum(lo + block - 1, idx[None, :])
+        ok = bit & (lo <= idx[None, :])[:, None, :]
+        w = ok.to(torch.int32).reshape(-1)
+        diff.scatter_add_(0, (row + (lo // 64).clamp(max=nb)[:, None, :]).reshape(-1), w)
+        diff.scatter_add_(0, (row + (hi // 64 + 1).clamp(max=nb)[:, None, :]).reshape(-1), -w)
+    return diff.view(b, hq, nb, nb + 1).cumsum(-1)[..., :nb] > 0
+
+
+def _csr(table: torch.Tensor, values: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """Offsets and entries of a ``[items, candidates]`` bool table (entry = candidate index or ``values``)."""
+    counts = table.sum(-1, dtype=torch.int32)
+    off = torch.zeros(table.shape[0] + 1, dtype=torch.int32, device=table.device)
+    off[1:] = torch.cumsum(counts, 0)
+    hit = torch.nonzero(table)
+    entries = hit[:, 1] if values is None else values[hit[:, 1]]
+    if entries.numel() == 0:
+        entries = torch.zeros(1, dtype=torch.int32, device=table.device)
+    return off, entries.to(torch.int32).contiguous()
+
+
+def build_routing(q: torch.Tensor, k: torch.Tensor, meta: AttentionMeta, block: int, top_k: int) -> MobaRouting:
+    b, s, hq, _ = q.shape
+    hkv = k.shape[2]
+    g = hq // hkv
+    seg = meta.seg
+    doc_start = document_starts(seg)
+    sel = route(q, k, seg, doc_start, block, top_k)
+    touch = _touched_blocks(sel, seg, doc_start, block)                                # [B,Hq,nq64,nk64]
+    nb64, nb128 = s // 64, s // 128
+    nqp = (s + 255) // 256
+    # forward: (query pair descending, batch, head) x 128-key tiles
+    t = touch.view(b, hq, nb64, nb128, 2).any(-1)
+    if nb64 % 4:
+        t = torch.cat([t, torch.zeros((b, hq, 4 - nb64 % 4, nb128), dtype=torch.bool, device=t.device)], dim=2)
+    t = t.view(b, hq, nqp, 4, nb128).any(3)
+    fwd_off, fwd_list = _csr(t.permute(2, 0, 1, 3).flip(0).reshape(-1, nb128))
+    dense_tiles = sum(min(nb128, 2 * (p + 1)) for p in range(nqp)) * b * hq
+    visited = float(fwd_list.numel()) / max(1, dense_tiles)
+    # dQ: (query tile descending, batch, head) x 64-key blocks
+    t = touch.view(b, hq, nb128, 2, nb64).any(3)
+    dq_off, dq_list = _csr(t.permute(2, 0, 1, 3).flip(0).reshape(-1, nb64))
+    # dK/dV: (key tile ascending, batch, kv head) x (head in group, 64-query block)
+    t = touch.view(b, hkv, g, nb64, nb128, 2).any(-1).permute(4, 0, 1, 2, 3).reshape(-1, g * nb64)
+    packed = (torch.arange(g, device=t.device)[:, None] * (1 << 24) + torch.arange(nb64, device=t.device)[None, :])
+    dkv_off, dkv_list = _csr(t, packed.reshape(-1))
+    return MobaRouting(sel, doc_start, block, sel.shape[-1], fwd_off, fwd_list, dq_off, dq_list, dkv_off, dkv_list,
+                       visited)
+
+
+def moba_forward(q, k, v, meta: AttentionMeta, routing: MobaRouting, scale: float | None = None,
+                 spin_budget: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """Block-sparse forward; returns (O [B,S,Hq,D] bf16, LSE [B,Hq,S] fp32)."""
+    b, s, hq, d = q.shape
+    hkv = k.shape[2]
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    out = torch.empty((b, s, hq, d), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((b, hq, s), dtype=torch.float32, device=q.device)
+    r = routing
+    code = _lib.lib().ctb_attn_fwd_sparse(
+        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(meta.seg), _lib.ptr(meta.lim),
+        _lib.ptr(meta.kv_lo), _lib.ptr(meta.kv_hi), _lib.ptr(meta.kmin), _lib.ptr(meta.kmax),
+        _lib.ptr(r.fwd_off), _lib.ptr(r.fwd_list), _lib.ptr(r.sel), _lib.ptr(r.doc_start), r.block, r.words,
+        b, s, hq, hkv, d, ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)), ctypes.c_long(_row_stride(v)),
+        ctypes.c_long(_row_stride(out)), ctypes.c_float(scale), ctypes.c_longlong(spin_budget), _lib.stream_ptr())
+    _lib.check(code, "ctb_attn_fwd_sparse")
+    return out, lse
+
+
+def moba_backward(q, k, v, out, dout, lse, meta: AttentionMeta, routing: MobaRouting, scale: float | None = None,
+                  spin_budget: int = 0, dq=None, dk=None, dv=None):
+    """dQ and dK/dV of the block-sparse attention (same kernels as the dense backward, list-driven)."""
+    b, s, hq, d = q.shape
+    hkv = k.shape[2]
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    delta = attention_delta(out, dout)
+    dq = torch.empty((b, s, hq, d), dtype=torch.bfloat16, device=q.device) if dq is None else dq
+    dk = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dk is None else dk
+    dv = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dv is None else dv
+    r = routing
+    L = _lib.lib()
+    for mode, off, lst in ((0, r.dkv_off, r.dkv_list), (1, r.dq_off, r.dq_list)):
+        code = L.ctb_attn_bwd_sparse(
+            mode, _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
+            _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(meta.seg), _lib.ptr(meta.lim), _lib.ptr(meta.kv_lo),
+            _lib.ptr(meta.kv_hi), _lib.ptr(meta.q_lo), _lib.ptr(meta.q_hi), _lib.ptr(meta.seg_min64),
+            _lib.ptr(meta.seg_max64), _lib.ptr(meta.lim_min64), _lib.ptr(meta.lim_max64),
+            _lib.ptr(off), _lib.ptr(lst), _lib.ptr(r.sel), _lib.ptr(r.doc_start), r.block, r.words,
+            b, s, hq, hkv, d,
+            ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)), ctypes.c_long(_row_stride(v)),
+            ctypes.c_long(_row_stride(dout)), ctypes.c_long(_row_stride(dq)), ctypes.c_long(_row_stride(dk)),
+            ctypes.c_long(_row_stride(dv)), ctypes.c_float(scale), ctypes.c_longlong(spin_budget), _lib.stream_ptr())
+        _lib.check(code, "ctb_attn_bwd_sparse")
+    return dq, dk, dv
+
+
+class _MobaFlash(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, q, k, v, meta, block, top_k, scale):
+        routing = build_routing(q, k, meta, block, top_k)
+        out, lse = moba_forward(q, k, v, meta, routing, scale)
+        ctx.save_for_backward(q, k, v, out, lse)
+        ctx.meta, ctx.routing, ctx.scale = meta, routing, scale
+        return out
+
+    @staticmethod
+    def backward(ctx, dout):
+        q, k, v, out, lse = ctx.saved_tensors
+        dq, dk, dv = moba_backward(q, k, v, out, dout.contiguous(), lse, ctx.meta, ctx.routing, ctx.scale)
+        return dq, dk, dv, None, None, None, None
+
+
+def moba_flash_attention(q, k, v, segments, block: int, top_k: int, scale: float, meta: AttentionMeta | None = None):
+    """Differentiable MoBA attention for ``[B,S,H,D]`` bf16 CUDA tensors (``S`` a multiple of 128)."""
+    if block < 128:
+        raise ValueError("the sm_100a MoBA kernels need moba_block_size >= 128")
+    if meta is None:
+        from .attention import build_attention_meta
+
+        meta = build_attention_meta(segments.to(torch.int32), None)
+    return _MobaFlash.apply(q, k, v, meta, block, top_k, scale)
