@@ -44,6 +44,8 @@ def parse() -> argparse.Namespace:
     p.add_argument("--global-batch", type=int, default=32)
     p.add_argument("--micro-batch", type=int, default=4)
     p.add_argument("--remat", choices=("auto", "full", "none"), default="auto")
+    p.add_argument("--tp", type=int, default=1, help="tensor-parallel degree inside the N GPUs (the rest is FSDP); "
+                                                     "1 is the headline configuration")
     return p.parse_args()
 
 
@@ -147,16 +149,18 @@ def main() -> None:
 
     overrides = {"num_hidden_layers": args.layers} if args.layers else {}
     cfg = preset(args.model, **overrides)
-    if args.global_batch % world:
-        raise SystemExit("global batch must divide by the number of GPUs")
-    rows_per_rank = args.global_batch // world
+    if world % args.tp or args.global_batch % (world // args.tp):
+        raise SystemExit("--tp must divide the GPUs, and the data ranks the global batch")
+    data_world = world // args.tp
+    data_rank = rank // args.tp
+    rows_per_rank = args.global_batch // data_world
     micro = min(args.micro_batch, rows_per_rank)
     tcfg = TrainerConfig(
         micro_batch_rows=micro,
         adamw=AdamWConfig(weight_decay=0.1, max_grad_norm=1.0),
         schedule=ScheduleConfig(learning_rate=2e-5, learning_rate_end=2e-6, scheduler="cosine", warmup_steps=2,
                                 total_steps=1000),
-        fused_collectives=(args.impl == "ours"), remat=args.remat,
+        fused_collectives=(args.impl == "ours"), remat=args.remat, tp=args.tp,
     )
     trainer = Trainer(cfg, tcfg)
 
@@ -166,7 +170,7 @@ def main() -> None:
         data = pretraining_rows(args.global_batch, args.seq_len, cfg.vocab_size, eos_token_id=int(
             cfg.eos_token_id if isinstance(cfg.eos_token_id, int) else cfg.eos_token_id[0]),
             pad_token_id=cfg.pad_token_id, median_len=600.0, sigma=1.0, min_len=32, seed=seed)
-        mine = {k: torch.from_numpy(v[rank * rows_per_rank:(rank + 1) * rows_per_rank].copy()).pin_memory()
+        mine = {k: torch.from_numpy(v[data_rank * rows_per_rank:(data_rank + 1) * rows_per_rank].copy()).pin_memory()
                 for k, v in data.items()}
         pool.append(mine)
     tokens_per_step = args.global_batch * args.seq_len
@@ -232,7 +236,8 @@ def main() -> None:
             "random-init N(0,0.02) weights)", "impl": args.impl,
             "config": {
                 "model": args.model + (f"-{args.layers}layers" if args.layers else ""), "global_batch": args.global_batch,
-                "seq_len": args.seq_len, "parallelism": f"fsdp{world}", "micro_batch_rows": micro,
+                "seq_len": args.seq_len, "parallelism": f"fsdp{data_world}" + (f"xtp{args.tp}" if args.tp > 1 else ""),
+                "micro_batch_rows": micro,
                 "grad_accumulation": rows_per_rank // micro, "loss": "cut cross-entropy",
                 "remat": f"auto: activations of {trainer.engine.kept_layers}/{cfg.num_hidden_layers} layers kept in "
                          "HBM, the rest recomputed per layer",

@@ -461,6 +461,7 @@ class FsdpStep:
 
     def run(self, micro_batches: list[dict[str, torch.Tensor]], lr_position: int | None = None) -> StepMetrics:
         rt = self.rt
+        self.engine.options.optimizer_step = rt.count      # MoBA's dense_after_step switch
         total = None
         for b in micro_batches:
             _, w = losses.aligned_targets_and_weights(b)

@@ -37,7 +37,7 @@ from ..ops.gemm import FlagSource, gemm, gemm_push, register_flag_source
 
 N_RING = 8             # symmetric gathered buffers in rotation
 N_RECV = 2             # receive buffers of the reduce-scatter in rotation
-PULL_CTAS = 32
+PULL_CTAS = 64
 REDUCE_CTAS = 148
 
 

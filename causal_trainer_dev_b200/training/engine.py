@@ -102,6 +102,34 @@ class LayerwiseEngine:
             gview.copy_(s.to(gview.dtype))
         self._count(2)
 
+    # ------------------------------------------------------------------ attention (dense or MoBA)
+    def _uses_moba(self, li: int, seq: int) -> bool:
+        ao = self.options.attention_options
+        if ao is None or not ao.applies_to_layer(li, self.cfg.num_hidden_layers, self.options.optimizer_step):
+            return False
+        return ao.moba_top_k * min(ao.moba_block_size, seq) < seq     # otherwise the graph is exactly dense
+
+    def _attention_forward(self, q, k, v, ctx: dict, li: int):
+        """Returns (O, LSE, routing); routing is None for dense layers."""
+        if not self._uses_moba(li, ctx["seq"]):
+            o, lse = attn_ops.flash_attention_forward(q, k, v, ctx["meta"])
+            return o, lse, None
+        from ..ops import moba as moba_ops
+
+        ao = self.options.attention_options
+        routing = moba_ops.build_routing(q, k, ctx["meta"], min(ao.moba_block_size, ctx["seq"]), ao.moba_top_k)
+        o, lse = moba_ops.moba_forward(q, k, v, ctx["meta"], routing)
+        self._count(40)
+        return o, lse, routing
+
+    def _attention_backward(self, q, k, v, o, do, lse, routing, ctx: dict, dq, dk, dv) -> None:
+        if routing is None:
+            attn_ops.flash_attention_backward(q, k, v, o, do, lse, ctx["meta"], dq=dq, dk=dk, dv=dv)
+        else:
+            from ..ops import moba as moba_ops
+
+            moba_ops.moba_backward(q, k, v, o, do, lse, ctx["meta"], routing, dq=dq, dk=dk, dv=dv)
+
     # ------------------------------------------------------------------ layer forward
     def _layer_forward(self, w: dict[str, torch.Tensor], resid: torch.Tensor, branch: torch.Tensor | None, ctx: dict,
                        li: int, save: str | None) -> tuple[torch.Tensor, torch.Tensor, dict | None]:
@@ -116,7 +144,7 @@ class LayerwiseEngine:
         q = qkv[:, :qw].view(b, s, cfg.num_attention_heads, d_head)
         k = qkv[:, qw:qw + kvw].view(b, s, cfg.num_key_value_heads, d_head)
         v = qkv[:, qw + kvw:].view(b, s, cfg.num_key_value_heads, d_head)
-        o, lse = attn_ops.flash_attention_forward(q, k, v, ctx["meta"])
+        o, lse, routing = self._attention_forward(q, k, v, ctx, li)
         attn_out = gemm(o.view(t, qw), w["o_w"])
         n2, rstd2, h = ew.rmsnorm_forward(x, w["ln2"], cfg.rms_norm_eps, residual=attn_out)
         gu = gemm(n2, w["gu_w"])
@@ -125,9 +153,10 @@ class LayerwiseEngine:
         self._count(10)
         saved = None
         if save == "all":      # transient: consumed by the backward pass that follows at once
-            saved = dict(x=x, n1=n1, rstd1=rstd1, qkv=qkv, o=o, lse=lse, h=h, n2=n2, rstd2=rstd2, gu=gu, act=act)
+            saved = dict(x=x, n1=n1, rstd1=rstd1, qkv=qkv, o=o, lse=lse, h=h, n2=n2, rstd2=rstd2, gu=gu, act=act,
+                         routing=routing)
         elif save == "keep":   # kept from the forward pass: the three cheap tensors are rebuilt in backward
-            saved = dict(x=x, rstd1=rstd1, qkv=qkv, o=o, lse=lse, h=h, rstd2=rstd2, gu=gu)
+            saved = dict(x=x, rstd1=rstd1, qkv=qkv, o=o, lse=lse, h=h, rstd2=rstd2, gu=gu, routing=routing)
         return h, mlp, saved
 
     # ------------------------------------------------------------------ layer backward
@@ -167,8 +196,8 @@ class LayerwiseEngine:
         dq = dqkv[:, :qw].view(b, s, cfg.num_attention_heads, d_head)
         dk = dqkv[:, qw:qw + kvw].view(b, s, cfg.num_key_value_heads, d_head)
         dv = dqkv[:, qw + kvw:].view(b, s, cfg.num_key_value_heads, d_head)
-        attn_ops.flash_attention_backward(q, k, v, sv["o"], do.view(b, s, cfg.num_attention_heads, d_head), sv["lse"],
-                                          ctx["meta"], dq=dq, dk=dk, dv=dv)
+        self._attention_backward(q, k, v, sv["o"], do.view(b, s, cfg.num_attention_heads, d_head), sv["lse"],
+                                 sv.get("routing"), ctx, dq, dk, dv)
         ew.rope_inplace(dqkv, ctx["cos"], ctx["sin"], cfg.num_attention_heads + cfg.num_key_value_heads, d_head,
                         cfg.rotary_dim, cfg.rope_style, inverse=True)
         dn1 = gemm(dqkv, w["qkv_w"], b_mn=True)

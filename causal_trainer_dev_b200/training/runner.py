@@ -225,7 +225,7 @@ class TrainingRun:
         self.param_dtype = torch.bfloat16 if args.param_dtype == "bfloat16" else torch.float32
         self.use_engine = (self.cuda and self.param_dtype == torch.bfloat16 and args.dtype == "bfloat16"
                            and args.attn_mechanism != "vanilla" and not args.lora and args.loss_implementation != "xla"
-                           and args.attention_options is None)
+                           and (args.attention_options is None or args.attention_options.backend != "reference"))
         if self.lattice.size("sp") > 1:
             raise NotImplementedError("the sp axis must be 1: long sequences are sharded by token rows over tp")
         if self.lattice.size("tp") > 1 and not self.use_engine:
@@ -365,7 +365,7 @@ class TrainingRun:
             tcfg = TrainerConfig(micro_batch_rows=a.micro_batch_rows or a.total_batch_size // data_ranks, adamw=adamw,
                                  schedule=schedule, seed=a.seed, fused_collectives=a.fused_collectives,
                                  cut_chunk_rows=a.cut_chunk_size or 4096, tp=tp)
-            options = EngineOptions(cut_chunk_rows=tcfg.cut_chunk_rows)
+            options = EngineOptions(cut_chunk_rows=tcfg.cut_chunk_rows, attention_options=a.attention_options)
             # parameters, gradients and optimizer state are sharded over dp x fsdp (a dp replica
             # would only cost memory); tensor-parallel ranks hold slices of every projection
             data_group = self.lattice.group(("dp", "fsdp"))
@@ -401,7 +401,7 @@ class TrainingRun:
                 grad_dtype = torch.float32 if a.gradient_accumulation_steps > 1 else torch.bfloat16
                 producer = LayerwiseEngine(self.cfg, LocalProvider(self.params, grad_dtype), EngineOptions(
                     cut_chunk_rows=a.cut_chunk_size or 4096, train_lm_head="lm_head" not in frozen,
-                    train_embed="embed" not in frozen))
+                    train_embed="embed" not in frozen, attention_options=a.attention_options))
                 self.step_fn = TrainStep(self.params, producer, adamw, schedule, frozen=frozen)
             else:
                 opts = ForwardOptions(

@@ -143,6 +143,9 @@ class TrainStep:
         denom = torch.clamp(total, min=1.0)
         scale = float(1.0 / denom)
         nll_sum = None
+        options = getattr(self.producer, "options", None)
+        if options is not None and hasattr(options, "optimizer_step"):
+            options.optimizer_step = self.optimizer_step      # MoBA's dense_after_step switch
         for i, batch in enumerate(micro_batches):
             nll, _ = self.producer(batch, scale, i == 0)
             nll_sum = nll if nll_sum is None else nll_sum + nll

@@ -77,7 +77,7 @@ class TpLayerwiseEngine(LayerwiseEngine):
         q = qkv[:, :qw].view(b, s, cfg.num_attention_heads, d_head)
         k = qkv[:, qw:qw + kvw].view(b, s, cfg.num_key_value_heads, d_head)
         v = qkv[:, qw + kvw:].view(b, s, cfg.num_key_value_heads, d_head)
-        o, lse = attn_ops.flash_attention_forward(q, k, v, ctx["meta"])
+        o, lse, routing = self._attention_forward(q, k, v, ctx, li)
         attn_out = tp.gemm_reduce_scatter(o.view(t, qw), w["o_w"])
         g2 = tp.next_slot()
         _, rstd2, h = ew.rmsnorm_forward(x, w["ln2"], cfg.rms_norm_eps, residual=attn_out, out=g2.mine)
@@ -88,9 +88,9 @@ class TpLayerwiseEngine(LayerwiseEngine):
         self._count(16)
         saved = None
         if save == "all":
-            saved = dict(x=x, rstd1=rstd1, qkv=qkv, o=o, lse=lse, h=h, rstd2=rstd2, gu=gu, act=act)
+            saved = dict(x=x, rstd1=rstd1, qkv=qkv, o=o, lse=lse, h=h, rstd2=rstd2, gu=gu, act=act, routing=routing)
         elif save == "keep":
-            saved = dict(x=x, rstd1=rstd1, qkv=qkv, o=o, lse=lse, h=h, rstd2=rstd2, gu=gu)
+            saved = dict(x=x, rstd1=rstd1, qkv=qkv, o=o, lse=lse, h=h, rstd2=rstd2, gu=gu, routing=routing)
         return h, mlp, saved
 
     # ------------------------------------------------------------------ layer backward
@@ -133,8 +133,8 @@ class TpLayerwiseEngine(LayerwiseEngine):
         dq = dqkv[:, :qw].view(b, s, cfg.num_attention_heads, d_head)
         dk = dqkv[:, qw:qw + kvw].view(b, s, cfg.num_key_value_heads, d_head)
         dv = dqkv[:, qw + kvw:].view(b, s, cfg.num_key_value_heads, d_head)
-        attn_ops.flash_attention_backward(q, k, v, sv["o"], do.view(b, s, cfg.num_attention_heads, d_head), sv["lse"],
-                                          ctx["meta"], dq=dq, dk=dk, dv=dv)
+        self._attention_backward(q, k, v, sv["o"], do.view(b, s, cfg.num_attention_heads, d_head), sv["lse"],
+                                 sv.get("routing"), ctx, dq, dk, dv)
         ew.rope_inplace(dqkv, ctx["cos"], ctx["sin"], cfg.num_attention_heads + cfg.num_key_value_heads, d_head,
                         cfg.rotary_dim, cfg.rope_style, inverse=True)
         n1 = self._regather_norm(tp, sv["x"], w["ln1"])

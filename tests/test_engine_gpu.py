@@ -75,3 +75,34 @@ def test_engine_training_reduces_loss(cuda_lib):
     assert abs(first["loss"] - 8.3178) < 0.1  # ln(4096)
     assert last["loss"] < first["loss"] - 1.0
     assert engine.launches > 0
+
+
+def test_engine_with_moba_layers_matches_oracle(cuda_lib):
+    """MoBA layers in the engine (native routing + block-sparse kernels) against autograd through the
+    oracle decoder with the reference MoBA operator; routing near-ties may differ, so the bound is loose."""
+    from causal_trainer_dev_b200.models.config import preset
+    from causal_trainer_dev_b200.models.decoder import ForwardOptions
+    from causal_trainer_dev_b200.models.moba import AttentionOptions
+    from causal_trainer_dev_b200.models.params import ModelParams
+    from causal_trainer_dev_b200.training.engine import EngineOptions, LayerwiseEngine, LocalProvider
+    from causal_trainer_dev_b200.training.steps import AutogradProducer
+
+    cfg = preset("tiny", vocab_size=4096)
+    ao = AttentionOptions(method="moba", moba_block_size=128, moba_top_k=2, dense_prefix_layers=1)
+    base = ModelParams.init_random(cfg, seed=2, dtype=torch.bfloat16)
+    batch = _batch(cfg, 2, 1024)
+    ref = ModelParams(cfg, dtype=torch.float32, device="cuda")
+    ref.load_state_dict({k: v.float() for k, v in base.state_dict().items()})
+    opts = ForwardOptions(attn_mechanism="vanilla", attention_options=AttentionOptions(
+        method="moba", backend="reference", moba_block_size=128, moba_top_k=2, dense_prefix_layers=1))
+    nll_ref, _ = AutogradProducer(ref, opts)(batch, 1.0 / 1500, True)
+    eng_params = ModelParams(cfg, dtype=torch.bfloat16, device="cuda")
+    eng_params.load_state_dict(base.state_dict())
+    engine = LayerwiseEngine(cfg, LocalProvider(eng_params, torch.float32), EngineOptions(attention_options=ao))
+    nll, _ = engine(batch, 1.0 / 1500, True)
+    assert engine._uses_moba(1, 1024) and not engine._uses_moba(0, 1024)
+    assert abs(nll.item() - nll_ref.item()) / nll_ref.item() < 5e-3
+    for name in ("model.layers.1.self_attn.q_proj.weight", "model.layers.1.self_attn.v_proj.weight",
+                 "model.layers.0.mlp.down_proj.weight", "lm_head.weight"):
+        assert _rel(eng_params.grad_tensor(name), ref.grad_tensor(name)) < 0.1, name
+    assert cuda_lib.device_status() == (0, 0, 0, 0)
