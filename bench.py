@@ -35,8 +35,9 @@ def parse() -> argparse.Namespace:
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=3)
     p.add_argument("--warmup", type=int, default=3)
-    p.add_argument("--impl", choices=("ours", "reference", "nccl"), default="ours",
+    p.add_argument("--impl", choices=("ours", "reference", "nccl", "torch"), default="ours",
                    help="ours: fused in-kernel collectives; nccl: same engine with NCCL-only collectives; "
+                        "torch: stock PyTorch (cuBLAS, SDPA, autograd, FSDP2 over NCCL), none of our kernels; "
                         "reference: the unmodified reference trainer")
     p.add_argument("--model", default="llama3-8b")
     p.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; invalid as a result)")
@@ -162,7 +163,12 @@ def main() -> None:
                                 total_steps=1000),
         fused_collectives=(args.impl == "ours"), remat=args.remat, tp=args.tp,
     )
-    trainer = Trainer(cfg, tcfg)
+    if args.impl == "torch":
+        from causal_trainer_dev_b200.benchmarks.torch_baseline import TorchBaseline
+
+        trainer = TorchBaseline(cfg, micro)
+    else:
+        trainer = Trainer(cfg, tcfg)
 
     # Two distinct global batches, identical on every rank; each rank keeps its rows (pinned).
     pool = []
@@ -187,7 +193,8 @@ def main() -> None:
     # ---------------- device-timed region ----------------
     dev_batches = [trainer.upload(b) for b in pool]
     sync()
-    launches0 = trainer.launches()
+    ours = args.impl != "torch"
+    launches0 = trainer.launches() if ours else 0
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -200,8 +207,8 @@ def main() -> None:
     sync()
     ms = start.elapsed_time(end)
     clocks = sampler.stop() if rank == 0 else {}
-    launches = trainer.launches() - launches0
-    loss = float(metrics.loss)
+    launches = trainer.launches() - launches0 if ours else 0
+    loss = float(metrics.loss) if ours else float(metrics[0])
 
     # ---------------- end-to-end region (pinned host inputs, loss read back each step) ----------------
     h2d0, d2h0 = trainer.transfer_counters()
@@ -238,9 +245,9 @@ def main() -> None:
                 "model": args.model + (f"-{args.layers}layers" if args.layers else ""), "global_batch": args.global_batch,
                 "seq_len": args.seq_len, "parallelism": f"fsdp{data_world}" + (f"xtp{args.tp}" if args.tp > 1 else ""),
                 "micro_batch_rows": micro,
-                "grad_accumulation": rows_per_rank // micro, "loss": "cut cross-entropy",
-                "remat": f"auto: activations of {trainer.engine.kept_layers}/{cfg.num_hidden_layers} layers kept in "
-                         "HBM, the rest recomputed per layer",
+                "grad_accumulation": rows_per_rank // micro, "loss": "cut cross-entropy" if ours else "F.cross_entropy on 4096-row logit chunks",
+                "remat": (f"auto: activations of {trainer.engine.kept_layers}/{cfg.num_hidden_layers} layers kept in "
+                          "HBM, the rest recomputed per layer") if ours else "none (autograd keeps all activations)",
                 "optimizer": "AdamW, bf16 moments, global-norm clip", "l2": "inputs larger than L2 (weights + state "
                 "are tens of GB per GPU, 126 MB L2)",
             },
