@@ -57,6 +57,8 @@ struct GemmArgs {
   const float* ce_lse;
   const float* ce_coef;
   GemmPush push;
+  int* tile_counter;     // [2]: next tile to claim, CTAs that stopped claiming (dynamic_tiles only)
+  int dynamic_tiles;
 };
 
 // Host-side call description.
