@@ -45,6 +45,8 @@ def parse() -> argparse.Namespace:
     p.add_argument("--global-batch", type=int, default=32)
     p.add_argument("--micro-batch", type=int, default=4)
     p.add_argument("--remat", choices=("auto", "full", "none"), default="auto")
+    p.add_argument("--force-sharded-runtime", action="store_true",
+                   help="diagnostic: run the FSDP runtime on one GPU to measure its overhead without communication")
     p.add_argument("--tp", type=int, default=1, help="tensor-parallel degree inside the N GPUs (the rest is FSDP); "
                                                      "1 is the headline configuration")
     return p.parse_args()
@@ -137,8 +139,11 @@ def main() -> None:
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
     torch.cuda.set_device(local)
-    if world > 1:
+    if world > 1 or args.force_sharded_runtime:
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        os.environ.setdefault("MASTER_PORT", "29533")
+        os.environ.setdefault("RANK", "0")
+        os.environ.setdefault("WORLD_SIZE", "1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
@@ -162,6 +167,7 @@ def main() -> None:
         schedule=ScheduleConfig(learning_rate=2e-5, learning_rate_end=2e-6, scheduler="cosine", warmup_steps=2,
                                 total_steps=1000),
         fused_collectives=(args.impl == "ours"), remat=args.remat, tp=args.tp,
+        force_sharded_runtime=args.force_sharded_runtime,
     )
     if args.impl == "torch":
         from causal_trainer_dev_b200.benchmarks.torch_baseline import TorchBaseline
@@ -260,7 +266,7 @@ def main() -> None:
             "gpu_launches": launches,
         }
         print(json.dumps(result))
-    if world > 1:
+    if dist.is_initialized():
         dist.destroy_process_group()
 
 

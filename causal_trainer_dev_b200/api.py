@@ -35,6 +35,7 @@ class TrainerConfig:
     init: str = "normal"               # "normal": N(0, initializer_range) on the device; "hf": ModelParams.init_random
     remat: str = "auto"                # "auto": keep activations that fit, recompute the rest; "full"; "none"
     tp: int = 1                        # tensor-parallel degree; ranks are laid out (fsdp, tp) with tp fastest
+    force_sharded_runtime: bool = False  # run the FSDP runtime even on one rank (measures its own overhead)
 
 
 class Trainer:
@@ -65,7 +66,7 @@ class Trainer:
                                             EngineOptions(cut_chunk_rows=self.cfg.cut_chunk_rows, remat=self.cfg.remat),
                                             fused=self.cfg.fused_collectives)
             self.step_fn = self.runtime.make_step(self.engine)
-        elif self.world > 1 and self.cfg.fsdp:
+        elif (self.world > 1 or self.cfg.force_sharded_runtime) and self.cfg.fsdp:
             from .parallel.fsdp import FsdpRuntime
 
             self.runtime = FsdpRuntime(model, self.cfg, self.device)

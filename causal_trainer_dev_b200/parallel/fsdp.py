@@ -72,6 +72,7 @@ class _Gathered:
         self.epoch = 0
         self.pull_done = torch.cuda.Event()
         self.free_event: torch.cuda.Event | None = None   # main stream finished with the occupant
+        self.valid = True                                  # resident mode: holds the current parameters
         register_flag_source(self.source)
 
 
@@ -79,7 +80,7 @@ class FsdpRuntime:
     """Weight provider (see ``training.engine``) plus the sharded optimizer step."""
 
     def __init__(self, cfg: ModelConfig, tcfg, device: torch.device, group=None, full_cfg: ModelConfig | None = None,
-                 tp_group=None):
+                 tp_group=None, resident: str = "auto"):
         """``cfg`` describes what this rank stores: the whole model, or (with ``tp_group``) one
         tensor-parallel slice of ``full_cfg`` (see ``parallel.tp.tp_local_config``)."""
         _lib.require_gpu_lib()
@@ -156,8 +157,23 @@ class FsdpRuntime:
         self.accum: torch.Tensor | None = None
         self.sumsq = torch.zeros((len(self.units), REDUCE_CTAS * 8), dtype=torch.float32, device=device)
         self.finish_counter = torch.zeros(1, dtype=torch.int32, device=device)
-        self.gathered = [_Gathered(self.max_padded, device) for _ in range(N_GATHER)]
+        # Gathered weights: with room to spare (180 GB parts) every unit keeps its own gathered
+        # buffer for the whole optimizer step, so the forward pass of the first micro-batch is the
+        # only all-gather; otherwise three buffers rotate and every use re-gathers.
+        total_bytes = 2 * sum(u.padded for u in self.units.values())
+        free, _ = torch.cuda.mem_get_info(device)
+        self.resident = resident == "always" or (resident == "auto" and total_bytes < free // 4)
         self.where: dict[str, _Gathered] = {}
+        if self.resident:
+            self.gathered = []
+            for name, u in self.units.items():
+                g = _Gathered(u.padded, device)
+                g.unit = name
+                g.valid = False
+                self.gathered.append(g)
+                self.where[name] = g
+        else:
+            self.gathered = [_Gathered(self.max_padded, device) for _ in range(N_GATHER)]
         self.slot_of: dict[str, int] = {}
         self.slot_epoch = [0] * N_SLOTS          # epoch last published for each slot
         self.slot_counter = 0
@@ -244,9 +260,13 @@ class FsdpRuntime:
         raise RuntimeError("no gathered buffer free")
 
     def _start_pull(self, name: str, keep: set[str]) -> _Gathered:
-        g = self._pick_buffer(keep | {name})
-        if g.unit is not None:
-            self.where.pop(g.unit, None)
+        if self.resident:
+            g = self.where[name]
+            g.valid = True
+        else:
+            g = self._pick_buffer(keep | {name})
+            if g.unit is not None:
+                self.where.pop(g.unit, None)
         u = self.units[name]
         self.epoch += 1
         g.unit, g.epoch = name, self.epoch
@@ -274,12 +294,14 @@ class FsdpRuntime:
     def acquire(self, name: str, prefetch: str | None = None) -> Unit:
         keep = {name} | ({prefetch} if prefetch else set())
         g = self.where.get(name)
-        if g is None:
+        if g is None or not g.valid:
             g = self._start_pull(name, keep)
-        if prefetch is not None and prefetch not in self.where:
+        if prefetch is not None and (prefetch not in self.where or not self.where[prefetch].valid):
             self._start_pull(prefetch, keep)
         u = self.units[name]
-        if self.fused and name.startswith("layer."):
+        if g.pull_done.query():
+            pass                                # already complete (resident weights of an earlier pass)
+        elif self.fused and name.startswith("layer."):
             # vectors (norm scales, biases) are read by non-GEMM kernels: wait for their chunks only
             nvec = max(1, math.ceil(u.layout.vector_numel / CHUNK))
             code = _lib.lib().ctb_wait_flags(_lib.ptr(g.flags), 0, 1, nvec, ctypes.c_uint(g.epoch),
@@ -421,9 +443,13 @@ class FsdpRuntime:
                                 clip=clip)
         fence = torch.zeros(1, device=self.device)
         dist.all_reduce(fence, group=self.group)          # nobody pulls before every shard is updated
-        self.where.clear()
-        for g in self.gathered:
-            g.unit = None
+        if self.resident:
+            for g in self.gathered:
+                g.valid = False
+        else:
+            self.where.clear()
+            for g in self.gathered:
+                g.unit = None
         return grad_norm[0]
 
     def _replicated_index(self) -> torch.Tensor:
