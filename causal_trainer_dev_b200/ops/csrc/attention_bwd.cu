@@ -25,7 +25,7 @@
 namespace ctb {
 namespace attn {
 
-constexpr int BWD_THREADS = 384;
+constexpr int BWD_THREADS = 640;   // 4 service warps + 4 compute warpgroups
 constexpr int Y_STAGES = 3;
 
 enum : unsigned {
@@ -48,7 +48,8 @@ struct BwdSmem {
   static constexpr int OFF_Y = 2 * XT;        // stages of (Y1, Y2)
   static constexpr int OFF_T = OFF_Y + Y_STAGES * 2 * YT;  // per warpgroup: (P^T, dS)
   static constexpr int OFF_BAR = OFF_T + 2 * 2 * TT;
-  static constexpr int BYTES = OFF_BAR + 256 + 1024;
+  static constexpr int OFF_META = OFF_BAR + 256;           // per block buffer: lse*log2(e) and delta of 64 columns
+  static constexpr int BYTES = OFF_META + 1024 + 1024;
 };
 
 template <int D, int MODE>
@@ -131,7 +132,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
     for (int u = 0; u < 2; ++u) {
       mbar_init(&s_full[u], 1);
-      mbar_init(&t_full[u], 128);
+      mbar_init(&t_full[u], 256);
       mbar_init(&t_done[u], 1);
     }
     mbar_init(acc_full, 1);
@@ -246,7 +247,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
   } else if (warp >= 4) {
     // ------------------------------ compute warpgroups ------------------------------
-    const int u = (warp - 4) >> 2;
+    // Four compute warpgroups: block buffer u = wg & 1, and the two warpgroups of a buffer split
+    // its 64 columns (half = wg >> 1 takes columns [32 * half, 32 * half + 32)), so every
+    // scheduler has four compute warps to hide the TMEM and global load latencies with.
+    const int wg = (warp - 4) >> 2;
+    const int u = wg & 1;
+    const int half = wg >> 1;
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
@@ -268,23 +274,38 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     bool ok = true;
     uint32_t sph = 0, dph = 0;
     int uses = 0;
+    float* meta_l = reinterpret_cast<float*>(smem + L::OFF_META) + u * 128;
+    float* meta_d = meta_l + 64;
     for (int it = u; it < n_iter; it += 2, ++uses) {
       const int yb = y_block(it);
       const int y0 = yb * 64;
       const int hq = y_head(it);
-      if (!mbar_wait(&s_full[u], sph, abort_flag, st, SITE_B_CW_S, budget)) {
-        ok = false;
-        break;
+      // DKV: the per-query statistics of the 64 columns are fetched while S is still being
+      // computed (one value per thread of the first warpgroup of the pair) and shared below.
+      float meta_v = 0.f;
+      if (DKV && half == 0) {
+        const size_t base = (static_cast<size_t>(b) * args.Hq + hq) * args.S + y0;
+        meta_v = (r < 64) ? __ldg(args.lse + base + r) * LOG2E : __ldg(args.delta + base + r - 64);
       }
+      bool good = mbar_wait(&s_full[u], sph, abort_flag, st, SITE_B_CW_S, budget);
       sph ^= 1u;
-      if (uses > 0) {
-        if (!mbar_wait(&t_done[u], dph, abort_flag, st, SITE_B_CW_T, budget)) {
-          ok = false;
-          break;
-        }
+      if (good && uses > 0) {
+        good = mbar_wait(&t_done[u], dph, abort_flag, st, SITE_B_CW_T, budget);
         dph ^= 1u;
       }
       tc_fence_after();
+      if (DKV) {
+        // every thread of the pair reaches this barrier, also one whose wait gave up: the
+        // verdict is shared so that nobody is left waiting at it
+        if (good && half == 0) meta_l[r] = meta_v;   // r < 64: lse, r >= 64: delta (meta_d = meta_l + 64)
+        if (named_bar_or(6 + u, 256, !good)) {
+          ok = false;
+          break;
+        }
+      } else if (!good) {
+        ok = false;
+        break;
+      }
       // ---- visibility class of this row against the 64 columns ----
       const int cmin = args.seg_min64[b * nb64 + yb];
       const int cmax = args.seg_max64[b * nb64 + yb];
@@ -315,82 +336,85 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       }
       const int* col_seg = args.seg + b * args.S + y0;
       const int* col_lim = (args.lim != nullptr) ? args.lim + b * args.S + y0 : nullptr;
-      const float* col_lse = args.lse + (static_cast<size_t>(b) * args.Hq + hq) * args.S + y0;
-      const float* col_delta = args.delta + (static_cast<size_t>(b) * args.Hq + hq) * args.S + y0;
 #pragma unroll 1
-      for (int c = 0; c < 2; ++c) {
-        uint32_t rs[32], rd[32];
-        tmem_ld32(tmem_s[u] + lane_off + c * 32, rs);
-        tmem_ld32(tmem_dp[u] + lane_off + c * 32, rd);
+      for (int sub = 0; sub < 2; ++sub) {
+        const int c = half;
+        uint32_t rs[16], rd[16];
+        tmem_ld16(tmem_s[u] + lane_off + c * 32 + sub * 16, rs);
+        tmem_ld16(tmem_dp[u] + lane_off + c * 32 + sub * 16, rd);
         tmem_ld_wait();
-        float p[32], ds[32];
-        if (none) {
+        // eight columns at a time: probabilities and dS are packed and stored as soon as they
+        // exist, so only the two raw 16-column TMEM chunks stay live in registers
 #pragma unroll
-          for (int e = 0; e < 32; ++e) {
-            p[e] = 0.f;
-            ds[e] = 0.f;
-          }
-        } else {
+        for (int gg = 0; gg < 2; ++gg) {
+          const int g = sub * 2 + gg;
+          float p[8], ds[8];
+          if (none) {
 #pragma unroll
-          for (int e4 = 0; e4 < 8; ++e4) {
-            float l2[4], dl[4];
-            if (DKV) {
-              const float4 lv = __ldg(reinterpret_cast<const float4*>(col_lse) + c * 8 + e4);
-              const float4 dv = __ldg(reinterpret_cast<const float4*>(col_delta) + c * 8 + e4);
-              l2[0] = lv.x * LOG2E; l2[1] = lv.y * LOG2E; l2[2] = lv.z * LOG2E; l2[3] = lv.w * LOG2E;
-              dl[0] = dv.x; dl[1] = dv.y; dl[2] = dv.z; dl[3] = dv.w;
-            } else {
-              l2[0] = l2[1] = l2[2] = l2[3] = row_lse2;
-              dl[0] = dl[1] = dl[2] = dl[3] = row_delta;
+            for (int e = 0; e < 8; ++e) {
+              p[e] = 0.f;
+              ds[e] = 0.f;
             }
-            bool vis[4] = {true, true, true, true};
-            if (!all) {
-              const int4 sg = __ldg(reinterpret_cast<const int4*>(col_seg) + c * 8 + e4);
-              const int col0 = y0 + c * 32 + e4 * 4;
-              if (DKV) {
-                int4 lm = make_int4(col0, col0 + 1, col0 + 2, col0 + 3);
-                if (col_lim != nullptr) lm = __ldg(reinterpret_cast<const int4*>(col_lim) + c * 8 + e4);
-                vis[0] = (sg.x == row_seg) && (xi <= lm.x);
-                vis[1] = (sg.y == row_seg) && (xi <= lm.y);
-                vis[2] = (sg.z == row_seg) && (xi <= lm.z);
-                vis[3] = (sg.w == row_seg) && (xi <= lm.w);
-                if (col_sel != nullptr) {
-                  const unsigned* cs = col_sel + static_cast<size_t>(c * 32 + e4 * 4) * args.sp.words;
-                  const int bit = row_blk & 31;
+          } else {
 #pragma unroll
-                  for (int q4 = 0; q4 < 4; ++q4)
-                    vis[q4] = vis[q4] && ((__ldg(cs + static_cast<size_t>(q4) * args.sp.words) >> bit) & 1u);
-                }
+            for (int h4 = 0; h4 < 2; ++h4) {
+              const int e4 = g * 2 + h4;
+              float l2[4], dl[4];
+              if (DKV) {
+                const float4 lv = *(reinterpret_cast<const float4*>(meta_l) + c * 8 + e4);
+                const float4 dv = *(reinterpret_cast<const float4*>(meta_d) + c * 8 + e4);
+                l2[0] = lv.x; l2[1] = lv.y; l2[2] = lv.z; l2[3] = lv.w;
+                dl[0] = dv.x; dl[1] = dv.y; dl[2] = dv.z; dl[3] = dv.w;
               } else {
-                vis[0] = (sg.x == row_seg) && (col0 + 0 <= row_lim) && (col0 + 0 < bound ? v0 : v1);
-                vis[1] = (sg.y == row_seg) && (col0 + 1 <= row_lim) && (col0 + 1 < bound ? v0 : v1);
-                vis[2] = (sg.z == row_seg) && (col0 + 2 <= row_lim) && (col0 + 2 < bound ? v0 : v1);
-                vis[3] = (sg.w == row_seg) && (col0 + 3 <= row_lim) && (col0 + 3 < bound ? v0 : v1);
+                l2[0] = l2[1] = l2[2] = l2[3] = row_lse2;
+                dl[0] = dl[1] = dl[2] = dl[3] = row_delta;
+              }
+              bool vis[4] = {true, true, true, true};
+              if (!all) {
+                const int4 sg = __ldg(reinterpret_cast<const int4*>(col_seg) + c * 8 + e4);
+                const int col0 = y0 + c * 32 + e4 * 4;
+                if (DKV) {
+                  int4 lm = make_int4(col0, col0 + 1, col0 + 2, col0 + 3);
+                  if (col_lim != nullptr) lm = __ldg(reinterpret_cast<const int4*>(col_lim) + c * 8 + e4);
+                  vis[0] = (sg.x == row_seg) && (xi <= lm.x);
+                  vis[1] = (sg.y == row_seg) && (xi <= lm.y);
+                  vis[2] = (sg.z == row_seg) && (xi <= lm.z);
+                  vis[3] = (sg.w == row_seg) && (xi <= lm.w);
+                  if (col_sel != nullptr) {
+                    const unsigned* cs = col_sel + static_cast<size_t>(c * 32 + e4 * 4) * args.sp.words;
+                    const int bit = row_blk & 31;
+#pragma unroll
+                    for (int q4 = 0; q4 < 4; ++q4)
+                      vis[q4] = vis[q4] && ((__ldg(cs + static_cast<size_t>(q4) * args.sp.words) >> bit) & 1u);
+                  }
+                } else {
+                  vis[0] = (sg.x == row_seg) && (col0 + 0 <= row_lim) && (col0 + 0 < bound ? v0 : v1);
+                  vis[1] = (sg.y == row_seg) && (col0 + 1 <= row_lim) && (col0 + 1 < bound ? v0 : v1);
+                  vis[2] = (sg.z == row_seg) && (col0 + 2 <= row_lim) && (col0 + 2 < bound ? v0 : v1);
+                  vis[3] = (sg.w == row_seg) && (col0 + 3 <= row_lim) && (col0 + 3 < bound ? v0 : v1);
+                }
+              }
+#pragma unroll
+              for (int q4 = 0; q4 < 4; ++q4) {
+                const int e = gg * 8 + h4 * 4 + q4;
+                const float pe = vis[q4] ? fast_exp2(__uint_as_float(rs[e]) * args.scale_log2 - l2[q4]) : 0.f;
+                p[h4 * 4 + q4] = pe;
+                ds[h4 * 4 + q4] = pe * (__uint_as_float(rd[e]) - dl[q4]);
               }
             }
-#pragma unroll
-            for (int q4 = 0; q4 < 4; ++q4) {
-              const int e = e4 * 4 + q4;
-              const float pe = vis[q4] ? fast_exp2(__uint_as_float(rs[e]) * args.scale_log2 - l2[q4]) : 0.f;
-              p[e] = pe;
-              ds[e] = pe * (__uint_as_float(rd[e]) - dl[q4]);
-            }
           }
-        }
-#pragma unroll
-        for (int g = 0; g < 4; ++g) {
           uint4 v;
           if (DKV) {
-            v.x = pack_bf16(p[g * 8 + 0], p[g * 8 + 1]);
-            v.y = pack_bf16(p[g * 8 + 2], p[g * 8 + 3]);
-            v.z = pack_bf16(p[g * 8 + 4], p[g * 8 + 5]);
-            v.w = pack_bf16(p[g * 8 + 6], p[g * 8 + 7]);
+            v.x = pack_bf16(p[0], p[1]);
+            v.y = pack_bf16(p[2], p[3]);
+            v.z = pack_bf16(p[4], p[5]);
+            v.w = pack_bf16(p[6], p[7]);
             *reinterpret_cast<uint4*>(t_p + sw128_offset(r, c * 4 + g)) = v;
           }
-          v.x = pack_bf16(ds[g * 8 + 0], ds[g * 8 + 1]);
-          v.y = pack_bf16(ds[g * 8 + 2], ds[g * 8 + 3]);
-          v.z = pack_bf16(ds[g * 8 + 4], ds[g * 8 + 5]);
-          v.w = pack_bf16(ds[g * 8 + 6], ds[g * 8 + 7]);
+          v.x = pack_bf16(ds[0], ds[1]);
+          v.y = pack_bf16(ds[2], ds[3]);
+          v.z = pack_bf16(ds[4], ds[5]);
+          v.w = pack_bf16(ds[6], ds[7]);
           *reinterpret_cast<uint4*>(t_ds + sw128_offset(r, c * 4 + g)) = v;
         }
       }
@@ -403,15 +427,16 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       ok = mbar_wait(acc_full, 0, abort_flag, st, SITE_B_CW_ACC, budget);
       tc_fence_after();
     }
-    const bool any_bad = named_bar_or(2 + u, 128, !ok);
+    const bool any_bad = named_bar_or(2 + u, 256, !ok);
     const bool writes = DKV || (u == 0);
     if (!any_bad && writes) {
       // DKV: warpgroup 0 stores dV, warpgroup 1 stores dK (scaled); DQ: warpgroup 0 stores dQ (scaled).
       const uint32_t acc = (DKV && u == 1) ? tmem_acc2 : tmem_acc1;
       const float mul = (DKV && u == 0) ? 1.f : args.scale;
       uint8_t* stage_buf = smem + L::OFF_T + u * 2 * L::TT;  // 32 KiB: [HALVES][128 rows][128 B]
+      // the two warpgroups of the pair convert half of the head dimension each
 #pragma unroll 1
-      for (int c = 0; c < D / 32; ++c) {
+      for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
         uint32_t rr[32];
         if (n_iter > 0) {
           tmem_ld32(acc + lane_off + c * 32, rr);
@@ -431,8 +456,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         }
       }
       fence_proxy_async_smem();
-      named_bar_sync(4 + u, 128);
-      if (r == 0) {
+      named_bar_sync(4 + u, 256);
+      if (r == 0 && half == 0) {
         const CUtensorMap* mo = (DKV && u == 1) ? &map_out2 : &map_out1;
         const int oh = DKV ? hkv : head;
 #pragma unroll

@@ -31,20 +31,37 @@
 namespace ctb {
 namespace gemm {
 
-constexpr int BM = 128;
+constexpr int BM = 128;            // rows of one UMMA accumulator (one TMEM slot)
 constexpr int BN = 256;
 constexpr int BK = 64;
-constexpr int NSTAGE = 4;
-constexpr int A_STAGE = BM * BK * 2;   // 16 KiB
 constexpr int B_STAGE = BN * BK * 2;   // 32 KiB
 constexpr int EPI_BUF = 128 * 128;     // 128 rows x 128 B
-constexpr int OFF_B = NSTAGE * A_STAGE;
-constexpr int OFF_EPI = OFF_B + NSTAGE * B_STAGE;
-constexpr int OFF_BAR = OFF_EPI + 2 * EPI_BUF;
-constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;  // + barrier block + alignment slack
-constexpr int NTHREADS = 256;
-constexpr int GROUP_M = 16;
-constexpr int TQ = 4;          // depth of the tile-index queue
+constexpr int TQ = 4;                  // depth of the tile-index queue
+
+// A CTA tile is TM row sub-tiles of 128 rows that share one B tile:
+//   TM = 1: 128 x 256 tiles, 4 pipeline stages of 48 KiB, the two 256-column TMEM slots double-
+//           buffer the accumulator (the epilogue of tile i overlaps the main loop of tile i+1);
+//   TM = 2: 256 x 256 tiles, 3 stages of 64 KiB.  Each B k-block feeds two UMMAs, so a CTA reads a
+//           third fewer operand bytes per FLOP from L2 and the same 192 KiB of stages cover 1.5x
+//           as many tensor-core cycles of load latency; both TMEM slots belong to one tile and two
+//           epilogue warpgroups drain them at the tile's end.
+template <int TM>
+struct Cfg {
+  static constexpr int BMT = BM * TM;
+  static constexpr int NSTAGE = TM == 1 ? 4 : 3;
+  static constexpr int A_STAGE = BMT * BK * 2;
+  static constexpr int OFF_B = NSTAGE * A_STAGE;
+  static constexpr int OFF_EPI = OFF_B + NSTAGE * B_STAGE;
+  static constexpr int OFF_BAR = OFF_EPI + 2 * EPI_BUF;
+  static constexpr int SMEM_BYTES = OFF_BAR + 256 + 1024;  // + barrier block + alignment slack
+  static constexpr int THREADS = 128 + 128 * TM;           // 4 service warps + TM epilogue warpgroups
+  static constexpr int GROUP_M = 16 / TM;                  // tiles per band: 2048 rows either way
+  static constexpr int EPI_BUFS = 2 / TM;                  // staging buffers per epilogue warpgroup
+  // Declared thread capacity: caps registers (168 / 128 per thread) so that a 256-thread, 64-register
+  // pull or reduce CTA always fits beside a resident GEMM CTA (a GEMM that waits on flags would
+  // otherwise starve the kernel that publishes them).
+  static constexpr int BOUND = TM == 1 ? 384 : 512;
+};
 
 enum : unsigned {
   SITE_PRODUCER_EMPTY = 0x0101,
@@ -64,7 +81,9 @@ struct TileCoord {
 // slowly so the B tile stays hot in L2.  `n_rotate` shifts the column order so that a rank
 // starts on the weight rows it already owns while the all-gather pull brings the rest.
 // `m_rotate` does the same for row tiles when the A operand is being gathered.
+template <int TM>
 __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int n_rotate, int m_rotate) {
+  constexpr int GROUP_M = Cfg<TM>::GROUP_M;
   const int per_group = GROUP_M * num_n;
   const int group = tile / per_group;
   const int first_m = group * GROUP_M;
@@ -75,7 +94,7 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
   int m = first_m + local % rows + m_rotate;
   if (m >= num_m) m -= num_m;
   TileCoord c;
-  c.m0 = m * BM;
+  c.m0 = m * Cfg<TM>::BMT;
   c.n0 = n * BN;
   return c;
 }
@@ -83,7 +102,7 @@ __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, 
 // Copies a staged 128 x 128 B block (128-byte swizzle) to `out` (row stride `ld` elements) with
 // 16-byte stores: thread -> (row etid/8 + 16*i, 16-byte column etid%8), so a warp writes four
 // full 128 B rows per step.  Kept out of line so its address arithmetic does not raise the
-// register count of the whole kernel (a CTA must leave room for the pull kernels on its SM).
+// register count of the whole kernel.
 __device__ __noinline__ void push_block(const uint8_t* buf, __nv_bfloat16* out, long ld, int etid, int rows_left,
                                         int cols_left) {
   const int j = etid & 7;
@@ -98,32 +117,33 @@ __device__ __noinline__ void push_block(const uint8_t* buf, __nv_bfloat16* out, 
   }
 }
 
-// The kernel runs with NTHREADS (256) threads; declaring room for 384 caps it at 168 registers per
-// thread, which leaves a third of the register file to the small pull / reduce CTAs that must
-// share the SM with a resident GEMM CTA (a GEMM that waits on flags would otherwise starve the
-// kernel that publishes them).
-template <bool A_MN, bool B_MN, int EPI>
-__global__ void __launch_bounds__(384, 1)
+template <int TM, bool A_MN, bool B_MN, int EPI>
+__global__ void __launch_bounds__(Cfg<TM>::BOUND, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b,
             const __grid_constant__ CUtensorMap map_c, const GemmArgs args) {
+  using C = Cfg<TM>;
+  constexpr int NSTAGE = C::NSTAGE;
+  constexpr int A_STAGE = C::A_STAGE;
+  constexpr int BMT = C::BMT;
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
-  uint64_t* full = reinterpret_cast<uint64_t*>(smem + OFF_BAR);
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::OFF_BAR);
   uint64_t* empty = full + NSTAGE;
-  uint64_t* tfull = empty + NSTAGE;
-  uint64_t* tempty = tfull + 2;
-  uint64_t* tq_full = tempty + 2;        // tile queue: the producer claims tiles from a global counter
-  uint64_t* tq_empty = tq_full + TQ;     // and hands their indices to the MMA and epilogue warps
+  uint64_t* tfull = empty + NSTAGE;      // [2] TMEM slot s holds a finished accumulator
+  uint64_t* tempty = tfull + 2;          // [2] TMEM slot s has been drained
+  uint64_t* tq_full = tempty + 2;        // tile queue: the producer hands tile indices
+  uint64_t* tq_empty = tq_full + TQ;     // to the MMA and epilogue warps
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(tq_empty + TQ);
   volatile uint32_t* abort_flag = tmem_slot + 1;
   volatile int* tile_ring = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
   const int warp = threadIdx.x >> 5;
   const int lane = threadIdx.x & 31;
-  const int num_m = (args.M + BM - 1) / BM;
+  const int num_m = (args.M + BMT - 1) / BMT;
   const int num_n = (args.N + BN - 1) / BN;
   const int num_k = (args.K + BK - 1) / BK;
   const int total = num_m * num_n;
+  const int m_rot = args.m_rotate / TM < num_m ? args.m_rotate / TM : 0;   // given in 128-row units
   DeviceStatus* st = args.status;
 
   if (threadIdx.x == 0) {
@@ -137,7 +157,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     }
     for (int t = 0; t < TQ; ++t) {
       mbar_init(&tq_full[t], 1);
-      mbar_init(&tq_empty[t], 5);    // MMA thread + one lane of each epilogue warp
+      mbar_init(&tq_empty[t], 1 + 4 * TM);    // MMA thread + one lane of each epilogue warp
     }
     *abort_flag = 0u;
     mbar_fence_init();
@@ -218,7 +238,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         ok = (tile == -1);
         break;
       }
-      const TileCoord tc = tile_coord(tile, num_m, num_n, args.n_rotate, args.m_rotate);
+      const TileCoord tc = tile_coord<TM>(tile, num_m, num_n, args.n_rotate, m_rot);
       if (args.b_flags != nullptr && !b_all_seen) {
         // The elements of B this tile reads must have landed in this GPU's memory.  A
         // K-major B tile is rows [n0, n0+BN) of the weight; an MN-major B (dgrad) strides
@@ -239,14 +259,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       }
       if (args.a_flags != nullptr && !a_all_seen) {
         // Same for a gathered A operand (tensor-parallel all-gather of activation rows): a
-        // K-major A tile is rows [m0, m0+BM); an MN-major A waits for the whole matrix once.
+        // K-major A tile is rows [m0, m0+BMT); an MN-major A waits for the whole matrix once.
         long e0, e1;
         if (A_MN) {
           e0 = args.a_flag_base;
           e1 = args.a_flag_base + static_cast<long>(args.K) * args.lda;
           a_all_seen = true;
         } else {
-          const int mend = min(tc.m0 + BM, args.M);
+          const int mend = min(tc.m0 + BMT, args.M);
           e0 = args.a_flag_base + static_cast<long>(tc.m0) * args.lda;
           e1 = args.a_flag_base + static_cast<long>(mend - 1) * args.lda + args.K;
         }
@@ -264,13 +284,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           armed |= 1u << stage;
           armed_par = (armed_par & ~(1u << stage)) | (phase << stage);
           uint8_t* sa = smem + stage * A_STAGE;
-          uint8_t* sb = smem + OFF_B + stage * B_STAGE;
+          uint8_t* sb = smem + C::OFF_B + stage * B_STAGE;
           const int k0 = kb * BK;
           if (A_MN) {
 #pragma unroll
-            for (int a = 0; a < BM / 64; ++a) tma_load_2d(sa + a * 8192, &map_a, &full[stage], tc.m0 + a * 64, k0);
+            for (int a = 0; a < BMT / 64; ++a) tma_load_2d(sa + a * 8192, &map_a, &full[stage], tc.m0 + a * 64, k0);
           } else {
-            tma_load_2d(sa, &map_a, &full[stage], k0, tc.m0);
+#pragma unroll
+            for (int h = 0; h < TM; ++h) tma_load_2d(sa + h * 16384, &map_a, &full[stage], k0, tc.m0 + h * BM);
           }
           if (B_MN) {
 #pragma unroll
@@ -314,7 +335,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
       constexpr uint32_t idesc = make_idesc_bf16(BM, BN, A_MN, B_MN);
-      uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+      uint32_t stage = 0, phase = 0;
+      uint32_t uses[2] = {0, 0};     // completed uses of each TMEM slot
+      uint32_t next_slot = 0;        // TM == 1: slots alternate from tile to tile
       bool ok = true;
       uint32_t tq = 0, tq_phase = 0;
       while (ok) {
@@ -326,9 +349,6 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           tq_phase ^= 1u;
         }
         if (tile < 0) break;
-        if (!mbar_wait(&tempty[acc], acc_phase ^ 1u, abort_flag, st, SITE_MMA_TEMPTY, args.spin_budget)) break;
-        tc_fence_after();
-        const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_k; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag, st, SITE_MMA_FULL, args.spin_budget)) {
             ok = false;
@@ -336,13 +356,28 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
           tc_fence_after();
           const uint32_t sa = smem_u32(smem + stage * A_STAGE);
-          const uint32_t sb = smem_u32(smem + OFF_B + stage * B_STAGE);
+          const uint32_t sb = smem_u32(smem + C::OFF_B + stage * B_STAGE);
 #pragma unroll
           for (int k = 0; k < BK / 16; ++k) {
-            const uint64_t da = A_MN ? desc_mnmajor(sa, k, 8192) : desc_kmajor(sa, k);
             const uint64_t db = B_MN ? desc_mnmajor(sb, k, 8192) : desc_kmajor(sb, k);
-            umma_bf16(d_tmem, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+#pragma unroll
+            for (int h = 0; h < TM; ++h) {
+              const uint32_t slot = TM == 1 ? next_slot : static_cast<uint32_t>(h);
+              if (kb == 0 && k == 0) {
+                // the slot must have been drained by the epilogue of the tile that used it last
+                if (!mbar_wait(&tempty[slot], (uses[slot] & 1u) ^ 1u, abort_flag, st, SITE_MMA_TEMPTY,
+                               args.spin_budget)) {
+                  ok = false;
+                  break;
+                }
+                tc_fence_after();
+              }
+              const uint64_t da = A_MN ? desc_mnmajor(sa + h * 16384, k, 8192) : desc_kmajor(sa + h * 16384, k);
+              umma_bf16(tmem_base + slot * BN, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+            }
+            if (!ok) break;
           }
+          if (!ok) break;
           umma_commit(&empty[stage]);
           if (++stage == NSTAGE) {
             stage = 0;
@@ -350,24 +385,32 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           }
         }
         if (!ok) break;
-        umma_commit(&tfull[acc]);
-        acc ^= 1u;
-        if (acc == 0) acc_phase ^= 1u;
+#pragma unroll
+        for (int h = 0; h < TM; ++h) {
+          const uint32_t slot = TM == 1 ? next_slot : static_cast<uint32_t>(h);
+          umma_commit(&tfull[slot]);
+          ++uses[slot];
+        }
+        if (TM == 1) next_slot ^= 1u;
       }
     }
   } else if (warp >= 4) {
-    // ------------------------------ epilogue (4 warps, 128 TMEM lanes) ------------------------------
-    const int q = warp & 3;                 // TMEM lane quadrant of this warp
-    const int row = q * 32 + lane;          // row of the tile owned by this thread
-    const int etid = threadIdx.x - 128;
-    uint32_t acc = 0, acc_phase = 0, buf_idx = 0;
-    uint8_t* epi = smem + OFF_EPI;
+    // ------------------------------ epilogue (TM warpgroups of 4 warps, 128 TMEM lanes each) ------------
+    const int wg = (warp - 4) >> 2;          // TM == 2: warpgroup wg drains slot wg = rows [128 wg, 128 wg + 128)
+    const int q = warp & 3;                  // TMEM lane quadrant of this warp
+    const int row = q * 32 + lane;           // row of the 128-row sub-tile owned by this thread
+    const int etid = threadIdx.x - 128 - wg * 128;
+    const uint32_t bar_stage = 1 + wg;       // named barriers of this warpgroup
+    const uint32_t bar_vote = 3 + wg;
+    uint32_t uses[2] = {0, 0};
+    uint32_t next_slot = 0, buf_idx = 0;
+    uint8_t* epi = smem + C::OFF_EPI + wg * EPI_BUF;
     uint32_t tq = 0, tq_phase = 0;
     while (true) {
-      // The four epilogue warps decide together: a thread that gave up must not leave
+      // The four warps of a warpgroup decide together: a thread that gave up must not leave
       // the others waiting at the staging barriers below.
       const bool queued = mbar_wait(&tq_full[tq], tq_phase, abort_flag, st, SITE_TILE_QUEUE, args.spin_budget);
-      if (named_bar_or(2, 128, !queued)) break;
+      if (named_bar_or(bar_vote, 128, !queued)) break;
       const int tile = tile_ring[tq];
       __syncwarp();
       if (lane == 0) mbar_arrive(&tq_empty[tq]);
@@ -376,12 +419,16 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         tq_phase ^= 1u;
       }
       if (tile < 0) break;
-      const TileCoord tc = tile_coord(tile, num_m, num_n, args.n_rotate, args.m_rotate);
-      const bool got = mbar_wait(&tfull[acc], acc_phase, abort_flag, st, SITE_EPI_TFULL, args.spin_budget);
-      if (named_bar_or(2, 128, !got)) break;
+      const TileCoord tc = tile_coord<TM>(tile, num_m, num_n, args.n_rotate, m_rot);
+      const uint32_t slot = TM == 1 ? next_slot : static_cast<uint32_t>(wg);
+      const bool got = mbar_wait(&tfull[slot], uses[slot] & 1u, abort_flag, st, SITE_EPI_TFULL, args.spin_budget);
+      if (named_bar_or(bar_vote, 128, !got)) break;
+      ++uses[slot];
+      if (TM == 1) next_slot ^= 1u;
       tc_fence_after();
-      const uint32_t taddr = tmem_base + acc * BN + (static_cast<uint32_t>(q * 32) << 16);
-      const int grow = tc.m0 + row;
+      const uint32_t taddr = tmem_base + slot * BN + (static_cast<uint32_t>(q * 32) << 16);
+      const int m_sub = tc.m0 + wg * BM;     // first row of this warpgroup's sub-tile
+      const int grow = m_sub + row;
 
       if (EPI == EPI_CE_STATS) {
         // Online softmax statistics of this 256-column slab for one row per thread.
@@ -427,9 +474,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           uint32_t r[32];
           tmem_ld32(taddr + c * 32, r);
           tmem_ld_wait();
-          uint8_t* buf = epi + (buf_idx & 1u) * EPI_BUF;
-          if (etid == 0) tma_wait_group_read<1>();
-          named_bar_sync(1, 128);
+          uint8_t* buf = epi + (C::EPI_BUFS == 2 ? (buf_idx & 1u) * EPI_BUF : 0u);
+          if (etid == 0) tma_wait_group_read<C::EPI_BUFS - 1>();
+          named_bar_sync(bar_stage, 128);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             float4 v;
@@ -440,10 +487,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             *reinterpret_cast<float4*>(buf + sw128_offset(row, j)) = v;
           }
           fence_proxy_async_smem();
-          named_bar_sync(1, 128);
-          if (etid == 0) {
-            if (args.accumulate) tma_reduce_add_2d(&map_c, buf, col0, tc.m0);
-            else tma_store_2d(&map_c, buf, col0, tc.m0);
+          named_bar_sync(bar_stage, 128);
+          if (etid == 0 && m_sub < args.M) {
+            if (args.accumulate) tma_reduce_add_2d(&map_c, buf, col0, m_sub);
+            else tma_store_2d(&map_c, buf, col0, m_sub);
             tma_commit_group();
           }
           ++buf_idx;
@@ -460,84 +507,77 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         for (int c = 0; c < BN / 64; ++c) {
           const int col0 = tc.n0 + c * 64;
           if (col0 >= args.N) break;
-          uint32_t r0[32], r1[32];
-          tmem_ld32(taddr + c * 64, r0);
-          tmem_ld32(taddr + c * 64 + 32, r1);
-          tmem_ld_wait();
-          if (EPI == EPI_CE_DLOGITS) {
+          uint8_t* buf = epi + (C::EPI_BUFS == 2 ? (buf_idx & 1u) * EPI_BUF : 0u);
+          // 64 output columns per staged block, converted 32 at a time to keep registers low
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              float p0 = __expf(__uint_as_float(r0[j]) - lse);
-              float p1 = __expf(__uint_as_float(r1[j]) - lse);
-              if (col0 + j == target) p0 -= 1.f;
-              if (col0 + 32 + j == target) p1 -= 1.f;
-              r0[j] = __float_as_uint(p0 * coef);
-              r1[j] = __float_as_uint(p1 * coef);
+          for (int hh = 0; hh < 2; ++hh) {
+            uint32_t r[32];
+            tmem_ld32(taddr + c * 64 + hh * 32, r);
+            tmem_ld_wait();
+            const int cb = col0 + hh * 32;
+            if (EPI == EPI_CE_DLOGITS) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                float pv = __expf(__uint_as_float(r[j]) - lse);
+                if (cb + j == target) pv -= 1.f;
+                r[j] = __float_as_uint(pv * coef);
+              }
+            } else if (args.bias != nullptr) {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) {
+                const float bv = (cb + j < args.N) ? __bfloat162float(args.bias[cb + j]) : 0.f;
+                r[j] = __float_as_uint(__uint_as_float(r[j]) + bv);
+              }
             }
-          } else if (args.bias != nullptr) {
+            if (args.alpha != 1.f) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const float b0 = (col0 + j < args.N) ? __bfloat162float(args.bias[col0 + j]) : 0.f;
-              const float b1 = (col0 + 32 + j < args.N) ? __bfloat162float(args.bias[col0 + 32 + j]) : 0.f;
-              r0[j] = __float_as_uint(__uint_as_float(r0[j]) + b0);
-              r1[j] = __float_as_uint(__uint_as_float(r1[j]) + b1);
+              for (int j = 0; j < 32; ++j) r[j] = __float_as_uint(__uint_as_float(r[j]) * args.alpha);
             }
-          }
-          if (args.alpha != 1.f) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              r0[j] = __float_as_uint(__uint_as_float(r0[j]) * args.alpha);
-              r1[j] = __float_as_uint(__uint_as_float(r1[j]) * args.alpha);
+            if (hh == 0) {
+              // the staging block may still be read by the store that used it last
+              if (etid == 0) tma_wait_group_read<C::EPI_BUFS - 1>();
+              named_bar_sync(bar_stage, 128);
             }
-          }
-          uint8_t* buf = epi + (buf_idx & 1u) * EPI_BUF;
-          if (etid == 0) tma_wait_group_read<1>();
-          named_bar_sync(1, 128);
 #pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(r0[8 * j + 0]), __uint_as_float(r0[8 * j + 1]));
-            v.y = pack_bf16(__uint_as_float(r0[8 * j + 2]), __uint_as_float(r0[8 * j + 3]));
-            v.z = pack_bf16(__uint_as_float(r0[8 * j + 4]), __uint_as_float(r0[8 * j + 5]));
-            v.w = pack_bf16(__uint_as_float(r0[8 * j + 6]), __uint_as_float(r0[8 * j + 7]));
-            *reinterpret_cast<uint4*>(buf + sw128_offset(row, j)) = v;
-          }
-#pragma unroll
-          for (int j = 0; j < 4; ++j) {
-            uint4 v;
-            v.x = pack_bf16(__uint_as_float(r1[8 * j + 0]), __uint_as_float(r1[8 * j + 1]));
-            v.y = pack_bf16(__uint_as_float(r1[8 * j + 2]), __uint_as_float(r1[8 * j + 3]));
-            v.z = pack_bf16(__uint_as_float(r1[8 * j + 4]), __uint_as_float(r1[8 * j + 5]));
-            v.w = pack_bf16(__uint_as_float(r1[8 * j + 6]), __uint_as_float(r1[8 * j + 7]));
-            *reinterpret_cast<uint4*>(buf + sw128_offset(row, 4 + j)) = v;
+            for (int j = 0; j < 4; ++j) {
+              uint4 v;
+              v.x = pack_bf16(__uint_as_float(r[8 * j + 0]), __uint_as_float(r[8 * j + 1]));
+              v.y = pack_bf16(__uint_as_float(r[8 * j + 2]), __uint_as_float(r[8 * j + 3]));
+              v.z = pack_bf16(__uint_as_float(r[8 * j + 4]), __uint_as_float(r[8 * j + 5]));
+              v.w = pack_bf16(__uint_as_float(r[8 * j + 6]), __uint_as_float(r[8 * j + 7]));
+              *reinterpret_cast<uint4*>(buf + sw128_offset(row, hh * 4 + j)) = v;
+            }
           }
           if (EPI == EPI_PUSH) {
             // reduce-scatter by push: 128 threads copy the staged 128 x 128 B block into the
             // owner's receive buffer with 16-byte stores (peer memory: plain st.global only)
-            named_bar_sync(1, 128);
-            const int grow0 = args.push.row_offset + tc.m0;
-            const int dest = grow0 / args.push.rows_per_rank;
-            const long drow0 = static_cast<long>(args.push.src_rank) * args.push.rows_per_rank +
-                               (grow0 - dest * args.push.rows_per_rank);
-            push_block(buf, args.push.dest[dest] + drow0 * args.push.ld + col0, args.push.ld, etid,
-                       args.M - tc.m0, args.N - col0);
+            named_bar_sync(bar_stage, 128);
+            if (m_sub < args.M) {
+              const int grow0 = args.push.row_offset + m_sub;
+              const int dest = grow0 / args.push.rows_per_rank;
+              const long drow0 = static_cast<long>(args.push.src_rank) * args.push.rows_per_rank +
+                                 (grow0 - dest * args.push.rows_per_rank);
+              push_block(buf, args.push.dest[dest] + drow0 * args.push.ld + col0, args.push.ld, etid,
+                         args.M - m_sub, args.N - col0);
+            }
+            if (C::EPI_BUFS == 1) named_bar_sync(bar_stage, 128);   // one block: all copies out before it is refilled
           } else {
             fence_proxy_async_smem();
-            named_bar_sync(1, 128);
-            if (etid == 0) {
-              if (args.accumulate) tma_reduce_add_2d(&map_c, buf, col0, tc.m0);
-              else tma_store_2d(&map_c, buf, col0, tc.m0);
+            named_bar_sync(bar_stage, 128);
+            if (etid == 0 && m_sub < args.M) {
+              if (args.accumulate) tma_reduce_add_2d(&map_c, buf, col0, m_sub);
+              else tma_store_2d(&map_c, buf, col0, m_sub);
               tma_commit_group();
             }
           }
           ++buf_idx;
         }
-        if (EPI == EPI_PUSH) {
-          // this tile is on its way: count it, and publish the flag with the last one
+        if (EPI == EPI_PUSH && m_sub < args.M) {
+          // this 128-row piece is on its way: count it, and publish the flag with the last one
           __threadfence_system();
-          named_bar_sync(1, 128);
+          named_bar_sync(bar_stage, 128);
           if (etid == 0) {
-            const int dest = (args.push.row_offset + tc.m0) / args.push.rows_per_rank;
+            const int dest = (args.push.row_offset + m_sub) / args.push.rows_per_rank;
             const unsigned done = atomicAdd(args.push.counters + dest, 1u) + 1u;
             if (done == static_cast<unsigned>(args.push.tiles_per_dest)) {
               args.push.counters[dest] = 0u;
@@ -550,9 +590,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       }
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&tempty[acc]);
-      acc ^= 1u;
-      if (acc == 0) acc_phase ^= 1u;
+      if (lane == 0) mbar_arrive(&tempty[slot]);
     }
     if (etid == 0) tma_wait_group<0>();
   }
@@ -583,20 +621,19 @@ inline int* next_tile_counter() {
   return pool[dev] + 2 * (turn[dev]++ % POOL);
 }
 
-template <bool A_MN, bool B_MN, int EPI>
+template <int TM, bool A_MN, bool B_MN, int EPI>
 int launch(const CUtensorMap* ma, const CUtensorMap* mb, const CUtensorMap* mc, const GemmArgs& args, int grid,
            cudaStream_t stream) {
-  auto kern = gemm_kernel<A_MN, B_MN, EPI>;
-  static bool configured = false;  // per instantiation; the attribute is per function, all devices of the context
-  static int configured_dev = -1;
+  using C = Cfg<TM>;
+  auto kern = gemm_kernel<TM, A_MN, B_MN, EPI>;
+  static int configured_dev = -1;  // per instantiation; the attribute is per function and device
   int dev = 0;
   cudaGetDevice(&dev);
-  if (!configured || configured_dev != dev) {
-    CTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES));
-    configured = true;
+  if (configured_dev != dev) {
+    CTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM_BYTES));
     configured_dev = dev;
   }
-  kern<<<grid, NTHREADS, SMEM_BYTES, stream>>>(*ma, *mb, *mc, args);
+  kern<<<grid, C::THREADS, C::SMEM_BYTES, stream>>>(*ma, *mb, *mc, args);
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
 }
@@ -672,21 +709,34 @@ int run_gemm(const GemmCall& c) {
     if (c.push.rows_per_rank % BM || c.push.row_offset % BM || c.push.ld % 8 || c.N % 8)
       return fail("gemm: push needs 128-row aligned rank slabs and 16-byte aligned rows");
   }
-  const int tiles = ((c.M + BM - 1) / BM) * ((c.N + BN - 1) / BN);
+  // Tile shape: 256 x 256 when there are enough of them to fill the machine a few times over,
+  // 128 x 256 for small problems (CTB_GEMM_TM=1|2 forces one).
+  static const int forced_tm = [] {
+    const char* e = std::getenv("CTB_GEMM_TM");
+    return (e != nullptr && (e[0] == '1' || e[0] == '2')) ? e[0] - '0' : 0;
+  }();
+  const int num_n = (c.N + BN - 1) / BN;
+  const int tiles2 = ((c.M + 2 * BM - 1) / (2 * BM)) * num_n;
+  const int tm = forced_tm ? forced_tm : (tiles2 >= 2 * sm_count() ? 2 : 1);
+  const int tiles = tm == 2 ? tiles2 : ((c.M + BM - 1) / BM) * num_n;
   int grid = std::min(tiles, c.max_ctas > 0 ? c.max_ctas : sm_count());
   cudaStream_t s = static_cast<cudaStream_t>(c.stream);
-#define CTB_DISPATCH(AM, BMN)                                                         \
-  switch (c.epi) {                                                                    \
-    case EPI_STORE: return launch<AM, BMN, EPI_STORE>(ma, mb, mc, a, grid, s);        \
-    case EPI_CE_STATS: return launch<AM, BMN, EPI_CE_STATS>(ma, mb, mc, a, grid, s);  \
-    case EPI_CE_DLOGITS: return launch<AM, BMN, EPI_CE_DLOGITS>(ma, mb, mc, a, grid, s); \
-    case EPI_PUSH: return launch<AM, BMN, EPI_PUSH>(ma, mb, mc, a, grid, s);          \
-    default: return fail("gemm: unknown epilogue");                                   \
+#define CTB_DISPATCH_TM(TMV, AM, BMN)                                                       \
+  switch (c.epi) {                                                                          \
+    case EPI_STORE: return launch<TMV, AM, BMN, EPI_STORE>(ma, mb, mc, a, grid, s);         \
+    case EPI_CE_STATS: return launch<TMV, AM, BMN, EPI_CE_STATS>(ma, mb, mc, a, grid, s);   \
+    case EPI_CE_DLOGITS: return launch<TMV, AM, BMN, EPI_CE_DLOGITS>(ma, mb, mc, a, grid, s); \
+    case EPI_PUSH: return launch<TMV, AM, BMN, EPI_PUSH>(ma, mb, mc, a, grid, s);           \
+    default: return fail("gemm: unknown epilogue");                                         \
   }
+#define CTB_DISPATCH(AM, BMN)                 \
+  if (tm == 2) { CTB_DISPATCH_TM(2, AM, BMN) } \
+  CTB_DISPATCH_TM(1, AM, BMN)
   if (!c.a_mn && !c.b_mn) { CTB_DISPATCH(false, false) }
   if (!c.a_mn && c.b_mn) { CTB_DISPATCH(false, true) }
   if (c.a_mn && c.b_mn) { CTB_DISPATCH(true, true) }
   CTB_DISPATCH(true, false)
+#undef CTB_DISPATCH_TM
 #undef CTB_DISPATCH
 }
 
