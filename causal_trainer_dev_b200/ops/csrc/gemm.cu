@@ -717,7 +717,9 @@ int run_gemm(const GemmCall& c) {
   }();
   const int num_n = (c.N + BN - 1) / BN;
   const int tiles2 = ((c.M + 2 * BM - 1) / (2 * BM)) * num_n;
-  const int tm = forced_tm ? forced_tm : (tiles2 >= 2 * sm_count() ? 2 : 1);
+  // (the push epilogue copies every block out with the epilogue threads themselves and keeps its
+  // two staging blocks: it measured faster on the smaller tile)
+  const int tm = forced_tm ? forced_tm : ((tiles2 >= 2 * sm_count() && c.epi != EPI_PUSH) ? 2 : 1);
   const int tiles = tm == 2 ? tiles2 : ((c.M + BM - 1) / BM) * num_n;
   int grid = std::min(tiles, c.max_ctas > 0 ? c.max_ctas : sm_count());
   cudaStream_t s = static_cast<cudaStream_t>(c.stream);
