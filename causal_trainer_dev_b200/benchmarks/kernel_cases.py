@@ -74,6 +74,56 @@ def main() -> None:
             flops = 10.0 * b * hq * s * s * d / 2
         tf = flops / ms / 1e9
         out.update(ms=ms, causal_tflops=tf, fraction_of_measured_bf16_peak=tf / pk["bf16_tflops"])
+    elif case == "moba":
+        # one 32768-token row packed from 4 documents, MoBA block 4096, top-3 gated blocks + the
+        # current block, against dense segment-masked flash attention on the same tensors
+        from causal_trainer_dev_b200.ops import moba as M
+
+        b, s, hq, hkv, d, block, top_k = 1, 32768, 32, 8, 128, 4096, 4
+        g = torch.Generator().manual_seed(3)
+        lens = torch.randint(4096, 12289, (4,), generator=g).tolist()
+        lens[-1] = max(1, s - sum(lens[:-1])) if sum(lens[:-1]) < s else 0
+        if len(sys.argv) > 2 and sys.argv[2] == "one-document":
+            lens = [s]               # a single 32768-token document: 8 blocks, 4 of them visible per query
+        seg = torch.zeros(b, s, dtype=torch.int32)
+        pos = 0
+        for i, n in enumerate(lens):
+            n = min(n, s - pos)
+            seg[0, pos:pos + n] = i + 1
+            pos += n
+        seg = seg.to(dev)
+        q = torch.randn(b, s, hq, d, device=dev).bfloat16()
+        k = torch.randn(b, s, hkv, d, device=dev).bfloat16()
+        v = torch.randn(b, s, hkv, d, device=dev).bfloat16()
+        if len(sys.argv) > 2 and sys.argv[2] == "coherent":
+            # routing that neighbouring queries agree on (what trained models show): every key
+            # block carries its own direction and each group of 1024 queries leans towards three
+            # of the earlier blocks
+            lens = [s]
+            seg = torch.ones(b, s, dtype=torch.int32, device=dev)
+            blk = torch.arange(s, device=dev) // block
+            k = (k.float() * 0.3)
+            k[0, torch.arange(s, device=dev), :, blk] += 6.0
+            k = k.bfloat16()
+            qf = q.float() * 0.3
+            grp = torch.arange(s, device=dev) // 1024
+            for j in range(3):
+                want = (grp * 7 + j * 3) % torch.clamp(blk, min=1)
+                qf[0, torch.arange(s, device=dev), :, want] += 6.0
+            q = qf.bfloat16()
+        meta = A.build_attention_meta(seg)
+        routing = M.build_routing(q, k, meta, block, top_k)
+        o, lse = M.moba_forward(q, k, v, meta, routing)
+        do = torch.randn_like(o)
+        od, lsed = A.flash_attention_forward(q, k, v, meta)
+        out.update(
+            document_lengths=lens, visited_tile_fraction=routing.visited_fraction,
+            routing_ms=timed(lambda: M.build_routing(q, k, meta, block, top_k)),
+            moba_fwd_ms=timed(lambda: M.moba_forward(q, k, v, meta, routing)),
+            dense_fwd_ms=timed(lambda: A.flash_attention_forward(q, k, v, meta)),
+            moba_bwd_ms=timed(lambda: M.moba_backward(q, k, v, o, do, lse, meta, routing)),
+            dense_bwd_ms=timed(lambda: A.flash_attention_backward(q, k, v, od, do, lsed, meta)),
+        )
     elif case == "cut_ce":
         rows, d, vocab = 4096, 4096, 128256
         h = torch.randn(rows, d, device=dev).bfloat16()

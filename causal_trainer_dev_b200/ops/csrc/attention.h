@@ -23,6 +23,7 @@ struct SparseArgs {
   const int* it_list;      // forward: 128-key tile index; backward: 64-row block | head_in_group << 24
   const unsigned* sel;     // [B][Hq][S][words]
   const int* doc_start;    // [B][S]
+  const unsigned* allsel;  // [B][Hq][S/64][words] AND of sel over each 64-query block (backward dK/dV fast path)
   int block;               // >= 128
   int words;
 };

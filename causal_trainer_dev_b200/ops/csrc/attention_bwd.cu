@@ -324,9 +324,19 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const unsigned* col_sel = nullptr;
       if (sparse && !none) {
         if (DKV) {
-          all = false;
-          if ((row_blk >> 5) >= args.sp.words) none = true;
-          col_sel = args.sp.sel + ((static_cast<size_t>(b) * args.Hq + hq) * args.S + y0) * args.sp.words + (row_blk >> 5);
+          if ((row_blk >> 5) >= args.sp.words) {
+            none = true;
+          } else {
+            // when every query of the block selected this key's block the selection adds nothing
+            // to the segment / causal test and the row keeps its fast paths
+            const unsigned aw = __ldg(args.sp.allsel + ((static_cast<size_t>(b) * args.Hq + hq) * nb64 + yb) * args.sp.words +
+                                      (row_blk >> 5));
+            if (!((aw >> (row_blk & 31)) & 1u)) {
+              all = false;
+              col_sel = args.sp.sel + ((static_cast<size_t>(b) * args.Hq + hq) * args.S + y0) * args.sp.words +
+                        (row_blk >> 5);
+            }
+          }
         } else {
           const SparseRow sr = sparse_row(args.sp, b, head, args.Hq, args.S, xi, row_start, y0, 64);
           bound = sr.bound; v0 = sr.v0; v1 = sr.v1;
@@ -556,7 +566,7 @@ CTB_API int ctb_attn_bwd_sparse(int mode, const void* q, const void* k, const vo
                                 const int* lim, const int* kv_lo, const int* kv_hi, const int* q_lo, const int* q_hi,
                                 const int* seg_min64, const int* seg_max64, const int* lim_min64,
                                 const int* lim_max64, const int* it_off, const int* it_list, const unsigned* sel,
-                                const int* doc_start, int block, int words, int B, int S, int Hq, int Hkv, int D,
+                                const unsigned* allsel, const int* doc_start, int block, int words, int B, int S, int Hq, int Hkv, int D,
                                 long q_rs, long k_rs, long v_rs, long do_rs, long dq_rs, long dk_rs, long dv_rs,
                                 float scale, long long spin_budget, void* stream) {
   if (S % 128) return ctb::fail("attention: sequence length must be a multiple of 128");
@@ -571,7 +581,7 @@ CTB_API int ctb_attn_bwd_sparse(int mode, const void* q, const void* k, const vo
   c.dq_row_stride = dq_rs; c.dk_row_stride = dk_rs; c.dv_row_stride = dv_rs;
   c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
   c.sp.it_off = it_off; c.sp.it_list = it_list; c.sp.sel = sel; c.sp.doc_start = doc_start;
-  c.sp.block = block; c.sp.words = words;
+  c.sp.allsel = allsel; c.sp.block = block; c.sp.words = words;
   using namespace ctb::attn;
   if (D == 128) return mode == 0 ? launch_bwd<128, MODE_DKV>(c) : launch_bwd<128, MODE_DQ>(c);
   if (D == 64) return mode == 0 ? launch_bwd<64, MODE_DKV>(c) : launch_bwd<64, MODE_DQ>(c);

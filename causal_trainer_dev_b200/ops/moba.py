@@ -35,6 +35,7 @@ class MobaRouting:
     """Selection masks and CTA work lists of one layer."""
 
     sel: torch.Tensor          # [B,Hq,S,W] int32 bit masks of selected document-relative blocks
+    allsel: torch.Tensor       # [B,Hq,S/64,W] int32: AND of sel over each 64-query block (padding counts as all)
     doc_start: torch.Tensor    # [B,S] int32
     block: int
     words: int
@@ -98,6 +99,17 @@ def _touched_blocks(sel: torch.Tensor, seg: torch.Tensor, doc_start: torch.Tenso
     return diff.view(b, hq, nb, nb + 1).cumsum(-1)[..., :nb] > 0
 
 
+def _block_and(sel: torch.Tensor, seg: torch.Tensor) -> torch.Tensor:
+    """Bitwise AND of the selection masks over each block of 64 queries (padding rows count as all ones)."""
+    b, hq, s, words = sel.shape
+    eff = torch.where((seg != 0)[:, None, :, None], sel, torch.full_like(sel, -1)).view(b, hq, s // 64, 64, words)
+    n = 64
+    while n > 1:                      # log-step reduction: no bitwise-AND reduce in PyTorch
+        n //= 2
+        eff = eff[:, :, :, :n] & eff[:, :, :, n:2 * n]
+    return eff[:, :, :, 0].contiguous()
+
+
 def _csr(table: torch.Tensor, values: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
     """Offsets and entries of a ``[items, candidates]`` bool table (entry = candidate index or ``values``)."""
     counts = table.sum(-1, dtype=torch.int32)
@@ -118,6 +130,7 @@ def build_routing(q: torch.Tensor, k: torch.Tensor, meta: AttentionMeta, block: 
     doc_start = document_starts(seg)
     sel = route(q, k, seg, doc_start, block, top_k)
     touch = _touched_blocks(sel, seg, doc_start, block)                                # [B,Hq,nq64,nk64]
+    allsel = _block_and(sel, seg)
     nb64, nb128 = s // 64, s // 128
     nqp = (s + 255) // 256
     # forward: (query pair descending, batch, head) x 128-key tiles
@@ -135,7 +148,7 @@ def build_routing(q: torch.Tensor, k: torch.Tensor, meta: AttentionMeta, block: 
     t = touch.view(b, hkv, g, nb64, nb128, 2).any(-1).permute(4, 0, 1, 2, 3).reshape(-1, g * nb64)
     packed = (torch.arange(g, device=t.device)[:, None] * (1 << 24) + torch.arange(nb64, device=t.device)[None, :])
     dkv_off, dkv_list = _csr(t, packed.reshape(-1))
-    return MobaRouting(sel, doc_start, block, sel.shape[-1], fwd_off, fwd_list, dq_off, dq_list, dkv_off, dkv_list,
+    return MobaRouting(sel, allsel, doc_start, block, sel.shape[-1], fwd_off, fwd_list, dq_off, dq_list, dkv_off, dkv_list,
                        visited)
 
 
@@ -176,7 +189,7 @@ def moba_backward(q, k, v, out, dout, lse, meta: AttentionMeta, routing: MobaRou
             _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(meta.seg), _lib.ptr(meta.lim), _lib.ptr(meta.kv_lo),
             _lib.ptr(meta.kv_hi), _lib.ptr(meta.q_lo), _lib.ptr(meta.q_hi), _lib.ptr(meta.seg_min64),
             _lib.ptr(meta.seg_max64), _lib.ptr(meta.lim_min64), _lib.ptr(meta.lim_max64),
-            _lib.ptr(off), _lib.ptr(lst), _lib.ptr(r.sel), _lib.ptr(r.doc_start), r.block, r.words,
+            _lib.ptr(off), _lib.ptr(lst), _lib.ptr(r.sel), _lib.ptr(r.allsel), _lib.ptr(r.doc_start), r.block, r.words,
             b, s, hq, hkv, d,
             ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)), ctypes.c_long(_row_stride(v)),
             ctypes.c_long(_row_stride(dout)), ctypes.c_long(_row_stride(dq)), ctypes.c_long(_row_stride(dk)),
