@@ -86,6 +86,14 @@ class LoraState:
         return list(self.named_tensors())
 
     # ---- export ----
+    def pair_of_tensor(self, hf_name: str):
+        """``(A, B)`` of the adapter on projection weight ``hf_name``, else ``None``."""
+        parts = hf_name.split(".")
+        if len(parts) == 6 and parts[0] == "model" and parts[1] == "layers" and parts[-1] == "weight" \
+                and parts[4] in LORA_PROJECTIONS:
+            return self.pair(int(parts[2]), parts[4])
+        return None
+
     def merged_delta(self, hf_name: str) -> torch.Tensor | None:
         """``(A @ B)^T`` in HF ``[out,in]`` layout for a projection weight name, else ``None``."""
         parts = hf_name.split(".")
@@ -102,6 +110,11 @@ class LoraState:
                 return self.embed.detach().to(t.dtype)
             if self.train_embed_and_lm_head and name == "lm_head.weight":
                 return self.lm_head.detach().to(t.dtype)
+            pair = self.pair_of_tensor(name)
+            if pair is not None and t.is_cuda and t.dtype == torch.bfloat16:
+                from ..ops.gemm import lora_merge      # rank-r update on the tcgen05 GEMM
+
+                return lora_merge(t, pair[0].detach().to(t.device), pair[1].detach().to(t.device))
             delta = self.merged_delta(name)
             if delta is None:
                 return t

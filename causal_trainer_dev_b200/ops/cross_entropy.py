@@ -149,6 +149,52 @@ def cut_ce_backward(hidden, head, targets, lse, coef, *, chunk_rows: int = 4096,
     return dhidden, dhead
 
 
+def logits_ce_forward_backward(hidden, head, targets, weights, grad_scale: float = 1.0, *, chunk_rows: int = 4096,
+                               need_dhead: bool = True, dhead_out: torch.Tensor | None = None,
+                               dhead_accumulate: bool = False):
+    """Cross-entropy through a materialised bf16 logits slab per row chunk (the ``pallas`` loss
+    backend of the reference, src/causal_trainer/kernels/cross_entropy.py:216-251, 358-397):
+    logits GEMM -> row statistics kernel -> dlogits written in place over the logits -> dH, dW.
+
+    Returns ``(nll_sum, weight_sum, dhidden, dhead)``.  Rows with zero weight are skipped chunk-wise.
+    """
+    rows, d = hidden.shape
+    vocab = head.shape[0]
+    dev = hidden.device
+    tgt = targets.to(torch.int32).contiguous()
+    w = weights.to(torch.float32).contiguous()
+    coef = w * grad_scale
+    dhidden = torch.zeros_like(hidden)
+    dhead = None
+    if need_dhead:
+        dhead = dhead_out if dhead_out is not None else torch.empty((vocab, d), dtype=torch.bfloat16, device=dev)
+    chunk_rows = min(chunk_rows, rows)
+    ldl = (vocab + 7) // 8 * 8
+    slab = torch.empty((chunk_rows, ldl), dtype=torch.bfloat16, device=dev)
+    lse = torch.empty(rows, dtype=torch.float32, device=dev)
+    tl = torch.empty(rows, dtype=torch.float32, device=dev)
+    L = _lib.lib()
+    first = True
+    for start in range(0, rows, chunk_rows):
+        n = min(chunk_rows, rows - start)
+        h = hidden[start:start + n]
+        g = slab[:n, :vocab]
+        gemm(h, head, out=g)
+        code = L.ctb_logits_ce_stats(_lib.ptr(g), ctypes.c_long(ldl), n, vocab, _lib.ptr(tgt[start:start + n]),
+                                     _lib.ptr(lse[start:start + n]), _lib.ptr(tl[start:start + n]), _lib.stream_ptr())
+        _lib.check(code, "ctb_logits_ce_stats")
+        code = L.ctb_logits_ce_backward(_lib.ptr(g), ctypes.c_long(ldl), n, vocab, _lib.ptr(tgt[start:start + n]),
+                                        _lib.ptr(lse[start:start + n]), _lib.ptr(coef[start:start + n]),
+                                        _lib.stream_ptr())
+        _lib.check(code, "ctb_logits_ce_backward")
+        gemm(g, head, b_mn=True, out=dhidden[start:start + n])
+        if need_dhead:
+            gemm(g, h, a_mn=True, b_mn=True, out=dhead, accumulate=(dhead_accumulate or not first))
+        first = False
+    nll = torch.where(w != 0, (lse - tl) * w, torch.zeros_like(lse))
+    return nll.sum(), w.sum(), dhidden, dhead
+
+
 class _CutCE(torch.autograd.Function):
     @staticmethod
     def forward(ctx, hidden, head, targets, weights, chunk_rows):

@@ -372,6 +372,88 @@ __global__ void ce_combine_kernel(const float* __restrict__ pmax, const float* _
 }
 
 // ------------------------------------------------------------------------------------------
+// Cross-entropy over a materialised logits slab [rows, vocab] (bf16): one CTA per row.
+//   stats:    lse[row] = logsumexp(logits[row, :]), target_logit[row] (0 when the target is < 0)
+//   backward: logits[row, v] <- (exp(logits[row, v] - lse[row]) - [v == target]) * coef[row], in place
+// The projection-fused cut cross-entropy never writes logits; these two kernels are the variant
+// that does (the reference's `pallas` loss backend, src/causal_trainer/kernels/cross_entropy.py:
+// 99-189, 254-322), for when the slab is wanted anyway.
+// ------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256)
+logits_ce_stats_kernel(const __nv_bfloat16* __restrict__ logits, long ld, int vocab, const int* __restrict__ targets,
+                       float* __restrict__ lse, float* __restrict__ target_logit) {
+  __shared__ float scratch[33];
+  __shared__ float s_max;
+  const long row = blockIdx.x;
+  const __nv_bfloat16* x = logits + row * ld;
+  const int nvec = vocab / 8;
+  float m = -INFINITY;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 raw = reinterpret_cast<const uint4*>(x)[v];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h[e]);
+      m = fmaxf(m, fmaxf(f.x, f.y));
+    }
+  }
+  for (int c = nvec * 8 + threadIdx.x; c < vocab; c += blockDim.x) m = fmaxf(m, __bfloat162float(x[c]));
+  // block max through the sum helper's scratch: reduce per warp, then across warps
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) scratch[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = -INFINITY;
+    for (int w = 0; w < static_cast<int>(blockDim.x >> 5); ++w) t = fmaxf(t, scratch[w]);
+    s_max = t;
+  }
+  __syncthreads();
+  const float mx = s_max;
+  float acc = 0.f;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    const uint4 raw = reinterpret_cast<const uint4*>(x)[v];
+    const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h[e]);
+      acc += __expf(f.x - mx) + __expf(f.y - mx);
+    }
+  }
+  for (int c = nvec * 8 + threadIdx.x; c < vocab; c += blockDim.x) acc += __expf(__bfloat162float(x[c]) - mx);
+  const float total = block_sum(acc, scratch);
+  if (threadIdx.x == 0) {
+    lse[row] = mx + logf(total);
+    const int t = targets[row];
+    target_logit[row] = (t >= 0 && t < vocab) ? __bfloat162float(x[t]) : 0.f;
+  }
+}
+
+__global__ void __launch_bounds__(256)
+logits_ce_backward_kernel(__nv_bfloat16* __restrict__ logits, long ld, int vocab, const int* __restrict__ targets,
+                          const float* __restrict__ lse, const float* __restrict__ coef) {
+  const long row = blockIdx.x;
+  __nv_bfloat16* x = logits + row * ld;
+  const float l = lse[row], c = coef[row];
+  const int t = targets[row];
+  const int nvec = vocab / 8;
+  for (int v = threadIdx.x; v < nvec; v += blockDim.x) {
+    uint4 raw = reinterpret_cast<uint4*>(x)[v];
+    __nv_bfloat162* h = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h[e]);
+      const int col = v * 8 + e * 2;
+      const float a = (__expf(f.x - l) - (col == t ? 1.f : 0.f)) * c;
+      const float b = (__expf(f.y - l) - (col + 1 == t ? 1.f : 0.f)) * c;
+      h[e] = __floats2bfloat162_rn(a, b);
+    }
+    reinterpret_cast<uint4*>(x)[v] = raw;
+  }
+  for (int col = nvec * 8 + threadIdx.x; col < vocab; col += blockDim.x)
+    x[col] = __float2bfloat16((__expf(__bfloat162float(x[col]) - l) - (col == t ? 1.f : 0.f)) * c);
+}
+
+// ------------------------------------------------------------------------------------------
 // Sum of squares (fp32) of a bf16 / fp32 vector into per-block partials.
 // ------------------------------------------------------------------------------------------
 template <typename T>
@@ -541,6 +623,27 @@ CTB_API int ctb_ce_combine(const float* pmax, const float* psum, int slabs, cons
                            float* block_w, int rows, void* stream) {
   ce_combine_kernel<<<(rows + 255) / 256, 256, 0, static_cast<cudaStream_t>(stream)>>>(
       pmax, psum, slabs, target_logit, weights, grad_scale, lse, coef, block_nll, block_w, rows);
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// logits: [rows, vocab] bf16 with row stride ld (elements, multiple of 8); lse/target_logit: [rows].
+CTB_API int ctb_logits_ce_stats(const void* logits, long ld, int rows, int vocab, const int* targets, float* lse,
+                                float* target_logit, void* stream) {
+  if (ld % 8) return fail("logits_ce: row stride must be a multiple of 8 elements");
+  if (rows <= 0) return 0;
+  logits_ce_stats_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(logits), ld, vocab, targets, lse, target_logit);
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+CTB_API int ctb_logits_ce_backward(void* logits, long ld, int rows, int vocab, const int* targets, const float* lse,
+                                   const float* coef, void* stream) {
+  if (ld % 8) return fail("logits_ce: row stride must be a multiple of 8 elements");
+  if (rows <= 0) return 0;
+  logits_ce_backward_kernel<<<rows, 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<__nv_bfloat16*>(logits), ld, vocab, targets, lse, coef);
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
 }

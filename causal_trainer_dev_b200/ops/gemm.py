@@ -193,3 +193,26 @@ def linear_wgrad(
 ) -> torch.Tensor:
     """``dw[out,in] (+)= dy[T,out]^T @ x[T,in]`` reading both in place."""
     return gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=accumulate, out_dtype=out_dtype)
+
+
+def lora_merge(w: torch.Tensor, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """Merged projection weight ``W + (A @ B)^T`` for export (no alpha: the reference's convention,
+    src/causal_trainer/modeling/lora.py:279-295).
+
+    ``w`` is ``[out, in]``, ``a`` ``[in, r]``, ``b`` ``[r, out]`` (bf16, CUDA).  The rank-r update
+    runs on the tcgen05 GEMM with fp32 accumulation straight into an fp32 copy of ``w`` (TMA
+    reduce-add epilogue); the result is rounded once to ``w``'s dtype.
+    """
+    out_f, in_f = w.shape
+    r = a.shape[1]
+    if a.shape[0] != in_f or b.shape != (r, out_f):
+        raise ValueError("adapter shapes do not match the projection")
+    pad = (-r) % 8                    # leading dimensions must be multiples of 16 bytes
+    bt = b.t().contiguous().to(torch.bfloat16)            # [out, r]  K-major A operand
+    at = a.contiguous().to(torch.bfloat16)                # [in, r]   K-major B operand
+    if pad:
+        bt = torch.nn.functional.pad(bt, (0, pad))
+        at = torch.nn.functional.pad(at, (0, pad))
+    acc = w.float()
+    gemm(bt, at, out=acc, accumulate=True)
+    return acc.to(w.dtype)

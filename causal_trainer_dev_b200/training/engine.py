@@ -68,6 +68,7 @@ class EngineOptions:
     train_embed: bool = True
     train_norm: bool = True
     remat: str = "auto"                      # "auto" | "full" | "none"
+    loss_backend: str = "cut"                # "cut": projection-fused; "logits": materialised bf16 logits slab per chunk
     memory_reserve_bytes: int = 8 << 30
 
 
@@ -301,11 +302,16 @@ class LayerwiseEngine:
         y, rstd_f, xf = ew.rmsnorm_forward(resid, fw["norm"], cfg.rms_norm_eps, residual=branch)
         targets, weights = losses.aligned_targets_and_weights(batch)
         targets, weights = targets.reshape(-1), weights.reshape(-1)
-        nll, wsum, lse, coef = ce.cut_ce_forward(y, fw["lm_head"], targets, weights, grad_scale)
         train_head = self.options.train_lm_head
-        dy, _ = ce.cut_ce_backward(y, fw["lm_head"], targets, lse, coef, chunk_rows=self.options.cut_chunk_rows,
-                                   need_dhead=train_head, dhead_out=fg["lm_head"] if train_head else None,
-                                   dhead_accumulate=accumulate)
+        if self.options.loss_backend == "logits":
+            nll, wsum, dy, _ = ce.logits_ce_forward_backward(
+                y, fw["lm_head"], targets, weights, grad_scale, chunk_rows=self.options.cut_chunk_rows,
+                need_dhead=train_head, dhead_out=fg["lm_head"] if train_head else None, dhead_accumulate=accumulate)
+        else:
+            nll, wsum, lse, coef = ce.cut_ce_forward(y, fw["lm_head"], targets, weights, grad_scale)
+            dy, _ = ce.cut_ce_backward(y, fw["lm_head"], targets, lse, coef, chunk_rows=self.options.cut_chunk_rows,
+                                       need_dhead=train_head, dhead_out=fg["lm_head"] if train_head else None,
+                                       dhead_accumulate=accumulate)
         self._count(4 + 3 * ((y.shape[0] + self.options.cut_chunk_rows - 1) // self.options.cut_chunk_rows))
         dout, _ = ew.rmsnorm_backward(dy, xf, fw["norm"], rstd_f, dw_out=fg["norm"], dw_accumulate=accumulate)
         del y, dy, xf

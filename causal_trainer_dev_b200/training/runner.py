@@ -401,7 +401,8 @@ class TrainingRun:
                 grad_dtype = torch.float32 if a.gradient_accumulation_steps > 1 else torch.bfloat16
                 producer = LayerwiseEngine(self.cfg, LocalProvider(self.params, grad_dtype), EngineOptions(
                     cut_chunk_rows=a.cut_chunk_size or 4096, train_lm_head="lm_head" not in frozen,
-                    train_embed="embed" not in frozen, attention_options=a.attention_options))
+                    train_embed="embed" not in frozen, attention_options=a.attention_options,
+                    loss_backend="logits" if a.loss_implementation == "pallas" else "cut"))
                 self.step_fn = TrainStep(self.params, producer, adamw, schedule, frozen=frozen)
             else:
                 opts = ForwardOptions(

@@ -54,3 +54,16 @@ def test_linear_triplet_matches_autograd(cuda_lib):
     assert _rel(G.linear_forward(x, w), x.float() @ w.float().t()) < 4e-3
     assert _rel(G.linear_dgrad(dy, w), dy.float() @ w.float()) < 4e-3
     assert _rel(G.linear_wgrad(dy, x), dy.float().t() @ x.float()) < 4e-3
+
+
+def test_lora_merge_matches_fp32_reference(cuda_lib):
+    from causal_trainer_dev_b200.ops.gemm import lora_merge
+
+    torch.manual_seed(5)
+    for out_f, in_f, r in ((512, 384, 16), (256, 1024, 12)):
+        w = (torch.randn(out_f, in_f, device="cuda") * 0.05).bfloat16()
+        a = (torch.randn(in_f, r, device="cuda") * 0.1).bfloat16()
+        b = (torch.randn(r, out_f, device="cuda") * 0.1).bfloat16()
+        ref = (w.float() + (a.float() @ b.float()).t()).bfloat16()
+        got = lora_merge(w, a, b)
+        assert (got.float() - ref.float()).abs().max() <= 2 * ref.float().abs().max() * 2 ** -8
