@@ -112,13 +112,18 @@ def load_parameters(source: str | os.PathLike[str], params: ModelParams) -> None
 def tp_window(name: str, cfg: ModelConfig, tp: int, tp_rank: int) -> tuple[int, int, int, int, str]:
     """``(row0, rows, col0, cols, kind)`` of the part of Hugging Face tensor ``name`` that tensor-
     parallel rank ``tp_rank`` stores; ``kind`` is how the parts tile the tensor: ``"rows"``
-    (column-parallel weights, biases, embedding, head), ``"cols"`` (row-parallel o/down weights)
-    or ``"rep"`` (norm scales, every rank holds all of it)."""
+    (column-parallel weights, biases, embedding, head), ``"cols"`` (row-parallel o/down weights),
+    ``"rep"`` (norm scales, every rank holds all of it) or ``"heads"`` (key/value projections with
+    fewer heads than ranks: row blocks, each stored by ``tp / Hkv`` consecutive ranks)."""
     d, q, kv, f, v = cfg.hidden_size, cfg.query_width, cfg.key_value_width, cfg.intermediate_size, cfg.vocab_size
     leaf = name.split(".")[-2]
     vector = name.endswith(".bias") or "norm" in name
     if "norm" in name:
         return 0, d, 0, 1, "rep"
+    if leaf in ("k_proj", "v_proj") and cfg.num_key_value_heads % tp:
+        # fewer key/value heads than ranks: groups of tp / Hkv ranks hold a copy of one whole head
+        rep = tp // cfg.num_key_value_heads
+        return (tp_rank // rep) * cfg.head_dim, cfg.head_dim, 0, (1 if vector else d), "heads"
     rows_of = {"q_proj": q, "k_proj": kv, "v_proj": kv, "gate_proj": f, "up_proj": f, "embed_tokens": v, "lm_head": v}
     if leaf in rows_of:
         n = rows_of[leaf] // tp
@@ -234,8 +239,13 @@ class TensorSource:
             return rt.gather_object_to_zero((tp_rank, x - t0, mine))
 
         kind = "rows" if tp == 1 else tp_window(name, self.cfg, tp, 0)[4]
-        if kind in ("rows", "rep"):
-            for r in range(1 if kind == "rep" else tp):
+        if kind in ("rows", "rep", "heads"):
+            owners = range(tp)
+            if kind == "rep":
+                owners = range(1)
+            elif kind == "heads":
+                owners = range(0, tp, tp // self.cfg.num_key_value_heads)     # first rank of every head
+            for r in owners:
                 for a in range(0, local_numel, step):
                     b = min(local_numel, a + step)
                     pieces = gather_round(r, a, b)

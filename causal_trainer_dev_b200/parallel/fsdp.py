@@ -421,11 +421,10 @@ class FsdpRuntime:
         self.main.wait_stream(self.reduce_stream)
         total = self.sumsq.sum().reshape(1)
         if self.tp_world > 1:
-            # norm scales are replicated over tp: every tp rank holds the same (already summed)
-            # gradient, so its square counts once
-            rep = self._replicated_index()
-            if rep.numel():
-                total = total - (1.0 - 1.0 / self.tp_world) * self.grad_shards[rep].float().pow(2).sum()
+            # norm scales (and shared key/value heads) are replicated over tp ranks: every copy
+            # holds the same, already summed, gradient, so its square counts once
+            for index, copies in self._replicated_index():
+                total = total - (1.0 - 1.0 / copies) * self.grad_shards[index].float().pow(2).sum()
             dist.all_reduce(total, group=self.tp_group)
         dist.all_reduce(total, group=self.group)          # also orders every peer's pulls before the update
         grad_norm = torch.sqrt(total)
@@ -452,21 +451,30 @@ class FsdpRuntime:
                 g.unit = None
         return grad_norm[0]
 
-    def _replicated_index(self) -> torch.Tensor:
-        """Arena positions, inside this rank's shards, of parameters replicated over tp."""
+    def _replicated_index(self) -> list[tuple[torch.Tensor, int]]:
+        """``(arena positions inside this rank's shards, copies)`` of parameters that several tp
+        ranks hold copies of: norm scales (all ranks) and shared key/value heads."""
         if getattr(self, "_rep_index", None) is None:
-            from .tp import REPLICATED_SEGMENTS
+            from .tp import REPLICATED_SEGMENTS, kv_replicas
 
-            pieces = []
+            kv_rep = kv_replicas(self.full_cfg, self.tp_world)
+            ql, kvl = self.cfg.query_width, self.cfg.key_value_width
+            classes: dict[int, list[torch.Tensor]] = {}
             for name, u in self.units.items():
                 lo, hi = self.rank * u.shard_elems, (self.rank + 1) * u.shard_elems
                 for seg in u.layout.segments:
                     if seg.name in REPLICATED_SEGMENTS:
-                        a, b = max(seg.offset, lo), min(seg.offset + seg.numel, hi)
-                        if b > a:
-                            pieces.append(torch.arange(u.arena_offset + a - lo, u.arena_offset + b - lo,
-                                                       device=self.device))
-            self._rep_index = torch.cat(pieces) if pieces else torch.zeros(0, dtype=torch.long, device=self.device)
+                        a, b, copies = seg.offset, seg.offset + seg.numel, self.tp_world
+                    elif kv_rep > 1 and seg.name in ("qkv_w", "qkv_b"):
+                        inner = seg.numel // seg.shape[0]
+                        a, b, copies = seg.offset + ql * inner, seg.offset + (ql + 2 * kvl) * inner, kv_rep
+                    else:
+                        continue
+                    a, b = max(a, lo), min(b, hi)
+                    if b > a:
+                        classes.setdefault(copies, []).append(
+                            torch.arange(u.arena_offset + a - lo, u.arena_offset + b - lo, device=self.device))
+            self._rep_index = [(torch.cat(v), k) for k, v in classes.items()]
         return self._rep_index
 
     # ------------------------------------------------------------------ step driver

@@ -41,13 +41,27 @@ PULL_CTAS = 64
 REDUCE_CTAS = 148
 
 
+def kv_replicas(cfg: ModelConfig, tp: int) -> int:
+    """How many tp ranks hold a copy of the same key/value head (1 when every rank has its own)."""
+    if cfg.num_key_value_heads % tp == 0:
+        return 1
+    if tp % cfg.num_key_value_heads:
+        raise ValueError(f"tp={tp} must divide, or be a multiple of, the key/value heads ({cfg.num_key_value_heads})")
+    return tp // cfg.num_key_value_heads
+
+
 def tp_local_config(cfg: ModelConfig, tp: int) -> ModelConfig:
-    """Shapes of one tensor-parallel slice: heads, FFN width and vocabulary divided by ``tp``."""
+    """Shapes of one tensor-parallel slice: heads, FFN width and vocabulary divided by ``tp``.
+
+    With fewer key/value heads than ranks (MQA: one head) every rank keeps one whole K/V head, a
+    copy shared by ``tp / Hkv`` ranks, as the reference replicates its single K/V head over tp
+    (src/causal_trainer/kernels/efficient_attention.py:305).
+    """
     if tp == 1:
         return cfg
-    if cfg.num_attention_heads % tp or cfg.num_key_value_heads % tp:
-        raise ValueError(f"tp={tp} must divide the query heads ({cfg.num_attention_heads}) and the key/value heads "
-                         f"({cfg.num_key_value_heads})")
+    if cfg.num_attention_heads % tp:
+        raise ValueError(f"tp={tp} must divide the query heads ({cfg.num_attention_heads})")
+    rep = kv_replicas(cfg, tp)
     if cfg.intermediate_size % tp or cfg.vocab_size % tp:
         raise ValueError(f"tp={tp} must divide intermediate_size and vocab_size")
     if (cfg.intermediate_size // tp) % 8:
@@ -55,7 +69,8 @@ def tp_local_config(cfg: ModelConfig, tp: int) -> ModelConfig:
     local_vocab = cfg.vocab_size // tp
     eos = cfg.eos_token_id if isinstance(cfg.eos_token_id, tuple) else (cfg.eos_token_id,)
     return dataclasses.replace(
-        cfg, num_attention_heads=cfg.num_attention_heads // tp, num_key_value_heads=cfg.num_key_value_heads // tp,
+        cfg, num_attention_heads=cfg.num_attention_heads // tp,
+        num_key_value_heads=1 if rep > 1 else cfg.num_key_value_heads // tp,
         intermediate_size=cfg.intermediate_size // tp, vocab_size=local_vocab,
         # token ids stay global; the slice only needs ids that validate against its own row count
         pad_token_id=min(cfg.pad_token_id, local_vocab - 1), eos_token_id=tuple(min(e, local_vocab - 1) for e in eos))
@@ -67,10 +82,13 @@ def slice_unit_tensor(name: str, full: torch.Tensor, cfg: ModelConfig, tp: int, 
     if tp == 1 or name in ("ln1", "ln2", "norm"):
         return full
     q, kv, f = cfg.query_width, cfg.key_value_width, cfg.intermediate_size
-    ql, kvl, fl = q // tp, kv // tp, f // tp
+    ql, fl = q // tp, f // tp
+    rep = kv_replicas(cfg, tp)
+    kvl = cfg.head_dim if rep > 1 else kv // tp
+    kv_index = rank // rep if rep > 1 else rank
     if name in ("qkv_w", "qkv_b"):
-        parts = [full[rank * ql:(rank + 1) * ql], full[q + rank * kvl:q + (rank + 1) * kvl],
-                 full[q + kv + rank * kvl:q + kv + (rank + 1) * kvl]]
+        parts = [full[rank * ql:(rank + 1) * ql], full[q + kv_index * kvl:q + (kv_index + 1) * kvl],
+                 full[q + kv + kv_index * kvl:q + kv + (kv_index + 1) * kvl]]
         return torch.cat(parts, 0)
     if name == "gu_w":
         return torch.cat([full[rank * fl:(rank + 1) * fl], full[f + rank * fl:f + (rank + 1) * fl]], 0)
@@ -89,9 +107,12 @@ def merge_unit_tensor(name: str, parts: list[torch.Tensor], cfg: ModelConfig) ->
     tp = len(parts)
     if tp == 1 or name in ("ln1", "ln2", "norm"):
         return parts[0]
-    ql, kvl, fl = cfg.query_width // tp, cfg.key_value_width // tp, cfg.intermediate_size // tp
+    ql, fl = cfg.query_width // tp, cfg.intermediate_size // tp
+    rep = kv_replicas(cfg, tp)
+    kvl = cfg.head_dim if rep > 1 else cfg.key_value_width // tp
     if name in ("qkv_w", "qkv_b"):
-        return torch.cat([p[:ql] for p in parts] + [p[ql:ql + kvl] for p in parts] + [p[ql + kvl:] for p in parts], 0)
+        owners = parts[::rep]                      # one rank per key/value head
+        return torch.cat([p[:ql] for p in parts] + [p[ql:ql + kvl] for p in owners] + [p[ql + kvl:] for p in owners], 0)
     if name == "gu_w":
         return torch.cat([p[:fl] for p in parts] + [p[fl:] for p in parts], 0)
     if name in ("o_w", "down_w"):

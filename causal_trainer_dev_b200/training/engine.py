@@ -68,6 +68,7 @@ class EngineOptions:
     train_embed: bool = True
     train_norm: bool = True
     remat: str = "auto"                      # "auto" | "full" | "none"
+    compact_loss_rows: bool = True           # run the LM head only on rows with non-zero loss weight
     loss_backend: str = "cut"                # "cut": projection-fused; "logits": materialised bf16 logits slab per chunk
     memory_reserve_bytes: int = 8 << 30
 
@@ -303,6 +304,27 @@ class LayerwiseEngine:
         targets, weights = losses.aligned_targets_and_weights(batch)
         targets, weights = targets.reshape(-1), weights.reshape(-1)
         train_head = self.options.train_lm_head
+        # Active-row compaction: with sparse supervision (assistant-only loss, MaskGIT targets) only
+        # the rows that carry weight go through the LM head; their gradients are scattered back.
+        # (src/causal_trainer/kernels/cut_cross_entropy.py:673-694; stable order, so results do not
+        # depend on it.)
+        full_rows = y.shape[0]
+        active = None
+        if self.options.compact_loss_rows:
+            idx = torch.nonzero(weights != 0).reshape(-1)
+            if idx.numel() < 0.9 * full_rows:
+                pad = (-idx.numel()) % 128
+                if pad:      # whole 128-row tiles; padding repeats row 0 with zero weight
+                    idx_p = torch.cat([idx, idx.new_zeros(pad)])
+                    wmask = torch.cat([torch.ones_like(idx, dtype=weights.dtype), weights.new_zeros(pad)])
+                else:
+                    idx_p, wmask = idx, torch.ones_like(idx, dtype=weights.dtype)
+                active = idx_p
+                y_all = y
+                y = y_all.index_select(0, idx_p)
+                targets = targets.index_select(0, idx_p)
+                weights = weights.index_select(0, idx_p) * wmask
+                self._count(6)
         if self.options.loss_backend == "logits":
             nll, wsum, dy, _ = ce.logits_ce_forward_backward(
                 y, fw["lm_head"], targets, weights, grad_scale, chunk_rows=self.options.cut_chunk_rows,
@@ -313,6 +335,10 @@ class LayerwiseEngine:
                                        need_dhead=train_head, dhead_out=fg["lm_head"] if train_head else None,
                                        dhead_accumulate=accumulate)
         self._count(4 + 3 * ((y.shape[0] + self.options.cut_chunk_rows - 1) // self.options.cut_chunk_rows))
+        if active is not None:
+            dy_full = torch.zeros((full_rows, dy.shape[1]), dtype=dy.dtype, device=dy.device)
+            dy_full.index_add_(0, active, dy)     # padded slots carry zero gradient (zero weight)
+            dy, y = dy_full, y_all
         dout, _ = ew.rmsnorm_backward(dy, xf, fw["norm"], rstd_f, dw_out=fg["norm"], dw_accumulate=accumulate)
         del y, dy, xf
         prov.release("final")

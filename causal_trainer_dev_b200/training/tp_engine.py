@@ -25,7 +25,7 @@ from ..ops import attention as attn_ops
 from ..ops import cross_entropy as ce
 from ..ops import elementwise as ew
 from ..ops.gemm import gemm
-from ..parallel.tp import Gathered, TpContext, tp_local_config
+from ..parallel.tp import Gathered, TpContext, kv_replicas, tp_local_config
 from . import losses
 from .engine import EngineOptions, LayerwiseEngine
 
@@ -42,6 +42,13 @@ class TpLayerwiseEngine(LayerwiseEngine):
         self.fused = fused
         self._contexts: dict[int, TpContext] = {}
         super().__init__(tp_local_config(full_cfg, self.tp_world), provider, options)
+        # fewer key/value heads than ranks: the ranks that share a head sum its weight gradients
+        self.kv_rep = kv_replicas(full_cfg, self.tp_world)
+        self.kv_group = None
+        if self.kv_rep > 1:
+            ranks = dist.get_process_group_ranks(tp_group)
+            first = self.tp_rank // self.kv_rep * self.kv_rep
+            self.kv_group = dist.new_group(ranks[first:first + self.kv_rep], use_local_synchronization=True)
 
     # ------------------------------------------------------------------ context
     def _tp(self, rows: int) -> TpContext:
@@ -246,6 +253,11 @@ class TpLayerwiseEngine(LayerwiseEngine):
             ln = unit.layout.segment("ln1")
             ln2 = unit.layout.segment("ln2")
             tp.all_reduce_replicated([gbuf[ln.offset:ln2.offset + ln2.numel]])
+            if self.kv_group is not None:
+                ql = cfg.query_width
+                dist.all_reduce(g["qkv_w"][ql:], group=self.kv_group)
+                if "qkv_b" in g:
+                    dist.all_reduce(g["qkv_b"][ql:], group=self.kv_group)
             prov.release(f"layer.{li}")
             prov.grads_ready(f"layer.{li}", last)
         # ---------------- embedding (vocabulary-parallel) ----------------

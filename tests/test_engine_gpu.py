@@ -106,3 +106,32 @@ def test_engine_with_moba_layers_matches_oracle(cuda_lib):
                  "model.layers.0.mlp.down_proj.weight", "lm_head.weight"):
         assert _rel(eng_params.grad_tensor(name), ref.grad_tensor(name)) < 0.1, name
     assert cuda_lib.device_status() == (0, 0, 0, 0)
+
+
+@pytest.mark.parametrize("backend", ["cut", "logits"])
+def test_engine_sparse_supervision_compacts_rows(cuda_lib, backend):
+    """Assistant-only style loss weights: the LM head runs on the supervised rows only (row
+    compaction) and both loss backends agree with the oracle."""
+    from causal_trainer_dev_b200.models.config import preset
+    from causal_trainer_dev_b200.models.decoder import ForwardOptions
+    from causal_trainer_dev_b200.models.params import ModelParams
+    from causal_trainer_dev_b200.training.engine import EngineOptions, LayerwiseEngine, LocalProvider
+    from causal_trainer_dev_b200.training.steps import AutogradProducer
+
+    cfg = preset("tiny", vocab_size=4096)
+    base = ModelParams.init_random(cfg, seed=4, dtype=torch.bfloat16)
+    batch = _batch(cfg, 2, 256)
+    g = torch.Generator().manual_seed(9)
+    batch["loss_weights"] = (torch.rand(2, 256, generator=g) < 0.3).float().cuda()
+    ref = ModelParams(cfg, dtype=torch.float32, device="cuda")
+    ref.load_state_dict({k: v.float() for k, v in base.state_dict().items()})
+    nll_ref, w_ref = AutogradProducer(ref, ForwardOptions(attn_mechanism="vanilla"))(batch, 1.0 / 150, True)
+    eng_params = ModelParams(cfg, dtype=torch.bfloat16, device="cuda")
+    eng_params.load_state_dict(base.state_dict())
+    engine = LayerwiseEngine(cfg, LocalProvider(eng_params, torch.float32), EngineOptions(loss_backend=backend))
+    nll, wsum = engine(batch, 1.0 / 150, True)
+    assert abs(wsum.item() - w_ref.item()) < 1e-3 and w_ref.item() < 0.5 * 512
+    assert abs(nll.item() - nll_ref.item()) / nll_ref.item() < 5e-3
+    for name in ("lm_head.weight", "model.norm.weight", "model.layers.1.mlp.down_proj.weight",
+                 "model.layers.0.self_attn.q_proj.weight", "model.embed_tokens.weight"):
+        assert _rel(eng_params.grad_tensor(name), ref.grad_tensor(name)) < 0.06, name

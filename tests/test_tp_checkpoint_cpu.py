@@ -29,7 +29,8 @@ src, dst = Path(sys.argv[2]), Path(sys.argv[3])
 dist.init_process_group("gloo")
 rank = dist.get_rank()
 tp, fsdp = 2, 2
-full = preset("tiny", vocab_size=512, num_hidden_layers=2, intermediate_size=384, attention_bias=True)
+full = preset("tiny", vocab_size=512, num_hidden_layers=2, intermediate_size=384, attention_bias=True,
+              num_key_value_heads=int(sys.argv[4]))
 local = tp_local_config(full, tp)
 
 
@@ -65,13 +66,18 @@ dist.destroy_process_group()
 '''
 
 
-def test_tp_fsdp_load_and_export_roundtrip(tmp_path):
+import pytest
+
+
+@pytest.mark.parametrize("kv_heads", [2, 1])
+def test_tp_fsdp_load_and_export_roundtrip(tmp_path, kv_heads):
     from causal_trainer_dev_b200.checkpointing import huggingface as hfio
     from causal_trainer_dev_b200.checkpointing import safetensors_io as st
     from causal_trainer_dev_b200.models.config import preset
     from causal_trainer_dev_b200.models.params import ModelParams
 
-    cfg = preset("tiny", vocab_size=512, num_hidden_layers=2, intermediate_size=384, attention_bias=True)
+    cfg = preset("tiny", vocab_size=512, num_hidden_layers=2, intermediate_size=384, attention_bias=True,
+                 num_key_value_heads=kv_heads)
     params = ModelParams.init_random(cfg, seed=4)
     for name, t in params.named_tensors():      # biases and norm scales that are not constant
         if t.dim() == 1:
@@ -83,8 +89,8 @@ def test_tp_fsdp_load_and_export_roundtrip(tmp_path):
     script.write_text(WORKER)
     env = dict(os.environ, OMP_NUM_THREADS="1")
     res = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4",
-                          "--master-addr", "127.0.0.1", "--master-port", "29877", str(script), str(ROOT), str(src),
-                          str(dst)], capture_output=True, text=True, timeout=300, env=env)
+                          "--master-addr", "127.0.0.1", "--master-port", str(29877 + kv_heads), str(script), str(ROOT),
+                          str(src), str(dst), str(kv_heads)], capture_output=True, text=True, timeout=300, env=env)
     assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-3000:]
     a, b = st.load_file(src / "model.safetensors"), st.load_file(dst / "model.safetensors")
     assert list(a) == list(b)
@@ -99,7 +105,8 @@ def test_tp_window_agrees_with_unit_slicing():
     from causal_trainer_dev_b200.models.params import ModelParams
     from causal_trainer_dev_b200.parallel.tp import slice_unit_tensor, tp_local_config
 
-    cfg = preset("tiny", vocab_size=512, num_hidden_layers=1, intermediate_size=384, attention_bias=True)
+    cfg = preset("tiny", vocab_size=512, num_hidden_layers=1, intermediate_size=384, attention_bias=True,
+                 num_key_value_heads=1)
     full = ModelParams.init_random(cfg, seed=1, dtype=torch.float32)
     tp = 2
     local_cfg = tp_local_config(cfg, tp)

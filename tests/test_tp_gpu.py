@@ -62,3 +62,12 @@ def test_fsdp2_tp2_training_matches_fsdp4(cuda_lib, tmp_path):
     fsdp = _launch(["train", "1", "fused", "3"], 4, tmp_path / "fsdp4.json", 29636)
     assert mixed["status"] == [0, 0, 0, 0]
     _close(mixed["history"], fsdp["history"], 2e-2, 3e-2)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_tp2_with_one_shared_kv_head_matches_fsdp2(cuda_lib, tmp_path):
+    """MQA: both tensor-parallel ranks keep a copy of the single key/value head and sum its gradients."""
+    tp = _launch(["train", "2", "fused", "3", "1"], 2, tmp_path / "tp_mqa.json", 29637)
+    fsdp = _launch(["train", "1", "fused", "3", "1"], 2, tmp_path / "fsdp_mqa.json", 29638)
+    assert tp["status"] == [0, 0, 0, 0]
+    _close(tp["history"], fsdp["history"], 2e-2, 3e-2)
