@@ -150,23 +150,28 @@ def _row_stride(t: torch.Tensor) -> int:
 
 def flash_attention_forward(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: AttentionMeta, scale: float | None = None,
-    out: torch.Tensor | None = None, spin_budget: int = 0,
+    out: torch.Tensor | None = None, spin_budget: int = 0, q_offset: int = 0,
 ) -> tuple[torch.Tensor, torch.Tensor]:
-    """Runs the tcgen05 forward kernel; returns (O [B,S,Hq,D] bf16, LSE [B,Hq,S] fp32)."""
-    b, s, hq, d = q.shape
+    """Runs the tcgen05 forward kernel; returns (O [B,Sq,Hq,D] bf16, LSE [B,Hq,Sq] fp32).
+
+    Under sequence parallelism ``q`` holds only the queries ``[q_offset, q_offset + Sq)`` of every
+    row while ``k`` / ``v`` (and ``meta``) cover the whole sequence.
+    """
+    b, sq, hq, d = q.shape
+    s = k.shape[1]
     hkv = k.shape[2]
     scale = 1.0 / math.sqrt(d) if scale is None else scale
     if out is None:
-        out = torch.empty((b, s, hq, d), dtype=torch.bfloat16, device=q.device)
-    lse = torch.empty((b, hq, s), dtype=torch.float32, device=q.device)
-    code = _lib.lib().ctb_attn_fwd(
+        out = torch.empty((b, sq, hq, d), dtype=torch.bfloat16, device=q.device)
+    lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
+    code = _lib.lib().ctb_attn_fwd_range(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(meta.seg), _lib.ptr(meta.lim),
         _lib.ptr(meta.kv_lo), _lib.ptr(meta.kv_hi), _lib.ptr(meta.kmin), _lib.ptr(meta.kmax),
-        b, s, hq, hkv, d, ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)),
+        b, s, sq, q_offset, hq, hkv, d, ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)),
         ctypes.c_long(_row_stride(v)), ctypes.c_long(_row_stride(out)), ctypes.c_float(scale),
         ctypes.c_longlong(spin_budget), _lib.stream_ptr(),
     )
-    _lib.check(code, "ctb_attn_fwd")
+    _lib.check(code, "ctb_attn_fwd_range")
     return out, lse
 
 
@@ -174,31 +179,37 @@ def flash_attention_backward(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, dout: torch.Tensor, lse: torch.Tensor,
     meta: AttentionMeta, scale: float | None = None, spin_budget: int = 0,
     dq: torch.Tensor | None = None, dk: torch.Tensor | None = None, dv: torch.Tensor | None = None,
+    q_offset: int = 0,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
-    """dQ (query-tile-owned kernel) and dK/dV (key-tile-owned kernel, group reduced in TMEM)."""
-    b, s, hq, d = q.shape
+    """dQ (query-tile-owned kernel) and dK/dV (key-tile-owned kernel, group reduced in TMEM).
+
+    With a query range (``q_offset``, ``Sq < S``) dK / dV are this rank's partial sums over its
+    queries, for all ``S`` keys.
+    """
+    b, sq, hq, d = q.shape
+    s = k.shape[1]
     hkv = k.shape[2]
     scale = 1.0 / math.sqrt(d) if scale is None else scale
     from .elementwise import attention_delta
 
     _row_stride(out), _row_stride(dout)
-    delta = attention_delta(out, dout)  # [B,Hq,S] fp32
-    dq = torch.empty((b, s, hq, d), dtype=torch.bfloat16, device=q.device) if dq is None else dq
+    delta = attention_delta(out, dout)  # [B,Hq,Sq] fp32
+    dq = torch.empty((b, sq, hq, d), dtype=torch.bfloat16, device=q.device) if dq is None else dq
     dk = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dk is None else dk
     dv = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dv is None else dv
     L = _lib.lib()
     for mode in (0, 1):
-        code = L.ctb_attn_bwd(
+        code = L.ctb_attn_bwd_range(
             mode, _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
             _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(meta.seg), _lib.ptr(meta.lim), _lib.ptr(meta.kv_lo),
             _lib.ptr(meta.kv_hi), _lib.ptr(meta.q_lo), _lib.ptr(meta.q_hi), _lib.ptr(meta.seg_min64),
             _lib.ptr(meta.seg_max64), _lib.ptr(meta.lim_min64), _lib.ptr(meta.lim_max64),
-            b, s, hq, hkv, d,
+            b, s, sq, q_offset, hq, hkv, d,
             ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)), ctypes.c_long(_row_stride(v)),
             ctypes.c_long(_row_stride(dout)), ctypes.c_long(_row_stride(dq)), ctypes.c_long(_row_stride(dk)),
             ctypes.c_long(_row_stride(dv)), ctypes.c_float(scale), ctypes.c_longlong(spin_budget), _lib.stream_ptr(),
         )
-        _lib.check(code, "ctb_attn_bwd")
+        _lib.check(code, "ctb_attn_bwd_range")
     return dq, dk, dv
 
 

@@ -28,8 +28,12 @@ struct SparseArgs {
   int words;
 };
 
+// Sequence parallelism: a rank may hold only the queries [q_off, q_off + Sq) of every row while
+// keys and values cover the whole sequence of S tokens.  Q / O / dQ / dO / LSE / delta are then
+// indexed by the local query position, the visibility metadata by the global one.
 struct FwdArgs {
   int B, S, Hq, Hkv;
+  int Sq, q_off;
   float scale_log2;
   const int* seg;
   const int* lim;
@@ -47,6 +51,7 @@ struct FwdCall {
   const void* q; const void* k; const void* v; void* o; float* lse;
   const int* seg; const int* lim; const int* kv_lo; const int* kv_hi; const int* kmin; const int* kmax;
   int B, S, Hq, Hkv;
+  int Sq = 0, q_off = 0;     // Sq == 0: all S queries
   long q_row_stride, k_row_stride, v_row_stride, o_row_stride;
   float scale;
   long long spin_budget;
@@ -61,6 +66,7 @@ enum : int { MODE_DKV = 0, MODE_DQ = 1 };
 //   lim_min64 / lim_max64 [B,S/64]  min / max of lim over each 64-token block
 struct BwdArgs {
   int B, S, Hq, Hkv;
+  int Sq, q_off;
   float scale, scale_log2;
   const int* seg;
   const int* lim;
@@ -86,6 +92,7 @@ struct BwdCall {
   const int* seg; const int* lim; const int* kv_lo; const int* kv_hi; const int* q_lo; const int* q_hi;
   const int* seg_min64; const int* seg_max64; const int* lim_min64; const int* lim_max64;
   int B, S, Hq, Hkv;
+  int Sq = 0, q_off = 0;
   long q_row_stride, k_row_stride, v_row_stride, do_row_stride, dq_row_stride, dk_row_stride, dv_row_stride;
   float scale;
   long long spin_budget;

@@ -90,8 +90,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     b = idx % args.B;
     const int kb = idx / args.B;  // ascending: key blocks near the start see the most queries
     x0 = kb * 128;
-    const int qlo = args.q_lo[b * nb128 + kb];
-    const int qhi = args.q_hi[b * nb128 + kb];
+    // only the queries this rank holds, [q_off, q_off + Sq), are walked
+    const int qlo = max(args.q_lo[b * nb128 + kb], args.q_off);
+    const int qhi = min(args.q_hi[b * nb128 + kb], args.q_off + args.Sq);
     y_lo64 = qlo / 64;
     y_n64 = qhi > qlo ? (qhi + 63) / 64 - y_lo64 : 0;
     heads_in_loop = group;
@@ -99,10 +100,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     head = idx % args.Hq;       // query head
     idx /= args.Hq;
     b = idx % args.B;
-    const int qb = nb128 - 1 - idx / args.B;  // descending: late query blocks see the most keys
-    x0 = qb * 128;
-    const int klo = args.kv_lo[b * nb128 + qb];
-    const int khi = args.kv_hi[b * nb128 + qb];
+    const int qb = args.Sq / 128 - 1 - idx / args.B;  // descending: late query blocks see the most keys
+    x0 = qb * 128;                                    // row of the local Q / dO / dQ
+    const int klo = args.kv_lo[b * nb128 + args.q_off / 128 + qb];
+    const int khi = args.kv_hi[b * nb128 + args.q_off / 128 + qb];
     y_lo64 = klo / 64;
     y_n64 = khi > klo ? (khi + 63) / 64 - y_lo64 : 0;
     heads_in_loop = 1;
@@ -169,7 +170,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       uint32_t stage = 0, phase = 0;
       for (int it = 0; it < n_iter; ++it) {
         const int yh = DKV ? y_head(it) : hkv;
-        const int y0 = y_block(it) * 64;
+        const int y0 = y_block(it) * 64 - (DKV ? args.q_off : 0);   // streamed queries are stored locally
         if (!mbar_wait(&y_empty[stage], phase ^ 1u, abort_flag, st, SITE_B_PROD, budget)) break;
         mbar_expect_tx(&y_full[stage], 2 * L::YT);
         uint8_t* dst = smem + L::OFF_Y + stage * 2 * L::YT;
@@ -258,7 +259,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
     uint8_t* t_p = smem + L::OFF_T + u * 2 * L::TT;
     uint8_t* t_ds = t_p + L::TT;
-    const int xi = x0 + r;  // key index (DKV) or query index (DQ) of this thread's row
+    // position in the whole sequence of this thread's row: a key (DKV) or a local query (DQ)
+    const int xi = x0 + r + (DKV ? 0 : args.q_off);
+    const int xi_local = x0 + r;
     const float LOG2E = 1.4426950408889634f;
     int row_seg = args.seg[b * args.S + xi];
     int row_lim = xi;
@@ -268,8 +271,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     float row_lse2 = 0.f, row_delta = 0.f;
     if (!DKV) {
       if (args.lim != nullptr) row_lim = args.lim[b * args.S + xi];
-      row_lse2 = args.lse[(static_cast<size_t>(b) * args.Hq + head) * args.S + xi] * LOG2E;
-      row_delta = args.delta[(static_cast<size_t>(b) * args.Hq + head) * args.S + xi];
+      row_lse2 = args.lse[(static_cast<size_t>(b) * args.Hq + head) * args.Sq + xi_local] * LOG2E;
+      row_delta = args.delta[(static_cast<size_t>(b) * args.Hq + head) * args.Sq + xi_local];
     }
     bool ok = true;
     uint32_t sph = 0, dph = 0;
@@ -284,7 +287,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // computed (one value per thread of the first warpgroup of the pair) and shared below.
       float meta_v = 0.f;
       if (DKV && half == 0) {
-        const size_t base = (static_cast<size_t>(b) * args.Hq + hq) * args.S + y0;
+        const size_t base = (static_cast<size_t>(b) * args.Hq + hq) * args.Sq + (y0 - args.q_off);
         meta_v = (r < 64) ? __ldg(args.lse + base + r) * LOG2E : __ldg(args.delta + base + r - 64);
       }
       bool good = mbar_wait(&s_full[u], sph, abort_flag, st, SITE_B_CW_S, budget);
@@ -489,25 +492,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 template <int D, int MODE>
 int launch_bwd(const BwdCall& c) {
   using L = BwdSmem<D>;
-  auto make = [&](const void* base, int heads, long row_stride, int rows) -> const CUtensorMap* {
-    const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(heads), static_cast<uint64_t>(c.S),
+  const int Sq = c.Sq > 0 ? c.Sq : c.S;
+  auto make = [&](const void* base, int heads, long row_stride, int rows, int seq) -> const CUtensorMap* {
+    const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(heads), static_cast<uint64_t>(seq),
                               static_cast<uint64_t>(c.B)};
     const uint64_t strides[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(row_stride),
-                                 static_cast<uint64_t>(row_stride) * c.S};
+                                 static_cast<uint64_t>(row_stride) * seq};
     const uint32_t box[4] = {64, 1, static_cast<uint32_t>(rows), 1};
     return get_tensor_map_4d(base, Elt::BF16, dims, strides, box, true);
   };
   constexpr bool DKV = (MODE == MODE_DKV);
   // Resident operands use 128-row boxes, streamed operands 64-row boxes.
-  const CUtensorMap* mq = make(c.q, c.Hq, c.q_row_stride, DKV ? 64 : 128);
-  const CUtensorMap* mk = make(c.k, c.Hkv, c.k_row_stride, DKV ? 128 : 64);
-  const CUtensorMap* mv = make(c.v, c.Hkv, c.v_row_stride, DKV ? 128 : 64);
-  const CUtensorMap* mdo = make(c.dout, c.Hq, c.do_row_stride, DKV ? 64 : 128);
-  const CUtensorMap* mo1 = DKV ? make(c.dv, c.Hkv, c.dv_row_stride, 128) : make(c.dq, c.Hq, c.dq_row_stride, 128);
-  const CUtensorMap* mo2 = DKV ? make(c.dk, c.Hkv, c.dk_row_stride, 128) : mo1;
+  const CUtensorMap* mq = make(c.q, c.Hq, c.q_row_stride, DKV ? 64 : 128, Sq);
+  const CUtensorMap* mk = make(c.k, c.Hkv, c.k_row_stride, DKV ? 128 : 64, c.S);
+  const CUtensorMap* mv = make(c.v, c.Hkv, c.v_row_stride, DKV ? 128 : 64, c.S);
+  const CUtensorMap* mdo = make(c.dout, c.Hq, c.do_row_stride, DKV ? 64 : 128, Sq);
+  const CUtensorMap* mo1 = DKV ? make(c.dv, c.Hkv, c.dv_row_stride, 128, c.S)
+                               : make(c.dq, c.Hq, c.dq_row_stride, 128, Sq);
+  const CUtensorMap* mo2 = DKV ? make(c.dk, c.Hkv, c.dk_row_stride, 128, c.S) : mo1;
   if (!mq || !mk || !mv || !mdo || !mo1 || !mo2) return 1;
   BwdArgs a{};
   a.B = c.B; a.S = c.S; a.Hq = c.Hq; a.Hkv = c.Hkv;
+  a.Sq = Sq; a.q_off = c.q_off;
   a.scale = c.scale;
   a.scale_log2 = c.scale * 1.4426950408889634f;
   a.seg = c.seg; a.lim = c.lim; a.kv_lo = c.kv_lo; a.kv_hi = c.kv_hi; a.q_lo = c.q_lo; a.q_hi = c.q_hi;
@@ -524,7 +530,7 @@ int launch_bwd(const BwdCall& c) {
     CTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES));
     configured_dev = dev;
   }
-  const int grid = c.B * (DKV ? c.Hkv : c.Hq) * (c.S / 128);
+  const int grid = DKV ? c.B * c.Hkv * (c.S / 128) : c.B * c.Hq * (Sq / 128);
   kern<<<grid, BWD_THREADS, L::BYTES, static_cast<cudaStream_t>(c.stream)>>>(*mq, *mk, *mv, *mdo, *mo1, *mo2, a);
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
@@ -548,6 +554,32 @@ CTB_API int ctb_attn_bwd(int mode, const void* q, const void* k, const void* v, 
   c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi; c.q_lo = q_lo; c.q_hi = q_hi;
   c.seg_min64 = seg_min64; c.seg_max64 = seg_max64; c.lim_min64 = lim_min64; c.lim_max64 = lim_max64;
   c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
+  c.q_row_stride = q_rs; c.k_row_stride = k_rs; c.v_row_stride = v_rs; c.do_row_stride = do_rs;
+  c.dq_row_stride = dq_rs; c.dk_row_stride = dk_rs; c.dv_row_stride = dv_rs;
+  c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
+  using namespace ctb::attn;
+  if (D == 128) return mode == 0 ? launch_bwd<128, MODE_DKV>(c) : launch_bwd<128, MODE_DQ>(c);
+  if (D == 64) return mode == 0 ? launch_bwd<64, MODE_DKV>(c) : launch_bwd<64, MODE_DQ>(c);
+  return ctb::fail("attention: head_dim must be 64 or 128");
+}
+
+// Sequence-parallel backward: q / dout / dq, lse and delta hold the Sq queries [q_off, q_off + Sq)
+// of every row; k / v / dk / dv cover all S keys (dk / dv are this rank's partial sums).
+CTB_API int ctb_attn_bwd_range(int mode, const void* q, const void* k, const void* v, const void* dout, void* dq,
+                               void* dk, void* dv, const float* lse, const float* delta, const int* seg,
+                               const int* lim, const int* kv_lo, const int* kv_hi, const int* q_lo, const int* q_hi,
+                               const int* seg_min64, const int* seg_max64, const int* lim_min64,
+                               const int* lim_max64, int B, int S, int Sq, int q_off, int Hq, int Hkv, int D,
+                               long q_rs, long k_rs, long v_rs, long do_rs, long dq_rs, long dk_rs, long dv_rs,
+                               float scale, long long spin_budget, void* stream) {
+  if (S % 128 || Sq % 128 || q_off % 128 || q_off < 0 || q_off + Sq > S)
+    return ctb::fail("attention: S, Sq and q_off must be multiples of 128 with q_off + Sq <= S");
+  if (Hq % Hkv) return ctb::fail("attention: Hq must be a multiple of Hkv");
+  ctb::attn::BwdCall c{};
+  c.q = q; c.k = k; c.v = v; c.dout = dout; c.dq = dq; c.dk = dk; c.dv = dv; c.lse = lse; c.delta = delta;
+  c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi; c.q_lo = q_lo; c.q_hi = q_hi;
+  c.seg_min64 = seg_min64; c.seg_max64 = seg_max64; c.lim_min64 = lim_min64; c.lim_max64 = lim_max64;
+  c.B = B; c.S = S; c.Sq = Sq; c.q_off = q_off; c.Hq = Hq; c.Hkv = Hkv;
   c.q_row_stride = q_rs; c.k_row_stride = k_rs; c.v_row_stride = v_rs; c.do_row_stride = do_rs;
   c.dq_row_stride = dq_rs; c.dk_row_stride = dk_rs; c.dv_row_stride = dv_rs;
   c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;

@@ -74,7 +74,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const long long budget = args.spin_budget;
 
   // ---- work item ----
-  const int nqp = (args.S + 255) / 256;
+  const int nqp = (args.Sq + 255) / 256;
   int idx = blockIdx.x;
   const int h = idx % args.Hq;
   idx /= args.Hq;
@@ -87,11 +87,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   int lo_t[2], hi_t[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    tile_valid[t] = (q0 + t * 128) < args.S;
+    tile_valid[t] = (q0 + t * 128) < args.Sq;
     lo_t[t] = 0;
     hi_t[t] = 0;
     if (tile_valid[t]) {
-      const int qb = q0 / 128 + t;
+      const int qb = (args.q_off + q0) / 128 + t;      // query block in the whole sequence
       const int lo_tok = args.kv_lo[b * nqb + qb];
       const int hi_tok = args.kv_hi[b * nqb + qb];
       if (hi_tok > lo_tok) {
@@ -260,7 +260,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     uint8_t* pbuf = smem + L::OFF_P + t * L::PT;
     bool ok = true;
     float m_ref = -INFINITY, l_sum = 0.f;
-    const int qi = q0 + t * 128 + r;
+    const int qi_local = q0 + t * 128 + r;             // row of Q / O / LSE held by this rank
+    const int qi = args.q_off + qi_local;              // its position in the whole sequence
     int my_seg = 0, my_lim = qi, my_start = 0;
     if (tile_valid[t]) {
       my_seg = args.seg[b * args.S + qi];
@@ -419,7 +420,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tma_wait_group<0>();
       }
       const float lse = (l_sum > 0.f) ? (m_ref + log2f(l_sum)) * 0.6931471805599453f : 0.f;
-      args.lse[(static_cast<size_t>(b) * args.Hq + h) * args.S + qi] = lse;
+      args.lse[(static_cast<size_t>(b) * args.Hq + h) * args.Sq + qi_local] = lse;
     }
   }
 
@@ -434,19 +435,20 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 template <int D>
 int launch_fwd(const FwdCall& c) {
   using L = FwdSmem<D>;
-  const uint64_t dq[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.Hq), static_cast<uint64_t>(c.S),
+  const int Sq = c.Sq > 0 ? c.Sq : c.S;
+  const uint64_t dq[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.Hq), static_cast<uint64_t>(Sq),
                           static_cast<uint64_t>(c.B)};
   const uint64_t dk[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.Hkv), static_cast<uint64_t>(c.S),
                           static_cast<uint64_t>(c.B)};
   const uint32_t box[4] = {64, 1, 128, 1};
   const uint64_t sq[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.q_row_stride),
-                          static_cast<uint64_t>(c.q_row_stride) * c.S};
+                          static_cast<uint64_t>(c.q_row_stride) * Sq};
   const uint64_t sk[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.k_row_stride),
                           static_cast<uint64_t>(c.k_row_stride) * c.S};
   const uint64_t sv[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.v_row_stride),
                           static_cast<uint64_t>(c.v_row_stride) * c.S};
   const uint64_t so[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.o_row_stride),
-                          static_cast<uint64_t>(c.o_row_stride) * c.S};
+                          static_cast<uint64_t>(c.o_row_stride) * Sq};
   const CUtensorMap* mq = get_tensor_map_4d(c.q, Elt::BF16, dq, sq, box, true);
   const CUtensorMap* mk = get_tensor_map_4d(c.k, Elt::BF16, dk, sk, box, true);
   const CUtensorMap* mv = get_tensor_map_4d(c.v, Elt::BF16, dk, sv, box, true);
@@ -454,6 +456,7 @@ int launch_fwd(const FwdCall& c) {
   if (!mq || !mk || !mv || !mo) return 1;
   FwdArgs a{};
   a.B = c.B; a.S = c.S; a.Hq = c.Hq; a.Hkv = c.Hkv;
+  a.Sq = Sq; a.q_off = c.q_off;
   a.scale_log2 = c.scale * 1.4426950408889634f;
   a.seg = c.seg; a.lim = c.lim; a.kv_lo = c.kv_lo; a.kv_hi = c.kv_hi; a.kmin = c.kmin; a.kmax = c.kmax;
   a.lse = c.lse;
@@ -468,7 +471,7 @@ int launch_fwd(const FwdCall& c) {
     CTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES));
     configured_dev = dev;
   }
-  const int grid = c.B * c.Hq * ((c.S + 255) / 256);
+  const int grid = c.B * c.Hq * ((Sq + 255) / 256);
   kern<<<grid, FWD_THREADS, L::BYTES, static_cast<cudaStream_t>(c.stream)>>>(*mq, *mk, *mv, *mo, a);
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
@@ -488,6 +491,26 @@ CTB_API int ctb_attn_fwd(const void* q, const void* k, const void* v, void* o, f
   ctb::attn::FwdCall c{};
   c.q = q; c.k = k; c.v = v; c.o = o; c.lse = lse; c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi;
   c.kmin = kmin; c.kmax = kmax; c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
+  c.q_row_stride = q_row_stride; c.k_row_stride = k_row_stride; c.v_row_stride = v_row_stride;
+  c.o_row_stride = o_row_stride; c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
+  if (D == 128) return ctb::attn::launch_fwd<128>(c);
+  if (D == 64) return ctb::attn::launch_fwd<64>(c);
+  return ctb::fail("attention: head_dim must be 64 or 128");
+}
+
+// Sequence-parallel forward: q / o hold the Sq queries [q_off, q_off + Sq) of every row, k / v all
+// S keys; lse is [B, Hq, Sq].  q_off and Sq must be multiples of 128.
+CTB_API int ctb_attn_fwd_range(const void* q, const void* k, const void* v, void* o, float* lse, const int* seg,
+                               const int* lim, const int* kv_lo, const int* kv_hi, const int* kmin, const int* kmax,
+                               int B, int S, int Sq, int q_off, int Hq, int Hkv, int D, long q_row_stride,
+                               long k_row_stride, long v_row_stride, long o_row_stride, float scale,
+                               long long spin_budget, void* stream) {
+  if (S % 128 || Sq % 128 || q_off % 128 || q_off < 0 || q_off + Sq > S)
+    return ctb::fail("attention: S, Sq and q_off must be multiples of 128 with q_off + Sq <= S");
+  if (Hq % Hkv) return ctb::fail("attention: Hq must be a multiple of Hkv");
+  ctb::attn::FwdCall c{};
+  c.q = q; c.k = k; c.v = v; c.o = o; c.lse = lse; c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi;
+  c.kmin = kmin; c.kmax = kmax; c.B = B; c.S = S; c.Sq = Sq; c.q_off = q_off; c.Hq = Hq; c.Hkv = Hkv;
   c.q_row_stride = q_row_stride; c.k_row_stride = k_row_stride; c.v_row_stride = v_row_stride;
   c.o_row_stride = o_row_stride; c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
   if (D == 128) return ctb::attn::launch_fwd<128>(c);

@@ -95,3 +95,38 @@ def test_deterministic(cuda_lib):
     _, second = _run(2, 512, 4, 2, 128, seg, seed=5)
     for a, c in zip(first, second):
         assert torch.equal(a, c)
+
+
+def test_query_range_matches_slices_of_the_full_pass(cuda_lib):
+    """Sequence parallelism: a rank that holds queries [q_off, q_off + Sq) and all keys gets the
+    same O / LSE / dQ rows as the full pass, and the ranks' partial dK / dV add up to the full ones."""
+    from causal_trainer_dev_b200.ops import attention as A
+
+    torch.manual_seed(7)
+    b, s, hq, hkv, d, parts = 2, 1024, 4, 2, 128, 4
+    seg = torch.ones(b, s, dtype=torch.int32, device="cuda")
+    seg[0, 300:] = 2
+    seg[0, 900:] = 0
+    seg[1, 517:] = 2
+    meta = A.build_attention_meta(seg)
+    q = (torch.randn(b, s, hq, d, device="cuda") * 0.7).bfloat16()
+    k = (torch.randn(b, s, hkv, d, device="cuda") * 0.7).bfloat16()
+    v = torch.randn(b, s, hkv, d, device="cuda").bfloat16()
+    do = torch.randn(b, s, hq, d, device="cuda").bfloat16()
+    o, lse = A.flash_attention_forward(q, k, v, meta)
+    dq, dk, dv = A.flash_attention_backward(q, k, v, o, do, lse, meta)
+    sq = s // parts
+    dk_sum = torch.zeros_like(dk, dtype=torch.float32)
+    dv_sum = torch.zeros_like(dv, dtype=torch.float32)
+    for r in range(parts):
+        sl = slice(r * sq, (r + 1) * sq)
+        q_r, do_r = q[:, sl].contiguous(), do[:, sl].contiguous()
+        o_r, lse_r = A.flash_attention_forward(q_r, k, v, meta, q_offset=r * sq)
+        assert torch.equal(o_r, o[:, sl]) and torch.equal(lse_r, lse[:, :, sl])
+        dq_r, dk_r, dv_r = A.flash_attention_backward(q_r, k, v, o_r, do_r, lse_r, meta, q_offset=r * sq)
+        assert torch.equal(dq_r, dq[:, sl])
+        dk_sum += dk_r.float()
+        dv_sum += dv_r.float()
+    assert (dk_sum - dk.float()).abs().max() <= 0.02 * dk.float().abs().max()
+    assert (dv_sum - dv.float()).abs().max() <= 0.02 * dv.float().abs().max()
+    assert cuda_lib.device_status() == (0, 0, 0, 0)
