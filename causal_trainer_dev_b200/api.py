@@ -35,6 +35,7 @@ class TrainerConfig:
     init: str = "normal"               # "normal": N(0, initializer_range) on the device; "hf": ModelParams.init_random
     remat: str = "auto"                # "auto": keep activations that fit, recompute the rest; "full"; "none"
     tp: int = 1                        # tensor-parallel degree; ranks are laid out (fsdp, tp) with tp fastest
+    sp: int = 1                        # sequence-parallel degree (queries sharded, K/V all-gathered); needs tp == 1
     force_sharded_runtime: bool = False  # run the FSDP runtime even on one rank (measures its own overhead)
 
 
@@ -48,7 +49,24 @@ class Trainer:
         self._bytes_h2d = 0
         self._bytes_d2h = 0
         self.data_rank, self.data_world = self.rank, self.world
-        if self.cfg.tp > 1:
+        if self.cfg.sp > 1:
+            from .parallel.fsdp import FsdpRuntime
+            from .parallel.runtime import RankLattice
+            from .training.sp_engine import SpLayerwiseEngine
+
+            if self.cfg.tp > 1:
+                raise ValueError("sp > 1 and tp > 1 cannot be combined")
+            if self.world % self.cfg.sp:
+                raise ValueError(f"sp={self.cfg.sp} must divide the number of ranks ({self.world})")
+            self.lattice = RankLattice((1, self.world // self.cfg.sp, 1, 1, self.cfg.sp), self.rank)
+            shard_group = self.lattice.group(("fsdp", "sp"))      # sp ranks are further FSDP ranks
+            sp_group = self.lattice.group(("sp",))
+            self.data_rank, self.data_world = self.lattice.coords()["fsdp"], self.world // self.cfg.sp
+            self.runtime = FsdpRuntime(model, self.cfg, self.device, group=shard_group)
+            self.engine = SpLayerwiseEngine(model, sp_group, self.runtime,
+                                            EngineOptions(cut_chunk_rows=self.cfg.cut_chunk_rows, remat=self.cfg.remat))
+            self.step_fn = self.runtime.make_step(self.engine)
+        elif self.cfg.tp > 1:
             from .parallel.fsdp import FsdpRuntime
             from .parallel.runtime import RankLattice
             from .parallel.tp import tp_local_config

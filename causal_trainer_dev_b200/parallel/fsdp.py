@@ -499,7 +499,7 @@ class FsdpStep:
         total = None
         for b in micro_batches:
             _, w = losses.aligned_targets_and_weights(b)
-            s = w.sum(dtype=torch.float32)
+            s = self.engine.select_tokens(w).sum(dtype=torch.float32)
             total = s if total is None else total + s
         total = total.reshape(1).clone()
         dist.all_reduce(total, group=rt.group)

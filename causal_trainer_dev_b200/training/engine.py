@@ -92,6 +92,11 @@ class LayerwiseEngine:
     def _count(self, n: int = 1) -> None:
         self.launches += n
 
+    def select_tokens(self, t: torch.Tensor) -> torch.Tensor:
+        """The part of a ``[B, S, ...]`` batch tensor this rank computes on (everything, unless the
+        sequence is split over ranks)."""
+        return t
+
     def _wgrad(self, dy: torch.Tensor, x: torch.Tensor, gview: torch.Tensor, accumulate: bool) -> None:
         gemm(dy, x, a_mn=True, b_mn=True, out=gview, accumulate=accumulate)
         self._count()
@@ -257,7 +262,7 @@ class LayerwiseEngine:
         ctx = self._context(batch)
         cfg = self.cfg
         embed = self.provider.acquire("embed")
-        resid = ew.embedding_gather(batch["input_ids"], embed.view("embed"))
+        resid = ew.embedding_gather(self.select_tokens(batch["input_ids"]), embed.view("embed"))
         self.provider.release("embed")
         branch = None
         for li in range(cfg.num_hidden_layers):
@@ -279,7 +284,8 @@ class LayerwiseEngine:
         nl = cfg.num_hidden_layers
         # ---------------- forward: keep (resid, branch) per layer ----------------
         embed = prov.acquire("embed", prefetch="layer.0")
-        resid = ew.embedding_gather(batch["input_ids"], embed.view("embed"))
+        local_ids = self.select_tokens(batch["input_ids"])
+        resid = ew.embedding_gather(local_ids, embed.view("embed"))
         self._count()
         prov.release("embed")
         branch = None
@@ -302,7 +308,7 @@ class LayerwiseEngine:
         fg = self._views(final, prov.grad_buffer("final"))
         y, rstd_f, xf = ew.rmsnorm_forward(resid, fw["norm"], cfg.rms_norm_eps, residual=branch)
         targets, weights = losses.aligned_targets_and_weights(batch)
-        targets, weights = targets.reshape(-1), weights.reshape(-1)
+        targets, weights = self.select_tokens(targets).reshape(-1), self.select_tokens(weights).reshape(-1)
         train_head = self.options.train_lm_head
         # Active-row compaction: with sparse supervision (assistant-only loss, MaskGIT targets) only
         # the rows that carry weight go through the LM head; their gradients are scattered back.
@@ -363,7 +369,7 @@ class LayerwiseEngine:
             gbuf = prov.grad_buffer("embed")[seg.offset:seg.offset + seg.numel].view(seg.shape)
             if first:
                 gbuf.zero_()
-            ew.embedding_backward(batch["input_ids"], dout, gbuf, cfg.pad_token_id)
+            ew.embedding_backward(local_ids, dout, gbuf, cfg.pad_token_id)
             self._count(5)
             prov.grads_ready("embed", last)
         return nll, wsum

@@ -226,8 +226,10 @@ class TrainingRun:
         self.use_engine = (self.cuda and self.param_dtype == torch.bfloat16 and args.dtype == "bfloat16"
                            and args.attn_mechanism != "vanilla" and not args.lora and args.loss_implementation != "xla"
                            and (args.attention_options is None or args.attention_options.backend != "reference"))
-        if self.lattice.size("sp") > 1:
-            raise NotImplementedError("the sp axis must be 1: long sequences are sharded by token rows over tp")
+        if self.lattice.size("sp") > 1 and (self.lattice.size("tp") > 1 or not self.use_engine
+                                            or args.attention_options is not None):
+            raise ValueError("sequence parallelism (sp > 1) runs on the bf16 CUDA engine with tp = 1 and dense "
+                             "attention; shard long MoBA rows over tp instead")
         if self.lattice.size("tp") > 1 and not self.use_engine:
             raise ValueError("tensor parallelism (tp > 1) runs on the bf16 CUDA engine only: it needs GPUs, "
                              "--attn_mechanism efficient, a fused loss, no LoRA and dense attention")
@@ -356,8 +358,8 @@ class TrainingRun:
             else (self.source if self.has_weights else None)
         data_ranks = self.lattice.size("dp") * self.lattice.size("fsdp")
         self.lora: LoraState | None = None
-        tp = self.lattice.size("tp")
-        if self.use_engine and (data_ranks > 1 or tp > 1):
+        tp, sp = self.lattice.size("tp"), self.lattice.size("sp")
+        if self.use_engine and (data_ranks > 1 or tp > 1 or sp > 1):
             from ..api import TrainerConfig
             from ..parallel.fsdp import FsdpRuntime
             from .engine import EngineOptions, LayerwiseEngine
@@ -368,8 +370,13 @@ class TrainingRun:
             options = EngineOptions(cut_chunk_rows=tcfg.cut_chunk_rows, attention_options=a.attention_options)
             # parameters, gradients and optimizer state are sharded over dp x fsdp (a dp replica
             # would only cost memory); tensor-parallel ranks hold slices of every projection
-            data_group = self.lattice.group(("dp", "fsdp"))
-            if tp > 1:
+            data_group = self.lattice.group(("dp", "fsdp", "sp") if sp > 1 else ("dp", "fsdp"))
+            if sp > 1:
+                from .sp_engine import SpLayerwiseEngine
+
+                self.runtime = FsdpRuntime(self.cfg, tcfg, self.device, group=data_group)
+                engine = SpLayerwiseEngine(self.cfg, self.lattice.group(("sp",)), self.runtime, options)
+            elif tp > 1:
                 from ..parallel.tp import tp_local_config
                 from .tp_engine import TpLayerwiseEngine
 

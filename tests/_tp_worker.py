@@ -91,7 +91,7 @@ def run_ops(out_path: str) -> None:
         Path(out_path).write_text(json.dumps(gathered))
 
 
-def run_train(out_path: str, tp: int, fused: bool, steps: int, kv_heads: int = 2) -> None:
+def run_train(out_path: str, tp: int, fused: bool, steps: int, kv_heads: int = 2, sp: int = 1) -> None:
     from causal_trainer_dev_b200.api import Trainer, TrainerConfig
     from causal_trainer_dev_b200.data.synthetic import pretraining_rows
     from causal_trainer_dev_b200.models.config import preset
@@ -101,7 +101,7 @@ def run_train(out_path: str, tp: int, fused: bool, steps: int, kv_heads: int = 2
     rank = dist.get_rank()
     cfg = preset("tiny", vocab_size=4096, num_hidden_layers=3, intermediate_size=512, num_key_value_heads=kv_heads)
     tcfg = TrainerConfig(micro_batch_rows=2, adamw=AdamWConfig(weight_decay=0.1, max_grad_norm=1.0),
-                         schedule=ScheduleConfig(1e-3, 0.0, "constant", 0, 10), fused_collectives=fused, seed=3, tp=tp)
+                         schedule=ScheduleConfig(1e-3, 0.0, "constant", 0, 10), fused_collectives=fused, seed=3, tp=tp, sp=sp)
     trainer = Trainer(cfg, tcfg)
     rows = 8
     data = pretraining_rows(rows, 256, cfg.vocab_size, eos_token_id=2, pad_token_id=0, median_len=80, min_len=8, seed=5)
@@ -122,7 +122,7 @@ def main() -> None:
         run_ops(sys.argv[2])
     else:
         run_train(sys.argv[2], int(sys.argv[3]), sys.argv[4] == "fused", int(sys.argv[5]),
-                  int(sys.argv[6]) if len(sys.argv) > 6 else 2)
+                  int(sys.argv[6]) if len(sys.argv) > 6 else 2, int(sys.argv[7]) if len(sys.argv) > 7 else 1)
     dist.destroy_process_group()
 
 

@@ -71,3 +71,12 @@ def test_tp2_with_one_shared_kv_head_matches_fsdp2(cuda_lib, tmp_path):
     fsdp = _launch(["train", "1", "fused", "3", "1"], 2, tmp_path / "fsdp_mqa.json", 29638)
     assert tp["status"] == [0, 0, 0, 0]
     _close(tp["history"], fsdp["history"], 2e-2, 3e-2)
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_sequence_parallel_sp2_matches_fsdp2(cuda_lib, tmp_path):
+    """sp = 2: each rank computes half of every row's tokens, K/V are all-gathered, dK/dV reduce-scattered."""
+    sp = _launch(["train", "1", "fused", "3", "2", "2"], 2, tmp_path / "sp.json", 29639)
+    fsdp = _launch(["train", "1", "fused", "3", "2", "1"], 2, tmp_path / "fsdp_sp.json", 29640)
+    assert sp["status"] == [0, 0, 0, 0]
+    _close(sp["history"], fsdp["history"], 2e-2, 3e-2)
