@@ -58,6 +58,27 @@ def main() -> None:
         ms = timed(fn)
         tf = 2.0 * m * n * k / ms / 1e9
         out.update(ms=ms, tflops=tf, fraction_of_measured_bf16_peak=tf / pk["bf16_tflops"])
+    elif case == "layer_gemms":
+        # the GEMMs of one Llama-3-8B layer at 16384 tokens: forward, dgrad and wgrad (bf16 store and
+        # fp32 accumulate through TMA reduce-add) of the four projections
+        t, dm, ff, qkv = 16384, 4096, 14336, 6144
+        x = torch.randn(t, dm, device=dev).bfloat16()
+        res = {}
+        for name, n_out, k_in in (("qkv", qkv, dm), ("o", dm, dm), ("gate_up", 2 * ff, dm), ("down", dm, ff)):
+            a = torch.randn(t, k_in, device=dev).bfloat16()
+            w = torch.randn(n_out, k_in, device=dev).bfloat16()
+            dy = torch.randn(t, n_out, device=dev).bfloat16()
+            g16 = torch.empty(n_out, k_in, device=dev, dtype=torch.bfloat16)
+            g32 = torch.zeros(n_out, k_in, device=dev, dtype=torch.float32)
+            fl = 2.0 * t * n_out * k_in / 1e9
+            res[name] = {
+                "fwd_tflops": fl / timed(lambda: G.gemm(a, w)),
+                "dgrad_tflops": fl / timed(lambda: G.gemm(dy, w, b_mn=True)),
+                "wgrad_bf16_tflops": fl / timed(lambda: G.gemm(dy, a, a_mn=True, b_mn=True, out=g16)),
+                "wgrad_f32_accumulate_tflops": fl / timed(lambda: G.gemm(dy, a, a_mn=True, b_mn=True, out=g32, accumulate=True)),
+            }
+            res[name] = {k: round(v, 1) for k, v in res[name].items()}
+        out.update(res)
     elif case in ("attn_fwd", "attn_bwd"):
         b, s, hq, hkv, d = 2, 4096, 32, 8, 128
         q = torch.randn(b, s, hq, d, device=dev).bfloat16()

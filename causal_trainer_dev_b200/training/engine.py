@@ -68,6 +68,7 @@ class EngineOptions:
     train_embed: bool = True
     train_norm: bool = True
     remat: str = "auto"                      # "auto" | "full" | "none"
+    overlap_wgrad: bool = False              # issue weight-gradient GEMMs on a second stream (measured: no gain)
     compact_loss_rows: bool = True           # run the LM head only on rows with non-zero loss weight
     loss_backend: str = "cut"                # "cut": projection-fused; "logits": materialised bf16 logits slab per chunk
     memory_reserve_bytes: int = 8 << 30
@@ -84,6 +85,10 @@ class LayerwiseEngine:
         self.launches = 0
         self.kept_layers = 0
         self._inv_freq: torch.Tensor | None = None
+        import os
+
+        overlap = self.options.overlap_wgrad and os.environ.get("CTB_OVERLAP_WGRAD", "1") != "0"
+        self._wgrad_stream = torch.cuda.Stream() if overlap else None
 
     # ------------------------------------------------------------------ helpers
     def _views(self, unit: Unit, base: torch.Tensor | None = None) -> dict[str, torch.Tensor]:
@@ -98,8 +103,25 @@ class LayerwiseEngine:
         return t
 
     def _wgrad(self, dy: torch.Tensor, x: torch.Tensor, gview: torch.Tensor, accumulate: bool) -> None:
-        gemm(dy, x, a_mn=True, b_mn=True, out=gview, accumulate=accumulate)
+        """Weight gradient ``dy^T x``.  With ``overlap_wgrad`` it is issued on a second stream: nothing
+        in the layer waits for it, so the partly filled last wave of one persistent GEMM is filled by
+        the first CTAs of the next kernel instead of leaving SMs idle."""
+        side = self._wgrad_stream
+        if side is None:
+            gemm(dy, x, a_mn=True, b_mn=True, out=gview, accumulate=accumulate)
+        else:
+            ev = torch.cuda.Event()
+            ev.record()
+            side.wait_event(ev)
+            with torch.cuda.stream(side):
+                gemm(dy, x, a_mn=True, b_mn=True, out=gview, accumulate=accumulate)
+            dy.record_stream(side)
+            x.record_stream(side)
         self._count()
+
+    def _join_wgrads(self) -> None:
+        if self._wgrad_stream is not None:
+            torch.cuda.current_stream().wait_stream(self._wgrad_stream)
 
     def _bias_grad(self, dy: torch.Tensor, gview: torch.Tensor, accumulate: bool) -> None:
         s = dy.float().sum(0)
@@ -360,6 +382,7 @@ class LayerwiseEngine:
                 _, _, saved = self._layer_forward(w, layer_in[0], layer_in[1], ctx, li, save="all")
             dout = self._layer_backward(w, g, saved, dout, ctx, accumulate)
             del saved, layer_in
+            self._join_wgrads()
             prov.release(f"layer.{li}")
             prov.grads_ready(f"layer.{li}", last)
         # ---------------- embedding ----------------

@@ -42,6 +42,7 @@ class TpLayerwiseEngine(LayerwiseEngine):
         self.fused = fused
         self._contexts: dict[int, TpContext] = {}
         super().__init__(tp_local_config(full_cfg, self.tp_world), provider, options)
+        self._wgrad_stream = None      # weight gradients read ring buffers that later all-gathers reuse
         # fewer key/value heads than ranks: the ranks that share a head sum its weight gradients
         self.kv_rep = kv_replicas(full_cfg, self.tp_world)
         self.kv_group = None
