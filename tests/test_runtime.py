@@ -48,6 +48,11 @@ def test_single_process_collectives_are_identities():
 
 
 WORKER = r'''
+import os as _os
+def say(*parts):
+    # one write() per line: lines of different ranks never interleave inside the shared pipe
+    _os.write(1, (" ".join(str(p) for p in parts) + "\n").encode())
+
 import sys, numpy as np, torch.distributed as dist
 sys.path.insert(0, sys.argv[1])
 from causal_trainer_dev_b200.parallel import runtime as rt
@@ -63,29 +68,29 @@ if scenario == "merge":
     assert out["loss_weights"].dtype == np.float32 and np.float32(1.1) == out["loss_weights"][1, 0]   # bit-exact floats
     rt.assert_equal(rt.digest_of({"same": 1}), "flags")
     rt.sync_processes("done")
-    print("MERGE-OK", rank)
+    say("MERGE-OK", rank)
 elif scenario == "error":
     err = ValueError("rank one broke") if rank == 1 else None
     try:
         rt.raise_if_any_process_error(err, "load dataset")
-        print("NO-ERROR", rank)
+        say("NO-ERROR", rank)
     except ValueError as e:
-        print("OWN-ERROR", rank, e)
+        say("OWN-ERROR", rank, e)
     except RuntimeError as e:
-        print("PEER-ERROR", rank, e)
+        say("PEER-ERROR", rank, e)
 elif scenario == "mismatch":
     try:
         rt.assert_equal(rt.digest_of({"rank": rank if rank == 2 else 0}), "command-line arguments")
-        print("AGREE", rank)
+        say("AGREE", rank)
     except RuntimeError as e:
-        print("MISMATCH", rank, e)
+        say("MISMATCH", rank, e)
 elif scenario == "zero":
     try:
         rt.raise_if_process_zero_error(OSError("disk full") if rank == 0 else None, "write manifest")
     except OSError as e:
-        print("ZERO-OWN", rank)
+        say("ZERO-OWN", rank)
     except RuntimeError as e:
-        print("ZERO-PEER", rank, e)
+        say("ZERO-PEER", rank, e)
 dist.destroy_process_group()
 '''
 
