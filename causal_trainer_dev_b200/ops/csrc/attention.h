@@ -19,7 +19,10 @@ namespace attn {
 // (64-row block, head) pairs (backward) that host code derived from the union of its rows'
 // selections, instead of a contiguous range.
 struct SparseArgs {
-  const int* it_off;       // [work items + 1] offsets into it_list, work items in blockIdx order
+  const int* it_off;       // [work items + 1] offsets into it_list, work items in blockIdx order; or, when
+                           // it_cnt is set, unused: item i owns it_list[i * it_stride ..] with it_cnt[i] entries
+  const int* it_cnt;
+  int it_stride;
   const int* it_list;      // forward: 128-key tile index; backward: 64-row block | head_in_group << 24
   const unsigned* sel;     // [B][Hq][S][words]
   const int* doc_start;    // [B][S]
@@ -99,6 +102,17 @@ struct BwdCall {
   void* stream;
   SparseArgs sp{};
 };
+
+// First entry and length of the work list of CTA `item`.
+__device__ __forceinline__ void sparse_list(const SparseArgs& sp, int item, int& base, int& count) {
+  if (sp.it_cnt != nullptr) {
+    base = item * sp.it_stride;
+    count = sp.it_cnt[item];
+  } else {
+    base = sp.it_off[item];
+    count = sp.it_off[item + 1] - base;
+  }
+}
 
 // Selection bit of document-relative block `blk` for (batch b, head h, query qi).
 __device__ __forceinline__ bool sparse_bit(const SparseArgs& sp, int b, int h, int Hq, int S, int qi, int blk) {

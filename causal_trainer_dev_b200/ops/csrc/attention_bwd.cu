@@ -114,8 +114,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const bool sparse = args.sp.it_list != nullptr;
   const int* it_list = nullptr;
   if (sparse) {
-    const int base = args.sp.it_off[blockIdx.x];
-    n_iter = args.sp.it_off[blockIdx.x + 1] - base;
+    int base;
+    sparse_list(args.sp, blockIdx.x, base, n_iter);
     it_list = args.sp.it_list + base;
   }
   // iteration -> (64-row block of the streamed operand, query head)
@@ -597,8 +597,9 @@ CTB_API int ctb_attn_bwd_sparse(int mode, const void* q, const void* k, const vo
                                 void* dk, void* dv, const float* lse, const float* delta, const int* seg,
                                 const int* lim, const int* kv_lo, const int* kv_hi, const int* q_lo, const int* q_hi,
                                 const int* seg_min64, const int* seg_max64, const int* lim_min64,
-                                const int* lim_max64, const int* it_off, const int* it_list, const unsigned* sel,
-                                const unsigned* allsel, const int* doc_start, int block, int words, int B, int S, int Hq, int Hkv, int D,
+                                const int* lim_max64, const int* it_off, const int* it_cnt, int it_stride,
+                                const int* it_list, const unsigned* sel, const unsigned* allsel, const int* doc_start,
+                                int block, int words, int B, int S, int Hq, int Hkv, int D,
                                 long q_rs, long k_rs, long v_rs, long do_rs, long dq_rs, long dk_rs, long dv_rs,
                                 float scale, long long spin_budget, void* stream) {
   if (S % 128) return ctb::fail("attention: sequence length must be a multiple of 128");
@@ -612,7 +613,8 @@ CTB_API int ctb_attn_bwd_sparse(int mode, const void* q, const void* k, const vo
   c.q_row_stride = q_rs; c.k_row_stride = k_rs; c.v_row_stride = v_rs; c.do_row_stride = do_rs;
   c.dq_row_stride = dq_rs; c.dk_row_stride = dk_rs; c.dv_row_stride = dv_rs;
   c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
-  c.sp.it_off = it_off; c.sp.it_list = it_list; c.sp.sel = sel; c.sp.doc_start = doc_start;
+  c.sp.it_off = it_off; c.sp.it_cnt = it_cnt; c.sp.it_stride = it_stride; c.sp.it_list = it_list; c.sp.sel = sel;
+  c.sp.doc_start = doc_start;
   c.sp.allsel = allsel; c.sp.block = block; c.sp.words = words;
   using namespace ctb::attn;
   if (D == 128) return mode == 0 ? launch_bwd<128, MODE_DKV>(c) : launch_bwd<128, MODE_DQ>(c);

@@ -111,9 +111,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const bool sparse = args.sp.it_list != nullptr;
   const int* kv_list = nullptr;
   if (sparse) {
-    const int item = blockIdx.x;
-    const int base = args.sp.it_off[item];
-    const int cnt = args.sp.it_off[item + 1] - base;
+    int base, cnt;
+    sparse_list(args.sp, blockIdx.x, base, cnt);
     kv_list = args.sp.it_list + base;
     n0 = tile_valid[0] ? cnt : 0;
     n1 = tile_valid[1] ? cnt : 0;
@@ -522,8 +521,9 @@ CTB_API int ctb_attn_fwd_range(const void* q, const void* k, const void* v, void
 // has B * Hq * ceil(S / 256) + 1 entries in the order (query pair descending, batch, head) of the grid.
 CTB_API int ctb_attn_fwd_sparse(const void* q, const void* k, const void* v, void* o, float* lse, const int* seg,
                                 const int* lim, const int* kv_lo, const int* kv_hi, const int* kmin, const int* kmax,
-                                const int* it_off, const int* it_list, const unsigned* sel, const int* doc_start,
-                                int block, int words, int B, int S, int Hq, int Hkv, int D, long q_row_stride,
+                                const int* it_off, const int* it_cnt, int it_stride, const int* it_list,
+                                const unsigned* sel, const int* doc_start, int block, int words, int B, int S, int Hq,
+                                int Hkv, int D, long q_row_stride,
                                 long k_row_stride, long v_row_stride, long o_row_stride, float scale,
                                 long long spin_budget, void* stream) {
   if (S % 128) return ctb::fail("attention: sequence length must be a multiple of 128");
@@ -534,8 +534,8 @@ CTB_API int ctb_attn_fwd_sparse(const void* q, const void* k, const void* v, voi
   c.kmin = kmin; c.kmax = kmax; c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
   c.q_row_stride = q_row_stride; c.k_row_stride = k_row_stride; c.v_row_stride = v_row_stride;
   c.o_row_stride = o_row_stride; c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
-  c.sp.it_off = it_off; c.sp.it_list = it_list; c.sp.sel = sel; c.sp.doc_start = doc_start;
-  c.sp.block = block; c.sp.words = words;
+  c.sp.it_off = it_off; c.sp.it_cnt = it_cnt; c.sp.it_stride = it_stride; c.sp.it_list = it_list; c.sp.sel = sel;
+  c.sp.doc_start = doc_start; c.sp.block = block; c.sp.words = words;
   if (D == 128) return ctb::attn::launch_fwd<128>(c);
   if (D == 64) return ctb::attn::launch_fwd<64>(c);
   return ctb::fail("attention: head_dim must be 64 or 128");

@@ -190,3 +190,160 @@ CTB_API int ctb_moba_route(const void* q, long q_row_stride, const float* pooled
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------
+// Work lists of the block-sparse flash kernels, built on the GPU without a host round trip.
+//
+//   moba_touch    per (batch, head, 64-query block): a bitmap over the 64-key blocks that at least
+//                 one of its rows selected (own block up to the diagonal included), and the AND of
+//                 the rows' selection masks (padding rows count as all ones).
+//   moba_lists    per CTA of the flash kernels (a warp per work item): the ascending list of
+//                 candidates whose bit is set, at a fixed stride, plus its length:
+//                   mode 0  forward      item (query pair descending, batch, head)      -> 128-key tiles
+//                   mode 1  dQ           item (query tile descending, batch, head)      -> 64-key blocks
+//                   mode 2  dK/dV        item (key tile ascending, batch, kv head)      -> (head in group << 24) | 64-query block
+//
+// Reference counterpart: the query grouping of the Pallas path (stable argsort by block id,
+// padded groups, src/causal_trainer/kernels/grouped_moba.py:25-57).
+// ------------------------------------------------------------------------------------------
+namespace ctb {
+namespace moba {
+
+constexpr int MAX_TOUCH_WORDS = 128;   // 64-key blocks per row / 32: sequences up to 262144 tokens
+constexpr int MAX_SEL_WORDS = 64;      // selection words per row: up to 2048 blocks per document
+
+// grid (S/64, Hq, B), 64 threads.  touch: [B][Hq][S/64][tw] words, tw = S/64/32 rounded up.
+__global__ void __launch_bounds__(64)
+moba_touch_kernel(const unsigned* __restrict__ sel, const int* __restrict__ seg, const int* __restrict__ doc_start,
+                  int S, int Hq, int block, int words, int tw, unsigned* __restrict__ touch,
+                  unsigned* __restrict__ allsel) {
+  __shared__ unsigned bits[MAX_TOUCH_WORDS];
+  __shared__ unsigned all_and[MAX_SEL_WORDS];
+  const int q64 = blockIdx.x, h = blockIdx.y, b = blockIdx.z;
+  for (int w = threadIdx.x; w < tw; w += 64) bits[w] = 0u;
+  if (threadIdx.x < words) all_and[threadIdx.x] = 0xffffffffu;
+  __syncthreads();
+  const int i = q64 * 64 + threadIdx.x;
+  const int sg = seg[b * S + i];
+  const unsigned* my = sel + ((static_cast<size_t>(b) * Hq + h) * S + i) * words;
+  if (sg != 0) {
+    const int start = doc_start[b * S + i];
+    for (int w = 0; w < words; ++w) {
+      unsigned m = my[w];
+      atomicAnd(&all_and[w], m);
+      while (m) {
+        const int c = w * 32 + __ffs(m) - 1;
+        m &= m - 1;
+        const int lo = start + c * block;
+        if (lo > i) continue;
+        const int hi = min(lo + block - 1, i);
+        int k0 = lo >> 6;
+        const int k1 = hi >> 6;
+        while (k0 <= k1) {                         // set bits k0..k1, one word at a time
+          const int word = k0 >> 5;
+          const int last = min(k1, word * 32 + 31);
+          const unsigned from = 0xffffffffu << (k0 & 31);
+          const unsigned upto = 0xffffffffu >> (31 - (last & 31));
+          atomicOr(&bits[word], from & upto);
+          k0 = last + 1;
+        }
+      }
+    }
+  }
+  __syncthreads();
+  unsigned* out = touch + ((static_cast<size_t>(b) * Hq + h) * (S / 64) + q64) * tw;
+  for (int w = threadIdx.x; w < tw; w += 64) out[w] = bits[w];
+  if (threadIdx.x < words)
+    allsel[((static_cast<size_t>(b) * Hq + h) * (S / 64) + q64) * words + threadIdx.x] =
+        all_and[threadIdx.x];
+}
+
+// One warp per work item; 8 warps per CTA.
+__global__ void __launch_bounds__(256)
+moba_lists_kernel(int mode, const unsigned* __restrict__ touch, int B, int S, int Hq, int Hkv, int tw, int items,
+                  int stride, int* __restrict__ list, int* __restrict__ count) {
+  const int item = blockIdx.x * 8 + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (item >= items) return;
+  const int nb64 = S / 64, nb128 = S / 128;
+  int* out = list + static_cast<size_t>(item) * stride;
+  int n = 0;
+  auto row = [&](int b, int h, int q64) -> const unsigned* {
+    return touch + ((static_cast<size_t>(b) * Hq + h) * nb64 + q64) * tw;
+  };
+  if (mode == 0 || mode == 1) {
+    const int per = mode == 0 ? (S + 255) / 256 : nb128;          // query groups per (b, h)
+    const int h = item % Hq;
+    const int b = (item / Hq) % B;
+    const int grp = per - 1 - item / (Hq * B);
+    const int rows = mode == 0 ? 4 : 2;                            // 64-query blocks per group
+    const int cand = mode == 0 ? nb128 : nb64;
+    for (int c0 = 0; c0 < cand; c0 += 32) {
+      const int c = c0 + lane;
+      bool hit = false;
+      if (c < cand) {
+        for (int r = 0; r < rows; ++r) {
+          const int q64 = grp * rows + r;
+          if (q64 >= nb64) break;
+          const unsigned* t = row(b, h, q64);
+          if (mode == 0) {
+            const int k64 = 2 * c;                                  // two 64-key blocks per 128-key tile
+            hit = hit || ((t[k64 >> 5] >> (k64 & 31)) & 3u);
+          } else {
+            hit = hit || ((t[c >> 5] >> (c & 31)) & 1u);
+          }
+        }
+      }
+      const unsigned mask = __ballot_sync(0xffffffffu, hit);
+      if (hit) out[n + __popc(mask & ((1u << lane) - 1u))] = c;
+      n += __popc(mask);
+    }
+  } else {
+    const int g = Hq / Hkv;
+    const int hkv = item % Hkv;
+    const int b = (item / Hkv) % B;
+    const int kt = item / (Hkv * B);
+    const int k64 = 2 * kt;
+    const int cand = g * nb64;
+    for (int c0 = 0; c0 < cand; c0 += 32) {
+      const int c = c0 + lane;
+      bool hit = false;
+      if (c < cand) {
+        const int gi = c / nb64, q64 = c % nb64;
+        const unsigned* t = row(b, hkv * g + gi, q64);
+        hit = ((t[k64 >> 5] >> (k64 & 31)) & 3u) != 0u;
+      }
+      const unsigned mask = __ballot_sync(0xffffffffu, hit);
+      if (hit) out[n + __popc(mask & ((1u << lane) - 1u))] = ((c / nb64) << 24) | (c % nb64);
+      n += __popc(mask);
+    }
+  }
+  if (lane == 0) count[item] = n;
+}
+
+}  // namespace moba
+}  // namespace ctb
+
+// touch: [B][Hq][S/64][tw] words with tw = ceil(S/64/32); allsel: [B][Hq][S/64][words].
+CTB_API int ctb_moba_touch(const unsigned* sel, const int* seg, const int* doc_start, int B, int S, int Hq, int block,
+                           int words, int tw, unsigned* touch, unsigned* allsel, void* stream) {
+  if (S % 128 || block < 128) return fail("moba_touch: S must be a multiple of 128 and block >= 128");
+  if (tw > moba::MAX_TOUCH_WORDS || tw * 32 < S / 64) return fail("moba_touch: sequence too long for the touch bitmap");
+  if (words > moba::MAX_SEL_WORDS) return fail("moba_touch: at most 2048 blocks per document");
+  dim3 grid(S / 64, Hq, B);
+  moba::moba_touch_kernel<<<grid, 64, 0, static_cast<cudaStream_t>(stream)>>>(sel, seg, doc_start, S, Hq, block, words,
+                                                                            tw, touch, allsel);
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// list: [items][stride] int32, count: [items].  Items and strides per mode: see moba_lists above.
+CTB_API int ctb_moba_lists(int mode, const unsigned* touch, int B, int S, int Hq, int Hkv, int tw, int items,
+                           int stride, int* list, int* count, void* stream) {
+  if (mode < 0 || mode > 2) return fail("moba_lists: mode must be 0, 1 or 2");
+  if (items <= 0) return 0;
+  moba::moba_lists_kernel<<<(items + 7) / 8, 256, 0, static_cast<cudaStream_t>(stream)>>>(mode, touch, B, S, Hq, Hkv, tw,
+                                                                                       items, stride, list, count);
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}

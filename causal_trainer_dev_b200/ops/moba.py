@@ -5,8 +5,9 @@ Pipeline of one layer (all on the GPU):
 1. ``ctb_moba_pool``   mean key of every complete document-relative block (fp32);
 2. ``ctb_moba_route``  per (token, query head): ``q . mean(K_block)`` over the completed blocks
    before the query's own, top-(k-1) with ties to the earlier block, as a selection bit mask;
-3. work lists: for every CTA of the flash kernels the key tiles (forward), the 64-key blocks
-   (dQ) and the (64-query block, head) pairs (dK/dV) that at least one of its rows selected;
+3. ``ctb_moba_touch`` / ``ctb_moba_lists``  work lists: for every CTA of the flash kernels the key
+   tiles (forward), the 64-key blocks (dQ) and the (64-query block, head) pairs (dK/dV) that at
+   least one of its rows selected, at a fixed stride with a count per CTA (no host round trip);
 4. the tcgen05 flash kernels of ``csrc/attention_fwd.cu`` / ``attention_bwd.cu`` walk those
    lists and test the selection bits per row, so one softmax covers the union of the query's own
    block (causal) and its selected blocks, and unselected key tiles are never loaded.
@@ -31,6 +32,25 @@ from .elementwise import attention_delta
 
 
 @dataclass
+class WorkList:
+    """Per-CTA work list: CSR (``off`` [items+1], ``entries``) or strided (``count`` [items],
+    ``entries`` [items, stride])."""
+
+    entries: torch.Tensor
+    off: torch.Tensor | None = None
+    count: torch.Tensor | None = None
+    stride: int = 0
+
+    def lengths(self) -> torch.Tensor:
+        return self.count if self.count is not None else (self.off[1:] - self.off[:-1])
+
+    def item(self, i: int) -> list[int]:
+        if self.count is not None:
+            return self.entries.view(-1, self.stride)[i, :int(self.count[i])].tolist()
+        return self.entries[int(self.off[i]):int(self.off[i + 1])].tolist()
+
+
+@dataclass
 class MobaRouting:
     """Selection masks and CTA work lists of one layer."""
 
@@ -39,13 +59,17 @@ class MobaRouting:
     doc_start: torch.Tensor    # [B,S] int32
     block: int
     words: int
-    fwd_off: torch.Tensor
-    fwd_list: torch.Tensor
-    dq_off: torch.Tensor
-    dq_list: torch.Tensor
-    dkv_off: torch.Tensor
-    dkv_list: torch.Tensor
-    visited_fraction: float    # key tiles visited by the forward kernel / tiles a dense causal kernel visits
+    fwd: WorkList
+    dq: WorkList
+    dkv: WorkList
+
+    @property
+    def visited_fraction(self) -> float:
+        """Key tiles visited by the forward kernel / tiles a dense causal kernel visits (reads back)."""
+        b, hq, s, _ = self.sel.shape
+        nqp, nb128 = (s + 255) // 256, s // 128
+        dense = sum(min(nb128, 2 * (p + 1)) for p in range(nqp)) * b * hq
+        return float(self.fwd.lengths().sum()) / max(1, dense)
 
 
 def document_starts(seg: torch.Tensor) -> torch.Tensor:
@@ -122,13 +146,16 @@ def _csr(table: torch.Tensor, values: torch.Tensor | None = None) -> tuple[torch
     return off, entries.to(torch.int32).contiguous()
 
 
-def build_routing(q: torch.Tensor, k: torch.Tensor, meta: AttentionMeta, block: int, top_k: int) -> MobaRouting:
+def build_routing_reference(q: torch.Tensor, k: torch.Tensor, meta: AttentionMeta, block: int, top_k: int,
+                            sel: torch.Tensor | None = None) -> MobaRouting:
+    """Work lists from PyTorch ops (scatter / cumsum / nonzero); the oracle of :func:`build_routing`."""
     b, s, hq, _ = q.shape
     hkv = k.shape[2]
     g = hq // hkv
     seg = meta.seg
     doc_start = document_starts(seg)
-    sel = route(q, k, seg, doc_start, block, top_k)
+    if sel is None:
+        sel = route(q, k, seg, doc_start, block, top_k)
     touch = _touched_blocks(sel, seg, doc_start, block)                                # [B,Hq,nq64,nk64]
     allsel = _block_and(sel, seg)
     nb64, nb128 = s // 64, s // 128
@@ -139,8 +166,6 @@ def build_routing(q: torch.Tensor, k: torch.Tensor, meta: AttentionMeta, block: 
         t = torch.cat([t, torch.zeros((b, hq, 4 - nb64 % 4, nb128), dtype=torch.bool, device=t.device)], dim=2)
     t = t.view(b, hq, nqp, 4, nb128).any(3)
     fwd_off, fwd_list = _csr(t.permute(2, 0, 1, 3).flip(0).reshape(-1, nb128))
-    dense_tiles = sum(min(nb128, 2 * (p + 1)) for p in range(nqp)) * b * hq
-    visited = float(fwd_list.numel()) / max(1, dense_tiles)
     # dQ: (query tile descending, batch, head) x 64-key blocks
     t = touch.view(b, hq, nb128, 2, nb64).any(3)
     dq_off, dq_list = _csr(t.permute(2, 0, 1, 3).flip(0).reshape(-1, nb64))
@@ -148,8 +173,38 @@ def build_routing(q: torch.Tensor, k: torch.Tensor, meta: AttentionMeta, block: 
     t = touch.view(b, hkv, g, nb64, nb128, 2).any(-1).permute(4, 0, 1, 2, 3).reshape(-1, g * nb64)
     packed = (torch.arange(g, device=t.device)[:, None] * (1 << 24) + torch.arange(nb64, device=t.device)[None, :])
     dkv_off, dkv_list = _csr(t, packed.reshape(-1))
-    return MobaRouting(sel, allsel, doc_start, block, sel.shape[-1], fwd_off, fwd_list, dq_off, dq_list, dkv_off, dkv_list,
-                       visited)
+    return MobaRouting(sel, allsel, doc_start, block, sel.shape[-1], WorkList(fwd_list, off=fwd_off),
+                       WorkList(dq_list, off=dq_off), WorkList(dkv_list, off=dkv_off))
+
+
+def build_routing(q: torch.Tensor, k: torch.Tensor, meta: AttentionMeta, block: int, top_k: int) -> MobaRouting:
+    """Routing and work lists entirely on the GPU, no host round trip: pool, route, a touch bitmap per
+    64-query block, then one warp per flash-kernel CTA compacts its candidates (``csrc/moba.cu``)."""
+    b, s, hq, _ = q.shape
+    hkv = k.shape[2]
+    g = hq // hkv
+    seg = meta.seg
+    dev = q.device
+    doc_start = document_starts(seg)
+    sel = route(q, k, seg, doc_start, block, top_k)
+    words = sel.shape[-1]
+    nb64, nb128, nqp = s // 64, s // 128, (s + 255) // 256
+    tw = -(-nb64 // 32)
+    L = _lib.lib()
+    touch = torch.empty((b, hq, nb64, tw), dtype=torch.int32, device=dev)
+    allsel = torch.empty((b, hq, nb64, words), dtype=torch.int32, device=dev)
+    code = L.ctb_moba_touch(_lib.ptr(sel), _lib.ptr(seg), _lib.ptr(doc_start), b, s, hq, block, words, tw,
+                            _lib.ptr(touch), _lib.ptr(allsel), _lib.stream_ptr())
+    _lib.check(code, "ctb_moba_touch")
+    lists = []
+    for mode, items, stride in ((0, b * hq * nqp, nb128), (1, b * hq * nb128, nb64), (2, b * hkv * nb128, g * nb64)):
+        entries = torch.empty((items, stride), dtype=torch.int32, device=dev)
+        count = torch.empty(items, dtype=torch.int32, device=dev)
+        code = L.ctb_moba_lists(mode, _lib.ptr(touch), b, s, hq, hkv, tw, items, stride, _lib.ptr(entries),
+                                _lib.ptr(count), _lib.stream_ptr())
+        _lib.check(code, "ctb_moba_lists")
+        lists.append(WorkList(entries, count=count, stride=stride))
+    return MobaRouting(sel, allsel, doc_start, block, words, *lists)
 
 
 def moba_forward(q, k, v, meta: AttentionMeta, routing: MobaRouting, scale: float | None = None,
@@ -164,7 +219,8 @@ def moba_forward(q, k, v, meta: AttentionMeta, routing: MobaRouting, scale: floa
     code = _lib.lib().ctb_attn_fwd_sparse(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(meta.seg), _lib.ptr(meta.lim),
         _lib.ptr(meta.kv_lo), _lib.ptr(meta.kv_hi), _lib.ptr(meta.kmin), _lib.ptr(meta.kmax),
-        _lib.ptr(r.fwd_off), _lib.ptr(r.fwd_list), _lib.ptr(r.sel), _lib.ptr(r.doc_start), r.block, r.words,
+        _lib.ptr(r.fwd.off), _lib.ptr(r.fwd.count), r.fwd.stride, _lib.ptr(r.fwd.entries), _lib.ptr(r.sel),
+        _lib.ptr(r.doc_start), r.block, r.words,
         b, s, hq, hkv, d, ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)), ctypes.c_long(_row_stride(v)),
         ctypes.c_long(_row_stride(out)), ctypes.c_float(scale), ctypes.c_longlong(spin_budget), _lib.stream_ptr())
     _lib.check(code, "ctb_attn_fwd_sparse")
@@ -183,13 +239,14 @@ def moba_backward(q, k, v, out, dout, lse, meta: AttentionMeta, routing: MobaRou
     dv = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dv is None else dv
     r = routing
     L = _lib.lib()
-    for mode, off, lst in ((0, r.dkv_off, r.dkv_list), (1, r.dq_off, r.dq_list)):
+    for mode, wl in ((0, r.dkv), (1, r.dq)):
         code = L.ctb_attn_bwd_sparse(
             mode, _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
             _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(meta.seg), _lib.ptr(meta.lim), _lib.ptr(meta.kv_lo),
             _lib.ptr(meta.kv_hi), _lib.ptr(meta.q_lo), _lib.ptr(meta.q_hi), _lib.ptr(meta.seg_min64),
             _lib.ptr(meta.seg_max64), _lib.ptr(meta.lim_min64), _lib.ptr(meta.lim_max64),
-            _lib.ptr(off), _lib.ptr(lst), _lib.ptr(r.sel), _lib.ptr(r.allsel), _lib.ptr(r.doc_start), r.block, r.words,
+            _lib.ptr(wl.off), _lib.ptr(wl.count), wl.stride, _lib.ptr(wl.entries), _lib.ptr(r.sel), _lib.ptr(r.allsel),
+            _lib.ptr(r.doc_start), r.block, r.words,
             b, s, hq, hkv, d,
             ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)), ctypes.c_long(_row_stride(v)),
             ctypes.c_long(_row_stride(dout)), ctypes.c_long(_row_stride(dq)), ctypes.c_long(_row_stride(dk)),

@@ -87,3 +87,28 @@ def test_moba_with_full_budget_equals_dense(cuda_lib):
     dense, lse_d = flash_attention_forward(q, k, v, meta)
     assert (sparse.float() - dense.float()).abs().max() < 1e-2
     assert (lse_s - lse_d).abs().max() < 1e-3
+
+
+@pytest.mark.parametrize("s,lengths", [(2048, [[1100, 700, 200], [2048]]), (1152, [[600, 500], [1000]])])
+def test_work_list_kernels_match_pytorch_builder(cuda_lib, s, lengths):
+    """The touch bitmap + list compaction kernels give the lists of the scatter / cumsum / nonzero builder."""
+    from causal_trainer_dev_b200.ops import moba as ops
+    from causal_trainer_dev_b200.ops.attention import build_attention_meta
+
+    torch.manual_seed(3)
+    dev = torch.device("cuda")
+    b, hq, hkv, d, block, top_k = 2, 4, 2, 128, 128, 3
+    seg = _segments(b, s, lengths, dev)
+    q = (torch.randn((b, s, hq, d), device=dev) * 0.8).bfloat16()
+    k = (torch.randn((b, s, hkv, d), device=dev) * 0.8).bfloat16()
+    meta = build_attention_meta(seg, None)
+    got = ops.build_routing(q, k, meta, block, top_k)
+    want = ops.build_routing_reference(q, k, meta, block, top_k, sel=got.sel)
+    assert torch.equal(got.allsel, want.allsel)
+    for name in ("fwd", "dq", "dkv"):
+        g, w = getattr(got, name), getattr(want, name)
+        assert torch.equal(g.lengths().cpu(), w.lengths().cpu()), name
+        n = g.lengths().numel()
+        for item in {0, 1, n // 3, n // 2, n - 2, n - 1}:
+            assert g.item(item) == w.item(item), (name, item)
+    assert abs(got.visited_fraction - want.visited_fraction) < 1e-9
