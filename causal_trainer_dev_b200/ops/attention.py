@@ -52,12 +52,48 @@ class AttentionMeta:
         return self.seg.shape[1]
 
 
-def build_attention_meta(segment_ids: torch.Tensor, attention_end: torch.Tensor | None = None) -> AttentionMeta:
-    """Builds block summaries from canonical segment ids (and MaskGIT ends).
+def attention_metadata(attention_mask: torch.Tensor, segment_ids: torch.Tensor | None = None,
+                       attention_end: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor, AttentionMeta]:
+    """Canonical segment ids, restart positions and the block summaries of one micro-batch.
 
-    ``segment_ids`` must already be canonical (contiguous runs numbered 1.., 0 for padding)
-    and ``S`` a multiple of 128.
+    On a GPU this is one launch of ``ctb_attention_meta`` (``csrc/attention_meta.cu``); elsewhere
+    the PyTorch formulation (also the kernel's test oracle).  Returns ``(seg, pos, meta)``.
     """
+    if not attention_mask.is_cuda:
+        from ..models.decoder import canonicalize_segment_ids, make_position_ids
+        seg = canonicalize_segment_ids(attention_mask, segment_ids)
+        return seg, make_position_ids(attention_mask, seg, canonical=True), build_attention_meta_reference(seg, attention_end)
+    bsz, s = attention_mask.shape
+    if s % BLOCK:
+        raise ValueError(f"sequence length {s} must be a multiple of {BLOCK}")
+    dev = attention_mask.device
+    i32 = lambda t: None if t is None else t.to(torch.int32).contiguous()  # noqa: E731
+    mask, label, end = i32(attention_mask), i32(segment_ids), i32(attention_end)
+    seg = torch.empty((bsz, s), dtype=torch.int32, device=dev)
+    pos = torch.empty_like(seg)
+    lim = torch.empty_like(seg)
+    scratch = torch.empty((bsz, 4, s), dtype=torch.int32, device=dev)
+    s128 = torch.empty((6, bsz, s // BLOCK), dtype=torch.int32, device=dev)
+    s64 = torch.empty((4, bsz, s // 64), dtype=torch.int32, device=dev)
+    code = _lib.lib().ctb_attention_meta(_lib.ptr(mask), _lib.ptr(label), _lib.ptr(end), bsz, s, _lib.ptr(seg),
+                                         _lib.ptr(pos), _lib.ptr(lim), _lib.ptr(scratch), _lib.ptr(s128), _lib.ptr(s64),
+                                         _lib.stream_ptr())
+    _lib.check(code, "ctb_attention_meta")
+    meta = AttentionMeta(seg, lim if attention_end is not None else None, s128[0], s128[1], s128[2], s128[3], s128[4],
+                         s128[5], s64[0], s64[1], s64[2], s64[3], attention_end)
+    return seg, pos, meta
+
+
+def build_attention_meta(segment_ids: torch.Tensor, attention_end: torch.Tensor | None = None) -> AttentionMeta:
+    """Block summaries from canonical segment ids (contiguous runs numbered 1.., 0 for padding) and
+    MaskGIT ends; ``S`` must be a multiple of 128."""
+    if segment_ids.is_cuda:
+        return attention_metadata(segment_ids != 0, segment_ids, attention_end)[2]
+    return build_attention_meta_reference(segment_ids, attention_end)
+
+
+def build_attention_meta_reference(segment_ids: torch.Tensor, attention_end: torch.Tensor | None = None) -> AttentionMeta:
+    """PyTorch formulation of :func:`build_attention_meta` (CPU path and test oracle)."""
     seg = segment_ids.to(torch.int32).contiguous()
     bsz, s = seg.shape
     if s % BLOCK:

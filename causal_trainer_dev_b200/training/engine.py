@@ -26,7 +26,6 @@ from dataclasses import dataclass
 import torch
 
 from ..models.config import ModelConfig
-from ..models.decoder import canonicalize_segment_ids, make_position_ids
 from ..models.params import ModelParams, Unit, embed_layout
 from ..ops import attention as attn_ops
 from ..ops import cross_entropy as ce
@@ -265,16 +264,15 @@ class LayerwiseEngine:
         cfg = self.cfg
         ids = batch["input_ids"]
         mask = batch["attention_mask"]
-        seg = canonicalize_segment_ids(mask, batch.get("segment_ids"))
+        end = batch.get("attention_end")
+        seg, restart_pos, meta = attn_ops.attention_metadata(mask, batch.get("segment_ids"), end)
         pos = batch.get("position_ids")
         if pos is None:
-            pos = make_position_ids(mask, seg, canonical=True)
+            pos = restart_pos
         if self._inv_freq is None or self._inv_freq.device != ids.device:
             self._inv_freq = ew.inverse_frequencies(cfg.rotary_dim, cfg.rope_theta, device=ids.device)
         cos, sin = ew.rope_table(pos, self._inv_freq)
-        end = batch.get("attention_end")
-        meta = attn_ops.build_attention_meta(seg, end)
-        self._count(30)  # metadata is a few dozen tiny launches, once per micro-batch
+        self._count(1)   # segments, positions and block summaries: one launch per micro-batch
         return dict(batch=ids.shape[0], seq=ids.shape[1], cos=cos, sin=sin, meta=meta, seg=seg)
 
     # ------------------------------------------------------------------ forward only

@@ -130,3 +130,49 @@ def test_query_range_matches_slices_of_the_full_pass(cuda_lib):
     assert (dk_sum - dk.float()).abs().max() <= 0.02 * dk.float().abs().max()
     assert (dv_sum - dv.float()).abs().max() <= 0.02 * dv.float().abs().max()
     assert cuda_lib.device_status() == (0, 0, 0, 0)
+
+
+@pytest.mark.parametrize("s", [128, 1152, 4096, 33024])
+@pytest.mark.parametrize("maskgit", [False, True])
+def test_metadata_kernel_matches_pytorch_formulation(cuda_lib, s, maskgit):
+    """Canonical segments, restart positions, visibility limits and block summaries from the one-launch kernel."""
+    from causal_trainer_dev_b200.models.decoder import canonicalize_segment_ids, make_position_ids
+    from causal_trainer_dev_b200.ops import attention as A
+
+    gen = torch.Generator().manual_seed(s + int(maskgit))
+    b = 3
+    mask = torch.ones((b, s), dtype=torch.int32)
+    label = torch.zeros((b, s), dtype=torch.int32)
+    end = torch.zeros((b, s), dtype=torch.int32)
+    for row in range(b):
+        p, doc = 0, 0
+        while p < s:
+            n = int(torch.randint(1, max(2, s // 3), (1,), generator=gen))
+            n = min(n, s - p)
+            label[row, p:p + n] = doc % 3            # labels repeat: a reused label after another run is a new segment
+            if doc % 4 == 3 and row != 1:
+                mask[row, p:p + n] = 0               # a hole of padding in the middle
+            elif maskgit and n > 8:                  # an image block in the middle of the document
+                lo = p + n // 4
+                hi = p + n // 2
+                end[row, lo:hi] = hi - 1
+            p += n
+            doc += 1
+    mask[0, s - s // 5:] = 0                         # trailing padding
+    dev = torch.device("cuda")
+    mask_d, label_d = mask.to(dev), label.to(dev)
+    end_d = end.to(dev) if maskgit else None
+    seg, pos, meta = A.attention_metadata(mask_d, label_d, end_d)
+    want_seg = canonicalize_segment_ids(mask_d, label_d)
+    assert torch.equal(seg, want_seg)
+    assert torch.equal(pos, make_position_ids(mask_d, want_seg, canonical=True))
+    want = A.build_attention_meta_reference(want_seg, end_d)
+    if maskgit:
+        assert torch.equal(meta.lim, want.lim)
+    else:
+        assert meta.lim is None and want.lim is None
+    for name in ("kv_lo", "kv_hi", "kmin", "kmax", "q_lo", "q_hi", "seg_min64", "seg_max64", "lim_min64", "lim_max64"):
+        assert torch.equal(getattr(meta, name), getattr(want, name)), name
+    # canonical ids in, the same ids out
+    again = A.build_attention_meta(seg, end_d)
+    assert torch.equal(again.seg, seg) and torch.equal(again.kv_lo, want.kv_lo) and torch.equal(again.q_hi, want.q_hi)
