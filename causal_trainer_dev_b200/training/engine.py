@@ -83,6 +83,7 @@ class LayerwiseEngine:
         self.options = options or EngineOptions()
         self.launches = 0
         self.kept_layers = 0
+        self.train_base = True                   # False: base weights frozen, no gradient buffers (LoRA)
         self._inv_freq: torch.Tensor | None = None
         import os
 
@@ -101,10 +102,28 @@ class LayerwiseEngine:
         sequence is split over ranks)."""
         return t
 
-    def _wgrad(self, dy: torch.Tensor, x: torch.Tensor, gview: torch.Tensor, accumulate: bool) -> None:
-        """Weight gradient ``dy^T x``.  With ``overlap_wgrad`` it is issued on a second stream: nothing
-        in the layer waits for it, so the partly filled last wave of one persistent GEMM is filled by
-        the first CTAs of the next kernel instead of leaving SMs idle."""
+    def _project(self, li: int, name: str, x: torch.Tensor, w: dict[str, torch.Tensor]) -> torch.Tensor:
+        """Projection ``name`` ("qkv" | "o" | "gu" | "down") of layer ``li``: ``x @ W^T (+ bias)``."""
+        self._count()
+        return gemm(x, w[name + "_w"], bias=w.get(name + "_b"))
+
+    def _project_backward(self, li: int, name: str, dy: torch.Tensor, x: torch.Tensor, w: dict[str, torch.Tensor],
+                          g: dict[str, torch.Tensor], accumulate: bool) -> torch.Tensor:
+        """Input gradient of projection ``name``; its weight (and bias) gradients go into ``g``."""
+        dx = gemm(dy, w[name + "_w"], b_mn=True)
+        self._count()
+        self._wgrad(dy, x, g[name + "_w"], accumulate)
+        if name + "_b" in w:
+            self._bias_grad(dy, g[name + "_b"], accumulate)
+        return dx
+
+    def _wgrad(self, dy: torch.Tensor, x: torch.Tensor, gview: torch.Tensor | None, accumulate: bool) -> None:
+        """Weight gradient ``dy^T x`` (skipped when the weight is frozen: ``gview`` is None).  With
+        ``overlap_wgrad`` it is issued on a second stream: nothing in the layer waits for it, so the
+        partly filled last wave of one persistent GEMM is filled by the first CTAs of the next kernel
+        instead of leaving SMs idle."""
+        if gview is None:
+            return
         side = self._wgrad_stream
         if side is None:
             gemm(dy, x, a_mn=True, b_mn=True, out=gview, accumulate=accumulate)
@@ -122,7 +141,9 @@ class LayerwiseEngine:
         if self._wgrad_stream is not None:
             torch.cuda.current_stream().wait_stream(self._wgrad_stream)
 
-    def _bias_grad(self, dy: torch.Tensor, gview: torch.Tensor, accumulate: bool) -> None:
+    def _bias_grad(self, dy: torch.Tensor, gview: torch.Tensor | None, accumulate: bool) -> None:
+        if gview is None:
+            return
         s = dy.float().sum(0)
         if accumulate:
             gview.add_(s.to(gview.dtype))
@@ -165,7 +186,7 @@ class LayerwiseEngine:
         t = resid.shape[0]
         qw, kvw, d_head = cfg.query_width, cfg.key_value_width, cfg.head_dim
         n1, rstd1, x = ew.rmsnorm_forward(resid, w["ln1"], cfg.rms_norm_eps, residual=branch)
-        qkv = gemm(n1, w["qkv_w"], bias=w.get("qkv_b"))
+        qkv = self._project(li, "qkv", n1, w)
         ew.rope_inplace(qkv, ctx["cos"], ctx["sin"], cfg.num_attention_heads + cfg.num_key_value_heads, d_head,
                         cfg.rotary_dim, cfg.rope_style)
         b, s = ctx["batch"], ctx["seq"]
@@ -173,12 +194,12 @@ class LayerwiseEngine:
         k = qkv[:, qw:qw + kvw].view(b, s, cfg.num_key_value_heads, d_head)
         v = qkv[:, qw + kvw:].view(b, s, cfg.num_key_value_heads, d_head)
         o, lse, routing = self._attention_forward(q, k, v, ctx, li)
-        attn_out = gemm(o.view(t, qw), w["o_w"])
+        attn_out = self._project(li, "o", o.view(t, qw), w)
         n2, rstd2, h = ew.rmsnorm_forward(x, w["ln2"], cfg.rms_norm_eps, residual=attn_out)
-        gu = gemm(n2, w["gu_w"])
+        gu = self._project(li, "gu", n2, w)
         act = ew.swiglu_forward(gu)
-        mlp = gemm(act, w["down_w"])
-        self._count(10)
+        mlp = self._project(li, "down", act, w)
+        self._count(6)
         saved = None
         if save == "all":      # transient: consumed by the backward pass that follows at once
             saved = dict(x=x, n1=n1, rstd1=rstd1, qkv=qkv, o=o, lse=lse, h=h, n2=n2, rstd2=rstd2, gu=gu, act=act,
@@ -189,7 +210,7 @@ class LayerwiseEngine:
 
     # ------------------------------------------------------------------ layer backward
     def _layer_backward(self, w: dict[str, torch.Tensor], g: dict[str, torch.Tensor], sv: dict, dout: torch.Tensor,
-                        ctx: dict, accumulate: bool) -> torch.Tensor:
+                        ctx: dict, accumulate: bool, li: int = 0) -> torch.Tensor:
         """``dout`` is the gradient of the layer output (h + mlp); returns the gradient of its input x."""
         cfg = self.cfg
         t = dout.shape[0]
@@ -203,19 +224,16 @@ class LayerwiseEngine:
             sv["n1"] = ew.rmsnorm_forward(sv["x"], w["ln1"], cfg.rms_norm_eps)[0]
             self._count(3)
         # MLP branch
-        dact = gemm(dout, w["down_w"], b_mn=True)
-        self._wgrad(dout, sv["act"], g["down_w"], accumulate)
+        dact = self._project_backward(li, "down", dout, sv["act"], w, g, accumulate)
         dgu = ew.swiglu_backward(sv["gu"], dact)
         del dact
-        dn2 = gemm(dgu, w["gu_w"], b_mn=True)
-        self._wgrad(dgu, sv["n2"], g["gu_w"], accumulate)
+        dn2 = self._project_backward(li, "gu", dgu, sv["n2"], w, g, accumulate)
         del dgu
         dh, _ = ew.rmsnorm_backward(dn2, sv["h"], w["ln2"], sv["rstd2"], dres=dout, dw_out=g["ln2"],
                                     dw_accumulate=accumulate)
         del dn2
         # attention branch: dh is the gradient of h = x + attn_out
-        do = gemm(dh, w["o_w"], b_mn=True)
-        self._wgrad(dh, sv["o"].view(t, qw), g["o_w"], accumulate)
+        do = self._project_backward(li, "o", dh, sv["o"].view(t, qw), w, g, accumulate)
         qkv = sv["qkv"]
         q = qkv[:, :qw].view(b, s, cfg.num_attention_heads, d_head)
         k = qkv[:, qw:qw + kvw].view(b, s, cfg.num_key_value_heads, d_head)
@@ -228,13 +246,10 @@ class LayerwiseEngine:
                                  sv.get("routing"), ctx, dq, dk, dv)
         ew.rope_inplace(dqkv, ctx["cos"], ctx["sin"], cfg.num_attention_heads + cfg.num_key_value_heads, d_head,
                         cfg.rotary_dim, cfg.rope_style, inverse=True)
-        dn1 = gemm(dqkv, w["qkv_w"], b_mn=True)
-        self._wgrad(dqkv, sv["n1"], g["qkv_w"], accumulate)
-        if "qkv_b" in w:
-            self._bias_grad(dqkv, g["qkv_b"], accumulate)
+        dn1 = self._project_backward(li, "qkv", dqkv, sv["n1"], w, g, accumulate)
         dx, _ = ew.rmsnorm_backward(dn1, sv["x"], w["ln1"], sv["rstd1"], dres=dh, dw_out=g["ln1"],
                                     dw_accumulate=accumulate)
-        self._count(12)
+        self._count(8)
         return dx
 
     # ------------------------------------------------------------------ activation policy
@@ -325,11 +340,11 @@ class LayerwiseEngine:
         # ---------------- head: final norm + cut cross-entropy ----------------
         final = prov.acquire("final", prefetch=f"layer.{nl - 1}")
         fw = self._views(final)
-        fg = self._views(final, prov.grad_buffer("final"))
+        fg = self._views(final, prov.grad_buffer("final")) if self.train_base else dict.fromkeys(fw)
         y, rstd_f, xf = ew.rmsnorm_forward(resid, fw["norm"], cfg.rms_norm_eps, residual=branch)
         targets, weights = losses.aligned_targets_and_weights(batch)
         targets, weights = self.select_tokens(targets).reshape(-1), self.select_tokens(weights).reshape(-1)
-        train_head = self.options.train_lm_head
+        train_head = self.options.train_lm_head and self.train_base
         # Active-row compaction: with sparse supervision (assistant-only loss, MaskGIT targets) only
         # the rows that carry weight go through the LM head; their gradients are scattered back.
         # (src/causal_trainer/kernels/cut_cross_entropy.py:673-694; stable order, so results do not
@@ -373,18 +388,18 @@ class LayerwiseEngine:
         for li in reversed(range(nl)):
             unit = prov.acquire(f"layer.{li}", prefetch=f"layer.{li - 1}" if li > 0 else "embed")
             w = self._views(unit)
-            g = self._views(unit, prov.grad_buffer(f"layer.{li}"))
+            g = self._views(unit, prov.grad_buffer(f"layer.{li}")) if self.train_base else dict.fromkeys(w)
             layer_in = inputs.pop()
             saved = kept.pop()
             if saved is None:
                 _, _, saved = self._layer_forward(w, layer_in[0], layer_in[1], ctx, li, save="all")
-            dout = self._layer_backward(w, g, saved, dout, ctx, accumulate)
+            dout = self._layer_backward(w, g, saved, dout, ctx, accumulate, li)
             del saved, layer_in
             self._join_wgrads()
             prov.release(f"layer.{li}")
             prov.grads_ready(f"layer.{li}", last)
         # ---------------- embedding ----------------
-        if self.options.train_embed:
+        if self.options.train_embed and self.train_base:
             lay = embed_layout(cfg)
             seg = lay.segment("embed")
             gbuf = prov.grad_buffer("embed")[seg.offset:seg.offset + seg.numel].view(seg.shape)

@@ -223,9 +223,13 @@ class TrainingRun:
         self.cuda = torch.cuda.is_available()
         self.device = torch.device("cuda", self.env.local_rank) if self.cuda else torch.device("cpu")
         self.param_dtype = torch.bfloat16 if args.param_dtype == "bfloat16" else torch.float32
-        self.use_engine = (self.cuda and self.param_dtype == torch.bfloat16 and args.dtype == "bfloat16"
-                           and args.attn_mechanism != "vanilla" and not args.lora and args.loss_implementation != "xla"
-                           and (args.attention_options is None or args.attention_options.backend != "reference"))
+        engine_ok = (self.cuda and self.param_dtype == torch.bfloat16 and args.dtype == "bfloat16"
+                     and args.attn_mechanism != "vanilla" and args.loss_implementation != "xla"
+                     and (args.attention_options is None or args.attention_options.backend != "reference"))
+        self.use_engine = engine_ok and not args.lora
+        # adapters on the CUDA engine: every rank holds the frozen base, adapter gradients are all-reduced
+        self.use_lora_engine = (engine_ok and args.lora and not args.lora_train_embed_and_lm_head
+                                and self.lattice.size("tp") == 1 and self.lattice.size("sp") == 1)
         if self.lattice.size("sp") > 1 and (self.lattice.size("tp") > 1 or not self.use_engine
                                             or args.attention_options is not None):
             raise ValueError("sequence parallelism (sp > 1) runs on the bf16 CUDA engine with tp = 1 and dense "
@@ -424,10 +428,20 @@ class TrainingRun:
                                                base=self.params)
                     if self.checkpoint is not None and self.artifact_kind == "peft-adapter":
                         self.lora.load_peft_tensors(st.load_file(self.checkpoint.path / "adapter_model.safetensors"))
-                    opts.lora = self.lora
-                    extra = [(t.detach(), t.dim() > 1, (lambda t=t: t.grad)) for _, t in self.lora.trainable()]
-                producer = AutogradProducer(self.params, opts, a.loss_implementation, a.loss_token_budget,
-                                            a.cut_chunk_size, lora=self.lora)
+                if self.use_lora_engine:
+                    from .engine import EngineOptions, LocalProvider
+                    from .lora_engine import LoraLayerwiseEngine
+
+                    producer = LoraLayerwiseEngine(self.cfg, LocalProvider(self.params, torch.bfloat16), self.lora, EngineOptions(
+                        cut_chunk_rows=a.cut_chunk_size or 4096, attention_options=a.attention_options,
+                        loss_backend="logits" if a.loss_implementation == "pallas" else "cut"))
+                    extra = producer.extra_regions()
+                else:
+                    if a.lora:
+                        opts.lora = self.lora
+                        extra = [(t.detach(), t.dim() > 1, (lambda t=t: t.grad)) for _, t in self.lora.trainable()]
+                    producer = AutogradProducer(self.params, opts, a.loss_implementation, a.loss_token_budget,
+                                                a.cut_chunk_size, lora=self.lora)
                 dp_group = rt.host_group() if (rt.process_count() > 1 and not self.cuda) else None
                 self.step_fn = TrainStep(self.params, producer, adamw, schedule, frozen=frozen, dp_group=dp_group,
                                          extra_regions=extra, train_base=not a.lora)

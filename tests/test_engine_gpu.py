@@ -135,3 +135,56 @@ def test_engine_sparse_supervision_compacts_rows(cuda_lib, backend):
     for name in ("lm_head.weight", "model.norm.weight", "model.layers.1.mlp.down_proj.weight",
                  "model.layers.0.self_attn.q_proj.weight", "model.embed_tokens.weight"):
         assert _rel(eng_params.grad_tensor(name), ref.grad_tensor(name)) < 0.06, name
+
+
+def test_lora_engine_matches_oracle_adapter_gradients(cuda_lib):
+    """Frozen base on the tcgen05 GEMMs + rank-r adapter paths against autograd through the oracle decoder."""
+    from causal_trainer_dev_b200.models.config import preset
+    from causal_trainer_dev_b200.models.decoder import ForwardOptions
+    from causal_trainer_dev_b200.models.lora import LoraState
+    from causal_trainer_dev_b200.models.params import ModelParams
+    from causal_trainer_dev_b200.training.engine import LocalProvider
+    from causal_trainer_dev_b200.training.lora_engine import LoraLayerwiseEngine
+    from causal_trainer_dev_b200.training.optimizer import AdamWConfig, ScheduleConfig
+    from causal_trainer_dev_b200.training.steps import AutogradProducer, TrainStep
+
+    cfg = preset("tiny", vocab_size=4096)
+    base = ModelParams.init_random(cfg, seed=1, dtype=torch.bfloat16)
+    batch = _batch(cfg, 2, 256)
+    lora = LoraState.init(cfg, 16, seed=4, dtype=torch.bfloat16, device="cuda")
+    gen = torch.Generator(device="cuda").manual_seed(9)
+    with torch.no_grad():
+        for key, b in lora.b.items():                # a trained adapter: B is no longer zero
+            b.copy_(torch.randn(b.shape, generator=gen, device="cuda") * 0.02)
+    # oracle: fp32 autograd on the same bf16-rounded base weights and adapters
+    ref = ModelParams(cfg, dtype=torch.float32, device="cuda")
+    ref.load_state_dict({k: v.float() for k, v in base.state_dict().items()})
+    ref_lora = LoraState(cfg, 16)
+    for key in lora.a:
+        ref_lora.a[key] = lora.a[key].detach().float().requires_grad_()
+        ref_lora.b[key] = lora.b[key].detach().float().requires_grad_()
+    nll_ref, _ = AutogradProducer(ref, ForwardOptions(attn_mechanism="vanilla", lora=ref_lora), lora=ref_lora)(
+        batch, 1.0 / 400, True)
+    params = ModelParams(cfg, dtype=torch.bfloat16, device="cuda")
+    params.load_state_dict(base.state_dict())
+    engine = LoraLayerwiseEngine(cfg, LocalProvider(params, torch.bfloat16), lora)
+    nll, _ = engine(batch, 1.0 / 400, True)
+    assert abs(nll.item() - nll_ref.item()) / nll_ref.item() < 5e-3
+    for key in lora.a:
+        ga, gb = engine.grads[key]
+        assert _rel(ga, ref_lora.a[key].grad) < 0.08, key
+        assert _rel(gb, ref_lora.b[key].grad) < 0.08, key
+    assert all(u.grad is None for u in params.units.values())          # no gradient memory for the frozen base
+    engine(batch, 1.0 / 400, False)                                     # accumulation over micro-batches
+    key = (1, "gate_proj")
+    assert _rel(engine.grads[key][0], 2 * ref_lora.a[key].grad) < 0.08
+    # adapters train, the base stays bit-identical
+    before = {k: v.clone() for k, v in params.state_dict().items()}
+    step = TrainStep(params, engine, AdamWConfig(weight_decay=0.0), ScheduleConfig(2e-3, 0.0, "constant", 0, 10),
+                     extra_regions=engine.extra_regions(), train_base=False)
+    first = step.run([batch]).to_floats()
+    for _ in range(6):
+        last = step.run([batch]).to_floats()
+    assert last["loss"] < first["loss"] - 0.05
+    assert all(torch.equal(v, before[k]) for k, v in params.state_dict().items())
+    assert cuda_lib.device_status() == (0, 0, 0, 0)

@@ -53,3 +53,24 @@ def test_cli_pallas_loss_backend_and_frozen_embeddings(cuda_lib, tmp_path):
     argv = _argv(tmp_path, "--max_steps", "3", "--loss_implementation", "pallas")
     assert runner.main(argv) == 0
     assert cuda_lib.device_status() == (0, 0, 0, 0)
+
+
+def test_cli_lora_runs_on_the_cuda_engine_and_writes_a_peft_adapter(cuda_lib, tmp_path):
+    from causal_trainer_dev_b200.checkpointing import safetensors_io as st
+    from causal_trainer_dev_b200.training import runner
+    from causal_trainer_dev_b200.training.arguments import parse_args
+    from causal_trainer_dev_b200.training.lora_engine import LoraLayerwiseEngine
+
+    argv = _argv(tmp_path, "--max_steps", "3", "--lora", "--lora_rank", "8", "--lora_save_adapter_only")
+    run = runner.TrainingRun(parse_args(argv))
+    assert run.use_lora_engine and not run.use_engine
+    run.resolve_model(); run.load_data(); run.discover_resume(); run.build_model()
+    assert isinstance(run.step_fn.producer, LoraLayerwiseEngine)
+    run.train()
+    out = tmp_path / "out"
+    cfg = json.loads((out / "adapter_config.json").read_text())
+    assert cfg["r"] == 8 and cfg["lora_alpha"] == 8
+    tensors = st.load_file(out / "adapter_model.safetensors")
+    b = tensors["base_model.model.model.layers.0.self_attn.q_proj.lora_B.weight"]
+    assert b.shape == (256, 8) and float(b.float().abs().max()) > 0.0       # B left zero: the adapter trained
+    assert cuda_lib.device_status() == (0, 0, 0, 0)
