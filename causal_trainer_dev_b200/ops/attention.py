@@ -42,6 +42,9 @@ class AttentionMeta:
     lim_min64: torch.Tensor      # [B,S/64] int32
     lim_max64: torch.Tensor      # [B,S/64] int32
     attention_end: torch.Tensor | None = None  # kept for the oracle backend
+    start: torch.Tensor | None = None        # [B,S] int32 first token of the token's run
+    end: torch.Tensor | None = None          # [B,S] int32 last token of the token's run
+    first_q: torch.Tensor | None = None      # [B,S] int32 first query that sees the token as a key
 
     @property
     def batch(self) -> int:
@@ -72,15 +75,15 @@ def attention_metadata(attention_mask: torch.Tensor, segment_ids: torch.Tensor |
     seg = torch.empty((bsz, s), dtype=torch.int32, device=dev)
     pos = torch.empty_like(seg)
     lim = torch.empty_like(seg)
-    scratch = torch.empty((bsz, 4, s), dtype=torch.int32, device=dev)
+    rows = torch.empty((4, bsz, s), dtype=torch.int32, device=dev)
     s128 = torch.empty((6, bsz, s // BLOCK), dtype=torch.int32, device=dev)
     s64 = torch.empty((4, bsz, s // 64), dtype=torch.int32, device=dev)
     code = _lib.lib().ctb_attention_meta(_lib.ptr(mask), _lib.ptr(label), _lib.ptr(end), bsz, s, _lib.ptr(seg),
-                                         _lib.ptr(pos), _lib.ptr(lim), _lib.ptr(scratch), _lib.ptr(s128), _lib.ptr(s64),
+                                         _lib.ptr(pos), _lib.ptr(lim), _lib.ptr(rows), _lib.ptr(s128), _lib.ptr(s64),
                                          _lib.stream_ptr())
     _lib.check(code, "ctb_attention_meta")
     meta = AttentionMeta(seg, lim if attention_end is not None else None, s128[0], s128[1], s128[2], s128[3], s128[4],
-                         s128[5], s64[0], s64[1], s64[2], s64[3], attention_end)
+                         s128[5], s64[0], s64[1], s64[2], s64[3], attention_end, rows[0], rows[1], rows[2])
     return seg, pos, meta
 
 
@@ -143,6 +146,7 @@ def build_attention_meta_reference(segment_ids: torch.Tensor, attention_end: tor
     return AttentionMeta(
         seg, lim, i32(kv_lo), i32(kv_hi), i32(kmin), i32(kmax), i32(q_lo), i32(q_hi),
         i32(seg64.amin(-1)), i32(seg64.amax(-1)), i32(lim64.amin(-1)), i32(lim64.amax(-1)), attention_end,
+        i32(seg_start), i32(seg_end), i32(first_q),
     )
 
 
@@ -202,7 +206,7 @@ def flash_attention_forward(
     lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
     code = _lib.lib().ctb_attn_fwd_range(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(meta.seg), _lib.ptr(meta.lim),
-        _lib.ptr(meta.kv_lo), _lib.ptr(meta.kv_hi), _lib.ptr(meta.kmin), _lib.ptr(meta.kmax),
+        _lib.ptr(meta.start), _lib.ptr(meta.kv_lo), _lib.ptr(meta.kv_hi),
         b, s, sq, q_offset, hq, hkv, d, ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)),
         ctypes.c_long(_row_stride(v)), ctypes.c_long(_row_stride(out)), ctypes.c_float(scale),
         ctypes.c_longlong(spin_budget), _lib.stream_ptr(),
@@ -238,8 +242,7 @@ def flash_attention_backward(
         code = L.ctb_attn_bwd_range(
             mode, _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
             _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(meta.seg), _lib.ptr(meta.lim), _lib.ptr(meta.kv_lo),
-            _lib.ptr(meta.kv_hi), _lib.ptr(meta.q_lo), _lib.ptr(meta.q_hi), _lib.ptr(meta.seg_min64),
-            _lib.ptr(meta.seg_max64), _lib.ptr(meta.lim_min64), _lib.ptr(meta.lim_max64),
+            _lib.ptr(meta.kv_hi), _lib.ptr(meta.q_lo), _lib.ptr(meta.q_hi), _lib.ptr(meta.start), _lib.ptr(meta.end), _lib.ptr(meta.first_q),
             b, s, sq, q_offset, hq, hkv, d,
             ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)), ctypes.c_long(_row_stride(v)),
             ctypes.c_long(_row_stride(dout)), ctypes.c_long(_row_stride(dq)), ctypes.c_long(_row_stride(dk)),

@@ -8,6 +8,8 @@ namespace attn {
 // Visibility metadata, built once per step and shared by all layers:
 //   seg    [B,S]      canonical run ids, 0 = padding
 //   lim    [B,S]      inclusive last visible key index = max(i, attention_end[i]); null => i
+//   row_start [B,S]   first token of the run that holds token i (the keys a query sees are the
+//                     contiguous interval [row_start[i], lim[i]])
 //   kv_lo  [B,S/128]  first key index any row of the 128-row query block can see
 //   kv_hi  [B,S/128]  one past the last such key index (kv_hi <= kv_lo: nothing visible)
 //   kmin/kmax [B,S/128] min / max segment id inside each 128-key block
@@ -40,10 +42,9 @@ struct FwdArgs {
   float scale_log2;
   const int* seg;
   const int* lim;
+  const int* row_start;
   const int* kv_lo;
   const int* kv_hi;
-  const int* kmin;
-  const int* kmax;
   float* lse;
   DeviceStatus* status;
   long long spin_budget;
@@ -52,7 +53,7 @@ struct FwdArgs {
 
 struct FwdCall {
   const void* q; const void* k; const void* v; void* o; float* lse;
-  const int* seg; const int* lim; const int* kv_lo; const int* kv_hi; const int* kmin; const int* kmax;
+  const int* seg; const int* lim; const int* row_start; const int* kv_lo; const int* kv_hi;
   int B, S, Hq, Hkv;
   int Sq = 0, q_off = 0;     // Sq == 0: all S queries
   long q_row_stride, k_row_stride, v_row_stride, o_row_stride;
@@ -64,9 +65,11 @@ struct FwdCall {
 
 enum : int { MODE_DKV = 0, MODE_DQ = 1 };
 
-// Extra metadata of the backward kernels, at 64-row granularity:
-//   seg_min64 / seg_max64 [B,S/64]  min / max segment id of each 64-token block
-//   lim_min64 / lim_max64 [B,S/64]  min / max of lim over each 64-token block
+// Extra metadata of the backward kernels, per token [B,S]:
+//   run_start / run_end   first / last token of the token's run
+//   first_q               first query that sees the token as a key
+// so the keys query i sees are [run_start[i], lim[i]] and the queries that see key j are
+// [first_q[j], run_end[j]].
 struct BwdArgs {
   int B, S, Hq, Hkv;
   int Sq, q_off;
@@ -77,10 +80,9 @@ struct BwdArgs {
   const int* kv_hi;
   const int* q_lo;
   const int* q_hi;
-  const int* seg_min64;
-  const int* seg_max64;
-  const int* lim_min64;
-  const int* lim_max64;
+  const int* run_start;
+  const int* run_end;
+  const int* first_q;
   const float* lse;
   const float* delta;
   DeviceStatus* status;
@@ -93,7 +95,7 @@ struct BwdCall {
   void* dq; void* dk; void* dv;
   const float* lse; const float* delta;
   const int* seg; const int* lim; const int* kv_lo; const int* kv_hi; const int* q_lo; const int* q_hi;
-  const int* seg_min64; const int* seg_max64; const int* lim_min64; const int* lim_max64;
+  const int* run_start; const int* run_end; const int* first_q;
   int B, S, Hq, Hkv;
   int Sq = 0, q_off = 0;
   long q_row_stride, k_row_stride, v_row_stride, do_row_stride, dq_row_stride, dk_row_stride, dv_row_stride;

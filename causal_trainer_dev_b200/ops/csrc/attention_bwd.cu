@@ -263,20 +263,28 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int xi = x0 + r + (DKV ? 0 : args.q_off);
     const int xi_local = x0 + r;
     const float LOG2E = 1.4426950408889634f;
-    int row_seg = args.seg[b * args.S + xi];
-    int row_lim = xi;
+    const int row_seg = args.seg[b * args.S + xi];
+    // interval of visible columns (whole-sequence positions): see the mask below
+    int row_a, row_b;
+    if (DKV) {
+      row_a = args.first_q[b * args.S + xi];
+      row_b = args.run_end[b * args.S + xi];
+    } else {
+      row_a = args.run_start[b * args.S + xi];
+      row_b = (args.lim != nullptr) ? args.lim[b * args.S + xi] : xi;
+    }
     const int row_start = sparse ? args.sp.doc_start[b * args.S + xi] : 0;
     // DKV: the document-relative block of this key is the bit every query column is tested for
     const int row_blk = (sparse && DKV) ? (xi - row_start) / args.sp.block : 0;
     float row_lse2 = 0.f, row_delta = 0.f;
     if (!DKV) {
-      if (args.lim != nullptr) row_lim = args.lim[b * args.S + xi];
       row_lse2 = args.lse[(static_cast<size_t>(b) * args.Hq + head) * args.Sq + xi_local] * LOG2E;
       row_delta = args.delta[(static_cast<size_t>(b) * args.Hq + head) * args.Sq + xi_local];
     }
     bool ok = true;
     uint32_t sph = 0, dph = 0;
     int uses = 0;
+    const uint64_t scale2 = pack_f32x2(args.scale_log2, args.scale_log2);
     float* meta_l = reinterpret_cast<float*>(smem + L::OFF_META) + u * 128;
     float* meta_d = meta_l + 64;
     for (int it = u; it < n_iter; it += 2, ++uses) {
@@ -288,7 +296,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       float meta_v = 0.f;
       if (DKV && half == 0) {
         const size_t base = (static_cast<size_t>(b) * args.Hq + hq) * args.Sq + (y0 - args.q_off);
-        meta_v = (r < 64) ? __ldg(args.lse + base + r) * LOG2E : __ldg(args.delta + base + r - 64);
+        meta_v = (r < 64) ? -__ldg(args.lse + base + r) * LOG2E : -__ldg(args.delta + base + r - 64);
       }
       bool good = mbar_wait(&s_full[u], sph, abort_flag, st, SITE_B_CW_S, budget);
       sph ^= 1u;
@@ -309,46 +317,43 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         ok = false;
         break;
       }
-      // ---- visibility class of this row against the 64 columns ----
-      const int cmin = args.seg_min64[b * nb64 + yb];
-      const int cmax = args.seg_max64[b * nb64 + yb];
-      bool none, all;
-      if (DKV) {
-        const int lmin = args.lim_min64[b * nb64 + yb];
-        const int lmax = args.lim_max64[b * nb64 + yb];
-        none = (row_seg == 0) || (row_seg < cmin) || (row_seg > cmax) || (lmax < xi);
-        all = (row_seg != 0) && (cmin == row_seg) && (cmax == row_seg) && (lmin >= xi);
-      } else {
-        none = (row_seg == 0) || (row_seg < cmin) || (row_seg > cmax) || (y0 > row_lim);
-        all = (row_seg != 0) && (cmin == row_seg) && (cmax == row_seg) && (y0 + 63 <= row_lim);
-      }
-      int bound = 0x7fffffff;
-      bool v0 = true, v1 = true;
+      // ---- visibility of this row against its 32 columns, as a bit mask.  The keys a query sees
+      // and the queries that see a key are both contiguous intervals (runs are contiguous):
+      //   DQ   row = query xi,  columns = keys     [start[xi], lim[xi]]
+      //   DKV  row = key xi,    columns = queries  [first_q[xi], end[xi]]
+      const int base = y0 + 32 * half;
+      unsigned vis32 = (row_seg == 0) ? 0u : (bits_from(row_a - base) & bits_upto(row_b - base));
       const unsigned* col_sel = nullptr;
-      if (sparse && !none) {
+      if (sparse && vis32 != 0u) {
         if (DKV) {
           if ((row_blk >> 5) >= args.sp.words) {
-            none = true;
+            vis32 = 0u;
           } else {
             // when every query of the block selected this key's block the selection adds nothing
-            // to the segment / causal test and the row keeps its fast paths
+            // to the interval test and the row keeps its fast paths
             const unsigned aw = __ldg(args.sp.allsel + ((static_cast<size_t>(b) * args.Hq + hq) * nb64 + yb) * args.sp.words +
                                       (row_blk >> 5));
-            if (!((aw >> (row_blk & 31)) & 1u)) {
-              all = false;
+            if (!((aw >> (row_blk & 31)) & 1u))
               col_sel = args.sp.sel + ((static_cast<size_t>(b) * args.Hq + hq) * args.S + y0) * args.sp.words +
                         (row_blk >> 5);
-            }
           }
         } else {
           const SparseRow sr = sparse_row(args.sp, b, head, args.Hq, args.S, xi, row_start, y0, 64);
-          bound = sr.bound; v0 = sr.v0; v1 = sr.v1;
-          none = !v0 && !v1;
-          all = all && v0 && v1;
+          const unsigned above = bits_from(sr.bound - base);               // keys >= bound
+          vis32 &= (sr.v0 ? ~above : 0u) | (sr.v1 ? above : 0u);
         }
       }
-      const int* col_seg = args.seg + b * args.S + y0;
-      const int* col_lim = (args.lim != nullptr) ? args.lim + b * args.S + y0 : nullptr;
+      if (col_sel != nullptr) {
+        // per-query selection bit of this key's block, for the 32 columns of this thread
+        const int bit = row_blk & 31;
+        unsigned selbits = 0u;
+#pragma unroll 4
+        for (int e = 0; e < 32; ++e)
+          selbits |= ((__ldg(col_sel + static_cast<size_t>(32 * half + e) * args.sp.words) >> bit) & 1u) << e;
+        vis32 &= selbits;
+      }
+      const bool none = vis32 == 0u;
+      const bool all = vis32 == 0xffffffffu;
 #pragma unroll 1
       for (int sub = 0; sub < 2; ++sub) {
         const int c = half;
@@ -379,40 +384,34 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
                 l2[0] = lv.x; l2[1] = lv.y; l2[2] = lv.z; l2[3] = lv.w;
                 dl[0] = dv.x; dl[1] = dv.y; dl[2] = dv.z; dl[3] = dv.w;
               } else {
-                l2[0] = l2[1] = l2[2] = l2[3] = row_lse2;
-                dl[0] = dl[1] = dl[2] = dl[3] = row_delta;
+                l2[0] = l2[1] = l2[2] = l2[3] = -row_lse2;
+                dl[0] = dl[1] = dl[2] = dl[3] = -row_delta;
               }
               bool vis[4] = {true, true, true, true};
               if (!all) {
-                const int4 sg = __ldg(reinterpret_cast<const int4*>(col_seg) + c * 8 + e4);
-                const int col0 = y0 + c * 32 + e4 * 4;
-                if (DKV) {
-                  int4 lm = make_int4(col0, col0 + 1, col0 + 2, col0 + 3);
-                  if (col_lim != nullptr) lm = __ldg(reinterpret_cast<const int4*>(col_lim) + c * 8 + e4);
-                  vis[0] = (sg.x == row_seg) && (xi <= lm.x);
-                  vis[1] = (sg.y == row_seg) && (xi <= lm.y);
-                  vis[2] = (sg.z == row_seg) && (xi <= lm.z);
-                  vis[3] = (sg.w == row_seg) && (xi <= lm.w);
-                  if (col_sel != nullptr) {
-                    const unsigned* cs = col_sel + static_cast<size_t>(c * 32 + e4 * 4) * args.sp.words;
-                    const int bit = row_blk & 31;
-#pragma unroll
-                    for (int q4 = 0; q4 < 4; ++q4)
-                      vis[q4] = vis[q4] && ((__ldg(cs + static_cast<size_t>(q4) * args.sp.words) >> bit) & 1u);
-                  }
-                } else {
-                  vis[0] = (sg.x == row_seg) && (col0 + 0 <= row_lim) && (col0 + 0 < bound ? v0 : v1);
-                  vis[1] = (sg.y == row_seg) && (col0 + 1 <= row_lim) && (col0 + 1 < bound ? v0 : v1);
-                  vis[2] = (sg.z == row_seg) && (col0 + 2 <= row_lim) && (col0 + 2 < bound ? v0 : v1);
-                  vis[3] = (sg.w == row_seg) && (col0 + 3 <= row_lim) && (col0 + 3 < bound ? v0 : v1);
-                }
+                const unsigned nib = vis32 >> (e4 * 4);      // e4 counts groups of four of the 32 columns
+                vis[0] = nib & 1u;
+                vis[1] = nib & 2u;
+                vis[2] = nib & 4u;
+                vis[3] = nib & 8u;
               }
+              // p = exp2(s * scale - lse), dS = p * (dP - delta): two columns per packed instruction
+              // (l2 / dl hold the negated statistics)
 #pragma unroll
-              for (int q4 = 0; q4 < 4; ++q4) {
-                const int e = gg * 8 + h4 * 4 + q4;
-                const float pe = vis[q4] ? fast_exp2(__uint_as_float(rs[e]) * args.scale_log2 - l2[q4]) : 0.f;
-                p[h4 * 4 + q4] = pe;
-                ds[h4 * 4 + q4] = pe * (__uint_as_float(rd[e]) - dl[q4]);
+              for (int pr = 0; pr < 2; ++pr) {
+                const int e = gg * 8 + h4 * 4 + pr * 2;
+                const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), scale2,
+                                              pack_f32x2(l2[pr * 2], l2[pr * 2 + 1]));
+                float xa, xb;
+                unpack_f32x2(x2, xa, xb);
+                const float pa = vis[pr * 2] ? fast_exp2(xa) : 0.f;
+                const float pb = vis[pr * 2 + 1] ? fast_exp2(xb) : 0.f;
+                const uint64_t d2 = add_f32x2(pack_f32x2(__uint_as_float(rd[e]), __uint_as_float(rd[e + 1])),
+                                              pack_f32x2(dl[pr * 2], dl[pr * 2 + 1]));
+                const uint64_t ds2 = mul_f32x2(pack_f32x2(pa, pb), d2);
+                p[h4 * 4 + pr * 2] = pa;
+                p[h4 * 4 + pr * 2 + 1] = pb;
+                unpack_f32x2(ds2, ds[h4 * 4 + pr * 2], ds[h4 * 4 + pr * 2 + 1]);
               }
             }
           }
@@ -517,7 +516,7 @@ int launch_bwd(const BwdCall& c) {
   a.scale = c.scale;
   a.scale_log2 = c.scale * 1.4426950408889634f;
   a.seg = c.seg; a.lim = c.lim; a.kv_lo = c.kv_lo; a.kv_hi = c.kv_hi; a.q_lo = c.q_lo; a.q_hi = c.q_hi;
-  a.seg_min64 = c.seg_min64; a.seg_max64 = c.seg_max64; a.lim_min64 = c.lim_min64; a.lim_max64 = c.lim_max64;
+  a.run_start = c.run_start; a.run_end = c.run_end; a.first_q = c.first_q;
   a.lse = c.lse; a.delta = c.delta;
   a.sp = c.sp;
   a.status = device_status();
@@ -543,8 +542,7 @@ int launch_bwd(const BwdCall& c) {
 // stride; lse and delta are [B,Hq,S] fp32.
 CTB_API int ctb_attn_bwd(int mode, const void* q, const void* k, const void* v, const void* dout, void* dq, void* dk,
                          void* dv, const float* lse, const float* delta, const int* seg, const int* lim,
-                         const int* kv_lo, const int* kv_hi, const int* q_lo, const int* q_hi, const int* seg_min64,
-                         const int* seg_max64, const int* lim_min64, const int* lim_max64, int B, int S, int Hq,
+                         const int* kv_lo, const int* kv_hi, const int* q_lo, const int* q_hi, const int* run_start, const int* run_end, const int* first_q, int B, int S, int Hq,
                          int Hkv, int D, long q_rs, long k_rs, long v_rs, long do_rs, long dq_rs, long dk_rs,
                          long dv_rs, float scale, long long spin_budget, void* stream) {
   if (S % 128) return ctb::fail("attention: sequence length must be a multiple of 128");
@@ -552,7 +550,7 @@ CTB_API int ctb_attn_bwd(int mode, const void* q, const void* k, const void* v, 
   ctb::attn::BwdCall c{};
   c.q = q; c.k = k; c.v = v; c.dout = dout; c.dq = dq; c.dk = dk; c.dv = dv; c.lse = lse; c.delta = delta;
   c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi; c.q_lo = q_lo; c.q_hi = q_hi;
-  c.seg_min64 = seg_min64; c.seg_max64 = seg_max64; c.lim_min64 = lim_min64; c.lim_max64 = lim_max64;
+  c.run_start = run_start; c.run_end = run_end; c.first_q = first_q;
   c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
   c.q_row_stride = q_rs; c.k_row_stride = k_rs; c.v_row_stride = v_rs; c.do_row_stride = do_rs;
   c.dq_row_stride = dq_rs; c.dk_row_stride = dk_rs; c.dv_row_stride = dv_rs;
@@ -568,8 +566,7 @@ CTB_API int ctb_attn_bwd(int mode, const void* q, const void* k, const void* v, 
 CTB_API int ctb_attn_bwd_range(int mode, const void* q, const void* k, const void* v, const void* dout, void* dq,
                                void* dk, void* dv, const float* lse, const float* delta, const int* seg,
                                const int* lim, const int* kv_lo, const int* kv_hi, const int* q_lo, const int* q_hi,
-                               const int* seg_min64, const int* seg_max64, const int* lim_min64,
-                               const int* lim_max64, int B, int S, int Sq, int q_off, int Hq, int Hkv, int D,
+                               const int* run_start, const int* run_end, const int* first_q, int B, int S, int Sq, int q_off, int Hq, int Hkv, int D,
                                long q_rs, long k_rs, long v_rs, long do_rs, long dq_rs, long dk_rs, long dv_rs,
                                float scale, long long spin_budget, void* stream) {
   if (S % 128 || Sq % 128 || q_off % 128 || q_off < 0 || q_off + Sq > S)
@@ -578,7 +575,7 @@ CTB_API int ctb_attn_bwd_range(int mode, const void* q, const void* k, const voi
   ctb::attn::BwdCall c{};
   c.q = q; c.k = k; c.v = v; c.dout = dout; c.dq = dq; c.dk = dk; c.dv = dv; c.lse = lse; c.delta = delta;
   c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi; c.q_lo = q_lo; c.q_hi = q_hi;
-  c.seg_min64 = seg_min64; c.seg_max64 = seg_max64; c.lim_min64 = lim_min64; c.lim_max64 = lim_max64;
+  c.run_start = run_start; c.run_end = run_end; c.first_q = first_q;
   c.B = B; c.S = S; c.Sq = Sq; c.q_off = q_off; c.Hq = Hq; c.Hkv = Hkv;
   c.q_row_stride = q_rs; c.k_row_stride = k_rs; c.v_row_stride = v_rs; c.do_row_stride = do_rs;
   c.dq_row_stride = dq_rs; c.dk_row_stride = dk_rs; c.dv_row_stride = dv_rs;
@@ -596,8 +593,7 @@ CTB_API int ctb_attn_bwd_range(int mode, const void* q, const void* k, const voi
 CTB_API int ctb_attn_bwd_sparse(int mode, const void* q, const void* k, const void* v, const void* dout, void* dq,
                                 void* dk, void* dv, const float* lse, const float* delta, const int* seg,
                                 const int* lim, const int* kv_lo, const int* kv_hi, const int* q_lo, const int* q_hi,
-                                const int* seg_min64, const int* seg_max64, const int* lim_min64,
-                                const int* lim_max64, const int* it_off, const int* it_cnt, int it_stride,
+                                const int* run_start, const int* run_end, const int* first_q, const int* it_off, const int* it_cnt, int it_stride,
                                 const int* it_list, const unsigned* sel, const unsigned* allsel, const int* doc_start,
                                 int block, int words, int B, int S, int Hq, int Hkv, int D,
                                 long q_rs, long k_rs, long v_rs, long do_rs, long dq_rs, long dk_rs, long dv_rs,
@@ -608,7 +604,7 @@ CTB_API int ctb_attn_bwd_sparse(int mode, const void* q, const void* k, const vo
   ctb::attn::BwdCall c{};
   c.q = q; c.k = k; c.v = v; c.dout = dout; c.dq = dq; c.dk = dk; c.dv = dv; c.lse = lse; c.delta = delta;
   c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi; c.q_lo = q_lo; c.q_hi = q_hi;
-  c.seg_min64 = seg_min64; c.seg_max64 = seg_max64; c.lim_min64 = lim_min64; c.lim_max64 = lim_max64;
+  c.run_start = run_start; c.run_end = run_end; c.first_q = first_q;
   c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
   c.q_row_stride = q_rs; c.k_row_stride = k_rs; c.v_row_stride = v_rs; c.do_row_stride = do_rs;
   c.dq_row_stride = dq_rs; c.dk_row_stride = dk_rs; c.dv_row_stride = dv_rs;

@@ -261,70 +261,67 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     float m_ref = -INFINITY, l_sum = 0.f;
     const int qi_local = q0 + t * 128 + r;             // row of Q / O / LSE held by this rank
     const int qi = args.q_off + qi_local;              // its position in the whole sequence
-    int my_seg = 0, my_lim = qi, my_start = 0;
+    int my_seg = 0, my_lim = qi, my_start = 0, my_first = 0;
     if (tile_valid[t]) {
       my_seg = args.seg[b * args.S + qi];
+      my_first = args.row_start[b * args.S + qi];
       if (args.lim != nullptr) my_lim = args.lim[b * args.S + qi];
       if (sparse) my_start = args.sp.doc_start[b * args.S + qi];
     }
     uint32_t sph = 0, dph = 0;
+    const uint64_t scale2 = pack_f32x2(args.scale_log2, args.scale_log2);
     for (int i = 0; i < n_mine; ++i) {
       const int j = kv_tile(i);
       const int k0 = j * 128;
-      if (!mbar_wait(&s_full[t], sph, abort_flag, st, SITE_F_SM_S, budget)) {
-        ok = false;
-        break;
-      }
-      sph ^= 1u;
-      tc_fence_after();
-      // ---- visibility class of this row for this key block ----
-      const int bmin = args.kmin[b * nqb + j];
-      const int bmax = args.kmax[b * nqb + j];
-      bool none = (my_seg == 0) || (my_seg < bmin) || (my_seg > bmax) || (k0 > my_lim);
-      bool all = (my_seg != 0) && (bmin == my_seg) && (bmax == my_seg) && (k0 + 127 <= my_lim);
+      // ---- visible columns of this row inside the key tile: the keys of a row's run are
+      // contiguous, so they form one interval [c_lo, c_hi] (tile-relative, may lie outside) ----
+      const int c_lo = my_first - k0;
+      const int c_hi = my_lim - k0;
+      bool none = (my_seg == 0) || (c_hi < 0) || (c_lo > 127);
       int bound = 0x7fffffff;     // keys below it need v0, keys from it on need v1
       bool v0 = true, v1 = true;
       if (sparse && !none) {
         const SparseRow sr = sparse_row(args.sp, b, h, args.Hq, args.S, qi, my_start, k0, 128);
         bound = sr.bound; v0 = sr.v0; v1 = sr.v1;
         none = !v0 && !v1;
-        all = all && v0 && v1;
       }
-      const int4* sp = reinterpret_cast<const int4*>(args.seg + b * args.S + k0);
-      // Scales 32 scores of chunk c and applies the mask (-inf where the key is hidden).
-      auto load_chunk = [&](int c, float (&x)[32]) {
-        uint32_t rr[32];
-        tmem_ld32(tmem_s[t] + lane_off + c * 32, rr);
-        tmem_ld_wait();
-        if (none) {
+      const bool all = !none && (c_lo <= 0) && (c_hi >= 127) && v0 && v1;
+      if (!mbar_wait(&s_full[t], sph, abort_flag, st, SITE_F_SM_S, budget)) {
+        ok = false;
+        break;
+      }
+      sph ^= 1u;
+      tc_fence_after();
+      // ---- the whole score row in registers: one TMEM round trip ----
+      uint32_t sc[128];
+      tmem_ld32x4(tmem_s[t] + lane_off, sc);
+      tmem_ld_wait();
+      if (!all) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) x[e] = -INFINITY;
-        } else {
+        for (int c = 0; c < 4; ++c) {
+          unsigned vis = none ? 0u : (bits_from(c_lo - 32 * c) & bits_upto(c_hi - 32 * c));
+          if (sparse) {
+            const unsigned above = bits_from(bound - k0 - 32 * c);      // keys >= bound
+            vis &= (v0 ? ~above : 0u) | (v1 ? above : 0u);
+          }
+          if (vis != 0xffffffffu) {
 #pragma unroll
-          for (int e = 0; e < 32; ++e) x[e] = __uint_as_float(rr[e]) * args.scale_log2;
-          if (!all) {
-#pragma unroll
-            for (int e4 = 0; e4 < 8; ++e4) {
-              const int4 sk = __ldg(sp + c * 8 + e4);
-              const int kk = k0 + c * 32 + e4 * 4;
-              if (!(sk.x == my_seg && kk + 0 <= my_lim && (kk + 0 < bound ? v0 : v1))) x[e4 * 4 + 0] = -INFINITY;
-              if (!(sk.y == my_seg && kk + 1 <= my_lim && (kk + 1 < bound ? v0 : v1))) x[e4 * 4 + 1] = -INFINITY;
-              if (!(sk.z == my_seg && kk + 2 <= my_lim && (kk + 2 < bound ? v0 : v1))) x[e4 * 4 + 2] = -INFINITY;
-              if (!(sk.w == my_seg && kk + 3 <= my_lim && (kk + 3 < bound ? v0 : v1))) x[e4 * 4 + 3] = -INFINITY;
-            }
+            for (int e = 0; e < 32; ++e)
+              if (!((vis >> e) & 1u)) sc[c * 32 + e] = 0xff800000u;     // -inf
           }
         }
-      };
-      // pass 1: row maximum (scores are re-read from TMEM in pass 2 instead of being
-      // held in 128 registers)
-      float mx = -INFINITY;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float x[32];
-        load_chunk(c, x);
-#pragma unroll
-        for (int e = 0; e < 32; ++e) mx = fmaxf(mx, x[e]);
       }
+      // ---- row maximum of the raw scores (the scale is positive), four independent chains ----
+      float mq[4];
+#pragma unroll
+      for (int c = 0; c < 4; ++c) {
+        mq[c] = __uint_as_float(sc[c * 32]);
+#pragma unroll
+        for (int e = 1; e < 31; e += 2)
+          mq[c] = fmax3(mq[c], __uint_as_float(sc[c * 32 + e]), __uint_as_float(sc[c * 32 + e + 1]));
+        mq[c] = fmaxf(mq[c], __uint_as_float(sc[c * 32 + 31]));
+      }
+      const float mx = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3])) * args.scale_log2;
       // ---- lazy running maximum ----
       const bool need = (mx > m_ref + 8.f) || (m_ref == -INFINITY && mx > -INFINITY);
       float alpha = 1.f;
@@ -343,41 +340,40 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         if (__any_sync(0xffffffffu, need)) {
           tc_fence_after();
 #pragma unroll 1
-          for (int c = 0; c < D / 32; ++c) {
-            uint32_t rr[32];
-            tmem_ld32(tmem_o[t] + lane_off + c * 32, rr);
+          for (int c = 0; c < D / 8; ++c) {      // narrow chunks: the score row stays in registers
+            uint32_t rr[8];
+            tmem_ld8(tmem_o[t] + lane_off + c * 8, rr);
             tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 32; ++e) rr[e] = __float_as_uint(__uint_as_float(rr[e]) * alpha);
-            tmem_st32(tmem_o[t] + lane_off + c * 32, rr);
+            for (int e = 0; e < 8; ++e) rr[e] = __float_as_uint(__uint_as_float(rr[e]) * alpha);
+            tmem_st8(tmem_o[t] + lane_off + c * 8, rr);
           }
           tmem_st_wait();
         }
       }
+      // ---- P = exp2(s * scale - m): packed fma / add on pairs, P as bf16 into the swizzled tile ----
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
-      float rs = 0.f;
-#pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        float x[32];
-        load_chunk(c, x);
+      const uint64_t neg_m2 = pack_f32x2(-m_use, -m_use);
+      uint64_t rs2 = pack_f32x2(0.f, 0.f);
 #pragma unroll
-        for (int g = 0; g < 4; ++g) {
-          float p[8];
+      for (int g = 0; g < 16; ++g) {
+        uint32_t w[4];
 #pragma unroll
-          for (int e = 0; e < 8; ++e) {
-            p[e] = fast_exp2(x[g * 8 + e] - m_use);
-            rs += p[e];
-          }
-          uint4 v;
-          v.x = pack_bf16(p[0], p[1]);
-          v.y = pack_bf16(p[2], p[3]);
-          v.z = pack_bf16(p[4], p[5]);
-          v.w = pack_bf16(p[6], p[7]);
-          const int chunk16 = c * 4 + g;  // 16-byte chunk index along the 128 keys
-          *reinterpret_cast<uint4*>(pbuf + (chunk16 / 8) * 16384 + sw128_offset(r, chunk16 % 8)) = v;
+        for (int jj = 0; jj < 4; ++jj) {
+          const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(sc[g * 8 + jj * 2]), __uint_as_float(sc[g * 8 + jj * 2 + 1])),
+                                        scale2, neg_m2);
+          float xa, xb;
+          unpack_f32x2(x2, xa, xb);
+          const float pa = fast_exp2(xa), pb = fast_exp2(xb);
+          rs2 = add_f32x2(rs2, pack_f32x2(pa, pb));
+          w[jj] = pack_bf16(pa, pb);
         }
+        // 16-byte chunk g of the row's 128 keys
+        *reinterpret_cast<uint4*>(pbuf + (g / 8) * 16384 + sw128_offset(r, g % 8)) = make_uint4(w[0], w[1], w[2], w[3]);
       }
-      l_sum += rs;
+      float rs_a, rs_b;
+      unpack_f32x2(rs2, rs_a, rs_b);
+      l_sum += rs_a + rs_b;
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&p_full[t]);
@@ -457,7 +453,7 @@ int launch_fwd(const FwdCall& c) {
   a.B = c.B; a.S = c.S; a.Hq = c.Hq; a.Hkv = c.Hkv;
   a.Sq = Sq; a.q_off = c.q_off;
   a.scale_log2 = c.scale * 1.4426950408889634f;
-  a.seg = c.seg; a.lim = c.lim; a.kv_lo = c.kv_lo; a.kv_hi = c.kv_hi; a.kmin = c.kmin; a.kmax = c.kmax;
+  a.seg = c.seg; a.lim = c.lim; a.row_start = c.row_start; a.kv_lo = c.kv_lo; a.kv_hi = c.kv_hi;
   a.lse = c.lse;
   a.sp = c.sp;
   a.status = device_status();
@@ -482,14 +478,14 @@ int launch_fwd(const FwdCall& c) {
 // q/k/v/o are [B, S, H, D] views with arbitrary row stride (elements between consecutive
 // tokens), so the packed QKV projection output is read in place.  lse is [B, Hq, S] fp32.
 CTB_API int ctb_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse, const int* seg,
-                         const int* lim, const int* kv_lo, const int* kv_hi, const int* kmin, const int* kmax, int B,
+                         const int* lim, const int* row_start, const int* kv_lo, const int* kv_hi, int B,
                          int S, int Hq, int Hkv, int D, long q_row_stride, long k_row_stride, long v_row_stride,
                          long o_row_stride, float scale, long long spin_budget, void* stream) {
   if (S % 128) return ctb::fail("attention: sequence length must be a multiple of 128");
   if (Hq % Hkv) return ctb::fail("attention: Hq must be a multiple of Hkv");
   ctb::attn::FwdCall c{};
-  c.q = q; c.k = k; c.v = v; c.o = o; c.lse = lse; c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi;
-  c.kmin = kmin; c.kmax = kmax; c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
+  c.q = q; c.k = k; c.v = v; c.o = o; c.lse = lse; c.seg = seg; c.lim = lim; c.row_start = row_start; c.kv_lo = kv_lo; c.kv_hi = kv_hi;
+  c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
   c.q_row_stride = q_row_stride; c.k_row_stride = k_row_stride; c.v_row_stride = v_row_stride;
   c.o_row_stride = o_row_stride; c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
   if (D == 128) return ctb::attn::launch_fwd<128>(c);
@@ -500,7 +496,7 @@ CTB_API int ctb_attn_fwd(const void* q, const void* k, const void* v, void* o, f
 // Sequence-parallel forward: q / o hold the Sq queries [q_off, q_off + Sq) of every row, k / v all
 // S keys; lse is [B, Hq, Sq].  q_off and Sq must be multiples of 128.
 CTB_API int ctb_attn_fwd_range(const void* q, const void* k, const void* v, void* o, float* lse, const int* seg,
-                               const int* lim, const int* kv_lo, const int* kv_hi, const int* kmin, const int* kmax,
+                               const int* lim, const int* row_start, const int* kv_lo, const int* kv_hi,
                                int B, int S, int Sq, int q_off, int Hq, int Hkv, int D, long q_row_stride,
                                long k_row_stride, long v_row_stride, long o_row_stride, float scale,
                                long long spin_budget, void* stream) {
@@ -508,8 +504,8 @@ CTB_API int ctb_attn_fwd_range(const void* q, const void* k, const void* v, void
     return ctb::fail("attention: S, Sq and q_off must be multiples of 128 with q_off + Sq <= S");
   if (Hq % Hkv) return ctb::fail("attention: Hq must be a multiple of Hkv");
   ctb::attn::FwdCall c{};
-  c.q = q; c.k = k; c.v = v; c.o = o; c.lse = lse; c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi;
-  c.kmin = kmin; c.kmax = kmax; c.B = B; c.S = S; c.Sq = Sq; c.q_off = q_off; c.Hq = Hq; c.Hkv = Hkv;
+  c.q = q; c.k = k; c.v = v; c.o = o; c.lse = lse; c.seg = seg; c.lim = lim; c.row_start = row_start; c.kv_lo = kv_lo; c.kv_hi = kv_hi;
+  c.B = B; c.S = S; c.Sq = Sq; c.q_off = q_off; c.Hq = Hq; c.Hkv = Hkv;
   c.q_row_stride = q_row_stride; c.k_row_stride = k_row_stride; c.v_row_stride = v_row_stride;
   c.o_row_stride = o_row_stride; c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
   if (D == 128) return ctb::attn::launch_fwd<128>(c);
@@ -520,7 +516,7 @@ CTB_API int ctb_attn_fwd_range(const void* q, const void* k, const void* v, void
 // Block-sparse (MoBA) forward: same operands plus the routing described at SparseArgs.  `it_off`
 // has B * Hq * ceil(S / 256) + 1 entries in the order (query pair descending, batch, head) of the grid.
 CTB_API int ctb_attn_fwd_sparse(const void* q, const void* k, const void* v, void* o, float* lse, const int* seg,
-                                const int* lim, const int* kv_lo, const int* kv_hi, const int* kmin, const int* kmax,
+                                const int* lim, const int* row_start, const int* kv_lo, const int* kv_hi,
                                 const int* it_off, const int* it_cnt, int it_stride, const int* it_list,
                                 const unsigned* sel, const int* doc_start, int block, int words, int B, int S, int Hq,
                                 int Hkv, int D, long q_row_stride,
@@ -530,8 +526,8 @@ CTB_API int ctb_attn_fwd_sparse(const void* q, const void* k, const void* v, voi
   if (Hq % Hkv) return ctb::fail("attention: Hq must be a multiple of Hkv");
   if (block < 128) return ctb::fail("sparse attention: the routing block must hold at least 128 tokens");
   ctb::attn::FwdCall c{};
-  c.q = q; c.k = k; c.v = v; c.o = o; c.lse = lse; c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi;
-  c.kmin = kmin; c.kmax = kmax; c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
+  c.q = q; c.k = k; c.v = v; c.o = o; c.lse = lse; c.seg = seg; c.lim = lim; c.row_start = row_start; c.kv_lo = kv_lo; c.kv_hi = kv_hi;
+  c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
   c.q_row_stride = q_row_stride; c.k_row_stride = k_row_stride; c.v_row_stride = v_row_stride;
   c.o_row_stride = o_row_stride; c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
   c.sp.it_off = it_off; c.sp.it_cnt = it_cnt; c.sp.it_stride = it_stride; c.sp.it_list = it_list; c.sp.sel = sel;

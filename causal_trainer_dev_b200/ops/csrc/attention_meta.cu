@@ -11,6 +11,9 @@
 //                ends where the mask drops or the caller's label changes
 //   pos[i]       i - first token of the run
 //   lim[i]       last key token i may see: max(i, attention_end[i]) clipped to its run
+//   start[i], end[i]   first / last token of the run; first_q[i] first query that sees key i.  The
+//                keys visible to query i are the interval [start[i], lim[i]], the queries that see
+//                key j the interval [first_q[j], end[j]]: the flash kernels mask by interval
 //   kv_lo/kv_hi  [S/128] key range [lo, hi) needed by the query block     kmin/kmax   min / max seg of the key block
 //   q_lo/q_hi    [S/128] query range [lo, hi) that can see the key block
 //   seg_min64 / seg_max64 / lim_min64 / lim_max64   [S/64] per 64-token block
@@ -57,7 +60,7 @@ struct Args {
   int* seg;             // [B,S]
   int* pos;             // [B,S]
   int* lim;             // [B,S]
-  int* scratch;         // [B,4,S]: run start, run end, first query, scatter buffer
+  int* rows;            // [4,B,S]: run start, run end (inclusive), first query that sees the key, scatter scratch
   int *kv_lo, *kv_hi, *kmin, *kmax, *q_lo, *q_hi;           // [B,S/128]
   int *seg_min64, *seg_max64, *lim_min64, *lim_max64;       // [B,S/64]
   int S;
@@ -73,10 +76,11 @@ __global__ void __launch_bounds__(THREADS) attention_meta_kernel(const Args a) {
   int* seg = a.seg + static_cast<size_t>(row) * S;
   int* pos = a.pos + static_cast<size_t>(row) * S;
   int* lim = a.lim + static_cast<size_t>(row) * S;
-  int* run_start = a.scratch + static_cast<size_t>(row) * 4 * S;
-  int* run_end = run_start + S;
-  int* first_q = run_end + S;
-  int* first_at = first_q + S;
+  const size_t plane = static_cast<size_t>(gridDim.x) * S;
+  int* run_start = a.rows + static_cast<size_t>(row) * S;
+  int* run_end = run_start + plane;
+  int* first_q = run_end + plane;
+  int* first_at = first_q + plane;
 
   const int per = (S + THREADS - 1) / THREADS;
   const int lo = min(S, static_cast<int>(threadIdx.x) * per);
@@ -197,11 +201,12 @@ __global__ void __launch_bounds__(THREADS) attention_meta_kernel(const Args a) {
 }  // namespace meta
 }  // namespace ctb
 
-// All tensors int32.  `label` and `att_end` may be null.  `scratch` holds 4 * B * S ints.
+// All tensors int32.  `label` and `att_end` may be null.  `rows` is [4][B][S]: per token the first
+// and last token of its run, the first query that sees it as a key, and one plane of scratch.
 // `summaries128` is [6][B][S/128] (kv_lo, kv_hi, kmin, kmax, q_lo, q_hi) and `summaries64` is
 // [4][B][S/64] (seg_min, seg_max, lim_min, lim_max).
 CTB_API int ctb_attention_meta(const int* mask, const int* label, const int* att_end, int B, int S, int* seg, int* pos,
-                               int* lim, int* scratch, int* summaries128, int* summaries64, void* stream) {
+                               int* lim, int* rows, int* summaries128, int* summaries64, void* stream) {
   using namespace ctb;
   if (B <= 0 || S <= 0 || S % 128) return fail("attention_meta: S must be a positive multiple of 128");
   meta::Args a;
@@ -211,7 +216,7 @@ CTB_API int ctb_attention_meta(const int* mask, const int* label, const int* att
   a.seg = seg;
   a.pos = pos;
   a.lim = lim;
-  a.scratch = scratch;
+  a.rows = rows;
   const size_t n128 = static_cast<size_t>(B) * (S / 128), n64 = static_cast<size_t>(B) * (S / 64);
   a.kv_lo = summaries128;
   a.kv_hi = summaries128 + n128;

@@ -218,7 +218,7 @@ def moba_forward(q, k, v, meta: AttentionMeta, routing: MobaRouting, scale: floa
     r = routing
     code = _lib.lib().ctb_attn_fwd_sparse(
         _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(meta.seg), _lib.ptr(meta.lim),
-        _lib.ptr(meta.kv_lo), _lib.ptr(meta.kv_hi), _lib.ptr(meta.kmin), _lib.ptr(meta.kmax),
+        _lib.ptr(meta.start), _lib.ptr(meta.kv_lo), _lib.ptr(meta.kv_hi),
         _lib.ptr(r.fwd.off), _lib.ptr(r.fwd.count), r.fwd.stride, _lib.ptr(r.fwd.entries), _lib.ptr(r.sel),
         _lib.ptr(r.doc_start), r.block, r.words,
         b, s, hq, hkv, d, ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)), ctypes.c_long(_row_stride(v)),
@@ -243,8 +243,7 @@ def moba_backward(q, k, v, out, dout, lse, meta: AttentionMeta, routing: MobaRou
         code = L.ctb_attn_bwd_sparse(
             mode, _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
             _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(meta.seg), _lib.ptr(meta.lim), _lib.ptr(meta.kv_lo),
-            _lib.ptr(meta.kv_hi), _lib.ptr(meta.q_lo), _lib.ptr(meta.q_hi), _lib.ptr(meta.seg_min64),
-            _lib.ptr(meta.seg_max64), _lib.ptr(meta.lim_min64), _lib.ptr(meta.lim_max64),
+            _lib.ptr(meta.kv_hi), _lib.ptr(meta.q_lo), _lib.ptr(meta.q_hi), _lib.ptr(meta.start), _lib.ptr(meta.end), _lib.ptr(meta.first_q),
             _lib.ptr(wl.off), _lib.ptr(wl.count), wl.stride, _lib.ptr(wl.entries), _lib.ptr(r.sel), _lib.ptr(r.allsel),
             _lib.ptr(r.doc_start), r.block, r.words,
             b, s, hq, hkv, d,

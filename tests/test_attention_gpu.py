@@ -173,6 +173,9 @@ def test_metadata_kernel_matches_pytorch_formulation(cuda_lib, s, maskgit):
         assert meta.lim is None and want.lim is None
     for name in ("kv_lo", "kv_hi", "kmin", "kmax", "q_lo", "q_hi", "seg_min64", "seg_max64", "lim_min64", "lim_max64"):
         assert torch.equal(getattr(meta, name), getattr(want, name)), name
+    live = want_seg != 0                 # per-token intervals are only defined on real tokens
+    for name in ("start", "end", "first_q"):
+        assert torch.equal(getattr(meta, name)[live], getattr(want, name)[live]), name
     # canonical ids in, the same ids out
     again = A.build_attention_meta(seg, end_d)
     assert torch.equal(again.seg, seg) and torch.equal(again.kv_lo, want.kv_lo) and torch.equal(again.q_hi, want.q_hi)
