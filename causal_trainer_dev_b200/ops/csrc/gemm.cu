@@ -143,6 +143,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   const int num_n = (args.N + BN - 1) / BN;
   const int num_k = (args.K + BK - 1) / BK;
   const int total = num_m * num_n;
+  // Split-K: a work unit is (tile, K slice); every slice adds its partial product into C with a
+  // TMA reduce, so a problem with few output tiles still fills all SMs in whole waves.
+  const int splits = args.split_k > 1 ? args.split_k : 1;
+  const int k_per = (num_k + splits - 1) / splits;
+  const int units = total * splits;
   const int m_rot = args.m_rotate / TM < num_m ? args.m_rotate / TM : 0;   // given in 128-row units
   DeviceStatus* st = args.status;
 
@@ -221,7 +226,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
       int tile = -1;
       if (lane == 0) {
         if (mbar_wait(&tq_empty[tq], tq_phase ^ 1u, abort_flag, st, SITE_TILE_QUEUE, args.spin_budget)) {
-          tile = pending < total ? pending : -1;
+          tile = pending < units ? pending : -1;
           if (tile >= 0) pending = claim(pending);
           tile_ring[tq] = tile;
           mbar_arrive(&tq_full[tq]);
@@ -238,7 +243,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         ok = (tile == -1);
         break;
       }
-      const TileCoord tc = tile_coord<TM>(tile, num_m, num_n, args.n_rotate, m_rot);
+      const int kb0 = (tile / total) * k_per;
+      const int kb1 = min(num_k, kb0 + k_per);
+      const TileCoord tc = tile_coord<TM>(tile % total, num_m, num_n, args.n_rotate, m_rot);
       if (args.b_flags != nullptr && !b_all_seen) {
         // The elements of B this tile reads must have landed in this GPU's memory.  A
         // K-major B tile is rows [n0, n0+BN) of the weight; an MN-major B (dgrad) strides
@@ -275,7 +282,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         fence_proxy_async_all();
       }
       if (lane == 0) {
-        for (int kb = 0; kb < num_k; ++kb) {
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1u, abort_flag, st, SITE_PRODUCER_EMPTY, args.spin_budget)) {
             ok = false;
             break;
@@ -349,7 +356,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           tq_phase ^= 1u;
         }
         if (tile < 0) break;
-        for (int kb = 0; kb < num_k; ++kb) {
+        const int kb0 = (tile / total) * k_per;
+        const int kb1 = min(num_k, kb0 + k_per);
+        for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag, st, SITE_MMA_FULL, args.spin_budget)) {
             ok = false;
             break;
@@ -363,7 +372,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 #pragma unroll
             for (int h = 0; h < TM; ++h) {
               const uint32_t slot = TM == 1 ? next_slot : static_cast<uint32_t>(h);
-              if (kb == 0 && k == 0) {
+              if (kb == kb0 && k == 0) {
                 // the slot must have been drained by the epilogue of the tile that used it last
                 if (!mbar_wait(&tempty[slot], (uses[slot] & 1u) ^ 1u, abort_flag, st, SITE_MMA_TEMPTY,
                                args.spin_budget)) {
@@ -373,7 +382,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
                 tc_fence_after();
               }
               const uint64_t da = A_MN ? desc_mnmajor(sa + h * 16384, k, 8192) : desc_kmajor(sa + h * 16384, k);
-              umma_bf16(tmem_base + slot * BN, da, db, idesc, (kb | k) != 0 ? 1u : 0u);
+              umma_bf16(tmem_base + slot * BN, da, db, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
             }
             if (!ok) break;
           }
@@ -419,7 +428,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         tq_phase ^= 1u;
       }
       if (tile < 0) break;
-      const TileCoord tc = tile_coord<TM>(tile, num_m, num_n, args.n_rotate, m_rot);
+      const TileCoord tc = tile_coord<TM>(tile % total, num_m, num_n, args.n_rotate, m_rot);
       const uint32_t slot = TM == 1 ? next_slot : static_cast<uint32_t>(wg);
       const bool got = mbar_wait(&tfull[slot], uses[slot] & 1u, abort_flag, st, SITE_EPI_TFULL, args.spin_budget);
       if (named_bar_or(bar_vote, 128, !got)) break;
@@ -489,7 +498,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           fence_proxy_async_smem();
           named_bar_sync(bar_stage, 128);
           if (etid == 0 && m_sub < args.M) {
-            if (args.accumulate) tma_reduce_add_2d(&map_c, buf, col0, m_sub);
+            if (args.accumulate || splits > 1) tma_reduce_add_2d(&map_c, buf, col0, m_sub);
             else tma_store_2d(&map_c, buf, col0, m_sub);
             tma_commit_group();
           }
@@ -565,7 +574,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             fence_proxy_async_smem();
             named_bar_sync(bar_stage, 128);
             if (etid == 0 && m_sub < args.M) {
-              if (args.accumulate) tma_reduce_add_2d(&map_c, buf, col0, m_sub);
+              if (args.accumulate || splits > 1) tma_reduce_add_2d(&map_c, buf, col0, m_sub);
               else tma_store_2d(&map_c, buf, col0, m_sub);
               tma_commit_group();
             }
@@ -607,6 +616,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
 // Pairs of (next tile, CTAs finished) counters, zero between launches (the kernel re-arms the pair
 // it used).  Launches rotate through the pool so kernels that overlap on different streams never
 // share a pair.
+inline int& split_k_mode() {
+  static int mode = [] {
+    const char* e = std::getenv("CTB_GEMM_SPLITK");
+    return (e != nullptr && e[0] == '1') ? 1 : 0;
+  }();
+  return mode;
+}
+
 inline int* next_tile_counter() {
   constexpr int POOL = 256;
   static int* pool[64] = {};
@@ -719,10 +736,54 @@ int run_gemm(const GemmCall& c) {
   const int tiles2 = ((c.M + 2 * BM - 1) / (2 * BM)) * num_n;
   // (the push epilogue copies every block out with the epilogue threads themselves and keeps its
   // two staging blocks: it measured faster on the smaller tile)
-  const int tm = forced_tm ? forced_tm : ((tiles2 >= 2 * sm_count() && c.epi != EPI_PUSH) ? 2 : 1);
-  const int tiles = tm == 2 ? tiles2 : ((c.M + BM - 1) / BM) * num_n;
-  int grid = std::min(tiles, c.max_ctas > 0 ? c.max_ctas : sm_count());
+  int tm = forced_tm ? forced_tm : ((tiles2 >= 2 * sm_count() && c.epi != EPI_PUSH) ? 2 : 1);
+  int tiles = tm == 2 ? tiles2 : ((c.M + BM - 1) / BM) * num_n;
   cudaStream_t s = static_cast<cudaStream_t>(c.stream);
+  // Split-K for plain products whose tile count leaves the last wave of CTAs mostly empty (weight
+  // gradients: few output tiles, K = tokens).  Candidates are scored by the fraction of SM-waves
+  // that do work, with a small charge per extra slice (its prologue, epilogue and reduce traffic)
+  // and for the smaller tile.  Off by default: alone the weight-gradient shapes of an 8B model run
+  // 4-17 % faster with it, but inside a power-capped training step the extra reduce traffic costs
+  // more clock than the idle SMs of the last wave did (measured -2.5 % tokens/s).
+  // CTB_GEMM_SPLITK=1 or ctb_gemm_set_split_k(1) turns it on.
+  const bool split_enabled = gemm::split_k_mode() != 0;
+  a.split_k = 1;
+  if (split_enabled && c.epi == EPI_STORE && c.bias == nullptr && c.a_flags == nullptr && c.b_flags == nullptr &&
+      c.max_ctas <= 0 && c.K >= 4096) {
+    const int sms = sm_count();
+    const int num_k = (c.K + gemm::BK - 1) / gemm::BK;
+    const int tiles1 = ((c.M + BM - 1) / BM) * num_n;
+    double best = 0.0;
+    int best_tm = tm, best_s = 1;
+    for (int cand_tm = 1; cand_tm <= 2; ++cand_tm) {
+      if (forced_tm && cand_tm != forced_tm) continue;
+      const int t = cand_tm == 2 ? tiles2 : tiles1;
+      for (int sp = 1; sp <= 8; ++sp) {
+        if (num_k < 32 * sp) break;
+        if (cand_tm == 2 && t * sp < 2 * sms) continue;          // the large tile wants a few waves
+        const long u = static_cast<long>(t) * sp;
+        const long waves = (u + sms - 1) / sms;
+        double score = static_cast<double>(u) / static_cast<double>(waves * sms);
+        score *= (cand_tm == 2 ? 1.0 : 0.93) * (1.0 - 0.012 * (sp - 1));
+        if (score > best + 1e-9) {
+          best = score;
+          best_tm = cand_tm;
+          best_s = sp;
+        }
+      }
+    }
+    if (best_s > 1) {
+      tm = best_tm;
+      tiles = (tm == 2 ? tiles2 : tiles1) * best_s;
+      a.split_k = best_s;
+      if (!c.accumulate) {
+        const size_t es = c.out_f32 ? 4 : 2;
+        CTB_CUDA_OK(cudaMemset2DAsync(c.C, static_cast<size_t>(c.ldc) * es, 0, static_cast<size_t>(c.N) * es,
+                                      static_cast<size_t>(c.M), s));
+      }
+    }
+  }
+  int grid = std::min(tiles, c.max_ctas > 0 ? c.max_ctas : sm_count());
 #define CTB_DISPATCH_TM(TMV, AM, BMN)                                                       \
   switch (c.epi) {                                                                          \
     case EPI_STORE: return launch<TMV, AM, BMN, EPI_STORE>(ma, mb, mc, a, grid, s);         \
@@ -822,4 +883,12 @@ CTB_API int ctb_ce_dlogits(const void* hidden, const void* head, void* g, int ro
   c.epi = ctb::EPI_CE_DLOGITS; c.stream = stream;
   c.ce_targets = targets; c.ce_lse = lse; c.ce_coef = coef;
   return ctb::run_gemm(c);
+}
+
+// 0: never split K; 1: split K when it fills the last wave (see launch_gemm).  Returns the previous mode.
+CTB_API int ctb_gemm_set_split_k(int mode) {
+  int& m = ctb::gemm::split_k_mode();
+  const int before = m;
+  m = mode != 0 ? 1 : 0;
+  return before;
 }

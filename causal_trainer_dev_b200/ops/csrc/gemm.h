@@ -33,6 +33,7 @@ struct GemmArgs {
   int M, N, K;
   int out_f32;
   int accumulate;
+  int split_k;            // > 1: work units are (tile, K slice), every slice reduce-adds into C
   float alpha;
   const __nv_bfloat16* bias;
   DeviceStatus* status;

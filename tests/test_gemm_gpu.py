@@ -67,3 +67,35 @@ def test_lora_merge_matches_fp32_reference(cuda_lib):
         ref = (w.float() + (a.float() @ b.float()).t()).bfloat16()
         got = lora_merge(w, a, b)
         assert (got.float() - ref.float()).abs().max() <= 2 * ref.float().abs().max() * 2 ** -8
+
+
+@pytest.mark.parametrize("shape", [(512, 512, 8192), (4096, 1024, 16384), (640, 328, 4104)])
+def test_split_k_weight_gradient_shapes(cuda_lib, shape):
+    """Few output tiles and a long K (dy^T x): the K slices reduce-add into one output."""
+    from causal_trainer_dev_b200.ops import gemm as G
+
+    m, n, k = shape
+    torch.manual_seed(5)
+    before = cuda_lib.lib().ctb_gemm_set_split_k(1)
+    try:
+        _check_split_k(G, m, n, k)
+    finally:
+        cuda_lib.lib().ctb_gemm_set_split_k(before)
+    assert cuda_lib.device_status() == (0, 0, 0, 0)
+
+
+def _check_split_k(G, m, n, k):
+    dy = (torch.randn(k, m, device="cuda") * 0.5).bfloat16()       # [tokens, out]
+    x = (torch.randn(k, n, device="cuda") * 0.5).bfloat16()        # [tokens, in]
+    ref = dy.float().t() @ x.float()
+    out32 = torch.full((m, n), 7.0, device="cuda")                 # overwritten, not accumulated
+    G.gemm(dy, x, a_mn=True, b_mn=True, out=out32)
+    assert _rel(out32, ref) < 1e-4
+    G.gemm(dy, x, a_mn=True, b_mn=True, out=out32, accumulate=True)
+    assert _rel(out32, 2 * ref) < 1e-4
+    out16 = torch.full((m, n), 7.0, device="cuda").bfloat16()
+    G.gemm(dy, x, a_mn=True, b_mn=True, out=out16)
+    assert _rel(out16, ref) < 8e-3
+    # K-major operands take the same path
+    out = G.gemm(dy.t().contiguous(), x.t().contiguous(), out_dtype=torch.float32)
+    assert _rel(out, ref) < 1e-4
