@@ -230,10 +230,10 @@ def flash_attention_backward(
     s = k.shape[1]
     hkv = k.shape[2]
     scale = 1.0 / math.sqrt(d) if scale is None else scale
-    from .elementwise import attention_delta
+    from .elementwise import attention_backward_stats
 
     _row_stride(out), _row_stride(dout)
-    delta = attention_delta(out, dout)  # [B,Hq,Sq] fp32
+    neg_lse2, neg_delta = attention_backward_stats(out, dout, lse)  # [B,Hq,Sq] fp32
     dq = torch.empty((b, sq, hq, d), dtype=torch.bfloat16, device=q.device) if dq is None else dq
     dk = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dk is None else dk
     dv = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dv is None else dv
@@ -241,7 +241,7 @@ def flash_attention_backward(
     for mode in (0, 1):
         code = L.ctb_attn_bwd_range(
             mode, _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
-            _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(meta.seg), _lib.ptr(meta.lim), _lib.ptr(meta.kv_lo),
+            _lib.ptr(neg_lse2), _lib.ptr(neg_delta), _lib.ptr(meta.seg), _lib.ptr(meta.lim), _lib.ptr(meta.kv_lo),
             _lib.ptr(meta.kv_hi), _lib.ptr(meta.q_lo), _lib.ptr(meta.q_hi), _lib.ptr(meta.start), _lib.ptr(meta.end), _lib.ptr(meta.first_q),
             b, s, sq, q_offset, hq, hkv, d,
             ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)), ctypes.c_long(_row_stride(v)),

@@ -83,8 +83,8 @@ struct BwdArgs {
   const int* run_start;
   const int* run_end;
   const int* first_q;
-  const float* lse;
-  const float* delta;
+  const float* neg_lse2;    // [B,Hq,Sq]  -lse * log2(e)
+  const float* neg_delta;   // [B,Hq,Sq]  -sum_d O dO      (both from ctb_attn_bwd_stats)
   DeviceStatus* status;
   long long spin_budget;
   SparseArgs sp;
@@ -93,7 +93,7 @@ struct BwdArgs {
 struct BwdCall {
   const void* q; const void* k; const void* v; const void* dout;
   void* dq; void* dk; void* dv;
-  const float* lse; const float* delta;
+  const float* neg_lse2; const float* neg_delta;
   const int* seg; const int* lim; const int* kv_lo; const int* kv_hi; const int* q_lo; const int* q_hi;
   const int* run_start; const int* run_end; const int* first_q;
   int B, S, Hq, Hkv;

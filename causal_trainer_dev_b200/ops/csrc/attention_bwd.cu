@@ -3,7 +3,8 @@
 //   MODE_DKV  KV-tile-owned: a CTA owns 128 keys of one KV head and walks every query
 //             block (64 rows) of every query head of the GQA group that can see them.
 //                 S^T = K Q^T          dP^T = V dO^T            (tcgen05, TMEM)
-//                 P^T = exp2(S^T c - lse),  dS^T = P^T (dP^T - delta)   (registers)
+//                 P^T = exp2(S^T c - lse),  dS^T = P^T (dP^T - delta)   (registers; the per-query
+//                 statistics arrive negated and in log2 units, ready for packed fma / add)
 //                 dV += P^T dO         dK += dS^T Q             (tcgen05, TMEM accumulators)
 //             The reduction over the group's query heads happens in the TMEM accumulators.
 //   MODE_DQ   Q-tile-owned: a CTA owns 128 query rows of one query head and walks the
@@ -11,8 +12,9 @@
 //             dQ += dS K.
 //
 // Structure of both: resident operand pair X (K,V or Q,dO), streamed pair Y (Q,dO or K,V)
-// through a 3-stage TMA ring, two compute warpgroups that alternate Y blocks so the tensor
-// core works on block i+1 while block i is exponentiated.  P^T / dS tiles are written as
+// through a 3-stage TMA ring, four compute warpgroups that share every Y block (16 of its 64
+// columns each) over two alternating S / dP buffers, so the tensor core works on block i+1 and
+// on the accumulate MMAs of block i-1 while block i is exponentiated.  P^T / dS tiles are written as
 // bf16 into 128B-swizzled K-major shared tiles; the Y tiles are reused in place as
 // MN-major operands of the accumulate MMAs.
 //
@@ -20,6 +22,8 @@
 // (src/causal_trainer/kernels/efficient_attention.py:985-1173, 1270-1436); the psum that
 // follows the reference's dK/dV kernel is not needed on one GPU because the group is reduced
 // in TMEM.
+#include <type_traits>
+
 #include "attention.h"
 
 namespace ctb {
@@ -48,8 +52,8 @@ struct BwdSmem {
   static constexpr int OFF_Y = 2 * XT;        // stages of (Y1, Y2)
   static constexpr int OFF_T = OFF_Y + Y_STAGES * 2 * YT;  // per warpgroup: (P^T, dS)
   static constexpr int OFF_BAR = OFF_T + 2 * 2 * TT;
-  static constexpr int OFF_META = OFF_BAR + 256;           // per block buffer: lse*log2(e) and delta of 64 columns
-  static constexpr int BYTES = OFF_META + 1024 + 1024;
+  static constexpr int OFF_STAT = OFF_BAR + 256;   // per Y stage: 64 x -lse*log2(e), 64 x -delta of the block's queries (DKV)
+  static constexpr int BYTES = OFF_STAT + Y_STAGES * 512 + 1024;
 };
 
 template <int D, int MODE>
@@ -133,7 +137,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
     for (int u = 0; u < 2; ++u) {
       mbar_init(&s_full[u], 1);
-      mbar_init(&t_full[u], 256);
+      mbar_init(&t_full[u], 512);
       mbar_init(&t_done[u], 1);
     }
     mbar_init(acc_full, 1);
@@ -172,8 +176,14 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const int yh = DKV ? y_head(it) : hkv;
         const int y0 = y_block(it) * 64 - (DKV ? args.q_off : 0);   // streamed queries are stored locally
         if (!mbar_wait(&y_empty[stage], phase ^ 1u, abort_flag, st, SITE_B_PROD, budget)) break;
-        mbar_expect_tx(&y_full[stage], 2 * L::YT);
+        mbar_expect_tx(&y_full[stage], 2 * L::YT + (DKV ? 512 : 0));
         uint8_t* dst = smem + L::OFF_Y + stage * 2 * L::YT;
+        if (DKV) {
+          // the per-query statistics of the block travel with it (256 B each, 256 B aligned)
+          const size_t stat = (static_cast<size_t>(b) * args.Hq + yh) * args.Sq + y0;
+          tma_load_1d(smem + L::OFF_STAT + stage * 512, args.neg_lse2 + stat, 256, &y_full[stage]);
+          tma_load_1d(smem + L::OFF_STAT + stage * 512 + 256, args.neg_delta + stat, 256, &y_full[stage]);
+        }
 #pragma unroll
         for (int hf = 0; hf < HALVES; ++hf) {
           tma_load_4d(dst + hf * 8192, my1, &y_full[stage], hf * 64, yh, y0, b);
@@ -248,21 +258,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     }
   } else if (warp >= 4) {
     // ------------------------------ compute warpgroups ------------------------------
-    // Four compute warpgroups: block buffer u = wg & 1, and the two warpgroups of a buffer split
-    // its 64 columns (half = wg >> 1 takes columns [32 * half, 32 * half + 32)), so every
-    // scheduler has four compute warps to hide the TMEM and global load latencies with.
+    // Four compute warpgroups work on every block together: warpgroup wg takes columns
+    // [16 wg, 16 wg + 16) of the 64-column block, so one block costs a single short pass (one TMEM
+    // round trip, 16 exponentials per thread).  The S / dP buffers alternate from block to block:
+    // the tensor core fills buffer 1 - u and runs the accumulate MMAs of the previous block while
+    // buffer u is exponentiated.
     const int wg = (warp - 4) >> 2;
-    const int u = wg & 1;
-    const int half = wg >> 1;
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-    uint8_t* t_p = smem + L::OFF_T + u * 2 * L::TT;
-    uint8_t* t_ds = t_p + L::TT;
     // position in the whole sequence of this thread's row: a key (DKV) or a local query (DQ)
     const int xi = x0 + r + (DKV ? 0 : args.q_off);
     const int xi_local = x0 + r;
-    const float LOG2E = 1.4426950408889634f;
     const int row_seg = args.seg[b * args.S + xi];
     // interval of visible columns (whole-sequence positions): see the mask below
     int row_a, row_b;
@@ -276,164 +283,156 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int row_start = sparse ? args.sp.doc_start[b * args.S + xi] : 0;
     // DKV: the document-relative block of this key is the bit every query column is tested for
     const int row_blk = (sparse && DKV) ? (xi - row_start) / args.sp.block : 0;
-    float row_lse2 = 0.f, row_delta = 0.f;
+    float neg_lse2 = 0.f, neg_delta = 0.f;      // DQ: per-row statistics (stored negated, lse in log2 units)
     if (!DKV) {
-      row_lse2 = args.lse[(static_cast<size_t>(b) * args.Hq + head) * args.Sq + xi_local] * LOG2E;
-      row_delta = args.delta[(static_cast<size_t>(b) * args.Hq + head) * args.Sq + xi_local];
+      neg_lse2 = args.neg_lse2[(static_cast<size_t>(b) * args.Hq + head) * args.Sq + xi_local];
+      neg_delta = args.neg_delta[(static_cast<size_t>(b) * args.Hq + head) * args.Sq + xi_local];
     }
     bool ok = true;
-    uint32_t sph = 0, dph = 0;
-    int uses = 0;
+    uint32_t sph = 0, dph = 0;             // bit u: phase parity of s_full[u] / t_done[u]
     const uint64_t scale2 = pack_f32x2(args.scale_log2, args.scale_log2);
-    float* meta_l = reinterpret_cast<float*>(smem + L::OFF_META) + u * 128;
-    float* meta_d = meta_l + 64;
-    for (int it = u; it < n_iter; it += 2, ++uses) {
-      const int yb = y_block(it);
-      const int y0 = yb * 64;
-      const int hq = y_head(it);
-      // DKV: the per-query statistics of the 64 columns are fetched while S is still being
-      // computed (one value per thread of the first warpgroup of the pair) and shared below.
-      float meta_v = 0.f;
-      if (DKV && half == 0) {
-        const size_t base = (static_cast<size_t>(b) * args.Hq + hq) * args.Sq + (y0 - args.q_off);
-        meta_v = (r < 64) ? -__ldg(args.lse + base + r) * LOG2E : -__ldg(args.delta + base + r - 64);
-      }
-      bool good = mbar_wait(&s_full[u], sph, abort_flag, st, SITE_B_CW_S, budget);
-      sph ^= 1u;
-      if (good && uses > 0) {
-        good = mbar_wait(&t_done[u], dph, abort_flag, st, SITE_B_CW_T, budget);
-        dph ^= 1u;
-      }
-      tc_fence_after();
-      if (DKV) {
-        // every thread of the pair reaches this barrier, also one whose wait gave up: the
-        // verdict is shared so that nobody is left waiting at it
-        if (good && half == 0) meta_l[r] = meta_v;   // r < 64: lse, r >= 64: delta (meta_d = meta_l + 64)
-        if (named_bar_or(6 + u, 256, !good)) {
-          ok = false;
-          break;
+    // dense walk: (block, head) advance without a division per iteration
+    int walk_block = 0, walk_head = 0;
+    uint32_t ystage = 0, yphase = 0;        // stage of the Y ring that holds block `it` (and its statistics)
+    for (int it = 0; it < n_iter; ++it) {
+      const int u = it & 1;
+      uint8_t* t_p = smem + L::OFF_T + u * 2 * L::TT;
+      uint8_t* t_ds = t_p + L::TT;
+      int yb, hq;
+      if (sparse) {
+        const int entry = __ldg(it_list + it);
+        yb = entry & 0xffffff;
+        hq = DKV ? hkv * group + (entry >> 24) : head;
+      } else {
+        yb = y_lo64 + walk_block;
+        hq = DKV ? hkv * group + walk_head : head;
+        if (++walk_block == y_n64) {
+          walk_block = 0;
+          ++walk_head;
         }
-      } else if (!good) {
-        ok = false;
-        break;
       }
-      // ---- visibility of this row against its 32 columns, as a bit mask.  The keys a query sees
+      const int y0 = yb * 64;
+      const int base = y0 + 16 * wg;            // first column of this thread
+      // ---- visibility of this row against its 16 columns, as a bit mask.  The keys a query sees
       // and the queries that see a key are both contiguous intervals (runs are contiguous):
       //   DQ   row = query xi,  columns = keys     [start[xi], lim[xi]]
       //   DKV  row = key xi,    columns = queries  [first_q[xi], end[xi]]
-      const int base = y0 + 32 * half;
-      unsigned vis32 = (row_seg == 0) ? 0u : (bits_from(row_a - base) & bits_upto(row_b - base));
-      const unsigned* col_sel = nullptr;
-      if (sparse && vis32 != 0u) {
+      unsigned vis = (row_seg == 0) ? 0u : (bits_from(row_a - base) & bits_upto(row_b - base) & 0xffffu);
+      if (sparse && vis != 0u) {
         if (DKV) {
           if ((row_blk >> 5) >= args.sp.words) {
-            vis32 = 0u;
+            vis = 0u;
           } else {
             // when every query of the block selected this key's block the selection adds nothing
-            // to the interval test and the row keeps its fast paths
             const unsigned aw = __ldg(args.sp.allsel + ((static_cast<size_t>(b) * args.Hq + hq) * nb64 + yb) * args.sp.words +
                                       (row_blk >> 5));
-            if (!((aw >> (row_blk & 31)) & 1u))
-              col_sel = args.sp.sel + ((static_cast<size_t>(b) * args.Hq + hq) * args.S + y0) * args.sp.words +
-                        (row_blk >> 5);
+            if (!((aw >> (row_blk & 31)) & 1u)) {
+              // per-query selection bit of this key's block, for the 16 columns of this thread
+              const unsigned* col_sel = args.sp.sel + ((static_cast<size_t>(b) * args.Hq + hq) * args.S + base) * args.sp.words +
+                                        (row_blk >> 5);
+              const int bit = row_blk & 31;
+              unsigned selbits = 0u;
+#pragma unroll 4
+              for (int e = 0; e < 16; ++e)
+                selbits |= ((__ldg(col_sel + static_cast<size_t>(e) * args.sp.words) >> bit) & 1u) << e;
+              vis &= selbits;
+            }
           }
         } else {
           const SparseRow sr = sparse_row(args.sp, b, head, args.Hq, args.S, xi, row_start, y0, 64);
           const unsigned above = bits_from(sr.bound - base);               // keys >= bound
-          vis32 &= (sr.v0 ? ~above : 0u) | (sr.v1 ? above : 0u);
+          vis &= (sr.v0 ? ~above : 0u) | (sr.v1 ? above : 0u);
         }
       }
-      if (col_sel != nullptr) {
-        // per-query selection bit of this key's block, for the 32 columns of this thread
-        const int bit = row_blk & 31;
-        unsigned selbits = 0u;
-#pragma unroll 4
-        for (int e = 0; e < 32; ++e)
-          selbits |= ((__ldg(col_sel + static_cast<size_t>(32 * half + e) * args.sp.words) >> bit) & 1u) << e;
-        vis32 &= selbits;
+      const bool all = vis == 0xffffu;
+      // DKV: per-query statistics of this thread's 16 columns, staged beside the block by the producer
+      const float4* lse_col = reinterpret_cast<const float4*>(smem + L::OFF_STAT + ystage * 512) + 4 * wg;
+      const float4* delta_col = lse_col + 16;
+      if (!mbar_wait(&s_full[u], (sph >> u) & 1u, abort_flag, st, SITE_B_CW_S, budget)) {
+        ok = false;
+        break;
       }
-      const bool none = vis32 == 0u;
-      const bool all = vis32 == 0xffffffffu;
-#pragma unroll 1
-      for (int sub = 0; sub < 2; ++sub) {
-        const int c = half;
-        uint32_t rs[16], rd[16];
-        tmem_ld16(tmem_s[u] + lane_off + c * 32 + sub * 16, rs);
-        tmem_ld16(tmem_dp[u] + lane_off + c * 32 + sub * 16, rd);
-        tmem_ld_wait();
-        // eight columns at a time: probabilities and dS are packed and stored as soon as they
-        // exist, so only the two raw 16-column TMEM chunks stay live in registers
+      sph ^= 1u << u;
+      if (DKV) {
+        // S was computed from this stage, so its bytes have landed; the wait makes the statistics
+        // written by the bulk copy visible to this thread
+        if (!mbar_wait(&y_full[ystage], yphase, abort_flag, st, SITE_B_CW_S, budget)) {
+          ok = false;
+          break;
+        }
+      }
+      if (it >= 2) {
+        // the accumulate MMAs of block it - 2 read the P^T / dS tiles this block overwrites
+        if (!mbar_wait(&t_done[u], (dph >> u) & 1u, abort_flag, st, SITE_B_CW_T, budget)) {
+          ok = false;
+          break;
+        }
+        dph ^= 1u << u;
+      }
+      tc_fence_after();
+      uint32_t rs[16], rd[16];
+      tmem_ld16(tmem_s[u] + lane_off + 16 * wg, rs);
+      tmem_ld16(tmem_dp[u] + lane_off + 16 * wg, rd);
+      tmem_ld_wait();
+      // Eight columns at a time: probabilities and dS are packed and stored as soon as they exist.
+      // MASKED = false is the path of a warp whose rows all see all 16 columns: no selects.
+      auto compute16 = [&](auto masked_tag) {
+        constexpr bool MASKED = decltype(masked_tag)::value;
 #pragma unroll
         for (int gg = 0; gg < 2; ++gg) {
-          const int g = sub * 2 + gg;
-          float p[8], ds[8];
-          if (none) {
+          uint32_t pw[4], dw[4];
 #pragma unroll
-            for (int e = 0; e < 8; ++e) {
-              p[e] = 0.f;
-              ds[e] = 0.f;
+          for (int h4 = 0; h4 < 2; ++h4) {
+            const int e4 = gg * 2 + h4;                  // group of four of the 16 columns
+            uint64_t l2[2], dl[2];                       // negated statistics, two columns per word
+            if (DKV) {
+              const float4 lv = lse_col[e4];
+              const float4 dv = delta_col[e4];
+              l2[0] = pack_f32x2(lv.x, lv.y);
+              l2[1] = pack_f32x2(lv.z, lv.w);
+              dl[0] = pack_f32x2(dv.x, dv.y);
+              dl[1] = pack_f32x2(dv.z, dv.w);
+            } else {
+              l2[0] = l2[1] = pack_f32x2(neg_lse2, neg_lse2);
+              dl[0] = dl[1] = pack_f32x2(neg_delta, neg_delta);
             }
-          } else {
+            // p = exp2(s * scale - lse), dS = p * (dP - delta): two columns per packed instruction
 #pragma unroll
-            for (int h4 = 0; h4 < 2; ++h4) {
-              const int e4 = g * 2 + h4;
-              float l2[4], dl[4];
-              if (DKV) {
-                const float4 lv = *(reinterpret_cast<const float4*>(meta_l) + c * 8 + e4);
-                const float4 dv = *(reinterpret_cast<const float4*>(meta_d) + c * 8 + e4);
-                l2[0] = lv.x; l2[1] = lv.y; l2[2] = lv.z; l2[3] = lv.w;
-                dl[0] = dv.x; dl[1] = dv.y; dl[2] = dv.z; dl[3] = dv.w;
-              } else {
-                l2[0] = l2[1] = l2[2] = l2[3] = -row_lse2;
-                dl[0] = dl[1] = dl[2] = dl[3] = -row_delta;
+            for (int pr = 0; pr < 2; ++pr) {
+              const int e = e4 * 4 + pr * 2;
+              const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), scale2, l2[pr]);
+              float xa, xb;
+              unpack_f32x2(x2, xa, xb);
+              float pa = fast_exp2(xa), pb = fast_exp2(xb);
+              if (MASKED) {
+                if (!((vis >> e) & 1u)) pa = 0.f;
+                if (!((vis >> (e + 1)) & 1u)) pb = 0.f;
               }
-              bool vis[4] = {true, true, true, true};
-              if (!all) {
-                const unsigned nib = vis32 >> (e4 * 4);      // e4 counts groups of four of the 32 columns
-                vis[0] = nib & 1u;
-                vis[1] = nib & 2u;
-                vis[2] = nib & 4u;
-                vis[3] = nib & 8u;
-              }
-              // p = exp2(s * scale - lse), dS = p * (dP - delta): two columns per packed instruction
-              // (l2 / dl hold the negated statistics)
-#pragma unroll
-              for (int pr = 0; pr < 2; ++pr) {
-                const int e = gg * 8 + h4 * 4 + pr * 2;
-                const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(rs[e]), __uint_as_float(rs[e + 1])), scale2,
-                                              pack_f32x2(l2[pr * 2], l2[pr * 2 + 1]));
-                float xa, xb;
-                unpack_f32x2(x2, xa, xb);
-                const float pa = vis[pr * 2] ? fast_exp2(xa) : 0.f;
-                const float pb = vis[pr * 2 + 1] ? fast_exp2(xb) : 0.f;
-                const uint64_t d2 = add_f32x2(pack_f32x2(__uint_as_float(rd[e]), __uint_as_float(rd[e + 1])),
-                                              pack_f32x2(dl[pr * 2], dl[pr * 2 + 1]));
-                const uint64_t ds2 = mul_f32x2(pack_f32x2(pa, pb), d2);
-                p[h4 * 4 + pr * 2] = pa;
-                p[h4 * 4 + pr * 2 + 1] = pb;
-                unpack_f32x2(ds2, ds[h4 * 4 + pr * 2], ds[h4 * 4 + pr * 2 + 1]);
-              }
+              const uint64_t d2 = add_f32x2(pack_f32x2(__uint_as_float(rd[e]), __uint_as_float(rd[e + 1])), dl[pr]);
+              const uint64_t ds2 = mul_f32x2(pack_f32x2(pa, pb), d2);
+              float da, db;
+              unpack_f32x2(ds2, da, db);
+              pw[h4 * 2 + pr] = pack_bf16(pa, pb);
+              dw[h4 * 2 + pr] = pack_bf16(da, db);
             }
           }
-          uint4 v;
-          if (DKV) {
-            v.x = pack_bf16(p[0], p[1]);
-            v.y = pack_bf16(p[2], p[3]);
-            v.z = pack_bf16(p[4], p[5]);
-            v.w = pack_bf16(p[6], p[7]);
-            *reinterpret_cast<uint4*>(t_p + sw128_offset(r, c * 4 + g)) = v;
-          }
-          v.x = pack_bf16(ds[0], ds[1]);
-          v.y = pack_bf16(ds[2], ds[3]);
-          v.z = pack_bf16(ds[4], ds[5]);
-          v.w = pack_bf16(ds[6], ds[7]);
-          *reinterpret_cast<uint4*>(t_ds + sw128_offset(r, c * 4 + g)) = v;
+          if (DKV) *reinterpret_cast<uint4*>(t_p + sw128_offset(r, wg * 2 + gg)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
+          *reinterpret_cast<uint4*>(t_ds + sw128_offset(r, wg * 2 + gg)) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
         }
-      }
+      };
+      if (__all_sync(0xffffffffu, all)) compute16(std::false_type{});
+      else compute16(std::true_type{});
       fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&t_full[u]);
+      if (++ystage == Y_STAGES) {
+        ystage = 0;
+        yphase ^= 1u;
+      }
     }
+    // the epilogue pairs the warpgroups: pair u converts accumulator u, each warpgroup half of it
+    const int u = wg & 1;
+    const int half = wg >> 1;
     // ---- epilogue: accumulators -> bf16 -> staging -> TMA store ----
     if (ok && n_iter > 0) {
       ok = mbar_wait(acc_full, 0, abort_flag, st, SITE_B_CW_ACC, budget);
@@ -517,7 +516,7 @@ int launch_bwd(const BwdCall& c) {
   a.scale_log2 = c.scale * 1.4426950408889634f;
   a.seg = c.seg; a.lim = c.lim; a.kv_lo = c.kv_lo; a.kv_hi = c.kv_hi; a.q_lo = c.q_lo; a.q_hi = c.q_hi;
   a.run_start = c.run_start; a.run_end = c.run_end; a.first_q = c.first_q;
-  a.lse = c.lse; a.delta = c.delta;
+  a.neg_lse2 = c.neg_lse2; a.neg_delta = c.neg_delta;
   a.sp = c.sp;
   a.status = device_status();
   a.spin_budget = c.spin_budget > 0 ? c.spin_budget : CTB_SPIN_BUDGET;
@@ -539,16 +538,16 @@ int launch_bwd(const BwdCall& c) {
 }  // namespace ctb
 
 // mode 0: dK/dV kernel, mode 1: dQ kernel.  All tensors are [B,S,H,D] views with a row
-// stride; lse and delta are [B,Hq,S] fp32.
+// stride; neg_lse2 = -lse * log2(e) and neg_delta = -sum_d O dO are [B,Hq,S] fp32 (ctb_attn_bwd_stats).
 CTB_API int ctb_attn_bwd(int mode, const void* q, const void* k, const void* v, const void* dout, void* dq, void* dk,
-                         void* dv, const float* lse, const float* delta, const int* seg, const int* lim,
+                         void* dv, const float* neg_lse2, const float* neg_delta, const int* seg, const int* lim,
                          const int* kv_lo, const int* kv_hi, const int* q_lo, const int* q_hi, const int* run_start, const int* run_end, const int* first_q, int B, int S, int Hq,
                          int Hkv, int D, long q_rs, long k_rs, long v_rs, long do_rs, long dq_rs, long dk_rs,
                          long dv_rs, float scale, long long spin_budget, void* stream) {
   if (S % 128) return ctb::fail("attention: sequence length must be a multiple of 128");
   if (Hq % Hkv) return ctb::fail("attention: Hq must be a multiple of Hkv");
   ctb::attn::BwdCall c{};
-  c.q = q; c.k = k; c.v = v; c.dout = dout; c.dq = dq; c.dk = dk; c.dv = dv; c.lse = lse; c.delta = delta;
+  c.q = q; c.k = k; c.v = v; c.dout = dout; c.dq = dq; c.dk = dk; c.dv = dv; c.neg_lse2 = neg_lse2; c.neg_delta = neg_delta;
   c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi; c.q_lo = q_lo; c.q_hi = q_hi;
   c.run_start = run_start; c.run_end = run_end; c.first_q = first_q;
   c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;
@@ -561,10 +560,10 @@ CTB_API int ctb_attn_bwd(int mode, const void* q, const void* k, const void* v, 
   return ctb::fail("attention: head_dim must be 64 or 128");
 }
 
-// Sequence-parallel backward: q / dout / dq, lse and delta hold the Sq queries [q_off, q_off + Sq)
+// Sequence-parallel backward: q / dout / dq, neg_lse2 and neg_delta hold the Sq queries [q_off, q_off + Sq)
 // of every row; k / v / dk / dv cover all S keys (dk / dv are this rank's partial sums).
 CTB_API int ctb_attn_bwd_range(int mode, const void* q, const void* k, const void* v, const void* dout, void* dq,
-                               void* dk, void* dv, const float* lse, const float* delta, const int* seg,
+                               void* dk, void* dv, const float* neg_lse2, const float* neg_delta, const int* seg,
                                const int* lim, const int* kv_lo, const int* kv_hi, const int* q_lo, const int* q_hi,
                                const int* run_start, const int* run_end, const int* first_q, int B, int S, int Sq, int q_off, int Hq, int Hkv, int D,
                                long q_rs, long k_rs, long v_rs, long do_rs, long dq_rs, long dk_rs, long dv_rs,
@@ -573,7 +572,7 @@ CTB_API int ctb_attn_bwd_range(int mode, const void* q, const void* k, const voi
     return ctb::fail("attention: S, Sq and q_off must be multiples of 128 with q_off + Sq <= S");
   if (Hq % Hkv) return ctb::fail("attention: Hq must be a multiple of Hkv");
   ctb::attn::BwdCall c{};
-  c.q = q; c.k = k; c.v = v; c.dout = dout; c.dq = dq; c.dk = dk; c.dv = dv; c.lse = lse; c.delta = delta;
+  c.q = q; c.k = k; c.v = v; c.dout = dout; c.dq = dq; c.dk = dk; c.dv = dv; c.neg_lse2 = neg_lse2; c.neg_delta = neg_delta;
   c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi; c.q_lo = q_lo; c.q_hi = q_hi;
   c.run_start = run_start; c.run_end = run_end; c.first_q = first_q;
   c.B = B; c.S = S; c.Sq = Sq; c.q_off = q_off; c.Hq = Hq; c.Hkv = Hkv;
@@ -591,7 +590,7 @@ CTB_API int ctb_attn_bwd_range(int mode, const void* q, const void* k, const voi
 // `it_list` holds 64-row block indices, with the head's index inside its GQA group in bits 24+
 // for mode 0.
 CTB_API int ctb_attn_bwd_sparse(int mode, const void* q, const void* k, const void* v, const void* dout, void* dq,
-                                void* dk, void* dv, const float* lse, const float* delta, const int* seg,
+                                void* dk, void* dv, const float* neg_lse2, const float* neg_delta, const int* seg,
                                 const int* lim, const int* kv_lo, const int* kv_hi, const int* q_lo, const int* q_hi,
                                 const int* run_start, const int* run_end, const int* first_q, const int* it_off, const int* it_cnt, int it_stride,
                                 const int* it_list, const unsigned* sel, const unsigned* allsel, const int* doc_start,
@@ -602,7 +601,7 @@ CTB_API int ctb_attn_bwd_sparse(int mode, const void* q, const void* k, const vo
   if (Hq % Hkv) return ctb::fail("attention: Hq must be a multiple of Hkv");
   if (block < 128) return ctb::fail("sparse attention: the routing block must hold at least 128 tokens");
   ctb::attn::BwdCall c{};
-  c.q = q; c.k = k; c.v = v; c.dout = dout; c.dq = dq; c.dk = dk; c.dv = dv; c.lse = lse; c.delta = delta;
+  c.q = q; c.k = k; c.v = v; c.dout = dout; c.dq = dq; c.dk = dk; c.dv = dv; c.neg_lse2 = neg_lse2; c.neg_delta = neg_delta;
   c.seg = seg; c.lim = lim; c.kv_lo = kv_lo; c.kv_hi = kv_hi; c.q_lo = q_lo; c.q_hi = q_hi;
   c.run_start = run_start; c.run_end = run_end; c.first_q = first_q;
   c.B = B; c.S = S; c.Hq = Hq; c.Hkv = Hkv;

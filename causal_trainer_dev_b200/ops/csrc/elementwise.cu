@@ -338,6 +338,37 @@ __global__ void attn_delta_kernel(const __nv_bfloat16* __restrict__ o, const __n
 }
 
 // ------------------------------------------------------------------------------------------
+// Per-query statistics of the attention backward, in the form its kernels consume:
+//   neg_delta[b][h][s] = -sum_d O dO        neg_lse2[b][h][s] = -lse[b][h][s] * log2(e)
+// (one warp per (token, head)), so the inner loops use packed fma / add without a negation.
+// ------------------------------------------------------------------------------------------
+__global__ void attn_bwd_stats_kernel(const __nv_bfloat16* __restrict__ o, const __nv_bfloat16* __restrict__ dout,
+                                      const float* __restrict__ lse, float* __restrict__ neg_lse2,
+                                      float* __restrict__ neg_delta, int B, int S, int H, int D, long o_rs, long do_rs) {
+  const long warp_id = (blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long total = static_cast<long>(B) * S * H;
+  if (warp_id >= total) return;
+  const int h = static_cast<int>(warp_id % H);
+  const long t = warp_id / H;
+  const __nv_bfloat16* op = o + t * o_rs + static_cast<long>(h) * D;
+  const __nv_bfloat16* dp = dout + t * do_rs + static_cast<long>(h) * D;
+  float acc = 0.f;
+  for (int c = lane * 2; c < D; c += 64) {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(op + c));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(dp + c));
+    acc += a.x * b.x + a.y * b.y;
+  }
+  acc = warp_sum(acc);
+  if (lane == 0) {
+    const long b_idx = t / S, s_idx = t % S;
+    const long i = (b_idx * H + h) * S + s_idx;
+    neg_delta[i] = -acc;
+    neg_lse2[i] = -lse[i] * 1.4426950408889634f;
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // Cut-CE combine: merges per-slab (max, sumexp) into lse[row], emits the weighted NLL per
 // row, the backward coefficient coef[row] = weight * grad_scale, and block partial sums of
 // (nll, weight) which the host-side wrapper adds up (fp32, fixed order: deterministic).
@@ -613,6 +644,19 @@ CTB_API int ctb_attn_delta(const void* o, const void* dout, float* delta, int B,
   const long blocks = (warps * 32 + threads - 1) / threads;
   attn_delta_kernel<<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(
       static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), delta, B, S, H, D, o_rs, do_rs);
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// o, dout: [B,S,H,D] bf16 views (row strides in elements); lse, neg_lse2, neg_delta: [B,H,S] fp32.
+CTB_API int ctb_attn_bwd_stats(const void* o, const void* dout, const float* lse, float* neg_lse2, float* neg_delta,
+                               int B, int S, int H, int D, long o_rs, long do_rs, void* stream) {
+  const long warps = static_cast<long>(B) * S * H;
+  const int threads = 256;
+  const long blocks = (warps * 32 + threads - 1) / threads;
+  attn_bwd_stats_kernel<<<static_cast<unsigned>(blocks), threads, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(o), static_cast<const __nv_bfloat16*>(dout), lse, neg_lse2, neg_delta, B, S, H,
+      D, o_rs, do_rs);
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -183,6 +183,19 @@ def attention_delta(o: torch.Tensor, dout: torch.Tensor) -> torch.Tensor:
     return delta
 
 
+def attention_backward_stats(o: torch.Tensor, dout: torch.Tensor, lse: torch.Tensor) -> tuple[torch.Tensor, torch.Tensor]:
+    """``(-lse * log2(e), -sum_d O*dO)``, both [B,H,S] fp32: the per-query statistics in the form the
+    flash backward kernels consume (packed fma / add, no negation in their inner loops)."""
+    b, s, h, d = o.shape
+    neg_lse2 = torch.empty((b, h, s), dtype=torch.float32, device=o.device)
+    neg_delta = torch.empty_like(neg_lse2)
+    code = _lib.lib().ctb_attn_bwd_stats(_lib.ptr(o), _lib.ptr(dout), _lib.ptr(lse), _lib.ptr(neg_lse2),
+                                         _lib.ptr(neg_delta), b, s, h, d, _l(o.stride(1)), _l(dout.stride(1)),
+                                         _lib.stream_ptr())
+    _lib.check(code, "ctb_attn_bwd_stats")
+    return neg_lse2, neg_delta
+
+
 # ------------------------------------------------------------------------------ optimizer pieces
 def sum_of_squares(x: torch.Tensor, round_bf16: bool = False) -> torch.Tensor:
     """fp32 scalar tensor on the device (no host sync).

@@ -28,7 +28,7 @@ import torch
 
 from . import lib as _lib
 from .attention import AttentionMeta, _row_stride
-from .elementwise import attention_delta
+from .elementwise import attention_backward_stats
 
 
 @dataclass
@@ -233,7 +233,7 @@ def moba_backward(q, k, v, out, dout, lse, meta: AttentionMeta, routing: MobaRou
     b, s, hq, d = q.shape
     hkv = k.shape[2]
     scale = 1.0 / math.sqrt(d) if scale is None else scale
-    delta = attention_delta(out, dout)
+    neg_lse2, neg_delta = attention_backward_stats(out, dout, lse)
     dq = torch.empty((b, s, hq, d), dtype=torch.bfloat16, device=q.device) if dq is None else dq
     dk = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dk is None else dk
     dv = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dv is None else dv
@@ -242,7 +242,7 @@ def moba_backward(q, k, v, out, dout, lse, meta: AttentionMeta, routing: MobaRou
     for mode, wl in ((0, r.dkv), (1, r.dq)):
         code = L.ctb_attn_bwd_sparse(
             mode, _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dout), _lib.ptr(dq), _lib.ptr(dk), _lib.ptr(dv),
-            _lib.ptr(lse), _lib.ptr(delta), _lib.ptr(meta.seg), _lib.ptr(meta.lim), _lib.ptr(meta.kv_lo),
+            _lib.ptr(neg_lse2), _lib.ptr(neg_delta), _lib.ptr(meta.seg), _lib.ptr(meta.lim), _lib.ptr(meta.kv_lo),
             _lib.ptr(meta.kv_hi), _lib.ptr(meta.q_lo), _lib.ptr(meta.q_hi), _lib.ptr(meta.start), _lib.ptr(meta.end), _lib.ptr(meta.first_q),
             _lib.ptr(wl.off), _lib.ptr(wl.count), wl.stride, _lib.ptr(wl.entries), _lib.ptr(r.sel), _lib.ptr(r.allsel),
             _lib.ptr(r.doc_start), r.block, r.words,
