@@ -10,10 +10,11 @@
 //   warp 1      TMEM allocation + single-thread tcgen05.mma issue   (warps 2-3 idle)
 //   warps 4-7   softmax of tile 0 (one query row per thread, TMEM lane = row)
 //   warps 8-11  softmax of tile 1
-// The softmax reads each score row from TMEM twice (maximum, then exponentials) instead of
-// holding 128 scores in registers.
-// S (fp32) and O (fp32) live in TMEM.  P is written as bf16 into a 128B-swizzled K-major
-// shared tile and consumed by the second MMA; V is consumed in place as an MN-major operand.
+// The softmax holds a whole score row (128 fp32) in registers: one TMEM round trip per tile.
+// S (fp32) and O (fp32) live in TMEM.  P is written back into TMEM as bf16 pairs over the first
+// half of its score row and is the TMEM A operand of the second MMA, so it never crosses shared
+// memory (the operand fetches of the two MMAs alone come close to the 128 B/clk of the SM); V is
+// consumed in place as an MN-major operand.
 // The running maximum is only raised when it grows by more than 2^8 (the O rescale in TMEM
 // is rare), the final O / l and LSE are written by the softmax warps.
 // KV blocks outside [kv_lo, kv_hi) of a query block are never visited (block skipping from
@@ -27,7 +28,7 @@ namespace ctb {
 namespace attn {
 
 constexpr int FWD_THREADS = 384;
-constexpr int KV_SLOTS = 3;
+constexpr int KV_SLOTS = 5;
 
 enum : unsigned {
   SITE_F_PROD = 0x0201,
@@ -42,11 +43,9 @@ template <int D>
 struct FwdSmem {
   static constexpr int HALVES = D / 64;
   static constexpr int QT = HALVES * 16384;        // one 128-row Q / K / V tile
-  static constexpr int PT = 2 * 16384;             // P tile: 128 rows x 128 keys bf16
-  static constexpr int OFF_Q = 0;
+  static constexpr int OFF_Q = 0;                  // two Q tiles; each doubles as the staging tile of its O
   static constexpr int OFF_KV = 2 * QT;
-  static constexpr int OFF_P = OFF_KV + KV_SLOTS * QT;
-  static constexpr int OFF_BAR = OFF_P + 2 * PT;
+  static constexpr int OFF_BAR = OFF_KV + KV_SLOTS * QT;
   static constexpr int BYTES = OFF_BAR + 256 + 1024;
 };
 
@@ -146,6 +145,9 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const uint32_t tmem_o[2] = {tmem_base + 256, tmem_base + 256 + D};
 
   if (warp < 4) {
+  // the service warpgroup hands most of its registers to the two softmax warpgroups, which hold a
+  // whole 128-column score row per thread
+  asm volatile("setmaxnreg.dec.sync.aligned.u32 72;" ::: "memory");
   if (warp == 0) {
     // ------------------------------ producer ------------------------------
     if (lane == 0 && nmax > 0) {
@@ -233,12 +235,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           }
           pph[t] ^= 1u;
           tc_fence_after();
-          const uint32_t pa = smem_u32(smem + L::OFF_P + t * L::PT);
+          // P is read from TMEM (bf16 pairs in the first 64 columns of the tile's score region):
+          // it never crosses shared memory, whose bandwidth the operand fetches of the MMAs saturate
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
-            const uint64_t da = desc_kmajor(pa + (k / 4) * 16384, k % 4);
             const uint64_t db = desc_mnmajor(va, k, 16384);
-            umma_bf16(tmem_o[t], da, db, idesc_o, (i | k) != 0 ? 1u : 0u);
+            umma_bf16_ts(tmem_o[t], tmem_s[t] + k * 8, db, idesc_o, (i | k) != 0 ? 1u : 0u);
           }
           umma_commit(&pv_done[t]);
           if (i + 1 < n_t[t]) issue_s(t, kslot);
@@ -251,12 +253,13 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   }
   } else {
     // ------------------------------ softmax warpgroups ------------------------------
+    asm volatile("setmaxnreg.inc.sync.aligned.u32 216;" ::: "memory");
     const int t = (warp - 4) >> 2;
     const int quad = warp & 3;
     const int r = quad * 32 + lane;
     const int n_mine = t == 0 ? n0 : n1;
     const uint32_t lane_off = static_cast<uint32_t>(quad * 32) << 16;
-    uint8_t* pbuf = smem + L::OFF_P + t * L::PT;
+    uint8_t* obuf = smem + L::OFF_Q + t * L::QT;       // staging of O: the Q tile is dead after the last S MMA
     bool ok = true;
     float m_ref = -INFINITY, l_sum = 0.f;
     const int qi_local = q0 + t * 128 + r;             // row of Q / O / LSE held by this rank
@@ -268,7 +271,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (args.lim != nullptr) my_lim = args.lim[b * args.S + qi];
       if (sparse) my_start = args.sp.doc_start[b * args.S + qi];
     }
-    uint32_t sph = 0, dph = 0;
+    uint32_t sph = 0;
     const uint64_t scale2 = pack_f32x2(args.scale_log2, args.scale_log2);
     for (int i = 0; i < n_mine; ++i) {
       const int j = kv_tile(i);
@@ -330,57 +333,50 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         m_ref = mx;
         l_sum *= alpha;
       }
-      if (i > 0) {
-        // PV(i-1) must be complete before P is overwritten or O is rescaled.
-        if (!mbar_wait(&pv_done[t], dph, abort_flag, st, SITE_F_SM_PV, budget)) {
-          ok = false;
-          break;
-        }
-        dph ^= 1u;
-        if (__any_sync(0xffffffffu, need)) {
-          tc_fence_after();
+      // PV(i-1) was issued before S(i) and the tensor core completes MMAs in issue order, so the
+      // scores of this tile being ready means O holds every earlier tile: no separate wait.
+      if (i > 0 && __any_sync(0xffffffffu, need)) {
 #pragma unroll 1
-          for (int c = 0; c < D / 8; ++c) {      // narrow chunks: the score row stays in registers
-            uint32_t rr[8];
-            tmem_ld8(tmem_o[t] + lane_off + c * 8, rr);
-            tmem_ld_wait();
+        for (int c = 0; c < D / 8; ++c) {      // narrow chunks: the score row stays in registers
+          uint32_t rr[8];
+          tmem_ld8(tmem_o[t] + lane_off + c * 8, rr);
+          tmem_ld_wait();
 #pragma unroll
-            for (int e = 0; e < 8; ++e) rr[e] = __float_as_uint(__uint_as_float(rr[e]) * alpha);
-            tmem_st8(tmem_o[t] + lane_off + c * 8, rr);
-          }
-          tmem_st_wait();
+          for (int e = 0; e < 8; ++e) rr[e] = __float_as_uint(__uint_as_float(rr[e]) * alpha);
+          tmem_st8(tmem_o[t] + lane_off + c * 8, rr);
         }
+        tmem_st_wait();
       }
-      // ---- P = exp2(s * scale - m): packed fma / add on pairs, P as bf16 into the swizzled tile ----
+      // ---- P = exp2(s * scale - m): packed fma / add on pairs; P goes back into TMEM as bf16 pairs
+      // over the first 64 columns of the score row this thread already holds in registers ----
       const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
       const uint64_t neg_m2 = pack_f32x2(-m_use, -m_use);
       uint64_t rs2 = pack_f32x2(0.f, 0.f);
 #pragma unroll
-      for (int g = 0; g < 16; ++g) {
-        uint32_t w[4];
+      for (int qt = 0; qt < 8; ++qt) {           // 16 scores -> 8 packed columns per store
+        uint32_t pw[8];
 #pragma unroll
-        for (int jj = 0; jj < 4; ++jj) {
-          const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(sc[g * 8 + jj * 2]), __uint_as_float(sc[g * 8 + jj * 2 + 1])),
-                                        scale2, neg_m2);
+        for (int jj = 0; jj < 8; ++jj) {
+          const int e = qt * 16 + jj * 2;
+          const uint64_t x2 = fma_f32x2(pack_f32x2(__uint_as_float(sc[e]), __uint_as_float(sc[e + 1])), scale2, neg_m2);
           float xa, xb;
           unpack_f32x2(x2, xa, xb);
           const float pa = fast_exp2(xa), pb = fast_exp2(xb);
           rs2 = add_f32x2(rs2, pack_f32x2(pa, pb));
-          w[jj] = pack_bf16(pa, pb);
+          pw[jj] = pack_bf16(pa, pb);
         }
-        // 16-byte chunk g of the row's 128 keys
-        *reinterpret_cast<uint4*>(pbuf + (g / 8) * 16384 + sw128_offset(r, g % 8)) = make_uint4(w[0], w[1], w[2], w[3]);
+        tmem_st8(tmem_s[t] + lane_off + qt * 8, pw);
       }
+      tmem_st_wait();
       float rs_a, rs_b;
       unpack_f32x2(rs2, rs_a, rs_b);
       l_sum += rs_a + rs_b;
-      fence_proxy_async_smem();
       tc_fence_before();
       mbar_arrive(&p_full[t]);
     }
     // ---- finalize ----
     if (ok && n_mine > 0) {
-      ok = mbar_wait(&pv_done[t], dph, abort_flag, st, SITE_F_SM_PV, budget);
+      ok = mbar_wait(&pv_done[t], static_cast<uint32_t>(n_mine - 1) & 1u, abort_flag, st, SITE_F_SM_PV, budget);
       tc_fence_after();
     }
     const bool any_bad = named_bar_or(2 + t, 128, !ok);
@@ -403,14 +399,14 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           v.y = pack_bf16(__uint_as_float(rr[jj * 8 + 2]) * inv, __uint_as_float(rr[jj * 8 + 3]) * inv);
           v.z = pack_bf16(__uint_as_float(rr[jj * 8 + 4]) * inv, __uint_as_float(rr[jj * 8 + 5]) * inv);
           v.w = pack_bf16(__uint_as_float(rr[jj * 8 + 6]) * inv, __uint_as_float(rr[jj * 8 + 7]) * inv);
-          *reinterpret_cast<uint4*>(pbuf + (c / 2) * 16384 + sw128_offset(r, (c % 2) * 4 + jj)) = v;
+          *reinterpret_cast<uint4*>(obuf + (c / 2) * 16384 + sw128_offset(r, (c % 2) * 4 + jj)) = v;
         }
       }
       fence_proxy_async_smem();
       named_bar_sync(4 + t, 128);
       if (r == 0) {
 #pragma unroll
-        for (int hf = 0; hf < HALVES; ++hf) tma_store_4d(&map_o, pbuf + hf * 16384, hf * 64, h, q0 + t * 128, b);
+        for (int hf = 0; hf < HALVES; ++hf) tma_store_4d(&map_o, obuf + hf * 16384, hf * 64, h, q0 + t * 128, b);
         tma_commit_group();
         tma_wait_group<0>();
       }
