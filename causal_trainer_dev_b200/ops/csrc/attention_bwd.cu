@@ -14,9 +14,10 @@
 // Structure of both: resident operand pair X (K,V or Q,dO), streamed pair Y (Q,dO or K,V)
 // through a 3-stage TMA ring, four compute warpgroups that share every Y block (16 of its 64
 // columns each) over two alternating S / dP buffers, so the tensor core works on block i+1 and
-// on the accumulate MMAs of block i-1 while block i is exponentiated.  P^T / dS tiles are written as
-// bf16 into 128B-swizzled K-major shared tiles; the Y tiles are reused in place as
-// MN-major operands of the accumulate MMAs.
+// on the accumulate MMAs of block i-1 while block i is exponentiated.  P^T / dS go back into TMEM
+// as bf16 pairs over the scores they were computed from and are the TMEM A operands of the
+// accumulate MMAs (they never cross shared memory); the Y tiles are reused in place as MN-major
+// B operands.
 //
 // Reference counterparts: causal_trainer_attention_dq / _dkv
 // (src/causal_trainer/kernels/efficient_attention.py:985-1173, 1270-1436); the psum that
@@ -30,7 +31,7 @@ namespace ctb {
 namespace attn {
 
 constexpr int BWD_THREADS = 640;   // 4 service warps + 4 compute warpgroups
-constexpr int Y_STAGES = 3;
+constexpr int Y_STAGES = 4;
 
 enum : unsigned {
   SITE_B_PROD = 0x0301,
@@ -47,11 +48,9 @@ struct BwdSmem {
   static constexpr int HALVES = D / 64;
   static constexpr int XT = HALVES * 16384;   // 128-row resident tile
   static constexpr int YT = HALVES * 8192;    // 64-row streamed tile
-  static constexpr int TT = 16384;            // 128 x 64 bf16 P^T or dS tile
   static constexpr int OFF_X = 0;             // X1, X2
   static constexpr int OFF_Y = 2 * XT;        // stages of (Y1, Y2)
-  static constexpr int OFF_T = OFF_Y + Y_STAGES * 2 * YT;  // per warpgroup: (P^T, dS)
-  static constexpr int OFF_BAR = OFF_T + 2 * 2 * TT;
+  static constexpr int OFF_BAR = OFF_Y + Y_STAGES * 2 * YT;
   static constexpr int OFF_STAT = OFF_BAR + 256;   // per Y stage: 64 x -lse*log2(e), 64 x -delta of the block's queries (DKV)
   static constexpr int BYTES = OFF_STAT + Y_STAGES * 512 + 1024;
 };
@@ -213,19 +212,18 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         tc_fence_after();
         const uint32_t y1 = smem_u32(smem + L::OFF_Y + astage * 2 * L::YT);
         const uint32_t y2 = y1 + L::YT;
-        const uint32_t tp = smem_u32(smem + L::OFF_T + u * 2 * L::TT);
-        const uint32_t tds = tp + L::TT;
+        // P^T / dS are bf16 pairs in TMEM: the 16 columns of group kk sit in the first 8 columns of
+        // the group's own 16-column slice of the S / dP buffer (written over the scores it read)
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           if (DKV) {
-            umma_bf16(tmem_acc1, desc_kmajor(tp, kk), desc_mnmajor(y2, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
-            umma_bf16(tmem_acc2, desc_kmajor(tds, kk), desc_mnmajor(y1, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
+            umma_bf16_ts(tmem_acc1, tmem_s[u] + 16 * kk, desc_mnmajor(y2, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
+            umma_bf16_ts(tmem_acc2, tmem_dp[u] + 16 * kk, desc_mnmajor(y1, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
           } else {
-            umma_bf16(tmem_acc1, desc_kmajor(tds, kk), desc_mnmajor(y1, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
+            umma_bf16_ts(tmem_acc1, tmem_dp[u] + 16 * kk, desc_mnmajor(y1, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
           }
         }
         umma_commit(&y_empty[astage]);
-        umma_commit(&t_done[u]);
         if (++astage == Y_STAGES) astage = 0;
         return true;
       };
@@ -289,15 +287,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       neg_delta = args.neg_delta[(static_cast<size_t>(b) * args.Hq + head) * args.Sq + xi_local];
     }
     bool ok = true;
-    uint32_t sph = 0, dph = 0;             // bit u: phase parity of s_full[u] / t_done[u]
+    uint32_t sph = 0;                      // bit u: phase parity of s_full[u]
     const uint64_t scale2 = pack_f32x2(args.scale_log2, args.scale_log2);
     // dense walk: (block, head) advance without a division per iteration
     int walk_block = 0, walk_head = 0;
     uint32_t ystage = 0, yphase = 0;        // stage of the Y ring that holds block `it` (and its statistics)
     for (int it = 0; it < n_iter; ++it) {
       const int u = it & 1;
-      uint8_t* t_p = smem + L::OFF_T + u * 2 * L::TT;
-      uint8_t* t_ds = t_p + L::TT;
       int yb, hq;
       if (sparse) {
         const int entry = __ldg(it_list + it);
@@ -361,14 +357,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           break;
         }
       }
-      if (it >= 2) {
-        // the accumulate MMAs of block it - 2 read the P^T / dS tiles this block overwrites
-        if (!mbar_wait(&t_done[u], (dph >> u) & 1u, abort_flag, st, SITE_B_CW_T, budget)) {
-          ok = false;
-          break;
-        }
-        dph ^= 1u << u;
-      }
+      // (the accumulate MMAs of block it - 2 read P^T / dS from this buffer; they were issued before
+      // the S / dP MMAs of this block and the tensor core completes MMAs in issue order)
       tc_fence_after();
       uint32_t rs[16], rd[16];
       tmem_ld16(tmem_s[u] + lane_off + 16 * wg, rs);
@@ -416,13 +406,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               dw[h4 * 2 + pr] = pack_bf16(da, db);
             }
           }
-          if (DKV) *reinterpret_cast<uint4*>(t_p + sw128_offset(r, wg * 2 + gg)) = make_uint4(pw[0], pw[1], pw[2], pw[3]);
-          *reinterpret_cast<uint4*>(t_ds + sw128_offset(r, wg * 2 + gg)) = make_uint4(dw[0], dw[1], dw[2], dw[3]);
+          if (DKV) tmem_st4(tmem_s[u] + lane_off + 16 * wg + 4 * gg, pw);
+          tmem_st4(tmem_dp[u] + lane_off + 16 * wg + 4 * gg, dw);
         }
       };
       if (__all_sync(0xffffffffu, all)) compute16(std::false_type{});
       else compute16(std::true_type{});
-      fence_proxy_async_smem();
+      tmem_st_wait();
       tc_fence_before();
       mbar_arrive(&t_full[u]);
       if (++ystage == Y_STAGES) {
@@ -444,7 +434,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // DKV: warpgroup 0 stores dV, warpgroup 1 stores dK (scaled); DQ: warpgroup 0 stores dQ (scaled).
       const uint32_t acc = (DKV && u == 1) ? tmem_acc2 : tmem_acc1;
       const float mul = (DKV && u == 0) ? 1.f : args.scale;
-      uint8_t* stage_buf = smem + L::OFF_T + u * 2 * L::TT;  // 32 KiB: [HALVES][128 rows][128 B]
+      uint8_t* stage_buf = smem + L::OFF_X + u * L::XT;      // the resident tile u is dead now: [HALVES][128 rows][128 B]
       // the two warpgroups of the pair convert half of the head dimension each
 #pragma unroll 1
       for (int c = half * (D / 64); c < (half + 1) * (D / 64); ++c) {
