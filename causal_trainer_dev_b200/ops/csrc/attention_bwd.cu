@@ -151,8 +151,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s[2] = {tmem_base, tmem_base + 64};
-  const uint32_t tmem_dp[2] = {tmem_base + 128, tmem_base + 192};
+  // S^T / dP^T (or S / dP) of block buffer u: 64 columns each (address arithmetic, not arrays: a
+  // runtime index into a local array would go through local memory)
+  auto tmem_s = [&](int u) -> uint32_t { return tmem_base + static_cast<uint32_t>(u) * 64u; };
+  auto tmem_dp = [&](int u) -> uint32_t { return tmem_base + 128u + static_cast<uint32_t>(u) * 64u; };
   const uint32_t tmem_acc1 = tmem_base + 256;       // dV (DKV) or dQ (DQ)
   const uint32_t tmem_acc2 = tmem_base + 256 + D;   // dK (DKV)
 
@@ -217,10 +219,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk) {
           if (DKV) {
-            umma_bf16_ts(tmem_acc1, tmem_s[u] + 16 * kk, desc_mnmajor(y2, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
-            umma_bf16_ts(tmem_acc2, tmem_dp[u] + 16 * kk, desc_mnmajor(y1, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
+            umma_bf16_ts(tmem_acc1, tmem_s(u) + 16 * kk, desc_mnmajor(y2, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
+            umma_bf16_ts(tmem_acc2, tmem_dp(u) + 16 * kk, desc_mnmajor(y1, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
           } else {
-            umma_bf16_ts(tmem_acc1, tmem_dp[u] + 16 * kk, desc_mnmajor(y1, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
+            umma_bf16_ts(tmem_acc1, tmem_dp(u) + 16 * kk, desc_mnmajor(y1, kk, 8192), idesc_acc, (k | kk) != 0 ? 1u : 0u);
           }
         }
         umma_commit(&y_empty[astage]);
@@ -238,11 +240,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         const uint32_t y2 = y1 + L::YT;
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          umma_bf16(tmem_s[u], desc_kmajor(x1 + (k / 4) * 16384, k % 4), desc_kmajor(y1 + (k / 4) * 8192, k % 4),
+          umma_bf16(tmem_s(u), desc_kmajor(x1 + (k / 4) * 16384, k % 4), desc_kmajor(y1 + (k / 4) * 8192, k % 4),
                     idesc_s, k != 0 ? 1u : 0u);
 #pragma unroll
         for (int k = 0; k < D / 16; ++k)
-          umma_bf16(tmem_dp[u], desc_kmajor(x2 + (k / 4) * 16384, k % 4), desc_kmajor(y2 + (k / 4) * 8192, k % 4),
+          umma_bf16(tmem_dp(u), desc_kmajor(x2 + (k / 4) * 16384, k % 4), desc_kmajor(y2 + (k / 4) * 8192, k % 4),
                     idesc_s, k != 0 ? 1u : 0u);
         umma_commit(&s_full[u]);
         if (++stage == Y_STAGES) {
@@ -361,8 +363,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       // the S / dP MMAs of this block and the tensor core completes MMAs in issue order)
       tc_fence_after();
       uint32_t rs[16], rd[16];
-      tmem_ld16(tmem_s[u] + lane_off + 16 * wg, rs);
-      tmem_ld16(tmem_dp[u] + lane_off + 16 * wg, rd);
+      tmem_ld16(tmem_s(u) + lane_off + 16 * wg, rs);
+      tmem_ld16(tmem_dp(u) + lane_off + 16 * wg, rd);
       tmem_ld_wait();
       // Eight columns at a time: probabilities and dS are packed and stored as soon as they exist.
       // MASKED = false is the path of a warp whose rows all see all 16 columns: no selects.
@@ -406,8 +408,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
               dw[h4 * 2 + pr] = pack_bf16(da, db);
             }
           }
-          if (DKV) tmem_st4(tmem_s[u] + lane_off + 16 * wg + 4 * gg, pw);
-          tmem_st4(tmem_dp[u] + lane_off + 16 * wg + 4 * gg, dw);
+          if (DKV) tmem_st4(tmem_s(u) + lane_off + 16 * wg + 4 * gg, pw);
+          tmem_st4(tmem_dp(u) + lane_off + 16 * wg + 4 * gg, dw);
         }
       };
       if (__all_sync(0xffffffffu, all)) compute16(std::false_type{});

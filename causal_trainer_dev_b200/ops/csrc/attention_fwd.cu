@@ -141,8 +141,8 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  const uint32_t tmem_s[2] = {tmem_base, tmem_base + 128};
-  const uint32_t tmem_o[2] = {tmem_base + 256, tmem_base + 256 + D};
+  auto tmem_s_of = [&](int t) -> uint32_t { return tmem_base + static_cast<uint32_t>(t) * 128u; };
+  auto tmem_o_of = [&](int t) -> uint32_t { return tmem_base + 256u + static_cast<uint32_t>(t) * D; };
 
   if (warp < 4) {
   // the service warpgroup hands most of its registers to the two softmax warpgroups, which hold a
@@ -199,7 +199,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
         for (int k = 0; k < D / 16; ++k) {
           const uint64_t da = desc_kmajor(qa + (k / 4) * 16384, k % 4);
           const uint64_t db = desc_kmajor(ka + (k / 4) * 16384, k % 4);
-          umma_bf16(tmem_s[t], da, db, idesc_s, k != 0 ? 1u : 0u);
+          umma_bf16(tmem_s_of(t), da, db, idesc_s, k != 0 ? 1u : 0u);
         }
         umma_commit(&s_full[t]);
       };
@@ -240,7 +240,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll
           for (int k = 0; k < 8; ++k) {
             const uint64_t db = desc_mnmajor(va, k, 16384);
-            umma_bf16_ts(tmem_o[t], tmem_s[t] + k * 8, db, idesc_o, (i | k) != 0 ? 1u : 0u);
+            umma_bf16_ts(tmem_o_of(t), tmem_s_of(t) + k * 8, db, idesc_o, (i | k) != 0 ? 1u : 0u);
           }
           umma_commit(&pv_done[t]);
           if (i + 1 < n_t[t]) issue_s(t, kslot);
@@ -297,7 +297,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       tc_fence_after();
       // ---- the whole score row in registers: one TMEM round trip ----
       uint32_t sc[128];
-      tmem_ld32x4(tmem_s[t] + lane_off, sc);
+      tmem_ld32x4(tmem_s_of(t) + lane_off, sc);
       tmem_ld_wait();
       if (!all) {
 #pragma unroll
@@ -339,11 +339,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 #pragma unroll 1
         for (int c = 0; c < D / 8; ++c) {      // narrow chunks: the score row stays in registers
           uint32_t rr[8];
-          tmem_ld8(tmem_o[t] + lane_off + c * 8, rr);
+          tmem_ld8(tmem_o_of(t) + lane_off + c * 8, rr);
           tmem_ld_wait();
 #pragma unroll
           for (int e = 0; e < 8; ++e) rr[e] = __float_as_uint(__uint_as_float(rr[e]) * alpha);
-          tmem_st8(tmem_o[t] + lane_off + c * 8, rr);
+          tmem_st8(tmem_o_of(t) + lane_off + c * 8, rr);
         }
         tmem_st_wait();
       }
@@ -365,7 +365,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           rs2 = add_f32x2(rs2, pack_f32x2(pa, pb));
           pw[jj] = pack_bf16(pa, pb);
         }
-        tmem_st8(tmem_s[t] + lane_off + qt * 8, pw);
+        tmem_st8(tmem_s_of(t) + lane_off + qt * 8, pw);
       }
       tmem_st_wait();
       float rs_a, rs_b;
@@ -386,7 +386,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       for (int c = 0; c < D / 32; ++c) {
         uint32_t rr[32];
         if (n_mine > 0) {
-          tmem_ld32(tmem_o[t] + lane_off + c * 32, rr);
+          tmem_ld32(tmem_o_of(t) + lane_off + c * 32, rr);
           tmem_ld_wait();
         } else {
 #pragma unroll
