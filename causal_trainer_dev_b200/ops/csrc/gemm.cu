@@ -663,6 +663,7 @@ int run_gemm(const GemmCall& c) {
   if ((c.lda % 8) || (c.ldb % 8)) return fail("gemm: lda and ldb must be multiples of 8 elements (16 bytes)");
   const bool needs_c = (c.epi != EPI_CE_STATS) && !c.push.enabled;
   if (needs_c && (c.ldc % (c.out_f32 ? 4 : 8))) return fail("gemm: ldc must be a multiple of 16 bytes");
+  if (gemm_pair_eligible(c)) return launch_gemm_pair(c);       // two-CTA 256 x 256 tiles (gemm_pair.cu)
   const CUtensorMap* ma = c.a_mn ? get_tensor_map_2d(c.A, Elt::BF16, c.M, c.K, c.lda, 64, 64, true)
                                  : get_tensor_map_2d(c.A, Elt::BF16, c.K, c.M, c.lda, 64, BM, true);
   if (!ma) return 1;

@@ -99,4 +99,10 @@ struct GemmCall {
 
 int run_gemm(const GemmCall& call);
 
+// Two-CTA variant (gemm_pair.cu): plain products on clusters of two CTAs with
+// tcgen05.mma.cta_group::2, selected by run_gemm when the mode is on (CTB_GEMM_PAIR=1 or
+// ctb_gemm_set_pair) and the call has no gathered operand, fused epilogue or bias.
+bool gemm_pair_eligible(const GemmCall& c);
+int launch_gemm_pair(const GemmCall& c);
+
 }  // namespace ctb

@@ -99,3 +99,28 @@ def _check_split_k(G, m, n, k):
     # K-major operands take the same path
     out = G.gemm(dy.t().contiguous(), x.t().contiguous(), out_dtype=torch.float32)
     assert _rel(out, ref) < 1e-4
+
+
+@pytest.mark.parametrize("shape", [(4864, 4864, 512), (5000, 4936, 520)])
+def test_two_cta_pair_kernel_matches_reference(cuda_lib, shape):
+    """tcgen05.mma.cta_group::2 on clusters of two CTAs: all operand layouts, bf16 / fp32 out, accumulate."""
+    from causal_trainer_dev_b200.ops import gemm as G
+
+    m, n, k = shape
+    torch.manual_seed(7)
+    a = torch.randn(m, k, device="cuda").bfloat16()
+    b = torch.randn(n, k, device="cuda").bfloat16()
+    ref = a.float() @ b.float().t()
+    before = cuda_lib.lib().ctb_gemm_set_pair(1)
+    try:
+        for a_mn in (False, True):
+            for b_mn in (False, True):
+                out = G.gemm(a.t().contiguous() if a_mn else a, b.t().contiguous() if b_mn else b, a_mn=a_mn, b_mn=b_mn)
+                assert _rel(out, ref) < 4e-3, (a_mn, b_mn)
+        acc = torch.randn(m, n, device="cuda")
+        expect = acc + 0.5 * ref
+        G.gemm(a, b, out=acc, accumulate=True, alpha=0.5)
+        assert _rel(acc, expect) < 1e-5
+    finally:
+        cuda_lib.lib().ctb_gemm_set_pair(before)
+    assert cuda_lib.device_status() == (0, 0, 0, 0)
