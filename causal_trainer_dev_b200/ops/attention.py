@@ -33,14 +33,8 @@ class AttentionMeta:
     lim: torch.Tensor | None     # [B,S] int32 inclusive last visible key (None: plain causal)
     kv_lo: torch.Tensor          # [B,S/128] int32
     kv_hi: torch.Tensor          # [B,S/128] int32
-    kmin: torch.Tensor           # [B,S/128] int32
-    kmax: torch.Tensor           # [B,S/128] int32
     q_lo: torch.Tensor           # [B,S/128] int32 first query that sees the key block
     q_hi: torch.Tensor           # [B,S/128] int32 one past the last such query
-    seg_min64: torch.Tensor      # [B,S/64] int32
-    seg_max64: torch.Tensor      # [B,S/64] int32
-    lim_min64: torch.Tensor      # [B,S/64] int32
-    lim_max64: torch.Tensor      # [B,S/64] int32
     attention_end: torch.Tensor | None = None  # kept for the oracle backend
     start: torch.Tensor | None = None        # [B,S] int32 first token of the token's run
     end: torch.Tensor | None = None          # [B,S] int32 last token of the token's run
@@ -76,14 +70,13 @@ def attention_metadata(attention_mask: torch.Tensor, segment_ids: torch.Tensor |
     pos = torch.empty_like(seg)
     lim = torch.empty_like(seg)
     rows = torch.empty((4, bsz, s), dtype=torch.int32, device=dev)
-    s128 = torch.empty((6, bsz, s // BLOCK), dtype=torch.int32, device=dev)
-    s64 = torch.empty((4, bsz, s // 64), dtype=torch.int32, device=dev)
+    s128 = torch.empty((4, bsz, s // BLOCK), dtype=torch.int32, device=dev)
     code = _lib.lib().ctb_attention_meta(_lib.ptr(mask), _lib.ptr(label), _lib.ptr(end), bsz, s, _lib.ptr(seg),
-                                         _lib.ptr(pos), _lib.ptr(lim), _lib.ptr(rows), _lib.ptr(s128), _lib.ptr(s64),
+                                         _lib.ptr(pos), _lib.ptr(lim), _lib.ptr(rows), _lib.ptr(s128),
                                          _lib.stream_ptr())
     _lib.check(code, "ctb_attention_meta")
-    meta = AttentionMeta(seg, lim if attention_end is not None else None, s128[0], s128[1], s128[2], s128[3], s128[4],
-                         s128[5], s64[0], s64[1], s64[2], s64[3], attention_end, rows[0], rows[1], rows[2])
+    meta = AttentionMeta(seg, lim if attention_end is not None else None, s128[0], s128[1], s128[2], s128[3],
+                         attention_end, rows[0], rows[1], rows[2])
     return seg, pos, meta
 
 
@@ -127,8 +120,6 @@ def build_attention_meta_reference(segment_ids: torch.Tensor, attention_end: tor
     kv_lo = blk(torch.where(valid, seg_start, torch.full_like(idx, big))).amin(-1)
     kv_hi = blk(torch.where(valid, lim_full + 1, torch.zeros_like(idx))).amax(-1)
     kv_lo = torch.where(kv_hi > 0, kv_lo, torch.zeros_like(kv_lo))
-    kmin = blk(seg).amin(-1)
-    kmax = blk(seg).amax(-1)
     # first query that sees key j: suffix-min over p >= j of min{i : lim[i] == p}
     if attention_end is None:
         first_q = idx
@@ -141,11 +132,8 @@ def build_attention_meta_reference(segment_ids: torch.Tensor, attention_end: tor
     q_hi = blk(torch.where(valid, seg_end + 1, torch.zeros_like(idx))).amax(-1)
     q_lo = torch.where(q_hi > 0, q_lo, torch.zeros_like(q_lo))
     i32 = lambda t: t.to(torch.int32).contiguous()  # noqa: E731
-    seg64 = seg.reshape(bsz, s // 64, 64)
-    lim64 = lim_full.reshape(bsz, s // 64, 64)
     return AttentionMeta(
-        seg, lim, i32(kv_lo), i32(kv_hi), i32(kmin), i32(kmax), i32(q_lo), i32(q_hi),
-        i32(seg64.amin(-1)), i32(seg64.amax(-1)), i32(lim64.amin(-1)), i32(lim64.amax(-1)), attention_end,
+        seg, lim, i32(kv_lo), i32(kv_hi), i32(q_lo), i32(q_hi), attention_end,
         i32(seg_start), i32(seg_end), i32(first_q),
     )
 

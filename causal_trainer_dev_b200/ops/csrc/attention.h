@@ -12,7 +12,6 @@ namespace attn {
 //                     contiguous interval [row_start[i], lim[i]])
 //   kv_lo  [B,S/128]  first key index any row of the 128-row query block can see
 //   kv_hi  [B,S/128]  one past the last such key index (kv_hi <= kv_lo: nothing visible)
-//   kmin/kmax [B,S/128] min / max segment id inside each 128-key block
 //   q_lo/q_hi [B,S/128] per 128-key block: range of query indices that can see it
 // MoBA block-sparse routing (all null / zero for dense attention).  Keys are cut into blocks of
 // `block` tokens counted from the start of their document; query i of head h may see key j of its

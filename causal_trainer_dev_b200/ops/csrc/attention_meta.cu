@@ -14,9 +14,8 @@
 //   start[i], end[i]   first / last token of the run; first_q[i] first query that sees key i.  The
 //                keys visible to query i are the interval [start[i], lim[i]], the queries that see
 //                key j the interval [first_q[j], end[j]]: the flash kernels mask by interval
-//   kv_lo/kv_hi  [S/128] key range [lo, hi) needed by the query block     kmin/kmax   min / max seg of the key block
+//   kv_lo/kv_hi  [S/128] key range [lo, hi) needed by the query block
 //   q_lo/q_hi    [S/128] query range [lo, hi) that can see the key block
-//   seg_min64 / seg_max64 / lim_min64 / lim_max64   [S/64] per 64-token block
 //
 // Reference counterparts: run-based segment ids and restart positions
 // (src/causal_trainer/modeling/rotary.py:13-50,82-110) and the per-block (min, max, max_end)
@@ -61,8 +60,7 @@ struct Args {
   int* pos;             // [B,S]
   int* lim;             // [B,S]
   int* rows;            // [4,B,S]: run start, run end (inclusive), first query that sees the key, scatter scratch
-  int *kv_lo, *kv_hi, *kmin, *kmax, *q_lo, *q_hi;           // [B,S/128]
-  int *seg_min64, *seg_max64, *lim_min64, *lim_max64;       // [B,S/64]
+  int *kv_lo, *kv_hi, *q_lo, *q_hi;                         // [B,S/128]
   int S;
 };
 
@@ -153,45 +151,26 @@ __global__ void __launch_bounds__(THREADS) attention_meta_kernel(const Args a) {
   const int nb128 = S / 128;
   for (int blk = warp; blk < nb128; blk += THREADS / 32) {
     int v_kv_lo = BIG, v_kv_hi = 0, v_q_lo = BIG, v_q_hi = 0;
-    int v_seg_min = BIG, v_seg_max = 0, v_lim_min = BIG, v_lim_max = 0;
     for (int e = 0; e < 4; ++e) {
       const int i = blk * 128 + lane * 4 + e;
-      const int sg = seg[i], l = lim[i];
-      if (sg != 0) {
+      if (seg[i] != 0) {
         v_kv_lo = min(v_kv_lo, run_start[i]);
-        v_kv_hi = max(v_kv_hi, l + 1);
+        v_kv_hi = max(v_kv_hi, lim[i] + 1);
         v_q_lo = min(v_q_lo, first_q[i]);
         v_q_hi = max(v_q_hi, run_end[i] + 1);
       }
-      v_seg_min = min(v_seg_min, sg);
-      v_seg_max = max(v_seg_max, sg);
-      v_lim_min = min(v_lim_min, l);
-      v_lim_max = max(v_lim_max, l);
     }
 #pragma unroll
     for (int off = 1; off < 32; off <<= 1) {
-      if (off == 16 && (lane == 0 || lane == 16)) {     // lanes 0-15 hold the first 64 tokens, 16-31 the second
-        const size_t o = static_cast<size_t>(row) * (S / 64) + blk * 2 + (lane >> 4);
-        a.seg_min64[o] = v_seg_min;
-        a.seg_max64[o] = v_seg_max;
-        a.lim_min64[o] = v_lim_min;
-        a.lim_max64[o] = v_lim_max;
-      }
       v_kv_lo = min(v_kv_lo, __shfl_xor_sync(0xffffffffu, v_kv_lo, off));
       v_kv_hi = max(v_kv_hi, __shfl_xor_sync(0xffffffffu, v_kv_hi, off));
       v_q_lo = min(v_q_lo, __shfl_xor_sync(0xffffffffu, v_q_lo, off));
       v_q_hi = max(v_q_hi, __shfl_xor_sync(0xffffffffu, v_q_hi, off));
-      v_seg_min = min(v_seg_min, __shfl_xor_sync(0xffffffffu, v_seg_min, off));
-      v_seg_max = max(v_seg_max, __shfl_xor_sync(0xffffffffu, v_seg_max, off));
-      v_lim_min = min(v_lim_min, __shfl_xor_sync(0xffffffffu, v_lim_min, off));
-      v_lim_max = max(v_lim_max, __shfl_xor_sync(0xffffffffu, v_lim_max, off));
     }
     if (lane == 0) {
       const size_t o = static_cast<size_t>(row) * nb128 + blk;
       a.kv_lo[o] = v_kv_hi > 0 ? v_kv_lo : 0;
       a.kv_hi[o] = v_kv_hi;
-      a.kmin[o] = v_seg_min;
-      a.kmax[o] = v_seg_max;
       a.q_lo[o] = v_q_hi > 0 ? v_q_lo : 0;
       a.q_hi[o] = v_q_hi;
     }
@@ -203,10 +182,9 @@ __global__ void __launch_bounds__(THREADS) attention_meta_kernel(const Args a) {
 
 // All tensors int32.  `label` and `att_end` may be null.  `rows` is [4][B][S]: per token the first
 // and last token of its run, the first query that sees it as a key, and one plane of scratch.
-// `summaries128` is [6][B][S/128] (kv_lo, kv_hi, kmin, kmax, q_lo, q_hi) and `summaries64` is
-// [4][B][S/64] (seg_min, seg_max, lim_min, lim_max).
+// `summaries` is [4][B][S/128]: kv_lo, kv_hi, q_lo, q_hi.
 CTB_API int ctb_attention_meta(const int* mask, const int* label, const int* att_end, int B, int S, int* seg, int* pos,
-                               int* lim, int* rows, int* summaries128, int* summaries64, void* stream) {
+                               int* lim, int* rows, int* summaries, void* stream) {
   using namespace ctb;
   if (B <= 0 || S <= 0 || S % 128) return fail("attention_meta: S must be a positive multiple of 128");
   meta::Args a;
@@ -217,17 +195,11 @@ CTB_API int ctb_attention_meta(const int* mask, const int* label, const int* att
   a.pos = pos;
   a.lim = lim;
   a.rows = rows;
-  const size_t n128 = static_cast<size_t>(B) * (S / 128), n64 = static_cast<size_t>(B) * (S / 64);
-  a.kv_lo = summaries128;
-  a.kv_hi = summaries128 + n128;
-  a.kmin = summaries128 + 2 * n128;
-  a.kmax = summaries128 + 3 * n128;
-  a.q_lo = summaries128 + 4 * n128;
-  a.q_hi = summaries128 + 5 * n128;
-  a.seg_min64 = summaries64;
-  a.seg_max64 = summaries64 + n64;
-  a.lim_min64 = summaries64 + 2 * n64;
-  a.lim_max64 = summaries64 + 3 * n64;
+  const size_t n128 = static_cast<size_t>(B) * (S / 128);
+  a.kv_lo = summaries;
+  a.kv_hi = summaries + n128;
+  a.q_lo = summaries + 2 * n128;
+  a.q_hi = summaries + 3 * n128;
   a.S = S;
   meta::attention_meta_kernel<<<B, meta::THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
   CTB_CUDA_OK(cudaGetLastError());

@@ -185,7 +185,8 @@ def build_routing(q: torch.Tensor, k: torch.Tensor, meta: AttentionMeta, block: 
     g = hq // hkv
     seg = meta.seg
     dev = q.device
-    doc_start = document_starts(seg)
+    # the run start of every token is part of the step's attention metadata (one launch per micro-batch)
+    doc_start = meta.start.contiguous() if meta.start is not None else document_starts(seg)
     sel = route(q, k, seg, doc_start, block, top_k)
     words = sel.shape[-1]
     nb64, nb128, nqp = s // 64, s // 128, (s + 255) // 256
