@@ -39,7 +39,6 @@ enum : unsigned {
   SITE_B_MMA_Y = 0x0303,
   SITE_B_MMA_T = 0x0304,
   SITE_B_CW_S = 0x0305,
-  SITE_B_CW_T = 0x0306,
   SITE_B_CW_ACC = 0x0307,
 };
 
@@ -71,8 +70,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   uint64_t* y_empty = y_full + Y_STAGES;
   uint64_t* s_full = y_empty + Y_STAGES;   // [2] S and dP of buffer u ready
   uint64_t* t_full = s_full + 2;           // [2] P^T / dS tiles of buffer u written
-  uint64_t* t_done = t_full + 2;           // [2] accumulate MMAs that read buffer u complete
-  uint64_t* acc_full = t_done + 2;
+  uint64_t* acc_full = t_full + 2;
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 1);
   volatile uint32_t* abort_flag = tmem_slot + 1;
 
@@ -137,7 +135,6 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     for (int u = 0; u < 2; ++u) {
       mbar_init(&s_full[u], 1);
       mbar_init(&t_full[u], 512);
-      mbar_init(&t_done[u], 1);
     }
     mbar_init(acc_full, 1);
     *abort_flag = 0u;
