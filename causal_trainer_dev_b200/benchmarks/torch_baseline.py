@@ -7,7 +7,6 @@ same-box, same-shape number to stand against (``bench.py --impl torch``).
 """
 from __future__ import annotations
 
-import math
 
 import torch
 import torch.distributed as dist

@@ -26,7 +26,6 @@ from pathlib import Path
 from typing import Any, Callable, Iterator
 
 import torch
-import torch.distributed as dist
 
 from ..models.config import ModelConfig
 from ..models.params import ModelParams, hf_export_order, hf_name_map, unit_layouts

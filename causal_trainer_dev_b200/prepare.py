@@ -19,7 +19,6 @@ from dataclasses import dataclass
 from pathlib import Path
 from typing import Any
 
-import numpy as np
 
 from .data.pipeline import (contiguous_shard_bounds, load_training_split, packed_dataset_to_arrays,
                             prepare_training_dataset)

@@ -16,7 +16,7 @@ from __future__ import annotations
 import argparse
 import math
 import sys
-from dataclasses import dataclass, field, fields, make_dataclass
+from dataclasses import dataclass, field, make_dataclass
 from pathlib import Path
 from typing import Any
 

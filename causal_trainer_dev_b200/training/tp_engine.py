@@ -21,7 +21,6 @@ import torch.distributed as dist
 
 from ..models.config import ModelConfig
 from ..models.params import embed_layout
-from ..ops import attention as attn_ops
 from ..ops import cross_entropy as ce
 from ..ops import elementwise as ew
 from ..ops.gemm import gemm
