@@ -1,0 +1,50 @@
+"""Small public helpers that the main paths do not exercise directly."""
+import pytest
+import torch
+
+from causal_trainer_dev_b200.models.config import preset
+from causal_trainer_dev_b200.models.freezing import split_trainable
+from causal_trainer_dev_b200.models.params import ModelParams
+from causal_trainer_dev_b200.parallel import runtime as rt
+from causal_trainer_dev_b200.parallel.tp import kv_replicas, merge_unit_tensor, slice_unit_tensor
+from causal_trainer_dev_b200.training.losses import mean_loss
+
+
+@pytest.mark.parametrize("kv_heads,tp", [(2, 2), (1, 2), (4, 4), (2, 4)])
+def test_tensor_parallel_slices_merge_back(kv_heads, tp):
+    """slice_unit_tensor / merge_unit_tensor are inverses, also when key/value heads are shared."""
+    cfg = preset("tiny", num_attention_heads=4, num_key_value_heads=kv_heads, intermediate_size=512)
+    q, kv, f, d = cfg.query_width, cfg.key_value_width, cfg.intermediate_size, cfg.hidden_size
+    gen = torch.Generator().manual_seed(0)
+    shapes = {"qkv_w": (q + 2 * kv, d), "qkv_b": (q + 2 * kv,), "o_w": (d, q), "gu_w": (2 * f, d), "down_w": (d, f),
+              "embed": (cfg.vocab_size, d), "lm_head": (cfg.vocab_size, d), "ln1": (d,)}
+    for name, shape in shapes.items():
+        full = torch.randn(shape, generator=gen)
+        parts = [slice_unit_tensor(name, full, cfg, tp, r) for r in range(tp)]
+        assert torch.equal(merge_unit_tensor(name, parts, cfg), full), name
+    rep = kv_replicas(cfg, tp)
+    assert rep == max(1, tp // kv_heads)
+    if rep > 1:     # ranks that share a key/value head hold identical K/V rows
+        full = torch.randn(shapes["qkv_w"], generator=gen)
+        a, b = slice_unit_tensor("qkv_w", full, cfg, tp, 0), slice_unit_tensor("qkv_w", full, cfg, tp, 1)
+        assert torch.equal(a[q // tp:], b[q // tp:]) and not torch.equal(a[:q // tp], b[:q // tp])
+
+
+def test_split_trainable_reports_frozen_components():
+    cfg = preset("tiny")
+    names = ModelParams(cfg, torch.float32, "cpu").hf_names()
+    frozen, trainable = split_trainable(cfg, ("embed", "norm"), names)
+    assert "model.embed_tokens.weight" in frozen and "model.norm.weight" in frozen
+    assert "model.layers.0.input_layernorm.weight" in frozen and "lm_head.weight" in trainable
+    assert sorted(frozen + trainable) == sorted(names)
+
+
+def test_single_process_host_collectives_are_identities():
+    assert rt.broadcast_object({"a": 1}) == {"a": 1}
+    assert rt.allgather_object(3) == [3]
+    assert rt.pickle_digest([1, 2]) == rt.pickle_digest([1, 2]) != rt.pickle_digest([2, 1])
+
+
+def test_mean_loss_guards_empty_batches():
+    assert float(mean_loss(torch.tensor(6.0), torch.tensor(3.0))) == 2.0
+    assert float(mean_loss(torch.tensor(0.0), torch.tensor(0.0))) == 0.0
