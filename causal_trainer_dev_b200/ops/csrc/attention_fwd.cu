@@ -6,15 +6,16 @@
 // One CTA owns 256 consecutive query rows of one (batch, query head): two 128-row tiles
 // that ping-pong so the tensor core computes one tile's S = Q K^T / O += P V while the
 // other tile's softmax runs.
-//   warp 0      TMA producer (Q tiles once, then K(j), V(j) through a 3-slot ring)
+//   warp 0      TMA producer (Q tiles once, then K(j), V(j) through a 5-slot ring)
 //   warp 1      TMEM allocation + single-thread tcgen05.mma issue   (warps 2-3 idle)
 //   warps 4-7   softmax of tile 0 (one query row per thread, TMEM lane = row)
 //   warps 8-11  softmax of tile 1
 // The softmax holds a whole score row (128 fp32) in registers: one TMEM round trip per tile.
 // S (fp32) and O (fp32) live in TMEM.  P is written back into TMEM as bf16 pairs over the first
 // half of its score row and is the TMEM A operand of the second MMA, so it never crosses shared
-// memory (the operand fetches of the two MMAs alone come close to the 128 B/clk of the SM); V is
-// consumed in place as an MN-major operand.
+// memory and the shared memory it would need holds two more K/V slots; V is consumed in place as
+// an MN-major operand.  The service warpgroup (warps 0-3) gives most of its registers to the two
+// softmax warpgroups (setmaxnreg).
 // The running maximum is only raised when it grows by more than 2^8 (the O rescale in TMEM
 // is rare), the final O / l and LSE are written by the softmax warps.
 // KV blocks outside [kv_lo, kv_hi) of a query block are never visited (block skipping from
