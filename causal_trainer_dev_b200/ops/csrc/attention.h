@@ -17,8 +17,8 @@ namespace attn {
 // `block` tokens counted from the start of their document; query i of head h may see key j of its
 // own document iff j <= lim[i] and bit ((j - doc_start[i]) / block) of its selection mask is set
 // (the query's own block is always selected).  Each CTA walks a list of key tiles (forward) or of
-// (64-row block, head) pairs (backward) that host code derived from the union of its rows'
-// selections, instead of a contiguous range.
+// (64-row block, head) pairs (backward) that the work-list kernels of moba.cu derived from the union
+// of its rows' selections, instead of a contiguous range.
 struct SparseArgs {
   const int* it_off;       // [work items + 1] offsets into it_list, work items in blockIdx order; or, when
                            // it_cnt is set, unused: item i owns it_list[i * it_stride ..] with it_cnt[i] entries

@@ -12,7 +12,7 @@
 //             dQ += dS K.
 //
 // Structure of both: resident operand pair X (K,V or Q,dO), streamed pair Y (Q,dO or K,V)
-// through a 3-stage TMA ring, four compute warpgroups that share every Y block (16 of its 64
+// through a 4-stage TMA ring, four compute warpgroups that share every Y block (16 of its 64
 // columns each) over two alternating S / dP buffers, so the tensor core works on block i+1 and
 // on the accumulate MMAs of block i-1 while block i is exponentiated.  P^T / dS go back into TMEM
 // as bf16 pairs over the scores they were computed from and are the TMEM A operands of the
