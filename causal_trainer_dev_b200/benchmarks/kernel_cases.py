@@ -1,6 +1,7 @@
 """Small, self-terminating single-kernel workloads for profiling and roofline numbers.
 
-    python -m causal_trainer_dev_b200.benchmarks.kernel_cases gemm|wgrad|attn_fwd|attn_bwd|cut_ce|rmsnorm|adamw
+    python -m causal_trainer_dev_b200.benchmarks.kernel_cases \
+        gemm|dgrad|wgrad|layer_gemms|attn_fwd|attn_bwd|moba [one-document|coherent]|cut_ce|rmsnorm|adamw
 
 Each case holds a few hundred MB (more than the 126 MB L2, far less than a GB-scale step),
 launches its kernel a handful of times, and prints device-timed milliseconds plus the achieved
