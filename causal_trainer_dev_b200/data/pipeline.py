@@ -31,16 +31,18 @@ LOCAL_SUFFIXES = {".json", ".jsonl", ".parquet", ".csv", ".tsv"}
 class RecordList:
     """In-memory list of source records with the small ``datasets.Dataset`` surface we use."""
 
-    def __init__(self, records: list[dict[str, Any]], fingerprint: str):
+    def __init__(self, records: list[dict[str, Any]], fingerprint: str, column_names: list[str] | None = None):
         self.records = records
         self._fingerprint = fingerprint
+        # kept explicitly so that an empty selection (a process with no rows) still knows its schema
+        self._column_names = list(column_names) if column_names is not None else (sorted(records[0]) if records else [])
 
     def __len__(self) -> int:
         return len(self.records)
 
     def __getitem__(self, index):
         if isinstance(index, slice):
-            return RecordList(self.records[index], f"{self._fingerprint}[{index.start}:{index.stop}]")
+            return RecordList(self.records[index], f"{self._fingerprint}[{index.start}:{index.stop}]", self._column_names)
         return self.records[index]
 
     def __iter__(self) -> Iterator[dict[str, Any]]:
@@ -48,12 +50,12 @@ class RecordList:
 
     @property
     def column_names(self) -> list[str]:
-        return sorted(self.records[0]) if self.records else []
+        return list(self._column_names)
 
     def select(self, indices, keep_in_memory: bool = True) -> "RecordList":
         idx = list(indices)
         return RecordList([self.records[i] for i in idx], hashlib.sha256(
-            (self._fingerprint + json.dumps(idx[:1] + idx[-1:] + [len(idx)])).encode()).hexdigest())
+            (self._fingerprint + json.dumps(idx[:1] + idx[-1:] + [len(idx)])).encode()).hexdigest(), self._column_names)
 
 
 def iter_local_records(path: Path) -> Iterator[dict[str, Any]]:
