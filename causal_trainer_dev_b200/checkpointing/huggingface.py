@@ -87,9 +87,13 @@ def expected_model_layout(cfg: ModelConfig, dtype: torch.dtype) -> dict[str, tup
 # --------------------------------------------------------------------------------------- loading
 def _check_source(index: st.SafeTensorIndex, cfg: ModelConfig) -> None:
     want = expected_model_layout(cfg, torch.bfloat16)
-    missing = [k for k in want if k not in index.where]
-    if missing:
-        raise KeyError(f"checkpoint is missing tensors: {missing[:4]}{'...' if len(missing) > 4 else ''}")
+    missing = sorted(k for k in want if k not in index.where)
+    unexpected = sorted(k for k in index.where if k not in want)
+    if missing or unexpected:
+        # an extra tensor (an output-projection bias, a tied or renamed head) is a different architecture
+        raise ValueError("checkpoint tensors do not exactly match the supported architecture; "
+                         f"missing {missing[:4]}{'...' if len(missing) > 4 else ''}, "
+                         f"unexpected {unexpected[:4]}{'...' if len(unexpected) > 4 else ''}")
     for key, (_, shape) in want.items():
         got = index.info(key).shape
         if tuple(got) != tuple(shape):
@@ -275,12 +279,17 @@ class TensorSource:
 def copy_hf_assets(source: Path | None, destination: Path, cfg: ModelConfig, dtype: torch.dtype) -> None:
     """``config.json`` (normalised, actual dtype) plus tokenizer files and chat templates."""
     destination.mkdir(parents=True, exist_ok=True)
-    config = cfg.to_dict()
+    # The source's config keeps its extra keys; every semantic field is rewritten from the model
+    # configuration.  Reading accepts the Transformers 5 spellings (``dtype``, ``rope_parameters``)
+    # but a full / merged checkpoint always goes back to the fixed source format
+    # (src/causal_trainer/checkpointing/huggingface.py:684-718).
+    config: dict[str, Any] = {}
     if source is not None and (source / "config.json").is_file():
-        original = json.loads((source / "config.json").read_text(encoding="utf-8"))
-        config = {**original, **{k: v for k, v in config.items() if k in original or k in ("torch_dtype",)}}
-    config["torch_dtype"] = TORCH_DTYPE_NAMES.get(dtype, "bfloat16")
+        config = json.loads((source / "config.json").read_text(encoding="utf-8"))
+    config.update(cfg.to_dict())
+    config.pop("rope_parameters", None)
     config.pop("dtype", None)
+    config["torch_dtype"] = TORCH_DTYPE_NAMES.get(dtype, "bfloat16")
     config.setdefault("architectures", ["LlamaForCausalLM"])
     (destination / "config.json").write_text(json.dumps(config, indent=2, sort_keys=True) + "\n", encoding="utf-8")
     if source is None:

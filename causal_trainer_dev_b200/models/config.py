@@ -23,7 +23,12 @@ _FAMILY_DEFAULTS = {
     "mistral": ("gpt-neox", False),
     "qwen2": ("gpt-neox", True),
     "qwen3": ("gpt-neox", False),
+    "glm": ("gpt-j", True),
+    "glm4": ("gpt-j", True),
 }
+# A config of any other model type follows the reference, whose single architecture pairs
+# adjacent channels (src/causal_trainer/modeling/config.py: rope_style defaults to "gpt-j").
+_OTHER_FAMILY = ("gpt-j", False)
 
 
 def _is_pos_int(value: Any) -> bool:
@@ -137,7 +142,7 @@ class ModelConfig:
                 norm["torch_dtype"] = norm["dtype"]
             elif "torch_dtype" not in norm:
                 norm["torch_dtype"] = None
-        family = _FAMILY_DEFAULTS.get(str(norm.get("model_type", "llama")), ("gpt-neox", False))
+        family = _FAMILY_DEFAULTS.get(str(norm.get("model_type", "llama")), _OTHER_FAMILY)
         norm.setdefault("rope_style", family[0])
         norm.setdefault("attention_bias", family[1])
         if "head_dim" not in norm or norm["head_dim"] is None:

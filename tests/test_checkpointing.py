@@ -143,3 +143,67 @@ def test_optimizer_state_roundtrip_and_pruning(tmp_path):
     _export(out, "checkpoint-9", step=9)
     removed = bundles.prune_periodic_exports(out, 2, "sig")
     assert [p.name for p in removed] == ["checkpoint-3"] and (out / "checkpoint-9").is_dir()
+
+
+def test_export_normalises_a_v5_config_and_copies_named_chat_templates(tmp_path):
+    """Reading accepts the Transformers 5 spellings; a merged checkpoint returns to the fixed source format."""
+    import json
+
+    import torch
+
+    from causal_trainer_dev_b200.checkpointing import huggingface as hfio
+    from causal_trainer_dev_b200.models.config import ModelConfig, preset
+
+    source, destination = tmp_path / "source", tmp_path / "destination"
+    (source / "chat_templates").mkdir(parents=True)
+    (source / "tokenizer.json").write_text("{}", encoding="utf-8")
+    (source / "chat_templates" / "tool_use.jinja").write_text("tool template", encoding="utf-8")
+    raw = {**preset("tiny").to_dict(), "custom_note": "kept"}
+    for key in ("torch_dtype", "rope_theta", "partial_rotary_factor", "rope_scaling"):
+        raw.pop(key)
+    raw["dtype"] = "float32"
+    raw["rope_parameters"] = {"rope_type": "default", "rope_theta": 1_000_000.0, "partial_rotary_factor": 0.5}
+    (source / "config.json").write_text(json.dumps(raw), encoding="utf-8")
+    cfg = ModelConfig.from_dict(raw)
+    assert cfg.rope_theta == 1_000_000.0 and cfg.partial_rotary_factor == 0.5 and cfg.torch_dtype == "float32"
+    hfio.copy_hf_assets(source, destination, cfg, torch.bfloat16)
+    written = json.loads((destination / "config.json").read_text(encoding="utf-8"))
+    assert "dtype" not in written and "rope_parameters" not in written
+    assert written["torch_dtype"] == "bfloat16"                      # the dtype of the tensors actually written
+    assert written["rope_scaling"] is None and written["rope_theta"] == 1_000_000.0
+    assert written["partial_rotary_factor"] == 0.5 and written["custom_note"] == "kept"
+    assert (destination / "tokenizer.json").is_file()
+    assert (destination / "chat_templates" / "tool_use.jinja").read_text(encoding="utf-8") == "tool template"
+
+
+def test_model_load_rejects_tensors_outside_the_architecture(tmp_path):
+    import torch
+
+    from causal_trainer_dev_b200.checkpointing import huggingface as hfio
+    from causal_trainer_dev_b200.checkpointing import safetensors_io as st
+    from causal_trainer_dev_b200.models.config import preset
+    from causal_trainer_dev_b200.models.params import ModelParams
+
+    cfg = preset("tiny", num_hidden_layers=1)
+    params = ModelParams.init_random(cfg, seed=0, dtype=torch.float32)
+    tensors = {name: params.tensor(name).clone() for name in params.hf_names()}
+    tensors["model.layers.0.self_attn.o_proj.bias"] = torch.zeros(cfg.hidden_size)
+    st.save_file(tensors, tmp_path / "model.safetensors")
+    with pytest.raises(ValueError, match="do not exactly match.*unexpected.*o_proj.bias"):
+        hfio.load_parameters(tmp_path, ModelParams(cfg, torch.float32, "cpu"))
+    del tensors["model.layers.0.self_attn.o_proj.bias"], tensors["model.norm.weight"]
+    st.save_file(tensors, tmp_path / "model.safetensors")
+    with pytest.raises(ValueError, match="do not exactly match.*missing.*model.norm.weight"):
+        hfio.load_parameters(tmp_path, ModelParams(cfg, torch.float32, "cpu"))
+
+
+def test_rope_pairing_default_follows_the_model_family():
+    from causal_trainer_dev_b200.models.config import ModelConfig, preset
+
+    raw = preset("tiny").to_dict()
+    del raw["rope_style"]
+    assert ModelConfig.from_dict({**raw, "model_type": "llama"}).rope_style == "gpt-neox"
+    assert ModelConfig.from_dict({**raw, "model_type": "opaque-metadata"}).rope_style == "gpt-j"
+    assert ModelConfig.from_dict({**raw, "model_type": "opaque-metadata", "rope_style": "gpt-neox"}).rope_style == "gpt-neox"
+    with pytest.raises(ValueError, match="rope_style"):
+        ModelConfig.from_dict({**raw, "rope_style": "llama"})
