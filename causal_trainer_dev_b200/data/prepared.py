@@ -307,13 +307,16 @@ def validate_prepared_batch(columns: Mapping[str, Any], *, max_sequence_length: 
             raise ValueError("prepared assistant_masks must contain only 0/1 values")
         if (am[mask == 0] != 0).any():
             raise ValueError("prepared assistant_masks must be zero outside the attention mask")
-    # a segment id may not come back after another run
+    # a segment id may not come back after its run ended, be it at another segment or at padding
     for r in range(rows):
-        s = seg[r][seg[r] > 0]
-        if s.size:
-            runs = s[np.r_[True, s[1:] != s[:-1]]]
-            if len(set(runs.tolist())) != len(runs):
-                raise ValueError(f"prepared row {r} reuses a segment id after another segment")
+        row = seg[r]
+        if row.size:
+            runs = row[np.r_[True, row[1:] != row[:-1]]]
+            seen: set[int] = set()
+            for sid in runs[runs > 0].tolist():
+                if sid in seen:
+                    raise ValueError(f"prepared row {r} reuses segment_id={sid} after its contiguous run")
+                seen.add(sid)
     edge = (mask[:, :-1] == 1) & (mask[:, 1:] == 1) & (seg[:, :-1] == seg[:, 1:]) & (w[:, 1:] > 0)
     if rows and not edge.any(axis=1).all():
         bad = int(np.flatnonzero(~edge.any(axis=1))[0])

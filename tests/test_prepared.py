@@ -84,10 +84,16 @@ def test_semantic_row_validation():
         ("input_ids", [[5, 6, 11, 0]], "max_token_id"), ("attention_mask", [[1, 2, 1, 0]], "0/1"),
         ("segment_ids", [[1, 1, 0, 0]], "positive exactly"), ("position_ids", [[0, 1, 2, 3]], "zero outside"),
         ("loss_weights", [[1.0, 1.0, 1.0, 0.5]], "zero outside"), ("loss_weights", [[1.0, 0.0, 0.0, 0.0]], "no positive-weight"),
-        ("segment_ids", [[1, 2, 1, 0]], "reuses a segment id"),
+        ("segment_ids", [[1, 2, 1, 0]], "reuses segment_id=1 after its contiguous run"),
     ]:
         with pytest.raises(ValueError, match=msg):
             P.validate_prepared_batch({**ok, field: value}, **kw)
+    # a run that padding interrupts has ended too; ids need not be monotonic as long as they are not reused
+    gap = dict(input_ids=[[5, 6, 0, 7]], attention_mask=[[1, 1, 0, 1]], position_ids=[[0, 1, 0, 0]],
+               segment_ids=[[1, 1, 0, 1]], loss_weights=[[0.0, 1.0, 0.0, 0.0]])
+    with pytest.raises(ValueError, match="reuses segment_id=1 after its contiguous run"):
+        P.validate_prepared_batch(gap, **kw)
+    P.validate_prepared_batch({**gap, "segment_ids": [[3, 3, 0, 2]]}, **kw)
 
 
 def test_prepared_streaming_envelopes(tmp_path):
