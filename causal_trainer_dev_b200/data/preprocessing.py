@@ -216,7 +216,8 @@ class Preprocessor:
             tools = [json.loads(t) if isinstance(t, str) else t for t in tools]
         opts = dict(chat_template_kwargs or {})
         # Spans are recovered on the untruncated rendering; all fields are cut together afterwards.
-        opts.update(tokenize=True, return_dict=True, return_assistant_tokens_mask=mode is not None,
+        opts.update(tokenize=True, return_dict=True, return_attention_mask=True,
+                    return_assistant_tokens_mask=mode is not None,
                     truncation=mode is None, max_length=None if mode is not None else limit)
         if tools is not None:
             opts["tools"] = tools
