@@ -112,15 +112,18 @@ FLAGS: tuple[Flag, ...] = (
     Flag("attention_dense_prefix_layers", int, 0, "Leading layers kept dense."),
     Flag("attention_dense_suffix_layers", int, 0, "Trailing layers kept dense."),
     Flag("attention_dense_after_step", int, None, "Use dense attention from this zero-based optimizer step."),
-    Flag("block_size_q", int, None, "Query block size (auto: 128 below 131072 tokens, 256, 512, then 1024)."),
+    Flag("block_size_q", int, None, "Query block size (auto: 128 below 131072 tokens, 256 below 262144, 512 below "
+         "524288, 1024 from there on)."),
     Flag("block_size_k", int, None, "Key block size (same automatic ladder)."),
     # ---- loss / memory ----
     Flag("loss_token_budget", int, 128, "Maximum local token rows of a chunked-logits slab."),
     Flag("loss_implementation", str, "auto",
          "cut: projection-fused kernels; pallas: chunked logits; xla: PyTorch oracle; auto: cut.",
          choices=("auto", "xla", "pallas", "cut")),
-    Flag("mlp_chunk_size", int, None, "Per-sequence MLP tile; auto 1024 for full training at 4096 <= S < 131072."),
-    Flag("scan_layers", "tribool", None, "Layer-loop representation flag kept for command compatibility."),
+    Flag("mlp_chunk_size", int, None, "Per-sequence MLP tile; auto: 1024 for full-parameter training at contexts of "
+         "4096 to 131071 tokens, off otherwise and always off for LoRA and sequence-parallel runs."),
+    Flag("scan_layers", "tribool", None, "Layer-loop representation flag kept for command compatibility (auto: on "
+         "for full-parameter training at contexts of at least 524288 tokens; part of the resume identity)."),
     Flag("projection_chunk_size", int, 0, "SP-local token rows per projection tile; 0 disables."),
     Flag("remat_group_size", int, 1, "Layers per rematerialized group."),
     Flag("cut_chunk_size", int, 0, "Local token rows per Cut loss chunk; 0 keeps the default."),
