@@ -123,7 +123,8 @@ FLAGS: tuple[Flag, ...] = (
     Flag("mlp_chunk_size", int, None, "Per-sequence MLP tile; auto: 1024 for full-parameter training at contexts of "
          "4096 to 131071 tokens, off otherwise and always off for LoRA and sequence-parallel runs."),
     Flag("scan_layers", "tribool", None, "Layer-loop representation flag kept for command compatibility (auto: on "
-         "for full-parameter training at contexts of at least 524288 tokens; part of the resume identity)."),
+         "for full-parameter training at contexts of at least 524288 tokens, and for single-row bf16 runs at 131072 "
+         "tokens, 262144 with MoBA; part of the resume identity)."),
     Flag("projection_chunk_size", int, 0, "SP-local token rows per projection tile; 0 disables."),
     Flag("remat_group_size", int, 1, "Layers per rematerialized group."),
     Flag("cut_chunk_size", int, 0, "Local token rows per Cut loss chunk; 0 keeps the default."),
