@@ -206,23 +206,27 @@ def find_latest_checkpoint(output_dir: str | Path, expected_signature: str, *,
 
 
 def resume_action(checkpoint: ResumeCheckpoint | None, *, output_dir: Path, total_steps: int) -> str:
-    """``start`` | ``continue`` | ``finalize`` | ``complete``; never silently resets training state
-    (src/causal_trainer/training/runner.py:573-600)."""
+    """What a launch does with the newest valid checkpoint: ``start`` (none), ``continue`` (partial run
+    with optimizer state), ``finalize`` (all steps done but only in a periodic directory) or
+    ``complete`` (nothing left to do).  Anything that would silently reset training state is an error
+    (decision table of src/causal_trainer/training/runner.py:573-600)."""
     if checkpoint is None:
         return "start"
-    if checkpoint.training_complete:
-        if checkpoint.path != output_dir:
+    at_root = checkpoint.path == output_dir
+    if checkpoint.training_complete:        # a stream that ended before its estimated horizon
+        if not at_root:
             raise ValueError("a completed streaming checkpoint must be stored at output_dir")
         return "complete"
     if checkpoint.total_steps != total_steps:
         raise ValueError(f"checkpoint total_steps={checkpoint.total_steps} does not match current plan {total_steps}")
-    if checkpoint.global_step < total_steps and not checkpoint.has_optimizer_state:
+    finished = checkpoint.global_step == total_steps
+    if finished:
+        return "complete" if at_root else "finalize"
+    if not checkpoint.has_optimizer_state:
         raise ValueError(
             "the latest checkpoint does not contain optimizer state, so exact continuation is impossible; optimizer "
             "state must have been saved before the interruption with --save_optimizer_state True, and enabling it "
             "only now cannot repair this checkpoint")
-    if checkpoint.global_step == total_steps:
-        return "complete" if checkpoint.path == output_dir else "finalize"
     return "continue"
 
 
