@@ -115,11 +115,20 @@ def _optimizer_state_valid(path: Path, step: int, checkpoint_id: str) -> bool:
         tensors, meta, _ = st.read_header(d / "state.safetensors")
     except (OSError, ValueError):
         return False
-    if meta.get("checkpoint_id") != checkpoint_id or manifest.get("tensor_count") != len(tensors):
+    entries = manifest.get("tensors")
+    if meta.get("checkpoint_id") != checkpoint_id or not isinstance(entries, list) \
+            or manifest.get("tensor_count") != len(tensors) or len(entries) != len(tensors):
         return False
-    for e in manifest.get("tensors", []):
+    fingerprint = hashlib.sha256(json.dumps(entries, separators=(",", ":"), sort_keys=True).encode("utf-8")).hexdigest()
+    if manifest.get("layout_fingerprint") != fingerprint:
+        return False
+    for e in entries:
+        if not isinstance(e, dict):
+            return False
         info = tensors.get(e.get("key"))
-        if info is None or info.dtype != e.get("dtype") or list(info.shape) != e.get("shape"):
+        # the manifest spells dtypes the numpy way ("int32"); the safetensors header says "I32"
+        if info is None or e.get("dtype") not in (info.dtype, st.PLAIN_DTYPE_NAMES.get(info.dtype)) \
+                or list(info.shape) != e.get("shape"):
             return False
     return True
 

@@ -352,8 +352,8 @@ def export_hf_checkpoint(destination: str | os.PathLike[str], source: TensorSour
 
 # --------------------------------------------------------------------------------------- optimizer state
 def layout_fingerprint(entries: list[dict[str, Any]]) -> str:
-    payload = [[e["path"], e["dtype"], e["shape"]] for e in entries]
-    return hashlib.sha256(json.dumps(payload, separators=(",", ":")).encode()).hexdigest()
+    """SHA-256 of the compact, key-sorted JSON of the manifest's tensor entries."""
+    return hashlib.sha256(json.dumps(entries, separators=(",", ":"), sort_keys=True).encode("utf-8")).hexdigest()
 
 
 def export_optimizer_checkpoint(destination: str | os.PathLike[str], state: list[tuple[str, torch.Tensor]], *,
@@ -369,7 +369,8 @@ def export_optimizer_checkpoint(destination: str | os.PathLike[str], state: list
     out.mkdir(parents=True, exist_ok=True)
     tensors = {f"state/{i:06d}": t.detach().cpu() for i, (_, t) in enumerate(state)}
     st.save_file(tensors, out / "state.safetensors", {"format": "pt", "checkpoint_id": checkpoint_id})
-    entries = [{"dtype": st.DTYPE_NAMES[t.dtype], "file": "state.safetensors", "key": f"state/{i:06d}", "ordinal": i,
+    entries = [{"dtype": st.PLAIN_DTYPE_NAMES[st.DTYPE_NAMES[t.dtype]], "file": "state.safetensors",
+                "key": f"state/{i:06d}", "ordinal": i,
                 "path": path, "shape": list(t.shape)} for i, (path, t) in enumerate(state)]
     manifest = {
         "format": "optimizer-state-safetensors", "format_version": 1, "global_step": int(global_step),

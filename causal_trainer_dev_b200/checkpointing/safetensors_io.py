@@ -29,6 +29,11 @@ DTYPES: dict[str, torch.dtype] = {
     "BOOL": torch.bool,
 }
 DTYPE_NAMES = {v: k for k, v in DTYPES.items()}
+# numpy-style spellings used by the optimizer-state manifest (src/causal_trainer/checkpointing/huggingface.py:1517-1600)
+PLAIN_DTYPE_NAMES = {
+    "BF16": "bfloat16", "F16": "float16", "F32": "float32", "F64": "float64", "I64": "int64", "I32": "int32",
+    "I16": "int16", "I8": "int8", "U8": "uint8", "BOOL": "bool",
+}
 
 
 def dtype_size(name: str) -> int:
@@ -77,7 +82,7 @@ def read_header(path: str | os.PathLike[str]) -> tuple[dict[str, TensorInfo], di
             dt, shape, (b0, b1) = entry["dtype"], tuple(int(x) for x in entry["shape"]), entry["data_offsets"]
         except (KeyError, TypeError, ValueError) as exc:
             raise ValueError(f"{path}: malformed entry for {name!r}") from exc
-        if dt not in DTYPES:
+        if not isinstance(dt, str) or dt not in DTYPES:
             raise ValueError(f"{path}: unsupported dtype {dt!r} for {name!r}")
         count = 1
         for s in shape:

@@ -145,6 +145,47 @@ def test_optimizer_state_roundtrip_and_pruning(tmp_path):
     assert [p.name for p in removed] == ["checkpoint-3"] and (out / "checkpoint-9").is_dir()
 
 
+def _refresh_inventory(path, optimizer):
+    mpath = path / bundles.MANIFEST_NAME
+    m = json.loads(mpath.read_text(encoding="utf-8"))
+    files = bundles.artifact_files(path, m["artifact_kind"], optimizer)
+    m["artifact_sizes"] = {str(f.relative_to(path)): f.stat().st_size for f in files}
+    m["artifact_digests"] = {str(f.relative_to(path)): bundles.file_sha256(f) for f in files}
+    mpath.write_text(json.dumps(m), encoding="utf-8")
+
+
+def test_optimizer_manifest_conventions_and_tampering(tmp_path):
+    """The optimizer manifest spells dtypes the numpy way and carries a fingerprint of its entries; a
+    manifest whose fingerprint does not match, or a model header with a malformed dtype, makes the
+    bundle corrupt rather than silently usable (also when the artifact inventory was refreshed)."""
+    out = tmp_path / "run"
+    _, _, d = _export(out, "checkpoint-4", step=4, optimizer=True)
+    mpath = d / "optimizer" / "manifest.json"
+    manifest = json.loads(mpath.read_text(encoding="utf-8"))
+    assert [e["dtype"] for e in manifest["tensors"]] == ["int64", "bfloat16", "bfloat16"]
+    assert manifest["layout_fingerprint"] == hfio.layout_fingerprint(manifest["tensors"])
+    assert bundles.find_latest_checkpoint(out, "sig").global_step == 4
+    manifest["layout_fingerprint"] = "0" * 64
+    mpath.write_text(json.dumps(manifest), encoding="utf-8")
+    _refresh_inventory(d, True)
+    with pytest.raises(ValueError, match="corrupt completed checkpoints"):
+        bundles.find_latest_checkpoint(out, "sig")
+    # a header whose dtype is not even a string
+    out2 = tmp_path / "run2"
+    _, _, d2 = _export(out2, "checkpoint-4", step=4)
+    model = d2 / "model.safetensors"
+    payload = model.read_bytes()
+    hlen = int.from_bytes(payload[:8], "little")
+    header = json.loads(payload[8:8 + hlen].decode("utf-8").rstrip(" "))
+    header["model.norm.weight"]["dtype"] = []
+    enc = json.dumps(header, separators=(",", ":")).encode("utf-8")
+    assert len(enc) <= hlen
+    model.write_bytes(payload[:8] + enc + b" " * (hlen - len(enc)) + payload[8 + hlen:])
+    _refresh_inventory(d2, False)
+    with pytest.raises(ValueError, match="corrupt completed checkpoints"):
+        bundles.find_latest_checkpoint(out2, "sig")
+
+
 def test_export_normalises_a_v5_config_and_copies_named_chat_templates(tmp_path):
     """Reading accepts the Transformers 5 spellings; a merged checkpoint returns to the fixed source format."""
     import json
