@@ -20,7 +20,7 @@ from pathlib import Path
 from typing import Any
 
 
-from .data.pipeline import (contiguous_shard_bounds, load_training_split, packed_dataset_to_arrays,
+from .data.pipeline import (load_training_split, packed_dataset_to_arrays, select_process_shard,
                             prepare_training_dataset)
 from .data.prepared import (PREPARED_MANIFEST_FILENAME, PreparedDatasetManifest, PreparedShard, field_names, sha256_file,
                             validate_prepared_batch, write_prepared_manifest, write_prepared_shard)
@@ -210,7 +210,7 @@ def tokenizer_digest(directory: Path) -> tuple[str, tuple[str, ...]]:
 def prepare_dataset(a: PrepareArguments) -> PreparedDatasetManifest:
     out = a.output_dir
     if out.exists() and any(out.iterdir()):
-        raise FileExistsError(f"output_dir must be empty or absent: {out}")
+        raise ValueError(f"output_dir must be empty or absent: {out}")
     tok_dir = resolve_tokenizer_directory(a)
     tokenizer = TrainingTokenizer.from_directory(tok_dir)
     tok_sha, tok_files = tokenizer_digest(tok_dir)
@@ -226,17 +226,17 @@ def prepare_dataset(a: PrepareArguments) -> PreparedDatasetManifest:
     names = field_names(a.uses_assistant_loss_mask)
     try:
         for index in range(a.num_shards):
-            start, stop = contiguous_shard_bounds(total, index, a.num_shards)
+            part, start = select_process_shard(source, process_index=index, process_count=a.num_shards)
             rows = prepare_training_dataset(
-                source[start:stop] if hasattr(source, "records") else source.select(range(start, stop)),
-                tokenizer, dataset_text_field=a.dataset_text_field, max_sequence_length=a.max_sequence_length,
+                part, tokenizer, dataset_text_field=a.dataset_text_field, max_sequence_length=a.max_sequence_length,
                 packing=a.packing, packing_batch_size=a.packing_batch_size, pad_token_id=pad_id,
                 assistant_only_loss=a.assistant_only_loss, last_assistant_only_loss=a.last_assistant_only_loss,
                 endprompt=endprompt_settings(a), num_proc=a.preprocessing_num_workers, example_index_offset=start,
                 allow_empty=True,
             )
             if not rows:
-                continue
+                raise ValueError(f"prepared shard {index} is empty; reduce num_shards or remove source rows that "
+                                 "are filtered by the loss settings")
             for r in rows:  # final weights are part of the artifact
                 if "loss_weights" not in r:
                     src = "assistant_masks" if a.uses_assistant_loss_mask else "attention_mask"
@@ -253,8 +253,6 @@ def prepare_dataset(a: PrepareArguments) -> PreparedDatasetManifest:
             rel = f"data/shard-{index:05d}-of-{a.num_shards:05d}.parquet"
             n = write_prepared_shard(cols, out / rel)
             shards.append(PreparedShard(rel, n, sha256_file(out / rel)))
-        if not shards:
-            raise ValueError("preprocessing produced no trainable rows")
         manifest = PreparedDatasetManifest(
             max_sequence_length=a.max_sequence_length, split=a.dataset_split, shards=tuple(shards),
             tokenizer={"name_or_path": a.tokenizer_name_or_path, "revision": a.tokenizer_revision, "sha256": tok_sha,
@@ -262,16 +260,20 @@ def prepare_dataset(a: PrepareArguments) -> PreparedDatasetManifest:
             source={"dataset_name": a.dataset_name, "dataset_config_name": a.dataset_config_name,
                     "dataset_revision": a.dataset_revision, "dataset_split": a.dataset_split, "rows": total,
                     "fingerprint": getattr(source, "_fingerprint", None)},
+            # same keys as the manifests written by the reference's prepare command
+            # (src/causal_trainer/prepare.py:379-400); never the access token
             preprocessing={
                 "dataset_text_field": a.dataset_text_field, "packing": a.packing,
                 "packing_batch_size": a.packing_batch_size, "assistant_only_loss": a.assistant_only_loss,
-                "last_assistant_only_loss": a.last_assistant_only_loss, "endprompt_enable": a.endprompt_enable,
-                "endprompt_logical_length": a.effective_endprompt_logical_length if a.endprompt_enable else None,
-                "endprompt_logical_length_min": a.effective_endprompt_logical_length_min if a.endprompt_enable else None,
-                "endprompt_prompts": list(a.endprompt_prompt_texts) if a.endprompt_enable else None,
-                "endprompt_prompt_loss_weight": a.endprompt_prompt_loss_weight if a.endprompt_enable else None,
-                "endprompt_context_loss_weight": a.endprompt_context_loss_weight if a.endprompt_enable else None,
-                "num_shards": a.num_shards,
+                "last_assistant_only_loss": a.last_assistant_only_loss,
+                "preprocessing_num_workers": a.preprocessing_num_workers, "num_shards": a.num_shards,
+                "endprompt": None if not a.endprompt_enable else {
+                    "logical_length_min": a.effective_endprompt_logical_length_min,
+                    "logical_length_max": a.effective_endprompt_logical_length,
+                    "prompts": list(a.endprompt_prompt_texts),
+                    "prompt_loss_weight": a.endprompt_prompt_loss_weight,
+                    "context_loss_weight": a.endprompt_context_loss_weight,
+                },
             },
             max_token_id=max_token, max_position_id=max_position,
             uses_assistant_loss_mask=a.uses_assistant_loss_mask,

@@ -40,7 +40,7 @@ def test_prepare_cli_writes_manifest_last_and_valid_shards(tmp_path):
 
 def test_output_dir_must_be_empty_and_failures_clean_up(tmp_path):
     _, out = _prepare(tmp_path)
-    with pytest.raises(FileExistsError):
+    with pytest.raises(ValueError, match="must be empty"):
         _prepare(tmp_path)
     bad = tmp_path / "bad"
     tok = tmp_path / "tok"
@@ -100,3 +100,24 @@ def test_prepared_streaming_envelopes(tmp_path):
     manifest, out = _prepare(tmp_path)
     env = list(P.iter_prepared_streaming_batches(str(out), manifest, num_epochs=2, window_size=3))
     assert sum(e.is_epoch_end for e in env) == 2 and sum(e.source_examples for e in env) == 2 * manifest.total_rows
+
+
+def test_manifest_records_preprocessing_without_secrets_and_rejects_empty_shards(tmp_path):
+    manifest, out = _prepare(tmp_path, extra=("--endprompt_enable", "--endprompt_logical_length", "16",
+                                              "--endprompt_prompts", "go on", "--token", "do-not-serialize-me"))
+    pre = manifest.preprocessing
+    assert set(pre) == {"dataset_text_field", "packing", "packing_batch_size", "assistant_only_loss",
+                        "last_assistant_only_loss", "preprocessing_num_workers", "num_shards", "endprompt"}
+    assert pre["endprompt"] == {"logical_length_min": 16, "logical_length_max": 16, "prompts": ["go on"],
+                                "prompt_loss_weight": 0.1, "context_loss_weight": 1.0}
+    assert "do-not-serialize-me" not in (out / P.PREPARED_MANIFEST_FILENAME).read_text(encoding="utf-8")
+    # more shards than source rows: the empty one is an error and nothing stays behind
+    tok = tmp_path / "tok"
+    one = tmp_path / "one.jsonl"
+    one.write_text(json.dumps({"text": "w1 w2 w3"}))
+    target = tmp_path / "too_many"
+    args = prepare.parse_args(["--dataset_name", str(one), "--tokenizer_name_or_path", str(tok), "--output_dir",
+                               str(target), "--max_sequence_length", "16", "--num_shards", "3"])
+    with pytest.raises(ValueError, match="prepared shard 1 is empty"):
+        prepare.prepare_dataset(args)
+    assert not (target / P.PREPARED_MANIFEST_FILENAME).exists() and not (target / "data").exists()
