@@ -182,8 +182,12 @@ class MetricWindow:
         self.latest = dict(m.to_floats(), step=step)
 
     def drain(self) -> dict[str, float] | None:
-        while self.pending:
-            self._pop()
+        """Reads back the newest pending step only (the device finishes steps in order, so that one
+        read synchronises all of them) and drops the references to the older ones."""
+        if self.pending:
+            step, m = self.pending[-1]
+            self.pending.clear()
+            self.latest = dict(m.to_floats(), step=step)
         return self.latest
 
 

@@ -80,7 +80,8 @@ def test_metric_window_keeps_a_bounded_number_of_steps_in_flight():
         w.push(i, m)
     assert [m.read for m in ms] == [True, True, False, False]     # only the two newest are still pending
     assert w.latest == {"loss": 1.0, "step": 1}
-    assert w.drain() == {"loss": 3.0, "step": 3} and all(m.read for m in ms)
+    assert w.drain() == {"loss": 3.0, "step": 3} and not w.pending
+    assert [m.read for m in ms] == [True, True, False, True]     # only the newest pending step is read back
 
 
 def test_split_accumulation_reshapes_or_refuses():
