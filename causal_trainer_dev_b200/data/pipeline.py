@@ -184,11 +184,19 @@ def source_dataset_identity(dataset) -> bytes:
 
 
 def prepare_training_dataset(dataset, tokenizer, *, dataset_text_field: str, max_sequence_length: int, packing: bool,
-                             packing_batch_size: int, pad_token_id: int, assistant_only_loss: bool = False,
+                             packing_batch_size: int, pad_token_id: int | None = None, assistant_only_loss: bool = False,
                              last_assistant_only_loss: bool = False, endprompt: EndPromptSettings | None = None,
                              num_proc: int | None = None, example_index_offset: int = 0,
-                             allow_empty: bool = False) -> list[dict[str, list]]:
-    """Tokenise and pack (or pad) one process shard into fixed-length rows."""
+                             allow_empty: bool = False, preprocessing_num_workers: int | None = None
+                             ) -> list[dict[str, list]]:
+    """Tokenise and pack (or pad) one process shard into fixed-length rows
+    (``preprocessing_num_workers`` is the flag's own name for ``num_proc``)."""
+    if num_proc is None:
+        num_proc = preprocessing_num_workers
+    if pad_token_id is None:       # the tokenizer's own padding id, else its end-of-text id
+        pad_token_id = getattr(tokenizer, "pad_token_id", None)
+        if pad_token_id is None:
+            pad_token_id = getattr(tokenizer, "eos_token_id", None) or 0
     pre = Preprocessor(tokenizer, dataset_text_field, max_sequence_length, assistant_only_loss,
                        last_assistant_only_loss, endprompt)
     examples = pre.run(dataset, example_index_offset=example_index_offset, allow_empty=allow_empty,
@@ -202,27 +210,40 @@ def prepare_training_dataset(dataset, tokenizer, *, dataset_text_field: str, max
 
 
 def packed_dataset_to_arrays(rows: Sequence[Mapping[str, Sequence]], *, max_sequence_length: int,
-                             assistant_only_loss: bool = False, has_explicit_loss_weights: bool | None = None
-                             ) -> dict[str, np.ndarray]:
-    """Typed ``[rows, S]`` columns: model fields int32 (+ ``assistant_masks``), ``loss_weights`` float32."""
+                             assistant_only_loss: bool = False, last_assistant_only_loss: bool = False,
+                             has_explicit_loss_weights: bool | None = None) -> dict[str, np.ndarray]:
+    """Typed ``[rows, S]`` columns: model fields int32 (+ ``assistant_masks``) and always a float32
+    ``loss_weights`` column: the rows' own weights when they carry them (EndPrompt), else the assistant
+    mask in the assistant-loss modes, else the attention mask
+    (src/causal_trainer/data/pipeline.py:338-393)."""
+    if assistant_only_loss and last_assistant_only_loss:
+        raise ValueError("assistant_only_loss and last_assistant_only_loss are mutually exclusive")
+    use_assistant_mask = assistant_only_loss or last_assistant_only_loss
     names = list(MODEL_FIELDS)
-    if assistant_only_loss:
+    if use_assistant_mask:
         names.append("assistant_masks")
+    count = len(rows)
     if has_explicit_loss_weights is None:
-        has_explicit_loss_weights = bool(rows) and "loss_weights" in rows[0]
+        has_explicit_loss_weights = count > 0 and "loss_weights" in rows[0]
     if has_explicit_loss_weights:
         names.append("loss_weights")
     out: dict[str, np.ndarray] = {}
     for name in names:
         dtype = np.float32 if name == "loss_weights" else np.int32
-        col = np.zeros((len(rows), max_sequence_length), dtype=dtype)
-        for i, row in enumerate(rows):
+        col = np.zeros((count, max_sequence_length), dtype=dtype)
+        for i in range(count):
+            row = rows[i]
             if name not in row:
                 raise ValueError(f"packed row {i} is missing field {name!r}")
             if len(row[name]) != max_sequence_length:
                 raise ValueError(f"packed row {i} field {name!r} has length {len(row[name])}, expected {max_sequence_length}")
             col[i] = row[name]
         out[name] = col
+    if "loss_weights" not in out:
+        source = out["assistant_masks"] if use_assistant_mask else out["attention_mask"]
+        out["loss_weights"] = source.astype(np.float32, copy=True)
+    if not np.isfinite(out["loss_weights"]).all() or (out["loss_weights"] < 0).any():
+        raise ValueError("prepared loss_weights must be finite and non-negative")
     return out
 
 

@@ -50,8 +50,13 @@ def test_empty_process_shard_keeps_the_schema():
 def test_typed_columns_and_fixed_shapes_of_an_empty_shard():
     rows = [{"input_ids": [1, 2, 3], "attention_mask": [0, 1, 1], "position_ids": [0, 0, 1], "segment_ids": [0, 1, 1]}]
     cols = packed_dataset_to_arrays(rows, max_sequence_length=3)
-    assert set(cols) == {"input_ids", "attention_mask", "position_ids", "segment_ids"}
-    assert all(v.dtype == np.int32 and v.shape == (1, 3) for v in cols.values())
+    assert set(cols) == {"input_ids", "attention_mask", "position_ids", "segment_ids", "loss_weights"}
+    assert all(v.shape == (1, 3) for v in cols.values())
+    assert all(v.dtype == np.int32 for k, v in cols.items() if k != "loss_weights")
+    np.testing.assert_array_equal(cols["loss_weights"], [[0.0, 1.0, 1.0]])      # normal loss: the attention mask
+    masked = packed_dataset_to_arrays([{**rows[0], "assistant_masks": [0, 0, 1]}], max_sequence_length=3,
+                                      last_assistant_only_loss=True)
+    np.testing.assert_array_equal(masked["loss_weights"], [[0.0, 0.0, 1.0]])    # assistant modes: the assistant mask
     empty = packed_dataset_to_arrays([], max_sequence_length=5, assistant_only_loss=True, has_explicit_loss_weights=True)
     assert set(empty) == {"input_ids", "attention_mask", "position_ids", "segment_ids", "assistant_masks", "loss_weights"}
     assert all(v.shape == (0, 5) for v in empty.values()) and empty["loss_weights"].dtype == np.float32
