@@ -3,7 +3,7 @@
 The base model is frozen: every projection still runs on the tcgen05 GEMM (forward and input
 gradient), but no base weight gradient is computed and no gradient or optimizer memory exists for
 the base weights.  Each adapted projection adds the rank-``r`` path ``(x @ A) @ B`` (no alpha
-multiplier; src/causal_trainer/modeling/lora.py:1-9,156-200) to the slice of the fused output that
+multiplier; src/causal_trainer/modeling/lora.py:1-9,218-242) to the slice of the fused output that
 belongs to it (``q | k | v`` inside ``qkv``, ``gate | up`` inside ``gu``) and its backward
 
     t  = x @ A            dB += t^T @ dy
