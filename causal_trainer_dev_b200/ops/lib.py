@@ -70,13 +70,36 @@ def ptr(t: torch.Tensor | None) -> ctypes.c_void_p:
     return ctypes.c_void_p(0 if t is None else t.data_ptr())
 
 
+# Where a bounded device wait gave up: the SITE_* codes of ops/csrc/*.cu.
 _SITES = {
     0x0101: "gemm producer: stage never freed",
     0x0102: "gemm mma: operands never arrived",
     0x0103: "gemm mma: accumulator never drained",
     0x0104: "gemm epilogue: accumulator never completed",
-    0x0105: "gemm producer: B-ready flag never published",
+    0x0105: "gemm producer: gathered-operand flag never published",
     0x0106: "gemm producer: copy still in flight at teardown",
+    0x0107: "gemm: tile queue never advanced",
+    0x0201: "attention forward producer: K/V slot never freed",
+    0x0202: "attention forward mma: Q never arrived",
+    0x0203: "attention forward mma: K/V never arrived",
+    0x0204: "attention forward mma: P never published",
+    0x0205: "attention forward softmax: scores never completed",
+    0x0206: "attention forward softmax: P V never completed",
+    0x0301: "attention backward producer: streamed stage never freed",
+    0x0302: "attention backward mma: resident tiles never arrived",
+    0x0303: "attention backward mma: streamed block never arrived",
+    0x0304: "attention backward mma: P^T / dS never published",
+    0x0305: "attention backward compute: S / dP never completed",
+    0x0307: "attention backward compute: accumulators never completed",
+    0x0401: "fsdp reduce-scatter: a peer's gradients never arrived",
+    0x0402: "fsdp: flags never published",
+    0x0501: "tensor-parallel all-gather: a peer's rows never became ready",
+    0x0502: "tensor-parallel reduce: a peer's partial tiles never arrived",
+    0x0503: "vocabulary-parallel cross-entropy: a peer's statistics never arrived",
+    0x0801: "two-CTA gemm producer: stage never freed",
+    0x0802: "two-CTA gemm mma: operands never arrived",
+    0x0803: "two-CTA gemm mma: accumulator never drained",
+    0x0804: "two-CTA gemm epilogue: accumulator never completed",
 }
 
 
