@@ -23,7 +23,7 @@ import numpy as np
 
 from .batching import MODEL_FIELDS
 from .packing import pack_examples, pad_examples
-from .preprocessing import EndPromptSettings, Preprocessor
+from .preprocessing import EndPromptSettings, Preprocessor, RowTable
 
 LOCAL_SUFFIXES = {".json", ".jsonl", ".parquet", ".csv", ".tsv"}
 
@@ -43,6 +43,8 @@ class RecordList:
     def __getitem__(self, index):
         if isinstance(index, slice):
             return RecordList(self.records[index], f"{self._fingerprint}[{index.start}:{index.stop}]", self._column_names)
+        if isinstance(index, str):
+            return [r[index] for r in self.records]
         return self.records[index]
 
     def __iter__(self) -> Iterator[dict[str, Any]]:
@@ -51,6 +53,11 @@ class RecordList:
     @property
     def column_names(self) -> list[str]:
         return list(self._column_names)
+
+    @property
+    def cache_files(self) -> list:
+        """Always empty: records live in memory, nothing is spilled to Arrow cache files."""
+        return []
 
     def select(self, indices, keep_in_memory: bool = True) -> "RecordList":
         idx = list(indices)
@@ -90,6 +97,14 @@ def iter_local_records(path: Path) -> Iterator[dict[str, Any]]:
         raise ValueError(f"unsupported local dataset extension: {suffix}")
 
 
+def load_dataset(*args, **kwargs):
+    """``datasets.load_dataset``, imported on first use (the import is slow and only Hub ids need it);
+    a module-level name so that a caller (or a test) can substitute it."""
+    from datasets import load_dataset as impl
+
+    return impl(*args, **kwargs)
+
+
 def load_training_split(name: str, split: str, *, token: str | None = None, config_name: str | None = None,
                         revision: str | None = None, streaming: bool = False):
     """A local tabular file (materialised, or lazily iterated when ``streaming``) or a Hub dataset."""
@@ -104,8 +119,6 @@ def load_training_split(name: str, split: str, *, token: str | None = None, conf
         stat = path.stat()
         fp = hashlib.sha256(f"{path.resolve()}:{stat.st_size}:{stat.st_mtime_ns}".encode()).hexdigest()
         return RecordList(list(iter_local_records(path)), fp)
-    from datasets import load_dataset
-
     from ..hf_retry import retry_hf_call
 
     return retry_hf_call(lambda: load_dataset(name, config_name, split=split, token=token, revision=revision,
@@ -202,11 +215,11 @@ def prepare_training_dataset(dataset, tokenizer, *, dataset_text_field: str, max
     examples = pre.run(dataset, example_index_offset=example_index_offset, allow_empty=allow_empty,
                        num_workers=num_proc)
     if not examples:
-        return []
+        return RowTable()
     if packing:
-        return pack_examples(examples, max_length=max_sequence_length, pad_token_id=pad_token_id,
-                             packing_batch_size=packing_batch_size)
-    return pad_examples(examples, max_length=max_sequence_length, pad_token_id=pad_token_id)
+        return RowTable(pack_examples(examples, max_length=max_sequence_length, pad_token_id=pad_token_id,
+                                      packing_batch_size=packing_batch_size))
+    return RowTable(pad_examples(examples, max_length=max_sequence_length, pad_token_id=pad_token_id))
 
 
 def packed_dataset_to_arrays(rows: Sequence[Mapping[str, Sequence]], *, max_sequence_length: int,

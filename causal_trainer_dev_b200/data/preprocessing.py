@@ -23,6 +23,33 @@ from dataclasses import dataclass
 from typing import Any, Iterable, Mapping, Sequence
 
 TokenizedExample = dict[str, list]
+
+
+class RowTable(list):
+    """A list of row dictionaries that also answers the column-wise questions code written against
+    ``datasets.Dataset`` asks: ``table["input_ids"]`` is that column as a list, ``column_names`` the
+    keys of the rows, and ``cache_files`` is empty because rows are never spilled to Arrow files."""
+
+    def __init__(self, rows=(), columns: Sequence[str] | None = None):
+        super().__init__(rows)
+        self._columns = list(columns) if columns is not None else None   # the schema of an empty table
+
+    def __getitem__(self, index):
+        if isinstance(index, str):
+            return [row[index] for row in self]
+        if isinstance(index, slice):
+            return RowTable(super().__getitem__(index), self._columns)
+        return super().__getitem__(index)
+
+    @property
+    def column_names(self) -> list[str]:
+        if self._columns is not None:
+            return list(self._columns)
+        return list(self[0]) if len(self) else []
+
+    @property
+    def cache_files(self) -> list:
+        return []
 _ASSISTANT_KEYS = ("assistant_masks", "assistant_mask", "assistant_tokens_mask")
 _ALL_FILTERED = ("All examples were filtered out because none contained a valid positive-weight training target "
                  "within max_sequence_length. Increase the limit or filter/shorten the source data.")
@@ -353,7 +380,15 @@ def preprocess_records(records, tokenizer, *, dataset_text_field: str, max_seque
     """Functional face of :class:`Preprocessor` (accepts any iterable, ``datasets.Dataset`` included)."""
     pre = Preprocessor(tokenizer, dataset_text_field, max_sequence_length, assistant_only_loss,
                        last_assistant_only_loss, endprompt)
-    return pre.run(records, example_index_offset=example_index_offset, allow_empty=allow_empty, num_workers=num_workers)
+    # the output schema is fixed by the options, not inferred from the first row, so a shard whose
+    # rows were all filtered out still merges with its siblings (src/causal_trainer/data/preprocessing.py:827-836)
+    columns = ["input_ids", "attention_mask"]
+    if assistant_only_loss or last_assistant_only_loss:
+        columns.append("assistant_masks")
+    if endprompt is not None:
+        columns += ["position_ids", "loss_weights"]
+    return RowTable(pre.run(records, example_index_offset=example_index_offset, allow_empty=allow_empty,
+                            num_workers=num_workers), columns)
 
 
 preprocess_dataset = preprocess_records

@@ -168,14 +168,46 @@ def endprompt_settings(a) -> EndPromptSettings | None:
                              a.endprompt_prompt_texts, a.endprompt_prompt_loss_weight, a.endprompt_context_loss_weight)
 
 
+def snapshot_download(*args, **kwargs):
+    """``huggingface_hub.snapshot_download``, imported on first use; a module-level name so that a
+    caller (or a test) can substitute it."""
+    from huggingface_hub import snapshot_download as impl
+
+    return impl(*args, **kwargs)
+
+
+def HfApi(*args, **kwargs):  # noqa: N802 - keeps the Hub client's own name
+    """``huggingface_hub.HfApi``, imported on first use; substitutable like :func:`snapshot_download`."""
+    from huggingface_hub import HfApi as impl
+
+    return impl(*args, **kwargs)
+
+
+def publish_to_hub(a: "PrepareArguments", out: Path) -> None:
+    """Create the dataset repository (and the branch ``--hub-revision`` names, which an upload does
+    not create by itself), then upload manifest and shards in one commit
+    (src/causal_trainer/prepare.py:404-430)."""
+    from .hf_retry import retry_hf_call
+
+    api = HfApi()
+    retry_hf_call(lambda: api.create_repo(a.hub_repo_id, token=a.token, private=a.private, repo_type="dataset",
+                                          exist_ok=True), description=f"create dataset repo {a.hub_repo_id}")
+    if a.hub_revision is not None:
+        retry_hf_call(lambda: api.create_branch(repo_id=a.hub_repo_id, branch=a.hub_revision, token=a.token,
+                                                repo_type="dataset", exist_ok=True),
+                      description=f"create branch {a.hub_revision}")
+    retry_hf_call(lambda: api.upload_folder(repo_id=a.hub_repo_id, folder_path=str(out), path_in_repo="",
+                                            token=a.token, repo_type="dataset", revision=a.hub_revision,
+                                            commit_message="Upload prepared dataset"),
+                  description=f"upload prepared dataset to {a.hub_repo_id}")
+
+
 def resolve_tokenizer_directory(a: PrepareArguments) -> Path:
     local = Path(a.tokenizer_name_or_path).expanduser()
     if local.is_dir():
         return local.resolve()
     if local.exists():
         raise ValueError(f"tokenizer_name_or_path must be a directory, got {local}")
-    from huggingface_hub import snapshot_download
-
     from .hf_retry import retry_hf_call
 
     return Path(retry_hf_call(lambda: snapshot_download(a.tokenizer_name_or_path, repo_type="model",
@@ -285,14 +317,7 @@ def prepare_dataset(a: PrepareArguments) -> PreparedDatasetManifest:
         shutil.rmtree(out, ignore_errors=True)
         raise
     if a.hub_repo_id is not None:
-        from huggingface_hub import HfApi
-
-        from .hf_retry import retry_hf_call
-
-        api = HfApi(token=a.token)
-        retry_hf_call(lambda: api.create_repo(a.hub_repo_id, repo_type="dataset", private=a.private, exist_ok=True))
-        retry_hf_call(lambda: api.upload_folder(repo_id=a.hub_repo_id, repo_type="dataset", folder_path=str(out),
-                                                revision=a.hub_revision))
+        publish_to_hub(a, out)
     return manifest
 
 

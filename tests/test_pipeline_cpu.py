@@ -99,3 +99,15 @@ def test_datasets_without_a_trainable_target_are_rejected_not_dropped():
     columns["loss_weights"][0] = columns["attention_mask"][0]
     with pytest.raises(ValueError, match="row 0 has no positive-weight causal target.*will not silently drop it"):
         pad_packed_arrays_to_batch_multiple(columns, batch_multiple=2)
+
+
+def test_rows_answer_column_questions_like_a_dataset():
+    from causal_trainer_dev_b200.data.pipeline import RecordList
+    from causal_trainer_dev_b200.data.preprocessing import RowTable
+
+    rows = RowTable([{"input_ids": [1, 2]}, {"input_ids": [3]}])
+    assert rows["input_ids"] == [[1, 2], [3]] and rows[1] == {"input_ids": [3]}
+    assert rows.column_names == ["input_ids"] and rows.cache_files == [] and isinstance(rows[:1], RowTable)
+    assert RowTable().column_names == []
+    records = RecordList([{"text": "a"}, {"text": "b"}], "fp")
+    assert records["text"] == ["a", "b"] and records.cache_files == []

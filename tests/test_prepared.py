@@ -1,4 +1,5 @@
 import json
+from pathlib import Path
 
 import numpy as np
 import pytest
@@ -121,3 +122,47 @@ def test_manifest_records_preprocessing_without_secrets_and_rejects_empty_shards
     with pytest.raises(ValueError, match="prepared shard 1 is empty"):
         prepare.prepare_dataset(args)
     assert not (target / P.PREPARED_MANIFEST_FILENAME).exists() and not (target / "data").exists()
+
+
+def test_hub_upload_creates_repo_and_branch_before_uploading_every_shard(tmp_path, monkeypatch):
+    calls = []
+
+    class FakeApi:
+        def create_repo(self, *args, **kwargs):
+            calls.append(("create", args, kwargs))
+
+        def create_branch(self, **kwargs):
+            calls.append(("branch", (), kwargs))
+
+        def upload_folder(self, **kwargs):
+            folder = Path(kwargs["folder_path"])
+            assert (folder / P.PREPARED_MANIFEST_FILENAME).is_file()
+            assert len(list((folder / "data").glob("*.parquet"))) == 2
+            calls.append(("upload", (), kwargs))
+
+    monkeypatch.setattr(prepare, "HfApi", FakeApi)
+    _prepare(tmp_path, shards=2, extra=("--hub-repo-id", "org/prepared", "--hub-revision", "data-branch", "--private",
+                                        "--token", "secret"))
+    assert [c[0] for c in calls] == ["create", "branch", "upload"]
+    assert calls[0][1:] == (("org/prepared",), {"token": "secret", "private": True, "repo_type": "dataset",
+                                                "exist_ok": True})
+    assert calls[1][2] == {"repo_id": "org/prepared", "branch": "data-branch", "token": "secret",
+                           "repo_type": "dataset", "exist_ok": True}
+    assert calls[2][2]["revision"] == "data-branch" and calls[2][2]["repo_type"] == "dataset"
+
+
+def test_remote_tokenizer_download_fetches_tokenizer_files_only(tmp_path, monkeypatch):
+    tok = write_tokenizer(tmp_path / "downloaded")
+    calls = []
+
+    def fake_snapshot_download(*args, **kwargs):
+        calls.append((args, kwargs))
+        return str(tok)
+
+    monkeypatch.setattr(prepare, "snapshot_download", fake_snapshot_download)
+    args = prepare.parse_args(["--dataset-name", "source", "--tokenizer-name-or-path", "org/tokenizer",
+                               "--tokenizer-revision", "abc123", "--token", "secret", "--output-dir",
+                               str(tmp_path / "out")])
+    assert str(prepare.resolve_tokenizer_directory(args)) == str(tok)
+    assert calls == [(("org/tokenizer",), {"repo_type": "model", "revision": "abc123", "token": "secret",
+                                           "allow_patterns": list(prepare.TOKENIZER_GLOBS)})]

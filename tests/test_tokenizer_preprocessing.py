@@ -83,3 +83,19 @@ def test_endprompt_logical_lengths_and_weights(tok):
     logical = s.logical_length_for_row(3)
     assert ex["position_ids"] == [0, 1, 2, 3, 4, 5, logical - 2, logical - 1]
     assert ex["loss_weights"] == [1.0] * 6 + [0.1, 0.1]
+
+
+def test_output_schema_follows_the_options_even_when_every_row_is_filtered(tok):
+    from causal_trainer_dev_b200.data.preprocessing import preprocess_records
+
+    empty = preprocess_records([{"messages": MSGS}], tok, dataset_text_field="messages", max_sequence_length=4,
+                               assistant_only_loss=True, allow_empty=True)
+    assert len(empty) == 0 and empty.column_names == ["input_ids", "attention_mask", "assistant_masks"]
+    s = EndPromptSettings(16, 24, ("w9 w10",))
+    for kwargs in ({}, {"endprompt": s}):
+        rows = preprocess_records([{"text": "w1 w2 w3 w4 w5 w6 w7"}], tok, dataset_text_field="text",
+                                  max_sequence_length=8, **kwargs)
+        assert sorted(rows[0]) == sorted(rows.column_names)
+    rows = preprocess_records([{"messages": MSGS}], tok, dataset_text_field="messages", max_sequence_length=16,
+                              assistant_only_loss=True, endprompt=s)
+    assert sorted(rows[0]) == sorted(rows.column_names)
