@@ -78,6 +78,21 @@ def arguments_digest(args) -> bytes:
     return rt.digest_of(values)
 
 
+def resolve_loss_implementation(args, backend: str = "cuda", *, cut_supported: bool = True) -> str:
+    """The loss backend a run uses: ``auto`` is the cut cross-entropy GEMM epilogues (never materialised
+    logits) wherever they apply, else the chunked-logits kernels (``pallas``, the flag value kept from
+    src/causal_trainer/training/runner.py:331-346); an explicit choice is kept as given.  ``cut_supported``
+    is false on the paths that cannot run the fused epilogues (CPU, fp32 compute)."""
+    if backend not in ("cuda", "cpu"):
+        raise ValueError(f"this trainer runs on CUDA (or on the CPU oracle path), not on {backend!r}")
+    chosen = args.loss_implementation
+    if chosen == "auto":
+        chosen = "cut" if cut_supported else "pallas"
+    if getattr(args, "cut_chunk_size", 0) > 0 and (chosen != "cut" or not cut_supported):
+        raise ValueError("cut_chunk_size requires the cut loss backend on a path that supports it")
+    return chosen
+
+
 def prepared_streaming_limits(total_rows: int, effective_batch: int, epochs: float, max_steps: int
                               ) -> tuple[int, int | None]:
     """``(total optimizer steps, whole epochs or None)`` for a prepared artifact of known size."""

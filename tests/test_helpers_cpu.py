@@ -48,3 +48,23 @@ def test_single_process_host_collectives_are_identities():
 def test_mean_loss_guards_empty_batches():
     assert float(mean_loss(torch.tensor(6.0), torch.tensor(3.0))) == 2.0
     assert float(mean_loss(torch.tensor(0.0), torch.tensor(0.0))) == 0.0
+
+
+def test_loss_backend_resolution():
+    from causal_trainer_dev_b200.training.arguments import parse_args
+    from causal_trainer_dev_b200.training.runner import resolve_loss_implementation
+
+    base = ["--repo-id", "local-model", "--dataset-name", "local-data"]
+    for mode in ([], ["--lora", "True"], ["--lora", "True", "--lora-train-embed-and-lm-head", "True"]):
+        args = parse_args(base + mode)
+        assert resolve_loss_implementation(args) == "cut"
+        assert resolve_loss_implementation(args, cut_supported=False) == "pallas"
+    for explicit in ("cut", "pallas", "xla"):
+        args = parse_args(base + ["--loss-implementation", explicit])
+        assert resolve_loss_implementation(args, cut_supported=explicit != "cut") == explicit
+    chunked = parse_args(base + ["--cut-chunk-size", "4"])
+    assert resolve_loss_implementation(chunked) == "cut"
+    with pytest.raises(ValueError, match="cut_chunk_size"):
+        resolve_loss_implementation(chunked, cut_supported=False)
+    with pytest.raises(ValueError, match="CUDA"):
+        resolve_loss_implementation(chunked, "tpu")
