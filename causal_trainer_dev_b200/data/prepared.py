@@ -219,6 +219,21 @@ def write_prepared_manifest(manifest: PreparedDatasetManifest, path: str | Path)
     Path(path).write_text(manifest.to_json(), encoding="utf-8")
 
 
+def hf_hub_download(**kwargs):
+    """``huggingface_hub.hf_hub_download``, imported on first use; a module-level name so that a
+    caller (or a test) can substitute it."""
+    from huggingface_hub import hf_hub_download as impl
+
+    return impl(**kwargs)
+
+
+def HfApi(*args, **kwargs):  # noqa: N802 - keeps the Hub client's own name
+    """``huggingface_hub.HfApi``, imported on first use; substitutable like :func:`hf_hub_download`."""
+    from huggingface_hub import HfApi as impl
+
+    return impl(*args, **kwargs)
+
+
 def load_prepared_manifest(name: str, *, token: str | None = None, revision: str | None = None,
                            cache_dir: str | Path | None = None, filename: str = PREPARED_MANIFEST_FILENAME
                            ) -> PreparedDatasetManifest:
@@ -227,8 +242,6 @@ def load_prepared_manifest(name: str, *, token: str | None = None, revision: str
         return read_prepared_manifest(p)
     if p.is_dir():
         return read_prepared_manifest(p / filename)
-    from huggingface_hub import hf_hub_download
-
     from ..hf_retry import retry_hf_call
 
     return read_prepared_manifest(retry_hf_call(lambda: hf_hub_download(
@@ -240,8 +253,6 @@ def resolve_prepared_revision(name: str, *, token: str | None = None, revision: 
     """Pins a Hub reference to a commit once so manifest and shards cannot race."""
     if Path(name).expanduser().exists():
         return None
-    from huggingface_hub import HfApi
-
     commit = getattr(HfApi().dataset_info(repo_id=name, revision=revision, token=token), "sha", None)
     if not isinstance(commit, str) or not commit:
         raise RuntimeError("Hugging Face did not return a prepared dataset commit SHA")
@@ -364,36 +375,76 @@ def read_prepared_shard(path: str | Path, manifest: PreparedDatasetManifest, bat
                                       uses_assistant_loss_mask=manifest.uses_assistant_loss_mask)
 
 
-def _resolve_shard(name: str, shard: PreparedShard, token: str | None, revision: str | None) -> Path:
+def _resolve_shard(name: str, shard: PreparedShard, token: str | None, revision: str | None,
+                   cache_dir: str | Path | None = None) -> Path:
     root = Path(name).expanduser()
     if root.is_file():
         root = root.parent
     if root.is_dir():
         return root / shard.path
-    from huggingface_hub import hf_hub_download
-
     from ..hf_retry import retry_hf_call
 
     return Path(retry_hf_call(lambda: hf_hub_download(repo_id=name, filename=shard.path, repo_type="dataset",
-                                                      revision=revision, token=token),
+                                                      revision=revision, token=token,
+                                                      cache_dir=None if cache_dir is None else str(cache_dir)),
                               description=f"download {shard.path}"))
 
 
+def _verify_shard(path: Path, shard: PreparedShard) -> None:
+    actual = sha256_file(path)
+    if actual != shard.sha256:
+        raise RuntimeError(f"prepared shard checksum mismatch for {shard.path!r}: expected {shard.sha256}, "
+                           f"got {actual}")
+
+
+class PreparedRowStream:
+    """Lazy, re-iterable rows of every shard of a prepared artifact, in manifest order; each pass
+    validates what it reads and checks every shard's row count."""
+
+    def __init__(self, files: Sequence[Path], manifest: PreparedDatasetManifest):
+        self.files = list(files)
+        self.manifest = manifest
+
+    def __iter__(self) -> Iterator[dict[str, list]]:
+        for path, shard in zip(self.files, self.manifest.shards):
+            rows = 0
+            for batch in read_prepared_shard(path, self.manifest):
+                n = len(batch["input_ids"])
+                rows += n
+                for i in range(n):
+                    yield {k: v[i].tolist() for k, v in batch.items()}
+            if rows != shard.rows:
+                raise ValueError(f"prepared shard {shard.path} has {rows} rows, manifest says {shard.rows}")
+
+
 def load_prepared_dataset(name: str, manifest: PreparedDatasetManifest | None = None, *, token: str | None = None,
-                          revision: str | None = None, process_index: int | None = None,
-                          process_count: int | None = None) -> dict[str, np.ndarray]:
-    """Typed columns of this process's shard interval (all shards when no process is given)."""
+                          revision: str | None = None, streaming: bool = False, process_index: int | None = None,
+                          process_count: int | None = None, cache_dir: str | Path | None = None,
+                          verify_checksums: bool = True):
+    """Typed columns of this process's contiguous shard interval (all shards when no process is
+    given); only that interval is downloaded.  ``streaming`` selects every shard instead (each
+    process reproduces the same global stream), checks the checksums up front and returns a lazy
+    :class:`PreparedRowStream` (src/causal_trainer/data/prepared.py:665-790)."""
     if (process_index is None) != (process_count is None):
         raise ValueError("process_index and process_count must be provided together")
-    manifest = manifest or load_prepared_manifest(name, token=token, revision=revision)
+    manifest = manifest or load_prepared_manifest(name, token=token, revision=revision, cache_dir=cache_dir)
+    if not isinstance(manifest, PreparedDatasetManifest):
+        raise TypeError("manifest must be a PreparedDatasetManifest")
+    if streaming:
+        files = [_resolve_shard(name, shard, token, revision, cache_dir) for shard in manifest.shards]
+        if verify_checksums:
+            for path, shard in zip(files, manifest.shards):
+                _verify_shard(path, shard)
+        return PreparedRowStream(files, manifest)
     shards = manifest.shards if process_index is None else assigned_prepared_shards(
         manifest, process_index=process_index, process_count=process_count)
+    files = [_resolve_shard(name, shard, token, revision, cache_dir) for shard in shards]
+    if verify_checksums:
+        for path, shard in zip(files, shards):
+            _verify_shard(path, shard)
     names = field_names(manifest.uses_assistant_loss_mask)
     parts: dict[str, list[np.ndarray]] = {n: [] for n in names}
-    for shard in shards:
-        path = _resolve_shard(name, shard, token, revision)
-        if sha256_file(path) != shard.sha256:
-            raise RuntimeError(f"prepared shard {shard.path} does not match its manifest SHA-256")
+    for path, shard in zip(files, shards):
         rows = 0
         for batch in read_prepared_shard(path, manifest):
             rows += len(batch["input_ids"])
@@ -407,7 +458,8 @@ def load_prepared_dataset(name: str, manifest: PreparedDatasetManifest | None = 
 
 
 def iter_prepared_streaming_batches(name: str, manifest: PreparedDatasetManifest, *, num_epochs: int | None,
-                                    window_size: int = 1000, token: str | None = None, revision: str | None = None
+                                    window_size: int = 1000, token: str | None = None, revision: str | None = None,
+                                    cache_dir: str | Path | None = None, verify_checksums: bool = True
                                     ) -> Iterator[StreamingBatchEnvelope]:
     """Streams a prepared artifact shard by shard as packing-window envelopes (one source row = one record)."""
     if type(window_size) is not int or window_size <= 0:
@@ -418,9 +470,9 @@ def iter_prepared_streaming_batches(name: str, manifest: PreparedDatasetManifest
 
     for epoch in (itertools.count() if num_epochs is None else range(num_epochs)):
         for shard in manifest.shards:
-            path = _resolve_shard(name, shard, token, revision)
-            if sha256_file(path) != shard.sha256:
-                raise ValueError(f"prepared shard {shard.path} does not match its manifest SHA-256")
+            path = _resolve_shard(name, shard, token, revision, cache_dir)
+            if verify_checksums:
+                _verify_shard(path, shard)
             rows = 0
             for batch in read_prepared_shard(path, manifest, batch_rows=window_size):
                 n = len(batch["input_ids"])

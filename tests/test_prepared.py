@@ -58,7 +58,7 @@ def test_corrupt_shard_is_detected_by_digest(tmp_path):
     blob = bytearray(f.read_bytes())
     blob[len(blob) // 2] ^= 0xFF
     f.write_bytes(blob)
-    with pytest.raises(RuntimeError, match="SHA-256"):
+    with pytest.raises(RuntimeError, match="checksum mismatch"):
         P.load_prepared_dataset(str(out), manifest)
 
 
@@ -166,3 +166,53 @@ def test_remote_tokenizer_download_fetches_tokenizer_files_only(tmp_path, monkey
     assert str(prepare.resolve_tokenizer_directory(args)) == str(tok)
     assert calls == [(("org/tokenizer",), {"repo_type": "model", "revision": "abc123", "token": "secret",
                                            "allow_patterns": list(prepare.TOKENIZER_GLOBS)})]
+
+
+def test_hub_loading_downloads_only_this_process_interval(tmp_path, monkeypatch):
+    import dataclasses
+
+    manifest, out = _prepare(tmp_path, shards=5)
+    downloads = []
+
+    def fake_download(**kwargs):
+        assert kwargs["repo_id"] == "org/prepared" and kwargs["repo_type"] == "dataset"
+        assert kwargs["revision"] == "prepared-commit" and kwargs["token"] == "secret"
+        downloads.append(kwargs["filename"])
+        return str(out / kwargs["filename"])
+
+    monkeypatch.setattr(P, "hf_hub_download", fake_download)
+    columns = P.load_prepared_dataset("org/prepared", manifest, revision="prepared-commit", token="secret",
+                                      process_index=1, process_count=2)
+    assert downloads == [s.path for s in manifest.shards[3:]]
+    assert len(columns["input_ids"]) == sum(s.rows for s in manifest.shards[3:])
+    # a process past the last file downloads nothing and gets typed empty columns
+    downloads.clear()
+    empty = P.load_prepared_dataset("org/prepared", manifest, process_index=7, process_count=8)
+    assert downloads == [] and empty["input_ids"].shape == (0, 16) and empty["loss_weights"].dtype == np.float32
+    # streaming selects every file, and checks all checksums before the first row is read
+    downloads.clear()
+    stream = P.load_prepared_dataset("org/prepared", manifest, streaming=True, revision="prepared-commit", token="secret")
+    assert downloads == [s.path for s in manifest.shards]
+    assert sum(1 for _ in stream) == manifest.total_rows == sum(1 for _ in stream)
+    corrupt = dataclasses.replace(manifest, shards=(dataclasses.replace(manifest.shards[0], sha256="0" * 64),
+                                                    *manifest.shards[1:]))
+    for kwargs in ({"process_index": 0, "process_count": 2}, {"streaming": True}):
+        with pytest.raises(RuntimeError, match="checksum mismatch"):
+            P.load_prepared_dataset(str(out), corrupt, **kwargs)
+    P.load_prepared_dataset(str(out), corrupt, verify_checksums=False)
+
+
+def test_loading_rejects_values_above_the_manifest_maxima(tmp_path):
+    import dataclasses
+
+    manifest, out = _prepare(tmp_path, shards=1)
+    for field, match in (("max_token_id", "max_token_id"), ("max_position_id", "max_position_id")):
+        lowered = dataclasses.replace(manifest, **{field: 0})
+        with pytest.raises(ValueError, match=match):
+            P.load_prepared_dataset(str(out), lowered)
+        with pytest.raises(ValueError, match=match):
+            list(P.iter_prepared_streaming_batches(str(out), lowered, num_epochs=1))
+    wrong_rows = dataclasses.replace(manifest, shards=(dataclasses.replace(manifest.shards[0],
+                                                                           rows=manifest.shards[0].rows + 1),))
+    with pytest.raises(ValueError, match="rows, manifest says"):
+        list(P.iter_prepared_streaming_batches(str(out), wrong_rows, num_epochs=1))
