@@ -103,5 +103,40 @@ def causal_lm_loss(hidden_states: torch.Tensor, head: torch.Tensor, batch: dict[
     return linear_cross_entropy(hidden_states.reshape(b * s, d), head, targets.reshape(-1), weights.reshape(-1), **kw)
 
 
+def shifted_loss_mask(input_ids, attention_mask, segment_ids=None, assistant_mask=None, loss_mask=None, labels=None, *,
+                      ignore_index: int = -100) -> tuple[torch.Tensor, torch.Tensor]:
+    """``(targets, supervised)``: the shifted targets and a boolean mask of the positions that carry
+    any weight (src/causal_trainer/training/losses.py:88-109)."""
+    targets, weights = shifted_targets_and_weights(input_ids, attention_mask, segment_ids, assistant_mask, loss_mask,
+                                                   labels, ignore_index=ignore_index)
+    return targets, weights > 0
+
+
+def chunked_causal_lm_loss(hidden_states: torch.Tensor, lm_head: torch.Tensor, input_ids: torch.Tensor,
+                           attention_mask: torch.Tensor | None, segment_ids: torch.Tensor | None = None,
+                           assistant_mask: torch.Tensor | None = None, loss_weights: torch.Tensor | None = None, *,
+                           token_budget: int = 128, loss_implementation: str = "xla", cut_chunk_size: int = 0,
+                           prediction_targets: torch.Tensor | None = None,
+                           prediction_weights: torch.Tensor | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    """``(nll_sum, weight_sum)`` from separate tensors instead of a batch dictionary, without ever
+    holding full-sequence logits (src/causal_trainer/training/losses.py:152-231).  ``lm_head`` is
+    ``[vocab, hidden]`` (the Hugging Face orientation).  The shifted rule multiplies padding,
+    segment-boundary, assistant and fractional weights; explicit ``prediction_targets`` /
+    ``prediction_weights`` (aligned to hidden-state positions) replace it."""
+    if (prediction_targets is None) != (prediction_weights is None):
+        raise ValueError("prediction_targets and prediction_weights must be supplied together")
+    b, s, d = hidden_states.shape
+    if prediction_targets is not None:
+        targets, weights = aligned_targets_and_weights({"input_ids": input_ids, "prediction_targets": prediction_targets,
+                                                        "prediction_weights": prediction_weights})
+    else:
+        t, w = shifted_targets_and_weights(input_ids, attention_mask, segment_ids, assistant_mask, loss_weights)
+        targets = torch.cat([t, torch.zeros_like(t[:, :1])], dim=1)
+        weights = torch.cat([w, torch.zeros_like(w[:, :1])], dim=1)
+    return linear_cross_entropy(hidden_states.reshape(b * s, d), lm_head, targets.reshape(-1), weights.reshape(-1),
+                                implementation=loss_implementation, token_budget=token_budget,
+                                cut_chunk_size=cut_chunk_size)
+
+
 def mean_loss(nll_sum: torch.Tensor, token_count: torch.Tensor) -> torch.Tensor:
     return nll_sum / torch.clamp(token_count, min=1.0)

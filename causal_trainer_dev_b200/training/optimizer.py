@@ -43,6 +43,23 @@ def learning_rate_at(cfg: ScheduleConfig, step: int) -> float:
     return cfg.learning_rate * ((1.0 - alpha) * cosine + alpha)
 
 
+def build_learning_rate_schedule(name: str, start: float, end: float, total_steps: int, warmup_steps: int = 0):
+    """``step -> learning rate`` as a plain function, with the argument checks of
+    src/causal_trainer/training/optimizer.py:9-39 (``end`` is an absolute value; a one-step run may
+    name one warm-up step, which is then dropped)."""
+    if total_steps <= 0:
+        raise ValueError("total_steps must be positive")
+    if not 0 <= warmup_steps < total_steps:
+        if warmup_steps == total_steps == 1:
+            warmup_steps = 0
+        else:
+            raise ValueError("warmup_steps must be in [0, total_steps)")
+    if name not in ("cosine", "linear", "constant"):
+        raise ValueError(f"unsupported scheduler: {name}")
+    cfg = ScheduleConfig(float(start), float(end), name, int(warmup_steps), int(total_steps))
+    return lambda step: learning_rate_at(cfg, int(step))
+
+
 @dataclass(frozen=True)
 class AdamWConfig:
     weight_decay: float = 0.0

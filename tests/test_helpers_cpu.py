@@ -68,3 +68,41 @@ def test_loss_backend_resolution():
         resolve_loss_implementation(chunked, cut_supported=False)
     with pytest.raises(ValueError, match="CUDA"):
         resolve_loss_implementation(chunked, "tpu")
+
+
+def test_schedule_builder_and_tensor_level_loss_entry_points():
+    from causal_trainer_dev_b200.training.losses import causal_lm_loss, chunked_causal_lm_loss, shifted_loss_mask
+    from causal_trainer_dev_b200.training.optimizer import build_learning_rate_schedule
+
+    sched = build_learning_rate_schedule("cosine", 1e-3, 1e-4, total_steps=10, warmup_steps=2)
+    assert sched(0) == 0.0 and sched(1) == pytest.approx(5e-4) and sched(2) == pytest.approx(1e-3)
+    assert sched(10) == pytest.approx(1e-4) and sched(6) == pytest.approx(1e-4 + 9e-4 * 0.5)
+    assert build_learning_rate_schedule("linear", 1.0, 0.0, 4)(2) == pytest.approx(0.5)
+    assert build_learning_rate_schedule("constant", 1.0, 0.0, 1, warmup_steps=1)(0) == 1.0
+    for bad in (dict(total_steps=0), dict(total_steps=4, warmup_steps=4), dict(total_steps=4, warmup_steps=-1)):
+        with pytest.raises(ValueError):
+            build_learning_rate_schedule("cosine", 1.0, 0.0, **bad)
+    with pytest.raises(ValueError, match="unsupported scheduler"):
+        build_learning_rate_schedule("exponential", 1.0, 0.0, 4)
+
+    gen = torch.Generator().manual_seed(0)
+    ids = torch.randint(1, 50, (2, 8), generator=gen)
+    mask = torch.tensor([[1] * 8, [1] * 6 + [0] * 2])
+    seg = torch.tensor([[1] * 4 + [2] * 4, [1] * 6 + [0] * 2])
+    frac = torch.rand(2, 8, generator=gen) * mask
+    hidden = torch.randn(2, 8, 16, generator=gen)
+    head = torch.randn(50, 16, generator=gen)
+    targets, supervised = shifted_loss_mask(ids, mask, seg)
+    assert supervised.dtype == torch.bool and not supervised[0, 3] and not supervised[1, 5:].any()
+    got = chunked_causal_lm_loss(hidden, head, ids, mask, seg, loss_weights=frac, token_budget=5)
+    want = causal_lm_loss(hidden, head, {"input_ids": ids, "attention_mask": mask, "segment_ids": seg,
+                                         "loss_weights": frac}, implementation="xla", token_budget=4096)
+    assert torch.allclose(got[0], want[0], rtol=1e-5) and torch.allclose(got[1], want[1])
+    logp = torch.log_softmax(hidden.reshape(-1, 16) @ head.t(), dim=-1)
+    pt = torch.randint(0, 50, (2, 8), generator=gen)
+    pw = torch.rand(2, 8, generator=gen)
+    nll, count = chunked_causal_lm_loss(hidden, head, ids, mask, prediction_targets=pt, prediction_weights=pw)
+    assert torch.allclose(nll, -(logp.gather(1, pt.reshape(-1, 1)).squeeze(1) * pw.reshape(-1)).sum(), rtol=1e-5)
+    assert torch.allclose(count, pw.sum())
+    with pytest.raises(ValueError, match="together"):
+        chunked_causal_lm_loss(hidden, head, ids, mask, prediction_targets=pt)
