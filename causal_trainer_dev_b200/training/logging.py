@@ -63,16 +63,52 @@ def device_memory_stats(device: torch.device | None) -> dict[str, float]:
             "peak_bytes_in_use_gib": torch.cuda.max_memory_allocated(device) / gib}
 
 
+class ExperimentLogger:
+    """Weights & Biases run when ``enabled`` (naming the flag without the package installed is an
+    error, src/causal_trainer/training/logging.py:30-46); a no-op otherwise."""
+
+    def __init__(self, enabled: bool, project: str, run_name: str | None, config: dict | None):
+        self._run = None
+        if enabled:
+            try:
+                import wandb
+            except ImportError as error:
+                raise RuntimeError("--use_wandb requires the wandb package") from error
+            self._run = wandb.init(project=project, name=run_name, config=config)
+
+    @property
+    def active(self) -> bool:
+        return self._run is not None
+
+    def log(self, values: dict, step: int) -> None:
+        if self._run is not None:
+            self._run.log(values, step=step)
+
+    def finish(self) -> None:
+        if self._run is not None:
+            self._run.finish()
+
+
+def memory_metrics(devices=None) -> dict[str, float]:
+    """``device_<i>/bytes_in_use_gib`` and ``device_<i>/peak_bytes_in_use_gib`` for the given CUDA
+    devices (this process's current device by default); empty without CUDA."""
+    if not torch.cuda.is_available():
+        return {}
+    devices = [torch.cuda.current_device()] if devices is None else list(devices)
+    out: dict[str, float] = {}
+    for device in devices:
+        index = torch.device("cuda", device).index if isinstance(device, int) else torch.device(device).index
+        for key, value in device_memory_stats(torch.device("cuda", index)).items():
+            out[f"device_{index}/{key}"] = value
+    return out
+
+
 def init_wandb(args):
+    """The run's :class:`ExperimentLogger` (rank 0 only calls this), or None when not asked for."""
     if not args.use_wandb:
         return None
-    try:
-        import wandb
-    except ImportError:
-        log.warning("--use_wandb was given but wandb is not installed; continuing without it")
-        return None
-    return wandb.init(project=args.wandb_project, name=args.wandb_run_name, config={
-        k: str(v) for k, v in vars(args).items()} if hasattr(args, "__dict__") else None)
+    config = {k: str(v) for k, v in vars(args).items()} if hasattr(args, "__dict__") else None
+    return ExperimentLogger(True, args.wandb_project, args.wandb_run_name, config)
 
 
 def log_step(latest: dict[str, float] | None, tracker: ThroughputTracker, device, wandb_run) -> None:

@@ -106,3 +106,30 @@ def test_schedule_builder_and_tensor_level_loss_entry_points():
     assert torch.allclose(count, pw.sum())
     with pytest.raises(ValueError, match="together"):
         chunked_causal_lm_loss(hidden, head, ids, mask, prediction_targets=pt)
+
+
+def test_experiment_logger_without_and_with_a_fake_wandb(monkeypatch):
+    import sys
+    import types
+
+    from causal_trainer_dev_b200.training import logging as tlog
+
+    quiet = tlog.ExperimentLogger(False, "p", None, {})
+    quiet.log({"loss": 1.0}, 3)
+    quiet.finish()
+    assert not quiet.active and tlog.init_wandb(types.SimpleNamespace(use_wandb=False)) is None
+    events = []
+    run = types.SimpleNamespace(log=lambda values, step: events.append(("log", values, step)),
+                                finish=lambda: events.append(("finish",)))
+    fake = types.ModuleType("wandb")
+    fake.init = lambda **kwargs: events.append(("init", kwargs)) or run
+    monkeypatch.setitem(sys.modules, "wandb", fake)
+    logger = tlog.init_wandb(types.SimpleNamespace(use_wandb=True, wandb_project="proj", wandb_run_name="r"))
+    logger.log({"loss": 2.0}, 7)
+    logger.finish()
+    assert events[0][0] == "init" and events[0][1]["project"] == "proj" and events[0][1]["name"] == "r"
+    assert events[1:] == [("log", {"loss": 2.0}, 7), ("finish",)]
+    monkeypatch.setitem(sys.modules, "wandb", None)      # import wandb now fails
+    with pytest.raises(RuntimeError, match="wandb"):
+        tlog.ExperimentLogger(True, "p", None, {})
+    assert tlog.memory_metrics() == {} or all(k.startswith("device_") for k in tlog.memory_metrics())
