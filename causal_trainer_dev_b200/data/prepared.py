@@ -336,6 +336,43 @@ def validate_prepared_batch(columns: Mapping[str, Any], *, max_sequence_length: 
     return out
 
 
+_INT32_MAX = int(np.iinfo(np.int32).max)
+
+
+def canonical_prepared_features(max_sequence_length: int, *, uses_assistant_loss_mask: bool = False
+                                ) -> dict[str, dict[str, Any]]:
+    """The fixed schema of a prepared row: per field its dtype and length (the manifest's ``schema``)."""
+    _plain_int(max_sequence_length, "max_sequence_length", minimum=1)
+    if type(uses_assistant_loss_mask) is not bool:
+        raise TypeError("uses_assistant_loss_mask must be a boolean")
+    return schema_dict(max_sequence_length, uses_assistant_loss_mask)
+
+
+def canonical_prepared_dataset(columns: Mapping[str, Any], *, max_sequence_length: int,
+                               uses_assistant_loss_mask: bool = False) -> dict[str, np.ndarray]:
+    """Typed ``[rows, S]`` int32 / float32 columns from any rectangular input, after every semantic
+    check (src/causal_trainer/data/prepared.py:557-576); what :func:`write_prepared_shard` takes."""
+    return validate_prepared_batch(columns, max_sequence_length=max_sequence_length, max_token_id=_INT32_MAX,
+                                   max_position_id=_INT32_MAX, uses_assistant_loss_mask=uses_assistant_loss_mask)
+
+
+def validate_prepared_dataset(columns: Mapping[str, Any], *, max_sequence_length: int,
+                              uses_assistant_loss_mask: bool = False, expected_rows: int | None = None,
+                              max_token_id: int | None = None, max_position_id: int | None = None) -> None:
+    """Row count, schema, value maxima and row semantics of materialised columns."""
+    if max_token_id is not None:
+        _plain_int(max_token_id, "prepared max_token_id")
+    if max_position_id is not None:
+        _plain_int(max_position_id, "prepared max_position_id")
+    arrays = validate_prepared_batch(columns, max_sequence_length=max_sequence_length,
+                                     max_token_id=_INT32_MAX if max_token_id is None else max_token_id,
+                                     max_position_id=_INT32_MAX if max_position_id is None else max_position_id,
+                                     uses_assistant_loss_mask=uses_assistant_loss_mask)
+    rows = len(arrays["input_ids"])
+    if expected_rows is not None and rows != expected_rows:
+        raise ValueError(f"prepared dataset has {rows} rows, expected {expected_rows}")
+
+
 # ----------------------------------------------------------------------------------------- parquet
 def write_prepared_shard(columns: Mapping[str, np.ndarray], path: str | Path) -> int:
     """Writes typed ``[rows, S]`` columns as fixed-size-list Parquet columns; returns the row count."""

@@ -373,6 +373,46 @@ def _worker_call(item: tuple[int, Mapping[str, Any]]) -> TokenizedExample:
     return _WORKER(item[1], item[0])
 
 
+# ---- one example at a time, as plain functions (src/causal_trainer/data/preprocessing.py:273-640) ----
+def tokenize_raw_text(text: str, tokenizer, *, max_sequence_length: int) -> TokenizedExample:
+    """Raw text: no special tokens are added, truncation at ``max_sequence_length``."""
+    return Preprocessor(tokenizer, "text", max_sequence_length).tokenize_raw_text(text)
+
+
+def tokenize_messages(messages, tokenizer, *, max_sequence_length: int, assistant_only_loss: bool = False,
+                      last_assistant_only_loss: bool = False, tools: Any = None,
+                      chat_template_kwargs: Mapping[str, Any] | None = None) -> TokenizedExample:
+    """A conversation through the chat template, with the assistant mask the loss mode asks for."""
+    pre = Preprocessor(tokenizer, "messages", max_sequence_length, assistant_only_loss, last_assistant_only_loss)
+    return pre.tokenize_messages(messages, tools=tools, chat_template_kwargs=chat_template_kwargs)
+
+
+def tokenize_endprompt_text(text: str, tokenizer, *, max_sequence_length: int, settings: EndPromptSettings,
+                            example_index: int) -> TokenizedExample:
+    """Raw text with this row's prompt anchored at its logical position."""
+    if not isinstance(text, str):
+        raise ValueError("EndPrompt is supported only for raw string records")
+    return Preprocessor(tokenizer, "text", max_sequence_length, endprompt=settings)({"text": text}, example_index)
+
+
+def tokenize_endprompt_messages(messages, tokenizer, *, max_sequence_length: int, assistant_only_loss: bool,
+                                last_assistant_only_loss: bool = False, settings: EndPromptSettings,
+                                example_index: int, tools: Any = None,
+                                chat_template_kwargs: Mapping[str, Any] | None = None) -> TokenizedExample:
+    """A conversation followed by this row's prompt."""
+    pre = Preprocessor(tokenizer, "messages", max_sequence_length, assistant_only_loss, last_assistant_only_loss,
+                       settings)
+    return pre({"messages": messages, "tools": tools, "chat_template_kwargs": chat_template_kwargs}, example_index)
+
+
+def preprocess_example(example: Mapping[str, Any], tokenizer, *, dataset_text_field: str, max_sequence_length: int,
+                       assistant_only_loss: bool = False, last_assistant_only_loss: bool = False,
+                       endprompt: EndPromptSettings | None = None, example_index: int = 0) -> TokenizedExample:
+    """One record; a string field is raw text, a sequence of mappings a conversation."""
+    return Preprocessor(tokenizer, dataset_text_field, max_sequence_length, assistant_only_loss,
+                        last_assistant_only_loss, endprompt)(example, example_index)
+
+
 def preprocess_records(records, tokenizer, *, dataset_text_field: str, max_sequence_length: int,
                        assistant_only_loss: bool = False, last_assistant_only_loss: bool = False,
                        endprompt: EndPromptSettings | None = None, example_index_offset: int = 0,

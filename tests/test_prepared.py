@@ -216,3 +216,22 @@ def test_loading_rejects_values_above_the_manifest_maxima(tmp_path):
                                                                            rows=manifest.shards[0].rows + 1),))
     with pytest.raises(ValueError, match="rows, manifest says"):
         list(P.iter_prepared_streaming_batches(str(out), wrong_rows, num_epochs=1))
+
+
+def test_canonical_columns_have_fixed_dtypes_and_validate_semantics():
+    columns = dict(input_ids=[[5, 6, 0, 0]], attention_mask=[[1, 1, 0, 0]], position_ids=[[0, 1, 0, 0]],
+                   segment_ids=[[1, 1, 0, 0]], loss_weights=[[0.0, 1.0, 0.0, 0.0]])
+    typed = P.canonical_prepared_dataset(columns, max_sequence_length=4)
+    assert all(v.shape == (1, 4) for v in typed.values())
+    assert typed["loss_weights"].dtype == np.float32 and typed["input_ids"].dtype == np.int32
+    assert P.canonical_prepared_features(4) == P.schema_dict(4, False)
+    assert "assistant_masks" in P.canonical_prepared_features(4, uses_assistant_loss_mask=True)
+    P.validate_prepared_dataset(typed, max_sequence_length=4, expected_rows=1, max_token_id=6, max_position_id=1)
+    with pytest.raises(ValueError, match="has 1 rows, expected 2"):
+        P.validate_prepared_dataset(typed, max_sequence_length=4, expected_rows=2)
+    with pytest.raises(ValueError, match="max_token_id=5"):
+        P.validate_prepared_dataset(typed, max_sequence_length=4, max_token_id=5)
+    with pytest.raises(ValueError, match="fields mismatch"):
+        P.canonical_prepared_dataset(columns, max_sequence_length=4, uses_assistant_loss_mask=True)
+    with pytest.raises(TypeError):
+        P.canonical_prepared_features(4, uses_assistant_loss_mask=1)

@@ -99,3 +99,25 @@ def test_output_schema_follows_the_options_even_when_every_row_is_filtered(tok):
     rows = preprocess_records([{"messages": MSGS}], tok, dataset_text_field="messages", max_sequence_length=16,
                               assistant_only_loss=True, endprompt=s)
     assert sorted(rows[0]) == sorted(rows.column_names)
+
+
+def test_function_level_tokenisation_matches_the_preprocessor(tok):
+    from causal_trainer_dev_b200.data import preprocessing as pp
+
+    s = EndPromptSettings(16, 24, ("w9 w10",))
+    text = "w1 w2 w3 w4 w5 w6 w7 w8 w9"
+    assert pp.tokenize_raw_text(text, tok, max_sequence_length=6) == Preprocessor(tok, "text", 6)({"text": text})
+    assert (pp.tokenize_messages(MSGS, tok, max_sequence_length=64, assistant_only_loss=True)
+            == Preprocessor(tok, "messages", 64, assistant_only_loss=True)({"messages": MSGS}))
+    assert (pp.tokenize_endprompt_text(text, tok, max_sequence_length=8, settings=s, example_index=3)
+            == Preprocessor(tok, "text", 8, endprompt=s)({"text": text}, 3))
+    assert (pp.tokenize_endprompt_messages(MSGS, tok, max_sequence_length=16, assistant_only_loss=True, settings=s,
+                                           example_index=2)
+            == Preprocessor(tok, "messages", 16, assistant_only_loss=True, endprompt=s)({"messages": MSGS}, 2))
+    assert (pp.preprocess_example({"messages": MSGS}, tok, dataset_text_field="messages", max_sequence_length=64,
+                                  last_assistant_only_loss=True)
+            == Preprocessor(tok, "messages", 64, last_assistant_only_loss=True)({"messages": MSGS}))
+    with pytest.raises(ValueError, match="raw string"):
+        pp.tokenize_endprompt_text(MSGS, tok, max_sequence_length=8, settings=s, example_index=0)
+    with pytest.raises(ValueError, match="must be positive"):
+        pp.tokenize_raw_text(text, tok, max_sequence_length=0)
