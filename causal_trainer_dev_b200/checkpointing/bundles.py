@@ -299,6 +299,23 @@ def save_checkpoint_bundle(destination: str | Path, *, export_model, export_opti
     return cid
 
 
+def save_adapter_checkpoint_bundle(lora, destination: str | Path, *, base_model_name_or_path: str, global_step: int,
+                                   total_steps: int, signature: str, revision: str | None = None,
+                                   export_optimizer=None, **manifest_fields) -> str:
+    """A ``peft-adapter`` bundle: the adapter files, optionally the optimizer state, then the
+    manifest (src/causal_trainer/checkpointing/bundles.py:951-1113).  Collective like
+    :func:`save_checkpoint_bundle`, which does the work."""
+    from .huggingface import export_adapter_checkpoint
+
+    def export_model(dest: Path, checkpoint_id: str) -> None:
+        export_adapter_checkpoint(dest, lora, base_model_name_or_path=base_model_name_or_path,
+                                  checkpoint_id=checkpoint_id, revision=revision)
+
+    return save_checkpoint_bundle(destination, export_model=export_model, export_optimizer=export_optimizer,
+                                  artifact_kind="peft-adapter", global_step=global_step, total_steps=total_steps,
+                                  signature=signature, **manifest_fields)
+
+
 def prune_periodic_exports(output_dir: str | Path, limit: int, signature: str) -> list[Path]:
     """Keeps the newest ``limit`` fully valid periodic bundles of this run (0 keeps all); rank 0 only."""
     if limit <= 0 or rt.process_index() != 0:

@@ -351,6 +351,26 @@ def export_hf_checkpoint(destination: str | os.PathLike[str], source: TensorSour
 
 
 # --------------------------------------------------------------------------------------- optimizer state
+def export_adapter_checkpoint(destination: str | os.PathLike[str], lora, *, base_model_name_or_path: str,
+                              checkpoint_id: str, revision: str | None = None) -> Path:
+    """PEFT adapter files of a :class:`~..models.lora.LoraState`: ``adapter_model.safetensors``
+    (``lora_A`` = ``A^T``, ``lora_B`` = ``B^T``, plus the trained embedding / LM-head copies when
+    present) and ``adapter_config.json`` with ``lora_alpha = r``
+    (src/causal_trainer/checkpointing/huggingface.py:1420-1514).  Adapters are replicated, so rank 0
+    writes and the other ranks return at once."""
+    from ..models.lora import peft_adapter_config
+
+    dest = Path(destination)
+    if rt.process_index() == 0:
+        dest.mkdir(parents=True, exist_ok=True)
+        st.save_file(lora.peft_tensors(), dest / "adapter_model.safetensors",
+                     {"format": "pt", "checkpoint_id": checkpoint_id})
+        config = peft_adapter_config(base_model_name_or_path, lora.rank,
+                                     train_embed_and_lm_head=lora.train_embed_and_lm_head, revision=revision)
+        (dest / "adapter_config.json").write_text(json.dumps(config, indent=2, sort_keys=True) + "\n")
+    return dest
+
+
 def layout_fingerprint(entries: list[dict[str, Any]]) -> str:
     """SHA-256 of the compact, key-sorted JSON of the manifest's tensor entries."""
     return hashlib.sha256(json.dumps(entries, separators=(",", ":"), sort_keys=True).encode("utf-8")).hexdigest()

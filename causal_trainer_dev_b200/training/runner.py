@@ -44,7 +44,7 @@ from ..data.preprocessing import EndPromptSettings
 from ..data.tokenizer import TrainingTokenizer
 from ..models.config import ModelConfig, validate_splash_block_size
 from ..models.decoder import ForwardOptions
-from ..models.lora import LoraState, peft_adapter_config
+from ..models.lora import LoraState
 from ..models.params import ModelParams
 from ..parallel import runtime as rt
 from . import logging as tlog
@@ -519,12 +519,8 @@ class TrainingRun:
 
         def export_model(dest: Path, cid: str) -> None:
             if self.artifact_kind == "peft-adapter":
-                if rt.process_index() == 0:
-                    st.save_file(self.lora.peft_tensors(), dest / "adapter_model.safetensors",
-                                 {"format": "pt", "checkpoint_id": cid})
-                    (dest / "adapter_config.json").write_text(json.dumps(peft_adapter_config(
-                        a.repo_id, a.lora_rank, train_embed_and_lm_head=a.lora_train_embed_and_lm_head,
-                        revision=a.revision), indent=2, sort_keys=True) + "\n")
+                hfio.export_adapter_checkpoint(dest, self.lora, base_model_name_or_path=a.repo_id, checkpoint_id=cid,
+                                               revision=a.revision)
                 return
             source = hfio.TensorSource(self.cfg, params=self.params, runtime=self.runtime,
                                        transform=self.lora.export_transform() if self.lora is not None else None)

@@ -248,3 +248,26 @@ def test_rope_pairing_default_follows_the_model_family():
     assert ModelConfig.from_dict({**raw, "model_type": "opaque-metadata", "rope_style": "gpt-neox"}).rope_style == "gpt-neox"
     with pytest.raises(ValueError, match="rope_style"):
         ModelConfig.from_dict({**raw, "rope_style": "llama"})
+
+
+def test_adapter_bundle_is_discoverable_and_reloads_bit_exact(tmp_path):
+    from causal_trainer_dev_b200.models.lora import LoraState
+
+    cfg = preset("tiny")
+    lora = LoraState.init(cfg, 4, seed=1, dtype=torch.float32)
+    for b in lora.b.values():
+        torch.nn.init.normal_(b.data)
+    sig = bundles.training_signature({"run": "adapter"})
+    dest = tmp_path / "out" / "checkpoint-3"
+    cid = bundles.save_adapter_checkpoint_bundle(lora, dest, base_model_name_or_path="org/base", global_step=3,
+                                                 total_steps=10, signature=sig, revision="abc")
+    config = json.loads((dest / "adapter_config.json").read_text())
+    assert config["r"] == config["lora_alpha"] == 4 and config["base_model_name_or_path"] == "org/base"
+    assert config["revision"] == "abc" and config["modules_to_save"] is None
+    found = bundles.find_latest_checkpoint(tmp_path / "out", sig, expected_artifact_kind="peft-adapter")
+    assert found is not None and found.global_step == 3 and found.checkpoint_id == cid
+    assert not found.has_optimizer_state
+    again = LoraState.init(cfg, 4, seed=2, dtype=torch.float32)
+    again.load_peft_tensors(st.load_file(dest / "adapter_model.safetensors"))
+    for key in lora.a:
+        assert torch.equal(again.a[key], lora.a[key]) and torch.equal(again.b[key], lora.b[key])
