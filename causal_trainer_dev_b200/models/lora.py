@@ -36,6 +36,66 @@ def validate_rank(rank: Any) -> int:
     return rank
 
 
+def lora_parameter_shapes(cfg: ModelConfig, rank: int) -> dict[str, tuple[int, ...]]:
+    """``"layers/<i>/<projection>/lora_a|lora_b" -> shape`` for every adapter leaf, in the stable
+    order of :meth:`LoraState.named_tensors` (A is ``[in, r]``, B is ``[r, out]``)."""
+    rank = validate_rank(rank)
+    dims = projection_dimensions(cfg)
+    out: dict[str, tuple[int, ...]] = {}
+    for layer in range(cfg.num_hidden_layers):
+        for name in LORA_PROJECTIONS:
+            fin, fout = dims[name]
+            out[f"layers/{layer}/{name}/lora_a"] = (fin, rank)
+            out[f"layers/{layer}/{name}/lora_b"] = (rank, fout)
+    return out
+
+
+def _check_pair(a: torch.Tensor, b: torch.Tensor) -> None:
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[0]:
+        raise ValueError(f"adapter shapes {tuple(a.shape)} and {tuple(b.shape)} do not form a rank-r product")
+
+
+def lora_linear_delta(x: torch.Tensor, a: torch.Tensor, b: torch.Tensor,
+                      compute_dtype: torch.dtype | None = None) -> torch.Tensor:
+    """``(x @ A) @ B`` without forming ``A @ B`` and without an alpha multiplier
+    (src/causal_trainer/modeling/lora.py:218-242)."""
+    _check_pair(a, b)
+    if x.shape[-1] != a.shape[0]:
+        raise ValueError(f"input width {x.shape[-1]} does not match lora_a input width {a.shape[0]}")
+    dtype = x.dtype if compute_dtype is None else compute_dtype
+    return (x.to(dtype) @ a.to(dtype)) @ b.to(dtype)
+
+
+def merge_lora_kernel(kernel: torch.Tensor, a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """``kernel + A @ B`` for a kernel in ``[in, out]`` layout, product accumulated in fp32, result
+    in the kernel's dtype (src/causal_trainer/modeling/lora.py:279-295)."""
+    _check_pair(a, b)
+    if kernel.dim() != 2:
+        raise ValueError(f"a merged projection kernel must be rank two, got shape {tuple(kernel.shape)}")
+    if tuple(kernel.shape) != (a.shape[0], b.shape[1]):
+        raise ValueError(f"kernel shape {tuple(kernel.shape)} is incompatible with adapter shapes "
+                         f"{tuple(a.shape)} and {tuple(b.shape)}")
+    return (kernel.float() + a.float() @ b.float()).to(kernel.dtype)
+
+
+def lora_parameter_to_peft_key(path: str) -> tuple[str, bool]:
+    """``(PEFT tensor name, transposed)`` of an adapter leaf path as :meth:`LoraState.named_tensors`
+    spells it (src/causal_trainer/modeling/lora.py:428-456): ``lora_A`` is ``A^T`` and ``lora_B`` is
+    ``B^T``; the embedding and LM-head copies are stored in the Hugging Face orientation already."""
+    parts = [p for p in path.split("/") if p]
+    if parts[:1] == ["adapters"]:
+        parts = parts[1:]
+    if parts == ["embed_tokens", "embedding"]:
+        return "base_model.model.model.embed_tokens.weight", False
+    if parts == ["lm_head", "kernel"]:
+        return "base_model.model.lm_head.weight", False
+    if len(parts) == 4 and parts[0] == "layers" and parts[1].isdigit() and parts[2] in LORA_PROJECTIONS \
+            and parts[3] in ("lora_a", "lora_b"):
+        leaf = "lora_A" if parts[3] == "lora_a" else "lora_B"
+        return f"base_model.model.model.layers.{int(parts[1])}.{_MODULE_OF[parts[2]]}.{parts[2]}.{leaf}.weight", True
+    raise KeyError(f"unknown adapter parameter path {path!r}")
+
+
 @dataclass
 class LoraState:
     """All adapter tensors of a model plus, optionally, trainable copies of embedding and head."""

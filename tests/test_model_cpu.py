@@ -173,3 +173,37 @@ def test_frozen_components_and_lora_keep_the_base_untouched():
     assert torch.allclose(D.decoder_forward(merged, ids, mask), adapted, atol=1e-4)
     peft = lora.peft_tensors()
     assert peft["base_model.model.model.layers.0.self_attn.q_proj.lora_A.weight"].shape == (4, cfg.hidden_size)
+
+
+def test_lora_function_level_helpers_agree_with_the_adapter_state():
+    import pytest
+    import torch
+
+    from causal_trainer_dev_b200.models import lora as L
+    from causal_trainer_dev_b200.models.config import preset
+
+    cfg = preset("tiny")
+    state = L.LoraState.init(cfg, 4, seed=3, dtype=torch.float32)
+    for b in state.b.values():
+        torch.nn.init.normal_(b.data)
+    shapes = L.lora_parameter_shapes(cfg, 4)
+    named = dict(state.named_tensors())
+    assert list(shapes) == list(named) and all(tuple(named[k].shape) == v for k, v in shapes.items())
+    peft = state.peft_tensors()
+    for path, tensor in named.items():
+        key, transposed = L.lora_parameter_to_peft_key(path)
+        assert transposed and torch.equal(peft[key], tensor.detach().t())
+    assert L.lora_parameter_to_peft_key("adapters/lm_head/kernel") == ("base_model.model.lm_head.weight", False)
+    with pytest.raises(KeyError):
+        L.lora_parameter_to_peft_key("layers/0/router/lora_a")
+    a, b = (t.detach() for t in state.pair(0, "q_proj"))
+    x = torch.randn(3, 5, a.shape[0])
+    kernel = torch.randn(a.shape[0], b.shape[1])
+    merged = L.merge_lora_kernel(kernel, a, b)
+    assert torch.allclose(x @ merged, x @ kernel + L.lora_linear_delta(x, a, b), atol=1e-4)
+    assert torch.allclose(merged.t(), kernel.t() + state.merged_delta("model.layers.0.self_attn.q_proj.weight"), atol=1e-6)
+    assert L.merge_lora_kernel(kernel.bfloat16(), a, b).dtype == torch.bfloat16
+    with pytest.raises(ValueError, match="incompatible"):
+        L.merge_lora_kernel(kernel.t().contiguous()[:, :3], a, b)
+    with pytest.raises(ValueError, match="input width"):
+        L.lora_linear_delta(x[..., :-1], a, b)
