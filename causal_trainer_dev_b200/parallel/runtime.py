@@ -45,6 +45,22 @@ class ProcessEnvironment:
     source: str
 
 
+def parse_local_device_ids(value: str | Sequence[int] | None) -> tuple[int, ...] | None:
+    """``--local_device_ids`` as distinct non-negative integers (None for an empty value).  One
+    process drives one GPU here, so the first id is the device this process uses."""
+    if value is None:
+        return None
+    if isinstance(value, str):
+        if not value.strip():
+            return None
+        values = tuple(int(part.strip()) for part in value.split(","))
+    else:
+        values = tuple(int(item) for item in value)
+    if not values or any(v < 0 for v in values) or len(set(values)) != len(values):
+        raise ValueError(f"local device IDs must be distinct non-negative integers, got {values!r}")
+    return values
+
+
 def detect_environment(coordinator_address: str | None = None, num_processes: int | None = None,
                        process_id: int | None = None, local_device_ids: str | None = None,
                        env: dict[str, str] | None = None) -> ProcessEnvironment:
@@ -55,7 +71,8 @@ def detect_environment(coordinator_address: str | None = None, num_processes: in
             raise ValueError("num_processes and process_id must be given together")
         if num_processes > 1 and coordinator_address is None:
             raise ValueError("coordinator_address is required for more than one process")
-        local = int(local_device_ids.split(",")[0]) if local_device_ids else int(e.get("LOCAL_RANK", process_id))
+        ids = parse_local_device_ids(local_device_ids)
+        local = ids[0] if ids else int(e.get("LOCAL_RANK", process_id))
         return ProcessEnvironment(coordinator_address, num_processes, process_id, local, "flags")
     if "RANK" in e and "WORLD_SIZE" in e:
         addr = f"{e.get('MASTER_ADDR', '127.0.0.1')}:{e.get('MASTER_PORT', '29500')}"
@@ -138,6 +155,33 @@ def resolve_mesh_shape(spec: str | Sequence[int], world: int) -> tuple[int, ...]
     elif known != world:
         raise ValueError(f"sharding axis product {known} does not match {world} devices")
     return tuple(sizes)
+
+
+resolve_axis_dims = resolve_mesh_shape      # the name src/causal_trainer/distributed/runtime.py:187 gives it
+
+_COLUMN_PARALLEL = ("q_proj", "k_proj", "v_proj", "gate_proj", "up_proj", "embed_tokens", "lm_head")
+_ROW_PARALLEL = ("o_proj", "down_proj")
+
+
+def parameter_partition_spec(name: str) -> tuple[str | None, ...]:
+    """Which mesh axis cuts which dimension of a parameter, as a tuple over the tensor's dimensions
+    in the Hugging Face ``[out, in]`` layout (the rule table of
+    src/causal_trainer/distributed/runtime.py:334-360, transposed to this layout).  Column-parallel
+    weights (q / k / v / gate / up, embedding, head) are cut over ``tp`` along the output rows and
+    row-parallel ones (o / down) along the input columns; ``fsdp`` cuts the other dimension there,
+    and here cuts the flat per-layer buffer that holds a rank's tensor-parallel part.  Biases follow
+    their weight's rows; norm scales are replicated over ``tp``.  ``name`` is a Hugging Face tensor
+    name or a ``/``-separated path (``.../kernel`` paths are read as ``[in, out]`` and answered in
+    that order)."""
+    parts = [p for p in name.replace("/", ".").split(".") if p]
+    leaf = parts[-1] if parts else ""
+    module = next((p for p in reversed(parts) if p in _COLUMN_PARALLEL + _ROW_PARALLEL), None)
+    if module is None or leaf in ("scale",) or "norm" in ".".join(parts[-2:]):
+        return ()
+    if leaf == "bias":
+        return ("tp",) if module in _COLUMN_PARALLEL else ()
+    spec = ("tp", "fsdp") if module in _COLUMN_PARALLEL else ("fsdp", "tp")
+    return spec[::-1] if leaf == "kernel" else spec
 
 
 @dataclass

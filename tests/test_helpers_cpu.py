@@ -133,3 +133,28 @@ def test_experiment_logger_without_and_with_a_fake_wandb(monkeypatch):
     with pytest.raises(RuntimeError, match="wandb"):
         tlog.ExperimentLogger(True, "p", None, {})
     assert tlog.memory_metrics() == {} or all(k.startswith("device_") for k in tlog.memory_metrics())
+
+
+def test_partition_rules_match_the_tensor_parallel_windows():
+    from causal_trainer_dev_b200.checkpointing.huggingface import tp_window
+
+    cfg = preset("tiny", num_attention_heads=4, num_key_value_heads=2, intermediate_size=512)
+    p = "model.layers.0."
+    for name in (p + "self_attn.q_proj.weight", p + "self_attn.k_proj.weight", p + "mlp.gate_proj.weight",
+                 p + "self_attn.o_proj.weight", p + "mlp.down_proj.weight", "model.embed_tokens.weight", "lm_head.weight",
+                 p + "self_attn.q_proj.bias", p + "input_layernorm.weight", "model.norm.weight"):
+        spec = rt.parameter_partition_spec(name)
+        kind = tp_window(name, cfg, 2, 1)[4]
+        expected = {"rows": "tp" in spec[:1], "cols": spec[1:2] == ("tp",), "rep": spec == ()}[kind]
+        assert expected, (name, spec, kind)
+    assert rt.parameter_partition_spec("layers/0/attention/q_proj/kernel") == ("fsdp", "tp")
+    assert rt.parameter_partition_spec("layers/0/attention/o_proj/kernel") == ("tp", "fsdp")
+    assert rt.parameter_partition_spec("layers/0/input_layernorm/scale") == ()
+    assert rt.resolve_axis_dims("-1, 1, 1, 4, 1", 32) == (8, 1, 1, 4, 1)
+    assert rt.parse_local_device_ids(" 2, 3 ") == (2, 3) and rt.parse_local_device_ids("") is None
+    assert rt.parse_local_device_ids([1]) == (1,) and rt.parse_local_device_ids(None) is None
+    for bad in ("1,1", "-1", []):
+        with pytest.raises(ValueError):
+            rt.parse_local_device_ids(bad)
+    env = rt.detect_environment("127.0.0.1:1", 2, 1, "5,6", env={})
+    assert env.local_rank == 5
