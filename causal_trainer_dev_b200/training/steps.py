@@ -163,3 +163,37 @@ class TrainStep:
         lr = learning_rate_at(self.schedule, step)
         grad_norm = self.optimizer.update(grads, lr)
         return StepMetrics(nll_sum / denom, nll_sum, total, grad_norm, lr)
+
+
+# ---- step builders as plain functions (src/causal_trainer/training/steps.py:26,213,378) ----------
+def make_train_step(params: ModelParams, options: ForwardOptions, *, adamw: AdamWConfig, schedule: ScheduleConfig,
+                    loss_implementation: str = "xla", token_budget: int = 4096, cut_chunk_size: int = 0,
+                    dp_group=None) -> TrainStep:
+    """Full-parameter step on the autograd producer (any device); ``step.run(micro_batches)`` makes
+    one optimizer update.  The layerwise CUDA engine is wired the same way by the runner, with
+    ``training.engine.LayerwiseEngine`` as the producer."""
+    producer = AutogradProducer(params, options, loss_implementation, token_budget, cut_chunk_size)
+    return TrainStep(params, producer, adamw, schedule, dp_group=dp_group)
+
+
+def make_frozen_full_train_step(params: ModelParams, options: ForwardOptions, frozen_parameters, *, adamw: AdamWConfig,
+                                schedule: ScheduleConfig, loss_implementation: str = "xla", token_budget: int = 4096,
+                                cut_chunk_size: int = 0, dp_group=None) -> TrainStep:
+    """Full-parameter step with ``lm_head`` / ``embed`` / ``norm`` components held fixed: they get
+    no optimizer region and no optimizer state."""
+    frozen = tuple(frozen_parameters)
+    if not frozen:
+        raise ValueError("frozen components must not be empty")
+    producer = AutogradProducer(params, options, loss_implementation, token_budget, cut_chunk_size)
+    return TrainStep(params, producer, adamw, schedule, frozen=frozen, dp_group=dp_group)
+
+
+def make_lora_train_step(params: ModelParams, lora, options: ForwardOptions, *, adamw: AdamWConfig,
+                         schedule: ScheduleConfig, loss_implementation: str = "xla", token_budget: int = 4096,
+                         cut_chunk_size: int = 0, dp_group=None) -> TrainStep:
+    """Adapter step: the base stays fixed (no gradients, no optimizer state for it), the adapter
+    leaves of ``lora`` (and its embedding / LM-head copies when it has them) are the regions."""
+    options.lora = lora
+    producer = AutogradProducer(params, options, loss_implementation, token_budget, cut_chunk_size, lora=lora)
+    extra = [(t.detach(), t.dim() > 1, (lambda t=t: t.grad)) for _, t in lora.trainable()]
+    return TrainStep(params, producer, adamw, schedule, dp_group=dp_group, extra_regions=extra, train_base=False)

@@ -207,3 +207,40 @@ def test_lora_function_level_helpers_agree_with_the_adapter_state():
         L.merge_lora_kernel(kernel.t().contiguous()[:, :3], a, b)
     with pytest.raises(ValueError, match="input width"):
         L.lora_linear_delta(x[..., :-1], a, b)
+
+
+def test_step_builder_functions_equal_the_hand_wired_steps():
+    import pytest
+
+    from causal_trainer_dev_b200.models.lora import LoraState
+    from causal_trainer_dev_b200.training.steps import (make_frozen_full_train_step, make_lora_train_step,
+                                                        make_train_step)
+
+    cfg = preset("tiny", vocab_size=300)
+    gen = torch.Generator().manual_seed(5)
+    ids = torch.randint(3, 300, (2, 16), generator=gen)
+    batch = dict(input_ids=ids, attention_mask=torch.ones(2, 16, dtype=torch.long))
+    kw = dict(adamw=AdamWConfig(0.1), schedule=ScheduleConfig(1e-2, 0, "constant", 0, 4))
+
+    built, wired = ModelParams.init_random(cfg, 0, torch.float32), ModelParams.init_random(cfg, 0, torch.float32)
+    a = make_train_step(built, ForwardOptions(), **kw).run([batch]).to_floats()
+    b = TrainStep(wired, AutogradProducer(wired, ForwardOptions()), kw["adamw"], kw["schedule"]).run([batch]).to_floats()
+    assert a == b and all(torch.equal(built.tensor(n), wired.tensor(n)) for n in built.hf_names())
+
+    p = ModelParams.init_random(cfg, 0, torch.float32)
+    before = {n: p.tensor(n).clone() for n in p.hf_names()}
+    make_frozen_full_train_step(p, ForwardOptions(), ("lm_head",), **kw).run([batch])
+    assert torch.equal(before["lm_head.weight"], p.tensor("lm_head.weight"))
+    assert not torch.equal(before["model.embed_tokens.weight"], p.tensor("model.embed_tokens.weight"))
+    with pytest.raises(ValueError, match="must not be empty"):
+        make_frozen_full_train_step(p, ForwardOptions(), (), **kw)
+
+    p = ModelParams.init_random(cfg, 0, torch.float32)
+    before = {n: p.tensor(n).clone() for n in p.hf_names()}
+    lora = LoraState.init(cfg, 4, seed=1, dtype=torch.float32)
+    step = make_lora_train_step(p, lora, ForwardOptions(), **kw)
+    first = step.run([batch]).to_floats()["loss"]
+    for _ in range(3):
+        last = step.run([batch]).to_floats()["loss"]
+    assert last < first and all(torch.equal(before[n], p.tensor(n)) for n in p.hf_names())
+    assert len(step.optimizer.m) == 2 * 7 * cfg.num_hidden_layers
