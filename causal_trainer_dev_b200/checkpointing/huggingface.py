@@ -17,6 +17,7 @@ every rank stays bounded by one round regardless of model size (``:787-988, 1099
 """
 from __future__ import annotations
 
+import dataclasses
 import hashlib
 import json
 import os
@@ -70,6 +71,49 @@ def load_hf_config(source: str | os.PathLike[str]) -> dict[str, Any]:
     if not isinstance(value, dict):
         raise ValueError(f"{path} must contain a JSON object")
     return value
+
+
+SafeTensorIndex = st.SafeTensorIndex          # the reader classes live in safetensors_io; these names keep
+TensorInfo = st.TensorInfo                    # code written against this module's reference counterpart working
+
+
+@dataclasses.dataclass(frozen=True)
+class TensorMapping:
+    """Where a leaf of the nested parameter tree is stored: its Hugging Face key, and whether the
+    stored tensor is the transpose of the tree's ``[in, out]`` kernel."""
+    parameter_path: str
+    hf_key: str
+    transpose: bool = False
+
+
+_TREE_LEAVES = {
+    ("attention", "kernel"): ("self_attn.{p}.weight", True), ("attention", "bias"): ("self_attn.{p}.bias", False),
+    ("mlp", "kernel"): ("mlp.{p}.weight", True),
+}
+_TREE_PROJECTIONS = {"attention": ("q_proj", "k_proj", "v_proj", "o_proj"), "mlp": ("gate_proj", "up_proj", "down_proj")}
+_TREE_TOP = {"embed_tokens/embedding": ("model.embed_tokens.weight", False), "norm/scale": ("model.norm.weight", False),
+             "lm_head/kernel": ("lm_head.weight", True)}
+
+
+def parameter_to_hf_mapping(path: str) -> TensorMapping:
+    """Nested-tree path (``layers/3/attention/q_proj/kernel``, optionally under ``model/``) to its
+    Hugging Face tensor (src/causal_trainer/checkpointing/huggingface.py:108-146).  Kernels are
+    ``[in, out]`` in the tree and ``[out, in]`` on disk, hence ``transpose``; this framework keeps
+    the on-disk orientation in memory (``ModelParams.tensor(hf_key)``)."""
+    path = path.strip("/")
+    path = path[len("model/"):] if path.startswith("model/") else path
+    if path in _TREE_TOP:
+        key, transpose = _TREE_TOP[path]
+        return TensorMapping(path, key, transpose)
+    parts = path.split("/")
+    if len(parts) >= 4 and parts[0] == "layers" and parts[1].isdigit():
+        prefix = f"model.layers.{parts[1]}."
+        if len(parts) == 4 and parts[2] in ("input_layernorm", "post_attention_layernorm") and parts[3] == "scale":
+            return TensorMapping(path, f"{prefix}{parts[2]}.weight")
+        if len(parts) == 5 and (parts[2], parts[4]) in _TREE_LEAVES and parts[3] in _TREE_PROJECTIONS[parts[2]]:
+            template, transpose = _TREE_LEAVES[(parts[2], parts[4])]
+            return TensorMapping(path, prefix + template.format(p=parts[3]), transpose)
+    raise KeyError(f"no Hugging Face tensor mapping for parameter path {path!r}")
 
 
 def expected_model_layout(cfg: ModelConfig, dtype: torch.dtype) -> dict[str, tuple[str, tuple[int, ...]]]:
@@ -440,3 +484,6 @@ def new_checkpoint_id() -> str:
     value = uuid.uuid4().hex if rt.process_index() == 0 else None
     raw = rt.host_broadcast_bytes(value.encode() if value else None, 32)
     return raw.decode("ascii")
+
+
+parameter_hf_layout = expected_model_layout   # name of src/causal_trainer/checkpointing/huggingface.py:149

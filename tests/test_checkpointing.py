@@ -271,3 +271,26 @@ def test_adapter_bundle_is_discoverable_and_reloads_bit_exact(tmp_path):
     again.load_peft_tensors(st.load_file(dest / "adapter_model.safetensors"))
     for key in lora.a:
         assert torch.equal(again.a[key], lora.a[key]) and torch.equal(again.b[key], lora.b[key])
+
+
+def test_tree_paths_map_onto_every_exported_tensor():
+    cfg = preset("tiny", attention_bias=True)
+    keys = set()
+    for i in range(cfg.num_hidden_layers):
+        for proj in ("q_proj", "k_proj", "v_proj", "o_proj"):
+            keys.add(hfio.parameter_to_hf_mapping(f"layers/{i}/attention/{proj}/kernel"))
+        for proj in ("q_proj", "k_proj", "v_proj"):
+            keys.add(hfio.parameter_to_hf_mapping(f"model/layers/{i}/attention/{proj}/bias"))
+        for proj in ("gate_proj", "up_proj", "down_proj"):
+            keys.add(hfio.parameter_to_hf_mapping(f"layers/{i}/mlp/{proj}/kernel"))
+        for norm in ("input_layernorm", "post_attention_layernorm"):
+            keys.add(hfio.parameter_to_hf_mapping(f"layers/{i}/{norm}/scale"))
+    for top in ("embed_tokens/embedding", "norm/scale", "lm_head/kernel"):
+        keys.add(hfio.parameter_to_hf_mapping(top))
+    assert {m.hf_key for m in keys} == set(hf_export_order(cfg))
+    assert all(m.transpose == (m.parameter_path.endswith("kernel")) for m in keys)
+    assert set(hfio.parameter_hf_layout(cfg, torch.bfloat16)) == set(hf_export_order(cfg))
+    for bad in ("layers/0/mlp/q_proj/kernel", "layers/0/mlp/up_proj/bias", "layers/x/mlp/up_proj/kernel", "router/kernel"):
+        with pytest.raises(KeyError):
+            hfio.parameter_to_hf_mapping(bad)
+    assert hfio.SafeTensorIndex is st.SafeTensorIndex and hfio.TensorInfo is st.TensorInfo
