@@ -3,7 +3,7 @@
 Rank 0 logs at INFO, other ranks at WARNING (src/causal_trainer/training/logging.py:7-12).
 Beyond the reference's ``steps_per_second`` this module reports tokens/s and model-FLOP
 utilisation against the measured bf16 peak of the box (``MEASURED_PEAKS.json`` when present,
-1400 TFLOP/s otherwise), because those are the numbers the framework is judged on.
+1400 TFLOP/s otherwise): the two figures a training run is usually compared by.
 """
 from __future__ import annotations
 
