@@ -55,6 +55,80 @@ class ThroughputTracker:
         return out
 
 
+class StepProfiler:
+    """``--profile_steps N``: device time of N optimizer steps, after ``skip`` untimed ones.
+
+    On CUDA each timed step is bracketed by CUDA events on the current stream and wrapped in an
+    NVTX range (``train_step/<n>``) so that a trace lines up with the numbers; on CPU the host clock
+    is used.  :meth:`finish` is collective: per step it takes the maximum over ranks, then reports
+    the mean step time, tokens/s of the whole job and MFU against the measured bf16 rate.
+    """
+
+    def __init__(self, count: int, device: torch.device | None, *, tokens_per_step: int, flops_per_token: float,
+                 n_gpus: int, skip: int = 2):
+        self.count, self.skip = max(0, int(count)), max(0, int(skip))
+        self.cuda = device is not None and device.type == "cuda"
+        self.device = device
+        self.tokens_per_step, self.flops_per_token, self.n_gpus = tokens_per_step, flops_per_token, max(1, n_gpus)
+        self.seen = 0
+        self._open = None
+        self._spans: list[tuple] = []
+
+    @property
+    def timing(self) -> bool:
+        return self.count > 0 and self.skip <= self.seen < self.skip + self.count
+
+    def begin(self) -> None:
+        if not self.timing:
+            return
+        if self.cuda:
+            torch.cuda.nvtx.range_push(f"train_step/{self.seen}")
+            start = torch.cuda.Event(enable_timing=True)
+            start.record()
+            self._open = start
+        else:
+            import time
+
+            self._open = time.perf_counter()
+
+    def end(self) -> None:
+        if self._open is not None:
+            if self.cuda:
+                stop = torch.cuda.Event(enable_timing=True)
+                stop.record()
+                torch.cuda.nvtx.range_pop()
+                self._spans.append((self._open, stop))
+            else:
+                import time
+
+                self._spans.append((self._open, time.perf_counter()))
+            self._open = None
+        self.seen += 1
+
+    def finish(self) -> dict | None:
+        """Collective when ``count > 0``; the report (same on every rank) or None when nothing was timed."""
+        if self.count <= 0:
+            return None
+        from ..parallel import runtime as rt
+
+        if self.cuda:
+            torch.cuda.synchronize(self.device)
+            local = [a.elapsed_time(b) for a, b in self._spans]
+        else:
+            local = [(b - a) * 1e3 for a, b in self._spans]
+        per_rank = rt.allgather_object(local)
+        steps = min(len(x) for x in per_rank)
+        if steps == 0:
+            return None
+        ms = [max(x[i] for x in per_rank) for i in range(steps)]
+        mean = sum(ms) / steps
+        tokens_per_s = self.tokens_per_step / (mean * 1e-3)
+        return {"profiled_steps": steps, "skipped_steps": self.skip, "ms_per_step": mean, "ms_per_step_min": min(ms),
+                "ms_per_step_max": max(ms), "tokens_per_second": tokens_per_s,
+                "mfu": tokens_per_s * self.flops_per_token / (self.n_gpus * measured_bf16_peak_tflops() * 1e12),
+                "clock": "cuda events, max over ranks" if self.cuda else "host clock, max over ranks"}
+
+
 def device_memory_stats(device: torch.device | None) -> dict[str, float]:
     if device is None or device.type != "cuda":
         return {}

@@ -625,6 +625,10 @@ class TrainingRun:
         tracker = tlog.ThroughputTracker(self.cfg, a.max_sequence_length, rt.process_count())
         wandb_run = tlog.init_wandb(a) if rt.process_index() == 0 else None
         window = MetricWindow(a.async_dispatch_steps)
+        profiler = tlog.StepProfiler(a.profile_steps, self.device if self.cuda else None,
+                                     tokens_per_step=a.effective_batch_size * a.max_sequence_length,
+                                     flops_per_token=self.cfg.flops_per_token(a.max_sequence_length),
+                                     n_gpus=rt.process_count())
         step = self.start_step
         if self.action != "finalize":
             batches = batching.prefetch_map(self.global_batches(), lambda b: (b, self.to_device(
@@ -652,7 +656,9 @@ class TrainingRun:
                     lr_position = streaming_schedule_position(
                         step - raw.epoch * self.plan.steps_per_epoch if hasattr(raw, "epoch") else step,
                         getattr(raw, "epoch", 0), self.plan.steps_per_epoch)
+                profiler.begin()
                 metrics = self.step_fn.run(micro, lr_position=lr_position)
+                profiler.end()
                 step += 1
                 if hasattr(raw, "source_examples_seen"):
                     self.source_examples_seen, self.stream_digest = raw.source_examples_seen, raw.stream_digest
@@ -669,6 +675,11 @@ class TrainingRun:
                     self.save_bundle(out / f"checkpoint-{step}", step)
                     bundles.prune_periodic_exports(out, a.save_total_limit, self.signature)
             window.drain()
+        profile = profiler.finish()
+        if profile is not None and rt.process_index() == 0:
+            log.info("profiled %(profiled_steps)d steps: %(ms_per_step).2f ms/step, %(tokens_per_second).0f tok/s, "
+                     "mfu %(mfu).3f (%(clock)s)", profile)
+            (out / "profile_steps.json").write_text(json.dumps(profile, indent=2, sort_keys=True) + "\n")
         if self.streaming and not self.plan.has_exact_step_limit:
             self.training_complete = True
             self.plan = dataclasses.replace(self.plan, total_steps=step)

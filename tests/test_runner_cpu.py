@@ -98,3 +98,22 @@ def test_pure_helpers():
     assert pos == [0, 2, 3, 3, 3, 6, 9]
     assert runner.project_streaming_progress_total(5, 1, 3) == 15 and runner.project_streaming_progress_total(10, 2, 3) == 15
     assert runner.project_streaming_progress_total(14, 3, 3) == 14
+
+
+def test_profile_steps_times_steps_after_the_warm_up_ones(tmp_path):
+    from causal_trainer_dev_b200.training.logging import StepProfiler
+
+    assert runner.main(_argv(tmp_path, "--max_steps", "5", "--profile_steps", "2")) == 0
+    report = json.loads((tmp_path / "out" / "profile_steps.json").read_text())
+    assert report["profiled_steps"] == 2 and report["skipped_steps"] == 2 and report["clock"].startswith("host clock")
+    assert report["ms_per_step_min"] <= report["ms_per_step"] <= report["ms_per_step_max"]
+    assert report["tokens_per_second"] > 0 and report["mfu"] > 0
+    assert bundles.find_latest_checkpoint(tmp_path / "out", json.loads(
+        (tmp_path / "out" / bundles.MANIFEST_NAME).read_text())["training_signature"]) is not None
+    idle = StepProfiler(0, None, tokens_per_step=1, flops_per_token=1.0, n_gpus=1)
+    idle.begin(); idle.end()
+    assert idle.finish() is None
+    short = StepProfiler(3, None, tokens_per_step=8, flops_per_token=1.0, n_gpus=1, skip=1)
+    for _ in range(2):
+        short.begin(); short.end()
+    assert short.finish()["profiled_steps"] == 1
