@@ -617,6 +617,9 @@ class TrainingRun:
         if self.action == "complete":
             log.info("training is already complete at step %d", self.start_step)
             return
+        if a.weight_distribution_log_steps:
+            log.warning("weight_distribution_log_steps is accepted for command compatibility; weight histograms are "
+                        "not logged (src/causal_trainer/training/runner.py:1760-1763 does the same)")
         if rt.process_index() == 0:
             out.mkdir(parents=True, exist_ok=True)
             (out / "training_args.json").write_text(json.dumps(
