@@ -94,6 +94,8 @@ class ClockSampler:
                  "-i", str(self.index)], stdout=open(self.path, "w"), stderr=subprocess.DEVNULL)
         except OSError:
             self.proc = None
+            if self.path and os.path.exists(self.path):
+                os.unlink(self.path)
 
     def stop(self) -> dict:
         out = {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}

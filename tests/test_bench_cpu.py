@@ -1,0 +1,55 @@
+"""Host-side pieces of the headline benchmark script: the reference arm's line and the clock sampler."""
+import importlib.util
+import json
+import os
+import stat
+import subprocess
+import sys
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parents[1]
+
+
+def _bench():
+    spec = importlib.util.spec_from_file_location("bench_under_test", ROOT / "bench.py")
+    module = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(module)
+    return module
+
+
+def test_reference_arm_prints_one_json_line_and_exits_zero():
+    done = subprocess.run([sys.executable, str(ROOT / "bench.py"), "--impl", "reference", "--gpus", "1", "--steps", "2",
+                           "--warmup", "3"], capture_output=True, text=True, timeout=600)
+    assert done.returncode == 0, done.stderr
+    lines = [line for line in done.stdout.splitlines() if line.strip()]
+    assert len(lines) == 1
+    record = json.loads(lines[0])
+    assert record["impl"] == "reference" and record["unavailable"].startswith("unavailable on this box")
+
+
+def test_clock_sampler_reads_median_clock_and_active_reasons(tmp_path, monkeypatch):
+    fake = tmp_path / "nvidia-smi"
+    fake.write_text("#!/bin/sh\n"
+                    "echo '0, 1500, 1965, 990.1, 0x4, Not Active, Not Active, Not Active, Active'\n"
+                    "echo '0, 1410, 1965, 1001.5, 0x4, Not Active, Not Active, Not Active, Active'\n"
+                    "echo '0, 1605, 1965, 870.0, 0x0, Not Active, Not Active, Not Active, Not Active'\n"
+                    "echo 'garbage line'\n"
+                    "exec sleep 30\n")
+    fake.chmod(fake.stat().st_mode | stat.S_IEXEC)
+    monkeypatch.setenv("PATH", f"{tmp_path}{os.pathsep}{os.environ['PATH']}")
+    sampler = _bench().ClockSampler(0)
+    sampler.start()
+    deadline = time.time() + 10
+    while time.time() < deadline and Path(sampler.path).read_text().count("\n") < 4:
+        time.sleep(0.05)
+    clocks = sampler.stop()
+    assert clocks["sm_mhz"] == 1500 and clocks["sm_max_mhz"] == 1965 and clocks["samples"] == 3
+    assert clocks["reasons"] == ["sw_power_cap"]
+
+
+def test_clock_sampler_without_nvidia_smi_reports_nothing(tmp_path, monkeypatch):
+    monkeypatch.setenv("PATH", str(tmp_path))
+    sampler = _bench().ClockSampler(0)
+    sampler.start()
+    assert sampler.stop() == {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
