@@ -117,3 +117,36 @@ def test_profile_steps_times_steps_after_the_warm_up_ones(tmp_path):
     for _ in range(2):
         short.begin(); short.end()
     assert short.finish()["profiled_steps"] == 1
+
+
+def test_training_from_a_prepared_artifact_materialised_and_streamed(tmp_path):
+    from causal_trainer_dev_b200 import prepare
+
+    base = _argv(tmp_path)
+    model, data = base[1], base[3]
+    prepared_dir = tmp_path / "prepared"
+    manifest = prepare.prepare_dataset(prepare.parse_args([
+        "--dataset_name", data, "--tokenizer_name_or_path", model, "--output_dir", str(prepared_dir),
+        "--max_sequence_length", "32", "--packing", "--num_shards", "2"]))
+    assert manifest.total_rows > 4
+
+    def argv(out, *extra):
+        args = list(base)
+        args[3] = str(prepared_dir)
+        args[5] = str(tmp_path / out)
+        return [*args, "--dataset_format", "prepared", *extra]
+
+    assert runner.main(argv("out_prepared", "--max_steps", "3")) == 0
+    done = json.loads((tmp_path / "out_prepared" / bundles.MANIFEST_NAME).read_text())
+    assert done["global_step"] == done["total_steps"] == 3
+    assert runner.main(argv("out_streamed", "--dataset_streaming", "--num_train_epochs", "1", "--no-shuffle")) == 0
+    streamed = json.loads((tmp_path / "out_streamed" / bundles.MANIFEST_NAME).read_text())
+    assert streamed["global_step"] == streamed["total_steps"] == manifest.total_rows // 2
+    assert streamed["source_examples_seen"] == manifest.total_rows and len(streamed["streaming_data_digest"]) == 64
+    # a shard that no longer matches its manifest stops the run before any step
+    shard = prepared_dir / manifest.shards[0].path
+    blob = bytearray(shard.read_bytes())
+    blob[len(blob) // 2] ^= 0xFF
+    shard.write_bytes(blob)
+    with pytest.raises(RuntimeError, match="checksum mismatch"):
+        runner.main(argv("out_corrupt", "--max_steps", "1"))
