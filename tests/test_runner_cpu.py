@@ -150,3 +150,44 @@ def test_training_from_a_prepared_artifact_materialised_and_streamed(tmp_path):
     shard.write_bytes(blob)
     with pytest.raises(RuntimeError, match="checksum mismatch"):
         runner.main(argv("out_corrupt", "--max_steps", "1"))
+
+
+def _chat_data(path, n=24):
+    grid = "<|image_1|><|image_2|><|image_3|>\n<|image_4|><|image_5|><|image_6|>"
+    rows = []
+    for i in range(n):
+        reply = f"w{i % 40} {grid} w{(i + 3) % 40}" if i % 2 else f"w{i % 40} w{(i + 1) % 40}"
+        rows.append({"messages": [{"role": "user", "content": f"w{(i * 5) % 40} w{(i * 7) % 40}"},
+                                  {"role": "assistant", "content": reply}]})
+    path.write_text("\n".join(json.dumps(r) for r in rows))
+    return path
+
+
+def test_chat_modes_assistant_only_with_frozen_components_and_maskgit(tmp_path):
+    base = _argv(tmp_path)
+    base[3] = str(_chat_data(tmp_path / "chat.jsonl"))
+    base[base.index("--max_sequence_length") + 1] = "64"
+    chat = [*base, "--dataset_text_field", "messages", "--assistant_only_loss", "--max_steps", "3"]
+
+    frozen = list(chat)
+    frozen[5] = str(tmp_path / "out_frozen")
+    run = runner.TrainingRun(parse_args([*frozen, "--frozen_parameters", "embed|norm"]))
+    run.resolve_model(); run.load_data(); run.discover_resume(); run.build_model()
+    before = {n: run.params.tensor(n).clone() for n in run.params.hf_names()}
+    run.train()
+    changed = {n for n in before if not torch.equal(before[n], run.params.tensor(n))}
+    assert "model.embed_tokens.weight" not in changed and not any("norm" in n for n in changed)
+    assert "lm_head.weight" in changed and "model.layers.0.mlp.up_proj.weight" in changed
+    saved = st.load_file(tmp_path / "out_frozen" / "model.safetensors")
+    assert torch.equal(saved["model.embed_tokens.weight"], before["model.embed_tokens.weight"])
+
+    mixed = list(chat)
+    mixed[5] = str(tmp_path / "out_maskgit")
+    assert runner.main([*mixed, "--maskgit_probability", "1.0"]) == 0
+    done = json.loads((tmp_path / "out_maskgit" / bundles.MANIFEST_NAME).read_text())
+    assert done["global_step"] == 3
+    # the MaskGIT probability is part of the run's identity: the plain run cannot resume from it
+    plain = list(chat)
+    plain[5] = str(tmp_path / "out_maskgit")
+    with pytest.raises(ValueError, match="incompatible"):
+        runner.main(plain)
