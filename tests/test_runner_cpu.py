@@ -191,3 +191,35 @@ def test_chat_modes_assistant_only_with_frozen_components_and_maskgit(tmp_path):
     plain[5] = str(tmp_path / "out_maskgit")
     with pytest.raises(ValueError, match="incompatible"):
         runner.main(plain)
+
+
+def test_two_gloo_ranks_train_the_same_model_as_one_process(tmp_path):
+    """Data parallel on CPU ranks: the global batch is split over two processes, the result is the
+    single-process model up to summation order."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    root = Path(__file__).resolve().parents[1]
+    # replicated preprocessing: every process packs the whole source, so both runs see the same rows
+    # (sharded preprocessing packs per process shard, which legitimately gives other rows)
+    single = _argv(tmp_path, "--max_steps", "3", "--preprocessing_mode", "replicated")
+    single[single.index("--total_batch_size") + 1] = "4"
+    assert runner.main(single) == 0
+    want = st.load_file(tmp_path / "out" / "model.safetensors")
+
+    multi = [a for a in single if a != "--no-distributed"]
+    multi[5] = str(tmp_path / "out2")
+    multi[multi.index("--sharding_axis") + 1] = "2,1,1,1,1"
+    env = dict(os.environ, PYTHONPATH=f"{root}{os.pathsep}{os.environ.get('PYTHONPATH', '')}", CUDA_VISIBLE_DEVICES="")
+    done = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                           "--master-addr", "127.0.0.1", "--master-port", "29517", "-m", "causal_trainer_dev_b200.train",
+                           *multi], env=env, capture_output=True, text=True, timeout=600, cwd=str(tmp_path))
+    assert done.returncode == 0, done.stderr[-3000:]
+    got = st.load_file(tmp_path / "out2" / "model.safetensors")
+    assert set(got) == set(want)
+    for name in want:
+        assert torch.allclose(got[name], want[name], atol=2e-5, rtol=1e-4), name
+    manifest = json.loads((tmp_path / "out2" / bundles.MANIFEST_NAME).read_text())
+    assert manifest["global_step"] == 3
