@@ -212,9 +212,14 @@ def test_two_gloo_ranks_train_the_same_model_as_one_process(tmp_path):
     multi = [a for a in single if a != "--no-distributed"]
     multi[5] = str(tmp_path / "out2")
     multi[multi.index("--sharding_axis") + 1] = "2,1,1,1,1"
+    import socket
+
+    with socket.socket() as probe:
+        probe.bind(("127.0.0.1", 0))
+        port = probe.getsockname()[1]
     env = dict(os.environ, PYTHONPATH=f"{root}{os.pathsep}{os.environ.get('PYTHONPATH', '')}", CUDA_VISIBLE_DEVICES="")
     done = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
-                           "--master-addr", "127.0.0.1", "--master-port", "29517", "-m", "causal_trainer_dev_b200.train",
+                           "--master-addr", "127.0.0.1", "--master-port", str(port), "-m", "causal_trainer_dev_b200.train",
                            *multi], env=env, capture_output=True, text=True, timeout=600, cwd=str(tmp_path))
     assert done.returncode == 0, done.stderr[-3000:]
     got = st.load_file(tmp_path / "out2" / "model.safetensors")
