@@ -11,8 +11,9 @@ def test_every_site_code_is_described():
     for path in sorted(csrc.iterdir()):
         if path.suffix in (".cu", ".cuh", ".h"):
             for name, value in re.findall(r"\b(SITE_[A-Z0-9_]+)\s*=\s*(0x[0-9a-fA-F]+)", path.read_text()):
-                codes[int(value, 16)] = f"{path.name}:{name}"
+                where = f"{path.name}:{name}"
+                assert int(value, 16) not in codes, f"{where} reuses the code of {codes[int(value, 16)]}"
+                codes[int(value, 16)] = where
     assert codes, "no site codes found"
     missing = {hex(c): where for c, where in codes.items() if c not in lib._SITES}
     assert not missing, missing
-    assert len(set(codes)) == len(codes)
