@@ -43,6 +43,9 @@ class Trainer:
     def __init__(self, model: ModelConfig, cfg: TrainerConfig | None = None, device: torch.device | None = None):
         self.model = model
         self.cfg = cfg or TrainerConfig()
+        if device is None and not torch.cuda.is_available():
+            raise RuntimeError("Trainer drives the sm_100a layerwise engine and needs a CUDA device; on a CPU use "
+                               "training.steps.make_train_step (the PyTorch oracle path)")
         self.device = device or torch.device("cuda", torch.cuda.current_device())
         self.world = dist.get_world_size() if dist.is_initialized() else 1
         self.rank = dist.get_rank() if dist.is_initialized() else 0

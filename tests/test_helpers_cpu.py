@@ -158,3 +158,11 @@ def test_partition_rules_match_the_tensor_parallel_windows():
             rt.parse_local_device_ids(bad)
     env = rt.detect_environment("127.0.0.1:1", 2, 1, "5,6", env={})
     assert env.local_rank == 5
+
+
+@pytest.mark.skipif(torch.cuda.is_available(), reason="checks the message of a box without CUDA")
+def test_trainer_without_cuda_names_the_cpu_path():
+    from causal_trainer_dev_b200.api import Trainer
+
+    with pytest.raises(RuntimeError, match="make_train_step"):
+        Trainer(preset("tiny"))
