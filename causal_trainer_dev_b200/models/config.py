@@ -13,9 +13,10 @@ from __future__ import annotations
 import json
 from dataclasses import asdict, dataclass, fields
 from pathlib import Path
-from typing import Any, Mapping
+from typing import Any, Mapping, Literal
 
 ROPE_STYLES = ("gpt-j", "gpt-neox")
+RopeStyle = Literal["gpt-j", "gpt-neox"]     # adjacent-pair or half-split rotary channel pairing
 
 # model_type -> (rope pairing, QKV bias) used when config.json does not say.
 _FAMILY_DEFAULTS = {
