@@ -48,6 +48,12 @@ class RowTable(list):
         return list(self[0]) if len(self) else []
 
     @property
+    def features(self) -> dict[str, str]:
+        """Element type per column (``loss_weights`` is ``float32``, every other field ``int64``), the
+        plain-dictionary counterpart of a ``datasets.Features`` of sequences."""
+        return {name: ("float32" if name == "loss_weights" else "int64") for name in self.column_names}
+
+    @property
     def cache_files(self) -> list:
         return []
 _ASSISTANT_KEYS = ("assistant_masks", "assistant_mask", "assistant_tokens_mask")

@@ -108,6 +108,7 @@ def test_rows_answer_column_questions_like_a_dataset():
     rows = RowTable([{"input_ids": [1, 2]}, {"input_ids": [3]}])
     assert rows["input_ids"] == [[1, 2], [3]] and rows[1] == {"input_ids": [3]}
     assert rows.column_names == ["input_ids"] and rows.cache_files == [] and isinstance(rows[:1], RowTable)
-    assert RowTable().column_names == []
+    assert RowTable().column_names == [] and rows.features == {"input_ids": "int64"}
+    assert RowTable([], ["input_ids", "loss_weights"]).features == {"input_ids": "int64", "loss_weights": "float32"}
     records = RecordList([{"text": "a"}, {"text": "b"}], "fp")
     assert records["text"] == ["a", "b"] and records.cache_files == []
