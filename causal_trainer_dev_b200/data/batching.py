@@ -32,17 +32,15 @@ class BatchPlan:
     @classmethod
     def create(cls, examples: int, global_micro_batch_size: int, accumulation_steps: int, epochs: float,
                max_steps: int) -> "BatchPlan":
-        effective = global_micro_batch_size * accumulation_steps
-        if examples <= 0:
-            raise ValueError("the prepared dataset must contain at least one row")
-        if examples % effective:
-            raise ValueError(
-                f"prepared dataset rows ({examples}) must be divisible by the effective global batch "
-                f"({effective}); append zero-loss rows before creating the batch plan"
-            )
-        per_epoch = examples // effective
-        total = max_steps if max_steps > 0 else max(1, math.floor(per_epoch * epochs))
-        return cls(examples, global_micro_batch_size, accumulation_steps, per_epoch, total)
+        rows_per_step = global_micro_batch_size * accumulation_steps
+        if examples < 1:
+            raise ValueError("a batch plan needs at least one dataset row")
+        whole_steps, leftover = divmod(examples, rows_per_step)
+        if leftover:
+            raise ValueError(f"{examples} dataset rows are not divisible by the {rows_per_step} rows one optimizer step "
+                             f"consumes; pad with zero-loss rows first (pad_packed_arrays_to_batch_multiple)")
+        steps = max_steps if max_steps > 0 else max(1, math.floor(whole_steps * epochs))
+        return cls(examples, global_micro_batch_size, accumulation_steps, whole_steps, steps)
 
     @property
     def effective_batch_size(self) -> int:
