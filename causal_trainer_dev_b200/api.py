@@ -15,6 +15,7 @@ import torch.distributed as dist
 
 from .models.config import ModelConfig
 from .models.params import ModelParams
+from .ops import lib as _lib
 from .training.engine import EngineOptions, LayerwiseEngine, LocalProvider
 from .training.optimizer import AdamWConfig, ScheduleConfig, learning_rate_at
 from .training.steps import TrainStep
@@ -146,6 +147,11 @@ class Trainer:
         packed = torch.stack([metrics.loss.float(), metrics.nll_sum.float(), metrics.token_count.float(),
                               metrics.grad_norm.float()]).cpu()
         self._bytes_d2h += packed.numel() * 4
+        # a bounded device wait that gave up during this step left a record: a step built on a
+        # flag that never arrived is wrong, so it ends here rather than in a later loss curve
+        failure = _lib.poll_device_status()
+        if failure is not None:
+            raise failure
         loss, nll, count, gnorm = packed.tolist()
         return {"loss": loss, "nll_sum": nll, "token_count": count, "grad_norm": gnorm,
                 "learning_rate": metrics.learning_rate}

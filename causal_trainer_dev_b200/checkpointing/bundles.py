@@ -73,18 +73,87 @@ def _read_manifest(path: Path) -> dict[str, Any] | None:
     return value if isinstance(value, dict) else None
 
 
+# What counts as part of a bundle.  Anything else that turns up beside it (a log, a hub cache, an
+# editor's swap file, training_args.json, profile_steps.json) is not hashed and cannot invalidate
+# a completed checkpoint.  Same convention on disk as src/causal_trainer/checkpointing/bundles.py:
+# 46-61, 315-385.
+_ASSET_FILES = frozenset({
+    "config.json", "generation_config.json", "tokenizer.json", "tokenizer.model", "tokenizer_config.json",
+    "special_tokens_map.json", "added_tokens.json", "vocab.json", "merges.txt", "chat_template.json",
+    "preprocessor_config.json", "processor_config.json",
+})
+_ASSET_ENDINGS = (".jinja", ".model", ".tiktoken")
+_ADAPTER_FILES = frozenset({"adapter_config.json", "adapter_model.safetensors"})
+_TOKENIZER_DATA = frozenset({"tokenizer.json", "tokenizer.model", "vocab.json"})
+
+
+def _top_level_class(name: str) -> str | None:
+    """``"asset" | "merged" | "adapter"`` for a file name directly under the bundle, else None."""
+    if name in _ADAPTER_FILES:
+        return "adapter"
+    if name in ("model.safetensors", "model.safetensors.index.json") or (
+            name.startswith("model-") and name.endswith(".safetensors")):
+        return "merged"
+    if name in _ASSET_FILES or name.startswith("tokenizer.") or name.endswith(_ASSET_ENDINGS):
+        return "asset"
+    return None
+
+
+def _real_file(p: Path) -> Path:
+    if "\\" in p.name or p.is_symlink() or not p.is_file():
+        raise RuntimeError(f"checkpoint artifact must be a regular file: {p}")
+    return p
+
+
 def artifact_files(path: Path, kind: str, has_optimizer: bool) -> list[Path]:
-    """Every regular file that belongs to a bundle (the manifest itself and nested bundles excluded)."""
-    out = []
-    for p in sorted(path.rglob("*")):
-        rel = p.relative_to(path)
-        if rel.parts[0].startswith("checkpoint-") or rel.name == MANIFEST_NAME or rel.name == "training_args.json":
-            continue
-        if rel.parts[0] == "optimizer" and not has_optimizer:
-            continue
-        if p.is_file() and not p.is_symlink() and not p.name.endswith(".tmp"):
-            out.append(p)
-    return out
+    """The files that make up a bundle of ``kind``, sorted by relative path.
+
+    Top level: model assets, tokenizer files and the weights of ``kind``; one level down
+    ``chat_templates/*.jinja`` and, when the bundle carries optimizer state, ``optimizer/*``.
+    Raises ``RuntimeError`` for a bundle that cannot be valid: weights of the other kind left
+    over from an earlier export, missing weights / config / tokenizer data, an ``optimizer``
+    directory the manifest does not announce (or the reverse), artifacts that are not regular
+    files.  Everything else in the directory is ignored."""
+    if kind not in ARTIFACT_KINDS:
+        raise ValueError(f"unknown checkpoint artifact kind {kind!r}")
+    found: dict[str, Path] = {}
+    classes: dict[str, set[str]] = {"asset": set(), "merged": set(), "adapter": set()}
+    for p in path.iterdir():
+        cls = _top_level_class(p.name)
+        if cls is not None:
+            found[p.name] = _real_file(p)
+            classes[cls].add(p.name)
+    templates = path / "chat_templates"
+    if templates.exists():
+        if templates.is_symlink() or not templates.is_dir():
+            raise RuntimeError(f"chat_templates must be a directory: {templates}")
+        for p in templates.iterdir():
+            if p.suffix != ".jinja":
+                raise RuntimeError(f"chat_templates may only hold .jinja files: {p}")
+            found[f"chat_templates/{p.name}"] = _real_file(p)
+    other = "adapter" if kind == "merged" else "merged"
+    if classes[other]:
+        raise RuntimeError(f"{kind} checkpoint holds stale {other} weights: {sorted(classes[other])}")
+    if kind == "merged":
+        if "model.safetensors" not in found or "config.json" not in found:
+            raise RuntimeError(f"checkpoint is missing model.safetensors or config.json: {path}")
+        if not any(n in _TOKENIZER_DATA or n.endswith((".model", ".tiktoken")) for n in classes["asset"]):
+            raise RuntimeError(f"checkpoint is missing tokenizer data: {path}")
+    elif classes["adapter"] != _ADAPTER_FILES:
+        raise RuntimeError(f"checkpoint is missing adapter weights or adapter_config.json: {path}")
+    opt = path / "optimizer"
+    if has_optimizer:
+        if opt.is_symlink() or not opt.is_dir():
+            raise RuntimeError(f"checkpoint is missing optimizer state: {opt}")
+        names = set()
+        for p in opt.iterdir():
+            found[f"optimizer/{p.name}"] = _real_file(p)
+            names.add(p.name)
+        if "manifest.json" not in names or not any(n.endswith(".safetensors") for n in names):
+            raise RuntimeError(f"optimizer state is incomplete: {opt}")
+    elif opt.exists():
+        raise RuntimeError(f"checkpoint holds stale optimizer state: {opt}")
+    return [found[k] for k in sorted(found)]
 
 
 def _header_matches(path: Path, checkpoint_id: str, layout: dict[str, tuple[str, tuple[int, ...]]] | None) -> bool:
@@ -137,15 +206,18 @@ def _artifacts_match(path: Path, manifest: dict[str, Any], verify_digests: bool)
     sizes, digests = manifest.get("artifact_sizes"), manifest.get("artifact_digests")
     if not isinstance(sizes, dict) or not isinstance(digests, dict) or set(sizes) != set(digests):
         return False
-    files = {str(p.relative_to(path)): p for p in artifact_files(path, manifest["artifact_kind"],
-                                                                  manifest["has_optimizer_state"])}
-    if set(files) != set(sizes):
+    try:
+        files = {p.relative_to(path).as_posix(): p
+                 for p in artifact_files(path, manifest["artifact_kind"], manifest["has_optimizer_state"])}
+        if set(files) != set(sizes):
+            return False
+        for rel, p in files.items():
+            if type(sizes[rel]) is not int or p.stat().st_size != sizes[rel] or not _is_hex(digests[rel], 64):
+                return False
+            if verify_digests and file_sha256(p) != digests[rel]:
+                return False
+    except (OSError, RuntimeError, ValueError):
         return False
-    for rel, p in files.items():
-        if p.stat().st_size != sizes[rel]:
-            return False
-        if verify_digests and file_sha256(p) != digests[rel]:
-            return False
     return True
 
 
@@ -250,8 +322,8 @@ def write_manifest(path: Path, *, artifact_kind: str, checkpoint_id: str, global
     files = artifact_files(path, artifact_kind, has_optimizer_state)
     manifest = {
         "format": BUNDLE_FORMAT, "format_version": BUNDLE_FORMAT_VERSION, "artifact_kind": artifact_kind,
-        "artifact_sizes": {str(p.relative_to(path)): p.stat().st_size for p in files},
-        "artifact_digests": {str(p.relative_to(path)): file_sha256(p) for p in files},
+        "artifact_sizes": {p.relative_to(path).as_posix(): p.stat().st_size for p in files},
+        "artifact_digests": {p.relative_to(path).as_posix(): file_sha256(p) for p in files},
         "checkpoint_id": checkpoint_id, "global_step": int(global_step), "total_steps": int(total_steps),
         "has_optimizer_state": bool(has_optimizer_state), "source_examples_seen": int(source_examples_seen),
         "streaming_data_digest": streaming_data_digest, "training_complete": bool(training_complete),

@@ -40,7 +40,18 @@ def _digest(paths: list[Path]) -> str:
         h.update(p.name.encode())
         h.update(p.read_bytes())
     h.update(" ".join(NVCC_FLAGS).encode())
+    h.update(_compiler_identity().encode())
     return h.hexdigest()
+
+
+def _compiler_identity() -> str:
+    """Release line of ``nvcc --version`` ("" without a compiler: a shipped library is then kept
+    as long as the sources match)."""
+    try:
+        out = subprocess.run([_nvcc(), "--version"], capture_output=True, text=True, timeout=60).stdout
+    except (RuntimeError, OSError, subprocess.SubprocessError):
+        return ""
+    return next((line.strip() for line in out.splitlines() if "release" in line), "")
 
 
 def sources() -> list[Path]:

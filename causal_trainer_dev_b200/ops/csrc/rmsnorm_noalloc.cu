@@ -187,6 +187,13 @@ extern "C" __attribute__((visibility("default"))) int ctb_rmsnorm_bwd_noalloc(
   if (d > CTB_NOALLOC_MAX_D)
     return refuse("rmsnorm_bwd_noalloc: d exceeds CTB_NOALLOC_MAX_D (8192), the size the static scratch was built for");
   if (!dy || !x || !w || !rstd || !dx) return refuse("rmsnorm_bwd_noalloc: dy, x, w, rstd and dx are required");
+  // The kernel moves rows in 16-byte vectors.  A pointer into the middle of a vector (a sliced
+  // view, an odd offset into a pool) would fault on the device, so it is refused here instead.
+  auto misaligned = [](const void* p, uintptr_t a) { return p != nullptr && (reinterpret_cast<uintptr_t>(p) % a) != 0; };
+  if (misaligned(dy, 16) || misaligned(x, 16) || misaligned(w, 16) || misaligned(dres, 16) || misaligned(dx, 16))
+    return refuse("rmsnorm_bwd_noalloc: dy, x, w, dres and dx must be 16-byte aligned");
+  if (misaligned(rstd, 4) || misaligned(dw, dw_f32 ? 4 : 2))
+    return refuse("rmsnorm_bwd_noalloc: rstd and dw must be aligned to their element size");
   float* table = nullptr;
   int sms = 0;
   if (table_for_current_device(&table, &sms)) return 1;   // first call on this device resolves the address

@@ -17,6 +17,9 @@
 //     still passes inputs (dy, x, w, rstd, optional dres) and outputs (dx, dw);
 //   * limit: d <= CTB_NOALLOC_MAX_D (8192) and d a multiple of 8; larger sizes are refused
 //     with a message (ctb_noalloc_last_error), nothing is launched;
+//   * dy, x, w, dres and dx are read and written in 16-byte vectors and must be 16-byte
+//     aligned (rstd and dw: aligned to their element); a misaligned pointer is refused the
+//     same way, before any launch;
 //   * cost: CTB_NOALLOC_MAX_PARTS * CTB_NOALLOC_MAX_D floats (9.5 MiB) of device memory on
 //     every GPU that loads the library, held until the process exits;
 //   * the first call on a device resolves the device address of the array (one

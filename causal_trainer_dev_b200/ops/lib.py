@@ -106,10 +106,25 @@ _SITES = {
 def device_status(raise_on_error: bool = True) -> tuple[int, int, int, int]:
     """Reads (and clears) the device status word written by bounded waits that gave up."""
     out = (ctypes.c_uint * 4)()
-    check(lib().ctb_status(out, stream_ptr()), "ctb_status")
+    if lib().ctb_status(out, stream_ptr()) != 0:        # launches nothing: not counted as a launch
+        raise KernelError(f"ctb_status: {lib().ctb_last_error().decode()}")
     code, block, d0, d1 = (int(x) for x in out)
     if code and raise_on_error:
         raise KernelError(
             f"device wait ran out: {_SITES.get(code, hex(code))} (block {block}, detail {d0}, {d1})"
         )
     return code, block, d0, d1
+
+
+def poll_device_status() -> KernelError | None:
+    """The production read of the status word: call it where a step's metrics have just been read
+    back (the stream is idle then, so the read costs one 16-byte copy).  Returns the error instead
+    of raising so that a caller with peers can put it to a vote first; None when every bounded
+    wait of the steps since the last poll completed, or when no GPU library is loaded."""
+    if not available():
+        return None
+    try:
+        device_status()
+    except KernelError as exc:
+        return exc
+    return None

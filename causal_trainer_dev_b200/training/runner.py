@@ -610,6 +610,14 @@ class TrainingRun:
                 micro.append({k: v[r0:r0 + sub] for k, v in rows.items()})
         return micro
 
+    def check_device_waits(self) -> None:
+        """Collective (all ranks reach it at the same steps): reads the status word the bounded
+        device waits write when they give up, and fails the run on every rank if any rank has a
+        record.  Called only where metrics were just read back, so the device is idle."""
+        from ..ops import lib as oplib
+
+        rt.raise_if_any_process_error(oplib.poll_device_status() if self.cuda else None, "device wait")
+
     # ---- the loop ----
     def train(self) -> None:
         a = self.args
@@ -648,10 +656,12 @@ class TrainingRun:
                 if self.streaming:
                     if self.vote_on_stream_batch(item[0] if item else None, error) == "eof":
                         break
-                elif error is not None:
+                else:
+                    # every rank takes part in the vote each iteration: a rank whose reader failed
+                    # must not be left alone in it while its peers enter the step's collectives
                     rt.raise_if_any_process_error(error, "read batch")
-                elif item is None:
-                    break
+                    if item is None:
+                        break
                 raw, micro = item
                 t0 = time.monotonic()
                 lr_position = None
@@ -672,12 +682,15 @@ class TrainingRun:
                     latest = window.drain()
                     if self.cuda:
                         torch.cuda.synchronize(self.device)
+                    self.check_device_waits()
                     tlog.log_step(latest, tracker, self.device if a.track_memory else None, wandb_run)
                 if a.save_steps and step % a.save_steps == 0 and step < self.plan.total_steps:
                     window.drain()
+                    self.check_device_waits()
                     self.save_bundle(out / f"checkpoint-{step}", step)
                     bundles.prune_periodic_exports(out, a.save_total_limit, self.signature)
             window.drain()
+            self.check_device_waits()
         profile = profiler.finish()
         if profile is not None and rt.process_index() == 0:
             log.info("profiled %(profiled_steps)d steps: %(ms_per_step).2f ms/step, %(tokens_per_second).0f tok/s, "

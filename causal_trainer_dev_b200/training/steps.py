@@ -79,6 +79,10 @@ class AutogradProducer:
     def __call__(self, batch, grad_scale, first):
         p = self.params
         opts = self.options
+        if first and self.lora is not None:
+            # adapter leaves accumulate in ``.grad`` over the micro-batches of ONE step only
+            for _, t in self.lora.trainable():
+                t.grad = None
         hidden = decoder_forward(
             p, batch["input_ids"], batch["attention_mask"], batch.get("segment_ids"), batch.get("position_ids"),
             batch.get("attention_end"), opts,

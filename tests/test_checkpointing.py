@@ -52,8 +52,12 @@ def _export(tmp_path, name="out", step=3, total=10, signature="sig", seed=0, opt
     params = ModelParams.init_random(cfg, seed=seed, dtype=torch.bfloat16)
     dest = tmp_path / name
 
+    from helpers import write_tokenizer
+
+    assets = write_tokenizer(tmp_path / "assets")
+
     def export_model(d, cid):
-        hfio.export_hf_checkpoint(d, hfio.TensorSource(cfg, params=params), checkpoint_id=cid)
+        hfio.export_hf_checkpoint(d, hfio.TensorSource(cfg, params=params), checkpoint_id=cid, assets_from=assets)
 
     export_opt = None
     if optimizer:
@@ -294,3 +298,27 @@ def test_tree_paths_map_onto_every_exported_tensor():
         with pytest.raises(KeyError):
             hfio.parameter_to_hf_mapping(bad)
     assert hfio.SafeTensorIndex is st.SafeTensorIndex and hfio.TensorInfo is st.TensorInfo
+
+
+def test_stray_files_do_not_invalidate_a_bundle_but_stale_weights_do(tmp_path):
+    _, _, dest = _export(tmp_path, name="out", step=10, total=10)
+    (dest / "train.log").write_text("noise")
+    (dest / "profile_steps.json").write_text("{}")
+    (dest / ".cache").mkdir()
+    (dest / ".cache" / "blob").write_text("x")
+    found = bundles.find_latest_checkpoint(dest, "sig")
+    assert found is not None and found.global_step == 10
+    manifest = json.loads((dest / bundles.MANIFEST_NAME).read_text())
+    assert "train.log" not in manifest["artifact_sizes"] and "model.safetensors" in manifest["artifact_sizes"]
+    assert "tokenizer.json" in manifest["artifact_sizes"] and "training_args.json" not in manifest["artifact_sizes"]
+    # adapter weights beside merged weights: the bundle cannot be trusted
+    (dest / "adapter_model.safetensors").write_bytes(b"\0" * 16)
+    with pytest.raises(ValueError, match="corrupt"):
+        bundles.find_latest_checkpoint(dest, "sig")
+    (dest / "adapter_model.safetensors").unlink()
+    # an optimizer directory the manifest does not announce
+    (dest / "optimizer").mkdir()
+    with pytest.raises(ValueError, match="corrupt"):
+        bundles.find_latest_checkpoint(dest, "sig")
+    with pytest.raises(RuntimeError, match="stale optimizer"):
+        bundles.artifact_files(dest, "merged", False)

@@ -244,3 +244,49 @@ def test_step_builder_functions_equal_the_hand_wired_steps():
         last = step.run([batch]).to_floats()["loss"]
     assert last < first and all(torch.equal(before[n], p.tensor(n)) for n in p.hf_names())
     assert len(step.optimizer.m) == 2 * 7 * cfg.num_hidden_layers
+
+
+def test_lora_gradients_do_not_leak_from_one_step_into_the_next():
+    """With lr = 0 and the same batch every step, the adapter gradient norm must not grow: each
+    optimizer step starts from empty adapter gradients.  Two micro-batches still accumulate."""
+    from causal_trainer_dev_b200.models.lora import LoraState
+    from causal_trainer_dev_b200.training.steps import make_lora_train_step
+
+    cfg = preset("tiny", vocab_size=300)
+    gen = torch.Generator().manual_seed(7)
+    ids = torch.randint(3, 300, (2, 16), generator=gen)
+    batch = dict(input_ids=ids, attention_mask=torch.ones(2, 16, dtype=torch.long))
+    p = ModelParams.init_random(cfg, 0, torch.float32)
+    lora = LoraState.init(cfg, 4, seed=1, dtype=torch.float32)
+    with torch.no_grad():
+        for b in lora.b.values():
+            b.normal_(0, 0.02, generator=gen)
+    step = make_lora_train_step(p, lora, ForwardOptions(), adamw=AdamWConfig(0.0, max_grad_norm=0.0),
+                                schedule=ScheduleConfig(0.0, 0, "constant", 0, 8))
+    norms = [step.run([batch]).to_floats()["grad_norm"] for _ in range(3)]
+    assert norms[0] > 0 and norms[1] == norms[0] and norms[2] == norms[0]
+    halves = [{k: v[i:i + 1] for k, v in batch.items()} for i in range(2)]
+    assert abs(step.run(halves).to_floats()["grad_norm"] - norms[0]) < 1e-5 * norms[0]
+
+    # a trajectory against torch.optim.AdamW on the same leaves
+    lora2 = LoraState.init(cfg, 4, seed=1, dtype=torch.float32)
+    ref = LoraState.init(cfg, 4, seed=1, dtype=torch.float32)
+    with torch.no_grad():
+        for k in lora2.b:
+            lora2.b[k].normal_(0, 0.02, generator=torch.Generator().manual_seed(3))
+            ref.b[k].copy_(lora2.b[k])
+    ours = make_lora_train_step(p, lora2, ForwardOptions(), adamw=AdamWConfig(0.0, max_grad_norm=0.0),
+                                schedule=ScheduleConfig(1e-3, 0, "constant", 0, 8))
+    leaves = [t for _, t in ref.trainable()]
+    opt = torch.optim.AdamW(leaves, lr=1e-3, betas=(0.9, 0.999), eps=1e-8, weight_decay=0.0)
+    from causal_trainer_dev_b200.training import losses
+    from causal_trainer_dev_b200.models.decoder import decoder_forward
+    for _ in range(3):
+        ours.run([batch])
+        opt.zero_grad()
+        hidden = decoder_forward(p, batch["input_ids"], batch["attention_mask"], None, None, None, ForwardOptions(lora=ref))
+        nll, wsum = losses.causal_lm_loss(hidden, p.units["final"].view("lm_head"), batch)
+        (nll / wsum).backward()
+        opt.step()
+    for (_, a), (_, b) in zip(lora2.trainable(), ref.trainable()):
+        assert torch.allclose(a, b, atol=2e-6, rtol=1e-4)
