@@ -38,6 +38,9 @@ class TrainerConfig:
     tp: int = 1                        # tensor-parallel degree; ranks are laid out (fsdp, tp) with tp fastest
     sp: int = 1                        # sequence-parallel degree (queries sharded, K/V all-gathered); needs tp == 1
     force_sharded_runtime: bool = False  # run the FSDP runtime even on one rank (measures its own overhead)
+    frozen: tuple[str, ...] = ()       # components held fixed: any of "lm_head", "embed", "norm"
+    loss_backend: str = "cut"          # "cut": projection-fused; "logits": bf16 logits slab per row chunk
+    attention_options: object | None = None   # models.moba.AttentionOptions for MoBA layers
 
 
 class Trainer:
@@ -66,9 +69,8 @@ class Trainer:
             shard_group = self.lattice.group(("fsdp", "sp"))      # sp ranks are further FSDP ranks
             sp_group = self.lattice.group(("sp",))
             self.data_rank, self.data_world = self.lattice.coords()["fsdp"], self.world // self.cfg.sp
-            self.runtime = FsdpRuntime(model, self.cfg, self.device, group=shard_group)
-            self.engine = SpLayerwiseEngine(model, sp_group, self.runtime,
-                                            EngineOptions(cut_chunk_rows=self.cfg.cut_chunk_rows, remat=self.cfg.remat))
+            self.runtime = FsdpRuntime(model, self.cfg, self.device, group=shard_group, frozen=self.cfg.frozen)
+            self.engine = SpLayerwiseEngine(model, sp_group, self.runtime, self._engine_options())
             self.step_fn = self.runtime.make_step(self.engine)
         elif self.cfg.tp > 1:
             from .parallel.fsdp import FsdpRuntime
@@ -83,23 +85,30 @@ class Trainer:
             tp_group = self.lattice.group(("tp",))
             self.data_rank, self.data_world = self.lattice.coords()["fsdp"], self.world // self.cfg.tp
             local = tp_local_config(model, self.cfg.tp)
+            if self.cfg.frozen:
+                raise ValueError("frozen components are not supported together with tensor parallelism")
             self.runtime = FsdpRuntime(local, self.cfg, self.device, group=fsdp_group, full_cfg=model, tp_group=tp_group)
-            self.engine = TpLayerwiseEngine(model, tp_group, self.runtime,
-                                            EngineOptions(cut_chunk_rows=self.cfg.cut_chunk_rows, remat=self.cfg.remat),
+            self.engine = TpLayerwiseEngine(model, tp_group, self.runtime, self._engine_options(),
                                             fused=self.cfg.fused_collectives)
             self.step_fn = self.runtime.make_step(self.engine)
         elif (self.world > 1 or self.cfg.force_sharded_runtime) and self.cfg.fsdp:
             from .parallel.fsdp import FsdpRuntime
 
-            self.runtime = FsdpRuntime(model, self.cfg, self.device)
-            self.engine = LayerwiseEngine(model, self.runtime, EngineOptions(cut_chunk_rows=self.cfg.cut_chunk_rows, remat=self.cfg.remat))
+            self.runtime = FsdpRuntime(model, self.cfg, self.device, frozen=self.cfg.frozen)
+            self.engine = LayerwiseEngine(model, self.runtime, self._engine_options())
             self.step_fn = self.runtime.make_step(self.engine)
         else:
             self.params = self._init_params()
             self.provider = LocalProvider(self.params, torch.bfloat16)
-            self.engine = LayerwiseEngine(model, self.provider, EngineOptions(cut_chunk_rows=self.cfg.cut_chunk_rows, remat=self.cfg.remat))
-            self.step_fn = TrainStep(self.params, self.engine, self.cfg.adamw, self.cfg.schedule)
+            self.engine = LayerwiseEngine(model, self.provider, self._engine_options())
+            self.step_fn = TrainStep(self.params, self.engine, self.cfg.adamw, self.cfg.schedule, frozen=self.cfg.frozen)
         self._accum_checked = False
+
+    def _engine_options(self) -> EngineOptions:
+        c = self.cfg
+        return EngineOptions(cut_chunk_rows=c.cut_chunk_rows, remat=c.remat, train_lm_head="lm_head" not in c.frozen,
+                             train_embed="embed" not in c.frozen, train_norm="norm" not in c.frozen,
+                             loss_backend=c.loss_backend, attention_options=c.attention_options)
 
     def _init_params(self) -> ModelParams:
         if self.cfg.init == "hf":

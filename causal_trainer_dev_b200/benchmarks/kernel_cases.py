@@ -1,7 +1,7 @@
 """Small, self-terminating single-kernel workloads for profiling and roofline numbers.
 
     python -m causal_trainer_dev_b200.benchmarks.kernel_cases \
-        gemm|dgrad|wgrad|layer_gemms|attn_fwd|attn_bwd|moba [one-document|coherent]|cut_ce|rmsnorm|adamw
+        gemm|dgrad|wgrad|layer_gemms|attn_fwd|attn_bwd|moba [one-document|coherent]|cut_ce|rmsnorm|adamw|adamw_arena
 
 Each case holds a few hundred MB (more than the 126 MB L2, far less than a GB-scale step),
 launches its kernel a handful of times, and prints device-timed milliseconds plus the achieved
@@ -171,6 +171,19 @@ def main() -> None:
         ms = timed(lambda: E.adamw_update(p, g, m, v, lr=1e-4, b1=0.9, b2=0.999, eps=1e-8, decay=0.1, step=2, clip=clip))
         gbs = 7.0 * n * 2 / ms / 1e6
         out.update(ms=ms, gbs=gbs, fraction_of_measured_copy_bandwidth=gbs / pk["hbm_gbs"])
+    elif case == "adamw_arena":
+        # the sharded runtime's sweep: one launch over a flat arena cut into decay / no-decay regions
+        n = 1 << 28
+        p, g, m, v = (torch.randn(n, device=dev).bfloat16() for _ in range(4))
+        v.abs_()
+        clip = torch.ones(1, device=dev)
+        cuts = sorted({0, n, *(int(x) // 8 * 8 for x in torch.linspace(0, n, 70).tolist())})
+        bounds = torch.tensor(cuts, dtype=torch.int64, device=dev)
+        modes = torch.tensor([i % 2 for i in range(len(cuts) - 1)], dtype=torch.int32, device=dev)
+        ms = timed(lambda: E.adamw_regions(p, g, m, v, bounds, modes, lr=1e-4, b1=0.9, b2=0.999, eps=1e-8, decay=0.1,
+                                           step=2, clip=clip))
+        gbs = 7.0 * n * 2 / ms / 1e6
+        out.update(ms=ms, gbs=gbs, fraction_of_measured_copy_bandwidth=gbs / pk["hbm_gbs"], elements=n)
     else:
         raise SystemExit(f"unknown case {case}")
     print(json.dumps(out))

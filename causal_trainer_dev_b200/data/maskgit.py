@@ -14,17 +14,123 @@ as MaskGIT this step.  A selected grid gets:
 Everything else stays next-token prediction.  All randomness is a pure function of
 ``(seed, absolute optimizer step)`` and the draw order is fixed (selection, ratio, choice), so
 a resumed run sees the same masks (src/causal_trainer/data/maskgit.py:20-135).
+
+The work is split in two: :class:`GridFinder` turns a token row into a list of
+:class:`Grid` spans (a scan over *runs* of code tokens, no randomness), and
+:class:`MaskGITBatchTransform` draws the masks for those spans and edits the batch arrays.
 """
 from __future__ import annotations
 
 import math
 import re
+from dataclasses import dataclass
 from typing import Iterator, Mapping
 
 import numpy as np
 
-_IMAGE_TOKEN = re.compile(r"<\|image_[0-9]+\|>\Z")
-_REQUIRED = ("[MASK]", "<|im_start|>", "<|im_end|>")
+_CODE_NAME = re.compile(r"<\|image_[0-9]+\|>\Z")
+_MARKERS = ("[MASK]", "<|im_start|>", "<|im_end|>")
+_NEWLINES = ("\n", "\r\n")
+_HEADER_TOKENS = 32          # how far into a turn the role header is looked for
+_SEPARATOR_TOKENS = 8        # a row separator longer than this many tokens is not a newline
+
+
+@dataclass(frozen=True)
+class Grid:
+    """One rectangular block of image codes inside an assistant turn."""
+    positions: np.ndarray      # indices of the code tokens, ascending
+
+    @property
+    def first(self) -> int:
+        return int(self.positions[0])
+
+    @property
+    def stop(self) -> int:
+        return int(self.positions[-1]) + 1
+
+
+class GridFinder:
+    """Locates image grids in one token row.  Text decisions (is this gap a newline? does this
+    turn belong to the assistant?) go through the tokenizer's decoder and are memoised by token
+    ids, so a batch of similar rows decodes each distinct piece once."""
+
+    def __init__(self, tokenizer, code_table: np.ndarray, start_id: int, end_id: int):
+        self.tokenizer = tokenizer
+        self.code_table = code_table
+        self.start_id, self.end_id = start_id, end_id
+        self._text: dict[tuple[int, ...], str] = {}
+
+    def _decoded(self, ids: np.ndarray) -> str:
+        key = tuple(int(i) for i in ids)
+        text = self._text.get(key)
+        if text is None:
+            text = self._text[key] = self.tokenizer.decode(list(key))
+        return text
+
+    def is_code(self, tokens: np.ndarray) -> np.ndarray:
+        return self.code_table[np.clip(tokens, 0, len(self.code_table) - 1)] & (tokens >= 0) & (
+            tokens < len(self.code_table))
+
+    def _documents(self, valid: np.ndarray, segments: np.ndarray) -> Iterator[tuple[int, int]]:
+        """Maximal spans of attended tokens with one segment id."""
+        edge = np.empty(len(valid) + 1, dtype=bool)
+        edge[0] = edge[-1] = True
+        edge[1:-1] = (segments[1:] != segments[:-1]) | (valid[1:] != valid[:-1])
+        cut = np.flatnonzero(edge)
+        for a, b in zip(cut[:-1], cut[1:]):
+            if valid[a]:
+                yield int(a), int(b)
+
+    def _assistant_turns(self, tokens: np.ndarray, a: int, b: int) -> Iterator[tuple[int, int]]:
+        """``(index of <|im_start|>, index of its <|im_end|>)`` for closed assistant turns of a document."""
+        opens = a + np.flatnonzero(tokens[a:b] == self.start_id)
+        closes = a + np.flatnonzero(tokens[a:b] == self.end_id)
+        if not len(opens) or not len(closes):
+            return
+        # the first close after each open must come before the next open (else the turn was cut off)
+        nxt = np.append(opens[1:], b)
+        which = np.searchsorted(closes, opens)
+        for o, limit, w in zip(opens, nxt, which):
+            if w < len(closes) and closes[w] < limit:
+                close = int(closes[w])
+                header = self._decoded(tokens[o + 1:min(close, o + 1 + _HEADER_TOKENS)])
+                if header.startswith(tuple("assistant" + nl for nl in _NEWLINES)):
+                    yield int(o), close
+
+    def _grids_of_turn(self, tokens: np.ndarray, code: np.ndarray, o: int, close: int) -> Iterator[Grid]:
+        inside = o + 1 + np.flatnonzero(code[o + 1:close])
+        if not len(inside):
+            return
+        # runs of adjacent codes = grid rows; a run boundary is a newline (same grid) or anything else (new grid)
+        breaks = np.flatnonzero(np.diff(inside) != 1) + 1
+        run_first = np.concatenate(([0], breaks))
+        run_stop = np.concatenate((breaks, [len(inside)]))
+        rows: list[tuple[int, int]] = []
+
+        def close_grid() -> Grid:
+            widths = {stop - first for first, stop in rows}
+            if len(widths) != 1:
+                raise ValueError("assistant image grid has unequal row widths")
+            return Grid(inside[rows[0][0]:rows[-1][1]])
+
+        for r, (first, stop) in enumerate(zip(run_first, run_stop)):
+            if rows:
+                gap = tokens[inside[rows[-1][1] - 1] + 1:inside[first]]
+                if len(gap) > _SEPARATOR_TOKENS or self._decoded(gap) not in _NEWLINES:
+                    yield close_grid()
+                    rows = []
+            rows.append((int(first), int(stop)))
+        yield close_grid()
+
+    def grids(self, tokens: np.ndarray, valid: np.ndarray, segments: np.ndarray) -> list[Grid]:
+        code = self.is_code(tokens)
+        if not code.any():
+            return []
+        found: list[Grid] = []
+        for a, b in self._documents(valid, segments):
+            for o, close in self._assistant_turns(tokens, a, b):
+                found.extend(self._grids_of_turn(tokens, code, o, close))
+        return found
 
 
 class MaskGITBatchTransform:
@@ -33,90 +139,67 @@ class MaskGITBatchTransform:
             raise ValueError("maskgit_probability must be between 0 and 1")
         self.probability, self.seed, self.tokenizer = probability, seed, tokenizer
         vocab = tokenizer.get_vocab()
-        for tok in _REQUIRED:
-            if tok not in vocab or tokenizer(tok)["input_ids"] != [vocab[tok]]:
-                raise ValueError(f"MaskGIT requires {tok!r} to encode as one token")
-        self.mask_id, self.start_id, self.end_id = (vocab[t] for t in _REQUIRED)
-        image_ids = [i for t, i in vocab.items() if _IMAGE_TOKEN.fullmatch(t)]
-        if not image_ids:
-            raise ValueError("MaskGIT requires <|image_i|> tokens in the tokenizer vocabulary")
-        top = max(max(vocab.values()), getattr(tokenizer, "pad_token_id", None) or 0)
-        self.is_image = np.zeros(top + 1, dtype=bool)
-        self.is_image[image_ids] = True
-
-    # ------------------------------------------------------------------ grid discovery
-    def _grids_in_message(self, tokens: np.ndarray, start: int, end: int) -> Iterator[np.ndarray]:
-        """Index arrays of the rectangular code grids between ``start`` and ``end`` (one assistant turn)."""
-        codes = start + 1 + np.flatnonzero(self.is_image[tokens[start + 1:end]])
+        ids = []
+        for marker in _MARKERS:
+            if marker not in vocab or tokenizer(marker)["input_ids"] != [vocab[marker]]:
+                raise ValueError(f"MaskGIT requires {marker!r} to encode as one token")
+            ids.append(vocab[marker])
+        self.mask_id, self.start_id, self.end_id = ids
+        codes = np.fromiter((i for name, i in vocab.items() if _CODE_NAME.fullmatch(name)), dtype=np.int64)
         if not len(codes):
-            return
-        cuts, row_breaks = [0], []
-        for g in np.flatnonzero(np.diff(codes) > 1):
-            between = tokens[codes[g] + 1:codes[g + 1]]
-            text = self.tokenizer.decode(between[:8].tolist()) if len(between) <= 8 else None
-            (row_breaks if text in ("\n", "\r\n") else cuts).append(int(g) + 1)
-        cuts.append(len(codes))
-        for first, last in zip(cuts[:-1], cuts[1:]):
-            edges = [first, *(r for r in row_breaks if first < r < last), last]
-            widths = np.diff(edges)
-            if np.any(widths != widths[0]):
-                raise ValueError("assistant image grid has unequal row widths")
-            yield codes[first:last]
+            raise ValueError("MaskGIT requires <|image_i|> tokens in the tokenizer vocabulary")
+        size = max(max(vocab.values()), getattr(tokenizer, "pad_token_id", None) or 0) + 1
+        self.is_image = np.zeros(size, dtype=bool)
+        self.is_image[codes] = True
+        self.finder = GridFinder(tokenizer, self.is_image, self.start_id, self.end_id)
 
-    def _blocks(self, tokens: np.ndarray, valid: np.ndarray, segments: np.ndarray):
-        if not self.is_image[np.clip(tokens, 0, len(self.is_image) - 1)].any():
-            return
-        change = (segments[1:] != segments[:-1]) | (valid[1:] != valid[:-1])
-        bounds = np.flatnonzero(np.r_[True, change, True])
-        for left, right in zip(bounds[:-1], bounds[1:]):
-            if not valid[left]:
-                continue
-            starts = left + np.flatnonzero(tokens[left:right] == self.start_id)
-            ends = left + np.flatnonzero(tokens[left:right] == self.end_id)
-            for n, s in enumerate(starts):
-                limit = starts[n + 1] if n + 1 < len(starts) else right
-                e = np.searchsorted(ends, s)
-                if e == len(ends) or ends[e] >= limit:
-                    continue  # unclosed (e.g. truncated) turn stays autoregressive
-                end = int(ends[e])
-                header = self.tokenizer.decode(tokens[s + 1:min(end, s + 33)].tolist())
-                if not header.startswith(("assistant\n", "assistant\r\n")):
-                    continue
-                for grid in self._grids_in_message(tokens, int(s), end):
-                    yield int(grid[0]), int(grid[-1]) + 1, grid
+    def _draw(self, rng: np.random.Generator, grid: Grid) -> np.ndarray | None:
+        """The masked positions of ``grid`` for this step, or None when the coin says autoregressive.
+        Draw order (a resume contract): selection, then ratio, then the choice of positions."""
+        if rng.random() >= self.probability:
+            return None
+        n = len(grid.positions)
+        count = max(1, math.ceil(n * math.cos(0.5 * math.pi * rng.random())))
+        return rng.choice(grid.positions, size=count, replace=False)
 
-    # ------------------------------------------------------------------ transform
     def __call__(self, batch: Mapping[str, np.ndarray], *, step: int) -> dict[str, np.ndarray]:
         if self.probability == 0.0:
             return dict(batch)
-        original = np.asarray(batch["input_ids"], dtype=np.int32)
-        valid = np.asarray(batch["attention_mask"]) != 0
+        source = np.asarray(batch["input_ids"], dtype=np.int32)
+        attended = np.asarray(batch["attention_mask"]) != 0
         segments = np.asarray(batch["segment_ids"])
         weights = np.asarray(batch["loss_weights"], dtype=np.float32)
-        tokens = original.copy()
-        targets = np.zeros_like(original)
-        pw = np.zeros_like(weights)
-        targets[:, :-1] = original[:, 1:]
-        pw[:, :-1] = weights[:, 1:] * (valid[:, :-1] & valid[:, 1:] & (segments[:, :-1] == segments[:, 1:]))
-        attention_end = np.broadcast_to(np.arange(original.shape[1], dtype=np.int32), original.shape).copy()
+        rows, length = source.shape
+
+        # next-token defaults: position i predicts token i + 1 inside one attended document
+        same_doc = attended[:, :-1] & attended[:, 1:] & (segments[:, :-1] == segments[:, 1:])
+        targets = np.concatenate([source[:, 1:], np.zeros((rows, 1), source.dtype)], axis=1)
+        pred_w = np.concatenate([weights[:, 1:] * same_doc, np.zeros((rows, 1), np.float32)], axis=1).astype(np.float32)
+        tokens = source.copy()
+        attention_end = np.tile(np.arange(length, dtype=np.int32), (rows, 1))
+
         rng = np.random.default_rng(np.random.SeedSequence([self.seed, step]))
-        for row in range(len(original)):
-            for start, end, grid in self._blocks(original[row], valid[row], segments[row]):
-                if not np.any(weights[row, grid] > 0) or rng.random() >= self.probability:
+        for r in range(rows):
+            for grid in self.finder.grids(source[r], attended[r], segments[r]):
+                if not (weights[r, grid.positions] > 0).any():
+                    continue                      # unsupervised grid: no draw at all
+                masked = self._draw(rng, grid)
+                if masked is None:
                     continue
-                count = max(1, math.ceil(len(grid) * math.cos(math.pi * 0.5 * rng.random())))
-                masked = rng.choice(grid, size=count, replace=False)
-                tokens[row, masked] = self.mask_id
-                attention_end[row, start:end] = end - 1
-                pw[row, max(0, start - 1):end] = 0.0
-                targets[row, masked] = original[row, masked]
-                pw[row, masked] = weights[row, masked]
-        return {**batch, "input_ids": tokens, "attention_end": attention_end, "prediction_targets": targets,
-                "prediction_weights": pw}
+                a, b = grid.first, grid.stop
+                attention_end[r, a:b] = b - 1                    # block-local bidirectional attention
+                pred_w[r, max(a - 1, 0):b] = 0.0                 # no next-token edge into, inside or out of the block
+                tokens[r, masked] = self.mask_id
+                targets[r, masked] = source[r, masked]           # same-position reconstruction
+                pred_w[r, masked] = weights[r, masked]
+        out = dict(batch)
+        out.update(input_ids=tokens, attention_end=attention_end, prediction_targets=targets, prediction_weights=pred_w)
+        return out
 
     def batches(self, batches, *, start_step: int) -> Iterator:
-        for step, batch in enumerate(batches, start=start_step):
-            if isinstance(batch, Mapping):
-                yield self(batch, step=step)
-            else:
-                yield batch.with_data(self(batch.data, step=step))
+        """Applies the transform to a stream of host batches (plain mappings or envelopes with
+        ``data`` / ``with_data``), numbering them from the absolute optimizer step ``start_step``."""
+        step = start_step
+        for item in batches:
+            yield self(item, step=step) if isinstance(item, Mapping) else item.with_data(self(item.data, step=step))
+            step += 1

@@ -64,8 +64,11 @@ def chunked_cross_entropy(hidden, head, targets, weights, token_budget: int = 40
     return total, weights.float().sum()
 
 
-def cut_ce_forward(hidden, head, targets, weights, grad_scale: float = 1.0, exchange=None):
+def cut_ce_forward(hidden, head, targets, weights, grad_scale: float | torch.Tensor = 1.0, exchange=None):
     """Returns (nll_sum, weight_sum, lse, coef); coef = weights * grad_scale for the backward.
+
+    ``grad_scale`` may be a one-element device tensor (the reciprocal of a token count that was
+    just all-reduced): it is applied on the device, so the caller never has to read it back.
 
     With ``exchange`` (vocabulary-parallel head: ``head`` holds this rank's vocabulary rows and
     ``targets`` are already relative to them, -1 elsewhere) the per-row statistics are combined
@@ -75,6 +78,9 @@ def cut_ce_forward(hidden, head, targets, weights, grad_scale: float = 1.0, exch
     vocab = head.shape[0]
     slabs = (vocab + SLAB - 1) // SLAB
     dev = hidden.device
+    scale_on_device = grad_scale if isinstance(grad_scale, torch.Tensor) else None
+    if scale_on_device is not None:
+        grad_scale = 1.0
     pmax = torch.empty((slabs, rows), dtype=torch.float32, device=dev)
     psum = torch.empty((slabs, rows), dtype=torch.float32, device=dev)
     tlogit = torch.zeros(rows, dtype=torch.float32, device=dev)
@@ -91,7 +97,10 @@ def cut_ce_forward(hidden, head, targets, weights, grad_scale: float = 1.0, exch
                           _lib.ptr(tlogit), *_flag_args(hit), *_flag_args(hit_a), m_rotate, _lib.stream_ptr())
     _lib.check(code, "ctb_ce_stats")
     if exchange is not None:
-        return exchange.ce_exchange(pmax, psum, slabs, tlogit, w, grad_scale)
+        nll, wsum, lse, coef = exchange.ce_exchange(pmax, psum, slabs, tlogit, w, grad_scale)
+        if scale_on_device is not None:
+            coef.mul_(scale_on_device.reshape(()).to(coef.dtype))
+        return nll, wsum, lse, coef
     lse = torch.empty(rows, dtype=torch.float32, device=dev)
     coef = torch.empty(rows, dtype=torch.float32, device=dev)
     nblk = (rows + 255) // 256
@@ -101,6 +110,8 @@ def cut_ce_forward(hidden, head, targets, weights, grad_scale: float = 1.0, exch
                             ctypes.c_float(grad_scale), _lib.ptr(lse), _lib.ptr(coef), _lib.ptr(bn), _lib.ptr(bw),
                             rows, _lib.stream_ptr())
     _lib.check(code, "ctb_ce_combine")
+    if scale_on_device is not None:
+        coef.mul_(scale_on_device.reshape(()).to(coef.dtype))
     return bn.sum(), bw.sum(), lse, coef
 
 

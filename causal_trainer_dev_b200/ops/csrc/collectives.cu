@@ -115,6 +115,43 @@ ag_pull_kernel(PeerPtrs shards, __nv_bfloat16* __restrict__ gathered, long shard
 }
 
 // ------------------------------------------------------------------------------------------
+// embedding rows straight from the shards that own them (all-gather + gather in one kernel)
+// ------------------------------------------------------------------------------------------
+// The embedding unit is a flat buffer cut into `world` equal shards; element e of the unit lives
+// on rank e / shard_elems.  Each thread moves one 16-byte vector of one token's row with a plain
+// peer load, so a step moves tokens x d elements over NVLink instead of the whole table.
+__global__ void __launch_bounds__(PULL_THREADS)
+embed_gather_peer_kernel(const int* __restrict__ ids, PeerPtrs shards, long shard_elems, long table_offset,
+                         __nv_bfloat16* __restrict__ out, long T, int d, int vocab) {
+  const int nvec = d / 8;
+  const long total = T * nvec;
+  constexpr int UNR = 4;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  for (long i0 = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i0 < total; i0 += stride * UNR) {
+    uint4 r[UNR];
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const long i = i0 + u * stride;
+      if (i < total) {
+        const long t = i / nvec;
+        const int v = static_cast<int>(i % nvec);
+        int id = ids[t];
+        id = id < 0 ? 0 : (id >= vocab ? vocab - 1 : id);
+        const long e = table_offset + static_cast<long>(id) * d + static_cast<long>(v) * 8;
+        const int src = static_cast<int>(e / shard_elems);
+        r[u] = ld_peer(reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(shards.p[src]) +
+                                                      (e - static_cast<long>(src) * shard_elems)));
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < UNR; ++u) {
+      const long i = i0 + u * stride;
+      if (i < total) reinterpret_cast<uint4*>(out)[i] = r[u];
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------
 // flags: publish to peers / wait locally
 // ------------------------------------------------------------------------------------------
 __global__ void signal_peers_kernel(PeerFlagPtrs pads, int world, int index, unsigned epoch) {
@@ -361,6 +398,26 @@ CTB_API int ctb_rs_reduce(const void* const* staging_ptrs, long shard_offset, lo
   a.done_index = done_index; a.finish_counter = finish_counter;
   a.budget = budget > 0 ? budget : CTB_SPIN_BUDGET; a.status = device_status();
   rs_reduce_kernel<<<ctas, PULL_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(a);
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// out[t] = table[ids[t]] where the table starts `table_offset` elements into a unit that is split
+// into `world` shards of `shard_elems` elements (shard_ptrs[r] = rank r's shard).
+CTB_API int ctb_embed_gather_peer(const int* ids, const void* const* shard_ptrs, int world, long shard_elems,
+                                  long table_offset, void* out, long T, int d, int vocab, void* stream) {
+  if (world > MAX_RANKS) return fail("embed_gather_peer: too many ranks");
+  if (d % 8 || shard_elems % 8 || table_offset % 8) return fail("embed_gather_peer: rows and shards must be 16-byte multiples");
+  if (table_offset + static_cast<long>(vocab) * d > shard_elems * world) return fail("embed_gather_peer: table exceeds the unit");
+  if (T <= 0) return 0;
+  PeerPtrs pp{};
+  for (int i = 0; i < world; ++i) pp.p[i] = shard_ptrs[i];
+  const long work = T * (d / 8);
+  long blocks = (work + PULL_THREADS * 4 - 1) / (PULL_THREADS * 4);
+  const long cap = static_cast<long>(sm_count()) * 4;
+  if (blocks > cap) blocks = cap;
+  embed_gather_peer_kernel<<<static_cast<unsigned>(blocks), PULL_THREADS, 0, static_cast<cudaStream_t>(stream)>>>(
+      ids, pp, shard_elems, table_offset, static_cast<__nv_bfloat16*>(out), T, d, vocab);
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
 }

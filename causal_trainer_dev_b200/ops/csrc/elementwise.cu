@@ -529,6 +529,101 @@ __global__ void adamw_kernel(__nv_bfloat16* __restrict__ p, const GT* __restrict
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// AdamW over a whole flat arena in one launch.  The arena is a sequence of regions
+// [bounds[r], bounds[r+1]) with a mode each: 1 = weight decay, 0 = no decay, -1 = frozen (the
+// region is skipped: no update, moments untouched).  16-byte accesses: eight elements of the
+// parameter, both moments and the gradient per thread per round, two rounds in flight.
+// ------------------------------------------------------------------------------------------
+constexpr int ADAM_MAX_REGIONS = 512;
+
+__device__ __forceinline__ float fast_sqrt(float x) {
+  float y;
+  asm("sqrt.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_rcp(float x) {
+  float y;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <typename GT>
+__global__ void __launch_bounds__(256)
+adamw_regions_kernel(__nv_bfloat16* __restrict__ p, const GT* __restrict__ g, __nv_bfloat16* __restrict__ m,
+                     __nv_bfloat16* __restrict__ v, long n, const long* __restrict__ bounds,
+                     const int* __restrict__ modes, int nreg, float lr, float b1, float b2, float eps, float decay,
+                     float bc1, float bc2, const float* __restrict__ clip, float gscale, int round_bf16) {
+  __shared__ long sb[ADAM_MAX_REGIONS + 1];
+  __shared__ int sm[ADAM_MAX_REGIONS];
+  for (int i = threadIdx.x; i <= nreg; i += blockDim.x) sb[i] = bounds[i];
+  for (int i = threadIdx.x; i < nreg; i += blockDim.x) sm[i] = modes[i];
+  __syncthreads();
+  const float cs = (clip ? *clip : 1.f) * gscale;
+  const float inv_bc1 = 1.f / bc1, inv_bc2 = 1.f / bc2;
+  auto region_of = [&](long e) {
+    int lo = 0, hi = nreg - 1;
+    while (lo < hi) {
+      const int mid = (lo + hi + 1) >> 1;
+      if (sb[mid] <= e) lo = mid; else hi = mid - 1;
+    }
+    return lo;
+  };
+  const long nvec = n / 8;
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x;
+  int cached = 0;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < nvec; i += stride) {
+    const long e0 = i * 8;
+    if (!(sb[cached] <= e0 && e0 < sb[cached + 1])) cached = region_of(e0);
+    const bool uniform = sb[cached + 1] >= e0 + 8;
+    if (uniform && sm[cached] < 0) continue;
+    uint4 pr = reinterpret_cast<const uint4*>(p)[i];
+    uint4 mr = reinterpret_cast<const uint4*>(m)[i];
+    uint4 vr = reinterpret_cast<const uint4*>(v)[i];
+    float gf[8];
+    if constexpr (sizeof(GT) == 4) {
+      const float4 g0 = reinterpret_cast<const float4*>(g)[2 * i];
+      const float4 g1 = reinterpret_cast<const float4*>(g)[2 * i + 1];
+      gf[0] = g0.x; gf[1] = g0.y; gf[2] = g0.z; gf[3] = g0.w;
+      gf[4] = g1.x; gf[5] = g1.y; gf[6] = g1.z; gf[7] = g1.w;
+      if (round_bf16) {
+#pragma unroll
+        for (int e = 0; e < 8; ++e) gf[e] = __bfloat162float(__float2bfloat16(gf[e]));
+      }
+    } else {
+      const uint4 gr = reinterpret_cast<const uint4*>(g)[i];
+      const __nv_bfloat162* gh = reinterpret_cast<const __nv_bfloat162*>(&gr);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float2 f = __bfloat1622float2(gh[e]);
+        gf[2 * e] = f.x;
+        gf[2 * e + 1] = f.y;
+      }
+    }
+    __nv_bfloat16* pe = reinterpret_cast<__nv_bfloat16*>(&pr);
+    __nv_bfloat16* me = reinterpret_cast<__nv_bfloat16*>(&mr);
+    __nv_bfloat16* ve = reinterpret_cast<__nv_bfloat16*>(&vr);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const int mode = uniform ? sm[cached] : sm[region_of(e0 + e)];
+      if (mode < 0) continue;
+      const float gi = gf[e] * cs;
+      const float mi = b1 * __bfloat162float(me[e]) + (1.f - b1) * gi;
+      const float vi = b2 * __bfloat162float(ve[e]) + (1.f - b2) * gi * gi;
+      const float pi = __bfloat162float(pe[e]);
+      // one sqrt.approx and one rcp.approx per element (2 ulp each, far below the bf16 rounding of the
+      // update): with IEEE division and square root the sweep is bound by instruction issue, not by HBM
+      const float upd = -lr * ((mi * inv_bc1) * fast_rcp(fast_sqrt(vi * inv_bc2) + eps) + (mode ? decay : 0.f) * pi);
+      me[e] = __float2bfloat16(mi);
+      ve[e] = __float2bfloat16(vi);
+      pe[e] = __float2bfloat16(pi + __bfloat162float(__float2bfloat16(upd)));
+    }
+    reinterpret_cast<uint4*>(p)[i] = pr;
+    reinterpret_cast<uint4*>(m)[i] = mr;
+    reinterpret_cast<uint4*>(v)[i] = vr;
+  }
+}
+
 }  // namespace ew
 }  // namespace ctb
 
@@ -719,6 +814,32 @@ CTB_API int ctb_adamw(void* p, const void* g, int g_f32, void* m, void* v, long 
                                                       static_cast<const __nv_bfloat16*>(g),
                                                       static_cast<__nv_bfloat16*>(m), static_cast<__nv_bfloat16*>(v), n,
                                                       lr, b1, b2, eps, decay, bc1, bc2, clip, gscale, 0);
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// AdamW over a flat arena of n elements (n % 8 == 0, 16-byte aligned bases) split into nreg
+// regions: bounds[nreg + 1] (device, ascending, bounds[0] = 0, bounds[nreg] = n) and
+// modes[nreg] (device: 1 decay, 0 no decay, -1 frozen).  One launch.
+CTB_API int ctb_adamw_regions(void* p, const void* g, int g_f32, void* m, void* v, long n, const long* bounds,
+                              const int* modes, int nreg, float lr, float b1, float b2, float eps, float decay,
+                              float bc1, float bc2, const float* clip, float gscale, int round_bf16, void* stream) {
+  if (n % 8) return fail("adamw_regions: the arena must be a whole number of 16-byte vectors");
+  if (nreg < 1 || nreg > ADAM_MAX_REGIONS) return fail("adamw_regions: between 1 and 512 regions");
+  auto misaligned = [](const void* q) { return (reinterpret_cast<uintptr_t>(q) & 15u) != 0; };
+  if (misaligned(p) || misaligned(g) || misaligned(m) || misaligned(v))
+    return fail("adamw_regions: parameter, gradient and moment arenas must be 16-byte aligned");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = grid_for(n / 8, 256, 8);
+  if (g_f32)
+    adamw_regions_kernel<float><<<grid, 256, 0, s>>>(
+        static_cast<__nv_bfloat16*>(p), static_cast<const float*>(g), static_cast<__nv_bfloat16*>(m),
+        static_cast<__nv_bfloat16*>(v), n, bounds, modes, nreg, lr, b1, b2, eps, decay, bc1, bc2, clip, gscale,
+        round_bf16);
+  else
+    adamw_regions_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
+        static_cast<__nv_bfloat16*>(p), static_cast<const __nv_bfloat16*>(g), static_cast<__nv_bfloat16*>(m),
+        static_cast<__nv_bfloat16*>(v), n, bounds, modes, nreg, lr, b1, b2, eps, decay, bc1, bc2, clip, gscale, 0);
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
 }

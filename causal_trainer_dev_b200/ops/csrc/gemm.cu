@@ -38,6 +38,10 @@ constexpr int B_STAGE = BN * BK * 2;   // 32 KiB
 constexpr int EPI_BUF = 128 * 128;     // 128 rows x 128 B
 constexpr int TQ = 4;                  // depth of the tile-index queue
 
+// Cycles producer warps spent waiting for chunk flags of gathered operands, summed over CTAs
+// since the last read (ctb_gemm_flag_wait_cycles): the exposed part of an all-gather -> GEMM.
+__device__ unsigned long long g_flag_wait_cycles = 0ull;
+
 // A CTA tile is TM row sub-tiles of 128 rows that share one B tile:
 //   TM = 1: 128 x 256 tiles, 4 pipeline stages of 48 KiB, the two 256-column TMEM slots double-
 //           buffer the accumulator (the epilogue of tile i overlaps the main loop of tile i+1);
@@ -260,7 +264,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           e0 = args.b_flag_base + static_cast<long>(tc.n0) * args.ldb;
           e1 = args.b_flag_base + static_cast<long>(nend - 1) * args.ldb + args.K;
         }
+        const long long w0 = clock64();
         ok = acquire_range(args.b_flags, args.b_flag_chunk, e0, e1, args.b_flag_epoch);
+        if (lane == 0) atomicAdd(&g_flag_wait_cycles, static_cast<unsigned long long>(clock64() - w0));
         if (!ok) break;
         fence_proxy_async_all();  // generic-proxy writes of the pull CTAs -> async-proxy reads below
       }
@@ -277,7 +283,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           e0 = args.a_flag_base + static_cast<long>(tc.m0) * args.lda;
           e1 = args.a_flag_base + static_cast<long>(mend - 1) * args.lda + args.K;
         }
+        const long long w0 = clock64();
         ok = acquire_range(args.a_flags, args.a_flag_chunk, e0, e1, args.a_flag_epoch);
+        if (lane == 0) atomicAdd(&g_flag_wait_cycles, static_cast<unsigned long long>(clock64() - w0));
         if (!ok) break;
         fence_proxy_async_all();
       }
@@ -892,4 +900,14 @@ CTB_API int ctb_gemm_set_split_k(int mode) {
   const int before = m;
   m = mode != 0 ? 1 : 0;
   return before;
+}
+
+// Sum over CTAs of the cycles GEMM producer warps waited for gathered-operand flags since the
+// previous call (the counter is cleared).  Synchronises the device; a diagnostic, not a hot path.
+CTB_API int ctb_gemm_flag_wait_cycles(unsigned long long* out) {
+  unsigned long long zero = 0ull;
+  CTB_CUDA_OK(cudaDeviceSynchronize());
+  CTB_CUDA_OK(cudaMemcpyFromSymbol(out, ctb::gemm::g_flag_wait_cycles, sizeof(*out)));
+  CTB_CUDA_OK(cudaMemcpyToSymbol(ctb::gemm::g_flag_wait_cycles, &zero, sizeof(zero)));
+  return 0;
 }

@@ -232,3 +232,16 @@ def adamw_update(p, g, m, v, *, lr, b1, b2, eps, decay, step, clip: torch.Tensor
         int(round_bf16), _lib.stream_ptr(),
     )
     _lib.check(code, "ctb_adamw")
+
+
+def adamw_regions(p, g, m, v, bounds: torch.Tensor, modes: torch.Tensor, *, lr, b1, b2, eps, decay, step,
+                  clip: torch.Tensor | None = None, gscale=1.0, round_bf16: bool = False) -> None:
+    """AdamW over a flat bf16 arena in ONE launch (16-byte accesses).  ``bounds`` (int64, device,
+    ``[R + 1]``) cuts the arena into regions and ``modes`` (int32, device, ``[R]``) says what each
+    gets: 1 weight decay, 0 no decay, -1 frozen (skipped, moments untouched).  Same arithmetic as
+    :func:`adamw_update` (src/causal_trainer/training/optimizer.py:42-75)."""
+    code = _lib.lib().ctb_adamw_regions(
+        _lib.ptr(p), _lib.ptr(g), int(g.dtype == torch.float32), _lib.ptr(m), _lib.ptr(v), _l(p.numel()),
+        _lib.ptr(bounds), _lib.ptr(modes), int(modes.numel()), _f(lr), _f(b1), _f(b2), _f(eps), _f(decay),
+        _f(1 - b1 ** step), _f(1 - b2 ** step), _lib.ptr(clip), _f(gscale), int(round_bf16), _lib.stream_ptr())
+    _lib.check(code, "ctb_adamw_regions")

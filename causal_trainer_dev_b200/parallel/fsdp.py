@@ -80,9 +80,13 @@ class FsdpRuntime:
     """Weight provider (see ``training.engine``) plus the sharded optimizer step."""
 
     def __init__(self, cfg: ModelConfig, tcfg, device: torch.device, group=None, full_cfg: ModelConfig | None = None,
-                 tp_group=None, resident: str = "auto"):
+                 tp_group=None, resident: str = "auto", frozen: tuple[str, ...] = ()):
         """``cfg`` describes what this rank stores: the whole model, or (with ``tp_group``) one
-        tensor-parallel slice of ``full_cfg`` (see ``parallel.tp.tp_local_config``)."""
+        tensor-parallel slice of ``full_cfg`` (see ``parallel.tp.tp_local_config``).  ``frozen``
+        names components (``lm_head`` / ``embed`` / ``norm``) that get no update: their regions of
+        the arena are skipped by AdamW (moments never touched, no weight decay) and their gradient
+        slots stay zero, so they do not enter the global norm
+        (src/causal_trainer/training/steps.py:213-375)."""
         _lib.require_gpu_lib()
         self.cfg, self.tcfg, self.device = cfg, tcfg, device
         self.full_cfg = full_cfg if full_cfg is not None else cfg
@@ -93,6 +97,10 @@ class FsdpRuntime:
         self.world = dist.get_world_size(self.group)
         self.rank = dist.get_rank(self.group)
         self.fused = bool(getattr(tcfg, "fused_collectives", True))
+        from ..models.freezing import frozen_segments
+
+        self.frozen = tuple(frozen)
+        self.frozen_segs = frozen_segments(self.full_cfg, self.frozen)
         self.grad_dtype = torch.bfloat16
         self.main = torch.cuda.current_stream(device)
         self.side = torch.cuda.Stream(device, priority=-1)       # all-gather pulls
@@ -162,18 +170,23 @@ class FsdpRuntime:
         # only all-gather; otherwise three buffers rotate and every use re-gathers.
         total_bytes = 2 * sum(u.padded for u in self.units.values())
         free, _ = torch.cuda.mem_get_info(device)
-        self.resident = resident == "always" or (resident == "auto" and total_bytes < free // 4)
+        fits = torch.tensor([int(total_bytes < free // 4)], dtype=torch.int32, device=device)
+        if self.world > 1:
+            # every rank must take the same branch (the number of pulls, hence the flag epochs,
+            # depends on it): the most constrained GPU decides
+            dist.all_reduce(fits, op=dist.ReduceOp.MIN, group=self.group)
+        if self.tp_group is not None:
+            dist.all_reduce(fits, op=dist.ReduceOp.MIN, group=self.tp_group)
+        self.resident = resident == "always" or (resident == "auto" and bool(fits.item()))
         self.where: dict[str, _Gathered] = {}
-        if self.resident:
-            self.gathered = []
-            for name, u in self.units.items():
-                g = _Gathered(u.padded, device)
-                g.unit = name
-                g.valid = False
-                self.gathered.append(g)
-                self.where[name] = g
-        else:
-            self.gathered = [_Gathered(self.max_padded, device) for _ in range(N_GATHER)]
+        # resident mode allocates a unit's gathered buffer at its first pull (the embedding unit is
+        # never pulled when its rows are fetched from the peers' shards directly)
+        self.gathered = [] if self.resident else [_Gathered(self.max_padded, device) for _ in range(N_GATHER)]
+        self._build_region_table()
+        a = tcfg.adamw
+        # AdamW inside the reduce kernel: possible when no global-norm clip has to be known first
+        self.fuse_adam = self.fused and a.max_grad_norm <= 0 and not self.frozen_segs and self.tp_world == 1
+        self.pending_lr = 0.0
         self.slot_of: dict[str, int] = {}
         self.slot_epoch = [0] * N_SLOTS          # epoch last published for each slot
         self.slot_counter = 0
@@ -181,7 +194,25 @@ class FsdpRuntime:
         self.count = 0                           # optimizer steps taken
         self.mb_first = True
         self.mb_last = True
+        self.trace: list[tuple[str, str, torch.cuda.Event, torch.cuda.Event]] | None = None   # see _traced
         self._init_parameters()
+
+    def _traced(self, kind: str, name: str, stream):
+        """Context manager: with ``self.trace`` set (``benchmarks/step_phases.py``) brackets the
+        launches issued inside it with timing events on ``stream``; otherwise does nothing."""
+        import contextlib
+
+        if self.trace is None:
+            return contextlib.nullcontext()
+
+        @contextlib.contextmanager
+        def bracket():
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record(stream)
+            yield
+            b.record(stream)
+            self.trace.append((kind, name, a, b))
+        return bracket()
 
     # ------------------------------------------------------------------ parameters
     def shard_view(self, name: str, of: torch.Tensor | None = None) -> torch.Tensor:
@@ -249,6 +280,47 @@ class FsdpRuntime:
         if dtype == torch.float32 and self.accum is None:
             self.accum = torch.zeros(self.arena_elems, dtype=torch.float32, device=self.device)
 
+    def _build_region_table(self) -> None:
+        """Cuts this rank's arena into AdamW regions: for every unit the part of its shard that
+        holds vectors (no decay), the part that holds matrices (decay), and inside both the
+        frozen segments (skipped).  One device table serves the single AdamW launch per step."""
+        cuts: list[tuple[int, int, int]] = []          # (arena start, arena stop, mode)
+        for name, u in self.units.items():
+            lo, hi = self.rank * u.shard_elems, (self.rank + 1) * u.shard_elems
+            marks = {lo, hi, min(max(u.layout.vector_numel, lo), hi)}
+            frozen_spans = []
+            for seg in u.layout.segments:
+                if (name, seg.name) in self.frozen_segs:
+                    a, b = max(seg.offset, lo), min(seg.offset + seg.numel, hi)
+                    if b > a:
+                        frozen_spans.append((a, b))
+                        marks.update((a, b))
+            edges = sorted(marks)
+            for a, b in zip(edges[:-1], edges[1:]):
+                if b <= a:
+                    continue
+                if any(fa <= a and b <= fb for fa, fb in frozen_spans):
+                    mode = -1
+                else:
+                    mode = 1 if a >= u.layout.vector_numel else 0
+                cuts.append((u.arena_offset + a - lo, u.arena_offset + b - lo, mode))
+        merged: list[list[int]] = []
+        for a, b, mode in cuts:
+            if merged and merged[-1][2] == mode and merged[-1][1] == a:
+                merged[-1][1] = b
+            else:
+                merged.append([a, b, mode])
+        self.adam_regions = [(a, b, mode) for a, b, mode in merged]
+        self.region_bounds = torch.tensor([r[0] for r in merged] + [self.arena_elems], dtype=torch.int64,
+                                          device=self.device)
+        self.region_modes = torch.tensor([r[2] for r in merged], dtype=torch.int32, device=self.device)
+
+    def _frozen_spans(self, name: str) -> list[tuple[int, int]]:
+        """Unit-local element ranges of ``name`` whose gradients are never produced."""
+        u = self.units[name]
+        return [(seg.offset, seg.offset + seg.numel) for seg in u.layout.segments
+                if (name, seg.name) in self.frozen_segs]
+
     # ------------------------------------------------------------------ all-gather (pull) + flags
     def _pick_buffer(self, keep: set[str]) -> _Gathered:
         for g in self.gathered:
@@ -261,7 +333,10 @@ class FsdpRuntime:
 
     def _start_pull(self, name: str, keep: set[str]) -> _Gathered:
         if self.resident:
-            g = self.where[name]
+            g = self.where.get(name)
+            if g is None:
+                g = _Gathered(self.units[name].padded, self.device)
+                self.gathered.append(g)
             g.valid = True
         else:
             g = self._pick_buffer(keep | {name})
@@ -278,7 +353,7 @@ class FsdpRuntime:
         self.where[name] = g
         if g.free_event is not None:
             self.side.wait_event(g.free_event)
-        with torch.cuda.stream(self.side):
+        with torch.cuda.stream(self.side), self._traced("pull", name, self.side):
             if self.fused:
                 ptrs = _ptr_array([p + 2 * u.arena_offset for p in self.param_ptrs])
                 code = _lib.lib().ctb_ag_pull(ptrs, _lib.ptr(g.buffer), ctypes.c_long(u.shard_elems), self.rank,
@@ -304,15 +379,18 @@ class FsdpRuntime:
         elif self.fused and name.startswith("layer."):
             # vectors (norm scales, biases) are read by non-GEMM kernels: wait for their chunks only
             nvec = max(1, math.ceil(u.layout.vector_numel / CHUNK))
-            code = _lib.lib().ctb_wait_flags(_lib.ptr(g.flags), 0, 1, nvec, ctypes.c_uint(g.epoch),
-                                             ctypes.c_longlong(self.spin_budget), _lib.stream_ptr())
+            with self._traced("wait", name, self.main):
+                code = _lib.lib().ctb_wait_flags(_lib.ptr(g.flags), 0, 1, nvec, ctypes.c_uint(g.epoch),
+                                                 ctypes.c_longlong(self.spin_budget), _lib.stream_ptr())
             _lib.check(code, "ctb_wait_flags")
         elif self.fused and name == "final":
-            code = _lib.lib().ctb_wait_flags(_lib.ptr(g.flags), 0, 1, 1, ctypes.c_uint(g.epoch),
-                                             ctypes.c_longlong(self.spin_budget), _lib.stream_ptr())
+            with self._traced("wait", name, self.main):
+                code = _lib.lib().ctb_wait_flags(_lib.ptr(g.flags), 0, 1, 1, ctypes.c_uint(g.epoch),
+                                                 ctypes.c_longlong(self.spin_budget), _lib.stream_ptr())
             _lib.check(code, "ctb_wait_flags")
         else:
-            self.main.wait_event(g.pull_done)   # embedding rows are gathered at random: whole unit
+            with self._traced("wait", name, self.main):
+                self.main.wait_event(g.pull_done)   # embedding rows are gathered at random: whole unit
         return Unit(u.layout, g.buffer[:u.layout.numel])
 
     def release(self, name: str) -> None:
@@ -321,6 +399,29 @@ class FsdpRuntime:
             ev = torch.cuda.Event()
             ev.record(self.main)
             g.free_event = ev
+
+    def prefetch(self, name: str) -> None:
+        """Starts the all-gather of ``name`` without waiting for any of it."""
+        g = self.where.get(name)
+        if g is None or not g.valid:
+            self._start_pull(name, {name})
+
+    def embedding_rows(self, ids: torch.Tensor) -> torch.Tensor | None:
+        """``embed[ids]`` fetched row by row from the shards that own the rows (16-byte peer loads
+        over NVLink): the all-gather and the gather as one kernel, moving ``tokens x d`` elements
+        instead of the whole table.  None when this runtime gathers through NCCL."""
+        if not self.fused:
+            return None
+        u = self.units["embed"]
+        seg = u.layout.segment("embed")
+        flat = ids.reshape(-1).to(torch.int32).contiguous()
+        out = torch.empty((flat.numel(), seg.shape[1]), dtype=torch.bfloat16, device=self.device)
+        ptrs = _ptr_array([p + 2 * u.arena_offset for p in self.param_ptrs])
+        code = _lib.lib().ctb_embed_gather_peer(_lib.ptr(flat), ptrs, self.world, ctypes.c_long(u.shard_elems),
+                                                ctypes.c_long(seg.offset), _lib.ptr(out), ctypes.c_long(flat.numel()),
+                                                int(seg.shape[1]), int(seg.shape[0]), _lib.stream_ptr())
+        _lib.check(code, "ctb_embed_gather_peer")
+        return out
 
     # ------------------------------------------------------------------ gradients
     def grad_buffer(self, name: str) -> torch.Tensor:
@@ -333,9 +434,10 @@ class FsdpRuntime:
             prev = self.slot_epoch[slot]
             if prev > 0 and self.fused:
                 # every peer must have finished reducing the previous occupant of this slot
-                code = _lib.lib().ctb_wait_flags(_lib.ptr(self.pads), self.done_base + slot * self.world, 1,
-                                                 self.world, ctypes.c_uint(prev), ctypes.c_longlong(self.spin_budget),
-                                                 _lib.stream_ptr())
+                with self._traced("slot", name, self.main):
+                    code = _lib.lib().ctb_wait_flags(_lib.ptr(self.pads), self.done_base + slot * self.world, 1,
+                                                     self.world, ctypes.c_uint(prev),
+                                                     ctypes.c_longlong(self.spin_budget), _lib.stream_ptr())
                 _lib.check(code, "ctb_wait_flags")
             elif prev > 0:
                 self.main.wait_stream(self.reduce_stream)
@@ -345,6 +447,8 @@ class FsdpRuntime:
                 view.zero_()
             else:
                 view[u.layout.numel:].zero_()
+                for a, b in self._frozen_spans(name):     # nothing writes these: keep them out of the norm
+                    view[a:b].zero_()
         return self.staging[slot * self.max_padded:slot * self.max_padded + self.units[name].padded]
 
     def grads_ready(self, name: str, last_microbatch: bool) -> None:
@@ -367,13 +471,23 @@ class FsdpRuntime:
             accum = self.accum[off:off + u.shard_elems] if self.accum is not None else None
             staging = _ptr_array([p + 2 * slot * self.max_padded for p in self.staging_ptrs])
             done = _ptr_array([p + 4 * (self.done_base + slot * self.world + self.rank) for p in self.pad_ptrs])
-            with torch.cuda.stream(self.reduce_stream):
+            with torch.cuda.stream(self.reduce_stream), self._traced("reduce", name, self.reduce_stream):
+                adam = int(last and self.fuse_adam)
+                sl = slice(off, off + u.shard_elems)
+                a = self.tcfg.adamw
+                step = self.count + 1
+                lo = self.rank * u.shard_elems
+                decay_from = min(max(u.layout.vector_numel, lo), lo + u.shard_elems) - lo
+                hyper = [self.pending_lr, a.beta1, a.beta2, a.epsilon, a.weight_decay, 1 - a.beta1 ** step,
+                         1 - a.beta2 ** step] if adam else [0.0] * 7
                 code = L.ctb_rs_reduce(
                     staging, ctypes.c_long(self.rank * u.shard_elems), ctypes.c_long(u.shard_elems), self.world,
                     _lib.ptr(self.pads), self.ready_base + slot * self.world, ctypes.c_uint(epoch),
                     _lib.ptr(accum), int(not first), int(last),
-                    _lib.ptr(self.grad_shards[off:off + u.shard_elems]), _lib.ptr(self.sumsq[idx]),
-                    0, None, None, None, ctypes.c_long(0), *(ctypes.c_float(0.0),) * 7,
+                    None if adam else _lib.ptr(self.grad_shards[sl]), _lib.ptr(self.sumsq[idx]),
+                    adam, _lib.ptr(self.param_arena[sl]) if adam else None, _lib.ptr(self.m[sl]) if adam else None,
+                    _lib.ptr(self.v[sl]) if adam else None, ctypes.c_long(decay_from),
+                    *(ctypes.c_float(x) for x in hyper),
                     done, 0, _lib.ptr(self.finish_counter), REDUCE_CTAS, ctypes.c_longlong(self.spin_budget),
                     ctypes.c_void_p(self.reduce_stream.cuda_stream),
                 )
@@ -382,7 +496,7 @@ class FsdpRuntime:
             ev = torch.cuda.Event()
             ev.record(self.main)
             self.reduce_stream.wait_event(ev)
-            with torch.cuda.stream(self.reduce_stream):
+            with torch.cuda.stream(self.reduce_stream), self._traced("reduce", name, self.reduce_stream):
                 src = self.staging[slot * self.max_padded:slot * self.max_padded + u.padded]
                 red = torch.empty(u.shard_elems, dtype=torch.bfloat16, device=self.device)
                 dist.reduce_scatter_tensor(red, src, group=self.group)
@@ -402,44 +516,33 @@ class FsdpRuntime:
                     self.sumsq[idx, 0] = g.float().pow(2).sum()
 
     # ------------------------------------------------------------------ optimizer step
-    def _adam_regions(self, name: str) -> list[tuple[int, int, bool]]:
-        """(start, stop, decay) pieces of this rank's shard, in shard-local element indices."""
-        u = self.units[name]
-        lo = self.rank * u.shard_elems
-        hi = lo + u.shard_elems
-        cut = min(max(u.layout.vector_numel, lo), hi)
-        out = []
-        if cut > lo:
-            out.append((0, cut - lo, False))
-        if hi > cut:
-            out.append((cut - lo, hi - lo, True))
-        return out
-
     def apply_update(self, lr: float) -> torch.Tensor:
+        """Global norm (one 4-byte all-reduce per axis), clip, then ONE AdamW launch over the whole
+        arena; with clipping off the update already happened inside the reduce kernels.  Ends with
+        a fence so that no peer pulls a shard that is still being updated."""
         a = self.tcfg.adamw
         self.main.wait_stream(self.side)
         self.main.wait_stream(self.reduce_stream)
-        total = self.sumsq.sum().reshape(1)
-        if self.tp_world > 1:
-            # norm scales (and shared key/value heads) are replicated over tp ranks: every copy
-            # holds the same, already summed, gradient, so its square counts once
-            for index, copies in self._replicated_index():
-                total = total - (1.0 - 1.0 / copies) * self.grad_shards[index].float().pow(2).sum()
-            dist.all_reduce(total, group=self.tp_group)
-        dist.all_reduce(total, group=self.group)          # also orders every peer's pulls before the update
-        grad_norm = torch.sqrt(total)
-        clip = torch.ones_like(grad_norm)
-        if a.max_grad_norm > 0:
-            clip = torch.clamp(a.max_grad_norm / torch.clamp(grad_norm, min=1e-16), max=1.0)
-            clip = torch.where(torch.isfinite(grad_norm), clip, torch.ones_like(clip))
+        with self._traced("norm", "all", self.main):
+            total = self.sumsq.sum().reshape(1)
+            if self.tp_world > 1:
+                # norm scales (and shared key/value heads) are replicated over tp ranks: every copy
+                # holds the same, already summed, gradient, so its square counts once
+                for index, copies in self._replicated_index():
+                    total = total - (1.0 - 1.0 / copies) * self.grad_shards[index].float().pow(2).sum()
+                dist.all_reduce(total, group=self.tp_group)
+            dist.all_reduce(total, group=self.group)      # also orders every peer's pulls before the update
+            grad_norm = torch.sqrt(total)
+            clip = None
+            if a.max_grad_norm > 0:
+                clip = torch.clamp(a.max_grad_norm / torch.clamp(grad_norm, min=1e-16), max=1.0)
+                clip = torch.where(torch.isfinite(grad_norm), clip, torch.ones_like(clip))
         self.count += 1
-        for name, u in self.units.items():
-            off = u.arena_offset
-            for lo, hi, decay in self._adam_regions(name):
-                sl = slice(off + lo, off + hi)
-                ew.adamw_update(self.param_arena[sl], self.grad_shards[sl], self.m[sl], self.v[sl], lr=lr, b1=a.beta1,
-                                b2=a.beta2, eps=a.epsilon, decay=a.weight_decay if decay else 0.0, step=self.count,
-                                clip=clip)
+        if not self.fuse_adam:
+            with self._traced("adamw", "all", self.main):
+                ew.adamw_regions(self.param_arena, self.grad_shards, self.m, self.v, self.region_bounds,
+                                 self.region_modes, lr=lr, b1=a.beta1, b2=a.beta2, eps=a.epsilon,
+                                 decay=a.weight_decay, step=self.count, clip=clip)
         fence = torch.zeros(1, device=self.device)
         dist.all_reduce(fence, group=self.group)          # nobody pulls before every shard is updated
         if self.resident:
@@ -504,9 +607,12 @@ class FsdpStep:
         total = total.reshape(1).clone()
         dist.all_reduce(total, group=rt.group)
         denom = torch.clamp(total, min=1.0)
-        scale = float(1.0 / denom)
+        scale = 1.0 / denom                                # stays on the device: no host round trip per step
         if len(micro_batches) > 1:
             rt.set_grad_dtype(torch.float32)
+        step = rt.count if lr_position is None else lr_position
+        lr = learning_rate_at(rt.tcfg.schedule, step)
+        rt.pending_lr = lr                                 # for reduce kernels that apply AdamW themselves
         nll_sum = None
         for i, batch in enumerate(micro_batches):
             rt.mb_first, rt.mb_last = i == 0, i == len(micro_batches) - 1
@@ -514,7 +620,5 @@ class FsdpStep:
             nll_sum = nll if nll_sum is None else nll_sum + nll
         nll_sum = nll_sum.reshape(1).clone()
         dist.all_reduce(nll_sum, group=rt.group)
-        step = rt.count if lr_position is None else lr_position
-        lr = learning_rate_at(rt.tcfg.schedule, step)
         grad_norm = rt.apply_update(lr)
         return StepMetrics((nll_sum / denom)[0], nll_sum[0], total[0], grad_norm, lr)

@@ -54,6 +54,12 @@ class LocalProvider:
     def release(self, name: str) -> None:
         pass
 
+    def prefetch(self, name: str) -> None:
+        pass
+
+    def embedding_rows(self, ids: torch.Tensor) -> torch.Tensor | None:
+        return None
+
     def grads_ready(self, name: str, last_microbatch: bool) -> None:
         pass
 
@@ -84,6 +90,7 @@ class LayerwiseEngine:
         self.launches = 0
         self.kept_layers = 0
         self.train_base = True                   # False: base weights frozen, no gradient buffers (LoRA)
+        self.marks: list[tuple[str, torch.cuda.Event]] | None = None   # phase boundaries (benchmarks/step_phases.py)
         self._inv_freq: torch.Tensor | None = None
         import os
 
@@ -96,6 +103,12 @@ class LayerwiseEngine:
 
     def _count(self, n: int = 1) -> None:
         self.launches += n
+
+    def _mark(self, name: str) -> None:
+        if self.marks is not None:
+            ev = torch.cuda.Event(enable_timing=True)
+            ev.record()
+            self.marks.append((name, ev))
 
     def select_tokens(self, t: torch.Tensor) -> torch.Tensor:
         """The part of a ``[B, S, ...]`` batch tensor this rank computes on (everything, unless the
@@ -179,6 +192,23 @@ class LayerwiseEngine:
 
             moba_ops.moba_backward(q, k, v, o, do, lse, ctx["meta"], routing, dq=dq, dk=dk, dv=dv)
 
+    def _embed(self, local_ids: torch.Tensor, first_layer: str) -> torch.Tensor:
+        """Token embeddings of this rank's tokens.  A sharded provider fetches just the rows it
+        needs from the shards that own them; otherwise the table is acquired like any unit."""
+        prov = self.provider
+        rows = prov.embedding_rows(local_ids) if hasattr(prov, "embedding_rows") else None
+        if rows is not None:
+            prov.prefetch(first_layer)
+        else:
+            embed = prov.acquire("embed", prefetch=first_layer)
+            rows = ew.embedding_gather(local_ids, embed.view("embed"))
+            prov.release("embed")
+        self._count()
+        return rows
+
+    def _norm_grad(self, g: dict[str, torch.Tensor], name: str) -> torch.Tensor | None:
+        return g[name] if self.options.train_norm else None
+
     # ------------------------------------------------------------------ layer forward
     def _layer_forward(self, w: dict[str, torch.Tensor], resid: torch.Tensor, branch: torch.Tensor | None, ctx: dict,
                        li: int, save: str | None) -> tuple[torch.Tensor, torch.Tensor, dict | None]:
@@ -229,7 +259,7 @@ class LayerwiseEngine:
         del dact
         dn2 = self._project_backward(li, "gu", dgu, sv["n2"], w, g, accumulate)
         del dgu
-        dh, _ = ew.rmsnorm_backward(dn2, sv["h"], w["ln2"], sv["rstd2"], dres=dout, dw_out=g["ln2"],
+        dh, _ = ew.rmsnorm_backward(dn2, sv["h"], w["ln2"], sv["rstd2"], dres=dout, dw_out=self._norm_grad(g, "ln2"),
                                     dw_accumulate=accumulate)
         del dn2
         # attention branch: dh is the gradient of h = x + attn_out
@@ -247,7 +277,7 @@ class LayerwiseEngine:
         ew.rope_inplace(dqkv, ctx["cos"], ctx["sin"], cfg.num_attention_heads + cfg.num_key_value_heads, d_head,
                         cfg.rotary_dim, cfg.rope_style, inverse=True)
         dn1 = self._project_backward(li, "qkv", dqkv, sv["n1"], w, g, accumulate)
-        dx, _ = ew.rmsnorm_backward(dn1, sv["x"], w["ln1"], sv["rstd1"], dres=dh, dw_out=g["ln1"],
+        dx, _ = ew.rmsnorm_backward(dn1, sv["x"], w["ln1"], sv["rstd1"], dres=dh, dw_out=self._norm_grad(g, "ln1"),
                                     dw_accumulate=accumulate)
         self._count(8)
         return dx
@@ -296,9 +326,7 @@ class LayerwiseEngine:
         """Final-norm hidden states [B*S, d] (evaluation / tests)."""
         ctx = self._context(batch)
         cfg = self.cfg
-        embed = self.provider.acquire("embed")
-        resid = ew.embedding_gather(self.select_tokens(batch["input_ids"]), embed.view("embed"))
-        self.provider.release("embed")
+        resid = self._embed(self.select_tokens(batch["input_ids"]), "layer.0")
         branch = None
         for li in range(cfg.num_hidden_layers):
             unit = self.provider.acquire(f"layer.{li}", prefetch=f"layer.{li + 1}" if li + 1 < cfg.num_hidden_layers else "final")
@@ -315,14 +343,13 @@ class LayerwiseEngine:
         cfg = self.cfg
         prov = self.provider
         accumulate = not first
+        self._mark("begin")
         ctx = self._context(batch)
         nl = cfg.num_hidden_layers
         # ---------------- forward: keep (resid, branch) per layer ----------------
-        embed = prov.acquire("embed", prefetch="layer.0")
         local_ids = self.select_tokens(batch["input_ids"])
-        resid = ew.embedding_gather(local_ids, embed.view("embed"))
-        self._count()
-        prov.release("embed")
+        resid = self._embed(local_ids, "layer.0")
+        self._mark("embedding")
         branch = None
         inputs: list[tuple[torch.Tensor, torch.Tensor | None]] = []
         kept: list[dict | None] = []
@@ -337,6 +364,7 @@ class LayerwiseEngine:
                                                     save="keep" if keep else None)
             kept.append(sv)
             prov.release(f"layer.{li}")
+        self._mark("layers forward")
         # ---------------- head: final norm + cut cross-entropy ----------------
         final = prov.acquire("final", prefetch=f"layer.{nl - 1}")
         fw = self._views(final)
@@ -380,13 +408,16 @@ class LayerwiseEngine:
             dy_full = torch.zeros((full_rows, dy.shape[1]), dtype=dy.dtype, device=dy.device)
             dy_full.index_add_(0, active, dy)     # padded slots carry zero gradient (zero weight)
             dy, y = dy_full, y_all
-        dout, _ = ew.rmsnorm_backward(dy, xf, fw["norm"], rstd_f, dw_out=fg["norm"], dw_accumulate=accumulate)
+        dout, _ = ew.rmsnorm_backward(dy, xf, fw["norm"], rstd_f, dw_out=self._norm_grad(fg, "norm"),
+                                      dw_accumulate=accumulate)
         del y, dy, xf
         prov.release("final")
         prov.grads_ready("final", last)
+        self._mark("head forward+backward")
         # ---------------- backward: recompute + hand-written layer backward ----------------
         for li in reversed(range(nl)):
-            unit = prov.acquire(f"layer.{li}", prefetch=f"layer.{li - 1}" if li > 0 else "embed")
+            # the embedding table is not read in the backward pass: nothing to prefetch for layer 0
+            unit = prov.acquire(f"layer.{li}", prefetch=f"layer.{li - 1}" if li > 0 else None)
             w = self._views(unit)
             g = self._views(unit, prov.grad_buffer(f"layer.{li}")) if self.train_base else dict.fromkeys(w)
             layer_in = inputs.pop()
@@ -398,6 +429,7 @@ class LayerwiseEngine:
             self._join_wgrads()
             prov.release(f"layer.{li}")
             prov.grads_ready(f"layer.{li}", last)
+        self._mark("layers backward")
         # ---------------- embedding ----------------
         if self.options.train_embed and self.train_base:
             lay = embed_layout(cfg)
@@ -408,4 +440,5 @@ class LayerwiseEngine:
             ew.embedding_backward(local_ids, dout, gbuf, cfg.pad_token_id)
             self._count(5)
             prov.grads_ready("embed", last)
+        self._mark("embedding backward")
         return nll, wsum

@@ -145,7 +145,7 @@ class TrainStep:
     def run(self, micro_batches: list[dict[str, torch.Tensor]], lr_position: int | None = None) -> StepMetrics:
         total = loss_weight_total(micro_batches, self.dp_group)
         denom = torch.clamp(total, min=1.0)
-        scale = float(1.0 / denom)
+        scale = 1.0 / denom          # a device scalar on GPU runs: the step never waits for the host to read it
         nll_sum = None
         options = getattr(self.producer, "options", None)
         if options is not None and hasattr(options, "optimizer_step"):

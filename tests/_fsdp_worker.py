@@ -14,6 +14,10 @@ def main() -> None:
     fused = sys.argv[1] == "fused"
     out_path = sys.argv[2]
     steps = int(sys.argv[3]) if len(sys.argv) > 3 else 2
+    extra = dict(kv.split("=", 1) for kv in sys.argv[4:])          # clip=0  frozen=lm_head,norm  micro=1
+    clip = float(extra.get("clip", "1.0"))
+    frozen = tuple(x for x in extra.get("frozen", "").split(",") if x)
+    micro = int(extra.get("micro", "2"))
     local = int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dist.init_process_group("nccl", device_id=torch.device("cuda", local))
@@ -25,9 +29,11 @@ def main() -> None:
 
     world, rank = dist.get_world_size(), dist.get_rank()
     cfg = preset("tiny", vocab_size=4096, num_hidden_layers=3)
-    tcfg = TrainerConfig(micro_batch_rows=2, adamw=AdamWConfig(weight_decay=0.1, max_grad_norm=1.0),
-                         schedule=ScheduleConfig(1e-3, 0.0, "constant", 0, 10), fused_collectives=fused, seed=3)
+    tcfg = TrainerConfig(micro_batch_rows=micro, adamw=AdamWConfig(weight_decay=0.1, max_grad_norm=clip),
+                         schedule=ScheduleConfig(1e-3, 0.0, "constant", 0, 10), fused_collectives=fused, seed=3,
+                         force_sharded_runtime=True, frozen=frozen)
     trainer = Trainer(cfg, tcfg)
+    before = {name: trainer.runtime.gather_full_unit(name).clone() for name in ("embed", "final", "layer.0")}
     rows = 8
     data = pretraining_rows(rows, 256, cfg.vocab_size, eos_token_id=2, pad_token_id=0, median_len=80, min_len=8, seed=5)
     per = rows // world
@@ -35,8 +41,20 @@ def main() -> None:
     history = [trainer.train_step(mine) for _ in range(steps)]
     status = lib.device_status(raise_on_error=False)
     checksum = float(trainer.runtime.gather_full_unit("layer.1").float().abs().sum())
+    from causal_trainer_dev_b200.models.params import unit_layouts
+
+    unchanged = {}
+    for lay in unit_layouts(cfg):
+        if lay.name in before:
+            now = trainer.runtime.gather_full_unit(lay.name)
+            for seg in lay.segments:
+                sl = slice(seg.offset, seg.offset + seg.numel)
+                unchanged[f"{lay.name}/{seg.name}"] = bool(torch.equal(now[sl], before[lay.name][sl]))
+    moments = float(trainer.runtime.m.float().abs().sum())
     if rank == 0:
-        Path(out_path).write_text(json.dumps({"history": history, "status": status, "checksum": checksum}))
+        Path(out_path).write_text(json.dumps({"history": history, "status": status, "checksum": checksum,
+                                              "unchanged": unchanged, "moments": moments,
+                                              "fuse_adam": bool(trainer.runtime.fuse_adam)}))
     dist.destroy_process_group()
 
 

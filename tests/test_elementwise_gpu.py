@@ -107,3 +107,31 @@ def test_embedding_delta_sumsq_adamw(cuda_lib):
     assert _rel(m, mr) < 4e-3 and _rel(v, vr) < 4e-3
     assert (p.float() - pr.float()).abs().max() <= 2 ** -7 * pr.float().abs().max()
     assert _rel(p, pr) < 1e-3
+
+
+@pytest.mark.parametrize("grad_dtype", [torch.bfloat16, torch.float32])
+def test_adamw_over_an_arena_of_regions_in_one_launch(cuda_lib, grad_dtype):
+    """Decay, no-decay and frozen regions with boundaries both on and off the 8-element grid,
+    against the fp32 PyTorch statement applied region by region."""
+    from causal_trainer_dev_b200.ops import elementwise as E
+
+    torch.manual_seed(5)
+    n = 8 * 9000
+    bounds = [0, 4096, 4099, 20000, 20008, 50001, n]
+    modes = [0, 1, -1, 0, 1, -1]
+    p = torch.randn(n, device="cuda").bfloat16()
+    g = (0.01 * torch.randn(n, device="cuda")).to(grad_dtype)
+    m = (0.01 * torch.randn(n, device="cuda")).bfloat16()
+    v = (1e-4 * torch.rand(n, device="cuda")).bfloat16()
+    pr, mr, vr = p.clone(), m.clone(), v.clone()
+    kw = dict(lr=1e-3, b1=0.9, b2=0.999, eps=1e-8, step=2)
+    for lo, hi, mode in zip(bounds[:-1], bounds[1:], modes):
+        if mode >= 0:
+            gr = g[lo:hi].bfloat16() if grad_dtype == torch.float32 else g[lo:hi]
+            E.adamw_reference(pr[lo:hi], gr, mr[lo:hi], vr[lo:hi], clip=0.25, decay=0.1 if mode else 0.0, **kw)
+    E.adamw_regions(p, g, m, v, torch.tensor(bounds, device="cuda"), torch.tensor(modes, dtype=torch.int32, device="cuda"),
+                    decay=0.1, clip=torch.tensor(0.25, device="cuda"), round_bf16=grad_dtype == torch.float32, **kw)
+    assert _rel(m, mr) < 4e-3 and _rel(v, vr) < 4e-3 and _rel(p, pr) < 1e-3
+    for lo, hi, mode in zip(bounds[:-1], bounds[1:], modes):
+        if mode < 0:   # frozen: bit-identical parameter and moments
+            assert torch.equal(p[lo:hi], pr[lo:hi]) and torch.equal(m[lo:hi], mr[lo:hi]) and torch.equal(v[lo:hi], vr[lo:hi])
