@@ -302,6 +302,28 @@ class PackedArrayDataset:
         return row
 
 
+    def take(self, indices: np.ndarray) -> dict[str, np.ndarray]:
+        """Columns of the rows ``indices`` (one fancy-index per column; virtual rows included)."""
+        indices = np.asarray(indices, dtype=np.int64)
+        indices = np.where(indices < 0, indices + len(self), indices)
+        if ((indices < 0) | (indices >= len(self))).any():
+            raise IndexError("row index out of range")
+        virtual = indices >= self.real_rows
+        source = np.minimum(indices, self.real_rows - 1)        # a virtual row copies the last real row
+        out = {k: v[source] for k, v in self.columns.items()}
+        if self._dummy is not None:
+            if "loss_weights" not in out:
+                basis = out["assistant_masks"] if "assistant_masks" in out else out["attention_mask"]
+                out["loss_weights"] = basis.astype(np.float32)
+            if virtual.any():
+                out["loss_weights"] = out["loss_weights"].copy()
+                out["loss_weights"][virtual] = 0.0
+                if "assistant_masks" in out:
+                    out["assistant_masks"] = out["assistant_masks"].copy()
+                    out["assistant_masks"][virtual] = 0
+        return out
+
+
 def first_row_without_target(columns: Mapping[str, np.ndarray], chunk: int = 4096) -> int | None:
     attention, segments = columns["attention_mask"], columns["segment_ids"]
     for start in range(0, attention.shape[0], chunk):

@@ -22,7 +22,6 @@ from typing import Any, Iterable, Iterator, Mapping, Sequence
 import numpy as np
 
 from .batching import MODEL_FIELDS
-from .packing import PackedExample
 
 UNKNOWN_TOTAL_STEPS = 2**31 - 1
 _DOMAIN = b"causal-trainer-stream-v1\0"
@@ -121,137 +120,199 @@ def streaming_global_batch_digest(batch: StreamingGlobalBatch) -> bytes:
     return _batch_digest(batch, include_stream_state=True)
 
 
-# ----------------------------------------------------------------------------------------- grouping
-def canonical_record(record: Mapping[str, Sequence], *, assistant_only_loss: bool) -> PackedExample:
-    missing = [f for f in MODEL_FIELDS if f not in record]
-    if missing:
-        raise ValueError(f"streaming packed record is missing model fields: {missing}")
-    out: PackedExample = {f: [int(v) for v in record[f]] for f in MODEL_FIELDS}
-    n = len(out["input_ids"])
-    if any(len(out[f]) != n for f in MODEL_FIELDS):
+# ----------------------------------------------------------------------------------------- rows as typed arrays
+_INT_FIELDS = MODEL_FIELDS
+_BATCH_FIELDS = (*MODEL_FIELDS, "loss_weights")
+
+
+def encode_row(record: Mapping[str, Sequence], *, assistant_only_loss: bool) -> dict[str, np.ndarray]:
+    """One packed record as typed 1-D arrays (``int32`` model fields, ``float32`` ``loss_weights``),
+    validated: aligned fields, finite non-negative weights (explicit > assistant mask > attention
+    mask), and at least one positive-weight target whose predecessor is an attended token of the
+    same segment (a row without one can never contribute a loss term)."""
+    absent = [f for f in _INT_FIELDS if f not in record]
+    if absent:
+        raise ValueError(f"streaming packed record is missing model fields: {absent}")
+    row = {f: np.asarray(record[f], dtype=np.int64).astype(np.int32) for f in _INT_FIELDS}
+    width = row["input_ids"].shape[0]
+    if any(v.ndim != 1 or v.shape[0] != width for v in row.values()):
         raise ValueError("streaming packed model fields are not aligned")
-    if "assistant_masks" in record:
-        am = [int(v) for v in record["assistant_masks"]]
-        if len(am) != n:
+    mask = record.get("assistant_masks")
+    if mask is not None:
+        mask = np.asarray(mask, dtype=np.int64).astype(np.int32)
+        if mask.shape != (width,):
             raise ValueError("streaming assistant mask is not aligned with input_ids")
-        out["assistant_masks"] = am
     elif assistant_only_loss:
         raise ValueError("assistant-masked streaming record is missing assistant_masks")
     if "loss_weights" in record:
-        w = [float(v) for v in record["loss_weights"]]
+        weights = np.asarray(record["loss_weights"], dtype=np.float64)
     else:
-        w = [float(v) for v in out["assistant_masks" if assistant_only_loss else "attention_mask"]]
-    if len(w) != n:
+        weights = (mask if assistant_only_loss else row["attention_mask"]).astype(np.float64)
+    if weights.shape != (width,):
         raise ValueError("streaming loss_weights are not aligned with input_ids")
-    wa = np.asarray(w, dtype=np.float32)
-    if not np.isfinite(wa).all() or (wa < 0).any():
+    weights = weights.astype(np.float32)
+    if not np.isfinite(weights).all() or (weights < 0).any():
         raise ValueError("streaming loss_weights must be finite and non-negative")
-    out["loss_weights"] = w
-    a = np.asarray(out["attention_mask"], dtype=np.int32)
-    s = np.asarray(out["segment_ids"], dtype=np.int32)
-    if not np.any((a[:-1] != 0) & (a[1:] != 0) & (s[:-1] != 0) & (s[:-1] == s[1:]) & (wa[1:] > 0)):
+    row["loss_weights"] = weights
+    attended, segment = row["attention_mask"] != 0, row["segment_ids"]
+    edge = attended[:-1] & attended[1:] & (segment[:-1] != 0) & (segment[:-1] == segment[1:]) & (weights[1:] > 0)
+    if not edge.any():
         raise ValueError("a streaming packed row has no positive-weight causal target with a valid same-segment "
                          "predecessor")
-    return out
+    return row
 
 
-def _zero_loss_copy(record: PackedExample) -> PackedExample:
-    out = {k: list(v) for k, v in record.items()}
-    out["loss_weights"] = [0.0] * len(record["input_ids"])
-    if "assistant_masks" in out:
-        out["assistant_masks"] = [0] * len(record["input_ids"])
-    return out
+class RowQueue:
+    """FIFO of encoded rows kept as 2-D arrays (one per field) plus the number of raw source rows
+    charged to each.  ``pop`` hands out the oldest ``n`` rows as a batch without touching Python
+    lists of token ids; the arrays grow by doubling."""
 
+    def __init__(self) -> None:
+        self.fields: dict[str, np.ndarray] | None = None
+        self.charge = np.zeros(0, dtype=np.int64)
+        self.head = 0
+        self.tail = 0
 
-def _stack(records: Sequence[PackedExample]) -> dict[str, np.ndarray]:
-    return {f: np.asarray([r[f] for r in records], dtype=np.float32 if f == "loss_weights" else np.int32)
-            for f in (*MODEL_FIELDS, "loss_weights")}
+    def __len__(self) -> int:
+        return self.tail - self.head
+
+    def _reserve(self, width: int, extra: int) -> None:
+        if self.fields is None:
+            cap = max(16, extra)
+            self.fields = {f: np.zeros((cap, width), dtype=np.float32 if f == "loss_weights" else np.int32)
+                           for f in _BATCH_FIELDS}
+            self.charge = np.zeros(cap, dtype=np.int64)
+            return
+        have = self.charge.shape[0]
+        if self.tail + extra <= have:
+            return
+        live = len(self)
+        cap = max(2 * have, live + extra)
+        for f, old in self.fields.items():
+            grown = np.zeros((cap, old.shape[1]), dtype=old.dtype)
+            grown[:live] = old[self.head:self.tail]
+            self.fields[f] = grown
+        charge = np.zeros(cap, dtype=np.int64)
+        charge[:live] = self.charge[self.head:self.tail]
+        self.charge, self.head, self.tail = charge, 0, live
+
+    def push(self, row: dict[str, np.ndarray], charge: int) -> None:
+        width = row["input_ids"].shape[0]
+        if self.fields is not None and self.fields["input_ids"].shape[1] != width:
+            raise ValueError("streaming packed rows have different lengths")
+        self._reserve(width, 1)
+        for f in _BATCH_FIELDS:
+            self.fields[f][self.tail] = row[f]
+        self.charge[self.tail] = charge
+        self.tail += 1
+
+    def pop(self, n: int, pad_to: int | None = None) -> tuple[dict[str, np.ndarray], int]:
+        """Oldest ``n`` rows as fresh arrays and their summed charge.  With ``pad_to`` the batch is
+        filled up with copies of its last row that carry zero loss weight."""
+        a, b = self.head, self.head + n
+        size = n if pad_to is None else pad_to
+        out = {}
+        for f, store in self.fields.items():
+            block = np.empty((size, store.shape[1]), dtype=store.dtype)
+            block[:n] = store[a:b]
+            if size > n:
+                block[n:] = 0.0 if f == "loss_weights" else store[b - 1]
+            out[f] = block
+        charged = int(self.charge[a:b].sum())
+        self.head = b
+        if self.head == self.tail:
+            self.head = self.tail = 0
+        return out, charged
 
 
 @dataclass(frozen=True)
-class _Grouped:
+class _Pending:
     data: dict[str, np.ndarray]
     source_examples: int
     epoch: int
     is_epoch_end: bool = False
 
 
-def _row_counts(envelope: Any) -> list[int]:
-    records = tuple(envelope.records)
-    if not records:
-        return []
+def _charges(envelope: Any, rows: int) -> np.ndarray:
+    """Raw source rows charged to each packed row of a window (all to the last row unless the
+    window says otherwise)."""
+    if rows == 0:                      # a fully filtered window: its source rows are charged later
+        return np.zeros(0, dtype=np.int64)
+    total = int(envelope.source_examples)
     explicit = getattr(envelope, "record_source_examples", None)
     if explicit is None:
-        counts = [0] * len(records)
-        counts[-1] = int(envelope.source_examples)
-        return counts
-    counts = [int(v) for v in explicit]
-    if len(counts) != len(records):
+        out = np.zeros(rows, dtype=np.int64)
+        out[-1] = total
+        return out
+    out = np.asarray([int(v) for v in explicit], dtype=np.int64)
+    if out.shape[0] != rows:
         raise ValueError("record_source_examples must align with streaming records")
-    if any(v < 0 for v in counts):
+    if (out < 0).any():
         raise ValueError("record_source_examples must be non-negative")
-    if sum(counts) != int(envelope.source_examples):
+    if int(out.sum()) != total:
         raise ValueError("record_source_examples must sum to source_examples")
-    return counts
+    return out
 
 
 class BatchGrouper:
-    """State machine: envelopes in, fixed-size grouped batches out (one batch is held back)."""
+    """Windows in, fixed-size batches out.  The newest complete batch is always held back one
+    turn: only when the next batch (or the end of the epoch) arrives is it known whether it closes
+    the epoch.  Source rows of windows that produced no packed row wait in ``orphans`` and are
+    charged to the next row that does arrive (or to the closing batch)."""
 
     def __init__(self, size: int, assistant_only_loss: bool):
         if size <= 0:
             raise ValueError("effective_batch_size must be positive")
         self.size, self.masked = size, assistant_only_loss
-        self.rows: list[tuple[PackedExample, int]] = []
-        self.held: _Grouped | None = None
-        self.unassigned = 0          # source rows of fully filtered windows, waiting for a row to charge
+        self.queue = RowQueue()
+        self.held: _Pending | None = None
+        self.orphans = 0
         self.epoch: int | None = None
 
-    def feed(self, envelope: Any) -> Iterator[_Grouped]:
+    def _hold(self, pending: _Pending) -> Iterator[_Pending]:
+        if self.held is not None:
+            yield self.held
+        self.held = pending
+
+    def feed(self, envelope: Any) -> Iterator[_Pending]:
         epoch = int(envelope.epoch)
         if self.epoch is None:
             self.epoch = epoch
         elif epoch != self.epoch:
             raise ValueError("streaming epoch changed without an epoch-end envelope")
-        records, counts = tuple(envelope.records), _row_counts(envelope)
+        records = tuple(envelope.records)
+        charges = _charges(envelope, len(records))
         if records:
-            counts[0] += self.unassigned
-            self.unassigned = 0
-            self.rows.extend((canonical_record(r, assistant_only_loss=self.masked), c)
-                             for r, c in zip(records, counts, strict=True))
+            charges[0] += self.orphans
+            self.orphans = 0
+            for record, charge in zip(records, charges):
+                self.queue.push(encode_row(record, assistant_only_loss=self.masked), int(charge))
         else:
-            self.unassigned += int(envelope.source_examples)
-        while len(self.rows) >= self.size:
-            take, self.rows = self.rows[:self.size], self.rows[self.size:]
-            if self.held is not None:
-                yield self.held
-            self.held = _Grouped(_stack([r for r, _ in take]), sum(c for _, c in take), epoch)
+            self.orphans += int(envelope.source_examples)
+        while len(self.queue) >= self.size:
+            data, charged = self.queue.pop(self.size)
+            yield from self._hold(_Pending(data, charged, epoch))
         if not bool(envelope.is_epoch_end):
             return
-        if self.rows:
-            if self.held is not None:
-                yield self.held
-            real = [r for r, _ in self.rows]
-            src = sum(c for _, c in self.rows) + self.unassigned
-            self.unassigned = 0
-            padded = real + [_zero_loss_copy(real[-1]) for _ in range(self.size - len(real))]
-            self.held = _Grouped(_stack(padded), src, epoch)
-            self.rows = []
-        elif self.held is not None and self.unassigned:
-            self.held = replace(self.held, source_examples=self.held.source_examples + self.unassigned)
-            self.unassigned = 0
+        leftover = len(self.queue)
+        if leftover:
+            data, charged = self.queue.pop(leftover, pad_to=self.size)
+            yield from self._hold(_Pending(data, charged + self.orphans, epoch))
+        elif self.held is not None and self.orphans:
+            self.held = replace(self.held, source_examples=self.held.source_examples + self.orphans)
+        self.orphans = 0
         if self.held is None:
             raise ValueError(f"streaming epoch {epoch} produced no trainable records after preprocessing")
-        yield replace(self.held, is_epoch_end=True)
-        self.held, self.epoch = None, None
+        closing, self.held, self.epoch = self.held, None, None
+        yield replace(closing, is_epoch_end=True)
 
     def finish(self) -> None:
-        if self.epoch is not None or self.rows or self.held is not None or self.unassigned:
+        if self.epoch is not None or len(self.queue) or self.held is not None or self.orphans:
             raise ValueError("streaming source ended without an epoch-end envelope")
 
 
 class StreamCursor:
-    """Running progress and digest over committed batches."""
+    """Progress counters and the chained SHA-256 over every committed batch."""
 
     def __init__(self) -> None:
         self.seen = 0
@@ -259,67 +320,77 @@ class StreamCursor:
         self.epoch: int | None = None
         self.digest = hashlib.sha256(_DOMAIN)
 
-    def advance(self, g: _Grouped) -> StreamingGlobalBatch:
+    def advance(self, pending: _Pending) -> StreamingGlobalBatch:
         if self.epoch is None:
-            self.epoch, self.epoch_seen = g.epoch, 0
-        elif g.epoch != self.epoch:
+            self.epoch, self.epoch_seen = pending.epoch, 0
+        elif pending.epoch != self.epoch:
             raise RuntimeError("streaming global batches changed epoch without completing the prior epoch")
-        batch = StreamingGlobalBatch(
-            data=g.data, source_examples=g.source_examples, source_examples_before=self.seen,
-            source_examples_seen=self.seen + g.source_examples, epoch_source_examples_before=self.epoch_seen,
-            epoch_source_examples_seen=self.epoch_seen + g.source_examples, epoch=g.epoch,
-            is_epoch_end=g.is_epoch_end, stream_digest_before=self.digest.hexdigest(), stream_digest="",
-        )
-        self.seen += g.source_examples
-        self.epoch_seen += g.source_examples
-        self.digest.update(_batch_digest(batch, include_stream_state=False))
-        if g.is_epoch_end:
-            self.epoch, self.epoch_seen = None, 0
-        return replace(batch, stream_digest=self.digest.hexdigest())
+        n = pending.source_examples
+        before = self.digest.hexdigest()
+        draft = StreamingGlobalBatch(
+            data=pending.data, source_examples=n, source_examples_before=self.seen, source_examples_seen=self.seen + n,
+            epoch_source_examples_before=self.epoch_seen, epoch_source_examples_seen=self.epoch_seen + n,
+            epoch=pending.epoch, is_epoch_end=pending.is_epoch_end, stream_digest_before=before, stream_digest="")
+        self.digest.update(_batch_digest(draft, include_stream_state=False))
+        self.seen += n
+        self.epoch_seen = 0 if pending.is_epoch_end else self.epoch_seen + n
+        if pending.is_epoch_end:
+            self.epoch = None
+        return replace(draft, stream_digest=self.digest.hexdigest())
+
+
+class _ResumePoint:
+    """What a checkpoint recorded about the stream before its step; checked once, exactly when the
+    replay stands at that step."""
+
+    def __init__(self, source_examples: int | None, digest: str | None):
+        if source_examples is not None and (type(source_examples) is not int or source_examples < 0):
+            raise ValueError("expected_source_examples_before must be a non-negative integer or None")
+        if digest is not None and (len(digest) != 64 or set(digest) - set("0123456789abcdef")):
+            raise ValueError("expected_stream_digest_before must be a lowercase SHA-256 digest or None")
+        self.source_examples, self.digest = source_examples, digest
+        self.done = False
+
+    def check(self, cursor: StreamCursor) -> None:
+        if self.done:
+            return
+        self.done = True
+        if self.source_examples is not None and cursor.seen != self.source_examples:
+            raise RuntimeError(f"streaming resume replay reached source example {cursor.seen}, but checkpoint "
+                               f"progress records {self.source_examples}")
+        if self.digest is not None and cursor.digest.hexdigest() != self.digest:
+            raise RuntimeError("streaming resume replay produced different training batches before the checkpoint; "
+                               "pin dataset_revision to the original immutable dataset commit")
 
 
 def iter_streaming_global_batches(envelopes: Iterable[Any], plan: StreamingBatchPlan, *, assistant_only_loss: bool,
                                   start_step: int = 0, expected_source_examples_before: int | None = None,
                                   expected_stream_digest_before: str | None = None) -> Iterator[StreamingGlobalBatch]:
+    """Replays the stream from its start: the first ``start_step`` batches only feed the cursor,
+    the checkpoint's record is verified when the replay reaches ``start_step`` (also when that is
+    the end of the stream), and everything after is yielded."""
     if start_step < 0 or start_step > plan.total_steps:
         raise ValueError(f"start_step must be in [0, {plan.total_steps}], got {start_step}")
-    if expected_source_examples_before is not None and (
-            type(expected_source_examples_before) is not int or expected_source_examples_before < 0):
-        raise ValueError("expected_source_examples_before must be a non-negative integer or None")
-    if expected_stream_digest_before is not None and (
-            len(expected_stream_digest_before) != 64
-            or any(c not in "0123456789abcdef" for c in expected_stream_digest_before)):
-        raise ValueError("expected_stream_digest_before must be a lowercase SHA-256 digest or None")
+    resume = _ResumePoint(expected_source_examples_before, expected_stream_digest_before)
     cursor = StreamCursor()
     grouper = BatchGrouper(plan.effective_batch_size, assistant_only_loss)
+    limit = plan.max_steps if plan.max_steps > 0 else None
     step = 0
-    checked = False
-
-    def check_resume_point() -> None:
-        nonlocal checked
-        if expected_source_examples_before is not None and cursor.seen != expected_source_examples_before:
-            raise RuntimeError(f"streaming resume replay reached source example {cursor.seen}, but checkpoint "
-                               f"progress records {expected_source_examples_before}")
-        if expected_stream_digest_before is not None and cursor.digest.hexdigest() != expected_stream_digest_before:
-            raise RuntimeError("streaming resume replay produced different training batches before the checkpoint; "
-                               "pin dataset_revision to the original immutable dataset commit")
-        checked = True
-
     for envelope in envelopes:
-        for grouped in grouper.feed(envelope):
-            if step == start_step and not checked:
-                check_resume_point()
-            batch = cursor.advance(grouped)
-            if step >= start_step:
-                yield batch
+        for pending in grouper.feed(envelope):
+            if step == start_step:
+                resume.check(cursor)
+            batch = cursor.advance(pending)
             step += 1
-            if plan.max_steps > 0 and step >= plan.max_steps:
-                if step == start_step and not checked:
-                    check_resume_point()
+            if step > start_step:
+                yield batch
+            if limit is not None and step >= limit:
+                if step == start_step:
+                    resume.check(cursor)
                 return
     grouper.finish()
     if step < start_step:
         raise RuntimeError(f"streaming resume requested optimizer step {start_step}, but the reconstructed source "
                            f"produced only {step} batches")
-    if step == start_step and not checked:
-        check_resume_point()
+    if step == start_step:
+        resume.check(cursor)
