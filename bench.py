@@ -223,11 +223,16 @@ def main() -> None:
     sync()
     t0 = time.perf_counter()
     start.record()
+    marks = [t0]
     for i in range(args.steps):
         out = trainer.train_step(pool[i % 2])
+        marks.append(time.perf_counter())
     end.record()
     sync()
     e2e_ms = max(start.elapsed_time(end), (time.perf_counter() - t0) * 1e3)
+    if rank == 0:
+        print("e2e wall per step (ms):", [round((b - a) * 1e3, 1) for a, b in zip(marks[:-1], marks[1:])],
+              "allocator retries:", torch.cuda.memory_stats().get("num_alloc_retries"), file=sys.stderr)
     h2d1, d2h1 = trainer.transfer_counters()
 
     if world > 1:

@@ -207,7 +207,7 @@ def flash_attention_backward(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, out: torch.Tensor, dout: torch.Tensor, lse: torch.Tensor,
     meta: AttentionMeta, scale: float | None = None, spin_budget: int = 0,
     dq: torch.Tensor | None = None, dk: torch.Tensor | None = None, dv: torch.Tensor | None = None,
-    q_offset: int = 0,
+    q_offset: int = 0, stats: tuple[torch.Tensor, torch.Tensor] | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor, torch.Tensor]:
     """dQ (query-tile-owned kernel) and dK/dV (key-tile-owned kernel, group reduced in TMEM).
 
@@ -221,7 +221,8 @@ def flash_attention_backward(
     from .elementwise import attention_backward_stats
 
     _row_stride(out), _row_stride(dout)
-    neg_lse2, neg_delta = attention_backward_stats(out, dout, lse)  # [B,Hq,Sq] fp32
+    # [B,Hq,Sq] fp32; a caller that splits one softmax over several passes hands in the shared ones
+    neg_lse2, neg_delta = attention_backward_stats(out, dout, lse) if stats is None else stats
     dq = torch.empty((b, sq, hq, d), dtype=torch.bfloat16, device=q.device) if dq is None else dq
     dk = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dk is None else dk
     dv = torch.empty((b, s, hkv, d), dtype=torch.bfloat16, device=q.device) if dv is None else dv

@@ -32,6 +32,23 @@ struct SparseArgs {
   int words;
 };
 
+// Grouped MoBA: the query rows that selected a key block were gathered into one contiguous
+// tensor (rows of a group adjacent, groups padded with zero rows to a multiple of 256), so the
+// history part of MoBA is dense attention of each group against its key block and its cost follows
+// the routing budget, not the sequence length.  Q / O / dO / dQ and the per-row statistics are then
+// indexed by the gathered row (one batch, one head), K / V / dK / dV by (batch, kv head, token).
+// One descriptor per CTA:
+//   x  batch | kv head << 16
+//   y  forward, dQ: first key of the group's block;  dK/dV: first key of the CTA's 128-key tile
+//   z  dK/dV: first gathered row of the group
+//   w  forward: rows of the CTA's 256-row tile that are real (0: nothing to do);  dQ: same for its
+//      128-row tile;  dK/dV: rows of the group including padding (a multiple of 64; 0: nothing to do)
+// No masks apply: every real row sees the whole block, padding rows are zero and contribute zero.
+struct GroupArgs {
+  const int4* desc;
+  int block;          // keys per group, a multiple of 128
+};
+
 // Sequence parallelism: a rank may hold only the queries [q_off, q_off + Sq) of every row while
 // keys and values cover the whole sequence of S tokens.  Q / O / dQ / dO / LSE / delta are then
 // indexed by the local query position, the visibility metadata by the global one.
@@ -48,6 +65,7 @@ struct FwdArgs {
   DeviceStatus* status;
   long long spin_budget;
   SparseArgs sp;
+  GroupArgs grp;
 };
 
 struct FwdCall {
@@ -60,6 +78,8 @@ struct FwdCall {
   long long spin_budget;
   void* stream;
   SparseArgs sp{};
+  GroupArgs grp{};
+  int gathered_rows = 0;     // grouped: capacity of the gathered row space (a multiple of 256)
 };
 
 enum : int { MODE_DKV = 0, MODE_DQ = 1 };
@@ -87,6 +107,7 @@ struct BwdArgs {
   DeviceStatus* status;
   long long spin_budget;
   SparseArgs sp;
+  GroupArgs grp;
 };
 
 struct BwdCall {
@@ -102,6 +123,9 @@ struct BwdCall {
   long long spin_budget;
   void* stream;
   SparseArgs sp{};
+  GroupArgs grp{};
+  int gathered_rows = 0;     // grouped: capacity of the gathered row space
+  int ctas = 0;              // grouped: CTAs to launch (one per descriptor)
 };
 
 // First entry and length of the work list of CTA `item`.

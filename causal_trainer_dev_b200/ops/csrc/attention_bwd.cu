@@ -83,9 +83,25 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const int nb64 = args.S / 64;
 
   // ---- work item ----
+  // grouped MoBA (see GroupArgs): gathered rows of one group against the keys of its block, no masks
+  const bool grouped = args.grp.desc != nullptr;
+  int4 gd = make_int4(0, 0, 0, 0);
+  if (grouped) {
+    gd = __ldg(args.grp.desc + blockIdx.x);
+    if (gd.w <= 0) return;                       // unused capacity: the whole CTA leaves
+  }
   int idx = blockIdx.x;
   int b, head, x0, y_lo64, y_n64, heads_in_loop;
-  if (DKV) {
+  if (grouped) {
+    // X = this CTA's resident tile: 128 keys of the block (dK/dV) or 128 gathered rows (dQ);
+    // Y = 64-row blocks of the group's gathered rows (dK/dV) or of the block's keys (dQ).
+    b = DKV ? (gd.x & 0xffff) : 0;
+    head = DKV ? (gd.x >> 16) : 0;
+    x0 = DKV ? gd.y : static_cast<int>(blockIdx.x) * 128;
+    y_lo64 = 0;
+    y_n64 = DKV ? gd.w / 64 : args.grp.block / 64;
+    heads_in_loop = 1;
+  } else if (DKV) {
     head = idx % args.Hkv;      // kv head
     idx /= args.Hkv;
     b = idx % args.B;
@@ -110,7 +126,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     heads_in_loop = 1;
   }
   int n_iter = y_n64 * heads_in_loop;
-  const int hkv = DKV ? head : head / group;
+  const int hkv = grouped ? (gd.x >> 16) : (DKV ? head : head / group);
+  const int kbatch = grouped ? (gd.x & 0xffff) : b;     // batch of the K / V / dK / dV tensors
+  const int y_base = grouped ? (DKV ? gd.z : gd.y) : 0; // first row (dK/dV) or key (dQ) of the streamed operand
   // Block-sparse routing: the (64-row block, head) pairs come from a list instead of a range.
   const bool sparse = args.sp.it_list != nullptr;
   const int* it_list = nullptr;
@@ -122,6 +140,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   // iteration -> (64-row block of the streamed operand, query head)
   auto y_block = [&](int it) -> int { return sparse ? (__ldg(it_list + it) & 0xffffff) : y_lo64 + it % y_n64; };
   auto y_head = [&](int it) -> int {
+    if (grouped) return 0;
     if (!DKV) return head;
     return hkv * group + (sparse ? (__ldg(it_list + it) >> 24) : it / y_n64);
   };
@@ -162,30 +181,32 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       const CUtensorMap* mx1 = DKV ? &map_k : &map_q;
       const CUtensorMap* mx2 = DKV ? &map_v : &map_do;
       const int xh = DKV ? hkv : head;
+      const int xb = DKV ? kbatch : b;
 #pragma unroll
       for (int hf = 0; hf < HALVES; ++hf) {
-        tma_load_4d(smem + L::OFF_X + hf * 16384, mx1, x_full, hf * 64, xh, x0, b);
-        tma_load_4d(smem + L::OFF_X + L::XT + hf * 16384, mx2, x_full, hf * 64, xh, x0, b);
+        tma_load_4d(smem + L::OFF_X + hf * 16384, mx1, x_full, hf * 64, xh, x0, xb);
+        tma_load_4d(smem + L::OFF_X + L::XT + hf * 16384, mx2, x_full, hf * 64, xh, x0, xb);
       }
       const CUtensorMap* my1 = DKV ? &map_q : &map_k;
       const CUtensorMap* my2 = DKV ? &map_do : &map_v;
       uint32_t stage = 0, phase = 0;
       for (int it = 0; it < n_iter; ++it) {
         const int yh = DKV ? y_head(it) : hkv;
-        const int y0 = y_block(it) * 64 - (DKV ? args.q_off : 0);   // streamed queries are stored locally
+        const int ybatch = DKV ? b * (grouped ? 0 : 1) : kbatch;
+        const int y0 = y_base + y_block(it) * 64 - (DKV ? args.q_off : 0);   // streamed queries are stored locally
         if (!mbar_wait(&y_empty[stage], phase ^ 1u, abort_flag, st, SITE_B_PROD, budget)) break;
         mbar_expect_tx(&y_full[stage], 2 * L::YT + (DKV ? 512 : 0));
         uint8_t* dst = smem + L::OFF_Y + stage * 2 * L::YT;
         if (DKV) {
           // the per-query statistics of the block travel with it (256 B each, 256 B aligned)
-          const size_t stat = (static_cast<size_t>(b) * args.Hq + yh) * args.Sq + y0;
+          const size_t stat = grouped ? static_cast<size_t>(y0) : (static_cast<size_t>(b) * args.Hq + yh) * args.Sq + y0;
           tma_load_1d(smem + L::OFF_STAT + stage * 512, args.neg_lse2 + stat, 256, &y_full[stage]);
           tma_load_1d(smem + L::OFF_STAT + stage * 512 + 256, args.neg_delta + stat, 256, &y_full[stage]);
         }
 #pragma unroll
         for (int hf = 0; hf < HALVES; ++hf) {
-          tma_load_4d(dst + hf * 8192, my1, &y_full[stage], hf * 64, yh, y0, b);
-          tma_load_4d(dst + L::YT + hf * 8192, my2, &y_full[stage], hf * 64, yh, y0, b);
+          tma_load_4d(dst + hf * 8192, my1, &y_full[stage], hf * 64, yh, y0, ybatch);
+          tma_load_4d(dst + L::YT + hf * 8192, my2, &y_full[stage], hf * 64, yh, y0, ybatch);
         }
         if (++stage == Y_STAGES) {
           stage = 0;
@@ -267,10 +288,13 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     // position in the whole sequence of this thread's row: a key (DKV) or a local query (DQ)
     const int xi = x0 + r + (DKV ? 0 : args.q_off);
     const int xi_local = x0 + r;
-    const int row_seg = args.seg[b * args.S + xi];
+    const int row_seg = grouped ? 1 : args.seg[b * args.S + xi];
     // interval of visible columns (whole-sequence positions): see the mask below
     int row_a, row_b;
-    if (DKV) {
+    if (grouped) {
+      row_a = -(1 << 30);       // everything is visible: padding rows hold zeros and contribute zero
+      row_b = 1 << 30;
+    } else if (DKV) {
       row_a = args.first_q[b * args.S + xi];
       row_b = args.run_end[b * args.S + xi];
     } else {
@@ -282,8 +306,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int row_blk = (sparse && DKV) ? (xi - row_start) / args.sp.block : 0;
     float neg_lse2 = 0.f, neg_delta = 0.f;      // DQ: per-row statistics (stored negated, lse in log2 units)
     if (!DKV) {
-      neg_lse2 = args.neg_lse2[(static_cast<size_t>(b) * args.Hq + head) * args.Sq + xi_local];
-      neg_delta = args.neg_delta[(static_cast<size_t>(b) * args.Hq + head) * args.Sq + xi_local];
+      const size_t at = grouped ? static_cast<size_t>(xi_local) : (static_cast<size_t>(b) * args.Hq + head) * args.Sq + xi_local;
+      neg_lse2 = args.neg_lse2[at];
+      neg_delta = args.neg_delta[at];
     }
     bool ok = true;
     uint32_t sph = 0;                      // bit u: phase parity of s_full[u]
@@ -306,7 +331,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           ++walk_head;
         }
       }
-      const int y0 = yb * 64;
+      const int y0 = yb * 64;                   // (grouped: relative to the group, and nothing is masked)
       const int base = y0 + 16 * wg;            // first column of this thread
       // ---- visibility of this row against its 16 columns, as a bit mask.  The keys a query sees
       // and the queries that see a key are both contiguous intervals (runs are contiguous):
@@ -460,8 +485,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       if (r == 0 && half == 0) {
         const CUtensorMap* mo = (DKV && u == 1) ? &map_out2 : &map_out1;
         const int oh = DKV ? hkv : head;
+        const int ob = DKV ? kbatch : b;
 #pragma unroll
-        for (int hf = 0; hf < HALVES; ++hf) tma_store_4d(mo, stage_buf + hf * 16384, hf * 64, oh, x0, b);
+        for (int hf = 0; hf < HALVES; ++hf) tma_store_4d(mo, stage_buf + hf * 16384, hf * 64, oh, x0, ob);
         tma_commit_group();
         tma_wait_group<0>();
       }
@@ -479,10 +505,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 template <int D, int MODE>
 int launch_bwd(const BwdCall& c) {
   using L = BwdSmem<D>;
-  const int Sq = c.Sq > 0 ? c.Sq : c.S;
-  auto make = [&](const void* base, int heads, long row_stride, int rows, int seq) -> const CUtensorMap* {
+  const bool grouped = c.grp.desc != nullptr;
+  const int Sq = grouped ? c.gathered_rows : (c.Sq > 0 ? c.Sq : c.S);
+  auto make = [&](const void* base, int heads, long row_stride, int rows, int seq, int batches) -> const CUtensorMap* {
     const uint64_t dims[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(heads), static_cast<uint64_t>(seq),
-                              static_cast<uint64_t>(c.B)};
+                              static_cast<uint64_t>(batches)};
     const uint64_t strides[3] = {static_cast<uint64_t>(D), static_cast<uint64_t>(row_stride),
                                  static_cast<uint64_t>(row_stride) * seq};
     const uint32_t box[4] = {64, 1, static_cast<uint32_t>(rows), 1};
@@ -490,13 +517,15 @@ int launch_bwd(const BwdCall& c) {
   };
   constexpr bool DKV = (MODE == MODE_DKV);
   // Resident operands use 128-row boxes, streamed operands 64-row boxes.
-  const CUtensorMap* mq = make(c.q, c.Hq, c.q_row_stride, DKV ? 64 : 128, Sq);
-  const CUtensorMap* mk = make(c.k, c.Hkv, c.k_row_stride, DKV ? 128 : 64, c.S);
-  const CUtensorMap* mv = make(c.v, c.Hkv, c.v_row_stride, DKV ? 128 : 64, c.S);
-  const CUtensorMap* mdo = make(c.dout, c.Hq, c.do_row_stride, DKV ? 64 : 128, Sq);
-  const CUtensorMap* mo1 = DKV ? make(c.dv, c.Hkv, c.dv_row_stride, 128, c.S)
-                               : make(c.dq, c.Hq, c.dq_row_stride, 128, Sq);
-  const CUtensorMap* mo2 = DKV ? make(c.dk, c.Hkv, c.dk_row_stride, 128, c.S) : mo1;
+  // grouped: Q / dO / dQ are the gathered rows (one batch, one head)
+  const int qh = grouped ? 1 : c.Hq, qb = grouped ? 1 : c.B;
+  const CUtensorMap* mq = make(c.q, qh, c.q_row_stride, DKV ? 64 : 128, Sq, qb);
+  const CUtensorMap* mk = make(c.k, c.Hkv, c.k_row_stride, DKV ? 128 : 64, c.S, c.B);
+  const CUtensorMap* mv = make(c.v, c.Hkv, c.v_row_stride, DKV ? 128 : 64, c.S, c.B);
+  const CUtensorMap* mdo = make(c.dout, qh, c.do_row_stride, DKV ? 64 : 128, Sq, qb);
+  const CUtensorMap* mo1 = DKV ? make(c.dv, c.Hkv, c.dv_row_stride, 128, c.S, c.B)
+                               : make(c.dq, qh, c.dq_row_stride, 128, Sq, qb);
+  const CUtensorMap* mo2 = DKV ? make(c.dk, c.Hkv, c.dk_row_stride, 128, c.S, c.B) : mo1;
   if (!mq || !mk || !mv || !mdo || !mo1 || !mo2) return 1;
   BwdArgs a{};
   a.B = c.B; a.S = c.S; a.Hq = c.Hq; a.Hkv = c.Hkv;
@@ -507,6 +536,7 @@ int launch_bwd(const BwdCall& c) {
   a.run_start = c.run_start; a.run_end = c.run_end; a.first_q = c.first_q;
   a.neg_lse2 = c.neg_lse2; a.neg_delta = c.neg_delta;
   a.sp = c.sp;
+  a.grp = c.grp;
   a.status = device_status();
   a.spin_budget = c.spin_budget > 0 ? c.spin_budget : CTB_SPIN_BUDGET;
   auto kern = attn_bwd_kernel<D, MODE>;
@@ -517,7 +547,8 @@ int launch_bwd(const BwdCall& c) {
     CTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES));
     configured_dev = dev;
   }
-  const int grid = DKV ? c.B * c.Hkv * (c.S / 128) : c.B * c.Hq * (Sq / 128);
+  const int grid = grouped ? c.ctas : (DKV ? c.B * c.Hkv * (c.S / 128) : c.B * c.Hq * (Sq / 128));
+  if (grid <= 0) return 0;
   kern<<<grid, BWD_THREADS, L::BYTES, static_cast<cudaStream_t>(c.stream)>>>(*mq, *mk, *mv, *mdo, *mo1, *mo2, a);
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
@@ -600,6 +631,33 @@ CTB_API int ctb_attn_bwd_sparse(int mode, const void* q, const void* k, const vo
   c.sp.it_off = it_off; c.sp.it_cnt = it_cnt; c.sp.it_stride = it_stride; c.sp.it_list = it_list; c.sp.sel = sel;
   c.sp.doc_start = doc_start;
   c.sp.allsel = allsel; c.sp.block = block; c.sp.words = words;
+  using namespace ctb::attn;
+  if (D == 128) return mode == 0 ? launch_bwd<128, MODE_DKV>(c) : launch_bwd<128, MODE_DQ>(c);
+  if (D == 64) return mode == 0 ? launch_bwd<64, MODE_DKV>(c) : launch_bwd<64, MODE_DQ>(c);
+  return ctb::fail("attention: head_dim must be 64 or 128");
+}
+
+// Grouped MoBA backward (see GroupArgs).  mode 0 (dK/dV): one CTA per (group, 128-key tile), `ctas`
+// descriptors; dk / dv are [B,S,Hkv,D] views that receive the history part (tiles of groups without
+// rows are not written: clear the buffers first).  mode 1 (dQ): one CTA per 128 gathered rows,
+// gathered_rows / 128 descriptors; dqg is [gathered_rows, D].  qg / dog / the statistics are the
+// gathered rows ([gathered_rows, D] contiguous, [gathered_rows] fp32, padding rows zero).
+CTB_API int ctb_attn_bwd_grouped(int mode, const void* qg, const void* k, const void* v, const void* dog, void* dqg,
+                                 void* dk, void* dv, const float* neg_lse2_g, const float* neg_delta_g,
+                                 const void* desc, int ctas, int gathered_rows, int block, int B, int S, int Hkv, int D,
+                                 long k_rs, long v_rs, long dk_rs, long dv_rs, float scale, long long spin_budget,
+                                 void* stream) {
+  if (S % 128 || block % 128 || block < 128) return ctb::fail("grouped attention: S and the block must be multiples of 128");
+  if (gathered_rows <= 0 || gathered_rows % 256) return ctb::fail("grouped attention: gathered rows must be a positive multiple of 256");
+  ctb::attn::BwdCall c{};
+  c.q = qg; c.k = k; c.v = v; c.dout = dog; c.dq = dqg; c.dk = dk; c.dv = dv;
+  c.neg_lse2 = neg_lse2_g; c.neg_delta = neg_delta_g;
+  c.B = B; c.S = S; c.Hq = Hkv; c.Hkv = Hkv;
+  c.q_row_stride = D; c.do_row_stride = D; c.dq_row_stride = D;
+  c.k_row_stride = k_rs; c.v_row_stride = v_rs; c.dk_row_stride = dk_rs; c.dv_row_stride = dv_rs;
+  c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
+  c.grp.desc = static_cast<const int4*>(desc); c.grp.block = block; c.gathered_rows = gathered_rows;
+  c.ctas = mode == 0 ? ctas : gathered_rows / 128;
   using namespace ctb::attn;
   if (D == 128) return mode == 0 ? launch_bwd<128, MODE_DKV>(c) : launch_bwd<128, MODE_DQ>(c);
   if (D == 64) return mode == 0 ? launch_bwd<64, MODE_DKV>(c) : launch_bwd<64, MODE_DQ>(c);

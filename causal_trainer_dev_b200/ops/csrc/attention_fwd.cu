@@ -74,23 +74,31 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
   const long long budget = args.spin_budget;
 
   // ---- work item ----
+  // grouped MoBA: this CTA's 256 gathered rows against one key block (see GroupArgs)
+  const bool grouped = args.grp.desc != nullptr;
+  int4 gd = make_int4(0, 0, 0, 0);
+  if (grouped) {
+    gd = __ldg(args.grp.desc + blockIdx.x);
+    if (gd.w <= 0) return;                       // capacity beyond the rows in use: the whole CTA leaves
+  }
   const int nqp = (args.Sq + 255) / 256;
   int idx = blockIdx.x;
-  const int h = idx % args.Hq;
+  const int h = grouped ? 0 : idx % args.Hq;
   idx /= args.Hq;
-  const int b = idx % args.B;
-  const int pair = nqp - 1 - idx / args.B;
+  const int b = grouped ? 0 : idx % args.B;
+  const int pair = grouped ? static_cast<int>(blockIdx.x) : nqp - 1 - idx / args.B;
   const int q0 = pair * 256;
-  const int hkv = h / (args.Hq / args.Hkv);
+  const int hkv = grouped ? (gd.x >> 16) : h / (args.Hq / args.Hkv);
+  const int kb = grouped ? (gd.x & 0xffff) : b;  // batch of the keys
   const int nqb = args.S / 128;
   bool tile_valid[2];
   int lo_t[2], hi_t[2];
 #pragma unroll
   for (int t = 0; t < 2; ++t) {
-    tile_valid[t] = (q0 + t * 128) < args.Sq;
+    tile_valid[t] = grouped ? (t * 128 < gd.w) : (q0 + t * 128) < args.Sq;
     lo_t[t] = 0;
     hi_t[t] = 0;
-    if (tile_valid[t]) {
+    if (tile_valid[t] && !grouped) {
       const int qb = (args.q_off + q0) / 128 + t;      // query block in the whole sequence
       const int lo_tok = args.kv_lo[b * nqb + qb];
       const int hi_tok = args.kv_hi[b * nqb + qb];
@@ -117,8 +125,15 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     n0 = tile_valid[0] ? cnt : 0;
     n1 = tile_valid[1] ? cnt : 0;
   }
+  if (grouped) {
+    n0 = args.grp.block / 128;
+    n1 = tile_valid[1] ? n0 : 0;
+  }
   const int nmax = max(n0, n1);
-  auto kv_tile = [&](int i) -> int { return sparse ? __ldg(kv_list + i) : lo + i; };
+  // first key of the i-th key tile this CTA visits
+  auto kv_pos = [&](int i) -> int {
+    return grouped ? gd.y + i * 128 : (sparse ? __ldg(kv_list + i) : lo + i) * 128;
+  };
 
   if (threadIdx.x == 0) {
     mbar_init(q_full, 1);
@@ -165,7 +180,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       uint32_t slot = 0, phase = 0;
       bool ok = true;
       for (int i = 0; ok && i < nmax; ++i) {
-        const int k0 = kv_tile(i) * 128;
+        const int k0 = kv_pos(i);
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
           if (!mbar_wait(&kv_empty[slot], phase ^ 1u, abort_flag, st, SITE_F_PROD, budget)) {
@@ -176,7 +191,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
           uint8_t* dst = smem + L::OFF_KV + slot * L::QT;
           const CUtensorMap* m = which == 0 ? &map_k : &map_v;
 #pragma unroll
-          for (int hf = 0; hf < HALVES; ++hf) tma_load_4d(dst + hf * 16384, m, &kv_full[slot], hf * 64, hkv, k0, b);
+          for (int hf = 0; hf < HALVES; ++hf) tma_load_4d(dst + hf * 16384, m, &kv_full[slot], hf * 64, hkv, k0, kb);
           if (++slot == KV_SLOTS) {
             slot = 0;
             phase ^= 1u;
@@ -266,7 +281,12 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     const int qi_local = q0 + t * 128 + r;             // row of Q / O / LSE held by this rank
     const int qi = args.q_off + qi_local;              // its position in the whole sequence
     int my_seg = 0, my_lim = qi, my_start = 0, my_first = 0;
-    if (tile_valid[t]) {
+    if (tile_valid[t] && grouped) {
+      // a real gathered row sees every key of the block; a padding row sees none
+      my_seg = (t * 128 + r < gd.w) ? 1 : 0;
+      my_first = -(1 << 30);
+      my_lim = 1 << 30;
+    } else if (tile_valid[t]) {
       my_seg = args.seg[b * args.S + qi];
       my_first = args.row_start[b * args.S + qi];
       if (args.lim != nullptr) my_lim = args.lim[b * args.S + qi];
@@ -275,8 +295,7 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
     uint32_t sph = 0;
     const uint64_t scale2 = pack_f32x2(args.scale_log2, args.scale_log2);
     for (int i = 0; i < n_mine; ++i) {
-      const int j = kv_tile(i);
-      const int k0 = j * 128;
+      const int k0 = kv_pos(i);
       // ---- visible columns of this row inside the key tile: the keys of a row's run are
       // contiguous, so they form one interval [c_lo, c_hi] (tile-relative, may lie outside) ----
       const int c_lo = my_first - k0;
@@ -427,9 +446,11 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
 template <int D>
 int launch_fwd(const FwdCall& c) {
   using L = FwdSmem<D>;
-  const int Sq = c.Sq > 0 ? c.Sq : c.S;
-  const uint64_t dq[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.Hq), static_cast<uint64_t>(Sq),
-                          static_cast<uint64_t>(c.B)};
+  const bool grouped = c.grp.desc != nullptr;
+  const int Sq = grouped ? c.gathered_rows : (c.Sq > 0 ? c.Sq : c.S);
+  // grouped: Q / O are the gathered rows, one batch and one head
+  const uint64_t dq[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(grouped ? 1 : c.Hq), static_cast<uint64_t>(Sq),
+                          static_cast<uint64_t>(grouped ? 1 : c.B)};
   const uint64_t dk[4] = {static_cast<uint64_t>(D), static_cast<uint64_t>(c.Hkv), static_cast<uint64_t>(c.S),
                           static_cast<uint64_t>(c.B)};
   const uint32_t box[4] = {64, 1, 128, 1};
@@ -447,12 +468,13 @@ int launch_fwd(const FwdCall& c) {
   const CUtensorMap* mo = get_tensor_map_4d(c.o, Elt::BF16, dq, so, box, true);
   if (!mq || !mk || !mv || !mo) return 1;
   FwdArgs a{};
-  a.B = c.B; a.S = c.S; a.Hq = c.Hq; a.Hkv = c.Hkv;
+  a.B = c.B; a.S = c.S; a.Hq = grouped ? 1 : c.Hq; a.Hkv = grouped ? 1 : c.Hkv;
   a.Sq = Sq; a.q_off = c.q_off;
   a.scale_log2 = c.scale * 1.4426950408889634f;
   a.seg = c.seg; a.lim = c.lim; a.row_start = c.row_start; a.kv_lo = c.kv_lo; a.kv_hi = c.kv_hi;
   a.lse = c.lse;
   a.sp = c.sp;
+  a.grp = c.grp;
   a.status = device_status();
   a.spin_budget = c.spin_budget > 0 ? c.spin_budget : CTB_SPIN_BUDGET;
   auto kern = attn_fwd_kernel<D>;
@@ -463,7 +485,7 @@ int launch_fwd(const FwdCall& c) {
     CTB_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::BYTES));
     configured_dev = dev;
   }
-  const int grid = c.B * c.Hq * ((Sq + 255) / 256);
+  const int grid = grouped ? Sq / 256 : c.B * c.Hq * ((Sq + 255) / 256);
   kern<<<grid, FWD_THREADS, L::BYTES, static_cast<cudaStream_t>(c.stream)>>>(*mq, *mk, *mv, *mo, a);
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
@@ -529,6 +551,25 @@ CTB_API int ctb_attn_fwd_sparse(const void* q, const void* k, const void* v, voi
   c.o_row_stride = o_row_stride; c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
   c.sp.it_off = it_off; c.sp.it_cnt = it_cnt; c.sp.it_stride = it_stride; c.sp.it_list = it_list; c.sp.sel = sel;
   c.sp.doc_start = doc_start; c.sp.block = block; c.sp.words = words;
+  if (D == 128) return ctb::attn::launch_fwd<128>(c);
+  if (D == 64) return ctb::attn::launch_fwd<64>(c);
+  return ctb::fail("attention: head_dim must be 64 or 128");
+}
+
+// Grouped MoBA forward (see GroupArgs): qg / og are [gathered_rows, D] contiguous, lse_g
+// [gathered_rows]; k / v are the usual [B,S,Hkv,D] views; desc has gathered_rows / 256 entries.
+CTB_API int ctb_attn_fwd_grouped(const void* qg, const void* k, const void* v, void* og, float* lse_g, const void* desc,
+                                 int gathered_rows, int block, int B, int S, int Hkv, int D, long k_row_stride,
+                                 long v_row_stride, float scale, long long spin_budget, void* stream) {
+  if (S % 128 || block % 128 || block < 128) return ctb::fail("grouped attention: S and the block must be multiples of 128");
+  if (gathered_rows <= 0 || gathered_rows % 256) return ctb::fail("grouped attention: gathered rows must be a positive multiple of 256");
+  if (B > 0xffff || Hkv > 0x7fff) return ctb::fail("grouped attention: batch or head count too large for the descriptor");
+  ctb::attn::FwdCall c{};
+  c.q = qg; c.k = k; c.v = v; c.o = og; c.lse = lse_g;
+  c.B = B; c.S = S; c.Hq = Hkv; c.Hkv = Hkv;
+  c.q_row_stride = D; c.k_row_stride = k_row_stride; c.v_row_stride = v_row_stride; c.o_row_stride = D;
+  c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
+  c.grp.desc = static_cast<const int4*>(desc); c.grp.block = block; c.gathered_rows = gathered_rows;
   if (D == 128) return ctb::attn::launch_fwd<128>(c);
   if (D == 64) return ctb::attn::launch_fwd<64>(c);
   return ctb::fail("attention: head_dim must be 64 or 128");

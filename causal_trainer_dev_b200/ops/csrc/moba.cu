@@ -347,3 +347,440 @@ CTB_API int ctb_moba_lists(int mode, const unsigned* touch, int B, int S, int Hq
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
 }
+
+// ------------------------------------------------------------------------------------------
+// Query grouping: cost proportional to the routing budget.
+//
+// A *group* is one complete key block of one (batch, kv head): (b, hkv, first key ks).  Every
+// (token, query head) row that selected the block joins the group; the rows of a group are laid
+// out next to each other in a gathered row space, groups one after another, each padded with zero
+// rows to a multiple of 256.  The history part of MoBA is then dense, unmasked attention of each
+// group's rows against its block (attention_fwd.cu / attention_bwd.cu, GroupArgs), and the own
+// block of every query is a separate causal pass; moba_merge combines the partial softmaxes by
+// their log-sum-exp.  The placement is a stable counting sort written without atomics, so that the
+// order of the rows inside a group (and with it every floating-point sum over a group) is a pure
+// function of the routing:
+//
+//   moba_rank    one warp per (batch, head, block index c): walks the sequence and gives every row
+//                that selected block c of its document its rank among such rows of the same
+//                (document, head); the last of them leaves the count in cnt[group][head in group].
+//   moba_groups  one CTA: exclusive scan of the padded group sizes -> first row of every group,
+//                offsets of the heads inside a group, the compact list of non-empty groups.
+//   moba_desc    descriptors of the CTAs of the grouped flash kernels.
+//   moba_fill    gathered position of every (row, pick) and its inverse.
+//
+// Reference counterpart: group_queries and its inverse permutation
+// (src/causal_trainer/kernels/grouped_moba.py:25-57).
+// ------------------------------------------------------------------------------------------
+namespace ctb {
+namespace moba {
+
+__global__ void __launch_bounds__(256)
+moba_rank_kernel(const unsigned* __restrict__ sel, const int* __restrict__ seg, const int* __restrict__ doc_start,
+                 int B, int S, int Hq, int Hkv, int block, int words, int nblk, int picks,
+                 int* __restrict__ rank, int* __restrict__ cnt) {
+  const long warp_id = (blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  const long total = static_cast<long>(B) * Hq * nblk;
+  if (warp_id >= total) return;
+  const int c = static_cast<int>(warp_id % nblk);
+  const int h = static_cast<int>((warp_id / nblk) % Hq);
+  const int b = static_cast<int>(warp_id / nblk / Hq);
+  const int gsize = Hq / Hkv;
+  const int hkv = h / gsize, hg = h % gsize;
+  const int nt128 = S / 128;
+  const int word = c >> 5;
+  const unsigned below = (1u << (c & 31)) - 1u;
+  int carry_start = -1, carry_count = 0;
+  for (int i0 = 0; i0 < S; i0 += 32) {
+    const int i = i0 + lane;
+    const int sg = seg[b * S + i];
+    const int st = doc_start[b * S + i];
+    const int cur = (i - st) / block;
+    const unsigned* mine = sel + ((static_cast<size_t>(b) * Hq + h) * S + i) * words;
+    const unsigned w = (sg != 0 && word < words) ? __ldg(mine + word) : 0u;
+    const bool picked = sg != 0 && c < cur && ((w >> (c & 31)) & 1u);
+    const unsigned peers = __match_any_sync(0xffffffffu, st);
+    const unsigned pk = __ballot_sync(0xffffffffu, picked);
+    const unsigned mates = peers & pk;
+    const int my_rank = __popc(mates & ((1u << lane) - 1u)) + (st == carry_start ? carry_count : 0);
+    if (picked) {
+      int j = __popc(w & below);                       // earlier picks of this row: its slot for block c
+      for (int x = 0; x < word; ++x) j += __popc(__ldg(mine + x));
+      if (j < picks) rank[((static_cast<size_t>(b) * Hq + h) * S + i) * picks + j] = my_rank;
+      if ((mates >> lane) == 1u) {                     // last picked row of this document in the chunk
+        const int g = (b * Hkv + hkv) * nt128 + ((st + c * block) >> 7);
+        cnt[g * gsize + hg] = my_rank + 1;             // later chunks overwrite with the larger count
+      }
+    }
+    const int last_start = __shfl_sync(0xffffffffu, st, 31);
+    const unsigned last_mates = __shfl_sync(0xffffffffu, mates, 31);
+    const int add = __popc(last_mates);
+    carry_count = (last_start == carry_start ? carry_count : 0) + add;
+    carry_start = last_start;
+  }
+}
+
+// ginfo[slot] = (batch | hkv << 16, first key, first gathered row, rows incl. padding); greal[slot] = real rows;
+// totals[0] = gathered rows in use, totals[1] = non-empty groups.
+__global__ void __launch_bounds__(1024)
+moba_groups_kernel(const int* __restrict__ cnt, const int* __restrict__ pool_start, int G, int gsize, int Hkv,
+                   int nt128, int* __restrict__ row0, int* __restrict__ hoff, int4* __restrict__ ginfo,
+                   int* __restrict__ greal, int* __restrict__ totals, int slot_cap) {
+  __shared__ int s_rows[1024];
+  __shared__ int s_slots[1024];
+  const int t = threadIdx.x;
+  const int per = (G + 1023) / 1024;
+  const int g_lo = t * per, g_hi = min(G, g_lo + per);
+  int rows = 0, slots = 0;
+  for (int g = g_lo; g < g_hi; ++g) {
+    int r = 0;
+    for (int x = 0; x < gsize; ++x) r += cnt[g * gsize + x];
+    if (r > 0) {
+      rows += (r + 255) & ~255;
+      ++slots;
+    }
+  }
+  s_rows[t] = rows;
+  s_slots[t] = slots;
+  __syncthreads();
+  // inclusive scan over the 1024 partial sums (Hillis-Steele, two values)
+  for (int off = 1; off < 1024; off <<= 1) {
+    const int a = t >= off ? s_rows[t - off] : 0;
+    const int c = t >= off ? s_slots[t - off] : 0;
+    __syncthreads();
+    s_rows[t] += a;
+    s_slots[t] += c;
+    __syncthreads();
+  }
+  int row = s_rows[t] - rows, slot = s_slots[t] - slots;
+  for (int g = g_lo; g < g_hi; ++g) {
+    int r = 0;
+    for (int x = 0; x < gsize; ++x) {
+      hoff[g * gsize + x] = r;
+      r += cnt[g * gsize + x];
+    }
+    row0[g] = row;
+    if (r > 0) {
+      const int padded = (r + 255) & ~255;
+      if (slot < slot_cap) {
+        const int tile = g % nt128, hkv = (g / nt128) % Hkv, b = g / nt128 / Hkv;
+        ginfo[slot] = make_int4(b | (hkv << 16), pool_start[b * nt128 + tile], row, padded);
+        greal[slot] = r;
+      }
+      row += padded;
+      ++slot;
+    }
+  }
+  if (t == 1023) {
+    totals[0] = s_rows[1023];
+    totals[1] = min(s_slots[1023], slot_cap);
+  }
+}
+
+__global__ void moba_desc_kernel(const int4* __restrict__ ginfo, const int* __restrict__ greal,
+                                 const int* __restrict__ totals, int tiles128_cap, int slot_cap, int block_tiles,
+                                 int4* __restrict__ fwd_desc, int4* __restrict__ dq_desc, int4* __restrict__ dkv_desc) {
+  const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+  const int total_rows = totals[0], n_slots = totals[1];
+  if (idx < tiles128_cap) {
+    const int row = idx * 128;
+    int4 d = make_int4(0, 0, 0, 0);
+    int real_left = 0;
+    if (row < total_rows) {
+      int lo = 0, hi = n_slots - 1;                 // last slot whose first row is <= row
+      while (lo < hi) {
+        const int mid = (lo + hi + 1) >> 1;
+        if (ginfo[mid].z <= row) lo = mid; else hi = mid - 1;
+      }
+      const int4 gi = ginfo[lo];
+      real_left = greal[lo] - (row - gi.z);
+      d = make_int4(gi.x, gi.y, 0, max(0, min(128, real_left)));
+    }
+    dq_desc[idx] = d;
+    if ((idx & 1) == 0) {
+      d.w = max(0, min(256, real_left));
+      fwd_desc[idx >> 1] = d;
+    }
+  }
+  const int k = idx - tiles128_cap;
+  if (k >= 0 && k < slot_cap * block_tiles) {
+    const int slot = k / block_tiles, t = k % block_tiles;
+    int4 d = make_int4(0, 0, 0, 0);
+    if (slot < n_slots) {
+      const int4 gi = ginfo[slot];
+      d = make_int4(gi.x, gi.y + t * 128, gi.z, gi.w);
+    }
+    dkv_desc[k] = d;
+  }
+}
+
+// One thread per (batch, head, token): gathered position of each of its picks.
+__global__ void moba_fill_kernel(const unsigned* __restrict__ sel, const int* __restrict__ seg,
+                                 const int* __restrict__ doc_start, const int* __restrict__ rank,
+                                 const int* __restrict__ row0, const int* __restrict__ hoff, int B, int S, int Hq,
+                                 int Hkv, int block, int words, int picks, int* __restrict__ row_of,
+                                 int* __restrict__ pos_of) {
+  const long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
+  const long total = static_cast<long>(B) * Hq * S;
+  if (idx >= total) return;
+  const int i = static_cast<int>(idx % S);
+  const int h = static_cast<int>((idx / S) % Hq);
+  const int b = static_cast<int>(idx / S / Hq);
+  const int gsize = Hq / Hkv;
+  const int hkv = h / gsize, hg = h % gsize;
+  const int nt128 = S / 128;
+  int* out = pos_of + idx * picks;
+  int j = 0;
+  const int sg = seg[b * S + i];
+  if (sg != 0) {
+    const int st = doc_start[b * S + i];
+    const int cur = (i - st) / block;
+    for (int w = 0; w < words && j < picks; ++w) {
+      unsigned bits = sel[idx * words + w];
+      while (bits != 0u && j < picks) {
+        const int c = w * 32 + (__ffs(bits) - 1);
+        bits &= bits - 1u;
+        if (c >= cur) continue;
+        const int g = (b * Hkv + hkv) * nt128 + ((st + c * block) >> 7);
+        const int pos = row0[g] + hoff[g * gsize + hg] + rank[idx * picks + j];
+        out[j] = pos;
+        row_of[pos] = (b * S + i) * Hq + h;
+        ++j;
+      }
+    }
+  }
+  for (; j < picks; ++j) out[j] = -1;
+}
+
+// Copies the rows named by row_of (token * Hq + head, -1 = padding -> zeros) into the gathered
+// space: bf16 rows of D elements from a [B,S,Hq,D] view, and optionally two per-row fp32 statistics
+// stored [B,Hq,S].  D / 8 threads per row; only the rows in use (totals[0]) are written.
+template <int D>
+__global__ void __launch_bounds__(256)
+moba_gather_kernel(const int* __restrict__ row_of, const int* __restrict__ totals, const __nv_bfloat16* __restrict__ src,
+                   long row_stride, int S, int Hq, __nv_bfloat16* __restrict__ dst, const float* __restrict__ stat_a,
+                   const float* __restrict__ stat_b, float* __restrict__ out_a, float* __restrict__ out_b) {
+  constexpr int TPR = D / 8;
+  const int total_rows = totals[0];
+  const long stride = static_cast<long>(gridDim.x) * blockDim.x / TPR;
+  const int v = threadIdx.x % TPR;
+  for (long pos = (blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x) / TPR; pos < total_rows; pos += stride) {
+    const int id = row_of[pos];
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    float a = 0.f, bb = 0.f;
+    if (id >= 0) {
+      const int h = id % Hq;
+      const long tok = id / Hq;
+      if (src != nullptr)
+        val = *reinterpret_cast<const uint4*>(src + tok * row_stride + static_cast<long>(h) * D + v * 8);
+      if (v == 0 && stat_a != nullptr) {
+        const long at = (tok / S * Hq + h) * S + tok % S;
+        a = stat_a[at];
+        bb = stat_b[at];
+      }
+    }
+    if (dst != nullptr) reinterpret_cast<uint4*>(dst + pos * D)[v] = val;
+    if (v == 0 && out_a != nullptr) {
+      out_a[pos] = a;
+      out_b[pos] = bb;
+    }
+  }
+}
+
+// Combines the own-block partial softmax (o, lse: in place) with the partials of the picks.
+template <int D>
+__global__ void __launch_bounds__(256)
+moba_merge_fwd_kernel(__nv_bfloat16* __restrict__ o, long o_row_stride, float* __restrict__ lse,
+                      const __nv_bfloat16* __restrict__ og, const float* __restrict__ lse_g,
+                      const int* __restrict__ pos_of, int B, int S, int Hq, int picks) {
+  constexpr int TPR = D / 8;
+  const long row = (blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x) / TPR;   // (b, h, i) order of pos_of
+  const int v = threadIdx.x % TPR;
+  if (row >= static_cast<long>(B) * Hq * S) return;
+  const int* mine = pos_of + row * picks;
+  if (mine[0] < 0) return;                             // no history: the own-block result is final
+  const int i = static_cast<int>(row % S);
+  const int h = static_cast<int>((row / S) % Hq);
+  const long tok = row / S / Hq * S + i;
+  __nv_bfloat16* op = o + tok * o_row_stride + static_cast<long>(h) * D + v * 8;
+  const float l0 = lse[row];
+  float m = l0;
+  for (int j = 0; j < picks; ++j) {
+    const int p = mine[j];
+    if (p >= 0) m = fmaxf(m, lse_g[p]);
+  }
+  float acc[8];
+  float wsum = __expf(l0 - m);
+  {
+    const uint4 raw = *reinterpret_cast<const uint4*>(op);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h2[e]);
+      acc[2 * e] = f.x * wsum;
+      acc[2 * e + 1] = f.y * wsum;
+    }
+  }
+  for (int j = 0; j < picks; ++j) {
+    const int p = mine[j];
+    if (p < 0) continue;
+    const float w = __expf(lse_g[p] - m);
+    wsum += w;
+    const uint4 raw = reinterpret_cast<const uint4*>(og + static_cast<long>(p) * D)[v];
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h2[e]);
+      acc[2 * e] += f.x * w;
+      acc[2 * e + 1] += f.y * w;
+    }
+  }
+  const float inv = 1.f / wsum;
+  uint4 out;
+  __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(acc[2 * e] * inv, acc[2 * e + 1] * inv);
+  *reinterpret_cast<uint4*>(op) = out;
+  if (v == 0) lse[row] = m + __logf(wsum);
+}
+
+// dq[b, i, h, :] += sum over the row's picks of dqg[pos].
+template <int D>
+__global__ void __launch_bounds__(256)
+moba_merge_dq_kernel(__nv_bfloat16* __restrict__ dq, long dq_row_stride, const __nv_bfloat16* __restrict__ dqg,
+                     const int* __restrict__ pos_of, int B, int S, int Hq, int picks) {
+  constexpr int TPR = D / 8;
+  const long row = (blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x) / TPR;
+  const int v = threadIdx.x % TPR;
+  if (row >= static_cast<long>(B) * Hq * S) return;
+  const int* mine = pos_of + row * picks;
+  if (mine[0] < 0) return;
+  const int i = static_cast<int>(row % S);
+  const int h = static_cast<int>((row / S) % Hq);
+  const long tok = row / S / Hq * S + i;
+  __nv_bfloat16* dp = dq + tok * dq_row_stride + static_cast<long>(h) * D + v * 8;
+  float acc[8];
+  {
+    const uint4 raw = *reinterpret_cast<const uint4*>(dp);
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h2[e]);
+      acc[2 * e] = f.x;
+      acc[2 * e + 1] = f.y;
+    }
+  }
+  for (int j = 0; j < picks; ++j) {
+    const int p = mine[j];
+    if (p < 0) continue;
+    const uint4 raw = reinterpret_cast<const uint4*>(dqg + static_cast<long>(p) * D)[v];
+    const __nv_bfloat162* h2 = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float2 f = __bfloat1622float2(h2[e]);
+      acc[2 * e] += f.x;
+      acc[2 * e + 1] += f.y;
+    }
+  }
+  uint4 out;
+  __nv_bfloat162* oh = reinterpret_cast<__nv_bfloat162*>(&out);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) oh[e] = __floats2bfloat162_rn(acc[2 * e], acc[2 * e + 1]);
+  *reinterpret_cast<uint4*>(dp) = out;
+}
+
+}  // namespace moba
+}  // namespace ctb
+
+// Grouping of the routed (token, head) rows by selected key block.  Sizes: G = B * Hkv * S / 128
+// potential groups, slot_cap = B * Hkv * ceil(S / block) non-empty ones at most, rows_cap gathered
+// rows (a multiple of 256, >= B * Hq * S * picks + 256 * slot_cap).  Buffers (all device, int32):
+//   rank [B,Hq,S,picks]  cnt [G, Hq/Hkv]  row0 [G]  hoff [G, Hq/Hkv]  ginfo [slot_cap] int4  greal [slot_cap]
+//   totals [2]  fwd_desc [rows_cap/256] int4  dq_desc [rows_cap/128] int4  dkv_desc [slot_cap * block/128] int4
+//   row_of [rows_cap]  pos_of [B,Hq,S,picks]
+CTB_API int ctb_moba_group(const unsigned* sel, const int* seg, const int* doc_start, const int* pool_start, int B,
+                           int S, int Hq, int Hkv, int block, int words, int picks, int rows_cap, int slot_cap,
+                           int* rank, int* cnt, int* row0, int* hoff, void* ginfo, int* greal, int* totals,
+                           void* fwd_desc, void* dq_desc, void* dkv_desc, int* row_of, int* pos_of, void* stream) {
+  if (S % 128 || block % 128 || block < 128) return fail("moba_group: S and the block must be multiples of 128");
+  if (picks < 1 || Hq % Hkv) return fail("moba_group: needs at least one pick per row and Hq a multiple of Hkv");
+  if (rows_cap % 256 || B > 0xffff || Hkv > 0x7fff) return fail("moba_group: sizes out of range");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int gsize = Hq / Hkv, nt128 = S / 128, G = B * Hkv * nt128;
+  const int nblk = (S + block - 1) / block;
+  CTB_CUDA_OK(cudaMemsetAsync(cnt, 0, sizeof(int) * static_cast<size_t>(G) * gsize, s));
+  CTB_CUDA_OK(cudaMemsetAsync(row_of, 0xff, sizeof(int) * static_cast<size_t>(rows_cap), s));
+  const long warps = static_cast<long>(B) * Hq * nblk;
+  moba::moba_rank_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, s>>>(
+      sel, seg, doc_start, B, S, Hq, Hkv, block, words, nblk, picks, rank, cnt);
+  CTB_CUDA_OK(cudaGetLastError());
+  moba::moba_groups_kernel<<<1, 1024, 0, s>>>(cnt, pool_start, G, gsize, Hkv, nt128, row0, hoff,
+                                              static_cast<int4*>(ginfo), greal, totals, slot_cap);
+  CTB_CUDA_OK(cudaGetLastError());
+  const int tiles128 = rows_cap / 128, block_tiles = block / 128;
+  const int work = tiles128 + slot_cap * block_tiles;
+  moba::moba_desc_kernel<<<(work + 255) / 256, 256, 0, s>>>(static_cast<const int4*>(ginfo), greal, totals, tiles128,
+                                                           slot_cap, block_tiles, static_cast<int4*>(fwd_desc),
+                                                           static_cast<int4*>(dq_desc), static_cast<int4*>(dkv_desc));
+  CTB_CUDA_OK(cudaGetLastError());
+  const long rows = static_cast<long>(B) * Hq * S;
+  moba::moba_fill_kernel<<<static_cast<unsigned>((rows + 255) / 256), 256, 0, s>>>(
+      sel, seg, doc_start, rank, row0, hoff, B, S, Hq, Hkv, block, words, picks, row_of, pos_of);
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// dst[pos] = src[row_of[pos]] (bf16 rows of a [B,S,Hq,D] view; may be null) and, when stat_a is
+// given, out_a / out_b [pos] = stat_a / stat_b [B,Hq,S]; padding rows become zero.
+CTB_API int ctb_moba_gather(const int* row_of, const int* totals, const void* src, long row_stride, int S, int Hq,
+                            int D, void* dst, const float* stat_a, const float* stat_b, float* out_a, float* out_b,
+                            int rows_cap, void* stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int grid = ctb::sm_count() * 8;
+  const __nv_bfloat16* sp = static_cast<const __nv_bfloat16*>(src);
+  __nv_bfloat16* dp = static_cast<__nv_bfloat16*>(dst);
+  if (D == 128)
+    moba::moba_gather_kernel<128><<<grid, 256, 0, s>>>(row_of, totals, sp, row_stride, S, Hq, dp, stat_a, stat_b, out_a, out_b);
+  else if (D == 64)
+    moba::moba_gather_kernel<64><<<grid, 256, 0, s>>>(row_of, totals, sp, row_stride, S, Hq, dp, stat_a, stat_b, out_a, out_b);
+  else
+    return fail("moba_gather: head_dim must be 64 or 128");
+  (void)rows_cap;
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+CTB_API int ctb_moba_merge_fwd(void* o, long o_row_stride, float* lse, const void* og, const float* lse_g,
+                               const int* pos_of, int B, int S, int Hq, int D, int picks, void* stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long threads = static_cast<long>(B) * Hq * S * (D / 8);
+  const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+  if (D == 128)
+    moba::moba_merge_fwd_kernel<128><<<grid, 256, 0, s>>>(static_cast<__nv_bfloat16*>(o), o_row_stride, lse,
+                                                          static_cast<const __nv_bfloat16*>(og), lse_g, pos_of, B, S, Hq, picks);
+  else if (D == 64)
+    moba::moba_merge_fwd_kernel<64><<<grid, 256, 0, s>>>(static_cast<__nv_bfloat16*>(o), o_row_stride, lse,
+                                                         static_cast<const __nv_bfloat16*>(og), lse_g, pos_of, B, S, Hq, picks);
+  else
+    return fail("moba_merge: head_dim must be 64 or 128");
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+CTB_API int ctb_moba_merge_dq(void* dq, long dq_row_stride, const void* dqg, const int* pos_of, int B, int S, int Hq,
+                              int D, int picks, void* stream) {
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const long threads = static_cast<long>(B) * Hq * S * (D / 8);
+  const unsigned grid = static_cast<unsigned>((threads + 255) / 256);
+  if (D == 128)
+    moba::moba_merge_dq_kernel<128><<<grid, 256, 0, s>>>(static_cast<__nv_bfloat16*>(dq), dq_row_stride,
+                                                         static_cast<const __nv_bfloat16*>(dqg), pos_of, B, S, Hq, picks);
+  else if (D == 64)
+    moba::moba_merge_dq_kernel<64><<<grid, 256, 0, s>>>(static_cast<__nv_bfloat16*>(dq), dq_row_stride,
+                                                        static_cast<const __nv_bfloat16*>(dqg), pos_of, B, S, Hq, picks);
+  else
+    return fail("moba_merge: head_dim must be 64 or 128");
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}

@@ -82,8 +82,9 @@ def document_starts(seg: torch.Tensor) -> torch.Tensor:
 
 
 def route(q: torch.Tensor, k: torch.Tensor, seg: torch.Tensor, doc_start: torch.Tensor, block: int,
-          top_k: int) -> torch.Tensor:
-    """Selection bit masks ``[B,Hq,S,W]`` (int32) from the pooling and routing kernels."""
+          top_k: int, with_pool_start: bool = False):
+    """Selection bit masks ``[B,Hq,S,W]`` (int32) from the pooling and routing kernels (and, on
+    request, ``pool_start [B,S/128]``: the first token of the complete block that starts in each tile)."""
     b, s, hq, d = q.shape
     hkv = k.shape[2]
     words = max(1, -(-(-(-s // block)) // 32))
@@ -98,7 +99,7 @@ def route(q: torch.Tensor, k: torch.Tensor, seg: torch.Tensor, doc_start: torch.
                             _lib.ptr(seg), _lib.ptr(doc_start), b, s, hq, hkv, d, block, top_k, words, _lib.ptr(sel),
                             _lib.stream_ptr())
     _lib.check(code, "ctb_moba_route")
-    return sel
+    return (sel, pool_start) if with_pool_start else sel
 
 
 def _touched_blocks(sel: torch.Tensor, seg: torch.Tensor, doc_start: torch.Tensor, block: int) -> torch.Tensor:
@@ -252,6 +253,161 @@ def moba_backward(q, k, v, out, dout, lse, meta: AttentionMeta, routing: MobaRou
             ctypes.c_long(_row_stride(dout)), ctypes.c_long(_row_stride(dq)), ctypes.c_long(_row_stride(dk)),
             ctypes.c_long(_row_stride(dv)), ctypes.c_float(scale), ctypes.c_longlong(spin_budget), _lib.stream_ptr())
         _lib.check(code, "ctb_attn_bwd_sparse")
+    return dq, dk, dv
+
+
+# ----------------------------------------------------------------------------------------- query grouping
+@dataclass
+class MobaGroups:
+    """Routing of one layer in grouped form: the (token, head) rows that selected a key block sit
+    next to each other in a gathered row space (``csrc/moba.cu``), so the history part of MoBA is
+    dense attention per group and its cost follows ``top_k * block``, whatever the routing."""
+
+    sel: torch.Tensor          # [B,Hq,S,W] selection bit masks
+    block: int
+    picks: int                 # top_k - 1
+    rows_cap: int              # capacity of the gathered row space (multiple of 256)
+    slot_cap: int              # most non-empty groups there can be
+    fwd_desc: torch.Tensor     # [rows_cap/256, 4] int32
+    dq_desc: torch.Tensor      # [rows_cap/128, 4]
+    dkv_desc: torch.Tensor     # [slot_cap * block/128, 4]
+    row_of: torch.Tensor       # [rows_cap] (token * Hq + head), -1 = padding
+    pos_of: torch.Tensor       # [B,Hq,S,picks] gathered position of each pick, -1 = none
+    totals: torch.Tensor       # [2] rows in use, non-empty groups
+    own_meta: AttentionMeta    # visibility of the own-block pass: every (document, block) is a run
+
+    def work_summary(self) -> dict:
+        """Reads back how much attention work the grouped pass does (tests, profiles)."""
+        rows, slots = (int(x) for x in self.totals.tolist())
+        real = int((self.row_of[:rows] >= 0).sum()) if rows else 0
+        return {"gathered_rows": rows, "real_rows": real, "groups": slots,
+                "history_tiles": rows // 128 * (self.block // 128)}
+
+
+def own_block_meta(meta: AttentionMeta, block: int) -> AttentionMeta:
+    """Metadata under which the dense kernels compute exactly the own-block part of MoBA: causal
+    attention inside each (document, block) run.  Cached on ``meta`` (one launch per micro-batch)."""
+    cache = meta.__dict__.setdefault("_own_block_meta", {})
+    if block not in cache:
+        seg = meta.seg
+        s = seg.shape[1]
+        idx = torch.arange(s, device=seg.device, dtype=torch.int32)[None, :]
+        nblk = -(-s // block)
+        runs = torch.where(seg != 0, seg * (nblk + 1) + (idx - meta.start) // block + 1, torch.zeros_like(seg))
+        from .attention import attention_metadata
+
+        cache[block] = attention_metadata((seg != 0).to(torch.int32), runs)[2]
+    return cache[block]
+
+
+def build_groups(q: torch.Tensor, k: torch.Tensor, meta: AttentionMeta, block: int, top_k: int) -> MobaGroups:
+    """Pool, route, then a stable counting sort of the routed rows by selected block (no host round
+    trip: capacities depend on shapes only, the kernels skip what is not in use)."""
+    b, s, hq, _ = q.shape
+    hkv = k.shape[2]
+    if block % 128:
+        raise ValueError("grouped MoBA needs moba_block_size to be a multiple of 128")
+    picks = top_k - 1
+    if picks < 1:
+        raise ValueError("grouped MoBA needs top_k >= 2 (top_k = 1 is the own block alone)")
+    dev = q.device
+    seg, doc_start = meta.seg, meta.start.contiguous()
+    sel, pool_start = route(q, k, seg, doc_start, block, top_k, with_pool_start=True)
+    words = sel.shape[-1]
+    gsize, nt128 = hq // hkv, s // 128
+    groups = b * hkv * nt128
+    slot_cap = b * hkv * (-(-s // block))
+    rows_cap = -(-(b * hq * s * picks) // 256) * 256 + 256 * slot_cap
+    i32 = lambda *shape: torch.empty(shape, dtype=torch.int32, device=dev)  # noqa: E731
+    rank, cnt, row0, hoff = i32(b, hq, s, picks), i32(groups, gsize), i32(groups), i32(groups, gsize)
+    ginfo, greal, totals = i32(slot_cap, 4), i32(slot_cap), i32(2)
+    fwd_desc, dq_desc, dkv_desc = i32(rows_cap // 256, 4), i32(rows_cap // 128, 4), i32(slot_cap * (block // 128), 4)
+    row_of, pos_of = i32(rows_cap), i32(b, hq, s, picks)
+    code = _lib.lib().ctb_moba_group(
+        _lib.ptr(sel), _lib.ptr(seg), _lib.ptr(doc_start), _lib.ptr(pool_start), b, s, hq, hkv, block, words, picks,
+        rows_cap, slot_cap, _lib.ptr(rank), _lib.ptr(cnt), _lib.ptr(row0), _lib.ptr(hoff), _lib.ptr(ginfo),
+        _lib.ptr(greal), _lib.ptr(totals), _lib.ptr(fwd_desc), _lib.ptr(dq_desc), _lib.ptr(dkv_desc), _lib.ptr(row_of),
+        _lib.ptr(pos_of), _lib.stream_ptr())
+    _lib.check(code, "ctb_moba_group")
+    return MobaGroups(sel, block, picks, rows_cap, slot_cap, fwd_desc, dq_desc, dkv_desc, row_of, pos_of, totals,
+                      own_block_meta(meta, block))
+
+
+def _gather(groups: MobaGroups, src: torch.Tensor | None, stats: tuple[torch.Tensor, torch.Tensor] | None, s: int,
+            hq: int, d: int):
+    dev = groups.row_of.device
+    dst = torch.empty((groups.rows_cap, d), dtype=torch.bfloat16, device=dev) if src is not None else None
+    out_a = out_b = None
+    if stats is not None:
+        out_a = torch.empty(groups.rows_cap, dtype=torch.float32, device=dev)
+        out_b = torch.empty(groups.rows_cap, dtype=torch.float32, device=dev)
+    code = _lib.lib().ctb_moba_gather(
+        _lib.ptr(groups.row_of), _lib.ptr(groups.totals), _lib.ptr(src),
+        ctypes.c_long(_row_stride(src) if src is not None else 0), s, hq, d, _lib.ptr(dst),
+        _lib.ptr(stats[0] if stats else None), _lib.ptr(stats[1] if stats else None), _lib.ptr(out_a), _lib.ptr(out_b),
+        groups.rows_cap, _lib.stream_ptr())
+    _lib.check(code, "ctb_moba_gather")
+    return dst, out_a, out_b
+
+
+def moba_grouped_forward(q, k, v, meta: AttentionMeta, groups: MobaGroups, scale: float | None = None,
+                         spin_budget: int = 0) -> tuple[torch.Tensor, torch.Tensor]:
+    """MoBA forward as own-block causal pass + dense history pass per group + log-sum-exp merge
+    (src/causal_trainer/kernels/grouped_moba.py:75-164, 418-423; moba_current_block.py:34-127).
+    Returns (O [B,S,Hq,D] bf16, LSE [B,Hq,S] fp32) of the single softmax over the union."""
+    from .attention import flash_attention_forward
+
+    b, s, hq, d = q.shape
+    hkv = k.shape[2]
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    out, lse = flash_attention_forward(q, k, v, groups.own_meta, scale, spin_budget=spin_budget)
+    qg, _, _ = _gather(groups, q, None, s, hq, d)
+    og = torch.empty_like(qg)
+    lse_g = torch.empty(groups.rows_cap, dtype=torch.float32, device=q.device)
+    L = _lib.lib()
+    code = L.ctb_attn_fwd_grouped(_lib.ptr(qg), _lib.ptr(k), _lib.ptr(v), _lib.ptr(og), _lib.ptr(lse_g),
+                                  _lib.ptr(groups.fwd_desc), groups.rows_cap, groups.block, b, s, hkv, d,
+                                  ctypes.c_long(_row_stride(k)), ctypes.c_long(_row_stride(v)), ctypes.c_float(scale),
+                                  ctypes.c_longlong(spin_budget), _lib.stream_ptr())
+    _lib.check(code, "ctb_attn_fwd_grouped")
+    code = L.ctb_moba_merge_fwd(_lib.ptr(out), ctypes.c_long(_row_stride(out)), _lib.ptr(lse), _lib.ptr(og),
+                                _lib.ptr(lse_g), _lib.ptr(groups.pos_of), b, s, hq, d, groups.picks, _lib.stream_ptr())
+    _lib.check(code, "ctb_moba_merge_fwd")
+    return out, lse
+
+
+def moba_grouped_backward(q, k, v, out, dout, lse, meta: AttentionMeta, groups: MobaGroups, scale: float | None = None,
+                          spin_budget: int = 0, dq=None, dk=None, dv=None):
+    """Backward of :func:`moba_grouped_forward`.  Every pass uses the statistics of the merged
+    softmax (total LSE, ``delta = sum O dO``), so the partial gradients simply add: own-block dQ / dK
+    / dV from the dense kernels, history dQ per gathered row (scattered back and added), history
+    dK / dV per key block over its group's rows (grouped_moba.py:177-272)."""
+    from .attention import flash_attention_backward
+
+    b, s, hq, d = q.shape
+    hkv = k.shape[2]
+    scale = 1.0 / math.sqrt(d) if scale is None else scale
+    stats = attention_backward_stats(out, dout, lse)
+    dq, dk, dv = flash_attention_backward(q, k, v, out, dout, lse, groups.own_meta, scale, spin_budget=spin_budget,
+                                          dq=dq, dk=dk, dv=dv, stats=stats)
+    qg, _, _ = _gather(groups, q, None, s, hq, d)
+    dog, lse_g, delta_g = _gather(groups, dout, stats, s, hq, d)
+    dqg = torch.empty_like(qg)
+    dkh = torch.zeros((b, s, hkv, d), dtype=torch.bfloat16, device=q.device)
+    dvh = torch.zeros_like(dkh)
+    L = _lib.lib()
+    for mode, desc in ((0, groups.dkv_desc), (1, groups.dq_desc)):
+        code = L.ctb_attn_bwd_grouped(
+            mode, _lib.ptr(qg), _lib.ptr(k), _lib.ptr(v), _lib.ptr(dog), _lib.ptr(dqg), _lib.ptr(dkh), _lib.ptr(dvh),
+            _lib.ptr(lse_g), _lib.ptr(delta_g), _lib.ptr(desc), desc.shape[0], groups.rows_cap, groups.block, b, s, hkv,
+            d, ctypes.c_long(_row_stride(k)), ctypes.c_long(_row_stride(v)), ctypes.c_long(_row_stride(dkh)),
+            ctypes.c_long(_row_stride(dvh)), ctypes.c_float(scale), ctypes.c_longlong(spin_budget), _lib.stream_ptr())
+        _lib.check(code, "ctb_attn_bwd_grouped")
+    code = L.ctb_moba_merge_dq(_lib.ptr(dq), ctypes.c_long(_row_stride(dq)), _lib.ptr(dqg), _lib.ptr(groups.pos_of), b, s,
+                               hq, d, groups.picks, _lib.stream_ptr())
+    _lib.check(code, "ctb_moba_merge_dq")
+    dk.add_(dkh)
+    dv.add_(dvh)
     return dq, dk, dv
 
 

@@ -39,10 +39,14 @@ def test_tp_primitives_match_references(cuda_lib, tmp_path):
 
 
 def _close(a: list[dict], b: list[dict], loss_tol: float, norm_tol: float) -> None:
-    for x, y in zip(a, b):
+    """Step 0 compares one forward / backward of identical weights (tight); later steps compare two
+    bf16 trajectories at a large learning rate, where rounding differences grow (looser)."""
+    trace = [(round(x["loss"], 4), round(y["loss"], 4), round(x["grad_norm"], 4), round(y["grad_norm"], 4))
+             for x, y in zip(a, b)]
+    for n, (x, y) in enumerate(zip(a, b)):
         assert x["token_count"] == y["token_count"]
-        assert abs(x["loss"] - y["loss"]) < loss_tol
-        assert abs(x["grad_norm"] - y["grad_norm"]) / y["grad_norm"] < norm_tol
+        assert abs(x["loss"] - y["loss"]) < (loss_tol if n == 0 else 3 * loss_tol), trace
+        assert abs(x["grad_norm"] - y["grad_norm"]) / y["grad_norm"] < (norm_tol if n == 0 else 2 * norm_tol), trace
 
 
 @pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
