@@ -1,6 +1,8 @@
 #!/usr/bin/env python
 """Headline benchmark: training tokens/s of a Llama-3-8B-shape model, seq 4096, global batch
 32 sequences, bf16, FSDP over N B200s of one node (strong scaling: the global batch is fixed).
+``--config`` selects the other named configurations (assistant-only SFT under FSDP x TP, 32768-token
+MoBA rows, mixed AR + MaskGIT); without it the headline runs.
 
     python bench.py --gpus 1 --steps 3 --warmup 3
     python -m torch.distributed.run --nnodes=1 --nproc-per-node 8 --master-addr 127.0.0.1 \
@@ -27,7 +29,6 @@ from pathlib import Path
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-METRIC = "tokens/s Llama-3-8B-shape seq4096 FSDP bf16"
 
 
 def parse() -> argparse.Namespace:
@@ -39,16 +40,20 @@ def parse() -> argparse.Namespace:
                    help="ours: fused in-kernel collectives; nccl: same engine with NCCL-only collectives; "
                         "torch: stock PyTorch (cuBLAS, SDPA, autograd, FSDP2 over NCCL), none of our kernels; "
                         "reference: the unmodified reference trainer")
-    p.add_argument("--model", default="llama3-8b")
+    p.add_argument("--config", default="llama8b-pretrain",
+                   help="named benchmark configuration (causal_trainer_dev_b200/benchmarks/configs.py); the default is "
+                        "the headline: Llama-3-8B shape, seq 4096, 32 rows, FSDP")
+    p.add_argument("--attention", choices=("auto", "dense"), default="auto",
+                   help="dense: run a MoBA configuration with dense segment-masked attention instead (comparison)")
     p.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; invalid as a result)")
-    p.add_argument("--seq-len", type=int, default=4096)
-    p.add_argument("--global-batch", type=int, default=32)
-    p.add_argument("--micro-batch", type=int, default=4)
+    p.add_argument("--seq-len", type=int, default=0, help="override the configuration's sequence length")
+    p.add_argument("--global-batch", type=int, default=0, help="override the configuration's global batch (rows)")
+    p.add_argument("--micro-batch", type=int, default=0, help="override the configuration's micro-batch rows")
     p.add_argument("--remat", choices=("auto", "full", "none"), default="auto")
     p.add_argument("--force-sharded-runtime", action="store_true",
                    help="diagnostic: run the FSDP runtime on one GPU to measure its overhead without communication")
-    p.add_argument("--tp", type=int, default=1, help="tensor-parallel degree inside the N GPUs (the rest is FSDP); "
-                                                     "1 is the headline configuration")
+    p.add_argument("--tp", type=int, default=0, help="tensor-parallel degree inside the N GPUs (the rest is FSDP); "
+                                                     "0: what the configuration names, capped by N")
     return p.parse_args()
 
 
@@ -151,43 +156,57 @@ def main() -> None:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}: launch with torch.distributed.run")
 
     from causal_trainer_dev_b200.api import Trainer, TrainerConfig
-    from causal_trainer_dev_b200.data.synthetic import pretraining_rows
-    from causal_trainer_dev_b200.models.config import preset
+    from causal_trainer_dev_b200.benchmarks import configs as bench_configs
     from causal_trainer_dev_b200.training.optimizer import AdamWConfig, ScheduleConfig
 
+    if args.config not in bench_configs.CONFIGS:
+        raise SystemExit(f"unknown --config {args.config!r}; known: {sorted(bench_configs.CONFIGS)}")
+    bc = bench_configs.CONFIGS[args.config]
     overrides = {"num_hidden_layers": args.layers} if args.layers else {}
-    cfg = preset(args.model, **overrides)
-    if world % args.tp or args.global_batch % (world // args.tp):
+    cfg = bench_configs.model_of(bc, **overrides)
+    seq_len = args.seq_len or bc.seq_len
+    global_batch = args.global_batch or bc.global_batch
+    tp = args.tp or min(bc.tp, world)
+    if world % tp or global_batch % (world // tp):
         raise SystemExit("--tp must divide the GPUs, and the data ranks the global batch")
-    data_world = world // args.tp
-    data_rank = rank // args.tp
-    rows_per_rank = args.global_batch // data_world
-    micro = min(args.micro_batch, rows_per_rank)
+    data_world = world // tp
+    data_rank = rank // tp
+    rows_per_rank = global_batch // data_world
+    micro = min(args.micro_batch or bc.micro_batch, rows_per_rank)
+    attention_options = None
+    if bc.moba is not None and args.attention == "auto":
+        from causal_trainer_dev_b200.models.moba import AttentionOptions
+
+        attention_options = AttentionOptions(method="moba", moba_block_size=bc.moba[0], moba_top_k=bc.moba[1])
     tcfg = TrainerConfig(
         micro_batch_rows=micro,
         adamw=AdamWConfig(weight_decay=0.1, max_grad_norm=1.0),
         schedule=ScheduleConfig(learning_rate=2e-5, learning_rate_end=2e-6, scheduler="cosine", warmup_steps=2,
                                 total_steps=1000),
-        fused_collectives=(args.impl == "ours"), remat=args.remat, tp=args.tp,
-        force_sharded_runtime=args.force_sharded_runtime,
+        fused_collectives=(args.impl == "ours"), remat=args.remat, tp=tp,
+        force_sharded_runtime=args.force_sharded_runtime, attention_options=attention_options,
     )
     if args.impl == "torch":
         from causal_trainer_dev_b200.benchmarks.torch_baseline import TorchBaseline
 
+        if tp > 1 or bc.moba is not None or args.config == "qwen1.5b-maskgit-fsdp8":
+            print(json.dumps({"impl": "torch", "config": args.config, "unavailable": "the stock-PyTorch arm covers "
+                              "FSDP-only next-token configurations (no tensor parallelism, MoBA or MaskGIT masks)"}))
+            return
         trainer = TorchBaseline(cfg, micro)
     else:
         trainer = Trainer(cfg, tcfg)
 
     # Two distinct global batches, identical on every rank; each rank keeps its rows (pinned).
     pool = []
+    executed = []
     for seed in (11, 12):
-        data = pretraining_rows(args.global_batch, args.seq_len, cfg.vocab_size, eos_token_id=int(
-            cfg.eos_token_id if isinstance(cfg.eos_token_id, int) else cfg.eos_token_id[0]),
-            pad_token_id=cfg.pad_token_id, median_len=600.0, sigma=1.0, min_len=32, seed=seed)
+        data = bc.make_rows(cfg, global_batch, seq_len, seed)
+        executed.append(bench_configs.executed_flops_per_token(cfg, data, seq_len))
         mine = {k: torch.from_numpy(v[data_rank * rows_per_rank:(data_rank + 1) * rows_per_rank].copy()).pin_memory()
                 for k, v in data.items()}
         pool.append(mine)
-    tokens_per_step = args.global_batch * args.seq_len
+    tokens_per_step = global_batch * seq_len
 
     def sync() -> None:
         if world > 1:
@@ -248,15 +267,19 @@ def main() -> None:
         if peaks_file.exists():
             peaks = json.loads(peaks_file.read_text())
         peak = float(peaks.get("bf16_tflops_sustained", 1400.0)) * 1e12
-        flops_per_token = cfg.flops_per_token(args.seq_len)
+        flops_per_token = cfg.flops_per_token(seq_len)
+        executed_flops = sum(executed) / len(executed)
         result = {
-            "metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
+            "metric": bc.metric, "value": value, "unit": "tokens/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong",
-            "vs_baseline": None, "dtype": "bf16", "data": "synthetic (packed log-normal documents, uniform token ids, "
-            "random-init N(0,0.02) weights)", "impl": args.impl,
+            "vs_baseline": None, "dtype": "bf16", "data": f"synthetic ({bc.data}; random-init N(0,0.02) weights)",
+            "impl": args.impl,
             "config": {
-                "model": args.model + (f"-{args.layers}layers" if args.layers else ""), "global_batch": args.global_batch,
-                "seq_len": args.seq_len, "parallelism": f"fsdp{data_world}" + (f"xtp{args.tp}" if args.tp > 1 else ""),
+                "name": bc.name, "model": bc.model + (f"-{args.layers}layers" if args.layers else ""),
+                "global_batch": global_batch, "seq_len": seq_len,
+                "parallelism": f"fsdp{data_world}" + (f"xtp{tp}" if tp > 1 else ""),
+                "attention": ("MoBA block %d top_k %d (grouped)" % bc.moba if attention_options is not None
+                              else "dense, segment-isolated flash attention"),
                 "micro_batch_rows": micro,
                 "grad_accumulation": rows_per_rank // micro, "loss": "cut cross-entropy" if ours else "F.cross_entropy on 4096-row logit chunks",
                 "remat": (f"auto: activations of {trainer.engine.kept_layers}/{cfg.num_hidden_layers} layers kept in "
@@ -266,6 +289,10 @@ def main() -> None:
             },
             "mfu_of_measured_sustained": value * flops_per_token / (world * peak),
             "model_flops_per_token": flops_per_token,
+            # the same with the attention FLOPs the segment-isolated rows actually need (documents
+            # are shorter than rows; the nominal figure charges full-row causal attention)
+            "mfu_executed_flops_of_measured_sustained": value * executed_flops / (world * peak),
+            "executed_flops_per_token": executed_flops,
             "loss_last_step": loss,
             "clocks": clocks,
             "e2e": {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": (h2d1 - h2d0) // args.steps,

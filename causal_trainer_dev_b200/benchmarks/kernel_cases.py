@@ -1,7 +1,7 @@
 """Small, self-terminating single-kernel workloads for profiling and roofline numbers.
 
     python -m causal_trainer_dev_b200.benchmarks.kernel_cases \
-        gemm|dgrad|wgrad|layer_gemms|attn_fwd|attn_bwd|moba [one-document|coherent]|cut_ce|rmsnorm|adamw|adamw_arena
+        gemm|dgrad|wgrad|layer_gemms|attn_fwd|attn_bwd|moba [one-document|one-document-128k|coherent]|cut_ce|rmsnorm|adamw|adamw_arena
 
 Each case holds a few hundred MB (more than the 126 MB L2, far less than a GB-scale step),
 launches its kernel a handful of times, and prints device-timed milliseconds plus the achieved
@@ -102,11 +102,13 @@ def main() -> None:
         from causal_trainer_dev_b200.ops import moba as M
 
         b, s, hq, hkv, d, block, top_k = 1, 32768, 32, 8, 128, 4096, 4
+        if len(sys.argv) > 2 and sys.argv[2] == "one-document-128k":
+            s, hq, hkv = 131072, 8, 2          # a quarter of the heads keeps the case within a few GB
         g = torch.Generator().manual_seed(3)
         lens = torch.randint(4096, 12289, (4,), generator=g).tolist()
         lens[-1] = max(1, s - sum(lens[:-1])) if sum(lens[:-1]) < s else 0
-        if len(sys.argv) > 2 and sys.argv[2] == "one-document":
-            lens = [s]               # a single 32768-token document: 8 blocks, 4 of them visible per query
+        if len(sys.argv) > 2 and sys.argv[2].startswith("one-document"):
+            lens = [s]               # a single document: 8 (32 at 128k) blocks, 4 of them visible per query
         seg = torch.zeros(b, s, dtype=torch.int32)
         pos = 0
         for i, n in enumerate(lens):
@@ -134,18 +136,34 @@ def main() -> None:
                 qf[0, torch.arange(s, device=dev), :, want] += 6.0
             q = qf.bfloat16()
         meta = A.build_attention_meta(seg)
-        routing = M.build_routing(q, k, meta, block, top_k)
-        o, lse = M.moba_forward(q, k, v, meta, routing)
-        do = torch.randn_like(o)
+        groups = M.build_groups(q, k, meta, block, top_k)
+        og, lseg = M.moba_grouped_forward(q, k, v, meta, groups)
+        do = torch.randn_like(og)
         od, lsed = A.flash_attention_forward(q, k, v, meta)
+        work = groups.work_summary()
+        nt = s // 128
         out.update(
-            document_lengths=lens, visited_tile_fraction=routing.visited_fraction,
-            routing_ms=timed(lambda: M.build_routing(q, k, meta, block, top_k)),
-            moba_fwd_ms=timed(lambda: M.moba_forward(q, k, v, meta, routing)),
+            shape=dict(tokens=s, q_heads=hq, kv_heads=hkv, head_dim=d, block=block, top_k=top_k),
+            document_lengths=lens, grouped_work=work,
+            # 128 x 128 score tiles: grouped history + own-block causal pass, against dense causal attention
+            grouped_tiles=work["history_tiles"] + hq * nt * (block // 128 + 1) // 2,
+            dense_causal_tiles=hq * nt * (nt + 1) // 2,
+            grouping_ms=timed(lambda: M.build_groups(q, k, meta, block, top_k)),
+            grouped_fwd_ms=timed(lambda: M.moba_grouped_forward(q, k, v, meta, groups)),
             dense_fwd_ms=timed(lambda: A.flash_attention_forward(q, k, v, meta)),
-            moba_bwd_ms=timed(lambda: M.moba_backward(q, k, v, o, do, lse, meta, routing)),
+            grouped_bwd_ms=timed(lambda: M.moba_grouped_backward(q, k, v, og, do, lseg, meta, groups)),
             dense_bwd_ms=timed(lambda: A.flash_attention_backward(q, k, v, od, do, lsed, meta)),
         )
+        if s <= 32768:
+            # the list-driven variant: one masked flash pass over the union of a tile's selections
+            routing = M.build_routing(q, k, meta, block, top_k)
+            o, lse = M.moba_forward(q, k, v, meta, routing)
+            out.update(
+                lists_visited_tile_fraction=routing.visited_fraction,
+                lists_routing_ms=timed(lambda: M.build_routing(q, k, meta, block, top_k)),
+                lists_fwd_ms=timed(lambda: M.moba_forward(q, k, v, meta, routing)),
+                lists_bwd_ms=timed(lambda: M.moba_backward(q, k, v, o, do, lse, meta, routing)),
+            )
     elif case == "cut_ce":
         rows, d, vocab = 4096, 4096, 128256
         h = torch.randn(rows, d, device=dev).bfloat16()

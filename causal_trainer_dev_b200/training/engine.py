@@ -77,6 +77,12 @@ class EngineOptions:
     compact_loss_rows: bool = True           # run the LM head only on rows with non-zero loss weight
     loss_backend: str = "cut"                # "cut": projection-fused; "logits": materialised bf16 logits slab per chunk
     memory_reserve_bytes: int = 8 << 30
+    remat_group_size: int = 1                # recomputed layers keep their input only at every G-th layer; the
+                                             # others' inputs are rebuilt group by group in the backward pass
+    mlp_chunk_rows: int = 0                  # > 0: the MLP runs in tiles of this many token rows and its [T, 2F]
+                                             # intermediate is never held whole (rebuilt per tile in backward)
+    moba_implementation: str = "grouped"     # "grouped": rows gathered by selected block, cost ~ top_k * block;
+                                             # "lists": one masked flash pass over the union of a tile's selections
 
 
 class LayerwiseEngine:
@@ -179,7 +185,13 @@ class LayerwiseEngine:
         from ..ops import moba as moba_ops
 
         ao = self.options.attention_options
-        routing = moba_ops.build_routing(q, k, ctx["meta"], min(ao.moba_block_size, ctx["seq"]), ao.moba_top_k)
+        block = min(ao.moba_block_size, ctx["seq"])
+        if self.options.moba_implementation == "grouped" and block % 128 == 0 and ao.moba_top_k >= 2:
+            routing = moba_ops.build_groups(q, k, ctx["meta"], block, ao.moba_top_k)
+            o, lse = moba_ops.moba_grouped_forward(q, k, v, ctx["meta"], routing)
+            self._count(11)
+            return o, lse, routing
+        routing = moba_ops.build_routing(q, k, ctx["meta"], block, ao.moba_top_k)
         o, lse = moba_ops.moba_forward(q, k, v, ctx["meta"], routing)
         self._count(40)
         return o, lse, routing
@@ -190,7 +202,10 @@ class LayerwiseEngine:
         else:
             from ..ops import moba as moba_ops
 
-            moba_ops.moba_backward(q, k, v, o, do, lse, ctx["meta"], routing, dq=dq, dk=dk, dv=dv)
+            if isinstance(routing, moba_ops.MobaGroups):
+                moba_ops.moba_grouped_backward(q, k, v, o, do, lse, ctx["meta"], routing, dq=dq, dk=dk, dv=dv)
+            else:
+                moba_ops.moba_backward(q, k, v, o, do, lse, ctx["meta"], routing, dq=dq, dk=dk, dv=dv)
 
     def _embed(self, local_ids: torch.Tensor, first_layer: str) -> torch.Tensor:
         """Token embeddings of this rank's tokens.  A sharded provider fetches just the rows it
@@ -226,9 +241,19 @@ class LayerwiseEngine:
         o, lse, routing = self._attention_forward(q, k, v, ctx, li)
         attn_out = self._project(li, "o", o.view(t, qw), w)
         n2, rstd2, h = ew.rmsnorm_forward(x, w["ln2"], cfg.rms_norm_eps, residual=attn_out)
-        gu = self._project(li, "gu", n2, w)
-        act = ew.swiglu_forward(gu)
-        mlp = self._project(li, "down", act, w)
+        chunk = self.options.mlp_chunk_rows
+        if chunk > 0 and t > chunk:
+            # tiled MLP (src/causal_trainer/modeling/architecture.py:509-534): bounded [chunk, 2F] intermediates
+            gu = act = None
+            mlp = torch.empty((t, cfg.hidden_size), dtype=n2.dtype, device=n2.device)
+            for r0 in range(0, t, chunk):
+                gu_c = self._project(li, "gu", n2[r0:r0 + chunk], w)
+                gemm(ew.swiglu_forward(gu_c), w["down_w"], bias=w.get("down_b"), out=mlp[r0:r0 + chunk])
+                self._count(2)
+        else:
+            gu = self._project(li, "gu", n2, w)
+            act = ew.swiglu_forward(gu)
+            mlp = self._project(li, "down", act, w)
         self._count(6)
         saved = None
         if save == "all":      # transient: consumed by the backward pass that follows at once
@@ -249,16 +274,29 @@ class LayerwiseEngine:
         if "act" not in sv:
             # kept activations: the memory-bound intermediates are cheaper to rebuild than to hold
             sv = dict(sv)
-            sv["act"] = ew.swiglu_forward(sv["gu"])
+            sv["act"] = ew.swiglu_forward(sv["gu"]) if sv["gu"] is not None else None
             sv["n2"] = ew.rmsnorm_forward(sv["h"], w["ln2"], cfg.rms_norm_eps)[0]
             sv["n1"] = ew.rmsnorm_forward(sv["x"], w["ln1"], cfg.rms_norm_eps)[0]
             self._count(3)
         # MLP branch
-        dact = self._project_backward(li, "down", dout, sv["act"], w, g, accumulate)
-        dgu = ew.swiglu_backward(sv["gu"], dact)
-        del dact
-        dn2 = self._project_backward(li, "gu", dgu, sv["n2"], w, g, accumulate)
-        del dgu
+        if sv["gu"] is None:
+            # tiled MLP: every tile rebuilds its gate/up product, then runs the usual backward on it
+            chunk = self.options.mlp_chunk_rows
+            dn2 = torch.empty_like(sv["n2"])
+            for r0 in range(0, t, chunk):
+                rows = slice(r0, r0 + chunk)
+                later = accumulate or r0 > 0
+                gu_c = self._project(li, "gu", sv["n2"][rows], w)
+                dact = self._project_backward(li, "down", dout[rows], ew.swiglu_forward(gu_c), w, g, later)
+                dgu = ew.swiglu_backward(gu_c, dact)
+                dn2[rows] = self._project_backward(li, "gu", dgu, sv["n2"][rows], w, g, later)
+                del gu_c, dact, dgu
+        else:
+            dact = self._project_backward(li, "down", dout, sv["act"], w, g, accumulate)
+            dgu = ew.swiglu_backward(sv["gu"], dact)
+            del dact
+            dn2 = self._project_backward(li, "gu", dgu, sv["n2"], w, g, accumulate)
+            del dgu
         dh, _ = ew.rmsnorm_backward(dn2, sv["h"], w["ln2"], sv["rstd2"], dres=dout, dw_out=self._norm_grad(g, "ln2"),
                                     dw_accumulate=accumulate)
         del dn2
@@ -355,11 +393,13 @@ class LayerwiseEngine:
         kept: list[dict | None] = []
         keep_layers = self._layers_to_keep(resid.shape[0])
         self.kept_layers = keep_layers
+        group = max(1, self.options.remat_group_size)
         for li in range(nl):
             unit = prov.acquire(f"layer.{li}", prefetch=f"layer.{li + 1}" if li + 1 < nl else "final")
             # the last layers are kept first: their activations are consumed soonest
             keep = li >= nl - keep_layers
-            inputs.append(None if keep else (resid, branch))
+            # a recomputed layer keeps its input; with remat groups only the first layer of a group does
+            inputs.append((resid, branch) if (not keep and li % group == 0) else None)
             resid, branch, sv = self._layer_forward(self._views(unit), resid, branch, ctx, li,
                                                     save="keep" if keep else None)
             kept.append(sv)
@@ -416,12 +456,22 @@ class LayerwiseEngine:
         self._mark("head forward+backward")
         # ---------------- backward: recompute + hand-written layer backward ----------------
         for li in reversed(range(nl)):
+            saved = kept.pop()
+            if saved is None and inputs[li] is None:
+                # remat group (src/causal_trainer/modeling/architecture.py:777-786): rebuild the inputs of
+                # the group's later layers from the one input the forward pass kept
+                first = li - li % group
+                x = inputs[first]
+                for j in range(first, li):
+                    uj = prov.acquire(f"layer.{j}")
+                    r, br, _ = self._layer_forward(self._views(uj), x[0], x[1], ctx, j, save=None)
+                    prov.release(f"layer.{j}")
+                    x = inputs[j + 1] = (r, br)
             # the embedding table is not read in the backward pass: nothing to prefetch for layer 0
             unit = prov.acquire(f"layer.{li}", prefetch=f"layer.{li - 1}" if li > 0 else None)
             w = self._views(unit)
             g = self._views(unit, prov.grad_buffer(f"layer.{li}")) if self.train_base else dict.fromkeys(w)
             layer_in = inputs.pop()
-            saved = kept.pop()
             if saved is None:
                 _, _, saved = self._layer_forward(w, layer_in[0], layer_in[1], ctx, li, save="all")
             dout = self._layer_backward(w, g, saved, dout, ctx, accumulate, li)

@@ -368,6 +368,30 @@ class TrainingRun:
                                             total_steps=self.plan.total_steps)
         self.start_step = self.checkpoint.global_step if self.checkpoint is not None else 0
 
+    def engine_options(self, frozen: tuple[str, ...] = ()):
+        """How the command line maps onto the CUDA engine, on every branch that builds one.  Flags
+        that describe the reference's XLA program and have no counterpart here are named in the log
+        instead of being dropped silently."""
+        from .engine import EngineOptions
+
+        a = self.args
+        remat = {"auto": "auto", "recompute": "full", "keep": "none"}[a.activation_memory]
+        if a.gradient_checkpointing == "disabled":
+            remat = "none"
+        if a.scan_layers:
+            log.info("scan_layers: the engine always runs one set of kernels per layer in a host loop; nothing to select")
+        if a.projection_chunk_size:
+            log.warning("projection_chunk_size=%d: projections are not tiled separately here; token rows are sharded "
+                        "over tp and the MLP is tiled by mlp_chunk_size", a.projection_chunk_size)
+        if a.attn_mechanism == "splash" or a.block_size_q != a.block_size_k:
+            log.info("block_size_q / block_size_k: the tcgen05 attention kernels use fixed 128-row query tiles and "
+                     "128-key tiles; the flags are validated and recorded in the resume signature only")
+        return EngineOptions(
+            cut_chunk_rows=a.cut_chunk_size or 4096, attention_options=a.attention_options, remat=remat,
+            remat_group_size=a.remat_group_size, mlp_chunk_rows=a.mlp_chunk_size,
+            train_lm_head="lm_head" not in frozen, train_embed="embed" not in frozen, train_norm="norm" not in frozen,
+            loss_backend="logits" if a.loss_implementation == "pallas" else "cut")
+
     # ---- stage 6: parameters, optimizer ----
     @_guarded("load parameters")
     def build_model(self) -> None:
@@ -390,14 +414,18 @@ class TrainingRun:
             tcfg = TrainerConfig(micro_batch_rows=a.micro_batch_rows or a.total_batch_size // data_ranks, adamw=adamw,
                                  schedule=schedule, seed=a.seed, fused_collectives=a.fused_collectives,
                                  cut_chunk_rows=a.cut_chunk_size or 4096, tp=tp)
-            options = EngineOptions(cut_chunk_rows=tcfg.cut_chunk_rows, attention_options=a.attention_options)
+            frozen = a.frozen_parameter_components
+            options = self.engine_options(frozen)
+            if tp > 1 and (frozen or options.loss_backend != "cut"):
+                raise ValueError("tensor parallelism runs the vocabulary-parallel cut cross-entropy with every "
+                                 "component trainable: --frozen_parameters and --loss_implementation pallas need tp = 1")
             # parameters, gradients and optimizer state are sharded over dp x fsdp (a dp replica
             # would only cost memory); tensor-parallel ranks hold slices of every projection
             data_group = self.lattice.group(("dp", "fsdp", "sp") if sp > 1 else ("dp", "fsdp"))
             if sp > 1:
                 from .sp_engine import SpLayerwiseEngine
 
-                self.runtime = FsdpRuntime(self.cfg, tcfg, self.device, group=data_group)
+                self.runtime = FsdpRuntime(self.cfg, tcfg, self.device, group=data_group, frozen=frozen)
                 engine = SpLayerwiseEngine(self.cfg, self.lattice.group(("sp",)), self.runtime, options)
             elif tp > 1:
                 from ..parallel.tp import tp_local_config
@@ -408,7 +436,7 @@ class TrainingRun:
                                            full_cfg=self.cfg, tp_group=tp_group)
                 engine = TpLayerwiseEngine(self.cfg, tp_group, self.runtime, options, fused=a.fused_collectives)
             else:
-                self.runtime = FsdpRuntime(self.cfg, tcfg, self.device, group=data_group)
+                self.runtime = FsdpRuntime(self.cfg, tcfg, self.device, group=data_group, frozen=frozen)
                 engine = LayerwiseEngine(self.cfg, self.runtime, options)
             if weights_from is not None:
                 hfio.load_sharded_parameters(weights_from, self.runtime)
@@ -429,10 +457,7 @@ class TrainingRun:
                 from .engine import EngineOptions, LayerwiseEngine, LocalProvider
 
                 grad_dtype = torch.float32 if a.gradient_accumulation_steps > 1 else torch.bfloat16
-                producer = LayerwiseEngine(self.cfg, LocalProvider(self.params, grad_dtype), EngineOptions(
-                    cut_chunk_rows=a.cut_chunk_size or 4096, train_lm_head="lm_head" not in frozen,
-                    train_embed="embed" not in frozen, attention_options=a.attention_options,
-                    loss_backend="logits" if a.loss_implementation == "pallas" else "cut"))
+                producer = LayerwiseEngine(self.cfg, LocalProvider(self.params, grad_dtype), self.engine_options(frozen))
                 self.step_fn = TrainStep(self.params, producer, adamw, schedule, frozen=frozen)
             else:
                 opts = ForwardOptions(
@@ -451,9 +476,8 @@ class TrainingRun:
                     from .engine import EngineOptions, LocalProvider
                     from .lora_engine import LoraLayerwiseEngine
 
-                    producer = LoraLayerwiseEngine(self.cfg, LocalProvider(self.params, torch.bfloat16), self.lora, EngineOptions(
-                        cut_chunk_rows=a.cut_chunk_size or 4096, attention_options=a.attention_options,
-                        loss_backend="logits" if a.loss_implementation == "pallas" else "cut"))
+                    producer = LoraLayerwiseEngine(self.cfg, LocalProvider(self.params, torch.bfloat16), self.lora,
+                                                   self.engine_options())
                     extra = producer.extra_regions()
                 else:
                     if a.lora:

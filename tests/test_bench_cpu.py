@@ -53,3 +53,32 @@ def test_clock_sampler_without_nvidia_smi_reports_nothing(tmp_path, monkeypatch)
     sampler = _bench().ClockSampler(0)
     sampler.start()
     assert sampler.stop() == {"sm_mhz": None, "sm_max_mhz": None, "reasons": []}
+
+
+def test_named_configurations_generate_rows_of_the_named_shape():
+    import numpy as np
+
+    from causal_trainer_dev_b200.benchmarks import configs
+
+    assert set(configs.CONFIGS) == {"llama8b-pretrain", "qwen7b-sft-fsdp4tp2", "llama8b-moba32k-fsdp2tp4",
+                                    "qwen1.5b-maskgit-fsdp8"}
+    for name, rows, seq in (("llama8b-pretrain", 2, 1024), ("qwen7b-sft-fsdp4tp2", 2, 1024),
+                            ("llama8b-moba32k-fsdp2tp4", 1, 4096), ("qwen1.5b-maskgit-fsdp8", 2, 4096)):
+        bc = configs.CONFIGS[name]
+        cfg = configs.model_of(bc)
+        data = bc.make_rows(cfg, rows, seq, 3)
+        assert data["input_ids"].shape == (rows, seq) and int(data["input_ids"].max()) < cfg.vocab_size
+        executed = configs.executed_flops_per_token(cfg, data, seq)
+        assert 0 < executed <= cfg.flops_per_token(seq) * 1.001      # segment isolation never adds work
+        if name == "qwen7b-sft-fsdp4tp2":
+            assert 0 < data["loss_weights"].mean() < 0.8              # assistant spans only
+        if name == "llama8b-moba32k-fsdp2tp4":
+            assert sorted(set(data["segment_ids"][0].tolist())) == [1, 2, 3, 4]
+        if name == "qwen1.5b-maskgit-fsdp8":
+            mask_id = 151936 + 16384
+            masked = data["input_ids"] == mask_id
+            assert masked.any() and (data["prediction_weights"][masked] == 1).all()
+            assert (data["attention_end"] >= np.arange(seq)[None, :]).all()
+            grid = data["attention_end"] > np.arange(seq)[None, :]
+            # no next-token target inside a bidirectional grid: only the masked codes carry weight there
+            assert (data["prediction_weights"][grid & ~masked] == 0).all()

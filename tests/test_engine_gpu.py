@@ -188,3 +188,38 @@ def test_lora_engine_matches_oracle_adapter_gradients(cuda_lib):
     assert last["loss"] < first["loss"] - 0.05
     assert all(torch.equal(v, before[k]) for k, v in params.state_dict().items())
     assert cuda_lib.device_status() == (0, 0, 0, 0)
+
+
+@pytest.mark.parametrize("remat,group,chunk", [("full", 2, 0), ("full", 3, 0), ("full", 3, 128), ("none", 1, 128),
+                                               ("none", 1, 0)])
+def test_memory_options_do_not_change_the_gradients(cuda_lib, remat, group, chunk):
+    """Recompute in groups of layers, tile the MLP, keep everything: the same gradients as
+    recomputing layer by layer.  Grouping only changes when a layer's input is rebuilt, so it is
+    bit-exact; the tiled MLP sums its weight gradients tile by tile and kept activations are
+    re-normalised from their rounded copies, so those agree to rounding."""
+    from causal_trainer_dev_b200.models.config import preset
+    from causal_trainer_dev_b200.models.params import ModelParams
+    from causal_trainer_dev_b200.training.engine import EngineOptions, LayerwiseEngine, LocalProvider
+
+    cfg = preset("tiny", vocab_size=4096, num_hidden_layers=5)
+    base = ModelParams.init_random(cfg, seed=2, dtype=torch.bfloat16)
+    batch = _batch(cfg, 2, 256)
+
+    def run(options):
+        params = ModelParams(cfg, dtype=torch.bfloat16, device="cuda")
+        params.load_state_dict(base.state_dict())
+        engine = LayerwiseEngine(cfg, LocalProvider(params, torch.float32), options)
+        nll, _ = engine(batch, 1.0 / 400, True)
+        return nll, params, engine
+
+    nll_0, p_0, _ = run(EngineOptions(remat="full"))
+    nll_1, p_1, engine = run(EngineOptions(remat=remat, remat_group_size=group, mlp_chunk_rows=chunk))
+    assert engine.kept_layers == (0 if remat == "full" else cfg.num_hidden_layers)
+    exact = remat == "full" and chunk == 0
+    assert torch.equal(nll_0, nll_1) if exact else abs(nll_0.item() - nll_1.item()) < 1e-3 * abs(nll_0.item())
+    for name in p_0.hf_names():
+        a, b = p_0.grad_tensor(name), p_1.grad_tensor(name)
+        if exact:
+            assert torch.equal(a, b), name
+        else:
+            assert _rel(b, a) < 2e-2, name
