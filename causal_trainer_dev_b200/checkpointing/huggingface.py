@@ -420,57 +420,120 @@ def layout_fingerprint(entries: list[dict[str, Any]]) -> str:
     return hashlib.sha256(json.dumps(entries, separators=(",", ":"), sort_keys=True).encode("utf-8")).hexdigest()
 
 
+def export_optimizer_stream(destination: str | os.PathLike[str], layout: list[tuple[str, torch.dtype, tuple[int, ...]]],
+                            pieces, *, global_step: int, checkpoint_id: str) -> None:
+    """Collective.  Writes ``optimizer/state.safetensors`` + ``optimizer/manifest.json`` from a stream.
+
+    ``layout`` names every tensor up front (``path``, dtype, shape; identical on all ranks) so the
+    header can be written first.  ``pieces`` yields, in the same order, ``(path, chunks)`` where
+    ``chunks`` iterates over consecutive flat pieces of the tensor.  Every rank drains both
+    iterators, because producing a piece may be a collective (a shard sent to rank 0); only rank 0
+    holds the piece and writes it, one piece at a time, so neither the device nor the host of any
+    rank ever holds more than one shard of one tensor
+    (src/causal_trainer/checkpointing/huggingface.py:787-988)."""
+    out = Path(destination) / "optimizer"
+    writer = None
+    error: BaseException | None = None
+    names = [f"state/{i:06d}" for i in range(len(layout))]
+    if rt.process_index() == 0:
+        try:
+            out.mkdir(parents=True, exist_ok=True)
+            writer = st.StreamingWriter(out / "state.safetensors",
+                                        [(n, st.DTYPE_NAMES[dt], tuple(shape)) for n, (_, dt, shape) in zip(names, layout)],
+                                        {"format": "pt", "checkpoint_id": checkpoint_id})
+        except BaseException as exc:  # noqa: BLE001 - reported to every rank below
+            error = exc
+    for name, (path, _, _), (got, chunks) in zip(names, layout, pieces):
+        if got != path:
+            raise ValueError(f"optimizer state arrives out of order: expected {path!r}, got {got!r}")
+        if writer is not None and error is None:
+            try:
+                writer.write_chunks(name, chunks)
+                continue
+            except BaseException as exc:  # noqa: BLE001
+                error = exc
+        for _ in chunks:               # still take part in the collectives behind the remaining pieces
+            pass
+    if rt.process_index() == 0 and error is None:
+        try:
+            writer.close()
+            entries = [{"dtype": st.PLAIN_DTYPE_NAMES[st.DTYPE_NAMES[dt]], "file": "state.safetensors", "key": n,
+                        "ordinal": i, "path": path, "shape": list(shape)}
+                       for i, (n, (path, dt, shape)) in enumerate(zip(names, layout))]
+            total = sum(int(torch.tensor([], dtype=dt).element_size()) * int(torch.Size(shape).numel())
+                        for _, dt, shape in layout)
+            manifest = {
+                "format": "optimizer-state-safetensors", "format_version": 1, "global_step": int(global_step),
+                "jax_version": f"torch-{torch.__version__}", "optax_version": "causal-trainer-b200-adamw-1",
+                "layout_fingerprint": layout_fingerprint(entries), "tensor_count": len(entries), "tensors": entries,
+                "total_size": int(total), "checkpoint_id": checkpoint_id,
+            }
+            tmp = out / "manifest.json.tmp"
+            tmp.write_text(json.dumps(manifest, indent=2, sort_keys=True) + "\n", encoding="utf-8")
+            os.replace(tmp, out / "manifest.json")
+        except BaseException as exc:  # noqa: BLE001
+            error = exc
+    elif writer is not None:
+        writer.abort()
+    rt.raise_if_process_zero_error(error, "write optimizer state")
+
+
 def export_optimizer_checkpoint(destination: str | os.PathLike[str], state: list[tuple[str, torch.Tensor]], *,
                                 global_step: int, checkpoint_id: str) -> None:
-    """Writes ``optimizer/state.safetensors`` + ``optimizer/manifest.json`` (rank 0; state already whole).
+    """Same files from state that is already whole on this process: an ordered list of
+    ``(path, tensor)``, ``count`` first, then ``mu/...`` and ``nu/...`` buffers."""
+    layout = [(path, t.dtype, tuple(t.shape)) for path, t in state]
+    export_optimizer_stream(destination, layout, ((path, iter([t.reshape(-1)])) for path, t in state),
+                            global_step=global_step, checkpoint_id=checkpoint_id)
 
-    ``state`` is an ordered list of ``(path, tensor)``: ``count`` first, then ``mu/<unit>`` and
-    ``nu/<unit>`` flat buffers.
-    """
-    if rt.process_index() != 0:
-        return
-    out = Path(destination) / "optimizer"
-    out.mkdir(parents=True, exist_ok=True)
-    tensors = {f"state/{i:06d}": t.detach().cpu() for i, (_, t) in enumerate(state)}
-    st.save_file(tensors, out / "state.safetensors", {"format": "pt", "checkpoint_id": checkpoint_id})
-    entries = [{"dtype": st.PLAIN_DTYPE_NAMES[st.DTYPE_NAMES[t.dtype]], "file": "state.safetensors",
-                "key": f"state/{i:06d}", "ordinal": i,
-                "path": path, "shape": list(t.shape)} for i, (path, t) in enumerate(state)]
-    manifest = {
-        "format": "optimizer-state-safetensors", "format_version": 1, "global_step": int(global_step),
-        "jax_version": f"torch-{torch.__version__}", "optax_version": "causal-trainer-b200-adamw-1",
-        "layout_fingerprint": layout_fingerprint(entries), "tensor_count": len(entries), "tensors": entries,
-        "total_size": int(sum(t.numel() * t.element_size() for t in tensors.values())), "checkpoint_id": checkpoint_id,
-    }
-    tmp = out / "manifest.json.tmp"
-    tmp.write_text(json.dumps(manifest, indent=2, sort_keys=True) + "\n", encoding="utf-8")
-    os.replace(tmp, out / "manifest.json")
+
+class OptimizerCheckpoint:
+    """Validated read access to a saved optimizer state: whole tensors or flat ranges of them (a rank
+    of a sharded run pages in only the bytes of its own shards)."""
+
+    def __init__(self, source: str | os.PathLike[str], expected_paths: list[str], *, global_step: int):
+        d = Path(source) / "optimizer"
+        manifest = json.loads((d / "manifest.json").read_text(encoding="utf-8"))
+        if manifest.get("format") != "optimizer-state-safetensors" or manifest.get("format_version") != 1:
+            raise ValueError("unsupported optimizer checkpoint format")
+        if manifest.get("optax_version") != "causal-trainer-b200-adamw-1":
+            raise ValueError("optimizer state was written by a different optimizer implementation")
+        if manifest.get("global_step") != global_step:
+            raise ValueError(f"optimizer state is for step {manifest.get('global_step')}, expected {global_step}")
+        if [e["path"] for e in manifest["tensors"]] != expected_paths:
+            raise ValueError("optimizer state layout does not match this run")
+        if manifest.get("layout_fingerprint") != layout_fingerprint(manifest["tensors"]):
+            raise ValueError("optimizer manifest fingerprint mismatch")
+        self.file = st.SafeTensorsFile(d / "state.safetensors")
+        if self.file.metadata.get("checkpoint_id") != manifest.get("checkpoint_id"):
+            self.file.close()
+            raise ValueError("optimizer state belongs to a different checkpoint")
+        self.keys = {e["path"]: e["key"] for e in manifest["tensors"]}
+        if "count" in self.keys and int(self.file.tensor(self.keys["count"])) != global_step:
+            self.file.close()
+            raise ValueError("optimizer step counter does not match the checkpoint step")
+
+    def tensor(self, path: str) -> torch.Tensor:
+        return self.file.tensor(self.keys[path]).clone()
+
+    def flat_range(self, path: str, start: int, stop: int) -> torch.Tensor:
+        return self.file.flat_range(self.keys[path], start, stop).clone()
+
+    def close(self) -> None:
+        self.file.close()
+
+    def __enter__(self) -> "OptimizerCheckpoint":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.close()
 
 
 def load_optimizer_checkpoint(source: str | os.PathLike[str], expected_paths: list[str], *, global_step: int
                               ) -> dict[str, torch.Tensor]:
-    """Reads optimizer state back; refuses a foreign framework version, layout or step."""
-    d = Path(source) / "optimizer"
-    manifest = json.loads((d / "manifest.json").read_text(encoding="utf-8"))
-    if manifest.get("format") != "optimizer-state-safetensors" or manifest.get("format_version") != 1:
-        raise ValueError("unsupported optimizer checkpoint format")
-    if manifest.get("optax_version") != "causal-trainer-b200-adamw-1":
-        raise ValueError("optimizer state was written by a different optimizer implementation")
-    if manifest.get("global_step") != global_step:
-        raise ValueError(f"optimizer state is for step {manifest.get('global_step')}, expected {global_step}")
-    paths = [e["path"] for e in manifest["tensors"]]
-    if paths != expected_paths:
-        raise ValueError("optimizer state layout does not match this run")
-    if manifest.get("layout_fingerprint") != layout_fingerprint(manifest["tensors"]):
-        raise ValueError("optimizer manifest fingerprint mismatch")
-    with st.SafeTensorsFile(d / "state.safetensors") as f:
-        if f.metadata.get("checkpoint_id") != manifest.get("checkpoint_id"):
-            raise ValueError("optimizer state belongs to a different checkpoint")
-        out = {e["path"]: f.tensor(e["key"]).clone() for e in manifest["tensors"]}
-    count = out.get("count")
-    if count is not None and int(count) != global_step:
-        raise ValueError("optimizer step counter does not match the checkpoint step")
-    return out
+    """Reads a whole optimizer state back; refuses a foreign framework version, layout or step."""
+    with OptimizerCheckpoint(source, expected_paths, global_step=global_step) as ckpt:
+        return {path: ckpt.tensor(path) for path in expected_paths}
 
 
 def remove_optimizer_checkpoint(destination: str | os.PathLike[str]) -> None:

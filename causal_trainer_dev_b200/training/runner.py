@@ -492,50 +492,103 @@ class TrainingRun:
             self.load_optimizer_state(self.checkpoint.path, self.checkpoint.global_step)
 
     # ---- optimizer state <-> checkpoint ----
-    def optimizer_state(self) -> list[tuple[str, torch.Tensor]]:
-        if self.runtime is not None:
-            r = self.runtime
-            out = [("count", torch.tensor(r.count, dtype=torch.int64))]
-            for kind, arena in (("mu", r.m), ("nu", r.v)):
-                for name, u in r.units.items():
-                    full = torch.empty(u.padded, dtype=torch.bfloat16, device=self.device)
-                    torch.distributed.all_gather_into_tensor(full, r.shard_view(name, of=arena).contiguous(), group=r.group)
-                    if r.tp_world == 1:
-                        out.append((f"{kind}/{name}", full[:u.layout.numel].cpu()))
-                        continue
-                    # one entry per tensor-parallel slice, in tp rank order
-                    slices = [torch.empty_like(full) for _ in range(r.tp_world)]
-                    torch.distributed.all_gather(slices, full, group=r.tp_group)
-                    for t, piece in enumerate(slices):
-                        out.append((f"{kind}/{name}/tp{t}", piece[:u.layout.numel].cpu()))
-            return out
-        opt = self.step_fn.optimizer
-        out = [("count", torch.tensor(opt.count, dtype=torch.int64))]
-        for i, (m, v) in enumerate(zip(opt.m, opt.v)):
-            out.append((f"mu/{i:05d}", m.detach().cpu()))
-            out.append((f"nu/{i:05d}", v.detach().cpu()))
+    def _state_entries(self) -> list[tuple[str, str, str, int]]:
+        """``(path, kind, unit, tp slice)`` of every moment buffer of the sharded runtime, in file order."""
+        r = self.runtime
+        out = []
+        for kind in ("mu", "nu"):
+            for name in r.units:
+                if r.tp_world == 1:
+                    out.append((f"{kind}/{name}", kind, name, 0))
+                else:       # one entry per tensor-parallel slice, in tp rank order
+                    out += [(f"{kind}/{name}/tp{t}", kind, name, t) for t in range(r.tp_world)]
         return out
 
-    def load_optimizer_state(self, path: Path, step: int) -> None:
-        names = [n for n, _ in self.optimizer_state()]
-        state = hfio.load_optimizer_checkpoint(path, names, global_step=step)
+    def optimizer_state_layout(self) -> list[tuple[str, torch.dtype, tuple[int, ...]]]:
         if self.runtime is not None:
             r = self.runtime
-            r.count = int(state["count"])
-            for kind, arena in (("mu", r.m), ("nu", r.v)):
-                for name, u in r.units.items():
-                    full = state[f"{kind}/{name}" if r.tp_world == 1 else f"{kind}/{name}/tp{r.tp_rank}"]
-                    lo = r.rank * u.shard_elems
-                    piece = full[lo:min(lo + u.shard_elems, full.numel())]
-                    view = r.shard_view(name, of=arena)
-                    view.zero_()
-                    view[:piece.numel()].copy_(piece)
-            return
+            return [("count", torch.int64, ())] + [(path, torch.bfloat16, (r.units[name].layout.numel,))
+                                                    for path, _, name, _ in self._state_entries()]
         opt = self.step_fn.optimizer
-        opt.count = int(state["count"])
+        out: list[tuple[str, torch.dtype, tuple[int, ...]]] = [("count", torch.int64, ())]
         for i, (m, v) in enumerate(zip(opt.m, opt.v)):
-            m.copy_(state[f"mu/{i:05d}"])
-            v.copy_(state[f"nu/{i:05d}"])
+            out += [(f"mu/{i:05d}", m.dtype, tuple(m.shape)), (f"nu/{i:05d}", v.dtype, tuple(v.shape))]
+        return out
+
+    def _owner_table(self) -> dict[tuple[int, int], int]:
+        """Global rank of the process that is shard ``s`` of tensor-parallel slice ``t``."""
+        if getattr(self, "_owners", None) is None:
+            r = self.runtime
+            mine = (r.tp_rank, r.rank, torch.distributed.get_rank())
+            everyone = [None] * torch.distributed.get_world_size()
+            torch.distributed.all_gather_object(everyone, mine)
+            self._owners = {}
+            for t, shard, g in everyone:
+                self._owners.setdefault((t, shard), g)      # replicas (dp, sp) hold the same shard: the first serves
+        return self._owners
+
+    def optimizer_state_pieces(self):
+        """Collective generator for ``hfio.export_optimizer_stream``: every moment buffer arrives at
+        process 0 shard by shard (one point-to-point transfer per shard), so no process ever holds
+        more than one shard of one unit beyond its own state
+        (src/causal_trainer/checkpointing/huggingface.py:1517-1646)."""
+        if self.runtime is None:
+            opt = self.step_fn.optimizer
+            yield "count", iter([torch.tensor([opt.count], dtype=torch.int64)])
+            for i, (m, v) in enumerate(zip(opt.m, opt.v)):
+                yield f"mu/{i:05d}", iter([m.detach().reshape(-1)])
+                yield f"nu/{i:05d}", iter([v.detach().reshape(-1)])
+            return
+        r = self.runtime
+        dist_ = torch.distributed
+        me = dist_.get_rank()
+        owners = self._owner_table()
+        yield "count", iter([torch.tensor([r.count], dtype=torch.int64)])
+
+        def shards(kind: str, name: str, t: int):
+            u = r.units[name]
+            arena = r.m if kind == "mu" else r.v
+            for shard in range(r.world):
+                lo = shard * u.shard_elems
+                valid = max(0, min(u.shard_elems, u.layout.numel - lo))
+                owner = owners[(t, shard)]
+                piece = None
+                if owner == me:
+                    piece = r.shard_view(name, of=arena)
+                    if me != 0:
+                        dist_.send(piece.contiguous(), dst=0)
+                elif me == 0:
+                    piece = torch.empty(u.shard_elems, dtype=torch.bfloat16, device=self.device)
+                    dist_.recv(piece, src=owner)
+                if valid and me == 0:
+                    yield piece[:valid]
+                elif valid:
+                    yield None
+
+        for path, kind, name, t in self._state_entries():
+            yield path, shards(kind, name, t)
+
+    def load_optimizer_state(self, path: Path, step: int) -> None:
+        names = [p for p, _, _ in self.optimizer_state_layout()]
+        with hfio.OptimizerCheckpoint(path, names, global_step=step) as ckpt:
+            if self.runtime is not None:
+                r = self.runtime
+                r.count = int(ckpt.tensor("count"))
+                for entry, kind, name, t in self._state_entries():
+                    if t != r.tp_rank:
+                        continue
+                    u = r.units[name]
+                    lo = r.rank * u.shard_elems
+                    piece = ckpt.flat_range(entry, lo, max(lo, min(lo + u.shard_elems, u.layout.numel)))
+                    view = r.shard_view(name, of=r.m if kind == "mu" else r.v)
+                    view.zero_()
+                    view[:piece.numel()].copy_(piece)       # only this rank's bytes were read
+                return
+            opt = self.step_fn.optimizer
+            opt.count = int(ckpt.tensor("count"))
+            for i, (m, v) in enumerate(zip(opt.m, opt.v)):
+                m.copy_(ckpt.tensor(f"mu/{i:05d}"))
+                v.copy_(ckpt.tensor(f"nu/{i:05d}"))
 
     # ---- checkpoint bundles ----
     def save_bundle(self, destination: Path, step: int) -> None:
@@ -552,10 +605,9 @@ class TrainingRun:
 
         export_optimizer = None
         if a.save_optimizer_state:
-            state = self.optimizer_state()
-
             def export_optimizer(dest: Path, cid: str) -> None:
-                hfio.export_optimizer_checkpoint(dest, state, global_step=step, checkpoint_id=cid)
+                hfio.export_optimizer_stream(dest, self.optimizer_state_layout(), self.optimizer_state_pieces(),
+                                             global_step=step, checkpoint_id=cid)
         bundles.save_checkpoint_bundle(
             destination, export_model=export_model, export_optimizer=export_optimizer, artifact_kind=self.artifact_kind,
             global_step=step, total_steps=self.plan.total_steps, signature=self.signature,
