@@ -203,8 +203,15 @@ def main() -> None:
     for seed in (11, 12):
         data = bc.make_rows(cfg, global_batch, seq_len, seed)
         executed.append(bench_configs.executed_flops_per_token(cfg, data, seq_len))
-        mine = {k: torch.from_numpy(v[data_rank * rows_per_rank:(data_rank + 1) * rows_per_rank].copy()).pin_memory()
-                for k, v in data.items()}
+        if args.impl == "torch":
+            # the same assignment of rows to ranks as the product path (equal attention cost per rank)
+            from causal_trainer_dev_b200.data.batching import attention_cost_per_row, balanced_row_assignment
+
+            rows = balanced_row_assignment(attention_cost_per_row(data["segment_ids"], data.get("attention_end")),
+                                           data_world)[data_rank]
+            mine = {k: torch.from_numpy(v[rows].copy()).pin_memory() for k, v in data.items()}
+        else:
+            mine = trainer.local_rows(data)
         pool.append(mine)
     tokens_per_step = global_batch * seq_len
 
@@ -278,13 +285,15 @@ def main() -> None:
                 "name": bc.name, "model": bc.model + (f"-{args.layers}layers" if args.layers else ""),
                 "global_batch": global_batch, "seq_len": seq_len,
                 "parallelism": f"fsdp{data_world}" + (f"xtp{tp}" if tp > 1 else ""),
-                "attention": ("MoBA block %d top_k %d (grouped)" % bc.moba if attention_options is not None
-                              else "dense, segment-isolated flash attention"),
+                "attention": (getattr(trainer, "attention", None) or (
+                    "MoBA block %d top_k %d (grouped)" % bc.moba if attention_options is not None
+                    else "dense, segment-isolated flash attention")),
                 "micro_batch_rows": micro,
                 "grad_accumulation": rows_per_rank // micro, "loss": "cut cross-entropy" if ours else "F.cross_entropy on 4096-row logit chunks",
                 "remat": (f"auto: activations of {trainer.engine.kept_layers}/{cfg.num_hidden_layers} layers kept in "
                           "HBM, the rest recomputed per layer") if ours else "none (autograd keeps all activations)",
-                "optimizer": "AdamW, bf16 moments, global-norm clip", "l2": "inputs larger than L2 (weights + state "
+                "optimizer": "AdamW, bf16 moments, global-norm clip",
+                "rows_to_ranks": "equal rows and near-equal attention cost per data rank", "l2": "inputs larger than L2 (weights + state "
                 "are tens of GB per GPU, 126 MB L2)",
             },
             "mfu_of_measured_sustained": value * flops_per_token / (world * peak),

@@ -126,6 +126,25 @@ class Trainer:
         return params
 
     # ------------------------------------------------------------------ data movement
+    def local_rows(self, global_batch: dict) -> dict[str, torch.Tensor]:
+        """This rank's rows of a global batch (NumPy arrays or tensors, identical on every rank) as
+        pinned host tensors.  Rows are dealt to the data ranks so that each gets the same number of
+        rows and nearly the same attention cost (``data.batching.balanced_row_assignment``): packed
+        rows of equal length differ several-fold in visible (query, key) pairs, and the step ends
+        when the slowest rank does."""
+        import numpy as np
+
+        from .data.batching import attention_cost_per_row, balanced_row_assignment
+
+        arrays = {k: (v.numpy() if isinstance(v, torch.Tensor) else np.asarray(v)) for k, v in global_batch.items()}
+        costs = attention_cost_per_row(arrays["segment_ids"], arrays.get("attention_end"))
+        rows = balanced_row_assignment(costs, self.data_world)[self.data_rank]
+        out = {}
+        for k, v in arrays.items():
+            t = torch.from_numpy(np.ascontiguousarray(v[rows]))
+            out[k] = t.pin_memory() if torch.cuda.is_available() else t
+        return out
+
     def upload(self, host_batch: dict[str, torch.Tensor]) -> dict[str, torch.Tensor]:
         out = {}
         for k, v in host_batch.items():

@@ -38,6 +38,8 @@ def main() -> None:
     p.add_argument("--micro-batch", type=int, default=4)
     p.add_argument("--impl", choices=("ours", "nccl"), default="ours")
     p.add_argument("--force-sharded-runtime", action="store_true")
+    p.add_argument("--contiguous-rows", action="store_true",
+                   help="give rank r rows [r * n, (r + 1) * n) instead of dealing rows by attention cost")
     args = p.parse_args()
 
     import torch
@@ -71,8 +73,11 @@ def main() -> None:
     eos = int(cfg.eos_token_id if isinstance(cfg.eos_token_id, int) else cfg.eos_token_id[0])
     data = pretraining_rows(args.global_batch, args.seq_len, cfg.vocab_size, eos_token_id=eos,
                             pad_token_id=cfg.pad_token_id, median_len=600.0, sigma=1.0, min_len=32, seed=11)
-    mine = {k: torch.from_numpy(v[rank * rows_per_rank:(rank + 1) * rows_per_rank].copy()).pin_memory()
-            for k, v in data.items()}
+    if args.contiguous_rows:
+        mine = {k: torch.from_numpy(v[rank * rows_per_rank:(rank + 1) * rows_per_rank].copy()).pin_memory()
+                for k, v in data.items()}
+    else:
+        mine = trainer.local_rows(data)
     batch = trainer.upload(mine)
     for _ in range(args.warmup):
         trainer.train_step_device(batch)

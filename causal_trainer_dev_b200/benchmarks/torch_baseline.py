@@ -1,9 +1,13 @@
 """Library baseline of the headline benchmark: the same Llama-shape training step written with
-stock PyTorch only — cuBLAS matmuls, ``scaled_dot_product_attention`` (flash backend, plain causal
-mask: segment isolation is dropped, which only helps the baseline), ``F.cross_entropy`` in row
-chunks, autograd, fused ``torch.optim.AdamW`` and, on several GPUs, ``fully_shard`` (FSDP2) over
-NCCL.  None of this repository's kernels run here.  It exists to give the product path a
-same-box, same-shape number to stand against (``bench.py --impl torch``).
+stock libraries only — cuBLAS matmuls, library flash attention, ``F.cross_entropy`` in row chunks,
+autograd, fused ``torch.optim.AdamW`` and, on several GPUs, ``fully_shard`` (FSDP2) over NCCL.
+None of this repository's kernels run here.  It exists to give the product path a same-box,
+same-shape number to stand against (``bench.py --impl torch``).
+
+Attention does the same work as the product path: the packed documents are attended separately
+(``flash_attn_varlen_func`` with the documents' cumulative lengths) when the ``flash_attn`` package
+is importable; otherwise ``scaled_dot_product_attention`` with a plain causal mask over the whole
+row, which is more attention FLOPs for the baseline (``attention`` in the result says which ran).
 """
 from __future__ import annotations
 
@@ -32,17 +36,24 @@ class Block(nn.Module):
         self.gu = nn.Linear(d, 2 * f, bias=False)
         self.down = nn.Linear(f, d, bias=False)
 
-    def forward(self, h, cos, sin):
+    def forward(self, h, cos, sin, varlen=None):
         cfg = self.cfg
         b, s, _ = h.shape
         q, kv = cfg.query_width, cfg.key_value_width
         x = self.qkv(self.ln1(h))
-        qh = x[..., :q].view(b, s, cfg.num_attention_heads, cfg.head_dim).transpose(1, 2)
-        kh = x[..., q:q + kv].view(b, s, cfg.num_key_value_heads, cfg.head_dim).transpose(1, 2)
-        vh = x[..., q + kv:].view(b, s, cfg.num_key_value_heads, cfg.head_dim).transpose(1, 2)
-        qh, kh = _rope(qh, cos, sin), _rope(kh, cos, sin)
-        a = F.scaled_dot_product_attention(qh, kh, vh, is_causal=True, enable_gqa=True)
-        h = h + self.o(a.transpose(1, 2).reshape(b, s, q))
+        qh = x[..., :q].view(b, s, cfg.num_attention_heads, cfg.head_dim)
+        kh = x[..., q:q + kv].view(b, s, cfg.num_key_value_heads, cfg.head_dim)
+        vh = x[..., q + kv:].view(b, s, cfg.num_key_value_heads, cfg.head_dim)
+        qh, kh = _rope(qh, cos[:, :, None, :], sin[:, :, None, :]), _rope(kh, cos[:, :, None, :], sin[:, :, None, :])
+        if varlen is not None:
+            # documents attended separately, like the product path: tokens flattened, cumulative lengths
+            fn, cu, longest = varlen
+            a = fn(qh.reshape(b * s, -1, cfg.head_dim), kh.reshape(b * s, -1, cfg.head_dim),
+                   vh.reshape(b * s, -1, cfg.head_dim), cu, cu, longest, longest, causal=True).reshape(b, s, q)
+        else:
+            a = F.scaled_dot_product_attention(qh.transpose(1, 2), kh.transpose(1, 2), vh.transpose(1, 2),
+                                               is_causal=True, enable_gqa=True).transpose(1, 2).reshape(b, s, q)
+        h = h + self.o(a)
         g, u = self.gu(self.ln2(h)).chunk(2, dim=-1)
         return h + self.down(F.silu(g) * u)
 
@@ -56,16 +67,16 @@ class Model(nn.Module):
         self.norm = nn.RMSNorm(cfg.hidden_size, eps=cfg.rms_norm_eps)
         self.head = nn.Linear(cfg.hidden_size, cfg.vocab_size, bias=False)
 
-    def forward(self, ids, targets, weights, denom: float, chunk_rows: int = 4096):
+    def forward(self, ids, targets, weights, denom: float, chunk_rows: int = 4096, positions=None, varlen=None):
         cfg = self.cfg
         b, s = ids.shape
-        pos = torch.arange(s, device=ids.device, dtype=torch.float32)
+        pos = (torch.arange(s, device=ids.device).expand(b, s) if positions is None else positions).float()
         inv = 1.0 / (cfg.rope_theta ** (torch.arange(0, cfg.head_dim, 2, device=ids.device).float() / cfg.head_dim))
-        ang = pos[:, None] * inv[None, :]
-        cos, sin = ang.cos().to(torch.bfloat16), ang.sin().to(torch.bfloat16)
+        ang = pos[:, :, None] * inv[None, None, :]
+        cos, sin = ang.cos().to(torch.bfloat16), ang.sin().to(torch.bfloat16)         # [b, s, half]
         h = self.embed(ids)
         for layer in self.layers:
-            h = layer(h, cos, sin)
+            h = layer(h, cos, sin, varlen)
         h = self.norm(h).view(b * s, -1)
         total = h.new_zeros((), dtype=torch.float32)
         t, w = targets.reshape(-1), weights.reshape(-1)
@@ -109,10 +120,38 @@ class TorchBaseline:
         self.opt = torch.optim.AdamW([{"params": decay, "weight_decay": 0.1}, {"params": plain, "weight_decay": 0.0}],
                                      lr=lr, betas=(0.9, 0.95), eps=1e-8, fused=True)
         self._h2d = self._d2h = 0
+        try:
+            from flash_attn import flash_attn_varlen_func
+
+            self.varlen_fn = flash_attn_varlen_func
+        except ImportError:
+            self.varlen_fn = None
+        self.attention = ("flash_attn varlen (documents attended separately)" if self.varlen_fn is not None
+                          else "SDPA causal over whole rows (no segment mask)")
+
+    @staticmethod
+    def _document_bounds(segments: torch.Tensor):
+        """Cumulative lengths of the runs of equal segment id over the flattened ``[rows * seq]`` tokens
+        (padding runs included: they attend among themselves, at zero loss weight)."""
+        flat = segments.reshape(-1)
+        rows, seq = segments.shape
+        change = torch.ones_like(flat, dtype=torch.bool)
+        change[1:] = flat[1:] != flat[:-1]
+        change[::seq] = True                              # a row boundary always starts a run
+        starts = torch.nonzero(change).reshape(-1).to(torch.int32)
+        cu = torch.cat([starts, torch.tensor([flat.numel()], dtype=torch.int32, device=flat.device)])
+        return cu, int((cu[1:] - cu[:-1]).max())
 
     def upload(self, host_batch):
         out = {}
-        for k in ("input_ids", "attention_mask", "segment_ids"):
+        if self.varlen_fn is not None:
+            # document bounds of every micro-batch, found on the host copy (no device read back)
+            seg = host_batch["segment_ids"]
+            out["_varlen"] = []
+            for r0 in range(0, seg.shape[0], self.micro):
+                cu, longest = self._document_bounds(seg[r0:r0 + self.micro])
+                out["_varlen"].append((cu.to(self.device, non_blocking=True), longest))
+        for k in ("input_ids", "attention_mask", "segment_ids", "position_ids"):
             v = host_batch[k]
             self._h2d += v.numel() * v.element_size()
             out[k] = v.to(self.device, non_blocking=True)
@@ -130,7 +169,13 @@ class TorchBaseline:
         loss_sum = None
         for r0 in range(0, rows, self.micro):
             sl = slice(r0, r0 + self.micro)
-            loss = self.model(batch["input_ids"][sl].long(), targets[sl].long().clamp(min=0), weights[sl].float(), denom)
+            varlen = positions = None
+            if self.varlen_fn is not None:
+                cu, longest = batch["_varlen"][r0 // self.micro]
+                varlen = (self.varlen_fn, cu, longest)
+                positions = batch["position_ids"][sl] if "position_ids" in batch else None
+            loss = self.model(batch["input_ids"][sl].long(), targets[sl].long().clamp(min=0), weights[sl].float(), denom,
+                              positions=positions, varlen=varlen)
             loss.backward()
             loss_sum = loss.detach() if loss_sum is None else loss_sum + loss.detach()
         norm = torch.nn.utils.clip_grad_norm_(self.model.parameters(), 1.0)

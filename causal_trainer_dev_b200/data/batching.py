@@ -152,6 +152,41 @@ def iter_global_batches(dataset, plan: BatchPlan, *, assistant_only_loss: bool, 
         yield collate(dataset, schedule.rows(step), assistant_only_loss)
 
 
+def attention_cost_per_row(segment_ids: np.ndarray, attention_end: np.ndarray | None = None) -> np.ndarray:
+    """Visible (query, key) pairs of every row under segment-isolated causal attention (with the
+    optional inclusive visibility end of MaskGIT blocks): what the row costs in the attention
+    kernels.  Rows of equal length can differ several-fold: one long document against many short ones."""
+    seg = np.asarray(segment_ids)
+    rows, s = seg.shape
+    idx = np.arange(s)[None, :]
+    first = np.ones((rows, s), dtype=bool)
+    first[:, 1:] = seg[:, 1:] != seg[:, :-1]
+    start = np.maximum.accumulate(np.where(first, idx, 0), axis=1)
+    lim = idx if attention_end is None else np.maximum(idx, np.asarray(attention_end))
+    return np.where(seg != 0, lim - start + 1, 0).sum(axis=1).astype(np.float64)
+
+
+def balanced_row_assignment(costs: np.ndarray, ranks: int) -> np.ndarray:
+    """``[ranks, rows / ranks]`` row indices: every rank gets the same number of rows and, as nearly
+    as a greedy pass can make it, the same total cost (largest rows first, each to the least loaded
+    rank that still has room).  The global batch and therefore the gradient are unchanged; only the
+    time the slowest rank needs for its share goes down.  Deterministic: ties go to the lower rank
+    and the lower row index, and rows keep their batch order inside a rank."""
+    costs = np.asarray(costs, dtype=np.float64)
+    n = costs.shape[0]
+    if ranks < 1 or n % ranks:
+        raise ValueError(f"{n} rows cannot be split evenly over {ranks} ranks")
+    per = n // ranks
+    load = np.zeros(ranks)
+    taken: list[list[int]] = [[] for _ in range(ranks)]
+    for row in np.argsort(-costs, kind="stable"):
+        open_ranks = [r for r in range(ranks) if len(taken[r]) < per]
+        r = min(open_ranks, key=lambda x: (load[x], x))
+        taken[r].append(int(row))
+        load[r] += costs[row]
+    return np.asarray([sorted(t) for t in taken], dtype=np.int64).reshape(ranks, per)
+
+
 def split_accumulation(batch: dict[str, Any], accumulation_steps: int) -> dict[str, Any]:
     """Reshapes ``[G*mb, ...]`` fields to ``[G, mb, ...]``."""
     bad = [k for k, v in batch.items() if v.shape[0] % accumulation_steps]

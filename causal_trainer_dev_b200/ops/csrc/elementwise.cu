@@ -624,6 +624,76 @@ adamw_regions_kernel(__nv_bfloat16* __restrict__ p, const GT* __restrict__ g, __
   }
 }
 
+// ------------------------------------------------------------------------------------------
+// Active-row compaction (rows whose loss weight is non-zero go through the LM head; the others do
+// not).  Stable: the compacted order is the row order, so results do not depend on it.
+//   active_count   rows with weight != 0 per block of 1024 rows
+//   active_fill    idx[k] = k-th active row; total[0] = number of active rows
+//   gather_rows    dst[j] = src[idx[j]]
+//   scatter_rows   dst[idx[j]] = src[j] for j < total (dst cleared by the caller)
+// ------------------------------------------------------------------------------------------
+constexpr int ACTIVE_BLOCK = 1024;
+
+__global__ void __launch_bounds__(ACTIVE_BLOCK)
+active_count_kernel(const float* __restrict__ w, int rows, int* __restrict__ block_counts) {
+  const int r = blockIdx.x * ACTIVE_BLOCK + threadIdx.x;
+  const int flag = (r < rows && w[r] != 0.f) ? 1 : 0;
+  const int n = __syncthreads_count(flag);
+  if (threadIdx.x == 0) block_counts[blockIdx.x] = n;
+}
+
+__global__ void __launch_bounds__(ACTIVE_BLOCK)
+active_fill_kernel(const float* __restrict__ w, int rows, const int* __restrict__ block_counts, int* __restrict__ idx,
+                   int* __restrict__ total) {
+  __shared__ int warp_sums[ACTIVE_BLOCK / 32];
+  __shared__ int base_s;
+  const int r = blockIdx.x * ACTIVE_BLOCK + threadIdx.x;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const bool flag = r < rows && w[r] != 0.f;
+  const unsigned votes = __ballot_sync(0xffffffffu, flag);
+  if (lane == 0) warp_sums[warp] = __popc(votes);
+  if (threadIdx.x == 0) {
+    int base = 0;
+    for (int b = 0; b < static_cast<int>(blockIdx.x); ++b) base += block_counts[b];
+    base_s = base;
+  }
+  __syncthreads();
+  int before = base_s;
+  for (int x = 0; x < warp; ++x) before += warp_sums[x];
+  if (flag) idx[before + __popc(votes & ((1u << lane) - 1u))] = r;
+  if (blockIdx.x == gridDim.x - 1 && threadIdx.x == 0) {
+    int sum = base_s;
+    for (int x = 0; x < ACTIVE_BLOCK / 32; ++x) sum += warp_sums[x];
+    total[0] = sum;
+  }
+}
+
+__global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long src_stride, const int* __restrict__ idx,
+                                   __nv_bfloat16* __restrict__ dst, long n, int d) {
+  const int nvec = d / 8;
+  const long work = n * nvec;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < work;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long j = i / nvec;
+    const int v = static_cast<int>(i % nvec);
+    reinterpret_cast<uint4*>(dst + j * d)[v] = reinterpret_cast<const uint4*>(src + idx[j] * src_stride)[v];
+  }
+}
+
+__global__ void scatter_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ idx,
+                                    const int* __restrict__ total, __nv_bfloat16* __restrict__ dst, long dst_stride,
+                                    long n, int d) {
+  const int nvec = d / 8;
+  const long live = min(n, static_cast<long>(total[0]));
+  const long work = live * nvec;
+  for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < work;
+       i += static_cast<long>(gridDim.x) * blockDim.x) {
+    const long j = i / nvec;
+    const int v = static_cast<int>(i % nvec);
+    reinterpret_cast<uint4*>(dst + idx[j] * dst_stride)[v] = reinterpret_cast<const uint4*>(src + j * d)[v];
+  }
+}
+
 }  // namespace ew
 }  // namespace ctb
 
@@ -840,6 +910,39 @@ CTB_API int ctb_adamw_regions(void* p, const void* g, int g_f32, void* m, void* 
     adamw_regions_kernel<__nv_bfloat16><<<grid, 256, 0, s>>>(
         static_cast<__nv_bfloat16*>(p), static_cast<const __nv_bfloat16*>(g), static_cast<__nv_bfloat16*>(m),
         static_cast<__nv_bfloat16*>(v), n, bounds, modes, nreg, lr, b1, b2, eps, decay, bc1, bc2, clip, gscale, 0);
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// idx[k] = k-th row with w != 0 (k < total[0]); block_counts is scratch of ceil(rows / 1024) ints.
+CTB_API int ctb_active_rows(const float* w, int rows, int* block_counts, int* idx, int* total, void* stream) {
+  if (rows <= 0) return fail("active_rows: no rows");
+  cudaStream_t s = static_cast<cudaStream_t>(stream);
+  const int blocks = (rows + ACTIVE_BLOCK - 1) / ACTIVE_BLOCK;
+  active_count_kernel<<<blocks, ACTIVE_BLOCK, 0, s>>>(w, rows, block_counts);
+  CTB_CUDA_OK(cudaGetLastError());
+  active_fill_kernel<<<blocks, ACTIVE_BLOCK, 0, s>>>(w, rows, block_counts, idx, total);
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// dst[j, :] = src[idx[j], :] for j < n (bf16 rows of d elements, d % 8 == 0).
+CTB_API int ctb_gather_rows(const void* src, long src_stride, const int* idx, void* dst, long n, int d, void* stream) {
+  if (d % 8 || src_stride % 8) return fail("gather_rows: rows must be whole 16-byte vectors");
+  if (n <= 0) return 0;
+  gather_rows_kernel<<<grid_for(n * (d / 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(src), src_stride, idx, static_cast<__nv_bfloat16*>(dst), n, d);
+  CTB_CUDA_OK(cudaGetLastError());
+  return 0;
+}
+
+// dst[idx[j], :] = src[j, :] for j < min(n, total[0]); rows of dst that no j names are left alone.
+CTB_API int ctb_scatter_rows(const void* src, const int* idx, const int* total, void* dst, long dst_stride, long n,
+                             int d, void* stream) {
+  if (d % 8 || dst_stride % 8) return fail("scatter_rows: rows must be whole 16-byte vectors");
+  if (n <= 0) return 0;
+  scatter_rows_kernel<<<grid_for(n * (d / 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+      static_cast<const __nv_bfloat16*>(src), idx, total, static_cast<__nv_bfloat16*>(dst), dst_stride, n, d);
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
 }

@@ -245,3 +245,42 @@ def adamw_regions(p, g, m, v, bounds: torch.Tensor, modes: torch.Tensor, *, lr, 
         _lib.ptr(bounds), _lib.ptr(modes), int(modes.numel()), _f(lr), _f(b1), _f(b2), _f(eps), _f(decay),
         _f(1 - b1 ** step), _f(1 - b2 ** step), _lib.ptr(clip), _f(gscale), int(round_bf16), _lib.stream_ptr())
     _lib.check(code, "ctb_adamw_regions")
+
+
+# ------------------------------------------------------------------------------ active-row compaction
+def active_rows(weights: torch.Tensor, tile: int = 128) -> tuple[torch.Tensor, torch.Tensor, int]:
+    """Rows with a non-zero weight, in row order: ``(idx, total, n)`` where ``idx`` (int32) holds the
+    active rows followed by zeros up to a whole number of ``tile`` rows, ``total`` is the device
+    count and ``n`` the same count on the host (one read back: the shapes that follow depend on
+    it).  Stable compaction by block scan (src/causal_trainer/kernels/cut_cross_entropy.py:673-694)."""
+    w = weights.reshape(-1).to(torch.float32).contiguous()
+    rows = w.numel()
+    dev = w.device
+    idx = torch.zeros(rows + tile, dtype=torch.int32, device=dev)
+    counts = torch.empty(-(-rows // 1024), dtype=torch.int32, device=dev)
+    total = torch.empty(1, dtype=torch.int32, device=dev)
+    code = _lib.lib().ctb_active_rows(_lib.ptr(w), rows, _lib.ptr(counts), _lib.ptr(idx), _lib.ptr(total),
+                                      _lib.stream_ptr())
+    _lib.check(code, "ctb_active_rows")
+    n = int(total.item())
+    padded = -(-n // tile) * tile
+    return idx[:padded], total, n
+
+
+def gather_rows(src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
+    """``src[idx]`` for a 2-D bf16 matrix with unit inner stride."""
+    out = torch.empty((idx.numel(), src.shape[1]), dtype=src.dtype, device=src.device)
+    code = _lib.lib().ctb_gather_rows(_lib.ptr(src), _l(src.stride(0)), _lib.ptr(idx), _lib.ptr(out), _l(idx.numel()),
+                                      src.shape[1], _lib.stream_ptr())
+    _lib.check(code, "ctb_gather_rows")
+    return out
+
+
+def scatter_rows(src: torch.Tensor, idx: torch.Tensor, total: torch.Tensor, rows: int) -> torch.Tensor:
+    """``out[idx[j]] = src[j]`` for the first ``total`` entries of ``idx``; every other row of the
+    ``[rows, d]`` result is zero."""
+    out = torch.zeros((rows, src.shape[1]), dtype=src.dtype, device=src.device)
+    code = _lib.lib().ctb_scatter_rows(_lib.ptr(src), _lib.ptr(idx), _lib.ptr(total), _lib.ptr(out), _l(out.stride(0)),
+                                       _l(idx.numel()), src.shape[1], _lib.stream_ptr())
+    _lib.check(code, "ctb_scatter_rows")
+    return out

@@ -80,14 +80,18 @@ class FsdpRuntime:
     """Weight provider (see ``training.engine``) plus the sharded optimizer step."""
 
     def __init__(self, cfg: ModelConfig, tcfg, device: torch.device, group=None, full_cfg: ModelConfig | None = None,
-                 tp_group=None, resident: str = "auto", frozen: tuple[str, ...] = ()):
+                 tp_group=None, resident: str = "auto", frozen: tuple[str, ...] = (), trainable: bool = True):
         """``cfg`` describes what this rank stores: the whole model, or (with ``tp_group``) one
         tensor-parallel slice of ``full_cfg`` (see ``parallel.tp.tp_local_config``).  ``frozen``
         names components (``lm_head`` / ``embed`` / ``norm``) that get no update: their regions of
         the arena are skipped by AdamW (moments never touched, no weight decay) and their gradient
         slots stay zero, so they do not enter the global norm
-        (src/causal_trainer/training/steps.py:213-375)."""
+        (src/causal_trainer/training/steps.py:213-375).  ``trainable=False`` is the frozen base of
+        adapter training: the runtime only shards and serves the weights (all-gather -> GEMM); it
+        allocates no gradient staging, no gradient shards and no moments, and ``grads_ready`` /
+        ``apply_update`` have nothing to do (src/causal_trainer/modeling/lora.py:178-200)."""
         _lib.require_gpu_lib()
+        self.trainable = trainable
         self.cfg, self.tcfg, self.device = cfg, tcfg, device
         self.full_cfg = full_cfg if full_cfg is not None else cfg
         self.tp_group = tp_group
@@ -135,7 +139,8 @@ class FsdpRuntime:
                 pass
             self.param_arena = symm_mem.empty(self.arena_elems, dtype=torch.bfloat16, device=device)
             self.h_params = symm_mem.rendezvous(self.param_arena, gname)
-            self.staging = symm_mem.empty(N_SLOTS * self.max_padded, dtype=torch.bfloat16, device=device)
+            self.staging = symm_mem.empty(N_SLOTS * self.max_padded if trainable else CHUNK, dtype=torch.bfloat16,
+                                          device=device)
             self.h_staging = symm_mem.rendezvous(self.staging, gname)
             self.pads = symm_mem.empty(n_pads, dtype=torch.int32, device=device)
             self.pads.zero_()
@@ -150,7 +155,8 @@ class FsdpRuntime:
         else:
             # a group of one (pure tensor parallelism): the same kernels run on ordinary memory
             self.param_arena = torch.zeros(self.arena_elems, dtype=torch.bfloat16, device=device)
-            self.staging = torch.zeros(N_SLOTS * self.max_padded, dtype=torch.bfloat16, device=device)
+            self.staging = torch.zeros(N_SLOTS * self.max_padded if trainable else CHUNK, dtype=torch.bfloat16,
+                                       device=device)
             self.pads = torch.zeros(n_pads, dtype=torch.int32, device=device)
             self.param_ptrs = [self.param_arena.data_ptr()]
             self.staging_ptrs = [self.staging.data_ptr()]
@@ -159,9 +165,10 @@ class FsdpRuntime:
         self.done_base = N_SLOTS * self.world     # pads[done_base + slot*world + rank]
 
         # ---- local state ----
-        self.m = torch.zeros(self.arena_elems, dtype=torch.bfloat16, device=device)
-        self.v = torch.zeros(self.arena_elems, dtype=torch.bfloat16, device=device)
-        self.grad_shards = torch.zeros(self.arena_elems, dtype=torch.bfloat16, device=device)
+        state_elems = self.arena_elems if trainable else 0
+        self.m = torch.zeros(state_elems, dtype=torch.bfloat16, device=device)
+        self.v = torch.zeros(state_elems, dtype=torch.bfloat16, device=device)
+        self.grad_shards = torch.zeros(state_elems, dtype=torch.bfloat16, device=device)
         self.accum: torch.Tensor | None = None
         self.sumsq = torch.zeros((len(self.units), REDUCE_CTAS * 8), dtype=torch.float32, device=device)
         self.finish_counter = torch.zeros(1, dtype=torch.int32, device=device)
@@ -277,7 +284,7 @@ class FsdpRuntime:
         return out[:u.layout.numel]
 
     def set_grad_dtype(self, dtype: torch.dtype) -> None:
-        if dtype == torch.float32 and self.accum is None:
+        if dtype == torch.float32 and self.accum is None and self.trainable:
             self.accum = torch.zeros(self.arena_elems, dtype=torch.float32, device=self.device)
 
     def _build_region_table(self) -> None:
@@ -425,6 +432,8 @@ class FsdpRuntime:
 
     # ------------------------------------------------------------------ gradients
     def grad_buffer(self, name: str) -> torch.Tensor:
+        if not self.trainable:
+            raise RuntimeError("this runtime serves frozen weights: it has no gradient buffers")
         if name in self.slot_of:
             slot = self.slot_of[name]
         else:
@@ -452,6 +461,8 @@ class FsdpRuntime:
         return self.staging[slot * self.max_padded:slot * self.max_padded + self.units[name].padded]
 
     def grads_ready(self, name: str, last_microbatch: bool) -> None:
+        if not self.trainable:
+            return                          # frozen base: no gradient was produced for this unit
         u = self.units[name]
         slot = self.slot_of.pop(name)
         self.epoch += 1
@@ -523,6 +534,10 @@ class FsdpRuntime:
         a = self.tcfg.adamw
         self.main.wait_stream(self.side)
         self.main.wait_stream(self.reduce_stream)
+        if not self.trainable:
+            # frozen base: the weights never change, so gathered copies stay valid from step to step
+            self.count += 1
+            return torch.zeros((), device=self.device)
         with self._traced("norm", "all", self.main):
             total = self.sumsq.sum().reshape(1)
             if self.tp_world > 1:

@@ -177,6 +177,8 @@ FLAGS: tuple[Flag, ...] = (
     Flag("fused_collectives", "bool", True, "In-kernel NVLink collectives (False: NCCL-only baseline path)."),
     Flag("micro_batch_rows", int, 0, "Rows per device micro-batch inside one step (0: all local rows at once)."),
     Flag("profile_steps", int, 0, "Device-time this many steps with CUDA events and report tokens/s and MFU."),
+    Flag("balance_rows", "bool", True, "Deal the rows of every global batch to the data ranks by attention cost (equal "
+         "rows, near-equal visible query-key pairs per rank) instead of by position."),
     Flag("activation_memory", str, "auto", "What the CUDA engine does with layer activations: auto keeps those of as "
          "many layers as fit in free HBM and recomputes the rest; recompute always recomputes (the meaning of "
          "gradient_checkpointing=nothing_saveable on small-memory devices); keep never recomputes. "

@@ -419,21 +419,18 @@ class LayerwiseEngine:
         # depend on it.)
         full_rows = y.shape[0]
         active = None
-        if self.options.compact_loss_rows:
-            idx = torch.nonzero(weights != 0).reshape(-1)
-            if idx.numel() < 0.9 * full_rows:
-                pad = (-idx.numel()) % 128
-                if pad:      # whole 128-row tiles; padding repeats row 0 with zero weight
-                    idx_p = torch.cat([idx, idx.new_zeros(pad)])
-                    wmask = torch.cat([torch.ones_like(idx, dtype=weights.dtype), weights.new_zeros(pad)])
-                else:
-                    idx_p, wmask = idx, torch.ones_like(idx, dtype=weights.dtype)
+        # (only batches that carry explicit weights can be sparse; asking costs one read back, which a
+        # plain next-token batch is spared)
+        if self.options.compact_loss_rows and ("loss_weights" in batch or "prediction_weights" in batch):
+            idx_p, n_active_dev, n_active = ew.active_rows(weights)     # whole 128-row tiles, row 0 repeated as padding
+            if n_active < 0.9 * full_rows:
                 active = idx_p
                 y_all = y
-                y = y_all.index_select(0, idx_p)
-                targets = targets.index_select(0, idx_p)
-                weights = weights.index_select(0, idx_p) * wmask
-                self._count(6)
+                y = ew.gather_rows(y_all, idx_p)
+                targets = targets.index_select(0, idx_p.long())
+                weights = weights.index_select(0, idx_p.long())
+                weights[n_active:] = 0                                   # padding slots carry no loss
+                self._count(5)
         if self.options.loss_backend == "logits":
             nll, wsum, dy, _ = ce.logits_ce_forward_backward(
                 y, fw["lm_head"], targets, weights, grad_scale, chunk_rows=self.options.cut_chunk_rows,
@@ -445,9 +442,7 @@ class LayerwiseEngine:
                                        dhead_accumulate=accumulate)
         self._count(4 + 3 * ((y.shape[0] + self.options.cut_chunk_rows - 1) // self.options.cut_chunk_rows))
         if active is not None:
-            dy_full = torch.zeros((full_rows, dy.shape[1]), dtype=dy.dtype, device=dy.device)
-            dy_full.index_add_(0, active, dy)     # padded slots carry zero gradient (zero weight)
-            dy, y = dy_full, y_all
+            dy, y = ew.scatter_rows(dy, active, n_active_dev, full_rows), y_all     # rows without loss get zero gradient
         dout, _ = ew.rmsnorm_backward(dy, xf, fw["norm"], rstd_f, dw_out=self._norm_grad(fg, "norm"),
                                       dw_accumulate=accumulate)
         del y, dy, xf

@@ -9,9 +9,17 @@ belongs to it (``q | k | v`` inside ``qkv``, ``gate | up`` inside ``gu``) and it
     t  = x @ A            dB += t^T @ dy
     dt = dy @ B^T         dA += x^T @ dt          dx += dt @ A^T
 
-The rank-``r`` products are a fraction ``r / d`` of the projection's FLOPs and run as library
-GEMMs; adapter gradients are accumulated in fp32 and handed to the optimizer step as extra
-regions (``training.steps.TrainStep``), which also all-reduces them over data-parallel replicas.
+The rank-``r`` products (a fraction ``r / d`` of the projection's FLOPs) run on the same tcgen05
+GEMM as the projections whenever ``r`` is a multiple of 8 (16-byte rows): the adapter output is
+accumulated straight into the projection's output slice and the input gradient into ``dx`` through
+the GEMM's reduce-add epilogue, the adapter gradients into fp32 buffers.  Adapter gradients are
+handed to the optimizer step as extra regions (``training.steps.TrainStep``), which also
+all-reduces them over data-parallel replicas.
+
+The weight provider may be the sharded runtime in its weights-only mode
+(``FsdpRuntime(trainable=False)``): the frozen base is then sharded over the data ranks and
+all-gathered into the consuming GEMMs like any trained model, with no gradient or optimizer memory
+behind it (src/causal_trainer/modeling/lora.py:178-242, src/causal_trainer/training/steps.py:378-552).
 """
 from __future__ import annotations
 
@@ -19,6 +27,7 @@ import torch
 
 from ..models.config import ModelConfig
 from ..models.lora import LoraState
+from ..ops.gemm import gemm
 from .engine import EngineOptions, LayerwiseEngine
 
 
@@ -57,11 +66,19 @@ class LoraLayerwiseEngine(LayerwiseEngine):
             out.append((t.detach(), t.dim() > 1, (lambda g=g: g)))
         return out
 
+    @staticmethod
+    def _on_tensor_cores(a: torch.Tensor, x: torch.Tensor) -> bool:
+        return a.shape[1] % 8 == 0 and a.dtype == torch.bfloat16 and x.dtype == torch.bfloat16
+
     def _project(self, li, name, x, w):
         y = super()._project(li, name, x, w)
         for proj, lo, hi in self._ranges[name]:
-            a, b = self.lora.pair(li, proj)
-            y[:, lo:hi].addmm_(x @ a, b)
+            a, b = self.lora.pair(li, proj)            # a [in, r], b [r, out]
+            if self._on_tensor_cores(a, x):
+                t = gemm(x, a, b_mn=True)                                   # x @ a
+                gemm(t, b, b_mn=True, out=y[:, lo:hi], accumulate=True)     # y += t @ b
+            else:
+                y[:, lo:hi].addmm_(x @ a, b)
             self._count(2)
         return y
 
@@ -71,16 +88,23 @@ class LoraLayerwiseEngine(LayerwiseEngine):
             a, b = self.lora.pair(li, proj)
             ga, gb = self.grads[(li, proj)]
             dys = dy[:, lo:hi]
-            t = x @ a
-            dt = dys @ b.t()
-            d_b = t.t() @ dys
-            d_a = x.t() @ dt
-            if accumulate:
-                ga.add_(d_a)
-                gb.add_(d_b)
+            if self._on_tensor_cores(a, x):
+                t = gemm(x, a, b_mn=True)                                             # x @ a           [T, r]
+                dt = gemm(dys, b)                                                     # dy @ b^T        [T, r]
+                gemm(t, dys, a_mn=True, b_mn=True, out=gb, accumulate=accumulate)     # dB (+)= t^T dy  [r, out]
+                gemm(x, dt, a_mn=True, b_mn=True, out=ga, accumulate=accumulate)      # dA (+)= x^T dt  [in, r]
+                gemm(dt, a, out=dx, accumulate=True)                                  # dx += dt @ a^T
             else:
-                ga.copy_(d_a)
-                gb.copy_(d_b)
-            dx.addmm_(dt, a.t())
+                t = x @ a
+                dt = dys @ b.t()
+                d_b = t.t() @ dys
+                d_a = x.t() @ dt
+                if accumulate:
+                    ga.add_(d_a)
+                    gb.add_(d_b)
+                else:
+                    ga.copy_(d_a)
+                    gb.copy_(d_b)
+                dx.addmm_(dt, a.t())
             self._count(7)
         return dx

@@ -406,7 +406,28 @@ class TrainingRun:
         data_ranks = self.lattice.size("dp") * self.lattice.size("fsdp")
         self.lora: LoraState | None = None
         tp, sp = self.lattice.size("tp"), self.lattice.size("sp")
-        if self.use_engine and (data_ranks > 1 or tp > 1 or sp > 1):
+        if self.use_lora_engine and data_ranks > 1:
+            # adapters over a frozen base that is sharded like a trained model: the runtime serves
+            # the weights (all-gather -> GEMM), adapters are replicated and their gradients all-reduced
+            from ..api import TrainerConfig
+            from ..parallel.fsdp import FsdpRuntime
+            from .lora_engine import LoraLayerwiseEngine
+
+            tcfg = TrainerConfig(micro_batch_rows=a.micro_batch_rows or a.total_batch_size // data_ranks, adamw=adamw,
+                                 schedule=schedule, seed=a.seed, fused_collectives=a.fused_collectives,
+                                 cut_chunk_rows=a.cut_chunk_size or 4096)
+            self.runtime = FsdpRuntime(self.cfg, tcfg, self.device, group=self.lattice.group(("dp", "fsdp")),
+                                       trainable=False)
+            if weights_from is not None:
+                hfio.load_sharded_parameters(weights_from, self.runtime)
+            self.params = None
+            self.lora = LoraState.init(self.cfg, a.lora_rank, seed=a.seed, dtype=self.param_dtype, device=self.device)
+            if self.checkpoint is not None and self.artifact_kind == "peft-adapter":
+                self.lora.load_peft_tensors(st.load_file(self.checkpoint.path / "adapter_model.safetensors"))
+            producer = LoraLayerwiseEngine(self.cfg, self.runtime, self.lora, self.engine_options())
+            self.step_fn = TrainStep(None, producer, adamw, schedule, extra_regions=producer.extra_regions(),
+                                     train_base=False)
+        elif self.use_engine and (data_ranks > 1 or tp > 1 or sp > 1):
             from ..api import TrainerConfig
             from ..parallel.fsdp import FsdpRuntime
             from .engine import EngineOptions, LayerwiseEngine
@@ -504,8 +525,12 @@ class TrainingRun:
                     out += [(f"{kind}/{name}/tp{t}", kind, name, t) for t in range(r.tp_world)]
         return out
 
+    def _sharded_state(self) -> bool:
+        """The optimizer state lives in the sharded runtime (not in a ``FlatAdamW`` of this process)."""
+        return self.runtime is not None and self.runtime.trainable
+
     def optimizer_state_layout(self) -> list[tuple[str, torch.dtype, tuple[int, ...]]]:
-        if self.runtime is not None:
+        if self._sharded_state():
             r = self.runtime
             return [("count", torch.int64, ())] + [(path, torch.bfloat16, (r.units[name].layout.numel,))
                                                     for path, _, name, _ in self._state_entries()]
@@ -532,7 +557,7 @@ class TrainingRun:
         process 0 shard by shard (one point-to-point transfer per shard), so no process ever holds
         more than one shard of one unit beyond its own state
         (src/causal_trainer/checkpointing/huggingface.py:1517-1646)."""
-        if self.runtime is None:
+        if not self._sharded_state():
             opt = self.step_fn.optimizer
             yield "count", iter([torch.tensor([opt.count], dtype=torch.int64)])
             for i, (m, v) in enumerate(zip(opt.m, opt.v)):
@@ -571,7 +596,7 @@ class TrainingRun:
     def load_optimizer_state(self, path: Path, step: int) -> None:
         names = [p for p, _, _ in self.optimizer_state_layout()]
         with hfio.OptimizerCheckpoint(path, names, global_step=step) as ckpt:
-            if self.runtime is not None:
+            if self._sharded_state():
                 r = self.runtime
                 r.count = int(ckpt.tensor("count"))
                 for entry, kind, name, t in self._state_entries():
@@ -676,8 +701,16 @@ class TrainingRun:
         split = batching.split_accumulation(data, a.gradient_accumulation_steps)
         for g in range(a.gradient_accumulation_steps):
             rows = {}
+            if a.balance_rows and ranks > 1:
+                # the same global batch on every rank; which rows a rank keeps is free, so they are dealt by
+                # cost: the step ends when the slowest rank does
+                costs = batching.attention_cost_per_row(
+                    split["segment_ids"][g], split["attention_end"][g] if "attention_end" in split else None)
+                keep = batching.balanced_row_assignment(costs, ranks)[idx]
+            else:
+                keep = np.arange(idx * per_micro, (idx + 1) * per_micro)
             for k, v in split.items():
-                t = torch.from_numpy(np.ascontiguousarray(v[g][idx * per_micro:(idx + 1) * per_micro]))
+                t = torch.from_numpy(np.ascontiguousarray(v[g][keep]))
                 if self.cuda:
                     t = t.pin_memory().to(self.device, non_blocking=True)
                 rows[k] = t

@@ -110,7 +110,7 @@ class AutogradProducer:
 class TrainStep:
     """Drives gradient producers and owns optimizer state for a :class:`ModelParams`."""
 
-    params: ModelParams
+    params: ModelParams | None        # None when the base is frozen and lives elsewhere (sharded adapter training)
     producer: Callable
     adamw: AdamWConfig
     schedule: ScheduleConfig
@@ -124,7 +124,7 @@ class TrainStep:
         self._grad_of: list[Callable[[], torch.Tensor]] = []
         from ..models.freezing import frozen_segments
 
-        frozen_segs = frozen_segments(self.params.config, tuple(self.frozen))
+        frozen_segs = frozen_segments(self.params.config, tuple(self.frozen)) if self.train_base else set()
         if self.train_base:
             for name, u in self.params.units.items():
                 for seg in u.layout.segments:

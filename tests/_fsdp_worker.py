@@ -10,7 +10,59 @@ import torch.distributed as dist
 sys.path.insert(0, str(Path(__file__).resolve().parents[1]))
 
 
+def lora_over_sharded_base(out_path: str) -> None:
+    """Adapter gradients with the frozen base served by the sharded runtime (weights-only mode)
+    against the same engine over a local copy of the base."""
+    from causal_trainer_dev_b200.api import TrainerConfig
+    from causal_trainer_dev_b200.data.synthetic import pretraining_rows
+    from causal_trainer_dev_b200.models.config import preset
+    from causal_trainer_dev_b200.models.lora import LoraState
+    from causal_trainer_dev_b200.models.params import ModelParams
+    from causal_trainer_dev_b200.ops import lib
+    from causal_trainer_dev_b200.parallel.fsdp import FsdpRuntime
+    from causal_trainer_dev_b200.training.engine import LocalProvider
+    from causal_trainer_dev_b200.training.lora_engine import LoraLayerwiseEngine
+    from causal_trainer_dev_b200.training.optimizer import AdamWConfig, ScheduleConfig
+
+    world, rank = dist.get_world_size(), dist.get_rank()
+    dev = torch.device("cuda", torch.cuda.current_device())
+    cfg = preset("tiny", vocab_size=4096, num_hidden_layers=2)
+    tcfg = TrainerConfig(adamw=AdamWConfig(), schedule=ScheduleConfig(1e-3, 0.0, "constant", 0, 10), seed=3)
+    runtime = FsdpRuntime(cfg, tcfg, dev, trainable=False)
+    assert runtime.m.numel() == 0 and runtime.grad_shards.numel() == 0      # no optimizer or gradient memory
+    local = ModelParams(cfg, torch.bfloat16, dev)
+    for name, unit in local.units.items():
+        unit.data.copy_(runtime.gather_full_unit(name))
+    lora = LoraState.init(cfg, 16, seed=4, dtype=torch.bfloat16, device=dev)
+    with torch.no_grad():
+        gen = torch.Generator(device=dev).manual_seed(9)
+        for b in lora.b.values():
+            b.normal_(0, 0.05, generator=gen)
+    data = pretraining_rows(2 * world, 256, cfg.vocab_size, eos_token_id=2, pad_token_id=0, median_len=80, min_len=8, seed=5)
+    mine = {k: torch.from_numpy(v[2 * rank:2 * rank + 2].copy()).to(dev) for k, v in data.items()}
+    sharded = LoraLayerwiseEngine(cfg, runtime, lora)
+    plain = LoraLayerwiseEngine(cfg, LocalProvider(local, torch.bfloat16), lora)
+    nll_s, _ = sharded(mine, 1.0 / 300, True)
+    nll_p, _ = plain(mine, 1.0 / 300, True)
+    worst = 0.0
+    for key in lora.a:
+        for gs, gp in zip(sharded.grads[key], plain.grads[key]):
+            worst = max(worst, float((gs - gp).norm() / gp.norm().clamp_min(1e-12)))
+    again, _ = sharded(mine, 1.0 / 300, True)         # second pass: the gathered weights are still valid
+    status = lib.device_status(raise_on_error=False)
+    if rank == 0:
+        Path(out_path).write_text(json.dumps({"worst": worst, "nll": [float(nll_s), float(nll_p), float(again)],
+                                              "status": status}))
+    dist.destroy_process_group()
+
+
 def main() -> None:
+    if sys.argv[1] == "lora":
+        local = int(os.environ["LOCAL_RANK"])
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        lora_over_sharded_base(sys.argv[2])
+        return
     fused = sys.argv[1] == "fused"
     out_path = sys.argv[2]
     steps = int(sys.argv[3]) if len(sys.argv) > 3 else 2

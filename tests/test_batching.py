@@ -52,3 +52,26 @@ def test_prefetch_converts_exactly_one_ahead():
     assert next(it) == 0 and seen == [0, 1]
     assert next(it) == 10 and seen == [0, 1, 2]
     assert list(it) == [20, 30] and seen == [0, 1, 2, 3]
+
+
+def test_rows_are_dealt_to_ranks_by_attention_cost():
+    from causal_trainer_dev_b200.data.batching import attention_cost_per_row, balanced_row_assignment
+    from causal_trainer_dev_b200.data.synthetic import pretraining_rows
+
+    data = pretraining_rows(32, 1024, 5000, eos_token_id=2, pad_token_id=0, median_len=150.0, sigma=1.0, min_len=8, seed=4)
+    cost = attention_cost_per_row(data["segment_ids"])
+    # one document of n tokens costs n (n + 1) / 2 pairs; padding costs nothing
+    seg = np.array([[1, 1, 1, 2, 2, 0, 0, 0]])
+    assert attention_cost_per_row(seg).tolist() == [6 + 3]
+    end = np.array([[0, 1, 2, 4, 4, 5, 6, 7]])               # the second document is bidirectional
+    assert attention_cost_per_row(seg, end).tolist() == [6 + 4]
+    for ranks in (2, 4, 8):
+        rows = balanced_row_assignment(cost, ranks)
+        assert rows.shape == (ranks, 32 // ranks) and sorted(rows.reshape(-1).tolist()) == list(range(32))
+        assert (np.diff(rows, axis=1) > 0).all()                                  # batch order kept inside a rank
+        contiguous = cost.reshape(ranks, -1).sum(1)
+        dealt = cost[rows].sum(1)
+        assert dealt.max() / dealt.mean() < 1.06 <= contiguous.max() / contiguous.mean()
+        assert np.array_equal(rows, balanced_row_assignment(cost, ranks))         # deterministic
+    with pytest.raises(ValueError, match="evenly"):
+        balanced_row_assignment(cost[:30], 4)

@@ -135,3 +135,25 @@ def test_adamw_over_an_arena_of_regions_in_one_launch(cuda_lib, grad_dtype):
     for lo, hi, mode in zip(bounds[:-1], bounds[1:], modes):
         if mode < 0:   # frozen: bit-identical parameter and moments
             assert torch.equal(p[lo:hi], pr[lo:hi]) and torch.equal(m[lo:hi], mr[lo:hi]) and torch.equal(v[lo:hi], vr[lo:hi])
+
+
+def test_active_row_compaction_is_stable_and_round_trips(cuda_lib):
+    from causal_trainer_dev_b200.ops import elementwise as E
+
+    torch.manual_seed(8)
+    rows, d = 5000, 256
+    w = (torch.rand(rows, device="cuda") > 0.6).float() * torch.rand(rows, device="cuda")
+    w[0] = 0.7                                           # row 0 is active AND the padding target
+    idx, total, n = E.active_rows(w)
+    want = torch.nonzero(w != 0).reshape(-1)
+    assert n == want.numel() == int(total) and idx.numel() == -(-n // 128) * 128
+    assert torch.equal(idx[:n].long(), want) and not idx[n:].any()
+    src = torch.randn(rows, d, device="cuda").bfloat16()
+    packed = E.gather_rows(src, idx)
+    assert torch.equal(packed[:n], src[want]) and torch.equal(packed[n:], src[:1].expand(idx.numel() - n, d))
+    back = E.scatter_rows(packed, idx, total, rows)
+    expect = torch.zeros_like(src)
+    expect[want] = src[want]
+    assert torch.equal(back, expect)                     # padding slots did not overwrite row 0
+    none, _, n0 = E.active_rows(torch.zeros(300, device="cuda"))
+    assert n0 == 0 and none.numel() == 0

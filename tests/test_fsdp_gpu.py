@@ -92,3 +92,10 @@ def test_frozen_components_on_the_sharded_runtime(cuda_lib, tmp_path):
         assert same == (key.split("/")[1] in ("lm_head", "norm", "ln1", "ln2")), key
     for a, c in zip(got["history"], single):
         assert abs(a["loss"] - c["loss"]) < 5e-2 and abs(a["grad_norm"] - c["grad_norm"]) / c["grad_norm"] < 5e-2
+
+
+def test_adapter_training_over_a_sharded_frozen_base(cuda_lib, tmp_path):
+    got = _launch("lora", N, tmp_path, 29618)
+    assert got["status"] == [0, 0, 0, 0]
+    assert got["worst"] < 2e-2                            # same adapter gradients as over a local base
+    assert abs(got["nll"][0] - got["nll"][1]) < 1e-3 * abs(got["nll"][1]) and got["nll"][0] == got["nll"][2]

@@ -124,3 +124,37 @@ def test_two_cta_pair_kernel_matches_reference(cuda_lib, shape):
     finally:
         cuda_lib.lib().ctb_gemm_set_pair(before)
     assert cuda_lib.device_status() == (0, 0, 0, 0)
+
+
+def test_low_rank_shapes_and_bf16_accumulation_into_a_column_slice(cuda_lib):
+    """The adapter products of LoRA: K or N as small as 16, results added into a slice of a wider
+    bf16 matrix (reduce-add epilogue) and into fp32 gradient buffers."""
+    from causal_trainer_dev_b200.ops import gemm as G
+
+    torch.manual_seed(11)
+    t, d_in, d_out, r = 1000, 512, 768, 16
+    x = (torch.randn(t, d_in, device="cuda") * 0.5).bfloat16()
+    a = (torch.randn(d_in, r, device="cuda") * 0.1).bfloat16()
+    b = (torch.randn(r, d_out, device="cuda") * 0.1).bfloat16()
+    y = torch.randn(t, 2 * d_out, device="cuda").bfloat16()
+    want = y.float().clone()
+    low = G.gemm(x, a, b_mn=True)                                         # x @ a
+    assert _rel(low, x.float() @ a.float()) < 4e-3
+    want[:, d_out:] += low.float() @ b.float()
+    G.gemm(low, b, b_mn=True, out=y[:, d_out:], accumulate=True)          # y[:, slice] += low @ b
+    assert _rel(y, want) < 6e-3 and torch.equal(y[:, :d_out].float(), want[:, :d_out])
+    dy = torch.randn(t, 2 * d_out, device="cuda").bfloat16()
+    dys = dy[:, d_out:]
+    dt = G.gemm(dys, b)                                                   # dy @ b^T
+    assert _rel(dt, dys.float() @ b.float().t()) < 4e-3
+    gb = torch.zeros(r, d_out, device="cuda")
+    G.gemm(low, dys, a_mn=True, b_mn=True, out=gb)                        # low^T @ dy
+    assert _rel(gb, low.float().t() @ dys.float()) < 1e-3
+    ga = torch.ones(d_in, r, device="cuda")
+    G.gemm(x, dt, a_mn=True, b_mn=True, out=ga, accumulate=True)          # += x^T @ dt
+    assert _rel(ga, 1 + x.float().t() @ dt.float()) < 1e-3
+    dx = torch.randn(t, d_in, device="cuda").bfloat16()
+    want_dx = dx.float() + dt.float() @ a.float().t()
+    G.gemm(dt, a, out=dx, accumulate=True)                                # dx += dt @ a^T
+    assert _rel(dx, want_dx) < 6e-3
+    assert cuda_lib.device_status() == (0, 0, 0, 0)
