@@ -36,7 +36,7 @@ class TrainerConfig:
     init: str = "normal"               # "normal": N(0, initializer_range) on the device; "hf": ModelParams.init_random
     remat: str = "auto"                # "auto": keep activations that fit, recompute the rest; "full"; "none"
     tp: int = 1                        # tensor-parallel degree; ranks are laid out (fsdp, tp) with tp fastest
-    sp: int = 1                        # sequence-parallel degree (queries sharded, K/V all-gathered); needs tp == 1
+    sp: int = 1                        # sequence-parallel degree (queries sharded, K/V all-gathered); may be combined with tp
     force_sharded_runtime: bool = False  # run the FSDP runtime even on one rank (measures its own overhead)
     frozen: tuple[str, ...] = ()       # components held fixed: any of "lm_head", "embed", "norm"
     loss_backend: str = "cut"          # "cut": projection-fused; "logits": bf16 logits slab per row chunk
@@ -59,18 +59,31 @@ class Trainer:
         if self.cfg.sp > 1:
             from .parallel.fsdp import FsdpRuntime
             from .parallel.runtime import RankLattice
-            from .training.sp_engine import SpLayerwiseEngine
+            from .training.sp_engine import SpLayerwiseEngine, sp_tp_engine
 
-            if self.cfg.tp > 1:
-                raise ValueError("sp > 1 and tp > 1 cannot be combined")
-            if self.world % self.cfg.sp:
-                raise ValueError(f"sp={self.cfg.sp} must divide the number of ranks ({self.world})")
-            self.lattice = RankLattice((1, self.world // self.cfg.sp, 1, 1, self.cfg.sp), self.rank)
+            sp, tp = self.cfg.sp, self.cfg.tp
+            if self.world % (sp * tp):
+                raise ValueError(f"sp * tp = {sp * tp} must divide the number of ranks ({self.world})")
+            fsdp = self.world // (sp * tp)
+            self.lattice = RankLattice((1, fsdp, 1, tp, sp), self.rank)
             shard_group = self.lattice.group(("fsdp", "sp"))      # sp ranks are further FSDP ranks
             sp_group = self.lattice.group(("sp",))
-            self.data_rank, self.data_world = self.lattice.coords()["fsdp"], self.world // self.cfg.sp
-            self.runtime = FsdpRuntime(model, self.cfg, self.device, group=shard_group, frozen=self.cfg.frozen)
-            self.engine = SpLayerwiseEngine(model, sp_group, self.runtime, self._engine_options())
+            self.data_rank, self.data_world = self.lattice.coords()["fsdp"], fsdp
+            if tp > 1:
+                # heads over tp, tokens over sp: the tensor-parallel schedule on each rank's token slice
+                from .parallel.tp import tp_local_config
+
+                if self.cfg.frozen:
+                    raise ValueError("frozen components are not supported together with tensor parallelism")
+                tp_group = self.lattice.group(("tp",))
+                self.runtime = FsdpRuntime(tp_local_config(model, tp), self.cfg, self.device, group=shard_group,
+                                           full_cfg=model, tp_group=tp_group)
+                self.engine = sp_tp_engine(model, tp_group, sp_group, self.runtime, self._engine_options(),
+                                           fused=self.cfg.fused_collectives)
+            else:
+                self.runtime = FsdpRuntime(model, self.cfg, self.device, group=shard_group, frozen=self.cfg.frozen)
+                self.engine = SpLayerwiseEngine(model, sp_group, self.runtime, self._engine_options(),
+                                                fused=self.cfg.fused_collectives)
             self.step_fn = self.runtime.make_step(self.engine)
         elif self.cfg.tp > 1:
             from .parallel.fsdp import FsdpRuntime

@@ -90,21 +90,58 @@ class StreamingBatchEnvelope:
 
 
 # ----------------------------------------------------------------------------------------- retrying reader
-def _hash_record(digest, record: SourceRecord, fields: tuple[str, ...] | None) -> None:
-    view = record if fields is None else {f: record[f] for f in fields if f in record}
-    raw = json.dumps(view, ensure_ascii=False, separators=(",", ":"), sort_keys=True, default=str).encode("utf-8")
-    digest.update(len(raw).to_bytes(8, "big"))
-    digest.update(raw)
+class PrefixLedger:
+    """How many source rows were handed on, and a running SHA-256 over them (optionally over a subset
+    of their fields).  A reopened source must reproduce the ledger before it may continue."""
+
+    def __init__(self, fields: tuple[str, ...] | None):
+        self.fields = fields
+        self.count = 0
+        self._hash = hashlib.sha256()
+
+    @staticmethod
+    def _absorb(h, record: SourceRecord, fields: tuple[str, ...] | None) -> None:
+        view = record if fields is None else {f: record[f] for f in fields if f in record}
+        raw = json.dumps(view, ensure_ascii=False, separators=(",", ":"), sort_keys=True, default=str).encode("utf-8")
+        h.update(len(raw).to_bytes(8, "big"))
+        h.update(raw)
+
+    def record(self, row: SourceRecord) -> None:
+        self._absorb(self._hash, row, self.fields)
+        self.count += 1
+
+    def skip_known_prefix(self, rows: Iterator[SourceRecord]) -> None:
+        """Consumes ``count`` rows from a freshly opened source and checks that they are the rows
+        already handed on."""
+        check = hashlib.sha256()
+        for seen in range(self.count):
+            try:
+                row = next(rows)
+            except StopIteration as exc:
+                raise _ShortReplay(f"the reconstructed streaming source ended after {seen} rows while {self.count} "
+                                   "previously yielded rows had to be skipped; reopening the same epoch") from exc
+            self._absorb(check, row, self.fields)
+        if check.digest() != self._hash.digest():
+            raise RuntimeError(
+                "the reconstructed streaming source prefix changed during retry; pin dataset_revision to an immutable "
+                "Hugging Face commit and ensure all hosts use the same deterministic source")
 
 
 class _ShortReplay(ConnectionError):
     """The reopened source ended before the already-delivered prefix: treated as transient."""
 
 
-class ReplayingReader:
-    """One epoch of ``source_factory(epoch)`` with reopen-and-replay on transient failures."""
+_EXHAUSTED = object()
 
-    _END = object()
+
+class ReplayingReader:
+    """One epoch of ``source_factory(epoch)``, surviving transient failures for as long as they last.
+
+    State: a :class:`PrefixLedger` of what was delivered.  Opening (or reopening) the source is one
+    retried operation -- open, skip the known prefix while re-hashing it, fetch the next row -- so the
+    back-off policy of ``hf_retry`` covers connection errors at any of the three.  A transient error
+    while reading on is parked and re-raised *inside* the next open attempt, which makes it count
+    against the same back-off clock instead of restarting it."""
 
     def __init__(self, source_factory: StreamingSourceFactory, epoch: int, *, initial_delay: float = 1.0,
                  max_delay: float = 60.0, operation: str = "streaming Hugging Face dataset",
@@ -113,56 +150,41 @@ class ReplayingReader:
             raise TypeError("source_factory must be callable")
         if type(epoch) is not int or epoch < 0:
             raise ValueError("epoch must be a non-negative integer")
-        self.factory, self.epoch = source_factory, epoch
-        self.initial_delay, self.max_delay, self.operation = initial_delay, max_delay, operation
-        self.fields = tuple(str(f) for f in digest_fields) if digest_fields is not None else None
-        if self.fields is not None and not self.fields:
+        fields = tuple(str(f) for f in digest_fields) if digest_fields is not None else None
+        if fields is not None and not fields:
             raise ValueError("digest_fields cannot be empty")
-        self.delivered = 0
-        self.prefix = hashlib.sha256()
+        self.factory, self.epoch = source_factory, epoch
+        self.retry = dict(initial_delay=initial_delay, max_delay=max_delay, operation=f"{operation} epoch {epoch}")
+        self.ledger = PrefixLedger(fields)
+        self._parked: Exception | None = None
 
-    def _open_after_prefix(self, pending: list[Exception]):
-        if pending:
-            raise pending.pop()
-        it = iter(self.factory(self.epoch))
-        check = hashlib.sha256()
-        for n in range(self.delivered):
-            try:
-                rec = next(it)
-            except StopIteration as exc:
-                raise _ShortReplay(f"the reconstructed streaming source ended after {n} rows while {self.delivered} "
-                                   "previously yielded rows had to be skipped; reopening the same epoch") from exc
-            _hash_record(check, rec, self.fields)
-        if check.digest() != self.prefix.digest():
-            raise RuntimeError(
-                "the reconstructed streaming source prefix changed during retry; pin dataset_revision to an immutable "
-                "Hugging Face commit and ensure all hosts use the same deterministic source")
-        try:
-            return it, next(it)
-        except StopIteration:
-            return it, self._END
+    @property
+    def delivered(self) -> int:
+        return self.ledger.count
+
+    def _open(self):
+        if self._parked is not None:
+            error, self._parked = self._parked, None
+            raise error
+        rows = iter(self.factory(self.epoch))
+        self.ledger.skip_known_prefix(rows)
+        return rows, next(rows, _EXHAUSTED)
 
     def __iter__(self) -> Iterator[SourceRecord]:
-        pending: list[Exception] = []
-        while True:
-            it, first = retry_hf_call(lambda: self._open_after_prefix(pending), initial_delay=self.initial_delay,
-                                      max_delay=self.max_delay, operation=f"{self.operation} epoch {self.epoch}")
-            if first is self._END:
-                return
-            record = first
-            while True:
-                self.delivered += 1
-                _hash_record(self.prefix, record, self.fields)
-                yield record
-                try:
-                    record = next(it)
-                except StopIteration:
-                    return
-                except Exception as exc:  # noqa: BLE001
-                    if not is_retryable_hf_error(exc):
-                        raise
-                    pending.append(exc)   # surfaces inside retry_hf_call so the backoff policy applies
-                    break
+        rows, row = retry_hf_call(self._open, **self.retry)
+        while row is not _EXHAUSTED:
+            self.ledger.record(row)
+            yield row
+            try:
+                row = next(rows, _EXHAUSTED)
+            except Exception as exc:  # noqa: BLE001
+                if not is_retryable_hf_error(exc):
+                    raise
+                self._parked = exc
+            if self._parked is not None:
+                # reopened outside the handler above: an error of the reopen (a changed prefix, say) must
+                # not inherit the transient error as its context and be mistaken for one
+                rows, row = retry_hf_call(self._open, **self.retry)
 
 
 def iter_retrying_records(source_factory: StreamingSourceFactory, epoch: int, *, initial_delay: float = 1.0,
@@ -185,30 +207,55 @@ def pack_window(examples: Sequence[Mapping[str, Any]], *, max_length: int, pad_t
 
 
 def ensure_loss_weights(record: PackedExample, *, assistant_only_loss: bool) -> PackedExample:
+    """A copy of ``record`` that states its loss weights (explicit > assistant mask > attention mask)."""
     out = {k: list(v) for k, v in record.items()}
-    if "loss_weights" not in out:
-        src = "assistant_masks" if assistant_only_loss else "attention_mask"
-        if src not in out:
-            raise ValueError(f"prepared streaming record is missing {src!r}")
-        out["loss_weights"] = [float(v) for v in out[src]]
-    else:
-        out["loss_weights"] = [float(v) for v in out["loss_weights"]]
-    if len(out["loss_weights"]) != len(out["input_ids"]):
+    basis = "loss_weights" if "loss_weights" in out else ("assistant_masks" if assistant_only_loss else "attention_mask")
+    if basis not in out:
+        raise ValueError(f"prepared streaming record is missing {basis!r}")
+    weights = [float(v) for v in out[basis]]
+    if len(weights) != len(out["input_ids"]):
         raise ValueError("prepared streaming loss_weights are not aligned with input_ids")
-    if any(v < 0 for v in out["loss_weights"]):
+    if min(weights, default=0.0) < 0:
         raise ValueError("prepared streaming loss_weights must be non-negative")
+    out["loss_weights"] = weights
     return out
 
 
 def assign_source_counts(per_row: Sequence[int], *, source_examples: int, trainable_examples: int) -> tuple[int, ...]:
+    """Source rows charged to each prepared row of a window: the examples packed into it, plus, on
+    the last row, the window's rows that preprocessing dropped."""
     if not per_row:
         return ()
-    out = [int(v) for v in per_row]
-    filtered = source_examples - trainable_examples
-    if filtered < 0 or sum(out) != trainable_examples:
+    counts = [int(v) for v in per_row]
+    dropped = source_examples - trainable_examples
+    if dropped < 0 or sum(counts) != trainable_examples:
         raise RuntimeError("streaming source provenance is inconsistent with prepared records")
-    out[-1] += filtered
-    return tuple(out)
+    counts[-1] += dropped
+    return tuple(counts)
+
+
+class WindowAssembler:
+    """Turns windows of raw source rows into envelopes of prepared rows (tokenise, then pack or pad)."""
+
+    def __init__(self, preprocessor: Preprocessor, *, max_sequence_length: int, pad_token_id: int, packing: bool,
+                 state_weights_from_mask: bool):
+        self.pre = preprocessor
+        self.length, self.pad, self.packing = max_sequence_length, pad_token_id, packing
+        self.masked = state_weights_from_mask
+
+    def envelope(self, window: list[SourceRecord], *, epoch: int, first_index: int) -> StreamingBatchEnvelope:
+        tokenized = self.pre.run(window, example_index_offset=first_index, allow_empty=True)
+        if self.packing:
+            rows, per_row = pack_window(tokenized, max_length=self.length, pad_token_id=self.pad)
+        else:
+            rows = pad_examples(tokenized, max_length=self.length, pad_token_id=self.pad)
+            per_row = [1] * len(rows)
+        return StreamingBatchEnvelope(
+            records=tuple(ensure_loss_weights(r, assistant_only_loss=self.masked) for r in rows),
+            source_examples=len(window),
+            record_source_examples=assign_source_counts(per_row, source_examples=len(window),
+                                                        trainable_examples=len(tokenized)),
+            epoch=epoch)
 
 
 def iter_streaming_batches(source_factory: StreamingSourceFactory, tokenizer: Any, *, num_epochs: int | None,
@@ -225,27 +272,20 @@ def iter_streaming_batches(source_factory: StreamingSourceFactory, tokenizer: An
         raise ValueError("packing_batch_size must be positive")
     if num_epochs is not None and (type(num_epochs) is not int or num_epochs <= 0):
         raise ValueError("num_epochs must be a positive integer or None")
-    pre = Preprocessor(tokenizer, dataset_text_field, max_sequence_length, assistant_only_loss,
-                       last_assistant_only_loss, endprompt)
-    masked = assistant_only_loss or last_assistant_only_loss
-    for epoch in (itertools.count() if num_epochs is None else range(num_epochs)):
-        reader = iter(ReplayingReader(source_factory, epoch, initial_delay=retry_initial_delay,
-                                      max_delay=retry_max_delay,
-                                      digest_fields=(dataset_text_field, "tools", "chat_template_kwargs")))
+    assembler = WindowAssembler(
+        Preprocessor(tokenizer, dataset_text_field, max_sequence_length, assistant_only_loss, last_assistant_only_loss,
+                     endprompt),
+        max_sequence_length=max_sequence_length, pad_token_id=pad_token_id, packing=packing,
+        state_weights_from_mask=assistant_only_loss or last_assistant_only_loss)
+    epochs = itertools.count() if num_epochs is None else range(num_epochs)
+    for epoch in epochs:
+        rows = iter(ReplayingReader(source_factory, epoch, initial_delay=retry_initial_delay, max_delay=retry_max_delay,
+                                    digest_fields=(dataset_text_field, "tools", "chat_template_kwargs")))
         consumed = 0
-        while window := list(islice(reader, packing_batch_size)):
-            tokenized = pre.run(window, example_index_offset=consumed, allow_empty=True)
+        while True:
+            window = list(islice(rows, packing_batch_size))
+            if not window:
+                break
+            yield assembler.envelope(window, epoch=epoch, first_index=consumed)
             consumed += len(window)
-            if packing:
-                rows, per_row = pack_window(tokenized, max_length=max_sequence_length, pad_token_id=pad_token_id)
-            else:
-                rows = pad_examples(tokenized, max_length=max_sequence_length, pad_token_id=pad_token_id)
-                per_row = [1] * len(rows)
-            yield StreamingBatchEnvelope(
-                records=tuple(ensure_loss_weights(r, assistant_only_loss=masked) for r in rows),
-                source_examples=len(window),
-                record_source_examples=assign_source_counts(per_row, source_examples=len(window),
-                                                            trainable_examples=len(tokenized)),
-                epoch=epoch,
-            )
-        yield StreamingBatchEnvelope((), 0, (), epoch, is_epoch_end=True)
+        yield StreamingBatchEnvelope((), 0, (), epoch, is_epoch_end=True)       # explicit end-of-epoch marker

@@ -179,11 +179,15 @@ def _row_stride(t: torch.Tensor) -> int:
 def flash_attention_forward(
     q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, meta: AttentionMeta, scale: float | None = None,
     out: torch.Tensor | None = None, spin_budget: int = 0, q_offset: int = 0,
+    kv_flags: tuple[torch.Tensor, int, int, int] | None = None,
 ) -> tuple[torch.Tensor, torch.Tensor]:
     """Runs the tcgen05 forward kernel; returns (O [B,Sq,Hq,D] bf16, LSE [B,Hq,Sq] fp32).
 
     Under sequence parallelism ``q`` holds only the queries ``[q_offset, q_offset + Sq)`` of every
-    row while ``k`` / ``v`` (and ``meta``) cover the whole sequence.
+    row while ``k`` / ``v`` (and ``meta``) cover the whole sequence.  ``kv_flags = (flags, chunk
+    elements, elements per gathered row, epoch)`` says that ``k`` / ``v`` are the two halves of a
+    buffer an all-gather pull is still filling: the kernel's producer warp acquires the chunk flags
+    of every key tile before loading it.
     """
     b, sq, hq, d = q.shape
     s = k.shape[1]
@@ -192,14 +196,18 @@ def flash_attention_forward(
     if out is None:
         out = torch.empty((b, sq, hq, d), dtype=torch.bfloat16, device=q.device)
     lse = torch.empty((b, hq, sq), dtype=torch.float32, device=q.device)
-    code = _lib.lib().ctb_attn_fwd_range(
-        _lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(meta.seg), _lib.ptr(meta.lim),
-        _lib.ptr(meta.start), _lib.ptr(meta.kv_lo), _lib.ptr(meta.kv_hi),
-        b, s, sq, q_offset, hq, hkv, d, ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)),
-        ctypes.c_long(_row_stride(v)), ctypes.c_long(_row_stride(out)), ctypes.c_float(scale),
-        ctypes.c_longlong(spin_budget), _lib.stream_ptr(),
-    )
-    _lib.check(code, "ctb_attn_fwd_range")
+    common = (_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(out), _lib.ptr(lse), _lib.ptr(meta.seg), _lib.ptr(meta.lim),
+              _lib.ptr(meta.start), _lib.ptr(meta.kv_lo), _lib.ptr(meta.kv_hi),
+              b, s, sq, q_offset, hq, hkv, d, ctypes.c_long(_row_stride(q)), ctypes.c_long(_row_stride(k)),
+              ctypes.c_long(_row_stride(v)), ctypes.c_long(_row_stride(out)), ctypes.c_float(scale))
+    if kv_flags is None:
+        code = _lib.lib().ctb_attn_fwd_range(*common, ctypes.c_longlong(spin_budget), _lib.stream_ptr())
+        _lib.check(code, "ctb_attn_fwd_range")
+    else:
+        flags, chunk, row_elems, epoch = kv_flags
+        code = _lib.lib().ctb_attn_fwd_gathered(*common, _lib.ptr(flags), ctypes.c_long(chunk), ctypes.c_long(row_elems),
+                                                ctypes.c_uint(epoch), ctypes.c_longlong(spin_budget), _lib.stream_ptr())
+        _lib.check(code, "ctb_attn_fwd_gathered")
     return out, lse
 
 

@@ -52,6 +52,17 @@ struct GroupArgs {
 // Sequence parallelism: a rank may hold only the queries [q_off, q_off + Sq) of every row while
 // keys and values cover the whole sequence of S tokens.  Q / O / dQ / dO / LSE / delta are then
 // indexed by the local query position, the visibility metadata by the global one.
+// Keys and values that an all-gather pull is still filling (sequence parallelism): K and V are the
+// two halves of one gathered [S, row_elems] buffer whose chunks of `chunk` elements each have a flag;
+// the producer warp acquires the flags of a 128-row tile before it issues the tile's copies, so the
+// transfer overlaps the attention over the rows that are already there.
+struct KvFlags {
+  const unsigned* flags;   // null: K / V are plain memory
+  long chunk;              // elements per flag
+  long row_elems;          // elements per gathered row (K and V widths together)
+  unsigned epoch;
+};
+
 struct FwdArgs {
   int B, S, Hq, Hkv;
   int Sq, q_off;
@@ -66,6 +77,7 @@ struct FwdArgs {
   long long spin_budget;
   SparseArgs sp;
   GroupArgs grp;
+  KvFlags kvf;
 };
 
 struct FwdCall {
@@ -80,6 +92,7 @@ struct FwdCall {
   SparseArgs sp{};
   GroupArgs grp{};
   int gathered_rows = 0;     // grouped: capacity of the gathered row space (a multiple of 256)
+  KvFlags kvf{};
 };
 
 enum : int { MODE_DKV = 0, MODE_DQ = 1 };

@@ -38,6 +38,7 @@ enum : unsigned {
   SITE_F_MMA_P = 0x0204,
   SITE_F_SM_S = 0x0205,
   SITE_F_SM_PV = 0x0206,
+  SITE_F_KV_FLAG = 0x0207,
 };
 
 template <int D>
@@ -181,6 +182,28 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant
       bool ok = true;
       for (int i = 0; ok && i < nmax; ++i) {
         const int k0 = kv_pos(i);
+        if (args.kvf.flags != nullptr) {
+          // gathered K / V (see KvFlags): the rows [k0, k0 + 128) of batch kb must have landed
+          const long e0 = (static_cast<long>(kb) * args.S + k0) * args.kvf.row_elems;
+          const long e1 = e0 + 128 * args.kvf.row_elems - 1;
+          for (long f = e0 / args.kvf.chunk; ok && f <= e1 / args.kvf.chunk; ++f) {
+            const long long t0 = clock64();
+            while (true) {
+              unsigned got;
+              asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(got) : "l"(args.kvf.flags + f) : "memory");
+              if (got >= args.kvf.epoch) break;
+              if (*abort_flag || clock64() - t0 > budget) {
+                *abort_flag = 1u;
+                report_failure(st, SITE_F_KV_FLAG, static_cast<unsigned>(f), args.kvf.epoch);
+                ok = false;
+                break;
+              }
+              __nanosleep(64);
+            }
+          }
+          if (!ok) break;
+          fence_proxy_async_all();   // generic-proxy writes of the pull CTAs -> async-proxy reads below
+        }
 #pragma unroll 1
         for (int which = 0; which < 2; ++which) {
           if (!mbar_wait(&kv_empty[slot], phase ^ 1u, abort_flag, st, SITE_F_PROD, budget)) {
@@ -475,6 +498,7 @@ int launch_fwd(const FwdCall& c) {
   a.lse = c.lse;
   a.sp = c.sp;
   a.grp = c.grp;
+  a.kvf = c.kvf;
   a.status = device_status();
   a.spin_budget = c.spin_budget > 0 ? c.spin_budget : CTB_SPIN_BUDGET;
   auto kern = attn_fwd_kernel<D>;
@@ -570,6 +594,29 @@ CTB_API int ctb_attn_fwd_grouped(const void* qg, const void* k, const void* v, v
   c.q_row_stride = D; c.k_row_stride = k_row_stride; c.v_row_stride = v_row_stride; c.o_row_stride = D;
   c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
   c.grp.desc = static_cast<const int4*>(desc); c.grp.block = block; c.gathered_rows = gathered_rows;
+  if (D == 128) return ctb::attn::launch_fwd<128>(c);
+  if (D == 64) return ctb::attn::launch_fwd<64>(c);
+  return ctb::fail("attention: head_dim must be 64 or 128");
+}
+
+// Sequence-parallel forward over gathered K / V whose all-gather may still be in flight: k and v are
+// the halves of one [B, S, row_elems] buffer (k at its start); flags / chunk / epoch as in KvFlags.
+CTB_API int ctb_attn_fwd_gathered(const void* q, const void* k, const void* v, void* o, float* lse, const int* seg,
+                                  const int* lim, const int* row_start, const int* kv_lo, const int* kv_hi,
+                                  int B, int S, int Sq, int q_off, int Hq, int Hkv, int D, long q_row_stride,
+                                  long k_row_stride, long v_row_stride, long o_row_stride, float scale,
+                                  const unsigned* kv_flags, long kv_chunk, long kv_row_elems, unsigned kv_epoch,
+                                  long long spin_budget, void* stream) {
+  if (S % 128 || Sq % 128 || q_off % 128 || q_off < 0 || q_off + Sq > S)
+    return ctb::fail("attention: S, Sq and q_off must be multiples of 128 with q_off + Sq <= S");
+  if (Hq % Hkv) return ctb::fail("attention: Hq must be a multiple of Hkv");
+  if (kv_flags != nullptr && (kv_chunk <= 0 || kv_row_elems <= 0)) return ctb::fail("attention: bad K/V flag geometry");
+  ctb::attn::FwdCall c{};
+  c.q = q; c.k = k; c.v = v; c.o = o; c.lse = lse; c.seg = seg; c.lim = lim; c.row_start = row_start; c.kv_lo = kv_lo; c.kv_hi = kv_hi;
+  c.B = B; c.S = S; c.Sq = Sq; c.q_off = q_off; c.Hq = Hq; c.Hkv = Hkv;
+  c.q_row_stride = q_row_stride; c.k_row_stride = k_row_stride; c.v_row_stride = v_row_stride;
+  c.o_row_stride = o_row_stride; c.scale = scale; c.spin_budget = spin_budget; c.stream = stream;
+  c.kvf.flags = kv_flags; c.kvf.chunk = kv_chunk; c.kvf.row_elems = kv_row_elems; c.kvf.epoch = kv_epoch;
   if (D == 128) return ctb::attn::launch_fwd<128>(c);
   if (D == 64) return ctb::attn::launch_fwd<64>(c);
   return ctb::fail("attention: head_dim must be 64 or 128");

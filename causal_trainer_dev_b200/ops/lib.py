@@ -85,6 +85,7 @@ _SITES = {
     0x0204: "attention forward mma: P never published",
     0x0205: "attention forward softmax: scores never completed",
     0x0206: "attention forward softmax: P V never completed",
+    0x0207: "attention forward producer: gathered K/V flag never published",
     0x0301: "attention backward producer: streamed stage never freed",
     0x0302: "attention backward mma: resident tiles never arrived",
     0x0303: "attention backward mma: streamed block never arrived",

@@ -306,6 +306,44 @@ class TpContext:
         if self.fused and self.world > 1:
             self.main.wait_event(self.pull_done[g.slot])
 
+    def gathered_flags(self, g: Gathered) -> tuple[torch.Tensor, int, int, int] | None:
+        """``(flags, chunk elements, row elements, epoch)`` of the all-gather last started on ``g``'s
+        slot, for consumers that acquire the chunk flags themselves (the attention producer warp);
+        None when the buffer is plain memory (one rank, NCCL variant, or the pull already finished)."""
+        if not self.fused or self.world == 1 or self.pull_done[g.slot].query():
+            return None
+        src = self.sources[g.slot]
+        return self.flags[g.slot], self.chunk, self.width, src.epoch
+
+    def reduce_scatter_rows(self, g: Gathered, out: torch.Tensor | None = None) -> torch.Tensor:
+        """Sum over the ranks of the ``[rows, width]`` partials each rank wrote into ``g.full`` (its
+        own ring slot), restricted to this rank's rows: every rank publishes "my partial is complete"
+        on its peers and then sums its row slice from all peers' slots with 16-byte peer loads, in
+        rank order, in fp32 (the fused reduce kernel of the FSDP runtime, ``csrc/collectives.cu``)."""
+        if out is None:
+            out = torch.empty((self.rows_per_rank, self.width), dtype=torch.bfloat16, device=self.device)
+        if self.world == 1:
+            out.copy_(g.full)
+            return out
+        if not self.fused:
+            dist.reduce_scatter_tensor(out.view(-1), g.full.reshape(-1), group=self.group)
+            return out
+        self.ag_count += 1
+        epoch = self.ag_count
+        slot = g.slot
+        L = _lib.lib()
+        code = L.ctb_signal_peers(self.pad_ptr_array, self.world, self.ag_base + slot * self.world + self.rank,
+                                  ctypes.c_uint(epoch), _lib.stream_ptr())
+        _lib.check(code, "ctb_signal_peers")
+        f = ctypes.c_float
+        code = L.ctb_rs_reduce(
+            self.ring_ptr_arrays[slot], ctypes.c_long(self.rank * self.slab), ctypes.c_long(self.slab), self.world,
+            _lib.ptr(self.pads), self.ag_base + slot * self.world, ctypes.c_uint(epoch), None, 0, 1, _lib.ptr(out), None,
+            0, None, None, None, ctypes.c_long(0), *(f(0.0),) * 7, None, 0, _lib.ptr(self.counters[48:]), PULL_CTAS,
+            ctypes.c_longlong(self.spin_budget), _lib.stream_ptr())
+        _lib.check(code, "ctb_rs_reduce")
+        return out
+
     # ------------------------------------------------------------------ GEMM -> reduce-scatter
     def gemm_reduce_scatter(self, a: torch.Tensor, b: torch.Tensor, *, b_mn: bool = False,
                             out: torch.Tensor | None = None) -> torch.Tensor:

@@ -121,6 +121,10 @@ class LayerwiseEngine:
         sequence is split over ranks)."""
         return t
 
+    def _local_seq(self, s: int) -> int:
+        """Tokens of a row of ``s`` tokens that this rank computes on."""
+        return s
+
     def _project(self, li: int, name: str, x: torch.Tensor, w: dict[str, torch.Tensor]) -> torch.Tensor:
         """Projection ``name`` ("qkv" | "o" | "gu" | "down") of layer ``li``: ``x @ W^T (+ bias)``."""
         self._count()

@@ -249,10 +249,9 @@ class TrainingRun:
         # adapters on the CUDA engine: every rank holds the frozen base, adapter gradients are all-reduced
         self.use_lora_engine = (engine_ok and args.lora and not args.lora_train_embed_and_lm_head
                                 and self.lattice.size("tp") == 1 and self.lattice.size("sp") == 1)
-        if self.lattice.size("sp") > 1 and (self.lattice.size("tp") > 1 or not self.use_engine
-                                            or args.attention_options is not None):
-            raise ValueError("sequence parallelism (sp > 1) runs on the bf16 CUDA engine with tp = 1 and dense "
-                             "attention; shard long MoBA rows over tp instead")
+        if self.lattice.size("sp") > 1 and (not self.use_engine or args.attention_options is not None):
+            raise ValueError("sequence parallelism (sp > 1) runs on the bf16 CUDA engine with dense attention; "
+                             "shard long MoBA rows over tp instead")
         if self.lattice.size("tp") > 1 and not self.use_engine:
             raise ValueError("tensor parallelism (tp > 1) runs on the bf16 CUDA engine only: it needs GPUs, "
                              "--attn_mechanism efficient, a fused loss, no LoRA and dense attention")
@@ -443,11 +442,21 @@ class TrainingRun:
             # parameters, gradients and optimizer state are sharded over dp x fsdp (a dp replica
             # would only cost memory); tensor-parallel ranks hold slices of every projection
             data_group = self.lattice.group(("dp", "fsdp", "sp") if sp > 1 else ("dp", "fsdp"))
-            if sp > 1:
+            if sp > 1 and tp > 1:
+                from ..parallel.tp import tp_local_config
+                from .sp_engine import sp_tp_engine
+
+                tp_group = self.lattice.group(("tp",))
+                self.runtime = FsdpRuntime(tp_local_config(self.cfg, tp), tcfg, self.device, group=data_group,
+                                           full_cfg=self.cfg, tp_group=tp_group)
+                engine = sp_tp_engine(self.cfg, tp_group, self.lattice.group(("sp",)), self.runtime, options,
+                                      fused=a.fused_collectives)
+            elif sp > 1:
                 from .sp_engine import SpLayerwiseEngine
 
                 self.runtime = FsdpRuntime(self.cfg, tcfg, self.device, group=data_group, frozen=frozen)
-                engine = SpLayerwiseEngine(self.cfg, self.lattice.group(("sp",)), self.runtime, options)
+                engine = SpLayerwiseEngine(self.cfg, self.lattice.group(("sp",)), self.runtime, options,
+                                           fused=a.fused_collectives)
             elif tp > 1:
                 from ..parallel.tp import tp_local_config
                 from .tp_engine import TpLayerwiseEngine

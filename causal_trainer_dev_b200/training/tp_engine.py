@@ -61,7 +61,7 @@ class TpLayerwiseEngine(LayerwiseEngine):
 
     def _context(self, batch):
         ctx = super()._context(batch)
-        ctx["tp"] = self._tp(ctx["batch"] * ctx["seq"])
+        ctx["tp"] = self._tp(ctx["batch"] * self._local_seq(ctx["seq"]))
         return ctx
 
     def _layers_to_keep(self, tokens: int) -> int:
@@ -162,7 +162,7 @@ class TpLayerwiseEngine(LayerwiseEngine):
         ctx = self._context(batch)
         cfg, tp = self.cfg, ctx["tp"]
         embed = self.provider.acquire("embed")
-        resid = tp.embed_lookup(batch["input_ids"], embed.view("embed"), self.full_cfg.vocab_size)
+        resid = tp.embed_lookup(self.select_tokens(batch["input_ids"]), embed.view("embed"), self.full_cfg.vocab_size)
         self.provider.release("embed")
         branch = None
         for li in range(cfg.num_hidden_layers):
@@ -188,7 +188,8 @@ class TpLayerwiseEngine(LayerwiseEngine):
         vocab_lo = self.tp_rank * vocab_local
         # ---------------- forward ----------------
         embed = prov.acquire("embed", prefetch="layer.0")
-        resid = tp.embed_lookup(batch["input_ids"], embed.view("embed"), full.vocab_size)
+        local_ids = self.select_tokens(batch["input_ids"])
+        resid = tp.embed_lookup(local_ids, embed.view("embed"), full.vocab_size)
         self._count(3)
         prov.release("embed")
         branch = None
@@ -211,7 +212,7 @@ class TpLayerwiseEngine(LayerwiseEngine):
         _, rstd_f, xf = ew.rmsnorm_forward(resid, fw["norm"], cfg.rms_norm_eps, residual=branch, out=gy.mine)
         y = tp.all_gather(gy)
         targets, weights = losses.aligned_targets_and_weights(batch)
-        targets, weights = targets.reshape(-1), weights.reshape(-1)
+        targets, weights = self.select_tokens(targets).reshape(-1), self.select_tokens(weights).reshape(-1)
         local_t = targets.to(torch.int32) - vocab_lo
         local_t = torch.where((local_t >= 0) & (local_t < vocab_local), local_t, torch.full_like(local_t, -1))
         nll, wsum, lse, coef = ce.cut_ce_forward(y, fw["lm_head"], local_t, weights, grad_scale, exchange=tp)
@@ -269,7 +270,7 @@ class TpLayerwiseEngine(LayerwiseEngine):
                 gtab.zero_()
             dx_full = tp.all_gather(dout)
             tp.wait_gathered(dout)
-            ew.embedding_backward(batch["input_ids"], dx_full, gtab, full.pad_token_id, vocab_lo)
+            ew.embedding_backward(local_ids, dx_full, gtab, full.pad_token_id, vocab_lo)
             self._count(8)
             prov.grads_ready("embed", last)
         return nll, wsum

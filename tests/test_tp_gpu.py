@@ -81,6 +81,18 @@ def test_tp2_with_one_shared_kv_head_matches_fsdp2(cuda_lib, tmp_path):
 def test_sequence_parallel_sp2_matches_fsdp2(cuda_lib, tmp_path):
     """sp = 2: each rank computes half of every row's tokens, K/V are all-gathered, dK/dV reduce-scattered."""
     sp = _launch(["train", "1", "fused", "3", "2", "2"], 2, tmp_path / "sp.json", 29639)
+    sp_nccl = _launch(["train", "1", "nccl", "3", "2", "2"], 2, tmp_path / "sp_nccl.json", 29641)
     fsdp = _launch(["train", "1", "fused", "3", "2", "1"], 2, tmp_path / "fsdp_sp.json", 29640)
     assert sp["status"] == [0, 0, 0, 0]
     _close(sp["history"], fsdp["history"], 2e-2, 3e-2)
+    _close(sp["history"], sp_nccl["history"], 2e-2, 3e-2)      # in-kernel K/V gather and dK/dV reduce against NCCL
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 4, reason="needs four GPUs")
+def test_sequence_times_tensor_parallel_matches_fsdp4(cuda_lib, tmp_path):
+    """sp = 2 x tp = 2: heads over tp, tokens over sp; K/V gathered and dK/dV summed over sp inside
+    the tensor-parallel schedule of each token slice."""
+    mixed = _launch(["train", "2", "fused", "3", "2", "2"], 4, tmp_path / "sptp.json", 29642)
+    fsdp = _launch(["train", "1", "fused", "3", "2", "1"], 4, tmp_path / "fsdp4b.json", 29643)
+    assert mixed["status"] == [0, 0, 0, 0]
+    _close(mixed["history"], fsdp["history"], 2e-2, 3e-2)
