@@ -344,6 +344,11 @@ class FsdpRuntime:
             if g is None:
                 g = _Gathered(self.units[name].padded, self.device)
                 self.gathered.append(g)
+                # the buffer and its flags were just cleared on the main stream: the pull (side
+                # stream) must not start before that, or the clearing would land on top of it
+                fresh = torch.cuda.Event()
+                fresh.record(self.main)
+                g.free_event = fresh
             g.valid = True
         else:
             g = self._pick_buffer(keep | {name})
