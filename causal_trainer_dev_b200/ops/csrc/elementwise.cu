@@ -668,21 +668,31 @@ active_fill_kernel(const float* __restrict__ w, int rows, const int* __restrict_
   }
 }
 
+// Row indices come from device memory: an index outside [0, rows) is recorded in the status word
+// (site, position, value) and the row is skipped; nothing is read or written out of bounds.
+enum : unsigned { SITE_GATHER_INDEX = 0x0601, SITE_SCATTER_INDEX = 0x0602 };
+
 __global__ void gather_rows_kernel(const __nv_bfloat16* __restrict__ src, long src_stride, const int* __restrict__ idx,
-                                   __nv_bfloat16* __restrict__ dst, long n, int d) {
+                                   __nv_bfloat16* __restrict__ dst, long n, int d, int rows, DeviceStatus* st) {
   const int nvec = d / 8;
   const long work = n * nvec;
   for (long i = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x; i < work;
        i += static_cast<long>(gridDim.x) * blockDim.x) {
     const long j = i / nvec;
     const int v = static_cast<int>(i % nvec);
-    reinterpret_cast<uint4*>(dst + j * d)[v] = reinterpret_cast<const uint4*>(src + idx[j] * src_stride)[v];
+    const int r = idx[j];
+    if (r < 0 || r >= rows) {
+      if (v == 0) report_failure(st, SITE_GATHER_INDEX, static_cast<unsigned>(j), static_cast<unsigned>(r));
+      reinterpret_cast<uint4*>(dst + j * d)[v] = make_uint4(0u, 0u, 0u, 0u);
+      continue;
+    }
+    reinterpret_cast<uint4*>(dst + j * d)[v] = reinterpret_cast<const uint4*>(src + r * src_stride)[v];
   }
 }
 
 __global__ void scatter_rows_kernel(const __nv_bfloat16* __restrict__ src, const int* __restrict__ idx,
                                     const int* __restrict__ total, __nv_bfloat16* __restrict__ dst, long dst_stride,
-                                    long n, int d) {
+                                    long n, int d, int rows, DeviceStatus* st) {
   const int nvec = d / 8;
   const long live = min(n, static_cast<long>(total[0]));
   const long work = live * nvec;
@@ -690,7 +700,12 @@ __global__ void scatter_rows_kernel(const __nv_bfloat16* __restrict__ src, const
        i += static_cast<long>(gridDim.x) * blockDim.x) {
     const long j = i / nvec;
     const int v = static_cast<int>(i % nvec);
-    reinterpret_cast<uint4*>(dst + idx[j] * dst_stride)[v] = reinterpret_cast<const uint4*>(src + j * d)[v];
+    const int r = idx[j];
+    if (r < 0 || r >= rows) {
+      if (v == 0) report_failure(st, SITE_SCATTER_INDEX, static_cast<unsigned>(j), static_cast<unsigned>(r));
+      continue;
+    }
+    reinterpret_cast<uint4*>(dst + r * dst_stride)[v] = reinterpret_cast<const uint4*>(src + j * d)[v];
   }
 }
 
@@ -926,23 +941,26 @@ CTB_API int ctb_active_rows(const float* w, int rows, int* block_counts, int* id
   return 0;
 }
 
-// dst[j, :] = src[idx[j], :] for j < n (bf16 rows of d elements, d % 8 == 0).
-CTB_API int ctb_gather_rows(const void* src, long src_stride, const int* idx, void* dst, long n, int d, void* stream) {
+// dst[j, :] = src[idx[j], :] for j < n (bf16 rows of d elements, d % 8 == 0; src has `rows` rows).
+CTB_API int ctb_gather_rows(const void* src, long src_stride, int rows, const int* idx, void* dst, long n, int d,
+                            void* stream) {
   if (d % 8 || src_stride % 8) return fail("gather_rows: rows must be whole 16-byte vectors");
   if (n <= 0) return 0;
   gather_rows_kernel<<<grid_for(n * (d / 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(src), src_stride, idx, static_cast<__nv_bfloat16*>(dst), n, d);
+      static_cast<const __nv_bfloat16*>(src), src_stride, idx, static_cast<__nv_bfloat16*>(dst), n, d, rows,
+      device_status());
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
 }
 
-// dst[idx[j], :] = src[j, :] for j < min(n, total[0]); rows of dst that no j names are left alone.
-CTB_API int ctb_scatter_rows(const void* src, const int* idx, const int* total, void* dst, long dst_stride, long n,
-                             int d, void* stream) {
+// dst[idx[j], :] = src[j, :] for j < min(n, total[0]); dst has `rows` rows, those no j names are left alone.
+CTB_API int ctb_scatter_rows(const void* src, const int* idx, const int* total, void* dst, long dst_stride, int rows,
+                             long n, int d, void* stream) {
   if (d % 8 || dst_stride % 8) return fail("scatter_rows: rows must be whole 16-byte vectors");
   if (n <= 0) return 0;
   scatter_rows_kernel<<<grid_for(n * (d / 8), 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-      static_cast<const __nv_bfloat16*>(src), idx, total, static_cast<__nv_bfloat16*>(dst), dst_stride, n, d);
+      static_cast<const __nv_bfloat16*>(src), idx, total, static_cast<__nv_bfloat16*>(dst), dst_stride, n, d, rows,
+      device_status());
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
 }

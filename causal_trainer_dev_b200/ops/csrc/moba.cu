@@ -519,8 +519,8 @@ __global__ void moba_desc_kernel(const int4* __restrict__ ginfo, const int* __re
 __global__ void moba_fill_kernel(const unsigned* __restrict__ sel, const int* __restrict__ seg,
                                  const int* __restrict__ doc_start, const int* __restrict__ rank,
                                  const int* __restrict__ row0, const int* __restrict__ hoff, int B, int S, int Hq,
-                                 int Hkv, int block, int words, int picks, int* __restrict__ row_of,
-                                 int* __restrict__ pos_of) {
+                                 int Hkv, int block, int words, int picks, int rows_cap, DeviceStatus* status,
+                                 int* __restrict__ row_of, int* __restrict__ pos_of) {
   const long idx = blockIdx.x * static_cast<long>(blockDim.x) + threadIdx.x;
   const long total = static_cast<long>(B) * Hq * S;
   if (idx >= total) return;
@@ -544,6 +544,13 @@ __global__ void moba_fill_kernel(const unsigned* __restrict__ sel, const int* __
         if (c >= cur) continue;
         const int g = (b * Hkv + hkv) * nt128 + ((st + c * block) >> 7);
         const int pos = row0[g] + hoff[g * gsize + hg] + rank[idx * picks + j];
+        if (pos < 0 || pos >= rows_cap) {
+          // cannot happen when the capacities match the routing; recorded instead of written out of bounds
+          report_failure(status, 0x0603u, static_cast<unsigned>(idx), static_cast<unsigned>(pos));
+          out[j] = -1;
+          ++j;
+          continue;
+        }
         out[j] = pos;
         row_of[pos] = (b * S + i) * Hq + h;
         ++j;
@@ -726,7 +733,7 @@ CTB_API int ctb_moba_group(const unsigned* sel, const int* seg, const int* doc_s
   CTB_CUDA_OK(cudaGetLastError());
   const long rows = static_cast<long>(B) * Hq * S;
   moba::moba_fill_kernel<<<static_cast<unsigned>((rows + 255) / 256), 256, 0, s>>>(
-      sel, seg, doc_start, rank, row0, hoff, B, S, Hq, Hkv, block, words, picks, row_of, pos_of);
+      sel, seg, doc_start, rank, row0, hoff, B, S, Hq, Hkv, block, words, picks, rows_cap, device_status(), row_of, pos_of);
   CTB_CUDA_OK(cudaGetLastError());
   return 0;
 }

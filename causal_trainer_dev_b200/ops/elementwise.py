@@ -270,8 +270,8 @@ def active_rows(weights: torch.Tensor, tile: int = 128) -> tuple[torch.Tensor, t
 def gather_rows(src: torch.Tensor, idx: torch.Tensor) -> torch.Tensor:
     """``src[idx]`` for a 2-D bf16 matrix with unit inner stride."""
     out = torch.empty((idx.numel(), src.shape[1]), dtype=src.dtype, device=src.device)
-    code = _lib.lib().ctb_gather_rows(_lib.ptr(src), _l(src.stride(0)), _lib.ptr(idx), _lib.ptr(out), _l(idx.numel()),
-                                      src.shape[1], _lib.stream_ptr())
+    code = _lib.lib().ctb_gather_rows(_lib.ptr(src), _l(src.stride(0)), src.shape[0], _lib.ptr(idx), _lib.ptr(out),
+                                      _l(idx.numel()), src.shape[1], _lib.stream_ptr())
     _lib.check(code, "ctb_gather_rows")
     return out
 
@@ -281,6 +281,6 @@ def scatter_rows(src: torch.Tensor, idx: torch.Tensor, total: torch.Tensor, rows
     ``[rows, d]`` result is zero."""
     out = torch.zeros((rows, src.shape[1]), dtype=src.dtype, device=src.device)
     code = _lib.lib().ctb_scatter_rows(_lib.ptr(src), _lib.ptr(idx), _lib.ptr(total), _lib.ptr(out), _l(out.stride(0)),
-                                       _l(idx.numel()), src.shape[1], _lib.stream_ptr())
+                                       rows, _l(idx.numel()), src.shape[1], _lib.stream_ptr())
     _lib.check(code, "ctb_scatter_rows")
     return out

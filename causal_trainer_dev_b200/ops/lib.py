@@ -97,6 +97,9 @@ _SITES = {
     0x0501: "tensor-parallel all-gather: a peer's rows never became ready",
     0x0502: "tensor-parallel reduce: a peer's partial tiles never arrived",
     0x0503: "vocabulary-parallel cross-entropy: a peer's statistics never arrived",
+    0x0601: "row gather: index outside the source (row skipped, zeros written)",
+    0x0602: "row scatter: index outside the destination (row skipped)",
+    0x0603: "MoBA grouping: gathered position outside the row space (pick dropped)",
     0x0801: "two-CTA gemm producer: stage never freed",
     0x0802: "two-CTA gemm mma: operands never arrived",
     0x0803: "two-CTA gemm mma: accumulator never drained",
@@ -112,7 +115,7 @@ def device_status(raise_on_error: bool = True) -> tuple[int, int, int, int]:
     code, block, d0, d1 = (int(x) for x in out)
     if code and raise_on_error:
         raise KernelError(
-            f"device wait ran out: {_SITES.get(code, hex(code))} (block {block}, detail {d0}, {d1})"
+            f"device check failed: {_SITES.get(code, hex(code))} (block {block}, detail {d0}, {d1})"
         )
     return code, block, d0, d1
 

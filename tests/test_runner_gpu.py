@@ -55,6 +55,25 @@ def test_cli_pallas_loss_backend_and_frozen_embeddings(cuda_lib, tmp_path):
     assert cuda_lib.device_status() == (0, 0, 0, 0)
 
 
+def test_cli_profiles_steps_with_cuda_events_and_honours_the_memory_flags(cuda_lib, tmp_path):
+    """``--profile_steps`` on a GPU (CUDA events, not the host clock), with every layer recomputed in
+    groups of two, the MLP tiled and the norm scales frozen."""
+    from causal_trainer_dev_b200.training import runner
+    from causal_trainer_dev_b200.training.arguments import parse_args
+
+    argv = _argv(tmp_path, "--max_steps", "5", "--profile_steps", "2", "--activation_memory", "recompute",
+                 "--mlp_chunk_size", "128", "--frozen_parameters", "norm")
+    run = runner.TrainingRun(parse_args(argv))
+    run.resolve_model(); run.load_data(); run.discover_resume(); run.build_model()
+    engine = run.step_fn.producer
+    assert engine.options.remat == "full" and engine.options.mlp_chunk_rows == 128 and not engine.options.train_norm
+    run.train()
+    assert engine.kept_layers == 0
+    profile = json.loads((tmp_path / "out" / "profile_steps.json").read_text())
+    assert profile["profiled_steps"] == 2 and profile["ms_per_step"] > 0 and "event" in profile["clock"].lower()
+    assert cuda_lib.device_status() == (0, 0, 0, 0)
+
+
 def test_cli_lora_runs_on_the_cuda_engine_and_writes_a_peft_adapter(cuda_lib, tmp_path):
     from causal_trainer_dev_b200.checkpointing import safetensors_io as st
     from causal_trainer_dev_b200.training import runner
