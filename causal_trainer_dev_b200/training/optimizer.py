@@ -84,6 +84,37 @@ class FlatAdamW:
         self.v = [torch.zeros_like(p) for p, _ in regions]
         self.count = 0
 
+    def attach_arenas(self, units: list, frozen: set[tuple[str, str]], region_of: dict[tuple[str, str], int]) -> None:
+        """Lets whole units be updated in ONE launch each (``ops.elementwise.adamw_regions``: 16-byte
+        accesses over the unit's flat buffer with a region table for decay / no decay / frozen),
+        instead of one launch per tensor.  ``units`` are flat bf16 CUDA parameter buffers with
+        segments; ``region_of[(unit, segment)]`` is the index of the segment's region.  The moments of
+        those regions become views into one flat buffer per unit, so checkpoints keep their layout."""
+        self.arenas = []
+        for u in units:
+            dev = u.data.device
+            m_flat, v_flat = torch.zeros_like(u.data), torch.zeros_like(u.data)
+            cuts, modes, covered = [0], [], []
+            for seg in u.layout.segments:                      # segments are ascending; gaps are alignment padding
+                if seg.offset > cuts[-1]:
+                    cuts.append(seg.offset)
+                    modes.append(-1)
+                key = (u.layout.name, seg.name)
+                cuts.append(seg.offset + seg.numel)
+                modes.append(-1 if key in frozen else (1 if seg.decay else 0))
+                if key in region_of:
+                    i = region_of[key]
+                    sl = slice(seg.offset, seg.offset + seg.numel)
+                    self.m[i], self.v[i] = m_flat[sl], v_flat[sl]
+                    covered.append(i)
+            if cuts[-1] < u.data.numel():
+                cuts.append(u.data.numel())
+                modes.append(-1)
+            self.arenas.append(dict(unit=u, m=m_flat, v=v_flat, regions=covered,
+                                    bounds=torch.tensor(cuts, dtype=torch.int64, device=dev),
+                                    modes=torch.tensor(modes, dtype=torch.int32, device=dev)))
+        self._in_arena = {i for a in self.arenas for i in a["regions"]}
+
     def state_tensors(self) -> list[torch.Tensor]:
         return [t for pair in zip(self.m, self.v) for t in pair]
 
@@ -100,17 +131,39 @@ class FlatAdamW:
 
     def update(self, grads: list[torch.Tensor], lr: float, grad_norm: torch.Tensor | None = None) -> torch.Tensor:
         c = self.cfg
+        arenas = getattr(self, "arenas", None)
+        # whole-unit path: usable when every unit's gradient is one flat buffer of matching size
+        by_unit = arenas is not None and all(a["unit"].grad is not None and a["unit"].grad.is_cuda
+                                             and a["unit"].grad.numel() == a["unit"].data.numel() for a in arenas)
+        skip = self._in_arena if by_unit else set()
         # fp32 accumulators feeding bf16 parameters: the cast to the parameter dtype happens
         # inside the kernels (norm and update both see the rounded value).
         rounding = [g.dtype == torch.float32 and p.dtype == torch.bfloat16 for (p, _), g in zip(self.regions, grads)]
         if grad_norm is None:
-            grad_norm = self.global_norm(grads, round_bf16=any(rounding))
+            rest = [g for i, g in enumerate(grads) if i not in skip]
+            total = self.global_norm(rest, round_bf16=any(rounding)).pow(2) if rest else None
+            if by_unit:
+                # frozen segments and alignment gaps hold zeros, so a unit's sum is that of its trained tensors
+                for a in arenas:
+                    g = a["unit"].grad
+                    sq = ew.sum_of_squares(g, round_bf16=g.dtype == torch.float32)
+                    total = sq if total is None else total + sq
+            grad_norm = torch.sqrt(total)
         clip = torch.ones_like(grad_norm)
         if c.max_grad_norm > 0:
             clip = torch.clamp(c.max_grad_norm / torch.clamp(grad_norm, min=1e-16), max=1.0)
             clip = torch.where(torch.isfinite(grad_norm), clip, torch.ones_like(clip))
         self.count += 1
-        for (p, decay), g, m, v in zip(self.regions, grads, self.m, self.v):
+        if by_unit:
+            with torch.no_grad():
+                for a in arenas:
+                    u = a["unit"]
+                    ew.adamw_regions(u.data, u.grad, a["m"], a["v"], a["bounds"], a["modes"], lr=lr, b1=c.beta1, b2=c.beta2,
+                                     eps=c.epsilon, decay=c.weight_decay, step=self.count, clip=clip.float().reshape(1),
+                                     round_bf16=u.grad.dtype == torch.float32)
+        for i, ((p, decay), g, m, v) in enumerate(zip(self.regions, grads, self.m, self.v)):
+            if i in skip:
+                continue
             kw = dict(lr=lr, b1=c.beta1, b2=c.beta2, eps=c.epsilon, decay=c.weight_decay if decay else 0.0,
                       step=self.count)
             with torch.no_grad():

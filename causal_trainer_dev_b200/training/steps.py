@@ -125,18 +125,26 @@ class TrainStep:
         from ..models.freezing import frozen_segments
 
         frozen_segs = frozen_segments(self.params.config, tuple(self.frozen)) if self.train_base else set()
+        region_of: dict[tuple[str, str], int] = {}
         if self.train_base:
             for name, u in self.params.units.items():
                 for seg in u.layout.segments:
                     if (name, seg.name) in frozen_segs:
                         continue
                     sl = slice(seg.offset, seg.offset + seg.numel)
+                    region_of[(name, seg.name)] = len(self._regions)
                     self._regions.append((u.data.detach()[sl], seg.decay))
                     self._grad_of.append(lambda u=u, sl=sl: u.grad[sl])
         for p, decay, g in self.extra_regions:
             self._regions.append((p, decay))
             self._grad_of.append(g)
         self.optimizer = FlatAdamW(self._regions, self.adamw)
+        units = list(self.params.units.values()) if self.train_base else []
+        from_engine = hasattr(self.producer, "provider")     # the CUDA engine leaves untrained segments' gradients at zero
+        if units and from_engine and self.dp_group is None and all(
+                u.data.is_cuda and u.data.dtype == torch.bfloat16 for u in units):
+            # single-replica bf16 training on a GPU: one AdamW launch per unit instead of one per tensor
+            self.optimizer.attach_arenas(units, frozen_segs, region_of)
 
     @property
     def optimizer_step(self) -> int:

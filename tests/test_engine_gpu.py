@@ -75,6 +75,38 @@ def test_engine_training_reduces_loss(cuda_lib):
     assert abs(first["loss"] - 8.3178) < 0.1  # ln(4096)
     assert last["loss"] < first["loss"] - 1.0
     assert engine.launches > 0
+    # one AdamW launch per unit; the per-tensor moments are views into the units' flat moment buffers
+    arenas = step.optimizer.arenas
+    assert len(arenas) == len(params.units)
+    assert all(m.data_ptr() >= a["m"].data_ptr() for a in arenas for m in (step.optimizer.m[i] for i in a["regions"]))
+    assert float(sum(a["m"].float().abs().sum() for a in arenas)) > 0
+
+
+def test_unit_wide_adamw_matches_the_per_tensor_update(cuda_lib):
+    """The same three steps with one AdamW launch per unit and with one per tensor."""
+    from causal_trainer_dev_b200.models.config import preset
+    from causal_trainer_dev_b200.models.params import ModelParams
+    from causal_trainer_dev_b200.training.engine import LayerwiseEngine, LocalProvider
+    from causal_trainer_dev_b200.training.optimizer import AdamWConfig, ScheduleConfig
+    from causal_trainer_dev_b200.training.steps import TrainStep
+
+    cfg = preset("tiny", vocab_size=4096)
+    batch = _batch(cfg, 2, 256)
+    results = []
+    for whole_units in (True, False):
+        params = ModelParams.init_random(cfg, seed=0, dtype=torch.bfloat16).to("cuda")
+        engine = LayerwiseEngine(cfg, LocalProvider(params, torch.bfloat16))
+        step = TrainStep(params, engine, AdamWConfig(weight_decay=0.1), ScheduleConfig(1e-3, 0.0, "constant", 0, 10),
+                         frozen=("norm",))
+        if not whole_units:
+            step.optimizer.arenas = None
+        history = [step.run([batch]).to_floats() for _ in range(3)]
+        results.append((history, params))
+    (ha, pa), (hb, pb) = results
+    for x, y in zip(ha, hb):
+        assert abs(x["loss"] - y["loss"]) < 2e-3 and abs(x["grad_norm"] - y["grad_norm"]) < 2e-3 * y["grad_norm"]
+    for name in pa.hf_names():
+        assert _rel(pa.tensor(name), pb.tensor(name)) < 2e-3, name
 
 
 def test_engine_with_moba_layers_matches_oracle(cuda_lib):
