@@ -43,8 +43,10 @@ def parse() -> argparse.Namespace:
     p.add_argument("--config", default="llama8b-pretrain",
                    help="named benchmark configuration (causal_trainer_dev_b200/benchmarks/configs.py); the default is "
                         "the headline: Llama-3-8B shape, seq 4096, 32 rows, FSDP")
-    p.add_argument("--attention", choices=("auto", "dense"), default="auto",
-                   help="dense: run a MoBA configuration with dense segment-masked attention instead (comparison)")
+    p.add_argument("--attention", choices=("auto", "dense", "sparse"), default="auto",
+                   help="for MoBA configurations.  auto: block-sparse passes, except on batches whose every document has at "
+                        "most top_k blocks (nothing to drop: the dense kernel computes the same function); sparse: always "
+                        "the block-sparse passes; dense: dense segment-masked attention (comparison)")
     p.add_argument("--layers", type=int, default=0, help="override the layer count (debugging only; invalid as a result)")
     p.add_argument("--seq-len", type=int, default=0, help="override the configuration's sequence length")
     p.add_argument("--global-batch", type=int, default=0, help="override the configuration's global batch (rows)")
@@ -174,7 +176,7 @@ def main() -> None:
     rows_per_rank = global_batch // data_world
     micro = min(args.micro_batch or bc.micro_batch, rows_per_rank)
     attention_options = None
-    if bc.moba is not None and args.attention == "auto":
+    if bc.moba is not None and args.attention != "dense":
         from causal_trainer_dev_b200.models.moba import AttentionOptions
 
         attention_options = AttentionOptions(method="moba", moba_block_size=bc.moba[0], moba_top_k=bc.moba[1])
@@ -185,6 +187,7 @@ def main() -> None:
                                 total_steps=1000),
         fused_collectives=(args.impl == "ours"), remat=args.remat, tp=tp,
         force_sharded_runtime=args.force_sharded_runtime, attention_options=attention_options,
+        moba_dense_shortcut=args.attention != "sparse",
     )
     if args.impl == "torch":
         from causal_trainer_dev_b200.benchmarks.torch_baseline import TorchBaseline
@@ -214,6 +217,16 @@ def main() -> None:
             mine = trainer.local_rows(data)
         pool.append(mine)
     tokens_per_step = global_batch * seq_len
+    moba_note = None
+    if attention_options is not None:
+        from causal_trainer_dev_b200.data.batching import longest_document
+
+        longest = max(longest_document(bc.make_rows(cfg, global_batch, seq_len, seed)["segment_ids"]) for seed in (11, 12))
+        dense_equal = longest <= bc.moba[0] * bc.moba[1]
+        moba_note = "MoBA block %d top_k %d (grouped by key block)" % bc.moba + (
+            f"; longest document {longest} tokens" + (
+                " <= top_k blocks, so nothing can be dropped and the dense kernel runs (same function)"
+                if dense_equal and args.attention == "auto" else ""))
 
     def sync() -> None:
         if world > 1:
@@ -286,8 +299,7 @@ def main() -> None:
                 "global_batch": global_batch, "seq_len": seq_len,
                 "parallelism": f"fsdp{data_world}" + (f"xtp{tp}" if tp > 1 else ""),
                 "attention": (getattr(trainer, "attention", None) or (
-                    "MoBA block %d top_k %d (grouped)" % bc.moba if attention_options is not None
-                    else "dense, segment-isolated flash attention")),
+                    moba_note if attention_options is not None else "dense, segment-isolated flash attention")),
                 "micro_batch_rows": micro,
                 "grad_accumulation": rows_per_rank // micro, "loss": "cut cross-entropy" if ours else "F.cross_entropy on 4096-row logit chunks",
                 "remat": (f"auto: activations of {trainer.engine.kept_layers}/{cfg.num_hidden_layers} layers kept in "

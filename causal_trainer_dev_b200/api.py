@@ -41,6 +41,7 @@ class TrainerConfig:
     frozen: tuple[str, ...] = ()       # components held fixed: any of "lm_head", "embed", "norm"
     loss_backend: str = "cut"          # "cut": projection-fused; "logits": bf16 logits slab per row chunk
     attention_options: object | None = None   # models.moba.AttentionOptions for MoBA layers
+    moba_dense_shortcut: bool = True   # rows whose documents all fit in top_k blocks run the (identical) dense kernel
 
 
 class Trainer:
@@ -121,7 +122,8 @@ class Trainer:
         c = self.cfg
         return EngineOptions(cut_chunk_rows=c.cut_chunk_rows, remat=c.remat, train_lm_head="lm_head" not in c.frozen,
                              train_embed="embed" not in c.frozen, train_norm="norm" not in c.frozen,
-                             loss_backend=c.loss_backend, attention_options=c.attention_options)
+                             loss_backend=c.loss_backend, attention_options=c.attention_options,
+                             moba_dense_shortcut=c.moba_dense_shortcut)
 
     def _init_params(self) -> ModelParams:
         if self.cfg.init == "hf":
@@ -165,6 +167,12 @@ class Trainer:
                 continue
             self._bytes_h2d += v.numel() * v.element_size()
             out[k] = v.to(self.device, non_blocking=True)
+        if self.cfg.attention_options is not None and "segment_ids" in host_batch:
+            # a host-side fact about the rows (no device read): lets a MoBA layer whose selection
+            # cannot leave anything out run as the dense kernel it is equal to
+            from .data.batching import longest_document
+
+            out["longest_document"] = longest_document(host_batch["segment_ids"].numpy())
         return out
 
     def split_micro_batches(self, batch: dict[str, torch.Tensor]) -> list[dict[str, torch.Tensor]]:
@@ -172,7 +180,8 @@ class Trainer:
         mb = min(self.cfg.micro_batch_rows, rows)
         if rows % mb:
             raise ValueError(f"{rows} local rows are not a multiple of micro_batch_rows={mb}")
-        return [{k: v[i:i + mb] for k, v in batch.items()} for i in range(0, rows, mb)]
+        return [{k: (v[i:i + mb] if isinstance(v, torch.Tensor) else v) for k, v in batch.items()}
+                for i in range(0, rows, mb)]
 
     # ------------------------------------------------------------------ steps
     def train_step_device(self, device_batch: dict[str, torch.Tensor]):

@@ -7,6 +7,8 @@
 * ``llama8b-moba32k-fsdp2tp4``  Llama-3-8B shape, rows of 32768 tokens from 4 documents, MoBA block
                                 4096 / top-3 + current, FSDP x TP 4 (``--attention dense`` for the
                                 dense segment-masked comparison on the same rows)
+* ``llama8b-moba32k-one-document`` / ``llama8b-moba128k-one-document``  the same model and MoBA settings on
+                                rows that are one document (8 / 32 blocks: the router has something to drop)
 * ``qwen1.5b-maskgit-fsdp8``    1.5B shape with image codes, seq 4096, mixed AR + MaskGIT, FSDP
 
 The tensor-parallel degree is capped by the number of GPUs the run has (tp = min(named tp, N)), so
@@ -58,6 +60,11 @@ def _long(cfg, rows, seq, seed):
                                         eos_token_id=_eos(cfg), pad_token_id=cfg.pad_token_id, seed=seed)
 
 
+def _one_document(cfg, rows, seq, seed):
+    return synthetic.long_document_rows(rows, seq, cfg.vocab_size, docs_per_row=1, min_len=seq, max_len=seq,
+                                        eos_token_id=_eos(cfg), pad_token_id=cfg.pad_token_id, seed=seed)
+
+
 def _maskgit(cfg, rows, seq, seed):
     return synthetic.maskgit_rows(rows, seq, text_vocab=151000, code_base=151936, num_codes=16384,
                                   mask_id=151936 + 16384, im_start=151644, im_end=151645, newline_id=198,
@@ -72,6 +79,12 @@ CONFIGS: dict[str, BenchConfig] = {c.name: c for c in (
     BenchConfig("llama8b-moba32k-fsdp2tp4", "tokens/s Llama-3-8B-shape 32768-token rows MoBA block4096 top3+current "
                 "FSDPxTP4 bf16", "llama3-8b", 32768, 2, 1, 4, _long, moba=(4096, 4),
                 data="rows of 32768 tokens packed from 4 documents of 4096-12288 tokens"),
+    BenchConfig("llama8b-moba32k-one-document", "tokens/s Llama-3-8B-shape 32768-token single-document rows MoBA "
+                "block4096 top3+current FSDPxTP4 bf16", "llama3-8b", 32768, 2, 1, 4, _one_document, moba=(4096, 4),
+                data="rows of one 32768-token document each"),
+    BenchConfig("llama8b-moba128k-one-document", "tokens/s Llama-3-8B-shape 131072-token single-document rows MoBA "
+                "block4096 top3+current FSDPxTP4 bf16", "llama3-8b", 131072, 2, 1, 4, _one_document, moba=(4096, 4),
+                data="rows of one 131072-token document each"),
     BenchConfig("qwen1.5b-maskgit-fsdp8", "tokens/s 1.5B-shape seq4096 mixed AR+MaskGIT FSDP bf16", "qwen2.5-1.5b-image",
                 4096, 64, 8, 1, _maskgit, data="conversations with 1-2 image-code grids (16x16 / 32x32) per assistant "
                 "turn, maskgit_probability 0.5, cosine mask ratio"),

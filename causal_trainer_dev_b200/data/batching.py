@@ -166,6 +166,21 @@ def attention_cost_per_row(segment_ids: np.ndarray, attention_end: np.ndarray | 
     return np.where(seg != 0, lim - start + 1, 0).sum(axis=1).astype(np.float64)
 
 
+def longest_document(segment_ids: np.ndarray) -> int:
+    """Tokens of the longest run of one non-zero segment id in any row: the longest document the
+    rows hold.  A block-sparse attention whose every document has no more blocks than a query may
+    select is exactly dense attention, which the engine then runs without the routing passes."""
+    seg = np.asarray(segment_ids)
+    if seg.size == 0:
+        return 0
+    rows, s = seg.shape
+    idx = np.arange(s)[None, :]
+    first = np.ones((rows, s), dtype=bool)
+    first[:, 1:] = seg[:, 1:] != seg[:, :-1]
+    start = np.maximum.accumulate(np.where(first, idx, 0), axis=1)
+    return int(np.where(seg != 0, idx - start + 1, 0).max())
+
+
 def balanced_row_assignment(costs: np.ndarray, ranks: int) -> np.ndarray:
     """``[ranks, rows / ranks]`` row indices: every rank gets the same number of rows and, as nearly
     as a greedy pass can make it, the same total cost (largest rows first, each to the least loaded

@@ -83,6 +83,8 @@ class EngineOptions:
                                              # intermediate is never held whole (rebuilt per tile in backward)
     moba_implementation: str = "grouped"     # "grouped": rows gathered by selected block, cost ~ top_k * block;
                                              # "lists": one masked flash pass over the union of a tile's selections
+    moba_dense_shortcut: bool = True         # batches whose longest document has at most top_k blocks (a host-side
+                                             # fact the batch carries) run the dense kernel: the same function
 
 
 class LayerwiseEngine:
@@ -175,15 +177,18 @@ class LayerwiseEngine:
         self._count(2)
 
     # ------------------------------------------------------------------ attention (dense or MoBA)
-    def _uses_moba(self, li: int, seq: int) -> bool:
+    def _uses_moba(self, li: int, seq: int, longest: int | None = None) -> bool:
         ao = self.options.attention_options
         if ao is None or not ao.applies_to_layer(li, self.cfg.num_hidden_layers, self.options.optimizer_step):
             return False
-        return ao.moba_top_k * min(ao.moba_block_size, seq) < seq     # otherwise the graph is exactly dense
+        # a document of at most top_k blocks leaves the router nothing to drop (blocks are counted from
+        # the document's first token, and the current block is one of the top_k): exactly dense
+        span = seq if longest is None or not self.options.moba_dense_shortcut else min(seq, max(int(longest), 1))
+        return ao.moba_top_k * min(ao.moba_block_size, seq) < span
 
     def _attention_forward(self, q, k, v, ctx: dict, li: int):
         """Returns (O, LSE, routing); routing is None for dense layers."""
-        if not self._uses_moba(li, ctx["seq"]):
+        if not self._uses_moba(li, ctx["seq"], ctx.get("longest")):
             o, lse = attn_ops.flash_attention_forward(q, k, v, ctx["meta"])
             return o, lse, None
         from ..ops import moba as moba_ops
@@ -360,7 +365,8 @@ class LayerwiseEngine:
             self._inv_freq = ew.inverse_frequencies(cfg.rotary_dim, cfg.rope_theta, device=ids.device)
         cos, sin = ew.rope_table(pos, self._inv_freq)
         self._count(1)   # segments, positions and block summaries: one launch per micro-batch
-        return dict(batch=ids.shape[0], seq=ids.shape[1], cos=cos, sin=sin, meta=meta, seg=seg)
+        return dict(batch=ids.shape[0], seq=ids.shape[1], cos=cos, sin=sin, meta=meta, seg=seg,
+                    longest=batch.get("longest_document"))
 
     # ------------------------------------------------------------------ forward only
     @torch.no_grad()

@@ -724,8 +724,10 @@ class TrainingRun:
                     t = t.pin_memory().to(self.device, non_blocking=True)
                 rows[k] = t
             sub = a.micro_batch_rows or per_micro
+            longest = batching.longest_document(split["segment_ids"][g][keep])
             for r0 in range(0, per_micro, sub):
                 micro.append({k: v[r0:r0 + sub] for k, v in rows.items()})
+                micro[-1]["longest_document"] = longest      # host-side hint for block-sparse layers
         return micro
 
     def check_device_waits(self) -> None:

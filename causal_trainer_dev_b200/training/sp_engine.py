@@ -74,7 +74,7 @@ class SequenceParallelAttention:
         ctx.update(seq=n, seq_full=s, q_off=lo)
         return ctx
 
-    def _uses_moba(self, li: int, seq: int) -> bool:
+    def _uses_moba(self, li: int, seq: int, longest: int | None = None) -> bool:
         return False
 
     # ------------------------------------------------------------------ K / V of one row over sp

@@ -75,3 +75,28 @@ def test_rows_are_dealt_to_ranks_by_attention_cost():
         assert np.array_equal(rows, balanced_row_assignment(cost, ranks))         # deterministic
     with pytest.raises(ValueError, match="evenly"):
         balanced_row_assignment(cost[:30], 4)
+
+
+def test_longest_document_and_the_dense_shortcut_of_block_sparse_layers():
+    from causal_trainer_dev_b200.data.batching import longest_document
+    from causal_trainer_dev_b200.models.config import ModelConfig
+    from causal_trainer_dev_b200.models.moba import AttentionOptions
+    from causal_trainer_dev_b200.training.engine import EngineOptions, LayerwiseEngine
+
+    seg = np.array([[1, 1, 1, 2, 2, 0, 0, 0],
+                    [1, 2, 2, 2, 2, 2, 1, 0]], dtype=np.int32)
+    assert longest_document(seg) == 5
+    assert longest_document(np.zeros((2, 8), dtype=np.int32)) == 0
+    assert longest_document(np.zeros((0, 8), dtype=np.int32)) == 0
+
+    cfg = ModelConfig(vocab_size=64, hidden_size=64, intermediate_size=128, num_hidden_layers=2, num_attention_heads=1,
+                      num_key_value_heads=1, head_dim=64)
+    ao = AttentionOptions(method="moba", moba_block_size=128, moba_top_k=2)
+    engine = LayerwiseEngine.__new__(LayerwiseEngine)        # only the dispatch rule is exercised
+    engine.cfg, engine.options = cfg, EngineOptions(attention_options=ao)
+    assert engine._uses_moba(0, 1024)                        # 8 blocks, a query keeps 2
+    assert engine._uses_moba(0, 1024, longest=257)           # a document of 3 blocks
+    assert not engine._uses_moba(0, 1024, longest=256)       # 2 blocks: nothing can be dropped
+    assert not engine._uses_moba(0, 256)
+    engine.options = EngineOptions(attention_options=ao, moba_dense_shortcut=False)
+    assert engine._uses_moba(0, 1024, longest=256)

@@ -61,9 +61,11 @@ def test_named_configurations_generate_rows_of_the_named_shape():
     from causal_trainer_dev_b200.benchmarks import configs
 
     assert set(configs.CONFIGS) == {"llama8b-pretrain", "qwen7b-sft-fsdp4tp2", "llama8b-moba32k-fsdp2tp4",
-                                    "qwen1.5b-maskgit-fsdp8"}
+                                    "qwen1.5b-maskgit-fsdp8", "llama8b-moba32k-one-document",
+                                    "llama8b-moba128k-one-document"}
     for name, rows, seq in (("llama8b-pretrain", 2, 1024), ("qwen7b-sft-fsdp4tp2", 2, 1024),
-                            ("llama8b-moba32k-fsdp2tp4", 1, 4096), ("qwen1.5b-maskgit-fsdp8", 2, 4096)):
+                            ("llama8b-moba32k-fsdp2tp4", 1, 4096), ("qwen1.5b-maskgit-fsdp8", 2, 4096),
+                            ("llama8b-moba32k-one-document", 1, 4096)):
         bc = configs.CONFIGS[name]
         cfg = configs.model_of(bc)
         data = bc.make_rows(cfg, rows, seq, 3)
@@ -74,6 +76,8 @@ def test_named_configurations_generate_rows_of_the_named_shape():
             assert 0 < data["loss_weights"].mean() < 0.8              # assistant spans only
         if name == "llama8b-moba32k-fsdp2tp4":
             assert sorted(set(data["segment_ids"][0].tolist())) == [1, 2, 3, 4]
+        if name == "llama8b-moba32k-one-document":
+            assert set(data["segment_ids"][0].tolist()) == {1}
         if name == "qwen1.5b-maskgit-fsdp8":
             mask_id = 151936 + 16384
             masked = data["input_ids"] == mask_id
