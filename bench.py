@@ -56,6 +56,8 @@ def parse() -> argparse.Namespace:
                    help="diagnostic: run the FSDP runtime on one GPU to measure its overhead without communication")
     p.add_argument("--tp", type=int, default=0, help="tensor-parallel degree inside the N GPUs (the rest is FSDP); "
                                                      "0: what the configuration names, capped by N")
+    p.add_argument("--sp", type=int, default=1, help="sequence-parallel degree (queries sharded over sp ranks, K/V gathered; "
+                                                     "the sp ranks are also FSDP ranks); not with MoBA layers")
     return p.parse_args()
 
 
@@ -169,10 +171,11 @@ def main() -> None:
     seq_len = args.seq_len or bc.seq_len
     global_batch = args.global_batch or bc.global_batch
     tp = args.tp or min(bc.tp, world)
-    if world % tp or global_batch % (world // tp):
-        raise SystemExit("--tp must divide the GPUs, and the data ranks the global batch")
-    data_world = world // tp
-    data_rank = rank // tp
+    sp = max(1, args.sp)
+    if world % (tp * sp) or global_batch % (world // (tp * sp)):
+        raise SystemExit("--tp x --sp must divide the GPUs, and the data ranks the global batch")
+    data_world = world // (tp * sp)
+    data_rank = rank // (tp * sp)
     rows_per_rank = global_batch // data_world
     micro = min(args.micro_batch or bc.micro_batch, rows_per_rank)
     attention_options = None
@@ -185,14 +188,14 @@ def main() -> None:
         adamw=AdamWConfig(weight_decay=0.1, max_grad_norm=1.0),
         schedule=ScheduleConfig(learning_rate=2e-5, learning_rate_end=2e-6, scheduler="cosine", warmup_steps=2,
                                 total_steps=1000),
-        fused_collectives=(args.impl == "ours"), remat=args.remat, tp=tp,
+        fused_collectives=(args.impl == "ours"), remat=args.remat, tp=tp, sp=sp,
         force_sharded_runtime=args.force_sharded_runtime, attention_options=attention_options,
         moba_dense_shortcut=args.attention != "sparse",
     )
     if args.impl == "torch":
         from causal_trainer_dev_b200.benchmarks.torch_baseline import TorchBaseline
 
-        if tp > 1 or bc.moba is not None or args.config == "qwen1.5b-maskgit-fsdp8":
+        if tp > 1 or sp > 1 or bc.moba is not None or args.config == "qwen1.5b-maskgit-fsdp8":
             print(json.dumps({"impl": "torch", "config": args.config, "unavailable": "the stock-PyTorch arm covers "
                               "FSDP-only next-token configurations (no tensor parallelism, MoBA or MaskGIT masks)"}))
             return
@@ -297,7 +300,7 @@ def main() -> None:
             "config": {
                 "name": bc.name, "model": bc.model + (f"-{args.layers}layers" if args.layers else ""),
                 "global_batch": global_batch, "seq_len": seq_len,
-                "parallelism": f"fsdp{data_world}" + (f"xtp{tp}" if tp > 1 else ""),
+                "parallelism": f"fsdp{data_world}" + (f"xtp{tp}" if tp > 1 else "") + (f"xsp{sp}" if sp > 1 else ""),
                 "attention": (getattr(trainer, "attention", None) or (
                     moba_note if attention_options is not None else "dense, segment-isolated flash attention")),
                 "micro_batch_rows": micro,
