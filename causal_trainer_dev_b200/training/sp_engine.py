@@ -11,7 +11,9 @@ MLP, the loss -- runs on the local slice unchanged; only attention communicates:
   memory that publishes one flag per chunk (``parallel.tp.TpContext``, the same machinery as the
   tensor-parallel activation gather); the flash kernel runs the local query range against all keys
   and its producer warp acquires the flags of each key tile before loading it, so the transfer
-  overlaps the attention over the keys that are already there (all-gather -> attention);
+  overlaps the attention over the keys that are already there (all-gather -> attention).  That
+  in-kernel wait is used when the forward grid leaves SMs free for the pull kernel's CTAs; larger
+  grids wait for the gather on the stream instead (``_flags_are_safe``);
 * backward: K / V are gathered again (nothing of size ``S`` is kept between the passes), the dQ
   kernel runs on the local queries and the dK/dV kernel on all keys, writing this rank's partial
   sums into a symmetric buffer; every rank then sums its own key slice from all peers' partials with
@@ -31,7 +33,7 @@ import torch.distributed as dist
 
 from ..models.config import ModelConfig
 from ..ops import attention as attn_ops
-from ..parallel.tp import TpContext
+from ..parallel.tp import PULL_CTAS, TpContext
 from .engine import EngineOptions, LayerwiseEngine
 
 
@@ -105,6 +107,19 @@ class SequenceParallelAttention:
         return g, full[:, :kvw].view(1, s, hkv, d), full[:, kvw:].view(1, s, hkv, d)
 
     # ------------------------------------------------------------------ attention
+    def _flags_are_safe(self, heads: int, queries: int, device) -> bool:
+        """Whether the forward kernel may wait for the gather's chunk flags itself.
+
+        A kernel that waits for another launch on the same GPU is only safe when both are certain to
+        be resident together.  A forward CTA takes a whole SM (its registers), so that holds when
+        the grid leaves enough SMs free for every pull CTA (four fit on one SM); a larger grid could
+        fill the GPU with waiting CTAs before the pull kernel is scheduled, and the bounded waits
+        would then expire.  Large grids therefore take the stream-level dependency: their attention
+        runs for many times the half millisecond the gather takes, so little overlap is lost."""
+        sms = torch.cuda.get_device_properties(device).multi_processor_count
+        ctas = heads * ((queries + 255) // 256)                  # the forward grid of one row
+        return ctas <= sms - (PULL_CTAS + 3) // 4
+
     def _attention_forward(self, q, k, v, ctx, li):
         b, n, hkv, d = k.shape
         s = ctx["seq_full"]
@@ -113,7 +128,7 @@ class SequenceParallelAttention:
         lse = torch.empty((b, q.shape[2], n), dtype=torch.float32, device=q.device)
         for row in range(b):
             g, k_full, v_full = self._gather_row(kv, k, v, row)
-            flags = kv.gathered_flags(g)
+            flags = kv.gathered_flags(g) if self._flags_are_safe(q.shape[2], n, q.device) else None
             if flags is None:
                 kv.wait_gathered(g)
             o_row, lse_row = attn_ops.flash_attention_forward(

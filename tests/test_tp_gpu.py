@@ -96,3 +96,19 @@ def test_sequence_times_tensor_parallel_matches_fsdp4(cuda_lib, tmp_path):
     fsdp = _launch(["train", "1", "fused", "3", "2", "1"], 4, tmp_path / "fsdp4b.json", 29643)
     assert mixed["status"] == [0, 0, 0, 0]
     _close(mixed["history"], fsdp["history"], 2e-2, 3e-2)
+
+
+def test_in_kernel_kv_flag_waits_only_when_the_pull_kernel_is_certain_to_be_resident(cuda_lib):
+    """The attention forward kernel may spin on the gather's flags only if its grid leaves SMs for
+    the pull kernel; larger grids must take the stream-level dependency (no device wait at all)."""
+    from causal_trainer_dev_b200.parallel.tp import PULL_CTAS
+    from causal_trainer_dev_b200.training.sp_engine import SequenceParallelAttention
+
+    sp = SequenceParallelAttention()
+    dev = torch.device("cuda", 0)
+    sms = torch.cuda.get_device_properties(dev).multi_processor_count
+    free = sms - (PULL_CTAS + 3) // 4
+    assert sp._flags_are_safe(4, 256, dev)                      # 4 CTAs
+    assert sp._flags_are_safe(free, 256, dev)
+    assert not sp._flags_are_safe(free + 1, 256, dev)
+    assert not sp._flags_are_safe(32, 32768, dev)               # 32 heads x 128 query pairs: many waves
