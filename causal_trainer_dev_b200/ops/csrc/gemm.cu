@@ -28,6 +28,10 @@
 #include <algorithm>
 #include <cstdlib>
 
+#ifndef CTB_TAIL_SPLIT_DEFAULT
+#define CTB_TAIL_SPLIT_DEFAULT 0
+#endif
+
 namespace ctb {
 namespace gemm {
 
@@ -85,6 +89,41 @@ struct TileCoord {
 // slowly so the B tile stays hot in L2.  `n_rotate` shifts the column order so that a rank
 // starts on the weight rows it already owns while the all-gather pull brings the rest.
 // `m_rotate` does the same for row tiles when the A operand is being gathered.
+// A work unit is a whole output tile, or one K slice of a tile whose slices reduce-add into C.
+//   split_k > 1   every tile is cut into split_k slices (unit = slice * tiles + tile);
+//   tail_splits   only the tiles [tail_first, tiles) -- the ones a last, mostly empty wave of CTAs
+//                 would compute -- are cut, into tail_splits slices each, so that the last wave
+//                 is as full as the others and only those few tiles pay reduce traffic.
+struct UnitMap {
+  int tile;      // output tile index
+  int kb0, kb1;  // k-block range of this unit
+  bool reduce;   // the unit adds into C instead of storing
+};
+__device__ __forceinline__ UnitMap map_unit(int unit, int total, int num_k, int splits, int k_per, int tail_first,
+                                            int tail_splits, int tail_k_per) {
+  UnitMap u;
+  if (tail_splits > 1) {
+    if (unit < tail_first) {
+      u.tile = unit;
+      u.kb0 = 0;
+      u.kb1 = num_k;
+      u.reduce = false;
+    } else {
+      const int v = unit - tail_first;
+      u.tile = tail_first + v / tail_splits;
+      u.kb0 = (v % tail_splits) * tail_k_per;
+      u.kb1 = min(num_k, u.kb0 + tail_k_per);
+      u.reduce = true;
+    }
+  } else {
+    u.tile = unit % total;
+    u.kb0 = (unit / total) * k_per;
+    u.kb1 = min(num_k, u.kb0 + k_per);
+    u.reduce = splits > 1;
+  }
+  return u;
+}
+
 template <int TM>
 __device__ __forceinline__ TileCoord tile_coord(int tile, int num_m, int num_n, int n_rotate, int m_rotate) {
   constexpr int GROUP_M = Cfg<TM>::GROUP_M;
@@ -151,7 +190,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
   // TMA reduce, so a problem with few output tiles still fills all SMs in whole waves.
   const int splits = args.split_k > 1 ? args.split_k : 1;
   const int k_per = (num_k + splits - 1) / splits;
-  const int units = total * splits;
+  const int tail_splits = (splits == 1 && args.tail_splits > 1) ? args.tail_splits : 1;
+  const int tail_first = tail_splits > 1 ? args.tail_first : total;
+  const int tail_k_per = (num_k + tail_splits - 1) / tail_splits;
+  const int units = tail_splits > 1 ? tail_first + (total - tail_first) * tail_splits : total * splits;
   const int m_rot = args.m_rotate / TM < num_m ? args.m_rotate / TM : 0;   // given in 128-row units
   DeviceStatus* st = args.status;
 
@@ -247,9 +289,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         ok = (tile == -1);
         break;
       }
-      const int kb0 = (tile / total) * k_per;
-      const int kb1 = min(num_k, kb0 + k_per);
-      const TileCoord tc = tile_coord<TM>(tile % total, num_m, num_n, args.n_rotate, m_rot);
+      const UnitMap um = map_unit(tile, total, num_k, splits, k_per, tail_first, tail_splits, tail_k_per);
+      const int kb0 = um.kb0, kb1 = um.kb1;
+      const TileCoord tc = tile_coord<TM>(um.tile, num_m, num_n, args.n_rotate, m_rot);
       if (args.b_flags != nullptr && !b_all_seen) {
         // The elements of B this tile reads must have landed in this GPU's memory.  A
         // K-major B tile is rows [n0, n0+BN) of the weight; an MN-major B (dgrad) strides
@@ -364,8 +406,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           tq_phase ^= 1u;
         }
         if (tile < 0) break;
-        const int kb0 = (tile / total) * k_per;
-        const int kb1 = min(num_k, kb0 + k_per);
+        const UnitMap um = map_unit(tile, total, num_k, splits, k_per, tail_first, tail_splits, tail_k_per);
+        const int kb0 = um.kb0, kb1 = um.kb1;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag, st, SITE_MMA_FULL, args.spin_budget)) {
             ok = false;
@@ -436,7 +478,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
         tq_phase ^= 1u;
       }
       if (tile < 0) break;
-      const TileCoord tc = tile_coord<TM>(tile % total, num_m, num_n, args.n_rotate, m_rot);
+      const UnitMap um = map_unit(tile, total, num_k, splits, k_per, tail_first, tail_splits, tail_k_per);
+      const bool add_into_c = args.accumulate || um.reduce;
+      const TileCoord tc = tile_coord<TM>(um.tile, num_m, num_n, args.n_rotate, m_rot);
       const uint32_t slot = TM == 1 ? next_slot : static_cast<uint32_t>(wg);
       const bool got = mbar_wait(&tfull[slot], uses[slot] & 1u, abort_flag, st, SITE_EPI_TFULL, args.spin_budget);
       if (named_bar_or(bar_vote, 128, !got)) break;
@@ -506,7 +550,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
           fence_proxy_async_smem();
           named_bar_sync(bar_stage, 128);
           if (etid == 0 && m_sub < args.M) {
-            if (args.accumulate || splits > 1) tma_reduce_add_2d(&map_c, buf, col0, m_sub);
+            if (add_into_c) tma_reduce_add_2d(&map_c, buf, col0, m_sub);
             else tma_store_2d(&map_c, buf, col0, m_sub);
             tma_commit_group();
           }
@@ -582,7 +626,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ C
             fence_proxy_async_smem();
             named_bar_sync(bar_stage, 128);
             if (etid == 0 && m_sub < args.M) {
-              if (args.accumulate || splits > 1) tma_reduce_add_2d(&map_c, buf, col0, m_sub);
+              if (add_into_c) tma_reduce_add_2d(&map_c, buf, col0, m_sub);
               else tma_store_2d(&map_c, buf, col0, m_sub);
               tma_commit_group();
             }
@@ -630,6 +674,32 @@ inline int& split_k_mode() {
     return (e != nullptr && e[0] == '1') ? 1 : 0;
   }();
   return mode;
+}
+
+// Tail split (see UnitMap): -1 = not decided yet (environment CTB_GEMM_TAIL_SPLIT, default on).
+inline int& tail_split_mode() {
+  static int mode = [] {
+    const char* e = std::getenv("CTB_GEMM_TAIL_SPLIT");
+    return (e != nullptr && e[0] == '0') ? 0 : ((e != nullptr && e[0] == '1') ? 1 : CTB_TAIL_SPLIT_DEFAULT);
+  }();
+  return mode;
+}
+
+// Host copy of tile_coord: first row / column of output tile `tile`.
+template <int TM>
+inline void host_tile_origin(int tile, int num_m, int num_n, int n_rotate, int m_rotate, int* m0, int* n0) {
+  constexpr int GROUP_M = Cfg<TM>::GROUP_M;
+  const int per_group = GROUP_M * num_n;
+  const int group = tile / per_group;
+  const int first_m = group * GROUP_M;
+  const int rows = std::min(GROUP_M, num_m - first_m);
+  const int local = tile - group * per_group;
+  int n = local / rows + n_rotate;
+  if (n >= num_n) n -= num_n;
+  int m = first_m + local % rows + m_rotate;
+  if (m >= num_m) m -= num_m;
+  *m0 = m * Cfg<TM>::BMT;
+  *n0 = n * BN;
 }
 
 inline int* next_tile_counter() {
@@ -792,6 +862,43 @@ int run_gemm(const GemmCall& c) {
       }
     }
   }
+  // Tail split for fp32 outputs (weight gradients accumulated over micro-batches): when the tiles
+  // do not fill a whole number of waves and the last wave would be less than half full, its tiles
+  // are cut into K slices that reduce-add into C, one slice per otherwise idle CTA.  Only those
+  // few tiles pay reduce traffic (and, on a first write, a memset), so unlike split-K over all
+  // tiles this does not cost clock inside a power-capped step.
+  a.tail_first = 0;
+  a.tail_splits = 1;
+  if (gemm::tail_split_mode() != 0 && a.split_k == 1 && c.epi == EPI_STORE && c.bias == nullptr && c.out_f32 &&
+      c.a_flags == nullptr && c.b_flags == nullptr && c.max_ctas <= 0 && !dynamic_tiles) {
+    const int sms = sm_count();
+    const int num_k = (c.K + gemm::BK - 1) / gemm::BK;
+    const int full = (tiles / sms) * sms;
+    const int tail = tiles - full;
+    if (full > 0 && tail > 0 && 2 * tail <= sms) {
+      int ts = std::min(sms / tail, 16);
+      // every slice must be non-empty and long enough to amortise its prologue and epilogue
+      while (ts > 1 && (num_k / ts < 16 || (ts - 1) * ((num_k + ts - 1) / ts) >= num_k)) --ts;
+      if (ts > 1) {
+        if (!c.accumulate) {
+          const int num_m_t = tm == 2 ? (c.M + 2 * BM - 1) / (2 * BM) : (c.M + BM - 1) / BM;
+          const int m_rot = a.m_rotate / tm < num_m_t ? a.m_rotate / tm : 0;
+          for (int t = full; t < tiles; ++t) {
+            int m0 = 0, n0 = 0;
+            if (tm == 2) gemm::host_tile_origin<2>(t, num_m_t, num_n, a.n_rotate, m_rot, &m0, &n0);
+            else gemm::host_tile_origin<1>(t, num_m_t, num_n, a.n_rotate, m_rot, &m0, &n0);
+            const int rows = std::min(tm * BM, c.M - m0), cols = std::min(static_cast<int>(BN), c.N - n0);
+            float* origin = static_cast<float*>(c.C) + static_cast<size_t>(m0) * c.ldc + n0;
+            CTB_CUDA_OK(cudaMemset2DAsync(origin, static_cast<size_t>(c.ldc) * 4, 0, static_cast<size_t>(cols) * 4,
+                                          static_cast<size_t>(rows), s));
+          }
+        }
+        a.tail_first = full;
+        a.tail_splits = ts;
+        tiles = full + tail * ts;
+      }
+    }
+  }
   int grid = std::min(tiles, c.max_ctas > 0 ? c.max_ctas : sm_count());
 #define CTB_DISPATCH_TM(TMV, AM, BMN)                                                       \
   switch (c.epi) {                                                                          \
@@ -897,6 +1004,15 @@ CTB_API int ctb_ce_dlogits(const void* hidden, const void* head, void* g, int ro
 // 0: never split K; 1: split K when it fills the last wave (see launch_gemm).  Returns the previous mode.
 CTB_API int ctb_gemm_set_split_k(int mode) {
   int& m = ctb::gemm::split_k_mode();
+  const int before = m;
+  m = mode != 0 ? 1 : 0;
+  return before;
+}
+
+// 0: never; 1: cut the tiles of a mostly empty last wave into K slices (fp32 outputs only, see
+// launch_gemm).  Returns the previous mode.
+CTB_API int ctb_gemm_set_tail_split(int mode) {
+  int& m = ctb::gemm::tail_split_mode();
   const int before = m;
   m = mode != 0 ? 1 : 0;
   return before;

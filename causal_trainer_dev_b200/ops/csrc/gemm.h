@@ -34,6 +34,8 @@ struct GemmArgs {
   int out_f32;
   int accumulate;
   int split_k;            // > 1: work units are (tile, K slice), every slice reduce-adds into C
+  int tail_first;         // with tail_splits > 1: tiles [tail_first, tiles) are cut into K slices,
+  int tail_splits;        //   tail_splits each; the tiles before them stay whole
   float alpha;
   const __nv_bfloat16* bias;
   DeviceStatus* status;

@@ -84,6 +84,36 @@ def test_split_k_weight_gradient_shapes(cuda_lib, shape):
     assert cuda_lib.device_status() == (0, 0, 0, 0)
 
 
+@pytest.mark.parametrize("shape", [(4096, 14336, 2048), (4096, 14336, 8192), (4000, 14400, 4104), (4096, 28672, 4096)])
+def test_tail_split_of_a_mostly_empty_last_wave(cuda_lib, shape):
+    """fp32 weight-gradient shapes whose tiles leave a small last wave: those tiles are cut into
+    K slices that reduce-add into C (first write and accumulation), the others stay whole."""
+    from causal_trainer_dev_b200.ops import gemm as G
+
+    m, n, k = shape
+    torch.manual_seed(6)
+    dy = (torch.randn(k, m, device="cuda") * 0.5).bfloat16()
+    x = (torch.randn(k, n, device="cuda") * 0.5).bfloat16()
+    ref = dy.float().t() @ x.float()
+    before = cuda_lib.lib().ctb_gemm_set_tail_split(1)
+    try:
+        out = torch.full((m, n), 7.0, device="cuda")               # overwritten, not accumulated
+        G.gemm(dy, x, a_mn=True, b_mn=True, out=out)
+        assert _rel(out, ref) < 1e-4
+        # every 256 x 256 block on its own: a tile that was skipped or added twice does not hide in the norm
+        blocks = (out - ref).abs().unfold(0, 128, 128).unfold(1, 128, 128).amax(dim=(-1, -2))
+        assert float(blocks.max()) < 0.05 * float(ref.abs().max())
+        G.gemm(dy, x, a_mn=True, b_mn=True, out=out, accumulate=True)
+        assert _rel(out, 2 * ref) < 1e-4
+        view = torch.full((m + 64, n + 64), 3.0, device="cuda")    # a strided destination keeps its frame
+        G.gemm(dy, x, a_mn=True, b_mn=True, out=view[:m, :n])
+        assert _rel(view[:m, :n], ref) < 1e-4
+        assert bool((view[m:, :] == 3.0).all()) and bool((view[:, n:] == 3.0).all())
+    finally:
+        cuda_lib.lib().ctb_gemm_set_tail_split(before)
+    assert cuda_lib.device_status() == (0, 0, 0, 0)
+
+
 def _check_split_k(G, m, n, k):
     dy = (torch.randn(k, m, device="cuda") * 0.5).bfloat16()       # [tokens, out]
     x = (torch.randn(k, n, device="cuda") * 0.5).bfloat16()        # [tokens, in]
