@@ -145,6 +145,10 @@ def main() -> None:
         out.update(
             shape=dict(tokens=s, q_heads=hq, kv_heads=hkv, head_dim=d, block=block, top_k=top_k),
             document_lengths=lens, grouped_work=work,
+            # a fingerprint of the grouping and of the grouped output (the grouping is a pure function
+            # of the routing, so variants of the grouping kernels must reproduce it bit for bit)
+            grouping_fingerprint=[int(groups.pos_of.to(torch.int64).sum()), int(groups.row_of.to(torch.int64).sum()),
+                                  float(og.double().sum()), float(lseg.double().sum())],
             # 128 x 128 score tiles: grouped history + own-block causal pass, against dense causal attention
             grouped_tiles=work["history_tiles"] + hq * nt * (block // 128 + 1) // 2,
             dense_causal_tiles=hq * nt * (nt + 1) // 2,

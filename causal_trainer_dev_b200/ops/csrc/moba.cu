@@ -421,6 +421,149 @@ moba_rank_kernel(const unsigned* __restrict__ sel, const int* __restrict__ seg, 
   }
 }
 
+// The same ranks computed by one CTA per (batch, head, block index): every thread owns a contiguous
+// span of the sequence and the spans are joined by a segmented scan keyed by the document, so the
+// depth is S / 1024 + log(1024) steps instead of S / 32.  The result is identical to the walk above
+// (ranks count earlier picked rows of the same document and head), so the grouping stays a pure
+// function of the routing; the group counts are left by atomicMax (cnt is zero before the launch).
+struct RankSpan {
+  int head;    // document key of the span's first token
+  int tail;    // document key of its last token
+  int cnt;     // picked rows among the trailing tokens that share `tail`
+  int flags;   // bit 0: every token of the span has the same key; bit 1: empty span
+};
+__device__ __forceinline__ RankSpan join_spans(const RankSpan& a, const RankSpan& b) {
+  if (b.flags & 2) return a;
+  if (a.flags & 2) return b;
+  RankSpan r;
+  r.head = a.head;
+  r.tail = b.tail;
+  if ((b.flags & 1) && b.head == a.tail) {
+    r.cnt = a.cnt + b.cnt;
+    r.flags = a.flags & 1;
+  } else {
+    r.cnt = b.cnt;
+    r.flags = 0;
+  }
+  return r;
+}
+__device__ __forceinline__ RankSpan shfl_up_span(const RankSpan& v, int delta) {
+  RankSpan r;
+  r.head = __shfl_up_sync(0xffffffffu, v.head, delta);
+  r.tail = __shfl_up_sync(0xffffffffu, v.tail, delta);
+  r.cnt = __shfl_up_sync(0xffffffffu, v.cnt, delta);
+  r.flags = __shfl_up_sync(0xffffffffu, v.flags, delta);
+  return r;
+}
+
+__global__ void __launch_bounds__(1024)
+moba_rank_scan_kernel(const unsigned* __restrict__ sel, const int* __restrict__ seg, const int* __restrict__ doc_start,
+                      int B, int S, int Hq, int Hkv, int block, int words, int nblk, int picks,
+                      int* __restrict__ rank, int* __restrict__ cnt) {
+  __shared__ RankSpan s_warp[32];
+  const int c = static_cast<int>(blockIdx.x % nblk);
+  const int h = static_cast<int>((blockIdx.x / nblk) % Hq);
+  const int b = static_cast<int>(blockIdx.x / nblk / Hq);
+  if (b >= B) return;
+  const int gsize = Hq / Hkv;
+  const int hkv = h / gsize, hg = h % gsize;
+  const int nt128 = S / 128;
+  const int word = c >> 5;
+  const unsigned bit = 1u << (c & 31);
+  const unsigned below = bit - 1u;
+  const int t = threadIdx.x, lane = t & 31, warp = t >> 5;
+  const int per = (S + 1023) / 1024;
+  const int i0 = min(S, t * per), i1 = min(S, i0 + per);
+  const size_t row_base = (static_cast<size_t>(b) * Hq + h) * S;
+  auto key_of = [&](int i) { return seg[b * S + i] != 0 ? doc_start[b * S + i] : -1; };
+  auto picked_at = [&](int i, int key, unsigned* w_out) {
+    if (key < 0 || word >= words) return false;
+    const unsigned w = __ldg(sel + (row_base + i) * words + word);
+    *w_out = w;
+    return c < (i - key) / block && (w & bit) != 0u;
+  };
+
+  // pass 1: the span's summary
+  RankSpan mine;
+  mine.head = mine.tail = -2;
+  mine.cnt = 0;
+  mine.flags = 2;
+  if (i0 < i1) {
+    mine.head = key_of(i0);
+    mine.tail = mine.head;
+    mine.flags = 1;
+    for (int i = i0; i < i1; ++i) {
+      const int key = key_of(i);
+      if (key != mine.tail) {
+        mine.tail = key;
+        mine.cnt = 0;
+        mine.flags = 0;
+      }
+      unsigned w;
+      if (picked_at(i, key, &w)) ++mine.cnt;
+    }
+  }
+  // inclusive scan over the CTA's spans: lanes, then warps
+  RankSpan incl = mine;
+#pragma unroll
+  for (int d = 1; d < 32; d <<= 1) {
+    const RankSpan up = shfl_up_span(incl, d);
+    if (lane >= d) incl = join_spans(up, incl);
+  }
+  if (lane == 31) s_warp[warp] = incl;
+  __syncthreads();
+  if (warp == 0) {
+    RankSpan w = s_warp[lane];
+#pragma unroll
+    for (int d = 1; d < 32; d <<= 1) {
+      const RankSpan up = shfl_up_span(w, d);
+      if (lane >= d) w = join_spans(up, w);
+    }
+    s_warp[lane] = w;
+  }
+  __syncthreads();
+  RankSpan before;                                  // everything left of this thread's span
+  before.head = before.tail = -2;
+  before.cnt = 0;
+  before.flags = 2;
+  if (warp > 0) before = s_warp[warp - 1];
+  {
+    const RankSpan left = shfl_up_span(incl, 1);    // lanes before this one, within the warp
+    if (lane > 0) before = join_spans(before, left);
+  }
+  if (i0 >= i1) return;
+
+  // pass 2: ranks of this span's picked rows
+  int run_key = mine.head;
+  int run = (!(before.flags & 2) && before.tail == run_key) ? before.cnt : 0;
+  int last_rank = -1;
+  auto close_run = [&]() {
+    if (last_rank >= 0) {
+      const int g = (b * Hkv + hkv) * nt128 + ((run_key + c * block) >> 7);
+      atomicMax(cnt + g * gsize + hg, last_rank + 1);
+    }
+    last_rank = -1;
+  };
+  for (int i = i0; i < i1; ++i) {
+    const int key = key_of(i);
+    if (key != run_key) {
+      close_run();
+      run_key = key;
+      run = 0;
+    }
+    unsigned w = 0u;
+    if (picked_at(i, key, &w)) {
+      const unsigned* row_words = sel + (row_base + i) * words;
+      int j = __popc(w & below);                       // earlier picks of this row: its slot for block c
+      for (int x = 0; x < word; ++x) j += __popc(__ldg(row_words + x));
+      if (j < picks) rank[(row_base + i) * picks + j] = run;
+      last_rank = run;
+      ++run;
+    }
+  }
+  close_run();
+}
+
 // ginfo[slot] = (batch | hkv << 16, first key, first gathered row, rows incl. padding); greal[slot] = real rows;
 // totals[0] = gathered rows in use, totals[1] = non-empty groups.
 __global__ void __launch_bounds__(1024)
@@ -719,8 +862,17 @@ CTB_API int ctb_moba_group(const unsigned* sel, const int* seg, const int* doc_s
   CTB_CUDA_OK(cudaMemsetAsync(cnt, 0, sizeof(int) * static_cast<size_t>(G) * gsize, s));
   CTB_CUDA_OK(cudaMemsetAsync(row_of, 0xff, sizeof(int) * static_cast<size_t>(rows_cap), s));
   const long warps = static_cast<long>(B) * Hq * nblk;
-  moba::moba_rank_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, s>>>(
-      sel, seg, doc_start, B, S, Hq, Hkv, block, words, nblk, picks, rank, cnt);
+  // CTB_MOBA_RANK=walk selects the one-warp-per-(head, block) walk; the default is the CTA-wide scan
+  static const bool walk = [] {
+    const char* e = std::getenv("CTB_MOBA_RANK");
+    return e != nullptr && e[0] == 'w';
+  }();
+  if (walk || warps > 0x7fffffffL)
+    moba::moba_rank_kernel<<<static_cast<unsigned>((warps * 32 + 255) / 256), 256, 0, s>>>(
+        sel, seg, doc_start, B, S, Hq, Hkv, block, words, nblk, picks, rank, cnt);
+  else
+    moba::moba_rank_scan_kernel<<<static_cast<unsigned>(warps), 1024, 0, s>>>(
+        sel, seg, doc_start, B, S, Hq, Hkv, block, words, nblk, picks, rank, cnt);
   CTB_CUDA_OK(cudaGetLastError());
   moba::moba_groups_kernel<<<1, 1024, 0, s>>>(cnt, pool_start, G, gsize, Hkv, nt128, row0, hoff,
                                               static_cast<int4*>(ginfo), greal, totals, slot_cap);

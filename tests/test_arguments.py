@@ -81,3 +81,12 @@ def test_frozen_parameters_are_normalised():
     assert parse_args(BASE + ["--frozen_parameters", "norm|lm_head"]).frozen_parameters == "lm_head|norm"
     with pytest.raises(ValueError):
         parse_frozen_parameter_components("attention")
+
+
+def test_flags_of_this_framework_have_defaults_and_choices():
+    a = parse_args(BASE)
+    assert a.balance_rows is True and a.activation_memory == "auto" and a.fused_collectives is True
+    b = parse_args(BASE + ["--no-balance-rows", "--activation-memory", "recompute", "--fused_collectives", "false"])
+    assert b.balance_rows is False and b.activation_memory == "recompute" and b.fused_collectives is False
+    with pytest.raises(SystemExit):
+        parse_args(BASE + ["--activation_memory", "sometimes"])
