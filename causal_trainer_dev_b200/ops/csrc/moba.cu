@@ -361,9 +361,11 @@ CTB_API int ctb_moba_lists(int mode, const unsigned* touch, int B, int S, int Hq
 // order of the rows inside a group (and with it every floating-point sum over a group) is a pure
 // function of the routing:
 //
-//   moba_rank    one warp per (batch, head, block index c): walks the sequence and gives every row
-//                that selected block c of its document its rank among such rows of the same
-//                (document, head); the last of them leaves the count in cnt[group][head in group].
+//   moba_rank    gives every row that selected block c of its document its rank among such rows of
+//                the same (document, head) and leaves the count in cnt[group][head in group]:
+//                moba_rank_scan_kernel, one CTA per (batch, head, c), a segmented scan over the
+//                sequence (default); moba_rank_kernel, one warp per (batch, head, c) walking the
+//                sequence (CTB_MOBA_RANK=walk; same result, kept for comparison).
 //   moba_groups  one CTA: exclusive scan of the padded group sizes -> first row of every group,
 //                offsets of the heads inside a group, the compact list of non-empty groups.
 //   moba_desc    descriptors of the CTAs of the grouped flash kernels.
