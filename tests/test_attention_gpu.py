@@ -69,6 +69,50 @@ def test_matches_oracle(cuda_lib, d, hq, hkv, layout):
     assert cuda_lib.device_status() == (0, 0, 0, 0)
 
 
+def test_matches_oracle_at_the_training_shape(cuda_lib):
+    """32 query / 8 key-value heads, 4096 tokens packed from six documents (the benchmark's layer
+    shape), forward and all three gradients against the fp32 PyTorch attention."""
+    from causal_trainer_dev_b200.ops import attention as A
+
+    b, s, hq, hkv, d = 1, 4096, 32, 8, 128
+    seg = _segments(b, s, 6)
+    (q, k, v, do), (o, lse, dq, dk, dv) = _run(b, s, hq, hkv, d, seg, seed=11)
+    qf, kf, vf = (t.float().requires_grad_() for t in (q, k, v))
+    ref = A.vanilla_attention(qf, kf, vf, seg, None)
+    ref.backward(do.float())
+    assert _rel(o, ref) < 0.04
+    assert _rel(dq, qf.grad) < 0.10
+    assert _rel(dk, kf.grad) < 0.12
+    assert _rel(dv, vf.grad) < 0.10
+    assert cuda_lib.device_status() == (0, 0, 0, 0)
+
+
+def test_gradients_vanish_outside_the_document_of_the_cotangent(cuda_lib):
+    """A cotangent that is non-zero in one document only: dQ, dK and dV are exactly zero everywhere
+    else (reference: tests/kernels/test_efficient_attention_tpu.py:353-424)."""
+    from causal_trainer_dev_b200.ops import attention as A
+
+    b, s, hq, hkv, d = 1, 1536, 8, 2, 128
+    seg = torch.ones(b, s, dtype=torch.int32, device="cuda")
+    seg[:, 500:1100] = 2
+    seg[:, 1100:] = 3
+    torch.manual_seed(4)
+    q = torch.randn(b, s, hq, d, device="cuda").bfloat16()
+    k = torch.randn(b, s, hkv, d, device="cuda").bfloat16()
+    v = torch.randn(b, s, hkv, d, device="cuda").bfloat16()
+    do = torch.zeros(b, s, hq, d, device="cuda").bfloat16()
+    do[:, 500:1100] = torch.randn(b, 600, hq, d, device="cuda").bfloat16()
+    meta = A.build_attention_meta(seg)
+    o, lse = A.flash_attention_forward(q, k, v, meta)
+    dq, dk, dv = A.flash_attention_backward(q, k, v, o, do, lse, meta)
+    inside = torch.zeros(s, dtype=torch.bool, device="cuda")
+    inside[500:1100] = True
+    for g in (dq, dk, dv):
+        assert torch.all(g[:, ~inside] == 0)
+        assert float(g[:, inside].float().abs().sum()) > 0
+    assert cuda_lib.device_status() == (0, 0, 0, 0)
+
+
 def test_no_leakage_between_documents(cuda_lib):
     """Perturbing document 1 changes nothing, bit for bit, in document 2."""
     from causal_trainer_dev_b200.ops import attention as A
