@@ -58,6 +58,8 @@ def parse() -> argparse.Namespace:
                                                      "0: what the configuration names, capped by N")
     p.add_argument("--sp", type=int, default=1, help="sequence-parallel degree (queries sharded over sp ranks, K/V gathered; "
                                                      "the sp ranks are also FSDP ranks); not with MoBA layers")
+    p.add_argument("--sp-layout", choices=("contiguous", "zigzag"), default="contiguous",
+                   help="which tokens of a row an sp rank computes: one slice, or chunks r and 2 sp - 1 - r (equal causal work)")
     return p.parse_args()
 
 
@@ -188,7 +190,7 @@ def main() -> None:
         adamw=AdamWConfig(weight_decay=0.1, max_grad_norm=1.0),
         schedule=ScheduleConfig(learning_rate=2e-5, learning_rate_end=2e-6, scheduler="cosine", warmup_steps=2,
                                 total_steps=1000),
-        fused_collectives=(args.impl == "ours"), remat=args.remat, tp=tp, sp=sp,
+        fused_collectives=(args.impl == "ours"), remat=args.remat, tp=tp, sp=sp, sp_layout=args.sp_layout,
         force_sharded_runtime=args.force_sharded_runtime, attention_options=attention_options,
         moba_dense_shortcut=args.attention != "sparse",
     )
@@ -300,7 +302,7 @@ def main() -> None:
             "config": {
                 "name": bc.name, "model": bc.model + (f"-{args.layers}layers" if args.layers else ""),
                 "global_batch": global_batch, "seq_len": seq_len,
-                "parallelism": f"fsdp{data_world}" + (f"xtp{tp}" if tp > 1 else "") + (f"xsp{sp}" if sp > 1 else ""),
+                "parallelism": f"fsdp{data_world}" + (f"xtp{tp}" if tp > 1 else "") + (f"xsp{sp}" + ("-zigzag" if args.sp_layout == "zigzag" else "") if sp > 1 else ""),
                 "attention": (getattr(trainer, "attention", None) or (
                     moba_note if attention_options is not None else "dense, segment-isolated flash attention")),
                 "micro_batch_rows": micro,

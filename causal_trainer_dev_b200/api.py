@@ -37,6 +37,7 @@ class TrainerConfig:
     remat: str = "auto"                # "auto": keep activations that fit, recompute the rest; "full"; "none"
     tp: int = 1                        # tensor-parallel degree; ranks are laid out (fsdp, tp) with tp fastest
     sp: int = 1                        # sequence-parallel degree (queries sharded, K/V all-gathered); may be combined with tp
+    sp_layout: str = "contiguous"      # "zigzag": rank r computes chunks r and 2 sp - 1 - r of every row (equal causal work)
     force_sharded_runtime: bool = False  # run the FSDP runtime even on one rank (measures its own overhead)
     frozen: tuple[str, ...] = ()       # components held fixed: any of "lm_head", "embed", "norm"
     loss_backend: str = "cut"          # "cut": projection-fused; "logits": bf16 logits slab per row chunk
@@ -80,11 +81,11 @@ class Trainer:
                 self.runtime = FsdpRuntime(tp_local_config(model, tp), self.cfg, self.device, group=shard_group,
                                            full_cfg=model, tp_group=tp_group)
                 self.engine = sp_tp_engine(model, tp_group, sp_group, self.runtime, self._engine_options(),
-                                           fused=self.cfg.fused_collectives)
+                                           fused=self.cfg.fused_collectives, layout=self.cfg.sp_layout)
             else:
                 self.runtime = FsdpRuntime(model, self.cfg, self.device, group=shard_group, frozen=self.cfg.frozen)
                 self.engine = SpLayerwiseEngine(model, sp_group, self.runtime, self._engine_options(),
-                                                fused=self.cfg.fused_collectives)
+                                                fused=self.cfg.fused_collectives, layout=self.cfg.sp_layout)
             self.step_fn = self.runtime.make_step(self.engine)
         elif self.cfg.tp > 1:
             from .parallel.fsdp import FsdpRuntime

@@ -179,6 +179,9 @@ FLAGS: tuple[Flag, ...] = (
     Flag("profile_steps", int, 0, "Device-time this many steps with CUDA events and report tokens/s and MFU."),
     Flag("balance_rows", "bool", True, "Deal the rows of every global batch to the data ranks by attention cost (equal "
          "rows, near-equal visible query-key pairs per rank) instead of by position."),
+    Flag("sp_layout", str, "contiguous", "Which tokens of a row a sequence-parallel rank computes: contiguous (one "
+         "slice per rank) or zigzag (chunks r and 2 sp - 1 - r of 2 sp chunks, equal causal attention work on every rank; "
+         "rows that do not split into whole 128-token tiles use contiguous slices).", choices=("contiguous", "zigzag")),
     Flag("activation_memory", str, "auto", "What the CUDA engine does with layer activations: auto keeps those of as "
          "many layers as fit in free HBM and recomputes the rest; recompute always recomputes (the meaning of "
          "gradient_checkpointing=nothing_saveable on small-memory devices); keep never recomputes. "

@@ -450,13 +450,13 @@ class TrainingRun:
                 self.runtime = FsdpRuntime(tp_local_config(self.cfg, tp), tcfg, self.device, group=data_group,
                                            full_cfg=self.cfg, tp_group=tp_group)
                 engine = sp_tp_engine(self.cfg, tp_group, self.lattice.group(("sp",)), self.runtime, options,
-                                      fused=a.fused_collectives)
+                                      fused=a.fused_collectives, layout=a.sp_layout)
             elif sp > 1:
                 from .sp_engine import SpLayerwiseEngine
 
                 self.runtime = FsdpRuntime(self.cfg, tcfg, self.device, group=data_group, frozen=frozen)
                 engine = SpLayerwiseEngine(self.cfg, self.lattice.group(("sp",)), self.runtime, options,
-                                           fused=a.fused_collectives)
+                                           fused=a.fused_collectives, layout=a.sp_layout)
             elif tp > 1:
                 from ..parallel.tp import tp_local_config
                 from .tp_engine import TpLayerwiseEngine

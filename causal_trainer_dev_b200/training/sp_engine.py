@@ -44,11 +44,14 @@ class SequenceParallelAttention:
     summed over sp here and, for shared key/value heads, over tp by that engine -- the reference's
     ``psum`` over ``("tp", "sp")``, src/causal_trainer/kernels/efficient_attention.py:296-310)."""
 
-    def _init_sp(self, sp_group, fused: bool) -> None:
+    def _init_sp(self, sp_group, fused: bool, layout: str = "contiguous") -> None:
+        if layout not in ("contiguous", "zigzag"):
+            raise ValueError(f"sp layout must be 'contiguous' or 'zigzag', got {layout!r}")
         self.sp_group = sp_group
         self.sp_world = dist.get_world_size(sp_group)
         self.sp_rank = dist.get_rank(sp_group)
         self.sp_fused = fused
+        self.sp_layout = layout
         self._kv_ctx: dict[tuple[int, int], TpContext] = {}
         if self.options.attention_options is not None and self.options.attention_options.method == "moba":
             raise ValueError("MoBA and sequence parallelism (sp > 1) cannot be combined: shard long rows over tp instead")
@@ -57,23 +60,56 @@ class SequenceParallelAttention:
     def _local_seq(self, s: int) -> int:
         return s // self.sp_world
 
+    def token_ranges(self, s: int) -> list[tuple[int, int]]:
+        """``(first token, count)`` of the pieces of a row this rank computes, in local order.
+
+        ``contiguous``: one slice per rank.  ``zigzag``: the row is cut into ``2 * sp`` chunks and
+        rank ``r`` takes chunks ``r`` and ``2 * sp - 1 - r``; under a causal mask every rank then
+        has the same number of visible (query, key) pairs, where contiguous slices give the last
+        rank ``(2 sp - 1) / sp`` times the mean.  Needs chunks of whole 128-row query tiles; rows
+        that do not divide fall back to contiguous slices."""
+        w, r = self.sp_world, self.sp_rank
+        if s % (w * 128):
+            raise ValueError(f"sequence length {s} must be a multiple of 128 * sp ({128 * w})")
+        if self._zigzag(s):
+            c = s // (2 * w)
+            return [(r * c, c), ((2 * w - 1 - r) * c, c)]
+        n = s // w
+        return [(r * n, n)]
+
+    def _zigzag(self, s: int) -> bool:
+        return self.sp_layout == "zigzag" and self.sp_world > 1 and s % (256 * self.sp_world) == 0
+
     def select_tokens(self, t: torch.Tensor) -> torch.Tensor:
-        s = t.shape[1]
-        if s % (self.sp_world * 128):
-            raise ValueError(f"sequence length {s} must be a multiple of 128 * sp ({128 * self.sp_world})")
-        n = s // self.sp_world
-        return t[:, self.sp_rank * n:(self.sp_rank + 1) * n].contiguous()
+        parts = [t[:, lo:lo + n] for lo, n in self.token_ranges(t.shape[1])]
+        return (parts[0] if len(parts) == 1 else torch.cat(parts, dim=1)).contiguous()
+
+    def _to_sequence_order(self, slabs: torch.Tensor, s: int) -> torch.Tensor:
+        """``[S, width]`` rows as the gather leaves them (one slab per rank, each in that rank's
+        local order) -> rows in sequence order."""
+        if not self._zigzag(s):
+            return slabs
+        w = self.sp_world
+        f = slabs.view(w, 2, s // (2 * w), -1)
+        return torch.cat([f[:, 0], f[:, 1].flip(0)], dim=0).reshape(s, -1)
+
+    def _to_slab_order(self, rows: torch.Tensor, out: torch.Tensor, s: int) -> None:
+        """Inverse of :meth:`_to_sequence_order`, written into ``out`` (a ring slot)."""
+        w = self.sp_world
+        c = s // (2 * w)
+        q, o = rows.view(2 * w, c, -1), out.view(w, 2, c, -1)
+        o[:, 0].copy_(q[:w])
+        o[:, 1].copy_(q[w:].flip(0))
 
     def _context(self, batch):
         ctx = super()._context(batch)            # metadata of the whole rows; rotary table of all positions
         s = ctx["seq"]
         n = s // self.sp_world
-        lo = self.sp_rank * n
         b = ctx["batch"]
         # the rotary table is [B*S, ...]: keep this rank's positions of every row
-        ctx["cos"] = ctx["cos"].view(b, s, -1)[:, lo:lo + n].reshape(b * n, -1).contiguous()
-        ctx["sin"] = ctx["sin"].view(b, s, -1)[:, lo:lo + n].reshape(b * n, -1).contiguous()
-        ctx.update(seq=n, seq_full=s, q_off=lo)
+        ctx["cos"] = self.select_tokens(ctx["cos"].view(b, s, -1)).reshape(b * n, -1)
+        ctx["sin"] = self.select_tokens(ctx["sin"].view(b, s, -1)).reshape(b * n, -1)
+        ctx.update(seq=n, seq_full=s, q_ranges=self.token_ranges(s))
         return ctx
 
     def _uses_moba(self, li: int, seq: int, longest: int | None = None) -> bool:
@@ -96,15 +132,20 @@ class SequenceParallelAttention:
                                       pick(meta.first_q))
 
     def _gather_row(self, kv: TpContext, k: torch.Tensor, v: torch.Tensor, b: int):
-        """Starts the all-gather of row ``b``'s keys and values; returns ``(slot, K [1,S,Hkv,D], V)``."""
+        """Starts the all-gather of row ``b``'s keys and values; returns the slot (``slot.full`` is
+        ``[S, 2 kvw]``: keys | values, one slab of local rows per rank)."""
         _, n, hkv, d = k.shape
         kvw = hkv * d
         g = kv.next_slot()
         g.mine[:, :kvw].copy_(k[b].reshape(n, kvw))
         g.mine[:, kvw:].copy_(v[b].reshape(n, kvw))
-        full = kv.all_gather(g)                                  # [S, 2 kvw]: keys | values of every token
-        s = full.shape[0]
-        return g, full[:, :kvw].view(1, s, hkv, d), full[:, kvw:].view(1, s, hkv, d)
+        kv.all_gather(g)
+        return g
+
+    @staticmethod
+    def _keys_values(rows: torch.Tensor, hkv: int, d: int):
+        s, kvw = rows.shape[0], hkv * d
+        return rows[:, :kvw].view(1, s, hkv, d), rows[:, kvw:].view(1, s, hkv, d)
 
     # ------------------------------------------------------------------ attention
     def _flags_are_safe(self, heads: int, queries: int, device) -> bool:
@@ -124,18 +165,26 @@ class SequenceParallelAttention:
         b, n, hkv, d = k.shape
         s = ctx["seq_full"]
         kv = self._gather_ctx(s, 2 * hkv * d, k.device)
+        zig = self._zigzag(s)
         o = torch.empty((b, n, q.shape[2], d), dtype=torch.bfloat16, device=q.device)
         lse = torch.empty((b, q.shape[2], n), dtype=torch.float32, device=q.device)
         for row in range(b):
-            g, k_full, v_full = self._gather_row(kv, k, v, row)
-            flags = kv.gathered_flags(g) if self._flags_are_safe(q.shape[2], n, q.device) else None
+            g = self._gather_row(kv, k, v, row)
+            # the kernel can follow the gather's flags only over a buffer that is in sequence order
+            flags = kv.gathered_flags(g) if not zig and self._flags_are_safe(q.shape[2], n, q.device) else None
             if flags is None:
                 kv.wait_gathered(g)
-            o_row, lse_row = attn_ops.flash_attention_forward(
-                q[row:row + 1], k_full, v_full, self._row_meta(ctx["meta"], row), q_offset=ctx["q_off"],
-                out=o[row:row + 1], kv_flags=flags)
-            lse[row:row + 1].copy_(lse_row)
-            self._count(5)
+            k_full, v_full = self._keys_values(self._to_sequence_order(g.full, s), hkv, d)
+            meta = self._row_meta(ctx["meta"], row)
+            at = 0
+            for lo, cnt in ctx["q_ranges"]:
+                _, lse_part = attn_ops.flash_attention_forward(
+                    q[row:row + 1, at:at + cnt], k_full, v_full, meta, q_offset=lo, out=o[row:row + 1, at:at + cnt],
+                    kv_flags=flags)
+                lse[row:row + 1, :, at:at + cnt].copy_(lse_part)
+                at += cnt
+                self._count(2)
+            self._count(3)
         return o, lse, {"sp": True}
 
     def _attention_backward(self, q, k, v, o, do, lse, aux, ctx, dq, dk, dv) -> None:
@@ -143,31 +192,48 @@ class SequenceParallelAttention:
         s = ctx["seq_full"]
         kvw = hkv * d
         kv = self._gather_ctx(s, 2 * kvw, k.device)
+        zig = self._zigzag(s)
+        ranges = ctx["q_ranges"]
         for row in range(b):
-            g, k_full, v_full = self._gather_row(kv, k, v, row)
+            g = self._gather_row(kv, k, v, row)
             kv.wait_gathered(g)                                  # the backward kernels read plain memory
+            k_full, v_full = self._keys_values(self._to_sequence_order(g.full, s), hkv, d)
             part = kv.next_slot()                                # this rank's partial dK | dV for all S keys
-            dk_full = part.full[:, :kvw].view(1, s, hkv, d)
-            dv_full = part.full[:, kvw:].view(1, s, hkv, d)
-            attn_ops.flash_attention_backward(
-                q[row:row + 1], k_full, v_full, o[row:row + 1], do[row:row + 1], lse[row:row + 1],
-                self._row_meta(ctx["meta"], row), dq=dq[row:row + 1], dk=dk_full, dv=dv_full, q_offset=ctx["q_off"])
-            mine = kv.reduce_scatter_rows(part)                  # [n, 2 kvw]: the key slice this rank projected
+            # partial sums in sequence order: the slot itself when that is also its slab order
+            total = torch.empty_like(part.full) if zig else part.full
+            extra = torch.empty_like(part.full) if len(ranges) > 1 else None
+            meta = self._row_meta(ctx["meta"], row)
+            at = 0
+            for i, (lo, cnt) in enumerate(ranges):
+                into = total if i == 0 else extra
+                dk_full, dv_full = self._keys_values(into, hkv, d)
+                attn_ops.flash_attention_backward(
+                    q[row:row + 1, at:at + cnt], k_full, v_full, o[row:row + 1, at:at + cnt], do[row:row + 1, at:at + cnt],
+                    lse[row:row + 1, :, at:at + cnt].contiguous(), meta, dq=dq[row:row + 1, at:at + cnt], dk=dk_full,
+                    dv=dv_full, q_offset=lo)
+                if i:
+                    total.add_(extra)
+                at += cnt
+                self._count(4)
+            if zig:
+                self._to_slab_order(total, part.full, s)
+            mine = kv.reduce_scatter_rows(part)                  # [n, 2 kvw]: the key rows this rank projected
             dk[row].copy_(mine[:, :kvw].view(n, hkv, d))
             dv[row].copy_(mine[:, kvw:].view(n, hkv, d))
-            self._count(9)
+            self._count(5)
 
 
 class SpLayerwiseEngine(SequenceParallelAttention, LayerwiseEngine):
     """Sequence parallelism on the plain layer schedule (every rank holds all heads)."""
 
-    def __init__(self, cfg: ModelConfig, sp_group, provider, options: EngineOptions | None = None, fused: bool = True):
+    def __init__(self, cfg: ModelConfig, sp_group, provider, options: EngineOptions | None = None, fused: bool = True,
+                 layout: str = "contiguous"):
         LayerwiseEngine.__init__(self, cfg, provider, options)
-        self._init_sp(sp_group, fused)
+        self._init_sp(sp_group, fused, layout)
 
 
 def sp_tp_engine(full_cfg: ModelConfig, tp_group, sp_group, provider, options: EngineOptions | None = None,
-                 fused: bool = True):
+                 fused: bool = True, layout: str = "contiguous"):
     """Sequence x tensor parallelism: the tensor-parallel schedule on this rank's token slice, its
     attention seeing the whole row through the sp gather."""
     from .tp_engine import TpLayerwiseEngine
@@ -175,6 +241,6 @@ def sp_tp_engine(full_cfg: ModelConfig, tp_group, sp_group, provider, options: E
     class SpTpLayerwiseEngine(SequenceParallelAttention, TpLayerwiseEngine):
         def __init__(self):
             TpLayerwiseEngine.__init__(self, full_cfg, tp_group, provider, options, fused=fused)
-            self._init_sp(sp_group, fused)
+            self._init_sp(sp_group, fused, layout)
 
     return SpTpLayerwiseEngine()

@@ -91,7 +91,8 @@ def run_ops(out_path: str) -> None:
         Path(out_path).write_text(json.dumps(gathered))
 
 
-def run_train(out_path: str, tp: int, fused: bool, steps: int, kv_heads: int = 2, sp: int = 1) -> None:
+def run_train(out_path: str, tp: int, fused: bool, steps: int, kv_heads: int = 2, sp: int = 1,
+              seq: int = 256, layouts: tuple[str, ...] = ("contiguous",)) -> None:
     from causal_trainer_dev_b200.api import Trainer, TrainerConfig
     from causal_trainer_dev_b200.data.synthetic import pretraining_rows
     from causal_trainer_dev_b200.models.config import preset
@@ -100,18 +101,25 @@ def run_train(out_path: str, tp: int, fused: bool, steps: int, kv_heads: int = 2
 
     rank = dist.get_rank()
     cfg = preset("tiny", vocab_size=4096, num_hidden_layers=3, intermediate_size=512, num_key_value_heads=kv_heads)
-    tcfg = TrainerConfig(micro_batch_rows=2, adamw=AdamWConfig(weight_decay=0.1, max_grad_norm=1.0),
-                         schedule=ScheduleConfig(1e-3, 0.0, "constant", 0, 10), fused_collectives=fused, seed=3, tp=tp, sp=sp)
-    trainer = Trainer(cfg, tcfg)
-    rows = 8
-    data = pretraining_rows(rows, 256, cfg.vocab_size, eos_token_id=2, pad_token_id=0, median_len=80, min_len=8, seed=5)
-    per = rows // trainer.data_world
-    lo = trainer.data_rank * per
-    mine = {k: torch.from_numpy(v[lo:lo + per].copy()).pin_memory() for k, v in data.items()}
-    history = [trainer.train_step(mine) for _ in range(steps)]
-    status = lib.device_status(raise_on_error=False)
+    result = {}
+    for layout in layouts:
+        tcfg = TrainerConfig(micro_batch_rows=2, adamw=AdamWConfig(weight_decay=0.1, max_grad_norm=1.0),
+                             schedule=ScheduleConfig(1e-3, 0.0, "constant", 0, 10), fused_collectives=fused, seed=3, tp=tp,
+                             sp=sp, sp_layout=layout)
+        trainer = Trainer(cfg, tcfg)
+        rows = 8
+        data = pretraining_rows(rows, seq, cfg.vocab_size, eos_token_id=2, pad_token_id=0, median_len=80 if seq == 256 else seq // 3, min_len=8,
+                                seed=5)
+        per = rows // trainer.data_world
+        lo = trainer.data_rank * per
+        mine = {k: torch.from_numpy(v[lo:lo + per].copy()).pin_memory() for k, v in data.items()}
+        history = [trainer.train_step(mine) for _ in range(steps)]
+        key = "history" if layout == layouts[0] else f"history_{layout}"
+        result[key] = history
+        del trainer
+    result["status"] = lib.device_status(raise_on_error=False)
     if rank == 0:
-        Path(out_path).write_text(json.dumps({"history": history, "status": status}))
+        Path(out_path).write_text(json.dumps(result))
 
 
 def main() -> None:
@@ -122,7 +130,9 @@ def main() -> None:
         run_ops(sys.argv[2])
     else:
         run_train(sys.argv[2], int(sys.argv[3]), sys.argv[4] == "fused", int(sys.argv[5]),
-                  int(sys.argv[6]) if len(sys.argv) > 6 else 2, int(sys.argv[7]) if len(sys.argv) > 7 else 1)
+                  int(sys.argv[6]) if len(sys.argv) > 6 else 2, int(sys.argv[7]) if len(sys.argv) > 7 else 1,
+                  int(sys.argv[8]) if len(sys.argv) > 8 else 256,
+                  tuple(sys.argv[9].split(",")) if len(sys.argv) > 9 else ("contiguous",))
     dist.destroy_process_group()
 
 

@@ -86,6 +86,7 @@ def test_frozen_parameters_are_normalised():
 def test_flags_of_this_framework_have_defaults_and_choices():
     a = parse_args(BASE)
     assert a.balance_rows is True and a.activation_memory == "auto" and a.fused_collectives is True
+    assert a.sp_layout == "contiguous" and parse_args(BASE + ["--sp-layout", "zigzag"]).sp_layout == "zigzag"
     b = parse_args(BASE + ["--no-balance-rows", "--activation-memory", "recompute", "--fused_collectives", "false"])
     assert b.balance_rows is False and b.activation_memory == "recompute" and b.fused_collectives is False
     with pytest.raises(SystemExit):

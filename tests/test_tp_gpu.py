@@ -98,6 +98,15 @@ def test_sequence_times_tensor_parallel_matches_fsdp4(cuda_lib, tmp_path):
     _close(mixed["history"], fsdp["history"], 2e-2, 3e-2)
 
 
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_zigzag_sequence_parallel_layout_matches_contiguous_slices(cuda_lib, tmp_path):
+    """sp = 2 with every rank computing chunks r and 3 - r of each row (equal causal work) trains
+    like sp = 2 with contiguous slices: the same tokens, dealt differently."""
+    both = _launch(["train", "1", "fused", "3", "2", "2", "512", "contiguous,zigzag"], 2, tmp_path / "zz.json", 29645)
+    assert both["status"] == [0, 0, 0, 0]
+    _close(both["history_zigzag"], both["history"], 2e-2, 3e-2)
+
+
 def test_in_kernel_kv_flag_waits_only_when_the_pull_kernel_is_certain_to_be_resident(cuda_lib):
     """The attention forward kernel may spin on the gather's flags only if its grid leaves SMs for
     the pull kernel; larger grids must take the stream-level dependency (no device wait at all)."""
