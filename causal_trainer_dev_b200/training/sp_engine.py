@@ -20,6 +20,11 @@ MLP, the loss -- runs on the local slice unchanged; only attention communicates:
   peer loads, in rank order, in fp32 (attention -> reduce-scatter).
 * ``fused=False`` is the NCCL variant of the same schedule (all-gather, reduce-scatter calls).
 
+Which tokens a rank computes is a layout choice (``token_ranges``): a contiguous slice per rank, as
+in the reference, or zig-zag chunks (``r`` and ``2 sp - 1 - r`` of ``2 sp``) that give every rank
+the same causal work; the per-token code never looks at token positions other than through the
+rotary table, so only the attention below and the order of the gathered K / V slabs know about it.
+
 Rows of a micro-batch are processed one at a time through the gather (a gathered buffer is one
 ``[S, 2 * kv_width]`` row), so the buffers do not grow with the batch.
 
