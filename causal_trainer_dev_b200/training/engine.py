@@ -342,12 +342,12 @@ class LayerwiseEngine:
             return 0
         if mode == "none":
             return cfg.num_hidden_layers
-        per_layer = tokens * 2 * (3 * cfg.hidden_size + 2 * cfg.query_width + 2 * cfg.key_value_width
-                                  + 2 * cfg.intermediate_size) + tokens * 12 * cfg.num_attention_heads
+        from .memory_plan import backward_working_set_bytes, layer_activation_bytes
+
+        per_layer = layer_activation_bytes(cfg, tokens)
         free, _ = torch.cuda.mem_get_info()
         cached = torch.cuda.memory_reserved() - torch.cuda.memory_allocated()
-        working_set = tokens * 2 * (6 * cfg.intermediate_size + 8 * cfg.hidden_size) + (self.options.cut_chunk_rows
-                                                                                        * cfg.vocab_size * 2)
+        working_set = backward_working_set_bytes(cfg, tokens, self.options.cut_chunk_rows)
         budget = free + cached - working_set - self.options.memory_reserve_bytes
         return max(0, min(cfg.num_hidden_layers, int(budget // per_layer)))
 
