@@ -63,3 +63,25 @@ def test_command_line_prints_the_plan(capsys):
     assert "layers_kept" in text and "moba_gathered_rows" in text and "GiB" in text
     with pytest.raises(ValueError):
         plan(preset("llama3-8b"), seq_len=4096 + 64, micro_rows=1)
+
+
+def test_engine_policy_counts_layers_from_the_same_figures(monkeypatch):
+    import torch
+
+    from causal_trainer_dev_b200.training.engine import EngineOptions, LayerwiseEngine
+
+    cfg = preset("llama3-8b")
+    engine = LayerwiseEngine.__new__(LayerwiseEngine)
+    engine.cfg, engine.options = cfg, EngineOptions()
+    tokens = 16384
+    per_layer = layer_activation_bytes(cfg, tokens)
+    working = backward_working_set_bytes(cfg, tokens, engine.options.cut_chunk_rows)
+    free = working + engine.options.memory_reserve_bytes + 5 * per_layer + per_layer // 2
+    monkeypatch.setattr(torch.cuda, "mem_get_info", lambda: (free, 0))
+    monkeypatch.setattr(torch.cuda, "memory_reserved", lambda: 0)
+    monkeypatch.setattr(torch.cuda, "memory_allocated", lambda: 0)
+    assert engine._layers_to_keep(tokens) == 5
+    engine.options = EngineOptions(remat="full")
+    assert engine._layers_to_keep(tokens) == 0
+    engine.options = EngineOptions(remat="none")
+    assert engine._layers_to_keep(tokens) == cfg.num_hidden_layers
