@@ -44,16 +44,20 @@ def _column(value: Any, name: str) -> list[Scalar]:
     raw = _to_list(value, name)
     if name in _FLOAT_FIELDS:
         try:
-            out = [float(x) for x in raw]
+            out = list(map(float, raw))
         except (TypeError, ValueError) as exc:
             raise ValueError(f"Per-token field {name!r} must contain numbers.") from exc
-        if any(not math.isfinite(x) for x in out):
+        if not all(map(math.isfinite, out)):
             raise ValueError(f"Per-token field {name!r} must contain only finite numbers.")
         return out
     try:
-        return [int(x) for x in raw]
+        return list(map(int, raw))
     except (TypeError, ValueError) as exc:
         raise ValueError(f"Per-token field {name!r} must contain integers.") from exc
+
+
+def _binary(values: list) -> bool:
+    return set(values) <= {0, 1}
 
 
 def normalize_example(example: Mapping[str, Any], max_length: int) -> PackedExample:
@@ -77,14 +81,14 @@ def normalize_example(example: Mapping[str, Any], max_length: int) -> PackedExam
             raise ValueError(f"Per-token field {key!r} has length {len(col)}, expected {len(full)}.")
         out[key] = col[:max_length]
     out.setdefault("attention_mask", [1] * len(out["input_ids"]))
-    if any(v not in (0, 1) for v in out["attention_mask"]):
+    if not _binary(out["attention_mask"]):
         raise ValueError("attention_mask must contain only binary 0/1 values.")
     for name in _ASSISTANT_FIELDS:
-        if name in out and any(v not in (0, 1) for v in out[name]):
+        if name in out and not _binary(out[name]):
             raise ValueError(f"{name} must contain only binary 0/1 values.")
-    if "position_ids" in out and any(v < 0 for v in out["position_ids"]):
+    if "position_ids" in out and min(out["position_ids"]) < 0:
         raise ValueError("position_ids must be non-negative.")
-    if "loss_weights" in out and any(v < 0.0 for v in out["loss_weights"]):
+    if "loss_weights" in out and min(out["loss_weights"]) < 0.0:
         raise ValueError("loss_weights must be non-negative.")
     return out
 
@@ -125,6 +129,9 @@ def best_fit_decreasing(examples: Sequence[PackedExample], *, max_length: int) -
 
 def run_metadata(attention_mask: Sequence[int], first_segment: int = 0) -> tuple[list[int], list[int], int]:
     """Positions and one-based segment ids of the contiguous valid runs of one example."""
+    n = len(attention_mask)
+    if n and type(attention_mask) is list and attention_mask.count(1) == n:
+        return list(range(n)), [first_segment + 1] * n, first_segment + 1     # one unbroken run
     positions, segments = [], []
     seg, cur, pos = first_segment, 0, 0
     for m in attention_mask:
@@ -156,7 +163,11 @@ def pad_example(example: Mapping[str, Sequence[Scalar]], *, max_length: int, pad
         raise ValueError("padding_side must be either 'left' or 'right'.")
     if "input_ids" not in example:
         raise ValueError("example must contain input_ids.")
-    cols = {k: _column(v, k) for k, v in example.items()}
+    return _pad_columns({k: _column(v, k) for k, v in example.items()}, max_length, pad_token_id, padding_side)
+
+
+def _pad_columns(cols: Mapping[str, list], max_length: int, pad_token_id: int, padding_side: str) -> PackedExample:
+    """``pad_example`` on columns that are already typed lists."""
     n = len(cols["input_ids"])
     if n > max_length:
         raise ValueError(f"Packed sequence length {n} exceeds max_length {max_length}.")
@@ -186,7 +197,9 @@ def _join_row(row: Sequence[PackedExample], fields: Sequence[str], max_length: i
     if not keep_positions:
         joined["position_ids"] = positions
     joined["segment_ids"] = segments
-    return pad_example(joined, max_length=max_length, pad_token_id=pad_token_id, padding_side=padding_side)
+    if padding_side not in ("left", "right"):
+        raise ValueError("padding_side must be either 'left' or 'right'.")
+    return _pad_columns(joined, max_length, pad_token_id, padding_side)
 
 
 def _windows(items: Iterable[Any], size: int) -> Iterator[list[Any]]:

@@ -86,3 +86,17 @@ def test_named_configurations_generate_rows_of_the_named_shape():
             grid = data["attention_end"] > np.arange(seq)[None, :]
             # no next-token target inside a bidirectional grid: only the masked codes carry weight there
             assert (data["prediction_weights"][grid & ~masked] == 0).all()
+
+
+def test_data_path_benchmark_reports_both_arms_and_checks_their_outputs():
+    from causal_trainer_dev_b200.benchmarks import data_bench
+
+    docs, tokens = data_bench._documents(300, 512, seed=2)
+    for case in (data_bench.packing_case, data_bench.streaming_case):
+        result = case(docs, tokens, 512)
+        assert result["mtokens_per_s"] > 0 and result["rows"] > 0
+        if "reference" in result:                    # the reference package is not installed beside the repository
+            assert result["reference"].startswith("unavailable")
+        else:                                        # same input through the reference's own functions
+            assert result.get("identical_rows", True) and result.get("identical_last_batch_digest", True)
+            assert result["reference_mtokens_per_s"] > 0
