@@ -1,13 +1,15 @@
-"""Host-side data path: throughput of packing and of the streaming batch grouper, on the CPU.
+"""Host-side data path: throughput of packing, of the streaming batch grouper and of the
+materialised batch iterator, on the CPU.
 
     python -m causal_trainer_dev_b200.benchmarks.data_bench [--documents 20000] [--seq_len 4096]
 
-Both cases run this package's implementation and, when the reference's pure-Python package is
+Every case runs this package's implementation and, when the reference's pure-Python package is
 importable from ``baseline/_ref`` (installed without its JAX dependencies; its ``data`` modules
 need none of them), the reference's own functions on the same input, unmodified, through their
 public entry points (``causal_trainer.data.packing.pack_examples``,
-``causal_trainer.data.streaming_batching.iter_streaming_global_batches``).  The outputs are
-compared (identical rows; identical digest of the last global batch) before a ratio is reported.
+``causal_trainer.data.streaming_batching.iter_streaming_global_batches``,
+``causal_trainer.data.batching.iter_global_batches``).  The outputs are compared (identical rows;
+identical digest of the last global batch; identical first batch) before a ratio is reported.
 One JSON line per case.
 """
 from __future__ import annotations
@@ -97,13 +99,47 @@ def streaming_case(docs: list[dict], tokens: int, seq_len: int) -> dict:
     return out
 
 
+def _epoch(mod, dataset, rows_per_batch: int):
+    plan = mod.BatchPlan.create(len(dataset), rows_per_batch, 1, 1.0, 0)
+    first, count = None, 0
+    for batch in mod.iter_global_batches(dataset, plan, assistant_only_loss=False, shuffle=True, seed=7):
+        first = batch if first is None else first
+        count += 1
+    return count, first
+
+
+def batching_case(docs: list[dict], tokens: int, seq_len: int) -> dict:
+    """One shuffled epoch of global batches over the packed rows.  The reference collates rows that
+    are Python lists (what its dataset hands out); this package keeps the packed rows as typed
+    columns (``data.pipeline.PackedArrayDataset``) and gathers them by index."""
+    from ..data import batching, packing
+    from ..data.pipeline import PackedArrayDataset
+
+    rows = packing.pack_examples(docs, max_length=seq_len, pad_token_id=0, packing_batch_size=1000)
+    rows = rows[: len(rows) // 32 * 32]
+    columns = {k: np.asarray([r[k] for r in rows], dtype=np.int32) for k in rows[0]}
+    (count, first), dt = _timed(lambda: _epoch(batching, PackedArrayDataset(columns), 32))
+    out = {"case": "iter_global_batches", "rows": len(rows), "global_batches": count, "seconds": round(dt, 3),
+           "mtokens_per_s": round(len(rows) * seq_len / dt / 1e6, 3)}
+    ref = _reference("batching")
+    if ref is None:
+        out["reference"] = "unavailable (baseline/_ref is not installed)"
+        return out
+    (ref_count, ref_first), ref_dt = _timed(lambda: _epoch(ref, rows, 32))
+    same = ref_count == count and sorted(ref_first) == sorted(first) and all(
+        np.array_equal(ref_first[k], first[k]) and ref_first[k].dtype == first[k].dtype for k in first)
+    out.update(reference_seconds=round(ref_dt, 3), reference_mtokens_per_s=round(len(rows) * seq_len / ref_dt / 1e6, 3),
+               identical_first_batch=bool(same), speedup_over_reference=round(ref_dt / dt, 2))
+    return out
+
+
 def main(argv: list[str] | None = None) -> int:
     p = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     p.add_argument("--documents", type=int, default=20000)
     p.add_argument("--seq_len", type=int, default=4096)
     a = p.parse_args(argv)
     docs, tokens = _documents(a.documents, a.seq_len)
-    for case in (packing_case, streaming_case):
+    for case in (packing_case, streaming_case, batching_case):
         print(json.dumps(case(docs, tokens, a.seq_len)), flush=True)
     return 0
 

@@ -92,11 +92,12 @@ def test_data_path_benchmark_reports_both_arms_and_checks_their_outputs():
     from causal_trainer_dev_b200.benchmarks import data_bench
 
     docs, tokens = data_bench._documents(300, 512, seed=2)
-    for case in (data_bench.packing_case, data_bench.streaming_case):
+    for case in (data_bench.packing_case, data_bench.streaming_case, data_bench.batching_case):
         result = case(docs, tokens, 512)
         assert result["mtokens_per_s"] > 0 and result["rows"] > 0
         if "reference" in result:                    # the reference package is not installed beside the repository
             assert result["reference"].startswith("unavailable")
         else:                                        # same input through the reference's own functions
             assert result.get("identical_rows", True) and result.get("identical_last_batch_digest", True)
+            assert result.get("identical_first_batch", True)
             assert result["reference_mtokens_per_s"] > 0
