@@ -58,13 +58,13 @@ class GridFinder:
         self.tokenizer = tokenizer
         self.code_table = code_table
         self.start_id, self.end_id = start_id, end_id
-        self._text: dict[tuple[int, ...], str] = {}
+        self._text: dict[bytes, str] = {}
 
     def _decoded(self, ids: np.ndarray) -> str:
-        key = tuple(int(i) for i in ids)
+        key = ids.tobytes()                      # the ids' bytes: one C call instead of a tuple of Python ints
         text = self._text.get(key)
         if text is None:
-            text = self._text[key] = self.tokenizer.decode(list(key))
+            text = self._text[key] = self.tokenizer.decode([int(i) for i in ids])
         return text
 
     def is_code(self, tokens: np.ndarray) -> np.ndarray:
