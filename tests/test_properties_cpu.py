@@ -152,3 +152,41 @@ def test_schedule_warms_up_linearly_then_decays_monotonically_to_the_end_value(n
     else:
         assert all(a >= b - 1e-12 for a, b in zip(tail, tail[1:]))
         assert values[total] == pytest.approx(end, abs=1e-12) and values[total + 2] == pytest.approx(end, abs=1e-12)
+
+
+# ------------------------------------------------------------------ chunked loss
+@settings(max_examples=30, deadline=None)
+@given(budget=st.integers(1, 40), seed=st.integers(0, 50), use_weights=st.booleans())
+def test_chunked_loss_is_independent_of_the_chunk_size_and_matches_full_logits(budget, seed, use_weights):
+    """Equivalence of execution modes: any token budget gives the sums (and gradients) of the plain
+    full-logits cross-entropy over the shifted, segment-aware targets."""
+    import torch.nn.functional as F
+
+    from causal_trainer_dev_b200.training.losses import chunked_causal_lm_loss
+
+    g = torch.Generator().manual_seed(seed)
+    b, s, d, vocab = 2, 12, 8, 17
+    hidden = torch.randn(b, s, d, generator=g, dtype=torch.float64).requires_grad_()
+    head = torch.randn(vocab, d, generator=g, dtype=torch.float64).requires_grad_()
+    ids = torch.randint(1, vocab, (b, s), generator=g)
+    mask = torch.ones(b, s, dtype=torch.int64)
+    mask[1, 9:] = 0
+    seg = torch.ones(b, s, dtype=torch.int64)
+    seg[0, 5:] = 2
+    seg[1, 9:] = 0
+    weights = torch.rand(b, s, generator=g, dtype=torch.float64) if use_weights else None
+    nll, count = chunked_causal_lm_loss(hidden, head, ids, mask, seg, loss_weights=weights, token_budget=budget)
+    # the definition: position i predicts token i + 1 when both are attended tokens of one document
+    w = ((seg[:, :-1] == seg[:, 1:]) & (seg[:, 1:] != 0) & (mask[:, :-1] == 1) & (mask[:, 1:] == 1)).double()
+    if weights is not None:
+        w = w * weights[:, 1:]
+    logits = hidden[:, :-1] @ head.t()
+    per_token = F.cross_entropy(logits.reshape(-1, vocab), ids[:, 1:].reshape(-1), reduction="none").reshape(b, s - 1)
+    want_nll, want_count = (per_token * w).sum(), w.sum()
+    # the loss is accumulated in fp32 whatever the inputs are
+    assert float(count.detach()) == pytest.approx(float(want_count), rel=1e-5)
+    assert float(nll.detach()) == pytest.approx(float(want_nll.detach()), rel=1e-5)
+    got = torch.autograd.grad(nll, (hidden, head))
+    ref = torch.autograd.grad(want_nll, (hidden, head))
+    for a, c in zip(got, ref):
+        torch.testing.assert_close(a.double(), c, rtol=1e-4, atol=1e-5)
